@@ -1,0 +1,135 @@
+/*
+ * yscv_cuda.h -- C ABI of the B200 (sm_100a) quantized-matmul library.
+ *
+ * Drop-in boundary for the quantized-matmul hot path of enthropy7/YSCV: the
+ * entry points below are what an FFI crate inside yscv-kernels / yscv-onnx
+ * would bind in place of the CPU kernels it calls today. Each declaration
+ * cites the reference interface it replaces (paths relative to the reference
+ * project root).
+ *
+ * Conventions
+ *  - Plain pointers and sizes only. Functions return 0 on success and a
+ *    negative yscv_cuda_status otherwise; yscv_cuda_last_error() returns a
+ *    thread-local message for the last failure on the calling thread.
+ *  - "host" entry points take host pointers with the reference's exact slice
+ *    layouts, copy in, run on the GPU, copy out and synchronise: they are the
+ *    literal drop-ins for the reference's free functions.
+ *  - "_dev" entry points take device pointers, enqueue on the context's stream
+ *    and return without synchronising: weights stay resident in HBM, which is
+ *    how a runner that uploads weights once at load time uses the library.
+ *  - There is no CPU fallback anywhere. Shapes a kernel cannot take are
+ *    rejected with YSCV_CUDA_ERR_UNSUPPORTED.
+ *  - A context owns one CUDA stream (or borrows the caller's); calls on one
+ *    context are serialised by the caller. Handles are immutable after
+ *    creation and may be shared between contexts of the same device.
+ *
+ * Layouts (identical to the reference's)
+ *  - packed int4 weights: [N rows][K/2 bytes], one row per output channel,
+ *    two's-complement nibbles, low nibble = even k
+ *    (crates/yscv-kernels/src/ops/int4_matmul.rs:12-18, 29-40).
+ *  - scales: [N][K/group_size] f32, no zero-point array (symmetric).
+ *  - int8 GEMM: A [M,K] row-major i8, B [K,N] row-major i8, out [M,N] i32
+ *    (crates/yscv-kernels/src/ops/int8_matmul.rs:195-208).
+ */
+#ifndef YSCV_CUDA_H
+#define YSCV_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    YSCV_CUDA_OK = 0,
+    YSCV_CUDA_ERR_BAD_ARG = -1,     /* the reference would debug_assert! */
+    YSCV_CUDA_ERR_CUDA = -2,        /* a CUDA runtime / driver call failed */
+    YSCV_CUDA_ERR_UNSUPPORTED = -3, /* no kernel for this shape; no CPU fallback */
+    YSCV_CUDA_ERR_TIMEOUT = -4,     /* a bounded device-side wait ran out */
+    YSCV_CUDA_ERR_NO_DEVICE = -5    /* no sm_100 device visible */
+} yscv_cuda_status;
+
+typedef struct yscv_cuda_ctx yscv_cuda_ctx;
+typedef struct yscv_cuda_int4_weight yscv_cuda_int4_weight;
+typedef struct yscv_cuda_i8b yscv_cuda_i8b;
+
+/* ---- context ------------------------------------------------------------ */
+
+/* Replaces the reference's CPU-feature probe (crates/yscv-cpu/src/lib.rs:74-154):
+ * checks that `device` is an sm_100 part and creates a stream on it. */
+int yscv_cuda_ctx_create(int device, yscv_cuda_ctx **out);
+/* Same, but enqueues on a stream the caller owns (cudaStream_t passed as void*). */
+int yscv_cuda_ctx_create_on_stream(int device, void *cuda_stream, yscv_cuda_ctx **out);
+void yscv_cuda_ctx_destroy(yscv_cuda_ctx *ctx);
+int yscv_cuda_ctx_synchronize(yscv_cuda_ctx *ctx);
+/* Reads and clears the device-side status word that bounded waits inside the
+ * kernels set when they give up (0 = none). */
+int yscv_cuda_ctx_device_status(yscv_cuda_ctx *ctx, int *status);
+const char *yscv_cuda_last_error(void);
+/* Counterpart of runtime_dispatch_report() (crates/yscv-kernels/src/core.rs:30-137):
+ * names the kernel variant the last call on this context dispatched to. */
+const char *yscv_cuda_last_kernel(const yscv_cuda_ctx *ctx);
+/* Number of kernels this library has launched on the context so far. */
+uint64_t yscv_cuda_ctx_launch_count(const yscv_cuda_ctx *ctx);
+/* Per-kernel timing, the counterpart of YSCV_RUNNER_PROFILE
+ * (crates/yscv-onnx/src/runner/profile.rs:1-120): while enabled, the dominant
+ * kernel of every call is bracketed by CUDA events on the context's stream.
+ * _read synchronises, returns the number of bracketed launches and their summed
+ * device time, and resets the counters. */
+int yscv_cuda_ctx_profile_enable(yscv_cuda_ctx *ctx, int enable);
+int yscv_cuda_ctx_profile_read(yscv_cuda_ctx *ctx, uint64_t *launches, double *total_ms);
+
+/* ---- int4 block-quantized GEMV / GEMM: host drop-ins --------------------- */
+
+/* packed_int4_gemv_dispatch (crates/yscv-kernels/src/ops/int4_matmul.rs:310-377) */
+int yscv_cuda_packed_int4_gemv(yscv_cuda_ctx *ctx, const uint8_t *weight_packed,
+                               const float *scales, const float *activation,
+                               float *output, size_t m_w, size_t k, size_t group_size);
+
+/* packed_int4_gemm_dispatch (crates/yscv-kernels/src/ops/int4_matmul.rs:548-605) */
+int yscv_cuda_packed_int4_gemm(yscv_cuda_ctx *ctx, const uint8_t *weight_packed,
+                               const float *scales, const float *activation,
+                               float *output, size_t m, size_t n, size_t k,
+                               size_t group_size);
+
+/* pack_int4_symmetric_per_group (crates/yscv-kernels/src/ops/int4_matmul.rs:611-646).
+ * `packed` (m_w*k/2 bytes) and `scales` (m_w*k/group_size floats) are caller-allocated. */
+int yscv_cuda_pack_int4_symmetric_per_group(yscv_cuda_ctx *ctx, const float *weights,
+                                            size_t m_w, size_t k, size_t group_size,
+                                            uint8_t *packed, float *scales);
+
+/* ---- int4: device-resident forms ---------------------------------------- */
+
+/* PackedInt4Weight (crates/yscv-onnx/src/quantize/packed_int4.rs:28-39) resident in
+ * HBM. _upload copies host slices; _wrap borrows device memory the caller keeps alive. */
+int yscv_cuda_int4_weight_upload(yscv_cuda_ctx *ctx, const uint8_t *packed,
+                                 const float *scales, size_t m_w, size_t k,
+                                 size_t group_size, yscv_cuda_int4_weight **out);
+int yscv_cuda_int4_weight_wrap(const uint8_t *d_packed, const float *d_scales, size_t m_w,
+                               size_t k, size_t group_size, yscv_cuda_int4_weight **out);
+void yscv_cuda_int4_weight_free(yscv_cuda_int4_weight *w);
+
+/* The int4 branch of exec_matmul (crates/yscv-onnx/src/runner/linear.rs:223-278) on
+ * device memory: d_activation [m,k] f32 -> d_output [m,n] f32. One pass over the
+ * weights for any m (the reference re-reads them m times when m < 8). m <= 16 takes
+ * the bandwidth-bound decode kernel, larger m the tensor-core prefill GEMM. */
+int yscv_cuda_int4_matmul_dev(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
+                              const float *d_activation, float *d_output, size_t m);
+
+/* The same operator as a runner calls it: weights resident (uploaded once at load
+ * time, like the reference's side-table built by quantize_matmul_weights_int4_packed,
+ * crates/yscv-onnx/src/quantize/packed_int4.rs:50-128), activation and output in host
+ * memory: copies activation [m,k] in, runs, copies output [m,n] out, synchronises. */
+int yscv_cuda_int4_matmul(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
+                          const float *activation, float *output, size_t m);
+
+/* pack_int4_symmetric_per_group on device memory: d_weights [m_w,k] f32. */
+int yscv_cuda_pack_int4_dev(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w,
+                            size_t k, size_t group_size, uint8_t *d_packed,
+                            float *d_scales);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

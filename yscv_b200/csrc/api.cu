@@ -1,0 +1,363 @@
+// C ABI of the library (see include/yscv_cuda.h): argument validation, host
+// staging for the drop-in entry points, dispatch to the kernels.
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace yscv {
+
+std::string &last_error() {
+    static thread_local std::string s;
+    return s;
+}
+
+int fail(int status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    last_error() = buf;
+    return status;
+}
+
+int DeviceBuffer::reserve(size_t want) {
+    if (want <= bytes && ptr) return YSCV_CUDA_OK;
+    if (ptr) {
+        YSCV_CUDA_TRY(cudaFree(ptr));
+        ptr = nullptr;
+        bytes = 0;
+    }
+    size_t sz = want < 256 ? 256 : want;
+    YSCV_CUDA_TRY(cudaMalloc(&ptr, sz));
+    bytes = sz;
+    return YSCV_CUDA_OK;
+}
+
+void DeviceBuffer::release() {
+    if (ptr) cudaFree(ptr);
+    ptr = nullptr;
+    bytes = 0;
+}
+
+static int check_int4_shape(size_t n, size_t k, size_t gs) {
+    if (gs == 0 || (gs & 1)) return fail(YSCV_CUDA_ERR_BAD_ARG, "group_size must be even and > 0, got %zu", gs);
+    if (k == 0 || k % gs != 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "k=%zu must be a positive multiple of group_size=%zu", k, gs);
+    if (n == 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "weight has no rows");
+    if (n >= (1u << 30) || k >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "dimension too large");
+    return YSCV_CUDA_OK;
+}
+
+// device-pointer int4 matmul, any m
+static int int4_matmul_dev(yscv_cuda_ctx *ctx, const uint8_t *d_packed, const float *d_scales,
+                           size_t n, size_t k, size_t gs, const float *d_act, float *d_out,
+                           size_t m) {
+    int rc = check_int4_shape(n, k, gs);
+    if (rc) return rc;
+    if (m == 0) return YSCV_CUDA_OK;
+    for (size_t m0 = 0; m0 < m; m0 += 16) {
+        const size_t mc = m - m0 < 16 ? m - m0 : 16;
+        const float *a = d_act + m0 * k;
+        float *o = d_out + m0 * n;
+        if (int4_gemv_fast_supported(mc, n, k, gs)) {
+            rc = ctx->scratch.reserve(int4_gemv_scratch_bytes(16, k));
+            if (rc) return rc;
+            rc = int4_gemv_fast(ctx, d_packed, d_scales, a, o, mc, n, k, ctx->scratch.ptr);
+        } else {
+            rc = int4_gemv_generic(ctx, d_packed, d_scales, a, o, mc, n, k, gs);
+        }
+        if (rc) return rc;
+    }
+    return YSCV_CUDA_OK;
+}
+
+}  // namespace yscv
+
+void yscv_cuda_ctx::prof_begin() {
+    if (!profiling) return;
+    if (prof_used == prof_events.size()) {
+        cudaEvent_t a, b;
+        if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+        prof_events.emplace_back(a, b);
+    }
+    cudaEventRecord(prof_events[prof_used].first, stream);
+}
+
+void yscv_cuda_ctx::prof_end() {
+    if (!profiling || prof_used >= prof_events.size()) return;
+    cudaEventRecord(prof_events[prof_used].second, stream);
+    prof_used++;
+}
+
+using namespace yscv;
+
+extern "C" {
+
+const char *yscv_cuda_last_error(void) { return last_error().c_str(); }
+
+static int ctx_create_impl(int device, cudaStream_t stream, bool borrow, yscv_cuda_ctx **out) {
+    if (!out) return fail(YSCV_CUDA_ERR_BAD_ARG, "out is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(YSCV_CUDA_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    if (device < 0 || device >= count) return fail(YSCV_CUDA_ERR_BAD_ARG, "device %d out of range (%d visible)", device, count);
+    cudaDeviceProp prop;
+    YSCV_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(YSCV_CUDA_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
+                    device, prop.major, prop.minor);
+    YSCV_CUDA_TRY(cudaSetDevice(device));
+    yscv_cuda_ctx *ctx = new yscv_cuda_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (borrow) {
+        ctx->stream = stream;
+        ctx->owns_stream = false;
+    } else {
+        cudaError_t se = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+        if (se != cudaSuccess) {
+            delete ctx;
+            return fail(YSCV_CUDA_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(se));
+        }
+        ctx->owns_stream = true;
+    }
+    cudaError_t me = cudaMalloc(&ctx->d_status, sizeof(int));
+    if (me == cudaSuccess) me = cudaMemset(ctx->d_status, 0, sizeof(int));
+    if (me != cudaSuccess) {
+        if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return fail(YSCV_CUDA_ERR_CUDA, "status word: %s", cudaGetErrorString(me));
+    }
+    *out = ctx;
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_ctx_create(int device, yscv_cuda_ctx **out) {
+    return ctx_create_impl(device, nullptr, false, out);
+}
+
+int yscv_cuda_ctx_create_on_stream(int device, void *cuda_stream, yscv_cuda_ctx **out) {
+    return ctx_create_impl(device, reinterpret_cast<cudaStream_t>(cuda_stream), true, out);
+}
+
+void yscv_cuda_ctx_destroy(yscv_cuda_ctx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    ctx->in0.release();
+    ctx->in1.release();
+    ctx->in2.release();
+    ctx->out0.release();
+    ctx->out1.release();
+    ctx->scratch.release();
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    for (auto &ev : ctx->prof_events) {
+        cudaEventDestroy(ev.first);
+        cudaEventDestroy(ev.second);
+    }
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+int yscv_cuda_ctx_synchronize(yscv_cuda_ctx *ctx) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_ctx_device_status(yscv_cuda_ctx *ctx, int *status) {
+    if (!ctx || !status) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    YSCV_CUDA_TRY(cudaMemcpyAsync(status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    YSCV_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_ctx_profile_enable(yscv_cuda_ctx *ctx, int enable) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    ctx->profiling = enable != 0;
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_ctx_profile_read(yscv_cuda_ctx *ctx, uint64_t *launches, double *total_ms) {
+    if (!ctx || !launches || !total_ms) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    double sum = 0.0;
+    for (size_t i = 0; i < ctx->prof_used; ++i) {
+        float ms = 0.0f;
+        YSCV_CUDA_TRY(cudaEventElapsedTime(&ms, ctx->prof_events[i].first, ctx->prof_events[i].second));
+        sum += ms;
+    }
+    *launches = ctx->prof_used;
+    *total_ms = sum;
+    ctx->prof_used = 0;
+    return YSCV_CUDA_OK;
+}
+
+const char *yscv_cuda_last_kernel(const yscv_cuda_ctx *ctx) { return ctx ? ctx->last_kernel : "none"; }
+
+uint64_t yscv_cuda_ctx_launch_count(const yscv_cuda_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+/* ---- int4 host drop-ins ---------------------------------------------------- */
+
+int yscv_cuda_packed_int4_gemm(yscv_cuda_ctx *ctx, const uint8_t *weight_packed,
+                               const float *scales, const float *activation, float *output,
+                               size_t m, size_t n, size_t k, size_t group_size) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    if (!weight_packed || !scales || !activation || !output)
+        return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    int rc = check_int4_shape(n, k, group_size);
+    if (rc) return rc;
+    if (m == 0) return YSCV_CUDA_OK;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    const size_t wb = n * k / 2, sb = n * (k / group_size) * sizeof(float);
+    const size_t ab = m * k * sizeof(float), ob = m * n * sizeof(float);
+    if ((rc = ctx->in0.reserve(wb)) || (rc = ctx->in1.reserve(sb)) || (rc = ctx->in2.reserve(ab)) ||
+        (rc = ctx->out0.reserve(ob)))
+        return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in0.ptr, weight_packed, wb, cudaMemcpyHostToDevice, ctx->stream));
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in1.ptr, scales, sb, cudaMemcpyHostToDevice, ctx->stream));
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in2.ptr, activation, ab, cudaMemcpyHostToDevice, ctx->stream));
+    rc = int4_matmul_dev(ctx, (const uint8_t *)ctx->in0.ptr, (const float *)ctx->in1.ptr, n, k,
+                         group_size, (const float *)ctx->in2.ptr, (float *)ctx->out0.ptr, m);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(output, ctx->out0.ptr, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_packed_int4_gemv(yscv_cuda_ctx *ctx, const uint8_t *weight_packed,
+                               const float *scales, const float *activation, float *output,
+                               size_t m_w, size_t k, size_t group_size) {
+    return yscv_cuda_packed_int4_gemm(ctx, weight_packed, scales, activation, output, 1, m_w, k,
+                                      group_size);
+}
+
+int yscv_cuda_pack_int4_dev(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w, size_t k,
+                            size_t group_size, uint8_t *d_packed, float *d_scales) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    if (!d_weights || !d_packed || !d_scales) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    int rc = check_int4_shape(m_w, k, group_size);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    return pack_int4(ctx, d_weights, m_w, k, group_size, d_packed, d_scales);
+}
+
+int yscv_cuda_pack_int4_symmetric_per_group(yscv_cuda_ctx *ctx, const float *weights, size_t m_w,
+                                            size_t k, size_t group_size, uint8_t *packed,
+                                            float *scales) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    if (!weights || !packed || !scales) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    int rc = check_int4_shape(m_w, k, group_size);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    const size_t wb = m_w * k * sizeof(float), pb = m_w * k / 2;
+    const size_t sb = m_w * (k / group_size) * sizeof(float);
+    if ((rc = ctx->in0.reserve(wb)) || (rc = ctx->out0.reserve(pb)) || (rc = ctx->out1.reserve(sb)))
+        return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in0.ptr, weights, wb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = pack_int4(ctx, (const float *)ctx->in0.ptr, m_w, k, group_size, (uint8_t *)ctx->out0.ptr,
+                   (float *)ctx->out1.ptr);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(packed, ctx->out0.ptr, pb, cudaMemcpyDeviceToHost, ctx->stream));
+    YSCV_CUDA_TRY(cudaMemcpyAsync(scales, ctx->out1.ptr, sb, cudaMemcpyDeviceToHost, ctx->stream));
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YSCV_CUDA_OK;
+}
+
+/* ---- int4 device-resident forms -------------------------------------------- */
+
+int yscv_cuda_int4_weight_upload(yscv_cuda_ctx *ctx, const uint8_t *packed, const float *scales,
+                                 size_t m_w, size_t k, size_t group_size,
+                                 yscv_cuda_int4_weight **out) {
+    if (!ctx || !out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    *out = nullptr;
+    if (!packed || !scales) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    int rc = check_int4_shape(m_w, k, group_size);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    const size_t wb = m_w * k / 2, sb = m_w * (k / group_size) * sizeof(float);
+    void *dp = nullptr, *ds = nullptr;
+    YSCV_CUDA_TRY(cudaMalloc(&dp, wb));
+    cudaError_t e = cudaMalloc(&ds, sb);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dp, packed, wb, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ds, scales, sb, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(dp);
+        if (ds) cudaFree(ds);
+        return fail(YSCV_CUDA_ERR_CUDA, "int4 weight upload: %s", cudaGetErrorString(e));
+    }
+    auto *w = new yscv_cuda_int4_weight();
+    w->d_packed = (const uint8_t *)dp;
+    w->d_scales = (const float *)ds;
+    w->m_w = m_w;
+    w->k = k;
+    w->group_size = group_size;
+    w->owns = true;
+    w->device = ctx->device;
+    *out = w;
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_int4_weight_wrap(const uint8_t *d_packed, const float *d_scales, size_t m_w, size_t k,
+                               size_t group_size, yscv_cuda_int4_weight **out) {
+    if (!out) return fail(YSCV_CUDA_ERR_BAD_ARG, "out is null");
+    *out = nullptr;
+    if (!d_packed || !d_scales) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    int rc = check_int4_shape(m_w, k, group_size);
+    if (rc) return rc;
+    auto *w = new yscv_cuda_int4_weight();
+    w->d_packed = d_packed;
+    w->d_scales = d_scales;
+    w->m_w = m_w;
+    w->k = k;
+    w->group_size = group_size;
+    w->owns = false;
+    w->device = -1;
+    *out = w;
+    return YSCV_CUDA_OK;
+}
+
+void yscv_cuda_int4_weight_free(yscv_cuda_int4_weight *w) {
+    if (!w) return;
+    if (w->owns) {
+        cudaSetDevice(w->device);
+        cudaFree(const_cast<uint8_t *>(w->d_packed));
+        cudaFree(const_cast<float *>(w->d_scales));
+    }
+    delete w;
+}
+
+int yscv_cuda_int4_matmul_dev(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
+                              const float *d_activation, float *d_output, size_t m) {
+    if (!ctx || !w) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (!d_activation || !d_output) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    return int4_matmul_dev(ctx, w->d_packed, w->d_scales, w->m_w, w->k, w->group_size, d_activation,
+                           d_output, m);
+}
+
+int yscv_cuda_int4_matmul(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
+                          const float *activation, float *output, size_t m) {
+    if (!ctx || !w) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (!activation || !output) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (m == 0) return YSCV_CUDA_OK;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    const size_t ab = m * w->k * sizeof(float), ob = m * w->m_w * sizeof(float);
+    int rc;
+    if ((rc = ctx->in2.reserve(ab)) || (rc = ctx->out0.reserve(ob))) return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in2.ptr, activation, ab, cudaMemcpyHostToDevice, ctx->stream));
+    rc = int4_matmul_dev(ctx, w->d_packed, w->d_scales, w->m_w, w->k, w->group_size,
+                         (const float *)ctx->in2.ptr, (float *)ctx->out0.ptr, m);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(output, ctx->out0.ptr, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YSCV_CUDA_OK;
+}
+
+}  // extern "C"

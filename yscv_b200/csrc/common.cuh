@@ -1,0 +1,72 @@
+// Internal definitions shared by the kernels and the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/yscv_cuda.h"
+
+namespace yscv {
+
+// Thread-local error text behind yscv_cuda_last_error().
+std::string &last_error();
+int fail(int status, const char *fmt, ...);
+
+#define YSCV_CUDA_TRY(expr)                                                         \
+    do {                                                                            \
+        cudaError_t _e = (expr);                                                    \
+        if (_e != cudaSuccess)                                                      \
+            return ::yscv::fail(YSCV_CUDA_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, \
+                                cudaGetErrorString(_e), __FILE__, __LINE__);        \
+    } while (0)
+
+// Grow-only device buffer owned by a context.
+struct DeviceBuffer {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    int reserve(size_t want);
+    void release();
+};
+
+}  // namespace yscv
+
+// Device status codes written by bounded waits inside kernels.
+enum : int {
+    YSCV_DEV_OK = 0,
+    YSCV_DEV_MBARRIER_TIMEOUT = 1,
+    YSCV_DEV_FLAG_TIMEOUT = 2,
+};
+
+struct yscv_cuda_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int *d_status = nullptr;   // device status word
+    uint64_t launches = 0;
+    const char *last_kernel = "none";
+    // optional per-kernel event timing (yscv_cuda_ctx_profile_*)
+    bool profiling = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;
+    size_t prof_used = 0;
+    void prof_begin();
+    void prof_end();
+    // staging for the host-pointer entry points
+    yscv::DeviceBuffer in0, in1, in2, out0, out1;
+    // scratch for kernels that need global memory beyond their operands
+    yscv::DeviceBuffer scratch;
+};
+
+struct yscv_cuda_int4_weight {
+    const uint8_t *d_packed = nullptr;
+    const float *d_scales = nullptr;
+    size_t m_w = 0, k = 0, group_size = 0;
+    bool owns = false;
+    int device = 0;
+};

@@ -1,0 +1,211 @@
+"""ctypes binding of include/yscv_cuda.h.
+
+Every call goes through the C ABI of ``libyscv_cuda.so``. Loading fails loudly
+when the library has not been built; nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+_LIB = None
+
+
+class YscvCudaError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"yscv_cuda status {status}: {message}")
+        self.status = status
+
+
+def library_path() -> Path:
+    return Path(__file__).resolve().parent / "libyscv_cuda.so"
+
+
+_u8p = C.POINTER(C.c_uint8)
+_i8p = C.POINTER(C.c_int8)
+_f32p = C.POINTER(C.c_float)
+_i32p = C.POINTER(C.c_int32)
+_vp = C.c_void_p
+_sz = C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/yscv_cuda.h one to one
+SIGNATURES = {
+    "yscv_cuda_ctx_create": (C.c_int, [C.c_int, C.POINTER(_vp)]),
+    "yscv_cuda_ctx_create_on_stream": (C.c_int, [C.c_int, _vp, C.POINTER(_vp)]),
+    "yscv_cuda_ctx_destroy": (None, [_vp]),
+    "yscv_cuda_ctx_synchronize": (C.c_int, [_vp]),
+    "yscv_cuda_ctx_device_status": (C.c_int, [_vp, C.POINTER(C.c_int)]),
+    "yscv_cuda_last_error": (C.c_char_p, []),
+    "yscv_cuda_last_kernel": (C.c_char_p, [_vp]),
+    "yscv_cuda_ctx_launch_count": (C.c_uint64, [_vp]),
+    "yscv_cuda_ctx_profile_enable": (C.c_int, [_vp, C.c_int]),
+    "yscv_cuda_ctx_profile_read": (C.c_int, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
+    "yscv_cuda_int4_matmul": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
+    "yscv_cuda_packed_int4_gemv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
+    "yscv_cuda_packed_int4_gemm": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz]),
+    "yscv_cuda_pack_int4_symmetric_per_group": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _vp, _vp]),
+    "yscv_cuda_int4_weight_upload": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, C.POINTER(_vp)]),
+    "yscv_cuda_int4_weight_wrap": (C.c_int, [_vp, _vp, _sz, _sz, _sz, C.POINTER(_vp)]),
+    "yscv_cuda_int4_weight_free": (None, [_vp]),
+    "yscv_cuda_int4_matmul_dev": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
+    "yscv_cuda_pack_int4_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _vp, _vp]),
+}
+
+
+def load_library():
+    """dlopen libyscv_cuda.so and attach the prototypes. Raises if it is missing."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not path.exists():
+        raise FileNotFoundError(
+            f"{path} is missing: build it with `python -m yscv_b200.build` "
+            "(there is no CPU fallback)")
+    lib = C.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the header and the library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _LIB = lib
+    return lib
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise YscvCudaError(rc, load_library().yscv_cuda_last_error().decode())
+
+
+def _host(a: np.ndarray, dtype) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=dtype)
+    return a
+
+
+def _ptr(a) -> int:
+    """Address of a numpy array's data, or a raw device pointer passed as int."""
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data
+    return int(a)
+
+
+class Int4Weight:
+    """PackedInt4Weight resident in HBM (owning or wrapping device memory)."""
+
+    def __init__(self, handle: int, m_w: int, k: int, group_size: int):
+        self.handle = handle
+        self.m_w, self.k, self.group_size = m_w, k, group_size
+
+    def free(self):
+        if self.handle:
+            load_library().yscv_cuda_int4_weight_free(self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Context:
+    """One CUDA stream on one sm_100 device (yscv_cuda_ctx)."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self.lib = load_library()
+        h = _vp()
+        if stream is None:
+            _check(self.lib.yscv_cuda_ctx_create(device, C.byref(h)))
+        else:
+            _check(self.lib.yscv_cuda_ctx_create_on_stream(device, _vp(stream), C.byref(h)))
+        self.handle = h.value
+        self.device = device
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.yscv_cuda_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- bookkeeping -------------------------------------------------------
+    def synchronize(self):
+        _check(self.lib.yscv_cuda_ctx_synchronize(self.handle))
+
+    def device_status(self) -> int:
+        s = C.c_int(0)
+        _check(self.lib.yscv_cuda_ctx_device_status(self.handle, C.byref(s)))
+        return s.value
+
+    def last_kernel(self) -> str:
+        return self.lib.yscv_cuda_last_kernel(self.handle).decode()
+
+    def launch_count(self) -> int:
+        return int(self.lib.yscv_cuda_ctx_launch_count(self.handle))
+
+    def profile_enable(self, on: bool):
+        _check(self.lib.yscv_cuda_ctx_profile_enable(self.handle, int(on)))
+
+    def profile_read(self):
+        """(bracketed launches, summed device ms) since the last read."""
+        n, ms = C.c_uint64(0), C.c_double(0.0)
+        _check(self.lib.yscv_cuda_ctx_profile_read(self.handle, C.byref(n), C.byref(ms)))
+        return int(n.value), float(ms.value)
+
+    # -- int4, host drop-ins -------------------------------------------------
+    def packed_int4_gemv(self, weight_packed, scales, activation, m_w, k, group_size):
+        wp, sc, act = _host(weight_packed, np.uint8), _host(scales, np.float32), _host(activation, np.float32)
+        out = np.empty(m_w, dtype=np.float32)
+        _check(self.lib.yscv_cuda_packed_int4_gemv(self.handle, _ptr(wp), _ptr(sc), _ptr(act),
+                                                   _ptr(out), m_w, k, group_size))
+        return out
+
+    def packed_int4_gemm(self, weight_packed, scales, activation, m, n, k, group_size):
+        wp, sc, act = _host(weight_packed, np.uint8), _host(scales, np.float32), _host(activation, np.float32)
+        out = np.empty((m, n), dtype=np.float32)
+        _check(self.lib.yscv_cuda_packed_int4_gemm(self.handle, _ptr(wp), _ptr(sc), _ptr(act),
+                                                   _ptr(out), m, n, k, group_size))
+        return out
+
+    def pack_int4_symmetric_per_group(self, weights, m_w, k, group_size):
+        w = _host(weights, np.float32)
+        packed = np.empty(m_w * k // 2, dtype=np.uint8)
+        scales = np.empty(m_w * (k // max(group_size, 1)), dtype=np.float32)
+        _check(self.lib.yscv_cuda_pack_int4_symmetric_per_group(
+            self.handle, _ptr(w), m_w, k, group_size, _ptr(packed), _ptr(scales)))
+        return packed, scales
+
+    # -- int4, device-resident ------------------------------------------------
+    def int4_weight_upload(self, packed, scales, m_w, k, group_size) -> Int4Weight:
+        wp, sc = _host(packed, np.uint8), _host(scales, np.float32)
+        h = _vp()
+        _check(self.lib.yscv_cuda_int4_weight_upload(self.handle, _ptr(wp), _ptr(sc), m_w, k,
+                                                     group_size, C.byref(h)))
+        return Int4Weight(h.value, m_w, k, group_size)
+
+    def int4_weight_wrap(self, d_packed: int, d_scales: int, m_w, k, group_size) -> Int4Weight:
+        h = _vp()
+        _check(self.lib.yscv_cuda_int4_weight_wrap(_vp(d_packed), _vp(d_scales), m_w, k,
+                                                   group_size, C.byref(h)))
+        return Int4Weight(h.value, m_w, k, group_size)
+
+    def int4_matmul_dev(self, w: Int4Weight, d_activation: int, d_output: int, m: int):
+        _check(self.lib.yscv_cuda_int4_matmul_dev(self.handle, w.handle, _vp(d_activation),
+                                                  _vp(d_output), m))
+
+    def int4_matmul(self, w: Int4Weight, activation, m: int, out=None):
+        """Resident weights, host activation [m,k] -> host output [m,n]."""
+        act = _host(activation, np.float32)
+        if out is None:
+            out = np.empty((m, w.m_w), dtype=np.float32)
+        _check(self.lib.yscv_cuda_int4_matmul(self.handle, w.handle, _ptr(act), _ptr(out), m))
+        return out
+
+    def pack_int4_dev(self, d_weights: int, m_w, k, group_size, d_packed: int, d_scales: int):
+        _check(self.lib.yscv_cuda_pack_int4_dev(self.handle, _vp(d_weights), m_w, k, group_size,
+                                                _vp(d_packed), _vp(d_scales)))
