@@ -68,7 +68,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -79,9 +79,10 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) >= 6:
-                self.rows.append(parts)
+                self.rows.append([time.perf_counter()] + parts)
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
+        """Summary of the samples that arrived inside [t0, t1] (host clock)."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -89,13 +90,17 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        rows = [r[1:] for r in self.rows if t0 is None or t0 <= r[0] <= t1]
+        window = "timed region"
+        if not rows:
+            rows, window = [r[1:] for r in self.rows], "whole run (no sample landed in the timed region)"
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(self.rows)}
+                "samples": len(rows), "window": window}
 
 
 def dist_env():
@@ -147,7 +152,7 @@ def run_reference(args):
     oracle = oracle_lib.load()
     threads = os.cpu_count() or 1
     copies = cpu_workload(oracle)
-    steps = max(1, args.steps)
+    steps = max(1, min(args.steps, 40))  # bounded sample: a step is ~30 ms of CPU work
     gbs, ms, calls = time_cpu(oracle, copies, M_HEADLINE, threads, steps, max(1, min(args.warmup, 2)))
     line = {
         "impl": "reference",
@@ -241,15 +246,16 @@ def run_cuda(args):
 
     def timed(m, steps, warmup, sample_clocks=False):
         with torch.cuda.stream(stream):
+            sampler = ClockSampler(local) if sample_clocks else None
+            if sampler:
+                sampler.start()
             for _ in range(warmup):
                 one_step(m)
             stream.synchronize()
             barrier()
             torch.cuda.synchronize()
-            sampler = ClockSampler(local) if sample_clocks else None
-            if sampler:
-                sampler.start()
             l0 = ctx.launch_count()
+            t_begin = time.perf_counter()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             for _ in range(steps):
@@ -258,7 +264,7 @@ def run_cuda(args):
             torch.cuda.synchronize()
             barrier()
             ms = e0.elapsed_time(e1)
-            clocks = sampler.stop() if sampler else None
+            clocks = sampler.stop(t_begin, time.perf_counter()) if sampler else None
             launches = ctx.launch_count() - l0
         if world > 1:
             import torch.distributed as dist
@@ -267,14 +273,14 @@ def run_cuda(args):
             ms = float(t.item())
         return ms, launches, clocks
 
-    steps, warmup = args.steps, max(3, args.warmup)
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
     ms, launches, clocks = timed(M_HEADLINE, steps, warmup, sample_clocks=True)
     calls = steps * COPIES
     value = algorithmic_bytes(M_HEADLINE) * calls * world / (ms * 1e-3) / 1e9
 
     by_m = {}
     for m in M_EXTRA:
-        ms_m, _, _ = timed(m, max(5, steps // 4), 3)
+        ms_m, _, _ = timed(m, max(5, steps // 4), max(3, warmup // 4))
         c_m = max(5, steps // 4) * COPIES
         by_m[str(m)] = {"gbs": algorithmic_bytes(m) * c_m * world / (ms_m * 1e-3) / 1e9,
                         "us_per_call": ms_m * 1e3 / c_m}
@@ -283,7 +289,7 @@ def run_cuda(args):
     peak, peak_kind = load_peaks()
     ctx.profile_enable(True)
     with torch.cuda.stream(stream):
-        for _ in range(max(5, steps // 4)):
+        for _ in range(max(5, min(steps // 4, 100))):
             one_step(M_HEADLINE)
     n_prof, prof_ms = ctx.profile_read()
     ctx.profile_enable(False)
@@ -296,7 +302,7 @@ def run_cuda(args):
                 "us_per_launch": kern_us, "launches_timed": n_prof}
 
     # ---- e2e: the operator call a runner makes (resident weights, host activations) ----
-    e2e_steps = max(3, steps // 4)
+    e2e_steps = max(3, min(steps // 4, 100))
     host_act = torch.randn(M_HEADLINE, K).pin_memory()
     host_out = torch.empty(M_HEADLINE, N).pin_memory()
     a_np, o_np = host_act.numpy(), host_out.numpy()
@@ -369,8 +375,8 @@ NCU_DRAM_BYTES_PER_LAUNCH = None
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

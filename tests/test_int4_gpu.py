@@ -98,9 +98,7 @@ def config2(oracle):
 def test_config2_parity(ctx, oracle, config2, m):
     k, n, g, packed, scales, _ = config2
     act = synth.normal(1, 1, m * k, 1.0)
-    want = oracle.exec_matmul_int4(packed, scales, act, m, n, k, g, threads=8)
-    if m == 1:  # also against the single-threaded scalar oracle proper
-        assert np.array_equal(want[0], oracle.int4_gemv(packed, scales, act, n, k, g))
+    want = oracle.exec_matmul_int4(packed, scales, act, m, n, k, g)  # scalar oracle
     got = ctx.packed_int4_gemm(packed, scales, act, m, n, k, g)
     assert "fast" in ctx.last_kernel()
     assert rel_err(got, want) <= REL_TOL, rel_err(got, want)

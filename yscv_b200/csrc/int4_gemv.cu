@@ -116,26 +116,70 @@ int4_gemv_generic_kernel(const uint8_t *__restrict__ wq, const float *__restrict
 // ---------------------------------------------------------------------------
 //
 // For activation row m and group G (32 consecutive k):
-//   e     : max|a| < 2^e
+//   e      : max|a| < 2^e
 //   afix_j = rint(a_j * 2^(21-e))                 |afix| <= 2^21
-//   afix  = d2*65536 + d1*256 + d0                d0,d1 in [-128,127], |d2| <= 32
-// Output layout (uint4 = 4 words):
-//   digits[((G*2 + h)*MP + m)*4 + t]  h=0: {d2.b0, d2.b1, d1.b0, d1.b1}
-//                                     h=1: {d0.b0, d0.b1, 0, 0}
-//     b0 = digits of k = 8t+{0,2,4,6}, b1 = digits of k = 8t+{1,3,5,7}
-//     (the B fragment of mma.m16n8k32 for column m, thread-in-quad t)
-//   meta[G*MP + m] = { 2^(e-21) as float, 8 * sum_j afix_j as int }
-// Rows m >= M (padding up to MP) are written as zeros.
+//   afix   = d2*65536 + d1*256 + d0               d0,d1 in [-128,127], |d2| <= 32
+//   as     = 2^(e-21),  corr = 8 * sum_j afix_j   (undoes the +8 bias of the nibbles)
+// A digit plane of one (m, G) is stored as the B fragment of mma.m16n8k32 for
+// one column: per thread-in-quad t two words, b0 = digits of k = 8t+{0,2,4,6},
+// b1 = digits of k = 8t+{1,3,5,7} (the order in which the nibbles of weight
+// word t come out of the unpack).
+//
+// The output is one contiguous blob per K stage (GS groups), in the exact
+// layout the matmul kernel keeps in shared memory:
+//
+//  "columns" form, M <= 2 (one MMA per group does all three planes):
+//    frag[GS][8 cols][4 t] uint4 = {b0, b1, as, nc}
+//      b0,b1 : col 0/1/2 = d2/d1/d0 of m=0, col 4/5/6 of m=1, cols 3 and 7 zero
+//      as,nc : what accumulator thread t needs, repeated for every col:
+//              t even: {as(m=t/2), -corr(m=t/2)}; t odd: {as(m=t/2), 0}
+//
+//  "planes" form, M >= 4 (three MMAs per group and 8 activation rows):
+//    h0[GS][MS][4 t] uint4 = {d2.b0, d2.b1, d1.b0, d1.b1}
+//    h1[GS][MS][4 t] uint2 = {d0.b0, d0.b1}
+//    meta[GS][MC] int2     = {as, -corr}
+//    MS = M slots incl. one all-zero slot for lanes without a row (MP=4: 5),
+//    MC = meta slots (8 or 16), zero beyond M.
+struct QuantLayout {
+    int mp, gs;          // padded M, groups per stage
+    int ms, mc;          // planes form: fragment slots, meta slots
+    int blob_bytes;      // bytes per K stage
+    int off_h1, off_meta;
+};
+
+static QuantLayout quant_layout(int mp, int gs) {
+    QuantLayout q;
+    q.mp = mp;
+    q.gs = gs;
+    if (mp <= 2) {
+        q.ms = 8;
+        q.mc = 4;
+        q.off_h1 = 0;
+        q.off_meta = 0;
+        q.blob_bytes = gs * 8 * 4 * 16;
+    } else {
+        q.ms = (mp < 8) ? mp + 1 : mp;
+        q.mc = (mp <= 8) ? 8 : 16;
+        q.off_h1 = gs * q.ms * 4 * 16;
+        q.off_meta = q.off_h1 + gs * q.ms * 4 * 8;
+        q.blob_bytes = q.off_meta + gs * q.mc * 8;
+    }
+    return q;
+}
+
 __global__ void __launch_bounds__(256)
-act_quant_kernel(const float *__restrict__ act, uint4 *__restrict__ digits,
-                 int2 *__restrict__ meta, int M, int MP, int K) {
+act_quant_kernel(const float *__restrict__ act, unsigned char *__restrict__ blobs, int M, int K,
+                 QuantLayout q) {
     const int lane = threadIdx.x & 31;
     const int groups = K / 32;
-    const int total = groups * MP;
+    const int slots = (q.mp <= 2) ? 2 : max(q.ms, q.mc);  // rows to visit per group (incl. zero rows)
+    const int total = groups * slots;
     for (int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total;
          item += gridDim.x * (blockDim.x >> 5)) {
-        const int G = item / MP, m = item % MP;
-        const float v = (m < M) ? act[(size_t)m * K + G * 32 + lane] : 0.0f;
+        const int Gabs = item / slots, m = item % slots;
+        const int ks = Gabs / q.gs, G = Gabs % q.gs;
+        unsigned char *blob = blobs + (size_t)ks * q.blob_bytes;
+        const float v = (m < M) ? act[(size_t)m * K + Gabs * 32 + lane] : 0.0f;
         float gmax = fabsf(v);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
@@ -145,7 +189,7 @@ act_quant_kernel(const float *__restrict__ act, uint4 *__restrict__ digits,
         if (gmax > 0.0f && !bad) (void)frexpf(gmax, &e);
         e = max(e, -100);  // keeps 2^(21-e) finite for vanishing groups
         const float up = ldexpf(1.0f, 21 - e);
-        int fx = bad ? 0 : __float2int_rn(v * up);
+        const int fx = bad ? 0 : __float2int_rn(v * up);
         int sum = fx;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -167,13 +211,35 @@ act_quant_kernel(const float *__restrict__ act, uint4 *__restrict__ digits,
                 b1[d] |= ((od >> (8 * d)) & 255u) << (8 * i);
             }
         }
-        if (lane < 4) {
-            digits[((size_t)(G * 2 + 0) * MP + m) * 4 + t] = make_uint4(b0[2], b1[2], b0[1], b1[1]);
-            digits[((size_t)(G * 2 + 1) * MP + m) * 4 + t] = make_uint4(b0[0], b1[0], 0u, 0u);
-        }
-        if (lane == 0) {
-            const float as = bad ? __int_as_float(0x7fc00000) : ldexpf(1.0f, e - 21);
-            meta[(size_t)G * MP + m] = make_int2(__float_as_int(as), 8 * sum);
+        const float as = (m < M) ? (bad ? __int_as_float(0x7fc00000) : ldexpf(1.0f, e - 21)) : 0.0f;
+        const int ncorr = -8 * sum;
+        if (q.mp <= 2) {
+            uint32_t *frag = reinterpret_cast<uint32_t *>(blob);  // [G][col][t][4 words]
+            if (lane < 4) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int d = 2 - c;  // col 0,1,2 = planes 2,1,0; col 3 = zero
+                    uint32_t *w = frag + ((G * 8 + 4 * m + c) * 4 + t) * 4;
+                    w[0] = (c < 3) ? b0[d < 0 ? 0 : d] : 0u;
+                    w[1] = (c < 3) ? b1[d < 0 ? 0 : d] : 0u;
+                }
+            }
+            if (lane < 16) {
+                // accumulator threads t = 2m (gets -corr) and 2m+1 (gets 0), in all 8 columns
+                const int col = lane >> 1, tt = 2 * m + (lane & 1);
+                uint32_t *w = frag + ((G * 8 + col) * 4 + tt) * 4;
+                w[2] = __float_as_uint(as);
+                w[3] = (lane & 1) ? 0u : (uint32_t)ncorr;
+            }
+        } else {
+            uint4 *h0 = reinterpret_cast<uint4 *>(blob);
+            uint2 *h1 = reinterpret_cast<uint2 *>(blob + q.off_h1);
+            int2 *meta = reinterpret_cast<int2 *>(blob + q.off_meta);
+            if (lane < 4 && m < q.ms) {
+                h0[(G * q.ms + m) * 4 + t] = make_uint4(b0[2], b1[2], b0[1], b1[1]);
+                h1[(G * q.ms + m) * 4 + t] = make_uint2(b0[0], b1[0]);
+            }
+            if (lane == 0 && m < q.mc) meta[G * q.mc + m] = make_int2(__float_as_int(as), ncorr);
         }
     }
 }
@@ -182,10 +248,9 @@ act_quant_kernel(const float *__restrict__ act, uint4 *__restrict__ digits,
 // Fast kernel
 // ---------------------------------------------------------------------------
 
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, bool valid) {
     const int sz = valid ? 16 : 0;  // src-size 0 => 16 bytes of zeros
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc), "r"(sz));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gsrc), "r"(sz));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void cp_async_wait_dyn(int n) {
@@ -201,13 +266,14 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {
     }
 }
 
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// D = A(u8, 16x32) * B(s8, 32x8) + C, int32 accumulate
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1, int c0, int c1, int c2, int c3) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2),
+          "r"(c3));
 }
 
 // (w ^ 0x88888888) & 0x0f0f0f0f in one LOP3: unsigned nibbles q+8 as bytes
@@ -217,24 +283,45 @@ __device__ __forceinline__ uint32_t nib_u8(uint32_t w) {
     return r;
 }
 
+// Shared-memory reads go through ordinary pointers (not volatile asm) so that the
+// compiler can hoist the loads of all the groups a warp handles in a stage above
+// the first MMA; `off` is a byte offset from the start of dynamic shared memory.
+__device__ __forceinline__ uint32_t lds32(const unsigned char *base, uint32_t off) {
+    return *reinterpret_cast<const uint32_t *>(base + off);
+}
+__device__ __forceinline__ float lds_f32(const unsigned char *base, uint32_t off) {
+    return *reinterpret_cast<const float *>(base + off);
+}
+__device__ __forceinline__ uint2 lds64(const unsigned char *base, uint32_t off) {
+    return *reinterpret_cast<const uint2 *>(base + off);
+}
+__device__ __forceinline__ uint4 lds128(const unsigned char *base, uint32_t off) {
+    return *reinterpret_cast<const uint4 *>(base + off);
+}
+
 struct FastGeom {
-    int tiles;        // 16-row tiles per row block (1..8)
-    int tiles_pow2;   // next power of two
-    int kslices;      // warps sharing one tile along K
+    int tiles;        // 16-row tiles per row block (1..TP2)
     int stages;       // ring depth
-    int w_bytes, s_bytes, d_bytes, a_bytes, stage_bytes;
-    int s_pitch;      // floats per row in the scale tile
+    int w_bytes, s_bytes, stage_bytes;
+    QuantLayout q;
 };
 
-// GS = groups (of 32 k) per stage: 16 (512 k) or 8 (256 k). MP = padded M.
-template <int MP, int GS>
+// MP  = padded M (1,2,4,8,16)
+// GS  = groups of 32 k per stage: 16 (512 k) or 8 (256 k)
+// TP2 = warps along the rows of a row block (2 or 8); the other 16/TP2 warps of
+//       a tile split the stage's groups between them
+template <int MP, int GS, int TP2>
 __global__ void __launch_bounds__(512, 1)
 int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ scales,
-                      const uint4 *__restrict__ digits, const int2 *__restrict__ meta,
-                      float *__restrict__ out, int M, int N, int K, FastGeom g) {
-    constexpr int NT = (MP > 8) ? 2 : 1;
-    constexpr int ATOMS = GS / 8;  // 128-byte swizzle atoms per row per stage
-    extern __shared__ __align__(128) unsigned char smem[];
+                      const unsigned char *__restrict__ blobs, float *__restrict__ out, int M,
+                      int N, int K, FastGeom g) {
+    constexpr bool COLS = (MP <= 2);           // digit planes in MMA columns
+    constexpr int NT = (MP > 8) ? 2 : 1;       // 8-wide activation tiles (planes form)
+    constexpr int NACC = COLS ? 2 : NT * 4;
+    constexpr int KSL = (16 / TP2 < GS) ? 16 / TP2 : GS;  // K slices per tile
+    constexpr int GPW = GS / KSL;              // groups per warp per stage
+    constexpr int S_PITCH = (GS + 4) * 4;      // bytes per row of the scale tile (80 / 48)
+    extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, t = lane & 3;
 
@@ -246,146 +333,202 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
     const int k_stages = K / (GS * 32);
     const int total = n_rb * k_stages;
     const int groups = K / 32;
-
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     float *red = reinterpret_cast<float *>(smem + (size_t)g.stages * g.stage_bytes);
 
-    auto issue = [&](int it) {
-        const int rb = it / k_stages, ks = it % k_stages;
-        const int row0 = r0 + rb * rb_rows;
-        unsigned char *st = smem + (size_t)(it % g.stages) * g.stage_bytes;
-        // weights: rb_rows x (GS*16) bytes, 16-byte chunks, chunk ^= row&7 inside each atom
-        const int wchunks = rb_rows * GS;
-        for (int i = tid; i < wchunks; i += 512) {
-            const int r = i / GS, c = i % GS;
-            const int atom = c >> 3, cc = c & 7;
-            unsigned char *dst = st + atom * (rb_rows * 128) + r * 128 + ((cc ^ (r & 7)) << 4);
-            const int row = row0 + r;
-            const bool ok = row < r1;
-            const uint8_t *src = wq + (size_t)(ok ? row : r0) * (K / 2) + (size_t)ks * (GS * 16) + c * 16;
-            cp_async16(dst, src, ok);
+    // ---- producer state: every thread owns up to 4 weight chunks, 1 scale chunk and
+    // ---- 2 digit-blob chunks per stage; pointers advance by one stage of K per issue
+    const int wchunks = rb_rows * GS;
+    const uint8_t *w_ptr[4];
+    uint32_t w_dst[4];
+    int w_row[4];
+    unsigned w_ok = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = tid + 512 * j;
+        const int r = i / GS, c = i % GS;
+        w_row[j] = (i < wchunks) ? r : -1;
+        w_dst[j] = (c >> 3) * (rb_rows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+        w_ptr[j] = wq + c * 16;
+    }
+    const int s_row = (tid < rb_rows * (GS / 4)) ? tid / (GS / 4) : -1;
+    const uint32_t s_dst = g.w_bytes + (tid / (GS / 4)) * S_PITCH + (tid % (GS / 4)) * 16;
+    const float *s_ptr = scales + (tid % (GS / 4)) * 4;
+    bool s_ok = false;
+    const int bchunks = g.q.blob_bytes / 16;
+    const uint32_t b_off = g.w_bytes + g.s_bytes;
+
+    int p_slot = 0, p_ks = 0, p_rb = 0;  // next stage to issue
+    auto issue = [&]() {
+        if (p_ks == 0) {  // (re)aim the pointers at the first K stage of row block p_rb
+            const int row0 = r0 + p_rb * rb_rows;
+            w_ok = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int row = row0 + w_row[j];
+                const bool ok = (w_row[j] >= 0) && (row < r1);
+                w_ok |= (ok ? 1u : 0u) << j;
+                const int i = tid + 512 * j;
+                w_ptr[j] = wq + (size_t)(ok ? row : r0) * (K / 2) + (i % GS) * 16;
+            }
+            const int srow = row0 + s_row;
+            s_ok = (s_row >= 0) && (srow < r1);
+            s_ptr = scales + (size_t)(s_ok ? srow : r0) * groups + (tid % (GS / 4)) * 4;
         }
-        // scales: rb_rows x GS floats, row pitch s_pitch floats
-        unsigned char *ss = st + g.w_bytes;
-        const int schunks = rb_rows * (GS / 4);
-        for (int i = tid; i < schunks; i += 512) {
-            const int r = i / (GS / 4), c = i % (GS / 4);
-            const int row = row0 + r;
-            const bool ok = row < r1;
-            const float *src = scales + (size_t)(ok ? row : r0) * groups + ks * GS + c * 4;
-            cp_async16(ss + r * (g.s_pitch * 4) + c * 16, src, ok);
+        const uint32_t st = smem_base + (uint32_t)p_slot * g.stage_bytes;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (w_row[j] >= 0) cp_async16(st + w_dst[j], w_ptr[j], (w_ok >> j) & 1u);
+            w_ptr[j] += GS * 16;
         }
-        // digit planes of this K range: GS*2*MP*4 uint4, contiguous
-        unsigned char *ds = ss + g.s_bytes;
-        const int dchunks = GS * 2 * MP * 4;
-        const uint4 *dsrc = digits + (size_t)ks * dchunks;
-        for (int i = tid; i < dchunks; i += 512) cp_async16(ds + i * 16, dsrc + i, true);
-        // meta: GS*MP int2
-        unsigned char *as = ds + g.d_bytes;
-        const int achunks = (GS * MP * 8 + 15) / 16;
-        const unsigned char *asrc = reinterpret_cast<const unsigned char *>(meta + (size_t)ks * GS * MP);
-        for (int i = tid; i < achunks; i += 512) cp_async16(as + i * 16, asrc + i * 16, true);
+        if (s_row >= 0) cp_async16(st + s_dst, s_ptr, s_ok);
+        s_ptr += GS;
+        const unsigned char *bsrc = blobs + (size_t)p_ks * g.q.blob_bytes;
+        for (int i = tid; i < bchunks; i += 512) cp_async16(st + b_off + i * 16, bsrc + i * 16, true);
+        if (++p_slot == g.stages) p_slot = 0;
+        if (++p_ks == k_stages) { p_ks = 0; ++p_rb; }
     };
 
     for (int p = 0; p < g.stages - 1; ++p) {
-        if (p < total) issue(p);
+        if (p < total) issue();
         cp_async_commit();
     }
 
-    const int tile = warp % g.tiles_pow2;
-    const int kslice = warp / g.tiles_pow2;
-    const bool active = (tile < g.tiles) && (kslice < g.kslices);
-    const int gpw = GS / g.kslices;  // groups per warp per stage
+    const int tile = warp % TP2;
+    const int kslice = warp / TP2;
+    const bool active = (tile < g.tiles) && (kslice < KSL);
+    const int G0 = kslice * GPW;  // first group of this warp inside a stage
 
-    float acc[NT][4];
+    // ---- consumer offsets, constant for the whole kernel (relative to the stage base) ----
+    // weight word of (row gq of this warp's tile, group G0+gi, thread-in-quad t); the row 8
+    // below is 1024 bytes further with the same swizzle phase.
+    uint32_t w_off[GPW];
 #pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[n][j] = 0.0f;
+    for (int gi = 0; gi < GPW; ++gi) {
+        const int G = G0 + gi;
+        w_off[gi] = (uint32_t)(G >> 3) * (rb_rows * 128) + (uint32_t)(tile * 16 + gq) * 128 +
+                    ((((uint32_t)G & 7u) ^ (uint32_t)gq) << 4) + t * 4;
+    }
+    const uint32_t sA_off = g.w_bytes + (uint32_t)(tile * 16 + gq) * S_PITCH + G0 * 4;
+    // columns form: one uint4 per unit; planes form: h0 / h1 / meta
+    const int mslot = (MP < 8) ? min(gq, g.q.ms - 1) : gq;
+    const uint32_t f_off = COLS ? b_off + (uint32_t)((G0 * 8 + gq) * 4 + t) * 16
+                                : b_off + (uint32_t)((G0 * g.q.ms + mslot) * 4 + t) * 16;
+    const uint32_t h1_off = b_off + g.q.off_h1 + (uint32_t)((G0 * g.q.ms + mslot) * 4 + t) * 8;
+    const uint32_t mt_off = b_off + g.q.off_meta + (uint32_t)(G0 * g.q.mc + 2 * t) * 8;
+    const uint32_t f_step = COLS ? 8 * 4 * 16 : g.q.ms * 4 * 16;  // bytes per group
+    const uint32_t h1_step = g.q.ms * 4 * 8, mt_step = g.q.mc * 8;
+    const int mul_hi = (t & 1) ? 1 : 65536;  // columns form: plane weight of this thread's c0
 
+    float acc[NACC];
+#pragma unroll
+    for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+
+    int c_slot = 0, c_ks = 0, c_rb = 0;  // stage being consumed
     for (int it = 0; it < total; ++it) {
         cp_async_wait_dyn(g.stages - 2);
         __syncthreads();
-        {
-            const int nxt = it + g.stages - 1;
-            if (nxt < total) issue(nxt);
-            cp_async_commit();
-        }
-        const unsigned char *st = smem + (size_t)(it % g.stages) * g.stage_bytes;
+        if (it + g.stages - 1 < total) issue();
+        cp_async_commit();
         if (active) {
-            const float *ss = reinterpret_cast<const float *>(st + g.w_bytes);
-            const uint4 *ds = reinterpret_cast<const uint4 *>(st + g.w_bytes + g.s_bytes);
-            const int2 *as = reinterpret_cast<const int2 *>(st + g.w_bytes + g.s_bytes + g.d_bytes);
-            const int rowA = tile * 16 + gq, rowB = rowA + 8;
-#pragma unroll 4
-            for (int gi = 0; gi < gpw; ++gi) {
-                const int G = kslice * gpw + gi;
-                const int atom = G >> 3, cc = G & 7;
-                const unsigned char *wa = st + atom * (rb_rows * 128);
-                const uint32_t wA = *reinterpret_cast<const uint32_t *>(
-                    wa + rowA * 128 + ((cc ^ (rowA & 7)) << 4) + t * 4);
-                const uint32_t wB = *reinterpret_cast<const uint32_t *>(
-                    wa + rowB * 128 + ((cc ^ (rowB & 7)) << 4) + t * 4);
+            const unsigned char *st = smem + (size_t)c_slot * g.stage_bytes;
+            float sA[GPW], sB[GPW];
+            if constexpr (GPW % 4 == 0) {
+#pragma unroll
+                for (int gi = 0; gi < GPW; gi += 4) {
+                    const uint4 x = lds128(st, sA_off + gi * 4);
+                    const uint4 y = lds128(st, sA_off + 8 * S_PITCH + gi * 4);
+                    sA[gi] = __uint_as_float(x.x); sA[gi + 1] = __uint_as_float(x.y);
+                    sA[gi + 2] = __uint_as_float(x.z); sA[gi + 3] = __uint_as_float(x.w);
+                    sB[gi] = __uint_as_float(y.x); sB[gi + 1] = __uint_as_float(y.y);
+                    sB[gi + 2] = __uint_as_float(y.z); sB[gi + 3] = __uint_as_float(y.w);
+                }
+            } else {
+#pragma unroll
+                for (int gi = 0; gi < GPW; ++gi) {
+                    sA[gi] = lds_f32(st, sA_off + gi * 4);
+                    sB[gi] = lds_f32(st, sA_off + 8 * S_PITCH + gi * 4);
+                }
+            }
+#pragma unroll
+            for (int gi = 0; gi < GPW; ++gi) {
+                const uint32_t wA = lds32(st, w_off[gi]), wB = lds32(st, w_off[gi] + 1024);
                 uint32_t a[4];
                 a[0] = nib_u8(wA);
                 a[1] = nib_u8(wB);
                 a[2] = nib_u8(wA >> 4);
                 a[3] = nib_u8(wB >> 4);
-                const float sA = ss[rowA * g.s_pitch + G], sB = ss[rowB * g.s_pitch + G];
+                if constexpr (COLS) {
+                    const uint4 f = lds128(st, f_off + gi * f_step);
+                    int c[4];
+                    mma_u8s8(c, a, f.x, f.y, 0, 0, 0, 0);
+                    const int vA = c[0] * mul_hi + (c[1] * 256 + (int)f.w);
+                    const int vB = c[2] * mul_hi + (c[3] * 256 + (int)f.w);
+                    const float as = __uint_as_float(f.z);
+                    acc[0] = fmaf(sA[gi] * as, (float)vA, acc[0]);
+                    acc[1] = fmaf(sB[gi] * as, (float)vB, acc[1]);
+                } else {
 #pragma unroll
-                for (int n = 0; n < NT; ++n) {
-                    const int mcol = n * 8 + gq;  // activation row this thread feeds as B column
-                    uint4 h0 = make_uint4(0, 0, 0, 0), h1 = make_uint4(0, 0, 0, 0);
-                    if (mcol < MP) {
-                        h0 = ds[((G * 2 + 0) * MP + mcol) * 4 + t];
-                        h1 = ds[((G * 2 + 1) * MP + mcol) * 4 + t];
+                    for (int n = 0; n < NT; ++n) {
+                        const uint4 h0 = lds128(st, f_off + gi * f_step + n * (8 * 4 * 16));
+                        const uint2 h1 = lds64(st, h1_off + gi * h1_step + n * (8 * 4 * 8));
+                        const uint4 mt = lds128(st, mt_off + gi * mt_step + n * (8 * 8));
+                        int c2[4], c1[4], c0[4];
+                        mma_u8s8(c2, a, h0.x, h0.y, 0, 0, 0, 0);
+                        mma_u8s8(c1, a, h0.z, h0.w, 0, 0, 0, 0);
+                        mma_u8s8(c0, a, h1.x, h1.y, (int)mt.y, (int)mt.w, (int)mt.y, (int)mt.w);
+                        const float as0 = __uint_as_float(mt.x), as1 = __uint_as_float(mt.z);
+                        const int v0 = c2[0] * 65536 + (c1[0] * 256 + c0[0]);
+                        const int v1 = c2[1] * 65536 + (c1[1] * 256 + c0[1]);
+                        const int v2 = c2[2] * 65536 + (c1[2] * 256 + c0[2]);
+                        const int v3 = c2[3] * 65536 + (c1[3] * 256 + c0[3]);
+                        acc[n * 4 + 0] = fmaf(sA[gi] * as0, (float)v0, acc[n * 4 + 0]);
+                        acc[n * 4 + 1] = fmaf(sA[gi] * as1, (float)v1, acc[n * 4 + 1]);
+                        acc[n * 4 + 2] = fmaf(sB[gi] * as0, (float)v2, acc[n * 4 + 2]);
+                        acc[n * 4 + 3] = fmaf(sB[gi] * as1, (float)v3, acc[n * 4 + 3]);
                     }
-                    // columns of the accumulator fragment this thread owns: 2t, 2t+1
-                    const int c0 = n * 8 + 2 * t;
-                    int2 m0 = make_int2(0, 0), m1 = make_int2(0, 0);
-                    if (c0 < MP) m0 = as[G * MP + c0];
-                    if (c0 + 1 < MP) m1 = as[G * MP + c0 + 1];
-                    int c[4] = {0, 0, 0, 0};
-                    mma_u8s8(c, a, h0.x, h0.y);  // d2
-                    c[0] <<= 8; c[1] <<= 8; c[2] <<= 8; c[3] <<= 8;
-                    mma_u8s8(c, a, h0.z, h0.w);  // d1
-                    c[0] = c[0] * 256 - m0.y;    // fold the -8*sum(afix) of the +8 nibble bias
-                    c[1] = c[1] * 256 - m1.y;
-                    c[2] = c[2] * 256 - m0.y;
-                    c[3] = c[3] * 256 - m1.y;
-                    mma_u8s8(c, a, h1.x, h1.y);  // d0
-                    const float as0 = __int_as_float(m0.x), as1 = __int_as_float(m1.x);
-                    acc[n][0] = fmaf(sA * as0, (float)c[0], acc[n][0]);
-                    acc[n][1] = fmaf(sA * as1, (float)c[1], acc[n][1]);
-                    acc[n][2] = fmaf(sB * as0, (float)c[2], acc[n][2]);
-                    acc[n][3] = fmaf(sB * as1, (float)c[3], acc[n][3]);
                 }
             }
         }
-        if ((it % k_stages) == k_stages - 1) {
+        if (++c_slot == g.stages) c_slot = 0;
+        if (++c_ks == k_stages) {
+            c_ks = 0;
             // end of a row block: combine the K slices in a fixed order and store
             if (active) {
 #pragma unroll
-                for (int n = 0; n < NT; ++n)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        red[(((kslice * g.tiles + tile) * NT + n) * 4 + j) * 32 + lane] = acc[n][j];
+                for (int j = 0; j < NACC; ++j)
+                    red[((kslice * g.tiles + tile) * NACC + j) * 32 + lane] = acc[j];
             }
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[n][j] = 0.0f;
+            for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
             __syncthreads();
-            const int row0 = r0 + (it / k_stages) * rb_rows;
-            const int items = g.tiles * NT * 128;
-            for (int i = tid; i < items; i += 512) {
-                const int l = i & 31, j = (i >> 5) & 3, n = (i >> 7) % NT, tl = (i >> 7) / NT;
-                float v = 0.0f;
-                for (int ks = 0; ks < g.kslices; ++ks)
-                    v += red[(((ks * g.tiles + tl) * NT + n) * 4 + j) * 32 + l];
-                const int row = row0 + tl * 16 + (l >> 2) + ((j & 2) ? 8 : 0);
-                const int m = n * 8 + 2 * (l & 3) + (j & 1);
-                if (row < r1 && m < M) out[(size_t)m * N + row] = v;
+            const int row0 = r0 + c_rb * rb_rows;
+            if constexpr (COLS) {
+                // element (tile, half, gq, m): sum over K slices and the thread pair t=2m,2m+1
+                const int items = g.tiles * 2 * 8 * MP;
+                for (int i = tid; i < items; i += 512) {
+                    const int m = i % MP, q8 = (i / MP) & 7, half = (i / (MP * 8)) & 1, tl = i / (MP * 16);
+                    float v = 0.0f;
+                    for (int ks = 0; ks < KSL; ++ks) {
+                        const float *p = red + ((ks * g.tiles + tl) * NACC + half) * 32 + q8 * 4 + 2 * m;
+                        v += p[0] + p[1];
+                    }
+                    const int row = row0 + tl * 16 + q8 + half * 8;
+                    if (row < r1 && m < M) out[(size_t)m * N + row] = v;
+                }
+            } else {
+                const int items = g.tiles * NACC * 32;
+                for (int i = tid; i < items; i += 512) {
+                    const int l = i & 31, j = (i >> 5) % NACC, tl = (i >> 5) / NACC;
+                    float v = 0.0f;
+                    for (int ks = 0; ks < KSL; ++ks)
+                        v += red[((ks * g.tiles + tl) * NACC + j) * 32 + l];
+                    const int row = row0 + tl * 16 + (l >> 2) + ((j & 2) ? 8 : 0);
+                    const int m = (j >> 2) * 8 + 2 * (l & 3) + (j & 1);
+                    if (row < r1 && m < M) out[(size_t)m * N + row] = v;
+                }
             }
+            ++c_rb;
             // `red` is next written after at least one more __syncthreads (top of the loop)
         }
     }
@@ -397,10 +540,18 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
 // ---------------------------------------------------------------------------
 
 static int padded_m(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16; }
+static int stage_groups(int mp, int k) { return (k % 512 == 0 && mp <= 4) ? 16 : 8; }
 
 size_t int4_gemv_scratch_bytes(size_t m, size_t k) {
-    const size_t mp = (size_t)padded_m((int)m);
-    return (k / 32) * 2 * mp * 4 * 16 + (k / 32) * mp * 8 + 256;
+    // worst case over every padded M up to the one requested
+    size_t worst = 0;
+    for (int mp = 1; mp <= padded_m((int)m); mp *= 2) {
+        const int gs = stage_groups(mp, (int)k);
+        const QuantLayout q = quant_layout(mp, gs);
+        const size_t b = (k / (32 * (size_t)gs)) * (size_t)q.blob_bytes;
+        worst = b > worst ? b : worst;
+    }
+    return worst + 256;
 }
 
 bool int4_gemv_fast_supported(size_t m, size_t n, size_t k, size_t gs) {
@@ -408,28 +559,24 @@ bool int4_gemv_fast_supported(size_t m, size_t n, size_t k, size_t gs) {
            n < (1u << 30) && k < (1u << 24);
 }
 
-template <int MP, int GS>
+template <int MP, int GS, int TP2>
 static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales,
-                       const uint4 *digits, const int2 *meta, float *out, int M, int N, int K) {
+                       const unsigned char *blobs, float *out, int M, int N, int K,
+                       const QuantLayout &q) {
     const int grid = ctx->sm_count;
     const int rows_per_cta = (N + grid - 1) / grid;
     FastGeom g;
-    g.tiles = min(8, (rows_per_cta + 15) / 16);
-    g.tiles_pow2 = 1;
-    while (g.tiles_pow2 < g.tiles) g.tiles_pow2 <<= 1;
-    g.kslices = min(16 / g.tiles_pow2, GS);
+    g.q = q;
+    g.tiles = min(TP2, (rows_per_cta + 15) / 16);
     const int rb_rows = g.tiles * 16;
     g.w_bytes = rb_rows * GS * 16;
-    g.s_pitch = GS + 4;  // 20 or 12 floats: rows land on distinct banks for 128-bit reads
-    g.s_bytes = rb_rows * g.s_pitch * 4;
-    g.d_bytes = GS * 2 * MP * 4 * 16;
-    g.a_bytes = ((GS * MP * 8 + 15) / 16) * 16;
-    g.stage_bytes = ((g.w_bytes + g.s_bytes + g.d_bytes + g.a_bytes + 127) / 128) * 128;
-    const int red_bytes = 16 * 2 * 4 * 32 * 4;
-    const int budget = 227 * 1024 - red_bytes;
+    g.s_bytes = rb_rows * (GS + 4) * 4;  // 80- or 48-byte rows land on distinct banks
+    g.stage_bytes = ((g.w_bytes + g.s_bytes + q.blob_bytes + 1023) / 1024) * 1024;
+    const int red_bytes = 16 * 8 * 32 * 4;
+    const int budget = 227 * 1024 - red_bytes - 1024;
     g.stages = max(2, min(8, budget / g.stage_bytes));
     const int smem = g.stages * g.stage_bytes + red_bytes;
-    auto kern = int4_gemv_fast_kernel<MP, GS>;
+    auto kern = int4_gemv_fast_kernel<MP, GS, TP2>;
     static int smem_set[16] = {0};  // per device: opt-in shared memory size already raised
     if (ctx->device >= 16 || !smem_set[ctx->device]) {
         YSCV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -437,36 +584,44 @@ static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scale
         if (ctx->device < 16) smem_set[ctx->device] = 1;
     }
     ctx->prof_begin();
-    kern<<<grid, 512, smem, ctx->stream>>>(wq, scales, digits, meta, out, M, N, K, g);
+    kern<<<grid, 512, smem, ctx->stream>>>(wq, scales, blobs, out, M, N, K, g);
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
     return YSCV_CUDA_OK;
 }
 
+template <int MP, int GS>
+static int launch_fast_tp(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales,
+                          const unsigned char *blobs, float *out, int M, int N, int K,
+                          const QuantLayout &q) {
+    const int rows_per_cta = (N + ctx->sm_count - 1) / ctx->sm_count;
+    if (rows_per_cta <= 32) return launch_fast<MP, GS, 2>(ctx, wq, scales, blobs, out, M, N, K, q);
+    return launch_fast<MP, GS, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
+}
+
 int int4_gemv_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, const float *act,
                    float *out, size_t m, size_t n, size_t k, void *scratch) {
     const int M = (int)m, N = (int)n, K = (int)k;
     const int MP = padded_m(M);
-    uint4 *digits = reinterpret_cast<uint4 *>(scratch);
-    int2 *meta = reinterpret_cast<int2 *>(reinterpret_cast<unsigned char *>(scratch) +
-                                          (size_t)(K / 32) * 2 * MP * 4 * 16);
-    const int items = (K / 32) * MP;
+    const int GS = stage_groups(MP, K);
+    const QuantLayout q = quant_layout(MP, GS);
+    unsigned char *blobs = reinterpret_cast<unsigned char *>(scratch);
+    const int items = (K / 32) * ((MP <= 2) ? 2 : max(q.ms, q.mc));
     const int qblocks = min((items + 7) / 8, 4 * ctx->sm_count);
-    act_quant_kernel<<<qblocks, 256, 0, ctx->stream>>>(act, digits, meta, M, MP, K);
+    act_quant_kernel<<<qblocks, 256, 0, ctx->stream>>>(act, blobs, M, K, q);
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
-    const bool wide = (K % 512 == 0) && MP <= 4;
     ctx->last_kernel = "int4_gemv_fast(imma,cp.async)";
     switch (MP) {
-        case 1: return wide ? launch_fast<1, 16>(ctx, wq, scales, digits, meta, out, M, N, K)
-                            : launch_fast<1, 8>(ctx, wq, scales, digits, meta, out, M, N, K);
-        case 2: return wide ? launch_fast<2, 16>(ctx, wq, scales, digits, meta, out, M, N, K)
-                            : launch_fast<2, 8>(ctx, wq, scales, digits, meta, out, M, N, K);
-        case 4: return wide ? launch_fast<4, 16>(ctx, wq, scales, digits, meta, out, M, N, K)
-                            : launch_fast<4, 8>(ctx, wq, scales, digits, meta, out, M, N, K);
-        case 8: return launch_fast<8, 8>(ctx, wq, scales, digits, meta, out, M, N, K);
-        default: return launch_fast<16, 8>(ctx, wq, scales, digits, meta, out, M, N, K);
+        case 1: return GS == 16 ? launch_fast_tp<1, 16>(ctx, wq, scales, blobs, out, M, N, K, q)
+                                : launch_fast_tp<1, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
+        case 2: return GS == 16 ? launch_fast_tp<2, 16>(ctx, wq, scales, blobs, out, M, N, K, q)
+                                : launch_fast_tp<2, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
+        case 4: return GS == 16 ? launch_fast_tp<4, 16>(ctx, wq, scales, blobs, out, M, N, K, q)
+                                : launch_fast_tp<4, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
+        case 8: return launch_fast_tp<8, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
+        default: return launch_fast_tp<16, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
     }
 }
 
