@@ -60,7 +60,9 @@ static int int4_matmul_dev(yscv_cuda_ctx *ctx, const uint8_t *d_packed, const fl
         const size_t mc = m - m0 < 16 ? m - m0 : 16;
         const float *a = d_act + m0 * k;
         float *o = d_out + m0 * n;
-        if (int4_gemv_fast_supported(mc, n, k, gs)) {
+        const bool aligned = ((reinterpret_cast<uintptr_t>(d_packed) | reinterpret_cast<uintptr_t>(d_scales) |
+                               reinterpret_cast<uintptr_t>(a)) & 15) == 0;
+        if (aligned && int4_gemv_fast_supported(mc, n, k, gs)) {
             rc = ctx->scratch.reserve(int4_gemv_scratch_bytes(16, k));
             if (rc) return rc;
             rc = int4_gemv_fast(ctx, d_packed, d_scales, a, o, mc, n, k, ctx->scratch.ptr);

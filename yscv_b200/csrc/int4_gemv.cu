@@ -21,15 +21,18 @@
 //    into a 22-bit block-fixed-point number, split into three signed 8-bit
 //    digit planes; the per-group integer dot  sum_j q_j * afix_j  is then exact
 //    in int32 (three mma.sync.m16n8k32.u8.s8 with a x256 between them), and only
-//    the per-(row,group) scale is applied in fp32. Weights are staged through
-//    shared memory by 16-byte cp.async in a multi-stage ring (coalesced 128-bit
-//    loads, no register cost for bytes in flight), read back conflict-free
-//    through an XOR swizzle, and turned into MMA fragments with 3 logic ops per
-//    8 nibbles. One persistent CTA per SM owns a contiguous row range; inside
-//    the CTA the K range of a stage is split across warps and the partial sums
-//    are combined in a fixed order (deterministic, no atomics).
+//    the per-(row,group) scale is applied in fp32. Weights, scales and digit
+//    planes are staged through shared memory by TMA (one producer thread per
+//    CTA issues three or four bulk copies per stage into an mbarrier-guarded
+//    ring; no register or issue-slot cost for bytes in flight), read back
+//    conflict-free through the hardware XOR swizzle, and turned into MMA
+//    fragments with 3 logic ops per 8 nibbles. One persistent CTA per SM owns a
+//    contiguous row range; inside the CTA the K range of a stage is split
+//    across warps and the partial sums are combined in a fixed order
+//    (deterministic, no atomics). Every mbarrier wait is bounded.
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tma.cuh"
 
 namespace yscv {
 
@@ -129,8 +132,10 @@ int4_gemv_generic_kernel(const uint8_t *__restrict__ wq, const float *__restrict
 // layout the matmul kernel keeps in shared memory:
 //
 //  "columns" form, M <= 2 (one MMA per group does all three planes):
-//    frag[GS][8 cols][4 t] uint4 = {b0, b1, as, nc}
+//    frag[GS][C cols][4 t] uint4 = {b0, b1, as, nc},  C = 4 (M=1) or 8 (M=2)
 //      b0,b1 : col 0/1/2 = d2/d1/d0 of m=0, col 4/5/6 of m=1, cols 3 and 7 zero
+//              (with C = 4, MMA columns 4..7 re-read columns 0..3; their products
+//              land in accumulator threads t = 2,3 whose `as` is zero)
 //      as,nc : what accumulator thread t needs, repeated for every col:
 //              t even: {as(m=t/2), -corr(m=t/2)}; t odd: {as(m=t/2), 0}
 //
@@ -152,11 +157,11 @@ static QuantLayout quant_layout(int mp, int gs) {
     q.mp = mp;
     q.gs = gs;
     if (mp <= 2) {
-        q.ms = 8;
+        q.ms = (mp == 1) ? 4 : 8;  // columns stored per group
         q.mc = 4;
         q.off_h1 = 0;
         q.off_meta = 0;
-        q.blob_bytes = gs * 8 * 4 * 16;
+        q.blob_bytes = gs * q.ms * 4 * 16;
     } else {
         q.ms = (mp < 8) ? mp + 1 : mp;
         q.mc = (mp <= 8) ? 8 : 16;
@@ -167,104 +172,121 @@ static QuantLayout quant_layout(int mp, int gs) {
     return q;
 }
 
-__global__ void __launch_bounds__(256)
-act_quant_kernel(const float *__restrict__ act, unsigned char *__restrict__ blobs, int M, int K,
-                 QuantLayout q) {
-    const int lane = threadIdx.x & 31;
-    const int groups = K / 32;
-    const int slots = (q.mp <= 2) ? 2 : max(q.ms, q.mc);  // rows to visit per group (incl. zero rows)
-    const int total = groups * slots;
-    for (int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total;
-         item += gridDim.x * (blockDim.x >> 5)) {
-        const int Gabs = item / slots, m = item % slots;
-        const int ks = Gabs / q.gs, G = Gabs % q.gs;
-        unsigned char *blob = blobs + (size_t)ks * q.blob_bytes;
-        const float v = (m < M) ? act[(size_t)m * K + Gabs * 32 + lane] : 0.0f;
-        float gmax = fabsf(v);
+// A quad (4 consecutive lanes) turns the 32 activations of (row m, group Gabs) into
+// digit planes and writes them into the blob of their K stage. Lane t of the quad
+// owns k = 8t..8t+7, which is exactly what fragment thread t needs, so the only
+// cross-lane traffic is the quad-wide max and sum. `blobs` may point to global or
+// shared memory. `src` (this lane's 8 floats) is null for padding rows (m >= M),
+// which produce zeros. All 32 lanes of the warp must call this together; lanes
+// whose item is out of range pass valid = false.
+__device__ __forceinline__ void quantize_group(const float *__restrict__ src, unsigned char *blobs,
+                                               const QuantLayout &q, int Gabs, int m, int t,
+                                               bool valid) {
+    float v[8];
+    if (src && valid) {
+        const float4 x = __ldg(reinterpret_cast<const float4 *>(src));
+        const float4 y = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+        v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+    } else {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
-        // a non-finite activation poisons the whole group, as it would in fp32
-        const bool bad = !(gmax <= 3.0e38f) || (__ballot_sync(0xffffffffu, v != v) != 0u);
-        int e = 0;
-        if (gmax > 0.0f && !bad) (void)frexpf(gmax, &e);
-        e = max(e, -100);  // keeps 2^(21-e) finite for vanishing groups
-        const float up = ldexpf(1.0f, 21 - e);
-        const int fx = bad ? 0 : __float2int_rn(v * up);
-        int sum = fx;
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
+    float gmax = 0.0f;
+    int nan = 0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    for (int i = 0; i < 8; ++i) {
+        gmax = fmaxf(gmax, fabsf(v[i]));
+        nan |= (v[i] != v[i]) ? 1 : 0;
+    }
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 1));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 2));
+    nan |= __shfl_xor_sync(0xffffffffu, nan, 1);
+    nan |= __shfl_xor_sync(0xffffffffu, nan, 2);
+    // a non-finite activation poisons the whole group, as it would in fp32
+    const bool bad = nan || !(gmax <= 3.0e38f);
+    int e = 0;
+    if (gmax > 0.0f && !bad) e = ((__float_as_int(gmax) >> 23) & 255) - 126;  // gmax < 2^e
+    e = max(e, -100);  // keeps 2^(21-e) finite for vanishing (or subnormal) groups
+    const float up = __int_as_float((127 + 21 - e) << 23);  // 2^(21-e)
+    int sum = 0;
+    uint32_t b0[3] = {0, 0, 0}, b1[3] = {0, 0, 0};  // per plane: k even / k odd digits
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int fx = bad ? 0 : __float2int_rn(v[i] * up);
+        sum += fx;
         const int d0 = ((fx + 128) & 255) - 128;
         const int r1 = (fx - d0) >> 8;
         const int d1 = ((r1 + 128) & 255) - 128;
         const int d2 = (r1 - d1) >> 8;
-        const uint32_t dp = (uint32_t)(d0 & 255) | ((uint32_t)(d1 & 255) << 8) |
-                            ((uint32_t)(d2 & 255) << 16);
-        const int t = lane & 3;
-        uint32_t b0[3] = {0, 0, 0}, b1[3] = {0, 0, 0};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t ev = __shfl_sync(0xffffffffu, dp, 8 * t + 2 * i);
-            const uint32_t od = __shfl_sync(0xffffffffu, dp, 8 * t + 2 * i + 1);
-#pragma unroll
-            for (int d = 0; d < 3; ++d) {
-                b0[d] |= ((ev >> (8 * d)) & 255u) << (8 * i);
-                b1[d] |= ((od >> (8 * d)) & 255u) << (8 * i);
-            }
-        }
-        const float as = (m < M) ? (bad ? __int_as_float(0x7fc00000) : ldexpf(1.0f, e - 21)) : 0.0f;
-        const int ncorr = -8 * sum;
-        if (q.mp <= 2) {
-            uint32_t *frag = reinterpret_cast<uint32_t *>(blob);  // [G][col][t][4 words]
-            if (lane < 4) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int d = 2 - c;  // col 0,1,2 = planes 2,1,0; col 3 = zero
-                    uint32_t *w = frag + ((G * 8 + 4 * m + c) * 4 + t) * 4;
-                    w[0] = (c < 3) ? b0[d < 0 ? 0 : d] : 0u;
-                    w[1] = (c < 3) ? b1[d < 0 ? 0 : d] : 0u;
-                }
-            }
-            if (lane < 16) {
-                // accumulator threads t = 2m (gets -corr) and 2m+1 (gets 0), in all 8 columns
-                const int col = lane >> 1, tt = 2 * m + (lane & 1);
-                uint32_t *w = frag + ((G * 8 + col) * 4 + tt) * 4;
-                w[2] = __float_as_uint(as);
-                w[3] = (lane & 1) ? 0u : (uint32_t)ncorr;
-            }
+        const int sh = 8 * (i >> 1);
+        if (i & 1) {
+            b1[0] |= (uint32_t)(d0 & 255) << sh; b1[1] |= (uint32_t)(d1 & 255) << sh; b1[2] |= (uint32_t)(d2 & 255) << sh;
         } else {
-            uint4 *h0 = reinterpret_cast<uint4 *>(blob);
-            uint2 *h1 = reinterpret_cast<uint2 *>(blob + q.off_h1);
-            int2 *meta = reinterpret_cast<int2 *>(blob + q.off_meta);
-            if (lane < 4 && m < q.ms) {
-                h0[(G * q.ms + m) * 4 + t] = make_uint4(b0[2], b1[2], b0[1], b1[1]);
-                h1[(G * q.ms + m) * 4 + t] = make_uint2(b0[0], b1[0]);
-            }
-            if (lane == 0 && m < q.mc) meta[G * q.mc + m] = make_int2(__float_as_int(as), ncorr);
+            b0[0] |= (uint32_t)(d0 & 255) << sh; b0[1] |= (uint32_t)(d1 & 255) << sh; b0[2] |= (uint32_t)(d2 & 255) << sh;
         }
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (!valid) return;
+    const int ks = Gabs / q.gs, G = Gabs % q.gs;
+    unsigned char *blob = blobs + (size_t)ks * q.blob_bytes;
+    const float as = src ? (bad ? __int_as_float(0x7fc00000)
+                                : __int_as_float((127 + e - 21) << 23))  // 2^(e-21)
+                         : 0.0f;
+    const int ncorr = -8 * sum;
+    if (q.mp <= 2) {
+        uint2 *frag = reinterpret_cast<uint2 *>(blob);  // [G][col][t] x {b0,b1 | as,nc}
+        const int C = q.ms;
+        if (4 * m < C) {
+#pragma unroll
+            for (int c = 0; c < 3; ++c)  // col 0,1,2 = planes 2,1,0
+                frag[((G * C + 4 * m + c) * 4 + t) * 2] = make_uint2(b0[2 - c], b1[2 - c]);
+            frag[((G * C + 4 * m + 3) * 4 + t) * 2] = make_uint2(0u, 0u);
+        }
+        // accumulator threads 2m (gets -corr) and 2m+1 (gets 0), in every column; the four
+        // lanes of the quad share the columns between them
+        for (int col = t; col < C; col += 4) {
+            frag[((G * C + col) * 4 + 2 * m) * 2 + 1] = make_uint2(__float_as_uint(as), (uint32_t)ncorr);
+            frag[((G * C + col) * 4 + 2 * m + 1) * 2 + 1] = make_uint2(__float_as_uint(as), 0u);
+        }
+    } else {
+        uint4 *h0 = reinterpret_cast<uint4 *>(blob);
+        uint2 *h1 = reinterpret_cast<uint2 *>(blob + q.off_h1);
+        int2 *meta = reinterpret_cast<int2 *>(blob + q.off_meta);
+        if (m < q.ms) {
+            h0[(G * q.ms + m) * 4 + t] = make_uint4(b0[2], b1[2], b0[1], b1[1]);
+            h1[(G * q.ms + m) * 4 + t] = make_uint2(b0[0], b1[0]);
+        }
+        if (t == 0 && m < q.mc) meta[G * q.mc + m] = make_int2(__float_as_int(as), ncorr);
+    }
+}
+
+// rows to visit per group, padding rows included
+__host__ __device__ inline int quant_slots(const QuantLayout &q) {
+    return (q.mp <= 2) ? 2 : (q.ms > q.mc ? q.ms : q.mc);
+}
+
+__global__ void __launch_bounds__(128)
+act_quant_kernel(const float *__restrict__ act, unsigned char *__restrict__ blobs, int M, int K,
+                 QuantLayout q) {
+    const int slots = quant_slots(q);
+    const int total = (K / 32) * slots;
+    const int t = threadIdx.x & 3;
+    const int quads = (gridDim.x * blockDim.x) >> 2;
+    const int rounds = (total + quads - 1) / quads;  // same trip count for every lane
+    for (int r = 0; r < rounds; ++r) {
+        const int item = r * quads + ((blockIdx.x * blockDim.x + threadIdx.x) >> 2);
+        const bool valid = item < total;
+        const int Gabs = valid ? item % (K / 32) : 0, m = valid ? item / (K / 32) : 0;
+        quantize_group(m < M ? act + (size_t)m * K + Gabs * 32 + 8 * t : nullptr, blobs, q, Gabs, m,
+                       t, valid);
     }
 }
 
 // ---------------------------------------------------------------------------
 // Fast kernel
 // ---------------------------------------------------------------------------
-
-__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, bool valid) {
-    const int sz = valid ? 16 : 0;  // src-size 0 => 16 bytes of zeros
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gsrc), "r"(sz));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-__device__ __forceinline__ void cp_async_wait_dyn(int n) {
-    switch (n) {
-        case 0: asm volatile("cp.async.wait_group 0;\n" ::); break;
-        case 1: asm volatile("cp.async.wait_group 1;\n" ::); break;
-        case 2: asm volatile("cp.async.wait_group 2;\n" ::); break;
-        case 3: asm volatile("cp.async.wait_group 3;\n" ::); break;
-        case 4: asm volatile("cp.async.wait_group 4;\n" ::); break;
-        case 5: asm volatile("cp.async.wait_group 5;\n" ::); break;
-        case 6: asm volatile("cp.async.wait_group 6;\n" ::); break;
-        default: asm volatile("cp.async.wait_group 7;\n" ::); break;
-    }
-}
 
 // D = A(u8, 16x32) * B(s8, 32x8) + C, int32 accumulate
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -299,6 +321,24 @@ __device__ __forceinline__ uint4 lds128(const unsigned char *base, uint32_t off)
     return *reinterpret_cast<const uint4 *>(base + off);
 }
 
+#ifdef YSCV_TRACE
+// debugging aid (not built by default): per-CTA timestamps of the consumer warp 0
+__device__ unsigned long long g_trace[148 * 32];
+extern "C" int yscv_trace_read(unsigned long long *dst) {
+    return (int)cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace));
+}
+#define TRACE(slot)                                                                     \
+    do {                                                                                \
+        if (tid == 0 && (slot) < 32) {                                                  \
+            unsigned long long _t;                                                      \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                      \
+            g_trace[blockIdx.x * 32 + (slot)] = _t;                                     \
+        }                                                                               \
+    } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
+
 struct FastGeom {
     int tiles;        // 16-row tiles per row block (1..TP2)
     int stages;       // ring depth
@@ -306,117 +346,141 @@ struct FastGeom {
     QuantLayout q;
 };
 
+constexpr int FAST_CONSUMER_WARPS = 16;
+constexpr int FAST_THREADS = (FAST_CONSUMER_WARPS + 1) * 32;  // + one producer warp
+
 // MP  = padded M (1,2,4,8,16)
 // GS  = groups of 32 k per stage: 16 (512 k) or 8 (256 k)
 // TP2 = warps along the rows of a row block (2 or 8); the other 16/TP2 warps of
 //       a tile split the stage's groups between them
-template <int MP, int GS, int TP2>
-__global__ void __launch_bounds__(512, 1)
-int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ scales,
-                      const unsigned char *__restrict__ blobs, float *__restrict__ out, int M,
-                      int N, int K, FastGeom g) {
+//
+// Shared memory: `stages` x { weights [GS/8 atoms][rows][128 B] (TMA 128B swizzle),
+// scales [rows][GS] f32 (TMA 64B / 32B swizzle), digit blob }, then the reduction
+// buffer, then the full[] / empty[] mbarriers.
+//
+// FUSEQ: the CTA quantises the activations itself into a shared-memory copy of the
+// digit blobs (all K stages resident) while the first weight stages are in flight;
+// otherwise the blobs come from global memory (act_quant_kernel ran before) and each
+// stage brings its own.
+template <int MP, int GS, int TP2, bool FUSEQ>
+__global__ void __launch_bounds__(FAST_THREADS, 1)
+int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
+                      const __grid_constant__ CUtensorMap tm_s,
+                      const unsigned char *__restrict__ blobs, const float *__restrict__ act,
+                      float *__restrict__ out, int M, int N, int K, FastGeom g,
+                      int *__restrict__ status) {
     constexpr bool COLS = (MP <= 2);           // digit planes in MMA columns
     constexpr int NT = (MP > 8) ? 2 : 1;       // 8-wide activation tiles (planes form)
     constexpr int NACC = COLS ? 2 : NT * 4;
     constexpr int KSL = (16 / TP2 < GS) ? 16 / TP2 : GS;  // K slices per tile
     constexpr int GPW = GS / KSL;              // groups per warp per stage
-    constexpr int S_PITCH = (GS + 4) * 4;      // bytes per row of the scale tile (80 / 48)
+    constexpr int ATOMS = GS / 8;              // 128-byte swizzle atoms per weight row per stage
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, t = lane & 3;
+    TRACE(0);
 
-    const int r0 = (int)(((long long)N * blockIdx.x) / gridDim.x);
-    const int r1 = (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x);
+    // N * gridDim.x < 2^31 is checked on the host: 32-bit division is enough
+    const int r0 = (int)(((unsigned)N * blockIdx.x) / gridDim.x);
+    const int r1 = (int)(((unsigned)N * (blockIdx.x + 1)) / gridDim.x);
     if (r0 >= r1) return;
     const int rb_rows = g.tiles * 16;
     const int n_rb = (r1 - r0 + rb_rows - 1) / rb_rows;
     const int k_stages = K / (GS * 32);
     const int total = n_rb * k_stages;
-    const int groups = K / 32;
-    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
-    float *red = reinterpret_cast<float *>(smem + (size_t)g.stages * g.stage_bytes);
+    const uint32_t ring_bytes = (uint32_t)g.stages * g.stage_bytes;
+    float *red = reinterpret_cast<float *>(smem + ring_bytes);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_full = smem_base + ring_bytes + 16 * 8 * 32 * 4;
+    const uint32_t bar_empty = bar_full + 8 * 8;
+    unsigned char *dig = smem + ring_bytes + 16 * 8 * 32 * 4 + 2 * 8 * 8;  // FUSEQ: resident blobs
+    // byte offset of the digit blob relative to the stage base (per-stage copy) or to `dig`
+    const uint32_t b_off = FUSEQ ? 0u : (uint32_t)(g.w_bytes + g.s_bytes);
 
-    // ---- producer state: every thread owns up to 4 weight chunks, 1 scale chunk and
-    // ---- 2 digit-blob chunks per stage; pointers advance by one stage of K per issue
-    const int wchunks = rb_rows * GS;
-    const uint8_t *w_ptr[4];
-    uint32_t w_dst[4];
-    int w_row[4];
-    unsigned w_ok = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int i = tid + 512 * j;
-        const int r = i / GS, c = i % GS;
-        w_row[j] = (i < wchunks) ? r : -1;
-        w_dst[j] = (c >> 3) * (rb_rows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-        w_ptr[j] = wq + c * 16;
+    if (tid == 0) {
+        for (int i = 0; i < g.stages; ++i) {
+            mbar_init(bar_full + i * 8, 1);
+            mbar_init(bar_empty + i * 8, FAST_CONSUMER_WARPS);
+        }
+        mbar_fence_init();
     }
-    const int s_row = (tid < rb_rows * (GS / 4)) ? tid / (GS / 4) : -1;
-    const uint32_t s_dst = g.w_bytes + (tid / (GS / 4)) * S_PITCH + (tid % (GS / 4)) * 16;
-    const float *s_ptr = scales + (tid % (GS / 4)) * 4;
-    bool s_ok = false;
-    const int bchunks = g.q.blob_bytes / 16;
-    const uint32_t b_off = g.w_bytes + g.s_bytes;
+    __syncthreads();
+    TRACE(1);
 
-    int p_slot = 0, p_ks = 0, p_rb = 0;  // next stage to issue
-    auto issue = [&]() {
-        if (p_ks == 0) {  // (re)aim the pointers at the first K stage of row block p_rb
-            const int row0 = r0 + p_rb * rb_rows;
-            w_ok = 0;
+    if (warp == FAST_CONSUMER_WARPS) {
+        // ---------------- producer: one thread drives the TMA ring ----------------
+        if (lane == 0) {
+            const uint32_t tx = (uint32_t)(g.w_bytes + g.s_bytes + (FUSEQ ? 0 : g.q.blob_bytes));
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_w));
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_s));
+            int slot = 0, ks = 0, rb = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int it = 0; it < total && alive; ++it) {
+                if (it >= g.stages) alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
+                if (!alive) break;
+                const uint32_t st = smem_base + (uint32_t)slot * g.stage_bytes;
+                const uint32_t full = bar_full + slot * 8;
+                const int row0 = r0 + rb * rb_rows;
+                mbar_expect_tx(full, tx);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int row = row0 + w_row[j];
-                const bool ok = (w_row[j] >= 0) && (row < r1);
-                w_ok |= (ok ? 1u : 0u) << j;
-                const int i = tid + 512 * j;
-                w_ptr[j] = wq + (size_t)(ok ? row : r0) * (K / 2) + (i % GS) * 16;
+                for (int a = 0; a < ATOMS; ++a)
+                    tma_load_2d(st + a * (rb_rows * 128), &tm_w, ks * (GS * 16) + a * 128, row0, full);
+                tma_load_2d(st + g.w_bytes, &tm_s, ks * GS, row0, full);
+                if constexpr (!FUSEQ)
+                    bulk_load(st + b_off, blobs + (size_t)ks * g.q.blob_bytes, g.q.blob_bytes, full);
+                if (++slot == g.stages) { slot = 0; phase ^= 1u; }
+                if (++ks == k_stages) { ks = 0; ++rb; }
             }
-            const int srow = row0 + s_row;
-            s_ok = (s_row >= 0) && (srow < r1);
-            s_ptr = scales + (size_t)(s_ok ? srow : r0) * groups + (tid % (GS / 4)) * 4;
+            // A consumer that gave up leaves copies unobserved: wait (bounded) for every
+            // stage this thread armed before the CTA may exit.
+            if (!alive) {
+                for (int i = 0; i < g.stages; ++i) mbar_wait(bar_full + i * 8, 0, nullptr);
+            }
         }
-        const uint32_t st = smem_base + (uint32_t)p_slot * g.stage_bytes;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (w_row[j] >= 0) cp_async16(st + w_dst[j], w_ptr[j], (w_ok >> j) & 1u);
-            w_ptr[j] += GS * 16;
-        }
-        if (s_row >= 0) cp_async16(st + s_dst, s_ptr, s_ok);
-        s_ptr += GS;
-        const unsigned char *bsrc = blobs + (size_t)p_ks * g.q.blob_bytes;
-        for (int i = tid; i < bchunks; i += 512) cp_async16(st + b_off + i * 16, bsrc + i * 16, true);
-        if (++p_slot == g.stages) p_slot = 0;
-        if (++p_ks == k_stages) { p_ks = 0; ++p_rb; }
-    };
-
-    for (int p = 0; p < g.stages - 1; ++p) {
-        if (p < total) issue();
-        cp_async_commit();
+        return;
     }
 
+    // ---------------- consumers ----------------
+    if constexpr (FUSEQ) {
+        // quantise the activations while the first weight stages are in flight
+        const int slots = quant_slots(g.q);
+        const int items = (K / 32) * slots;
+        constexpr int QUADS = FAST_CONSUMER_WARPS * 8;
+        const int rounds = (items + QUADS - 1) / QUADS;
+        for (int r = 0; r < rounds; ++r) {
+            const int item = r * QUADS + (tid >> 2);
+            const bool valid = item < items;
+            const int Gabs = valid ? item % (K / 32) : 0, m = valid ? item / (K / 32) : 0;
+            quantize_group(m < M ? act + (size_t)m * K + Gabs * 32 + 8 * t : nullptr, dig, g.q, Gabs,
+                           m, t, valid);
+        }
+        named_bar_sync(1, FAST_CONSUMER_WARPS * 32);
+    }
     const int tile = warp % TP2;
     const int kslice = warp / TP2;
     const bool active = (tile < g.tiles) && (kslice < KSL);
     const int G0 = kslice * GPW;  // first group of this warp inside a stage
+    const int rowA = tile * 16 + gq;  // the second row (rowA + 8) has the same swizzle phases
 
-    // ---- consumer offsets, constant for the whole kernel (relative to the stage base) ----
-    // weight word of (row gq of this warp's tile, group G0+gi, thread-in-quad t); the row 8
-    // below is 1024 bytes further with the same swizzle phase.
+    // offsets relative to the stage base, constant for the whole kernel
     uint32_t w_off[GPW];
 #pragma unroll
     for (int gi = 0; gi < GPW; ++gi) {
         const int G = G0 + gi;
-        w_off[gi] = (uint32_t)(G >> 3) * (rb_rows * 128) + (uint32_t)(tile * 16 + gq) * 128 +
-                    ((((uint32_t)G & 7u) ^ (uint32_t)gq) << 4) + t * 4;
+        w_off[gi] = (uint32_t)(G >> 3) * (rb_rows * 128) + (uint32_t)rowA * 128 +
+                    ((((uint32_t)G & 7u) ^ (uint32_t)(rowA & 7)) << 4) + t * 4;
     }
-    const uint32_t sA_off = g.w_bytes + (uint32_t)(tile * 16 + gq) * S_PITCH + G0 * 4;
-    // columns form: one uint4 per unit; planes form: h0 / h1 / meta
+    // scale tile: 16-byte chunk j of a row sits at chunk j ^ phase (TMA 64B / 32B swizzle)
+    const uint32_t s_phase = (GS == 16) ? ((rowA >> 1) & 3) : ((rowA >> 2) & 1);
+    const uint32_t s_row = g.w_bytes + (uint32_t)rowA * (GS * 4);
+    const int fc = COLS ? g.q.ms : 0;  // columns stored per group (columns form)
     const int mslot = (MP < 8) ? min(gq, g.q.ms - 1) : gq;
-    const uint32_t f_off = COLS ? b_off + (uint32_t)((G0 * 8 + gq) * 4 + t) * 16
+    const uint32_t f_off = COLS ? b_off + (uint32_t)((G0 * fc + (gq & (fc - 1))) * 4 + t) * 16
                                 : b_off + (uint32_t)((G0 * g.q.ms + mslot) * 4 + t) * 16;
     const uint32_t h1_off = b_off + g.q.off_h1 + (uint32_t)((G0 * g.q.ms + mslot) * 4 + t) * 8;
     const uint32_t mt_off = b_off + g.q.off_meta + (uint32_t)(G0 * g.q.mc + 2 * t) * 8;
-    const uint32_t f_step = COLS ? 8 * 4 * 16 : g.q.ms * 4 * 16;  // bytes per group
+    const uint32_t f_step = COLS ? fc * 4 * 16 : g.q.ms * 4 * 16;  // bytes per group
     const uint32_t h1_step = g.q.ms * 4 * 8, mt_step = g.q.mc * 8;
     const int mul_hi = (t & 1) ? 1 : 65536;  // columns form: plane weight of this thread's c0
 
@@ -424,20 +488,24 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
 #pragma unroll
     for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
 
-    int c_slot = 0, c_ks = 0, c_rb = 0;  // stage being consumed
+    int c_slot = 0, c_ks = 0, c_rb = 0;
+    uint32_t c_phase = 0;
+    bool dead = false;  // a wait ran out: keep walking the loop (the named barriers below
+                        // still need this warp) but stop waiting and computing
     for (int it = 0; it < total; ++it) {
-        cp_async_wait_dyn(g.stages - 2);
-        __syncthreads();
-        if (it + g.stages - 1 < total) issue();
-        cp_async_commit();
-        if (active) {
+        if (!dead) dead = !mbar_wait(bar_full + c_slot * 8, c_phase, status);
+        TRACE(2 + 2 * it);
+        if (active && !dead) {
             const unsigned char *st = smem + (size_t)c_slot * g.stage_bytes;
+            // digit blob of this K stage: inside the stage, or in the resident copy
+            const unsigned char *db = FUSEQ ? dig + (size_t)c_ks * g.q.blob_bytes : st;
             float sA[GPW], sB[GPW];
             if constexpr (GPW % 4 == 0) {
 #pragma unroll
                 for (int gi = 0; gi < GPW; gi += 4) {
-                    const uint4 x = lds128(st, sA_off + gi * 4);
-                    const uint4 y = lds128(st, sA_off + 8 * S_PITCH + gi * 4);
+                    const uint32_t ch = ((((uint32_t)(G0 + gi) >> 2) ^ s_phase) << 4);
+                    const uint4 x = lds128(st, s_row + ch);
+                    const uint4 y = lds128(st, s_row + 8 * (GS * 4) + ch);
                     sA[gi] = __uint_as_float(x.x); sA[gi + 1] = __uint_as_float(x.y);
                     sA[gi + 2] = __uint_as_float(x.z); sA[gi + 3] = __uint_as_float(x.w);
                     sB[gi] = __uint_as_float(y.x); sB[gi + 1] = __uint_as_float(y.y);
@@ -446,8 +514,10 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
             } else {
 #pragma unroll
                 for (int gi = 0; gi < GPW; ++gi) {
-                    sA[gi] = lds_f32(st, sA_off + gi * 4);
-                    sB[gi] = lds_f32(st, sA_off + 8 * S_PITCH + gi * 4);
+                    const uint32_t G = (uint32_t)(G0 + gi);
+                    const uint32_t o = (((G >> 2) ^ s_phase) << 4) + (G & 3u) * 4;
+                    sA[gi] = lds_f32(st, s_row + o);
+                    sB[gi] = lds_f32(st, s_row + 8 * (GS * 4) + o);
                 }
             }
 #pragma unroll
@@ -459,7 +529,7 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
                 a[2] = nib_u8(wA >> 4);
                 a[3] = nib_u8(wB >> 4);
                 if constexpr (COLS) {
-                    const uint4 f = lds128(st, f_off + gi * f_step);
+                    const uint4 f = lds128(db, f_off + gi * f_step);
                     int c[4];
                     mma_u8s8(c, a, f.x, f.y, 0, 0, 0, 0);
                     const int vA = c[0] * mul_hi + (c[1] * 256 + (int)f.w);
@@ -470,9 +540,9 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
                 } else {
 #pragma unroll
                     for (int n = 0; n < NT; ++n) {
-                        const uint4 h0 = lds128(st, f_off + gi * f_step + n * (8 * 4 * 16));
-                        const uint2 h1 = lds64(st, h1_off + gi * h1_step + n * (8 * 4 * 8));
-                        const uint4 mt = lds128(st, mt_off + gi * mt_step + n * (8 * 8));
+                        const uint4 h0 = lds128(db, f_off + gi * f_step + n * (8 * 4 * 16));
+                        const uint2 h1 = lds64(db, h1_off + gi * h1_step + n * (8 * 4 * 8));
+                        const uint4 mt = lds128(db, mt_off + gi * mt_step + n * (8 * 8));
                         int c2[4], c1[4], c0[4];
                         mma_u8s8(c2, a, h0.x, h0.y, 0, 0, 0, 0);
                         mma_u8s8(c1, a, h0.z, h0.w, 0, 0, 0, 0);
@@ -490,7 +560,11 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
                 }
             }
         }
-        if (++c_slot == g.stages) c_slot = 0;
+        // this warp is done reading the stage: hand the slot back to the producer
+        __syncwarp();
+        TRACE(3 + 2 * it);
+        if (lane == 0) mbar_arrive(bar_empty + c_slot * 8);
+        if (++c_slot == g.stages) { c_slot = 0; c_phase ^= 1u; }
         if (++c_ks == k_stages) {
             c_ks = 0;
             // end of a row block: combine the K slices in a fixed order and store
@@ -501,12 +575,12 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
             }
 #pragma unroll
             for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
-            __syncthreads();
+            named_bar_sync(1, FAST_CONSUMER_WARPS * 32);
             const int row0 = r0 + c_rb * rb_rows;
             if constexpr (COLS) {
                 // element (tile, half, gq, m): sum over K slices and the thread pair t=2m,2m+1
                 const int items = g.tiles * 2 * 8 * MP;
-                for (int i = tid; i < items; i += 512) {
+                for (int i = tid; i < items; i += FAST_CONSUMER_WARPS * 32) {
                     const int m = i % MP, q8 = (i / MP) & 7, half = (i / (MP * 8)) & 1, tl = i / (MP * 16);
                     float v = 0.0f;
                     for (int ks = 0; ks < KSL; ++ks) {
@@ -518,7 +592,7 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
                 }
             } else {
                 const int items = g.tiles * NACC * 32;
-                for (int i = tid; i < items; i += 512) {
+                for (int i = tid; i < items; i += FAST_CONSUMER_WARPS * 32) {
                     const int l = i & 31, j = (i >> 5) % NACC, tl = (i >> 5) / NACC;
                     float v = 0.0f;
                     for (int ks = 0; ks < KSL; ++ks)
@@ -529,10 +603,10 @@ int4_gemv_fast_kernel(const uint8_t *__restrict__ wq, const float *__restrict__ 
                 }
             }
             ++c_rb;
-            // `red` is next written after at least one more __syncthreads (top of the loop)
+            TRACE(30);
+            if (c_rb < n_rb) named_bar_sync(1, FAST_CONSUMER_WARPS * 32);  // `red` is reused
         }
     }
-    cp_async_wait_dyn(0);
 }
 
 // ---------------------------------------------------------------------------
@@ -555,14 +629,17 @@ size_t int4_gemv_scratch_bytes(size_t m, size_t k) {
 }
 
 bool int4_gemv_fast_supported(size_t m, size_t n, size_t k, size_t gs) {
-    return gs == 32 && k % 256 == 0 && k >= 256 && m >= 1 && m <= 16 && n >= 1 &&
-           n < (1u << 30) && k < (1u << 24);
+    return tensor_map_encoder() != nullptr && gs == 32 && k % 256 == 0 && k >= 256 && m >= 1 &&
+           m <= 16 && n >= 1 && n < (1u << 22) && k < (1u << 24);
 }
 
-template <int MP, int GS, int TP2>
+// Largest resident digit copy the fused-quantisation variant keeps in shared memory.
+constexpr int FUSEQ_MAX_DIGIT_BYTES = 72 * 1024;
+
+template <int MP, int GS, int TP2, bool FUSEQ>
 static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales,
-                       const unsigned char *blobs, float *out, int M, int N, int K,
-                       const QuantLayout &q) {
+                       const unsigned char *blobs, const float *act, float *out, int M, int N,
+                       int K, const QuantLayout &q) {
     const int grid = ctx->sm_count;
     const int rows_per_cta = (N + grid - 1) / grid;
     FastGeom g;
@@ -570,13 +647,25 @@ static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scale
     g.tiles = min(TP2, (rows_per_cta + 15) / 16);
     const int rb_rows = g.tiles * 16;
     g.w_bytes = rb_rows * GS * 16;
-    g.s_bytes = rb_rows * (GS + 4) * 4;  // 80- or 48-byte rows land on distinct banks
-    g.stage_bytes = ((g.w_bytes + g.s_bytes + q.blob_bytes + 1023) / 1024) * 1024;
+    g.s_bytes = rb_rows * GS * 4;
+    const int digit_bytes = FUSEQ ? (K / (32 * GS)) * q.blob_bytes : 0;
+    g.stage_bytes = ((g.w_bytes + g.s_bytes + (FUSEQ ? 0 : q.blob_bytes) + 1023) / 1024) * 1024;
     const int red_bytes = 16 * 8 * 32 * 4;
-    const int budget = 227 * 1024 - red_bytes - 1024;
+    const int bar_bytes = 2 * 8 * 8;
+    const int budget = 227 * 1024 - red_bytes - bar_bytes - digit_bytes - 1024;
     g.stages = max(2, min(8, budget / g.stage_bytes));
-    const int smem = g.stages * g.stage_bytes + red_bytes;
-    auto kern = int4_gemv_fast_kernel<MP, GS, TP2>;
+    const int smem = g.stages * g.stage_bytes + red_bytes + bar_bytes + digit_bytes;
+    // tensor maps: weights as bytes [N][K/2], box [rb_rows][128] with the 128-byte swizzle;
+    // scales as f32 [N][K/32], box [rb_rows][GS] with the swizzle that matches its width
+    CUtensorMap tm_w, tm_s;
+    int rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, (uint64_t)N, (uint64_t)K / 2,
+                       (uint64_t)K / 2, (uint32_t)rb_rows, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = encode_2d(&tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, scales, (uint64_t)N, (uint64_t)K / 32,
+                   (uint64_t)K / 8, (uint32_t)rb_rows, GS,
+                   GS == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc) return rc;
+    auto kern = int4_gemv_fast_kernel<MP, GS, TP2, FUSEQ>;
     static int smem_set[16] = {0};  // per device: opt-in shared memory size already raised
     if (ctx->device >= 16 || !smem_set[ctx->device]) {
         YSCV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -584,7 +673,8 @@ static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scale
         if (ctx->device < 16) smem_set[ctx->device] = 1;
     }
     ctx->prof_begin();
-    kern<<<grid, 512, smem, ctx->stream>>>(wq, scales, blobs, out, M, N, K, g);
+    kern<<<grid, FAST_THREADS, smem, ctx->stream>>>(tm_w, tm_s, blobs, act, out, M, N, K, g,
+                                                    ctx->d_status);
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
@@ -593,11 +683,26 @@ static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scale
 
 template <int MP, int GS>
 static int launch_fast_tp(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales,
-                          const unsigned char *blobs, float *out, int M, int N, int K,
-                          const QuantLayout &q) {
+                          const float *act, float *out, int M, int N, int K, void *scratch) {
+    const QuantLayout q = quant_layout(MP, GS);
     const int rows_per_cta = (N + ctx->sm_count - 1) / ctx->sm_count;
-    if (rows_per_cta <= 32) return launch_fast<MP, GS, 2>(ctx, wq, scales, blobs, out, M, N, K, q);
-    return launch_fast<MP, GS, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
+    const bool small = rows_per_cta <= 32;
+    if constexpr (MP <= 4) {
+        // few activation rows: every CTA quantises them itself, no separate launch
+        if ((K / (32 * GS)) * q.blob_bytes <= FUSEQ_MAX_DIGIT_BYTES) {
+            ctx->last_kernel = "int4_gemv_fast(imma,tma,fused-quant)";
+            return small ? launch_fast<MP, GS, 2, true>(ctx, wq, scales, nullptr, act, out, M, N, K, q)
+                         : launch_fast<MP, GS, 8, true>(ctx, wq, scales, nullptr, act, out, M, N, K, q);
+        }
+    }
+    unsigned char *blobs = reinterpret_cast<unsigned char *>(scratch);
+    const int items = (K / 32) * quant_slots(q);
+    act_quant_kernel<<<(items * 4 + 127) / 128, 128, 0, ctx->stream>>>(act, blobs, M, K, q);
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    ctx->last_kernel = "int4_gemv_fast(imma,tma)";
+    return small ? launch_fast<MP, GS, 2, false>(ctx, wq, scales, blobs, act, out, M, N, K, q)
+                 : launch_fast<MP, GS, 8, false>(ctx, wq, scales, blobs, act, out, M, N, K, q);
 }
 
 int int4_gemv_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, const float *act,
@@ -605,23 +710,15 @@ int int4_gemv_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, c
     const int M = (int)m, N = (int)n, K = (int)k;
     const int MP = padded_m(M);
     const int GS = stage_groups(MP, K);
-    const QuantLayout q = quant_layout(MP, GS);
-    unsigned char *blobs = reinterpret_cast<unsigned char *>(scratch);
-    const int items = (K / 32) * ((MP <= 2) ? 2 : max(q.ms, q.mc));
-    const int qblocks = min((items + 7) / 8, 4 * ctx->sm_count);
-    act_quant_kernel<<<qblocks, 256, 0, ctx->stream>>>(act, blobs, M, K, q);
-    YSCV_CUDA_TRY(cudaGetLastError());
-    ctx->launches++;
-    ctx->last_kernel = "int4_gemv_fast(imma,cp.async)";
     switch (MP) {
-        case 1: return GS == 16 ? launch_fast_tp<1, 16>(ctx, wq, scales, blobs, out, M, N, K, q)
-                                : launch_fast_tp<1, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
-        case 2: return GS == 16 ? launch_fast_tp<2, 16>(ctx, wq, scales, blobs, out, M, N, K, q)
-                                : launch_fast_tp<2, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
-        case 4: return GS == 16 ? launch_fast_tp<4, 16>(ctx, wq, scales, blobs, out, M, N, K, q)
-                                : launch_fast_tp<4, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
-        case 8: return launch_fast_tp<8, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
-        default: return launch_fast_tp<16, 8>(ctx, wq, scales, blobs, out, M, N, K, q);
+        case 1: return GS == 16 ? launch_fast_tp<1, 16>(ctx, wq, scales, act, out, M, N, K, scratch)
+                                : launch_fast_tp<1, 8>(ctx, wq, scales, act, out, M, N, K, scratch);
+        case 2: return GS == 16 ? launch_fast_tp<2, 16>(ctx, wq, scales, act, out, M, N, K, scratch)
+                                : launch_fast_tp<2, 8>(ctx, wq, scales, act, out, M, N, K, scratch);
+        case 4: return GS == 16 ? launch_fast_tp<4, 16>(ctx, wq, scales, act, out, M, N, K, scratch)
+                                : launch_fast_tp<4, 8>(ctx, wq, scales, act, out, M, N, K, scratch);
+        case 8: return launch_fast_tp<8, 8>(ctx, wq, scales, act, out, M, N, K, scratch);
+        default: return launch_fast_tp<16, 8>(ctx, wq, scales, act, out, M, N, K, scratch);
     }
 }
 
