@@ -129,6 +129,65 @@ int yscv_cuda_pack_int4_dev(yscv_cuda_ctx *ctx, const float *d_weights, size_t m
                             size_t k, size_t group_size, uint8_t *d_packed,
                             float *d_scales);
 
+/* ---- int8 GEMM: MatMulInteger / QLinearMatMul ------------------------------ */
+
+/* int8_matmul_dispatch (crates/yscv-kernels/src/ops/int8_matmul.rs:2407-2413): host
+ * a [m,k], b [k,n] row-major i8 -> host out [m,n] i32. B is transposed on the GPU on
+ * every call, as the reference's non-prepacked entry point does on the CPU. */
+int yscv_cuda_int8_matmul(yscv_cuda_ctx *ctx, const int8_t *a, const int8_t *b, size_t m,
+                          size_t k, size_t n, int32_t *out);
+
+/* pack_i8_b_for_matmul / PackedI8B (int8_matmul.rs:128-191): uploads b [k,n] once and
+ * keeps B^T (K-major, the tensor-core operand layout) and its column sums in HBM.
+ * _dev takes b already in device memory. */
+int yscv_cuda_pack_i8_b_for_matmul(yscv_cuda_ctx *ctx, const int8_t *b, size_t k, size_t n,
+                                   yscv_cuda_i8b **out);
+int yscv_cuda_pack_i8_b_dev(yscv_cuda_ctx *ctx, const int8_t *d_b, size_t k, size_t n,
+                            yscv_cuda_i8b **out);
+void yscv_cuda_i8b_free(yscv_cuda_i8b *b);
+size_t yscv_cuda_i8b_k(const yscv_cuda_i8b *b); /* PackedI8B::k() */
+size_t yscv_cuda_i8b_n(const yscv_cuda_i8b *b); /* PackedI8B::n() */
+
+/* int8_matmul_prepacked_dispatch (int8_matmul.rs:2420-2425): host a [m,k] -> host out. */
+int yscv_cuda_int8_matmul_prepacked(yscv_cuda_ctx *ctx, const int8_t *a, const yscv_cuda_i8b *b,
+                                    size_t m, int32_t *out);
+/* same on device memory, asynchronous on the context's stream */
+int yscv_cuda_int8_matmul_prepacked_dev(yscv_cuda_ctx *ctx, const int8_t *d_a,
+                                        const yscv_cuda_i8b *b, size_t m, int32_t *d_out);
+
+/* Epilogue of QLinearMatMul: the requant_scalar contract
+ * (crates/yscv-kernels/src/ops/int8_requant.rs:143-169): q = saturate(round((float)acc *
+ * composite + y_zero_point)), separate multiply and add, to [qmin, qmax] ([-128,127] for
+ * int8 output, [0,255] for uint8). round_mode 0 = ties to even (ONNX, the kernel-level
+ * contract), 1 = half away from zero (what the runner's exec_qlinear_matmul does with
+ * f32::round, crates/yscv-onnx/src/runner/linear.rs:481-485). */
+typedef struct {
+    int a_is_unsigned;    /* A holds uint8 instead of int8 */
+    int32_t a_zero_point; /* exact: acc = sum_k (a - a_zp) * b, any value */
+    float composite;      /* (a_scale * b_scale) / y_scale, computed in f32 by the caller */
+    float y_zero_point;
+    int32_t qmin, qmax;
+    int round_mode;
+} yscv_cuda_requant;
+
+/* exec_qlinear_matmul (crates/yscv-onnx/src/runner/linear.rs:438-537) with b_zero_point 0:
+ * a [m,k] bytes, prepacked b, out [m,n] one byte per element (uint8 or int8 per qmin/qmax).
+ * Non-zero a_zero_point is computed exactly in integers (the reference falls back to an
+ * fp32 GEMM there). */
+int yscv_cuda_qlinear_matmul(yscv_cuda_ctx *ctx, const void *a, const yscv_cuda_i8b *b, size_t m,
+                             const yscv_cuda_requant *rq, void *out);
+int yscv_cuda_qlinear_matmul_dev(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b,
+                                 size_t m, const yscv_cuda_requant *rq, void *d_out);
+
+/* exec_matmul_integer (crates/yscv-onnx/src/runner/linear.rs:648-737) with b_zero_point 0:
+ * out [m,n] i32 = (a - a_zero_point) x b, exact. */
+int yscv_cuda_matmul_integer(yscv_cuda_ctx *ctx, const void *a, int a_is_unsigned,
+                             int32_t a_zero_point, const yscv_cuda_i8b *b, size_t m,
+                             int32_t *out);
+int yscv_cuda_matmul_integer_dev(yscv_cuda_ctx *ctx, const void *d_a, int a_is_unsigned,
+                                 int32_t a_zero_point, const yscv_cuda_i8b *b, size_t m,
+                                 int32_t *d_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,178 @@
+"""Parity of the tcgen05 int8 GEMM and its MatMulInteger / QLinearMatMul epilogues
+against the CPU oracle, through the C ABI. Integer results are compared bit for bit."""
+import numpy as np
+import pytest
+
+import yscv_b200
+from yscv_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+# crates/yscv-kernels/src/ops/int8_matmul.rs:2458-2465
+def test_known_small_case(ctx):
+    out = ctx.int8_matmul(np.array([1, 2, 3, 4], np.int8), np.array([5, 6, 7, 8], np.int8), 2, 2, 2)
+    assert out.ravel().tolist() == [19, 22, 43, 50]
+
+
+# int8_matmul.rs:2502-2509
+def test_extreme_values(ctx):
+    a = np.full(128, -128, np.int8)
+    assert ctx.int8_matmul(a, a, 1, 128, 1)[0, 0] == 128 * 128 * 128
+
+
+# int8_matmul.rs:2467-2500: the reference's own shape lists, same LCG seeds, bit-exact
+@pytest.mark.parametrize("m,k,n", [(1, 1, 1), (2, 3, 4), (4, 16, 8), (5, 17, 6), (8, 64, 8)])
+def test_dispatch_matches_scalar(ctx, oracle, m, k, n):
+    a = oracle.lcg_i8(0xDEAD ^ (m * k), m * k)
+    b = oracle.lcg_i8(0xBEEF ^ (k * n), k * n)
+    assert np.array_equal(ctx.int8_matmul(a, b, m, k, n), oracle.int8_matmul(a, b, m, k, n))
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 1, 1), (1, 17, 5), (3, 31, 7), (4, 64, 16), (8, 127, 33), (16, 128, 64)])
+def test_prepacked_matches_scalar(ctx, oracle, m, k, n):
+    a = oracle.lcg_i8(0xA11CE ^ (m * k), m * k)
+    b = oracle.lcg_i8(0xB0B ^ (k * n), k * n)
+    packed = ctx.pack_i8_b(b, k, n)
+    assert (packed.k, packed.n) == (k, n)
+    assert np.array_equal(ctx.int8_matmul_prepacked(a, packed, m), oracle.int8_matmul(a, b, m, k, n))
+    packed.free()
+
+
+# ragged tiles: every tail of the 128 x {64,128,256} x 128 tiling, multi-tile persistence
+@pytest.mark.parametrize("m,k,n", [(129, 144, 65), (1, 4096, 257), (300, 272, 513), (127, 1000, 130),
+                                   (257, 128, 1024), (640, 2048, 768), (2048, 512, 4096)])
+def test_ragged_shapes(ctx, oracle, m, k, n):
+    a = synth.uniform_int(5, 0, m * k, -128, 127).astype(np.int8)
+    b = synth.uniform_int(5, 1, k * n, -128, 127).astype(np.int8)
+    packed = ctx.pack_i8_b(b, k, n)
+    got = ctx.int8_matmul_prepacked(a, packed, m)
+    want = oracle.int8_matmul_prepacked(a, oracle.transpose_b_i8(b, k, n), m, k, n, simd=True, threads=8)
+    assert np.array_equal(got, want), ctx.last_kernel()
+    assert ctx.device_status() == 0
+    packed.free()
+
+
+# BASELINE config 1: MatMulInteger, A u8 [64,1024] with a_zero_point 128, B i8 [1024,1024], seed 0
+def test_config1_matmul_integer(ctx, oracle):
+    m, k, n = 64, 1024, 1024
+    a = synth.uniform_int(0, 0, m * k, 0, 255).astype(np.uint8)
+    b = synth.uniform_int(0, 1, k * n, -127, 127).astype(np.int8)
+    packed = ctx.pack_i8_b(b, k, n)
+    got = ctx.matmul_integer(a, packed, m, a_zp=128)
+    # u8 with zero point 128 == i8 with zero point 0 after flipping the top bit
+    want = oracle.int8_matmul((a ^ 0x80).view(np.int8), b, m, k, n)
+    assert np.array_equal(got, want)
+    # and the runner-level semantics (f32-encoded operands, exact integer result)
+    runner = oracle.runner_matmul_integer(a.astype(np.float32), b.astype(np.float32), m, k, n, a_zp=128.0)
+    assert np.array_equal(got.astype(np.float32), runner)
+    # signed operand, zero point 0: the reference's int8 fast path
+    a8 = (a ^ 0x80).view(np.int8)
+    assert np.array_equal(ctx.matmul_integer(a8, packed, m), want)
+    packed.free()
+
+
+# crates/yscv-onnx/src/tests/coverage.rs:359-390 (zero-point offset known answer)
+def test_matmul_integer_zero_point_known_answer(ctx):
+    packed = ctx.pack_i8_b(np.array([1, 0, 0, 1], np.int8), 2, 2)
+    got = ctx.matmul_integer(np.array([10, 11, 12, 13], np.uint8), packed, 2, a_zp=10)
+    assert got.ravel().tolist() == [0, 1, 2, 3]
+    packed.free()
+
+
+# crates/yscv-kernels/src/ops/int8_requant.rs:1195-1227: round-half-even table and saturation
+def test_requant_known_answers(ctx):
+    one = ctx.pack_i8_b(np.array([1], np.int8), 1, 1)
+    acc = np.array([1, -1, 3, -3, 5, -5, 7, -7], np.int8)
+    got = ctx.qlinear_matmul(acc, one, 8, ctx.requant(0.5, 0.0, -128, 127))
+    assert got.ravel().tolist() == [0, 0, 2, -2, 2, -2, 4, -4]
+    away = ctx.qlinear_matmul(acc, one, 8, ctx.requant(0.5, 0.0, -128, 127, round_mode=1))
+    assert away.ravel().tolist() == [1, -1, 2, -2, 3, -3, 4, -4]
+    big = ctx.pack_i8_b(np.full(128, 127, np.int8), 128, 1)
+    a = np.concatenate([np.full(128, 127, np.int8), np.full(128, -128, np.int8)])
+    sat = ctx.qlinear_matmul(a, big, 2, ctx.requant(0.001, 0.0, -128, 127))
+    assert sat.ravel().tolist() == [127, -128]
+    usat = ctx.qlinear_matmul(a, big, 2, ctx.requant(0.001, 128.0, 0, 255))
+    assert usat.ravel().tolist() == [255, 0]
+    one.free()
+    big.free()
+
+
+# crates/yscv-onnx/src/tests/qlinear.rs:150-194: the runner's QLinearMatMul (f32::round, i8 clamp)
+def test_runner_qlinear_matmul_case(ctx, oracle):
+    a_int = (np.arange(32) - 16).astype(np.int8)
+    b_int = ((np.arange(32) * 7) % 31 - 15).astype(np.int8)
+    composite = np.float32(np.float32(0.05) * np.float32(0.1)) / np.float32(0.25)
+    packed = ctx.pack_i8_b(b_int, 8, 4)
+    got = ctx.qlinear_matmul(a_int, packed, 4, ctx.requant(composite, 0.0, -128, 127, round_mode=1))
+    want = oracle.runner_qlinear_matmul_fast(a_int.astype(np.float32), b_int.astype(np.float32), 4, 8, 4,
+                                             0.05, 0.1, 0.25, 0.0)
+    assert np.array_equal(got.astype(np.float32), want)
+    packed.free()
+
+
+def config3_inputs(oracle, m, k, n):
+    af = synth.normal(2, 0, m * k, 1.0)
+    bf = synth.normal(2, 1, k * n, 0.02)
+    a = oracle.quantize_linear(af, np.float32(6.0 / 255.0), 128.0, unsigned=True)
+    b_scale = np.float32(np.max(np.abs(bf)) / np.float32(127.0))
+    b = oracle.quantize_tensor_symmetric(bf, b_scale)
+    composite = np.float32(np.float32(np.float32(6.0 / 255.0) * b_scale) / np.float32(0.05))
+    return a, b, composite
+
+
+# BASELINE config 3 (QLinearMatMul, uint8 in / uint8 out, y_zero_point 128), reduced and full size
+@pytest.mark.parametrize("m,k,n", [(256, 1024, 512), (2048, 4096, 4096)])
+def test_config3_qlinear_matmul(ctx, oracle, m, k, n):
+    a, b, composite = config3_inputs(oracle, m, k, n)
+    packed = ctx.pack_i8_b(b, k, n)
+    got = ctx.qlinear_matmul(a, packed, m, ctx.requant(composite, 128.0, 0, 255, a_unsigned=True, a_zp=128))
+    acc = oracle.int8_matmul_prepacked((a ^ 0x80).view(np.int8), oracle.transpose_b_i8(b, k, n), m, k, n,
+                                       simd=True, threads=8)
+    if m * k * n <= 2 ** 28:  # the scalar oracle proper where it finishes in seconds
+        assert np.array_equal(acc, oracle.int8_matmul((a ^ 0x80).view(np.int8), b, m, k, n))
+    want = oracle.requant_range(acc, composite, 128.0, 0, 255).astype(np.uint8)
+    assert got.dtype == np.uint8 and np.array_equal(got, want)
+    assert 0 < np.count_nonzero(got == 128) < got.size  # the output is not saturated garbage
+    # raw accumulators through the MatMulInteger epilogue, and a checksum of checksums
+    raw = ctx.matmul_integer(a, packed, m, a_zp=128)
+    assert np.array_equal(raw, acc)
+    lhs = raw.astype(np.int64).sum(axis=1)
+    rhs = (a.astype(np.int64) - 128).reshape(m, k) @ b.astype(np.int64).reshape(k, n).sum(axis=1)
+    assert np.array_equal(lhs, rhs)
+    assert ctx.device_status() == 0
+    packed.free()
+
+
+def test_device_form_and_determinism(ctx, oracle):
+    import torch
+    m, k, n = 512, 1024, 1024
+    a, b, composite = config3_inputs(oracle, m, k, n)
+    d_b = torch.from_numpy(b.reshape(k, n)).cuda()
+    packed = ctx.pack_i8_b_dev(d_b.data_ptr(), k, n)
+    d_a = torch.from_numpy(a.reshape(m, k)).cuda()
+    d_out = torch.empty(m, n, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    rq = ctx.requant(composite, 128.0, 0, 255, a_unsigned=True, a_zp=128)
+    ctx.qlinear_matmul_dev(d_a.data_ptr(), packed, m, rq, d_out.data_ptr())
+    ctx.synchronize()
+    first = d_out.cpu().numpy()
+    host = ctx.qlinear_matmul(a, packed, m, rq)
+    assert np.array_equal(first, host)
+    d_acc = torch.empty(m, n, dtype=torch.int32, device="cuda")
+    ctx.matmul_integer_dev(d_a.data_ptr(), True, 128, packed, m, d_acc.data_ptr())
+    ctx.synchronize()
+    want = (a.astype(np.int32).reshape(m, k) - 128) @ b.astype(np.int32).reshape(k, n)
+    assert np.array_equal(d_acc.cpu().numpy(), want)
+    packed.free()
+
+
+def test_bad_arguments(ctx):
+    with pytest.raises(yscv_b200.YscvCudaError):
+        ctx.pack_i8_b(np.zeros(0, np.int8), 0, 4)
+    packed = ctx.pack_i8_b(np.zeros(16, np.int8), 4, 4)
+    with pytest.raises(yscv_b200.YscvCudaError) as e:
+        ctx.qlinear_matmul(np.zeros(4, np.int8), packed, 1, ctx.requant(1.0, 0.0, -200, 127))
+    assert e.value.status == -1
+    assert ctx.int8_matmul_prepacked(np.zeros(0, np.int8), packed, 0).shape == (0, 4)
+    packed.free()

@@ -7,6 +7,8 @@ own and no CPU fallback.
 """
 from .lib import (  # noqa: F401
     Context,
+    I8B,
+    Requant,
     Int4Weight,
     YscvCudaError,
     load_library,

@@ -362,4 +362,160 @@ int yscv_cuda_int4_matmul(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
     return YSCV_CUDA_OK;
 }
 
+/* ---- int8 GEMM -------------------------------------------------------------- */
+
+static int i8b_create(yscv_cuda_ctx *ctx, const int8_t *d_b, size_t k, size_t n, yscv_cuda_i8b **out) {
+    const size_t kp = (k + 15) / 16 * 16;
+    void *bt = nullptr, *cs = nullptr;
+    YSCV_CUDA_TRY(cudaMalloc(&bt, n * kp));
+    cudaError_t e = cudaMalloc(&cs, n * sizeof(int32_t));
+    if (e != cudaSuccess) {
+        cudaFree(bt);
+        return fail(YSCV_CUDA_ERR_CUDA, "cudaMalloc(colsum): %s", cudaGetErrorString(e));
+    }
+    int rc = pack_i8_b(ctx, d_b, k, n, (int8_t *)bt, (int32_t *)cs, kp);
+    if (rc) {
+        cudaFree(bt);
+        cudaFree(cs);
+        return rc;
+    }
+    auto *h = new yscv_cuda_i8b();
+    h->d_bt = (int8_t *)bt;
+    h->d_colsum = (int32_t *)cs;
+    h->k = k;
+    h->n = n;
+    h->kp = kp;
+    h->device = ctx->device;
+    *out = h;
+    return YSCV_CUDA_OK;
+}
+
+static int check_i8_shape(size_t k, size_t n) {
+    if (k == 0 || n == 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "int8 GEMM needs k > 0 and n > 0");
+    if (k >= (1u << 30) || n >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "dimension too large");
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_pack_i8_b_dev(yscv_cuda_ctx *ctx, const int8_t *d_b, size_t k, size_t n,
+                            yscv_cuda_i8b **out) {
+    if (!ctx || !out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    *out = nullptr;
+    if (!d_b) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    int rc = check_i8_shape(k, n);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    return i8b_create(ctx, d_b, k, n, out);
+}
+
+int yscv_cuda_pack_i8_b_for_matmul(yscv_cuda_ctx *ctx, const int8_t *b, size_t k, size_t n,
+                                   yscv_cuda_i8b **out) {
+    if (!ctx || !out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    *out = nullptr;
+    if (!b) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    int rc = check_i8_shape(k, n);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    if ((rc = ctx->in1.reserve(k * n))) return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in1.ptr, b, k * n, cudaMemcpyHostToDevice, ctx->stream));
+    rc = i8b_create(ctx, (const int8_t *)ctx->in1.ptr, k, n, out);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YSCV_CUDA_OK;
+}
+
+void yscv_cuda_i8b_free(yscv_cuda_i8b *b) {
+    if (!b) return;
+    cudaSetDevice(b->device);
+    cudaFree(b->d_bt);
+    cudaFree(b->d_colsum);
+    delete b;
+}
+
+size_t yscv_cuda_i8b_k(const yscv_cuda_i8b *b) { return b ? b->k : 0; }
+size_t yscv_cuda_i8b_n(const yscv_cuda_i8b *b) { return b ? b->n : 0; }
+
+static int i8_gemm_dev(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_t m,
+                       void *d_out, int a_unsigned, int a_zp, const yscv_cuda_requant *rq) {
+    if (!ctx || !b) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (!d_a || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (m == 0) return YSCV_CUDA_OK;
+    if (m >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "dimension too large");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    if (rq) {
+        if (rq->qmin > rq->qmax || rq->qmin < -128 || rq->qmax > 255 || rq->qmax - rq->qmin > 255)
+            return fail(YSCV_CUDA_ERR_BAD_ARG, "requant range [%d,%d] does not fit one byte", rq->qmin, rq->qmax);
+        return int8_gemm(ctx, d_a, b, m, d_out, rq->a_is_unsigned, rq->a_zero_point, 1, rq->composite,
+                         rq->y_zero_point, rq->qmin, rq->qmax, rq->round_mode);
+    }
+    return int8_gemm(ctx, d_a, b, m, d_out, a_unsigned, a_zp, 0, 0.0f, 0.0f, 0, 0, 0);
+}
+
+// host A in, host output out (elem_bytes per output element)
+static int i8_gemm_host(yscv_cuda_ctx *ctx, const void *a, const yscv_cuda_i8b *b, size_t m, void *out,
+                        size_t elem_bytes, int a_unsigned, int a_zp, const yscv_cuda_requant *rq) {
+    if (!ctx || !b) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (!a || !out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (m == 0) return YSCV_CUDA_OK;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    const size_t ab = m * b->k, ob = m * b->n * elem_bytes;
+    int rc;
+    if ((rc = ctx->in0.reserve(ab)) || (rc = ctx->out0.reserve(ob))) return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in0.ptr, a, ab, cudaMemcpyHostToDevice, ctx->stream));
+    rc = i8_gemm_dev(ctx, ctx->in0.ptr, b, m, ctx->out0.ptr, a_unsigned, a_zp, rq);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(out, ctx->out0.ptr, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_int8_matmul_prepacked_dev(yscv_cuda_ctx *ctx, const int8_t *d_a, const yscv_cuda_i8b *b,
+                                        size_t m, int32_t *d_out) {
+    return i8_gemm_dev(ctx, d_a, b, m, d_out, 0, 0, nullptr);
+}
+
+int yscv_cuda_int8_matmul_prepacked(yscv_cuda_ctx *ctx, const int8_t *a, const yscv_cuda_i8b *b,
+                                    size_t m, int32_t *out) {
+    return i8_gemm_host(ctx, a, b, m, out, sizeof(int32_t), 0, 0, nullptr);
+}
+
+int yscv_cuda_int8_matmul(yscv_cuda_ctx *ctx, const int8_t *a, const int8_t *b, size_t m, size_t k,
+                          size_t n, int32_t *out) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    if (!a || !b || !out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (m == 0 || n == 0) return YSCV_CUDA_OK;
+    if (k == 0) {
+        memset(out, 0, m * n * sizeof(int32_t));
+        return YSCV_CUDA_OK;
+    }
+    yscv_cuda_i8b *packed = nullptr;
+    int rc = yscv_cuda_pack_i8_b_for_matmul(ctx, b, k, n, &packed);
+    if (rc) return rc;
+    rc = yscv_cuda_int8_matmul_prepacked(ctx, a, packed, m, out);
+    yscv_cuda_i8b_free(packed);
+    return rc;
+}
+
+int yscv_cuda_qlinear_matmul_dev(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_t m,
+                                 const yscv_cuda_requant *rq, void *d_out) {
+    if (!rq) return fail(YSCV_CUDA_ERR_BAD_ARG, "requant parameters are null");
+    return i8_gemm_dev(ctx, d_a, b, m, d_out, 0, 0, rq);
+}
+
+int yscv_cuda_qlinear_matmul(yscv_cuda_ctx *ctx, const void *a, const yscv_cuda_i8b *b, size_t m,
+                             const yscv_cuda_requant *rq, void *out) {
+    if (!rq) return fail(YSCV_CUDA_ERR_BAD_ARG, "requant parameters are null");
+    return i8_gemm_host(ctx, a, b, m, out, 1, 0, 0, rq);
+}
+
+int yscv_cuda_matmul_integer_dev(yscv_cuda_ctx *ctx, const void *d_a, int a_is_unsigned,
+                                 int32_t a_zero_point, const yscv_cuda_i8b *b, size_t m,
+                                 int32_t *d_out) {
+    return i8_gemm_dev(ctx, d_a, b, m, d_out, a_is_unsigned, a_zero_point, nullptr);
+}
+
+int yscv_cuda_matmul_integer(yscv_cuda_ctx *ctx, const void *a, int a_is_unsigned, int32_t a_zero_point,
+                             const yscv_cuda_i8b *b, size_t m, int32_t *out) {
+    return i8_gemm_host(ctx, a, b, m, out, sizeof(int32_t), a_is_unsigned, a_zero_point, nullptr);
+}
+
 }  // extern "C"

@@ -70,3 +70,12 @@ struct yscv_cuda_int4_weight {
     bool owns = false;
     int device = 0;
 };
+
+// PackedI8B resident in HBM: B^T [n][kp] (kp = k rounded up to 16, zero padded)
+// and the column sums of B over k.
+struct yscv_cuda_i8b {
+    int8_t *d_bt = nullptr;
+    int32_t *d_colsum = nullptr;
+    size_t k = 0, n = 0, kp = 0;
+    int device = 0;
+};

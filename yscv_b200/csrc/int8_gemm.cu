@@ -1,0 +1,399 @@
+// int8 x int8 -> int32 GEMM on the 5th-generation tensor cores (tcgen05, sm_100a),
+// with the MatMulInteger / QLinearMatMul epilogues fused behind it.
+//
+// Replaces int8_matmul_dispatch / int8_matmul_prepacked_dispatch and the
+// requantisation pass that follows them in the reference
+// (crates/yscv-kernels/src/ops/int8_matmul.rs:195-227, 2407-2425;
+//  crates/yscv-kernels/src/ops/int8_requant.rs:143-169;
+//  crates/yscv-onnx/src/runner/linear.rs:438-537, 648-737).
+//
+// Operands: A [M][K] row-major (i8, or u8 with a zero point), B prepacked once
+// as B^T [N][Kp] (K-major, Kp = K rounded up to 16, zero padded) together with
+// its column sums; both are exactly what the MMA wants: K-major tiles fetched by
+// TMA with the 128-byte swizzle. Integer accumulation is exact, so the result
+// is bit-identical to the scalar CPU kernel in any order.
+//
+// Kernel: persistent, one CTA per SM, 192 threads, warp-specialised:
+//   warp 0      TMA producer: A tile [128][128 B] + B tile [BN][128 B] per stage
+//   warp 1      allocates TMEM, issues tcgen05.mma.kind::i8 (M=128, N=BN, K=32,
+//               four per stage), commits stages back to the producer and
+//               finished accumulators to the epilogue
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, subtract
+//               a_zp * colsum[n], then either store int32 or requantise
+//               ((float)acc * composite + y_zp with separate multiply and add,
+//               round, saturate) and store bytes
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of
+// tile i overlaps the main loop of tile i+1. All mbarrier waits are bounded; a
+// wait that runs out sets the context's status word and every role falls through
+// to the common exit, where TMEM is released.
+#include "common.cuh"
+#include "kernels.cuh"
+#include "tma.cuh"
+
+namespace yscv {
+
+constexpr int G8_BM = 128;
+constexpr int G8_BK = 128;  // bytes of K per stage = one 128-byte swizzle row
+constexpr int G8_THREADS = 192;
+
+struct G8Params {
+    int M, N, K;            // logical sizes (K = padded K of the prepacked B)
+    int m_blocks, n_blocks, k_blocks;
+    int stages;
+    int a_unsigned;         // A holds u8
+    int a_zp;               // subtracted through a_zp * colsum[n]
+    int mode;               // 0: int32 out, 1: requantised byte out
+    float composite, y_zp;
+    int qmin, qmax;
+    int round_mode;         // 0: ties to even, 1: half away from zero
+    long long ldc;          // elements per output row
+};
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+
+// K-major operand tile in shared memory, 128-byte swizzle, rows 128 bytes apart,
+// 8-row groups 1024 bytes apart (what a TMA box [rows][128 B] with SWIZZLE_128B writes).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);        // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused, K-major swizzled)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset: 8 rows
+    d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(G8_THREADS, 1)
+int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const int32_t *__restrict__ colsum, void *__restrict__ out, G8Params p,
+                    int *__restrict__ status) {
+    constexpr int A_BYTES = G8_BM * G8_BK;  // 16 KB
+    constexpr int B_BYTES = BN * G8_BK;     // 32 / 16 KB
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bars = smem_base + (uint32_t)p.stages * STAGE_BYTES;
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * 8;
+    const uint32_t bar_tfull = bars + 16 * 8, bar_tempty = bars + 18 * 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)p.stages * STAGE_BYTES + 20 * 8);
+
+    const int tiles = p.m_blocks * p.n_blocks;
+
+    if (tid == 0) {
+        for (int i = 0; i < p.stages; ++i) {
+            mbar_init(bar_full + i * 8, 1);
+            mbar_init(bar_empty + i * 8, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tfull + i * 8, 1);
+            mbar_init(bar_tempty + i * 8, 4);  // one arrival per epilogue warp
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        // 2 x BN columns of TMEM (power of two >= 32); released at the common exit below
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(2 * BN));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_a));
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_b));
+            int slot = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+                const int mb = t % p.m_blocks, nb = t / p.m_blocks;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
+                    if (!alive) break;
+                    const uint32_t st = smem_base + (uint32_t)slot * STAGE_BYTES;
+                    const uint32_t full = bar_full + slot * 8;
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(st, &tm_a, kb * G8_BK, mb * G8_BM, full);
+                    tma_load_2d(st + A_BYTES, &tm_b, kb * G8_BK, nb * BN, full);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = (2u << 4) | ((p.a_unsigned ? 0u : 1u) << 7) | (1u << 10) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(G8_BM >> 4) << 24);
+            int slot = 0, abuf = 0;
+            uint32_t phase = 0, aphase = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+                // the epilogue must have drained this accumulator buffer
+                alive = mbar_wait(bar_tempty + abuf * 8, aphase ^ 1u, status);
+                if (!alive) break;
+                tc_fence_after();
+                const uint32_t tacc = tmem_base + (uint32_t)abuf * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    alive = mbar_wait(bar_full + slot * 8, phase, status);
+                    if (!alive) break;
+                    tc_fence_after();
+                    const uint32_t st = smem_base + (uint32_t)slot * STAGE_BYTES;
+                    const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + A_BYTES);
+#pragma unroll
+                    for (int j = 0; j < G8_BK / 32; ++j)  // K = 32 per instruction: +32 bytes in the row
+                        umma_i8(tacc, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc,
+                                (kb > 0 || j > 0) ? 1u : 0u);
+                    umma_commit(bar_empty + slot * 8);  // stage free once these MMAs have read it
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                }
+                if (!alive) break;
+                umma_commit(bar_tfull + abuf * 8);  // accumulator complete
+                if (++abuf == 2) { abuf = 0; aphase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp%4).. ----------------
+        const int q = warp & 3;
+        int abuf = 0;
+        uint32_t aphase = 0;
+        bool alive = true;
+        for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+            const int mb = t % p.m_blocks, nb = t / p.m_blocks;
+            alive = mbar_wait(bar_tfull + abuf * 8, aphase, status);
+            if (!alive) break;
+            tc_fence_after();
+            const int row = mb * G8_BM + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)abuf * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c0, r);
+                const int col0 = nb * BN + c0;
+                if (row < p.M && col0 < p.N) {
+                    if (p.mode == 0) {
+                        int32_t *o = reinterpret_cast<int32_t *>(out) + (size_t)row * p.ldc + col0;
+                        if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                int4 v;
+                                v.x = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j);
+                                v.y = (int)r[j + 1] - p.a_zp * __ldg(colsum + col0 + j + 1);
+                                v.z = (int)r[j + 2] - p.a_zp * __ldg(colsum + col0 + j + 2);
+                                v.w = (int)r[j + 3] - p.a_zp * __ldg(colsum + col0 + j + 3);
+                                *reinterpret_cast<int4 *>(o + j) = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) o[j] = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j);
+                        }
+                    } else {
+                        uint8_t *o = reinterpret_cast<uint8_t *>(out) + (size_t)row * p.ldc + col0;
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int cc = (col0 + j < p.N) ? col0 + j : col0;
+                            const int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc);
+                            // separate multiply and add: the CPU kernel does not fuse them
+                            const float v = __fadd_rn(__fmul_rn((float)acc, p.composite), p.y_zp);
+                            const float rr = p.round_mode ? roundf(v) : rintf(v);
+                            const int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
+                            if ((j & 3) == 0) packed[j >> 2] = 0;
+                            packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
+                        }
+                        if (col0 + 32 <= p.N && (p.ldc & 15) == 0) {
+                            *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            *reinterpret_cast<uint4 *>(o + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) o[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
+                        }
+                    }
+                }
+            }
+            // all columns of this buffer have been read: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + abuf * 8);
+            if (++abuf == 2) { abuf = 0; aphase ^= 1u; }
+        }
+    }
+
+    // ---------------- common exit: release TMEM ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * BN));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// B prepack: [K][N] row-major -> B^T [N][Kp] (zero padded) + column sums
+// ---------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256)
+pack_i8_b_kernel(const int8_t *__restrict__ b, int8_t *__restrict__ bt, int32_t *__restrict__ colsum,
+                 int K, int N, int Kp) {
+    // one warp per output row n: lanes stride over k
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= N) return;
+    int s = 0;
+    for (int k = lane; k < Kp; k += 32) {
+        const int8_t v = (k < K) ? b[(size_t)k * N + n] : (int8_t)0;
+        bt[(size_t)n * Kp + k] = v;
+        s += v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) colsum[n] = s;
+}
+
+// pads A [M][K] to [M][Kp] when K is not a multiple of 16 (TMA row pitch)
+__global__ void pad_rows_kernel(const uint8_t *__restrict__ a, uint8_t *__restrict__ ap, int M, int K,
+                                int Kp) {
+    const size_t total = (size_t)M * Kp;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int k = (int)(i % Kp);
+        const size_t m = i / Kp;
+        ap[i] = (k < K) ? a[m * K + k] : (uint8_t)0;
+    }
+}
+
+int pack_i8_b(yscv_cuda_ctx *ctx, const int8_t *d_b, size_t k, size_t n, int8_t *d_bt,
+              int32_t *d_colsum, size_t kp) {
+    const int blocks = (int)((n + 7) / 8);
+    pack_i8_b_kernel<<<blocks, 256, 0, ctx->stream>>>(d_b, d_bt, d_colsum, (int)k, (int)n, (int)kp);
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    return YSCV_CUDA_OK;
+}
+
+template <int BN>
+static int launch_g8(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const yscv_cuda_i8b *b, size_t m,
+                     void *d_out, const G8Params &proto) {
+    G8Params p = proto;
+    p.M = (int)m;
+    p.N = (int)b->n;
+    p.K = (int)b->kp;
+    p.m_blocks = (p.M + G8_BM - 1) / G8_BM;
+    p.n_blocks = (p.N + BN - 1) / BN;
+    p.k_blocks = (p.K + G8_BK - 1) / G8_BK;
+    const int stage_bytes = G8_BM * G8_BK + BN * G8_BK;
+    p.stages = (227 * 1024 - 1024) / stage_bytes;
+    if (p.stages > 8) p.stages = 8;
+    const int smem = p.stages * stage_bytes + 256;
+    CUtensorMap tm_a, tm_b;
+    int rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d_a, m, b->kp, lda, G8_BM, G8_BK,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b->d_bt, b->n, b->kp, b->kp, BN, G8_BK,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    auto kern = int8_gemm_tc_kernel<BN>;
+    static int smem_set[16] = {0};
+    if (ctx->device >= 16 || !smem_set[ctx->device]) {
+        YSCV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        if (ctx->device < 16) smem_set[ctx->device] = 1;
+    }
+    const int tiles = p.m_blocks * p.n_blocks;
+    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    ctx->prof_begin();
+    kern<<<grid, G8_THREADS, smem, ctx->stream>>>(tm_a, tm_b, b->d_colsum, d_out, p, ctx->d_status);
+    ctx->prof_end();
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    return YSCV_CUDA_OK;
+}
+
+// d_a: [m][k] bytes (i8, or u8 when a_unsigned). mode 0: d_out int32 [m][n]; mode 1: bytes [m][n].
+int int8_gemm(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_t m, void *d_out,
+              int a_unsigned, int a_zp, int mode, float composite, float y_zp, int qmin, int qmax,
+              int round_mode) {
+    G8Params p = {};
+    p.a_unsigned = a_unsigned;
+    p.a_zp = a_zp;
+    p.mode = mode;
+    p.composite = composite;
+    p.y_zp = y_zp;
+    p.qmin = qmin;
+    p.qmax = qmax;
+    p.round_mode = round_mode;
+    p.ldc = (long long)b->n;
+    const void *a = d_a;
+    size_t lda = b->k;
+    if (b->k != b->kp || (reinterpret_cast<uintptr_t>(d_a) & 15)) {
+        // TMA needs a 16-byte aligned base and row pitch: stage A into a padded copy
+        int rc = ctx->scratch.reserve(m * b->kp);
+        if (rc) return rc;
+        const size_t total = m * b->kp;
+        const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+        pad_rows_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const uint8_t *>(d_a),
+                                                         reinterpret_cast<uint8_t *>(ctx->scratch.ptr),
+                                                         (int)m, (int)b->k, (int)b->kp);
+        YSCV_CUDA_TRY(cudaGetLastError());
+        ctx->launches++;
+        a = ctx->scratch.ptr;
+        lda = b->kp;
+    }
+    // wide tiles when there are enough of them to fill the machine, else narrower ones
+    const size_t tiles256 = ((m + G8_BM - 1) / G8_BM) * ((b->n + 255) / 256);
+    if (b->n >= 256 && tiles256 >= (size_t)ctx->sm_count) {
+        ctx->last_kernel = "int8_gemm_tc(tcgen05,128x256)";
+        return launch_g8<256>(ctx, a, lda, b, m, d_out, p);
+    }
+    if (b->n > 64) {
+        ctx->last_kernel = "int8_gemm_tc(tcgen05,128x128)";
+        return launch_g8<128>(ctx, a, lda, b, m, d_out, p);
+    }
+    ctx->last_kernel = "int8_gemm_tc(tcgen05,128x64)";
+    return launch_g8<64>(ctx, a, lda, b, m, d_out, p);
+}
+
+}  // namespace yscv

@@ -4,6 +4,7 @@
 #include <stdint.h>
 
 struct yscv_cuda_ctx;
+struct yscv_cuda_i8b;
 
 namespace yscv {
 
@@ -18,5 +19,12 @@ int int4_gemv_generic(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
 // int4_pack.cu
 int pack_int4(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w, size_t k, size_t gs,
               uint8_t *d_packed, float *d_scales);
+
+// int8_gemm.cu
+int pack_i8_b(yscv_cuda_ctx *ctx, const int8_t *d_b, size_t k, size_t n, int8_t *d_bt,
+              int32_t *d_colsum, size_t kp);
+int int8_gemm(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_t m, void *d_out,
+              int a_unsigned, int a_zp, int mode, float composite, float y_zp, int qmin, int qmax,
+              int round_mode);
 
 }  // namespace yscv

@@ -51,7 +51,26 @@ SIGNATURES = {
     "yscv_cuda_int4_weight_free": (None, [_vp]),
     "yscv_cuda_int4_matmul_dev": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
     "yscv_cuda_pack_int4_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _vp, _vp]),
+    "yscv_cuda_int8_matmul": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp]),
+    "yscv_cuda_pack_i8_b_for_matmul": (C.c_int, [_vp, _vp, _sz, _sz, C.POINTER(_vp)]),
+    "yscv_cuda_pack_i8_b_dev": (C.c_int, [_vp, _vp, _sz, _sz, C.POINTER(_vp)]),
+    "yscv_cuda_i8b_free": (None, [_vp]),
+    "yscv_cuda_i8b_k": (_sz, [_vp]),
+    "yscv_cuda_i8b_n": (_sz, [_vp]),
+    "yscv_cuda_int8_matmul_prepacked": (C.c_int, [_vp, _vp, _vp, _sz, _vp]),
+    "yscv_cuda_int8_matmul_prepacked_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp]),
+    "yscv_cuda_qlinear_matmul": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp]),
+    "yscv_cuda_qlinear_matmul_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp]),
+    "yscv_cuda_matmul_integer": (C.c_int, [_vp, _vp, C.c_int, C.c_int32, _vp, _sz, _vp]),
+    "yscv_cuda_matmul_integer_dev": (C.c_int, [_vp, _vp, C.c_int, C.c_int32, _vp, _sz, _vp]),
 }
+
+
+class Requant(C.Structure):
+    """yscv_cuda_requant."""
+    _fields_ = [("a_is_unsigned", C.c_int), ("a_zero_point", C.c_int32), ("composite", C.c_float),
+                ("y_zero_point", C.c_float), ("qmin", C.c_int32), ("qmax", C.c_int32),
+                ("round_mode", C.c_int)]
 
 
 def load_library():
@@ -100,6 +119,27 @@ class Int4Weight:
     def free(self):
         if self.handle:
             load_library().yscv_cuda_int4_weight_free(self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class I8B:
+    """PackedI8B resident in HBM."""
+
+    def __init__(self, handle: int):
+        self.handle = handle
+        lib = load_library()
+        self.k = int(lib.yscv_cuda_i8b_k(handle))
+        self.n = int(lib.yscv_cuda_i8b_n(handle))
+
+    def free(self):
+        if self.handle:
+            load_library().yscv_cuda_i8b_free(self.handle)
             self.handle = 0
 
     def __del__(self):
@@ -205,6 +245,61 @@ class Context:
             out = np.empty((m, w.m_w), dtype=np.float32)
         _check(self.lib.yscv_cuda_int4_matmul(self.handle, w.handle, _ptr(act), _ptr(out), m))
         return out
+
+    # -- int8 -------------------------------------------------------------------
+    def int8_matmul(self, a, b, m, k, n):
+        a8, b8 = _host(a, np.int8), _host(b, np.int8)
+        out = np.empty((m, n), dtype=np.int32)
+        _check(self.lib.yscv_cuda_int8_matmul(self.handle, _ptr(a8), _ptr(b8), m, k, n, _ptr(out)))
+        return out
+
+    def pack_i8_b(self, b, k, n) -> "I8B":
+        b8 = _host(b, np.int8)
+        h = _vp()
+        _check(self.lib.yscv_cuda_pack_i8_b_for_matmul(self.handle, _ptr(b8), k, n, C.byref(h)))
+        return I8B(h.value)
+
+    def pack_i8_b_dev(self, d_b: int, k, n) -> "I8B":
+        h = _vp()
+        _check(self.lib.yscv_cuda_pack_i8_b_dev(self.handle, _vp(d_b), k, n, C.byref(h)))
+        return I8B(h.value)
+
+    def int8_matmul_prepacked(self, a, b: "I8B", m):
+        a8 = _host(a, np.int8)
+        out = np.empty((m, b.n), dtype=np.int32)
+        _check(self.lib.yscv_cuda_int8_matmul_prepacked(self.handle, _ptr(a8), b.handle, m, _ptr(out)))
+        return out
+
+    def int8_matmul_prepacked_dev(self, d_a: int, b: "I8B", m, d_out: int):
+        _check(self.lib.yscv_cuda_int8_matmul_prepacked_dev(self.handle, _vp(d_a), b.handle, m, _vp(d_out)))
+
+    @staticmethod
+    def requant(composite, y_zp, qmin, qmax, a_unsigned=False, a_zp=0, round_mode=0) -> "Requant":
+        return Requant(int(a_unsigned), int(a_zp), float(composite), float(y_zp), int(qmin), int(qmax),
+                       int(round_mode))
+
+    def qlinear_matmul(self, a, b: "I8B", m, rq: "Requant"):
+        """a: uint8 or int8 [m,k] host; returns uint8 (qmin >= 0) or int8 [m,n]."""
+        a = np.ascontiguousarray(a)
+        assert a.dtype in (np.uint8, np.int8)
+        out = np.empty((m, b.n), dtype=np.uint8 if rq.qmin >= 0 else np.int8)
+        _check(self.lib.yscv_cuda_qlinear_matmul(self.handle, _ptr(a), b.handle, m, C.byref(rq), _ptr(out)))
+        return out
+
+    def qlinear_matmul_dev(self, d_a: int, b: "I8B", m, rq: "Requant", d_out: int):
+        _check(self.lib.yscv_cuda_qlinear_matmul_dev(self.handle, _vp(d_a), b.handle, m, C.byref(rq), _vp(d_out)))
+
+    def matmul_integer(self, a, b: "I8B", m, a_zp=0):
+        a = np.ascontiguousarray(a)
+        assert a.dtype in (np.uint8, np.int8)
+        out = np.empty((m, b.n), dtype=np.int32)
+        _check(self.lib.yscv_cuda_matmul_integer(self.handle, _ptr(a), int(a.dtype == np.uint8), a_zp,
+                                                 b.handle, m, _ptr(out)))
+        return out
+
+    def matmul_integer_dev(self, d_a: int, a_unsigned: bool, a_zp: int, b: "I8B", m, d_out: int):
+        _check(self.lib.yscv_cuda_matmul_integer_dev(self.handle, _vp(d_a), int(a_unsigned), a_zp, b.handle,
+                                                     m, _vp(d_out)))
 
     def pack_int4_dev(self, d_weights: int, m_w, k, group_size, d_packed: int, d_scales: int):
         _check(self.lib.yscv_cuda_pack_int4_dev(self.handle, _vp(d_weights), m_w, k, group_size,
