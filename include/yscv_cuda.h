@@ -124,6 +124,25 @@ int yscv_cuda_int4_matmul_dev(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w
 int yscv_cuda_int4_matmul(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
                           const float *activation, float *output, size_t m);
 
+/* No counterpart in the reference. yscv_cuda_int4_matmul_dev for callers that are not
+ * allowed to allocate device memory while they run: code inside a real-time or
+ * latency-critical loop, a plugin whose host forbids cudaMalloc after start-up, a
+ * process working under a fixed memory budget. The kernel's scratch (the digit planes
+ * of the activations) lives in an array built into the library, about 1.7 MB on every
+ * GPU that loads it, held until the process exits; this call performs no cudaMalloc,
+ * cudaFree or other allocating call. Limits: m <= 16, k <= 32768, group_size 32,
+ * k % 256 == 0, operands 16-byte aligned; anything else is rejected with
+ * YSCV_CUDA_ERR_UNSUPPORTED. The first call on each device looks up the array's
+ * device address; make that first call outside any stream capture. All calls on a
+ * device share the one array (it keeps the last call's contents; every word a call
+ * reads is rewritten by that call first, so nothing needs clearing), therefore two
+ * calls that overlap on the GPU, e.g. from two contexts or streams, race: serialise
+ * them. All pointers are device pointers; weights are passed directly, no handle. */
+int yscv_cuda_int4_matmul_dev_static(yscv_cuda_ctx *ctx, const uint8_t *d_packed,
+                                     const float *d_scales, size_t n, size_t k,
+                                     size_t group_size, const float *d_activation,
+                                     float *d_output, size_t m);
+
 /* pack_int4_symmetric_per_group on device memory: d_weights [m_w,k] f32. */
 int yscv_cuda_pack_int4_dev(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w,
                             size_t k, size_t group_size, uint8_t *d_packed,

@@ -722,6 +722,90 @@ int int4_gemv_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, c
     }
 }
 
+// ---------------------------------------------------------------------------
+// Entry point for callers that must not allocate
+// ---------------------------------------------------------------------------
+
+// Scratch of the allocation-free entry point: the digit planes of up to 16 activation
+// rows of length up to YSCV_STATIC_SCRATCH_MAX_K. Every GPU that loads this library
+// holds these ~1.7 MB until the process exits.
+constexpr size_t YSCV_STATIC_SCRATCH_MAX_K = 32768;
+constexpr size_t YSCV_STATIC_SCRATCH_BYTES = (YSCV_STATIC_SCRATCH_MAX_K / 256) * 13312 + 256;
+static __device__ __align__(256) unsigned char g_static_scratch[YSCV_STATIC_SCRATCH_BYTES];
+
+// In host code `g_static_scratch` is only a stand-in for the device array, never an
+// address a kernel may be given; the real address is looked up once per device.
+static void *g_static_scratch_ptr[64] = {nullptr};
+
+// the scratch-using variant only: digit planes are always produced by act_quant_kernel
+template <int MP, int GS>
+static int launch_scratch_variant(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales,
+                                  const float *act, float *out, int M, int N, int K,
+                                  unsigned char *blobs) {
+    const QuantLayout q = quant_layout(MP, GS);
+    const int rows_per_cta = (N + ctx->sm_count - 1) / ctx->sm_count;
+    const int items = (K / 32) * quant_slots(q);
+    act_quant_kernel<<<(items * 4 + 127) / 128, 128, 0, ctx->stream>>>(act, blobs, M, K, q);
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    ctx->last_kernel = "int4_gemv_fast(imma,tma,static-scratch)";
+    return rows_per_cta <= 32
+               ? launch_fast<MP, GS, 2, false>(ctx, wq, scales, blobs, act, out, M, N, K, q)
+               : launch_fast<MP, GS, 8, false>(ctx, wq, scales, blobs, act, out, M, N, K, q);
+}
+
+}  // namespace yscv
+
+extern "C" int yscv_cuda_int4_matmul_dev_static(yscv_cuda_ctx *ctx, const uint8_t *d_packed,
+                                                const float *d_scales, size_t n, size_t k,
+                                                size_t group_size, const float *d_activation,
+                                                float *d_output, size_t m) {
+    using namespace yscv;
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    if (!d_packed || !d_scales || !d_activation || !d_output)
+        return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (m == 0) return YSCV_CUDA_OK;
+    if (m > 16)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED,
+                    "the allocation-free entry point takes at most 16 activation rows, got %zu", m);
+    if (k > YSCV_STATIC_SCRATCH_MAX_K)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED,
+                    "k=%zu exceeds the %zu the built-in scratch array was sized for", k,
+                    (size_t)YSCV_STATIC_SCRATCH_MAX_K);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(d_packed) | reinterpret_cast<uintptr_t>(d_scales) |
+                           reinterpret_cast<uintptr_t>(d_activation)) & 15) == 0;
+    if (!aligned || !int4_gemv_fast_supported(m, n, k, group_size))
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED,
+                    "the allocation-free entry point needs group_size 32, k %% 256 == 0 and 16-byte "
+                    "aligned operands (n=%zu k=%zu group=%zu)", n, k, group_size);
+    if (int4_gemv_scratch_bytes(m, k) > YSCV_STATIC_SCRATCH_BYTES)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "scratch need exceeds the built-in array");
+    if (ctx->device < 0 || ctx->device >= 64) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "device index");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    if (!g_static_scratch_ptr[ctx->device]) {
+        // first call on this device: resolve the device address of the array
+        void *ptr = nullptr;
+        YSCV_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        g_static_scratch_ptr[ctx->device] = ptr;
+    }
+    unsigned char *blobs = reinterpret_cast<unsigned char *>(g_static_scratch_ptr[ctx->device]);
+    const int M = (int)m, N = (int)n, K = (int)k;
+    const int MP = padded_m(M);
+    const int GS = stage_groups(MP, K);
+    switch (MP) {
+        case 1: return GS == 16 ? launch_scratch_variant<1, 16>(ctx, d_packed, d_scales, d_activation, d_output, M, N, K, blobs)
+                                : launch_scratch_variant<1, 8>(ctx, d_packed, d_scales, d_activation, d_output, M, N, K, blobs);
+        case 2: return GS == 16 ? launch_scratch_variant<2, 16>(ctx, d_packed, d_scales, d_activation, d_output, M, N, K, blobs)
+                                : launch_scratch_variant<2, 8>(ctx, d_packed, d_scales, d_activation, d_output, M, N, K, blobs);
+        case 4: return GS == 16 ? launch_scratch_variant<4, 16>(ctx, d_packed, d_scales, d_activation, d_output, M, N, K, blobs)
+                                : launch_scratch_variant<4, 8>(ctx, d_packed, d_scales, d_activation, d_output, M, N, K, blobs);
+        case 8: return launch_scratch_variant<8, 8>(ctx, d_packed, d_scales, d_activation, d_output, M, N, K, blobs);
+        default: return launch_scratch_variant<16, 8>(ctx, d_packed, d_scales, d_activation, d_output, M, N, K, blobs);
+    }
+}
+
+namespace yscv {
+
 int int4_gemv_generic(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales,
                       const float *act, float *out, size_t m, size_t n, size_t k, size_t gs) {
     const int vec_ok = (k % 32 == 0) && (gs % 32 == 0) &&

@@ -51,6 +51,7 @@ SIGNATURES = {
     "yscv_cuda_int4_weight_free": (None, [_vp]),
     "yscv_cuda_int4_matmul_dev": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
     "yscv_cuda_pack_int4_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _vp, _vp]),
+    "yscv_cuda_int4_matmul_dev_static": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _vp, _sz]),
     "yscv_cuda_int8_matmul": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp]),
     "yscv_cuda_pack_i8_b_for_matmul": (C.c_int, [_vp, _vp, _sz, _sz, C.POINTER(_vp)]),
     "yscv_cuda_pack_i8_b_dev": (C.c_int, [_vp, _vp, _sz, _sz, C.POINTER(_vp)]),
@@ -300,6 +301,13 @@ class Context:
     def matmul_integer_dev(self, d_a: int, a_unsigned: bool, a_zp: int, b: "I8B", m, d_out: int):
         _check(self.lib.yscv_cuda_matmul_integer_dev(self.handle, _vp(d_a), int(a_unsigned), a_zp, b.handle,
                                                      m, _vp(d_out)))
+
+    def int4_matmul_dev_static(self, d_packed: int, d_scales: int, n, k, group_size,
+                               d_activation: int, d_output: int, m: int):
+        """Allocation-free variant: scratch is an array built into the library."""
+        _check(self.lib.yscv_cuda_int4_matmul_dev_static(
+            self.handle, _vp(d_packed), _vp(d_scales), n, k, group_size, _vp(d_activation),
+            _vp(d_output), m))
 
     def pack_int4_dev(self, d_weights: int, m_w, k, group_size, d_packed: int, d_scales: int):
         _check(self.lib.yscv_cuda_pack_int4_dev(self.handle, _vp(d_weights), m_w, k, group_size,
