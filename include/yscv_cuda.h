@@ -207,6 +207,56 @@ int yscv_cuda_matmul_integer_dev(yscv_cuda_ctx *ctx, const void *d_a, int a_is_u
                                  int32_t a_zero_point, const yscv_cuda_i8b *b, size_t m,
                                  int32_t *d_out);
 
+/* ---- fp32 operators between the quantized linears of a decoder step ---------- */
+/* All take device pointers and are asynchronous on the context's stream. The sequence
+ * position (*d_pos) and the token ids live in device memory, so that a whole decode
+ * step can be captured once in a CUDA graph and replayed. */
+
+/* embedding_lookup (crates/yscv-kernels/src/ops/embedding.rs:12): out[r] = weight[tokens[r]] */
+int yscv_cuda_embedding_dev(yscv_cuda_ctx *ctx, const float *d_weight, size_t vocab, size_t dim,
+                            const int32_t *d_tokens, size_t rows, float *d_out);
+
+/* rms_norm_last_dim_row (crates/yscv-kernels/src/ops/norm.rs:1497-1518) with the residual
+ * add in front: x_out = x + delta (delta and x_out may be null), normed = rmsnorm(x_out)*gamma */
+int yscv_cuda_add_rms_norm_dev(yscv_cuda_ctx *ctx, const float *d_x, const float *d_delta,
+                               const float *d_gamma, float eps, size_t rows, size_t hidden,
+                               float *d_x_out, float *d_normed);
+
+/* apply_rotary_embedding (crates/yscv-kernels/src/ops/rope.rs:24-117, rotate-half) on the
+ * q and k parts of fused qkv rows [q | k | v] at positions *d_pos + s, fused with the
+ * KvCache append (crates/yscv-onnx/src/runner/kv_cache.rs:118-254, f32 storage):
+ * caches are [batch][max_seq][n_kv][d_head]. q is rotated in place. */
+int yscv_cuda_rope_kv_append_dev(yscv_cuda_ctx *ctx, float *d_qkv, size_t batch, size_t seq,
+                                 size_t n_q, size_t n_kv, size_t d_head, float theta,
+                                 const int32_t *d_pos, float *d_kcache, float *d_vcache,
+                                 size_t max_seq);
+
+/* exec_grouped_query_attention (crates/yscv-onnx/src/runner/linear.rs:552-646) over the
+ * cache: keys 0 .. *d_pos + seq_q - 1, or 0 .. *d_pos + sq when causal. q rows are
+ * q_stride floats apart; out is [batch][seq_q][n_q*d_head]. */
+int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_stride, size_t batch,
+                                size_t seq_q, size_t n_q, size_t n_kv, size_t d_head,
+                                const float *d_kcache, const float *d_vcache, size_t max_seq,
+                                const int32_t *d_pos, int causal, float *d_out);
+
+/* SwiGLU on fused rows [gate | up] with the scalar SiLU of
+ * crates/yscv-kernels/src/ops/simd/activation.rs:1000-1005: out = gate/(1+exp(-gate)) * up */
+int yscv_cuda_swiglu_dev(yscv_cuda_ctx *ctx, const float *d_gate_up, size_t rows, size_t inter,
+                         float *d_out);
+
+/* fp32 matmul against a row-major [n,k] weight (the unquantized LM head):
+ * out[m,n] = x[m,k] . w[n,k] */
+int yscv_cuda_f32_matmul_dev(yscv_cuda_ctx *ctx, const float *d_w, const float *d_x, size_t m,
+                             size_t n, size_t k, float *d_out);
+
+/* greedy sampling as apps/llm-bench/src/main.rs:538-543 does it: per row the LAST index
+ * among equal maxima */
+int yscv_cuda_argmax_last_dev(yscv_cuda_ctx *ctx, const float *d_logits, size_t rows, size_t vocab,
+                              int32_t *d_out);
+
+/* *d_pos += by, on the stream (position_offset += 1, apps/llm-bench/src/main.rs:536) */
+int yscv_cuda_advance_pos_dev(yscv_cuda_ctx *ctx, int32_t *d_pos, int by);
+
 #ifdef __cplusplus
 }
 #endif

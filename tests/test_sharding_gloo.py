@@ -1,0 +1,78 @@
+"""The multi-rank path on CPU: two gloo ranks shard a packed int4 weight column- and
+row-parallel, compute their part with the CPU oracle, and exchange results exactly as
+the GPU ranks do over NCCL (all_gather / all_reduce)."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _worker(rank, world, port, q):
+    sys.path[:0] = [str(ROOT), str(ROOT / "oracle")]
+    import torch
+    import torch.distributed as dist
+    import oracle_lib
+    from yscv_b200 import sharding, synth
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        o = oracle_lib.load()
+        n, k, g, m = 64, 256, 32, 3
+        w = synth.normal(9, 0, n * k, 0.02)
+        packed, scales = o.pack_int4(w, n, k, g)
+        packed, scales = packed.reshape(n, k // 2), scales.reshape(n, k // g)
+        act = synth.normal(9, 1, m * k, 1.0).reshape(m, k)
+        full = o.exec_matmul_int4(packed.ravel(), scales.ravel(), act, m, n, k, g)
+        # column-parallel: own rows, all-gather the output columns
+        p, s = sharding.shard_rows(packed, scales, rank, world)
+        part = o.exec_matmul_int4(np.ascontiguousarray(p).ravel(), np.ascontiguousarray(s).ravel(), act, m,
+                                  n // world, k, g)
+        gathered = [torch.empty(m, n // world) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(part))
+        col_ok = np.array_equal(torch.cat(gathered, dim=1).numpy(), full)
+        # row-parallel: own K slice, all-reduce the fp32 partials
+        p, s = sharding.shard_cols(packed, scales, g, rank, world)
+        a = np.ascontiguousarray(sharding.shard_activation_cols(act, g, rank, world))
+        part = o.exec_matmul_int4(np.ascontiguousarray(p).ravel(), np.ascontiguousarray(s).ravel(), a, m, n,
+                                  k // world, g)
+        t = torch.from_numpy(part.copy())
+        dist.all_reduce(t)
+        err = float(np.max(np.abs(t.numpy() - full)) / np.max(np.abs(full)))
+        q.put((rank, col_ok, err))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharding_matches_single_rank():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, col_ok, err in results:
+        assert col_ok, f"rank {rank}: column-parallel shards do not reassemble the full output"
+        assert err <= 1e-6, f"rank {rank}: row-parallel partial sums differ by {err}"
+
+
+def test_shard_ranges_reject_bad_splits():
+    from yscv_b200 import sharding
+    assert sharding.row_range(64, 1, 4) == (16, 32)
+    assert sharding.col_range(256, 32, 3, 4) == (192, 256)
+    with pytest.raises(ValueError):
+        sharding.row_range(10, 0, 4)
+    with pytest.raises(ValueError):
+        sharding.col_range(96, 32, 0, 2)  # 48 per rank is not a multiple of the group
+    # Llama-3-70B shapes over 8 ranks (BASELINE config 5)
+    assert sharding.col_range(8192, 32, 7, 8) == (7168, 8192)
+    assert sharding.col_range(28672, 32, 1, 8) == (3584, 7168)

@@ -1,0 +1,374 @@
+// The fp32 operators that sit between the quantized linears of a Llama-shape
+// decoder step: embedding gather, RMSNorm (with the residual add fused in front),
+// rotate-half RoPE fused with the KV-cache append, GQA attention over the cache,
+// SwiGLU, the fp32 LM-head matmul and the greedy argmax.
+//
+// Semantics follow the reference's CPU operators
+//   RMSNorm   crates/yscv-kernels/src/ops/norm.rs:1497-1518
+//   RoPE      crates/yscv-kernels/src/ops/rope.rs:24-117 (rotate-half, pairs (i, i+d/2))
+//   GQA       crates/yscv-onnx/src/runner/linear.rs:552-646 (kv head = q head / group,
+//             max-subtracted softmax; causality is added here because the exported
+//             graphs the reference runs carry it in their mask)
+//   SiLU      crates/yscv-kernels/src/ops/simd/activation.rs:1000-1005
+//   embedding crates/yscv-kernels/src/ops/embedding.rs:12
+//   argmax    apps/llm-bench/src/main.rs:538-543 (LAST index among equal maxima)
+//   KV cache  crates/yscv-onnx/src/runner/kv_cache.rs:118-254 (f32 storage)
+// All of them are bandwidth-trivial next to the weight streams; they exist so that a
+// whole decode step stays on the device and can be replayed as one CUDA graph: the
+// sequence position and the token ids are read from device memory, never passed as
+// kernel arguments.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace yscv {
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[w] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < nw; ++i) t += red[i];
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float *red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[w] = v;
+    __syncthreads();
+    float t = -INFINITY;
+    for (int i = 0; i < nw; ++i) t = fmaxf(t, red[i]);
+    return t;
+}
+
+__global__ void embedding_kernel(const float *__restrict__ w, const int32_t *__restrict__ tokens,
+                                 float *__restrict__ out, int vocab, int dim) {
+    const int row = blockIdx.x;
+    int tok = tokens[row];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const float4 *src = reinterpret_cast<const float4 *>(w + (size_t)tok * dim);
+    float4 *dst = reinterpret_cast<float4 *>(out + (size_t)row * dim);
+    for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// x_out = x + delta (delta may be null); normed = x_out * (1/sqrt(mean(x_out^2)+eps)) * gamma
+__global__ void __launch_bounds__(256)
+add_rms_norm_kernel(const float *x, const float *__restrict__ delta,
+                    const float *__restrict__ gamma, float eps, int hidden,
+                    float *x_out, float *__restrict__ normed) {
+    __shared__ float red[8];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[base + i];
+        if (delta) v += delta[base + i];
+        if (x_out) x_out[base + i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    // x_out may alias x (in-place residual update): read the sum back instead of adding twice;
+    // every thread re-reads exactly the elements it wrote
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v;
+        if (x_out) {
+            v = x_out[base + i];
+        } else {
+            v = x[base + i];
+            if (delta) v += delta[base + i];
+        }
+        normed[base + i] = (v * inv) * gamma[i];
+    }
+}
+
+// qkv rows: [q (n_q*d) | k (n_kv*d) | v (n_kv*d)], row r = b*seq + s at position *pos + s.
+// Rotates q in place, writes rotated k and v into the cache at [b][position][head][d].
+__global__ void rope_kv_append_kernel(float *__restrict__ qkv, int seq, int n_q, int n_kv, int d,
+                                      float theta, const int32_t *__restrict__ pos,
+                                      float *__restrict__ kc, float *__restrict__ vc, int max_seq) {
+    const int row = blockIdx.x, b = row / seq, s = row % seq;
+    const int p = *pos + s;
+    const int half = d / 2;
+    const int row_w = (n_q + 2 * n_kv) * d;
+    float *r = qkv + (size_t)row * row_w;
+    const float fp = (float)p;
+    // q and k heads: one thread per (head, i < half)
+    for (int idx = threadIdx.x; idx < (n_q + n_kv) * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        const float inv_freq = 1.0f / powf(theta, 2.0f * (float)i / (float)d);
+        const float angle = inv_freq * fp;
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        float *v = r + (size_t)h * d;
+        const float x0 = v[i], x1 = v[i + half];
+        const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
+        if (h < n_q) {
+            v[i] = y0;
+            v[i + half] = y1;
+        } else if (p < max_seq) {
+            float *dst = kc + (((size_t)b * max_seq + p) * n_kv + (h - n_q)) * d;
+            dst[i] = y0;
+            dst[i + half] = y1;
+        }
+    }
+    if (p < max_seq) {
+        const float *vsrc = r + (size_t)(n_q + n_kv) * d;
+        float *vdst = vc + ((size_t)b * max_seq + p) * n_kv * d;
+        for (int i = threadIdx.x; i < n_kv * d; i += blockDim.x) vdst[i] = vsrc[i];
+    }
+}
+
+// One block per (b, q head, sq). Keys 0 .. *pos + sq (causal) or *pos + seq_q - 1.
+__global__ void __launch_bounds__(128)
+gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n_q, int n_kv, int d,
+                     const float *__restrict__ kc, const float *__restrict__ vc, int max_seq,
+                     const int32_t *__restrict__ pos, int causal, float *__restrict__ out) {
+    extern __shared__ float sm[];
+    float *scores = sm;           // max_seq
+    float *qs = sm + max_seq;     // d
+    __shared__ float red[4];
+    const int sq = blockIdx.x, qh = blockIdx.y, b = blockIdx.z;
+    const int kv_h = qh / (n_q / n_kv);
+    int limit = *pos + (causal ? sq + 1 : seq_q);
+    limit = limit > max_seq ? max_seq : limit;
+    const float scale = 1.0f / sqrtf((float)d);
+    const float *qrow = q + ((size_t)b * seq_q + sq) * q_stride + (size_t)qh * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = qrow[i];
+    __syncthreads();
+    const float *kb = kc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const float *vb = vc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float mx = -INFINITY;
+    // a warp per key: lanes stride over d (coalesced), shuffle-reduce
+    for (int sk = warp; sk < limit; sk += 4) {
+        const float *kr = kb + (size_t)sk * n_kv * d;
+        float dot = 0.0f;
+        for (int i = lane; i < d; i += 32) dot = fmaf(qs[i], kr[i], dot);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float sc = dot * scale;
+        if (lane == 0) scores[sk] = sc;
+        mx = fmaxf(mx, sc);
+    }
+    mx = block_max(mx, red);
+    float se = 0.0f;
+    for (int sk = threadIdx.x; sk < limit; sk += blockDim.x) {
+        const float e = expf(scores[sk] - mx);
+        scores[sk] = e;
+        se += e;
+    }
+    se = block_sum(se, red);
+    const float inv = se > 0.0f ? 1.0f / se : 0.0f;
+    float *orow = out + ((size_t)b * seq_q + sq) * (size_t)n_q * d + (size_t)qh * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int sk = 0; sk < limit; ++sk) acc = fmaf(scores[sk] * inv, vb[(size_t)sk * n_kv * d + i], acc);
+        orow[i] = acc;
+    }
+}
+
+// gate_up rows: [gate (inter) | up (inter)] -> out = silu(gate) * up
+__global__ void swiglu_kernel(const float *__restrict__ gu, float *__restrict__ out, size_t rows,
+                              int inter) {
+    const size_t total = rows * (size_t)inter;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / inter;
+        const int c = (int)(i % inter);
+        const float g = gu[r * 2 * inter + c], u = gu[r * 2 * inter + inter + c];
+        const float s = 1.0f / (1.0f + expf(-g));
+        out[i] = (g * s) * u;
+    }
+}
+
+// out[m][n] = sum_k x[m][k] * w[n][k]; one warp per weight row, up to 4 x rows per pass
+template <int MT>
+__global__ void __launch_bounds__(256)
+f32_matmul_kernel(const float *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
+                  int m0, int M, int N, int K) {
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    const int mt = min(MT, M - m0);
+    for (int n = blockIdx.x * wpb + (threadIdx.x >> 5); n < N; n += gridDim.x * wpb) {
+        const float4 *wr = reinterpret_cast<const float4 *>(w + (size_t)n * K);
+        float acc[MT];
+#pragma unroll
+        for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
+        for (int c = lane; c < K / 4; c += 32) {
+            const float4 wv = __ldg(wr + c);
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                if (i < mt) {
+                    const float4 xv = __ldg(reinterpret_cast<const float4 *>(x + (size_t)(m0 + i) * K) + c);
+                    acc[i] = fmaf(wv.x, xv.x, acc[i]);
+                    acc[i] = fmaf(wv.y, xv.y, acc[i]);
+                    acc[i] = fmaf(wv.z, xv.z, acc[i]);
+                    acc[i] = fmaf(wv.w, xv.w, acc[i]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            float v = acc[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && i < mt) out[(size_t)(m0 + i) * N + n] = v;
+        }
+    }
+}
+
+// greedy token per row: the LAST index among equal maxima (Iterator::max_by)
+__global__ void __launch_bounds__(256)
+argmax_last_kernel(const float *__restrict__ logits, int vocab, int32_t *__restrict__ out) {
+    __shared__ float bv[256];
+    __shared__ int bi[256];
+    const float *row = logits + (size_t)blockIdx.x * vocab;
+    float best = -INFINITY;
+    int idx = -1;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (idx < 0 || !(v < best)) {  // v >= best (or NaN): later index wins ties
+            best = v;
+            idx = i;
+        }
+    }
+    bv[threadIdx.x] = best;
+    bi[threadIdx.x] = idx;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float a = bv[threadIdx.x], b = bv[threadIdx.x + s];
+            const int ia = bi[threadIdx.x], ib = bi[threadIdx.x + s];
+            const bool take_b = ib >= 0 && (ia < 0 || b > a || (b == a && ib > ia));
+            if (take_b) {
+                bv[threadIdx.x] = b;
+                bi[threadIdx.x] = ib;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = bi[0] < 0 ? 0 : bi[0];
+}
+
+__global__ void advance_pos_kernel(int32_t *pos, int by) { *pos += by; }
+
+}  // namespace yscv
+
+using namespace yscv;
+
+#define DEC_PROLOGUE(ctx)                                                    \
+    if (!(ctx)) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");           \
+    YSCV_CUDA_TRY(cudaSetDevice((ctx)->device))
+#define DEC_EPILOGUE(ctx, name)                  \
+    YSCV_CUDA_TRY(cudaGetLastError());           \
+    (ctx)->launches++;                           \
+    (ctx)->last_kernel = name;                   \
+    return YSCV_CUDA_OK
+
+extern "C" {
+
+int yscv_cuda_embedding_dev(yscv_cuda_ctx *ctx, const float *d_weight, size_t vocab, size_t dim,
+                            const int32_t *d_tokens, size_t rows, float *d_out) {
+    DEC_PROLOGUE(ctx);
+    if (!d_weight || !d_tokens || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (dim % 4 != 0) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "embedding dim must be a multiple of 4");
+    if (rows == 0) return YSCV_CUDA_OK;
+    embedding_kernel<<<(unsigned)rows, 128, 0, ctx->stream>>>(d_weight, d_tokens, d_out, (int)vocab, (int)dim);
+    DEC_EPILOGUE(ctx, "embedding");
+}
+
+int yscv_cuda_add_rms_norm_dev(yscv_cuda_ctx *ctx, const float *d_x, const float *d_delta,
+                               const float *d_gamma, float eps, size_t rows, size_t hidden,
+                               float *d_x_out, float *d_normed) {
+    DEC_PROLOGUE(ctx);
+    if (!d_x || !d_gamma || !d_normed) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (rows == 0) return YSCV_CUDA_OK;
+    add_rms_norm_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(d_x, d_delta, d_gamma, eps, (int)hidden,
+                                                                 d_x_out, d_normed);
+    DEC_EPILOGUE(ctx, "add_rms_norm");
+}
+
+int yscv_cuda_rope_kv_append_dev(yscv_cuda_ctx *ctx, float *d_qkv, size_t batch, size_t seq, size_t n_q,
+                                 size_t n_kv, size_t d_head, float theta, const int32_t *d_pos,
+                                 float *d_kcache, float *d_vcache, size_t max_seq) {
+    DEC_PROLOGUE(ctx);
+    if (!d_qkv || !d_pos || !d_kcache || !d_vcache) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (d_head % 2 != 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "d_head must be even for RoPE");
+    if (batch * seq == 0) return YSCV_CUDA_OK;
+    rope_kv_append_kernel<<<(unsigned)(batch * seq), 128, 0, ctx->stream>>>(
+        d_qkv, (int)seq, (int)n_q, (int)n_kv, (int)d_head, theta, d_pos, d_kcache, d_vcache, (int)max_seq);
+    DEC_EPILOGUE(ctx, "rope_kv_append");
+}
+
+int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_stride, size_t batch,
+                                size_t seq_q, size_t n_q, size_t n_kv, size_t d_head,
+                                const float *d_kcache, const float *d_vcache, size_t max_seq,
+                                const int32_t *d_pos, int causal, float *d_out) {
+    DEC_PROLOGUE(ctx);
+    if (!d_q || !d_kcache || !d_vcache || !d_pos || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (n_kv == 0 || n_q % n_kv != 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "n_q must be a multiple of n_kv");
+    if (batch * seq_q == 0) return YSCV_CUDA_OK;
+    const size_t smem = (max_seq + d_head) * sizeof(float);
+    if (smem > 200 * 1024) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "max_seq %zu too long for the attention kernel", max_seq);
+    static int attr_set[16] = {0};
+    if (smem > 48 * 1024 && (ctx->device >= 16 || !attr_set[ctx->device])) {
+        YSCV_CUDA_TRY(cudaFuncSetAttribute(gqa_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (ctx->device < 16) attr_set[ctx->device] = 1;
+    }
+    dim3 grid((unsigned)seq_q, (unsigned)n_q, (unsigned)batch);
+    gqa_attention_kernel<<<grid, 128, smem, ctx->stream>>>(d_q, (int)q_stride, (int)seq_q, (int)n_q, (int)n_kv,
+                                                           (int)d_head, d_kcache, d_vcache, (int)max_seq,
+                                                           d_pos, causal, d_out);
+    DEC_EPILOGUE(ctx, "gqa_attention");
+}
+
+int yscv_cuda_swiglu_dev(yscv_cuda_ctx *ctx, const float *d_gate_up, size_t rows, size_t inter,
+                         float *d_out) {
+    DEC_PROLOGUE(ctx);
+    if (!d_gate_up || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (rows * inter == 0) return YSCV_CUDA_OK;
+    const size_t total = rows * inter;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 65535 ? (total + 255) / 256 : 65535);
+    swiglu_kernel<<<blocks, 256, 0, ctx->stream>>>(d_gate_up, d_out, rows, (int)inter);
+    DEC_EPILOGUE(ctx, "swiglu");
+}
+
+int yscv_cuda_f32_matmul_dev(yscv_cuda_ctx *ctx, const float *d_w, const float *d_x, size_t m, size_t n,
+                             size_t k, float *d_out) {
+    DEC_PROLOGUE(ctx);
+    if (!d_w || !d_x || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (k % 4 != 0) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "k must be a multiple of 4");
+    if (m * n == 0) return YSCV_CUDA_OK;
+    const unsigned blocks = (unsigned)((n + 7) / 8 < (size_t)(16 * ctx->sm_count) ? (n + 7) / 8 : 16 * ctx->sm_count);
+    for (size_t m0 = 0; m0 < m; m0 += 4) {
+        f32_matmul_kernel<4><<<blocks, 256, 0, ctx->stream>>>(d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k);
+        YSCV_CUDA_TRY(cudaGetLastError());
+        ctx->launches++;
+    }
+    ctx->last_kernel = "f32_matmul";
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_argmax_last_dev(yscv_cuda_ctx *ctx, const float *d_logits, size_t rows, size_t vocab,
+                              int32_t *d_out) {
+    DEC_PROLOGUE(ctx);
+    if (!d_logits || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (rows == 0) return YSCV_CUDA_OK;
+    if (vocab == 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "empty vocabulary");
+    argmax_last_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(d_logits, (int)vocab, d_out);
+    DEC_EPILOGUE(ctx, "argmax_last");
+}
+
+int yscv_cuda_advance_pos_dev(yscv_cuda_ctx *ctx, int32_t *d_pos, int by) {
+    DEC_PROLOGUE(ctx);
+    if (!d_pos) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    advance_pos_kernel<<<1, 1, 0, ctx->stream>>>(d_pos, by);
+    DEC_EPILOGUE(ctx, "advance_pos");
+}
+
+}  // extern "C"

@@ -64,6 +64,14 @@ SIGNATURES = {
     "yscv_cuda_qlinear_matmul_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp]),
     "yscv_cuda_matmul_integer": (C.c_int, [_vp, _vp, C.c_int, C.c_int32, _vp, _sz, _vp]),
     "yscv_cuda_matmul_integer_dev": (C.c_int, [_vp, _vp, C.c_int, C.c_int32, _vp, _sz, _vp]),
+    "yscv_cuda_embedding_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _sz, _vp]),
+    "yscv_cuda_add_rms_norm_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_float, _sz, _sz, _vp, _vp]),
+    "yscv_cuda_rope_kv_append_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _vp, _vp, _vp, _sz]),
+    "yscv_cuda_gqa_attention_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _sz, _vp, C.c_int, _vp]),
+    "yscv_cuda_swiglu_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
+    "yscv_cuda_f32_matmul_dev": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp]),
+    "yscv_cuda_argmax_last_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
+    "yscv_cuda_advance_pos_dev": (C.c_int, [_vp, _vp, C.c_int]),
 }
 
 
@@ -308,6 +316,35 @@ class Context:
         _check(self.lib.yscv_cuda_int4_matmul_dev_static(
             self.handle, _vp(d_packed), _vp(d_scales), n, k, group_size, _vp(d_activation),
             _vp(d_output), m))
+
+    # -- decoder operators (device pointers) ----------------------------------------
+    def embedding_dev(self, d_weight, vocab, dim, d_tokens, rows, d_out):
+        _check(self.lib.yscv_cuda_embedding_dev(self.handle, _vp(d_weight), vocab, dim, _vp(d_tokens), rows, _vp(d_out)))
+
+    def add_rms_norm_dev(self, d_x, d_delta, d_gamma, eps, rows, hidden, d_x_out, d_normed):
+        _check(self.lib.yscv_cuda_add_rms_norm_dev(self.handle, _vp(d_x), _vp(d_delta or 0), _vp(d_gamma), eps,
+                                                   rows, hidden, _vp(d_x_out or 0), _vp(d_normed)))
+
+    def rope_kv_append_dev(self, d_qkv, batch, seq, n_q, n_kv, d_head, theta, d_pos, d_kc, d_vc, max_seq):
+        _check(self.lib.yscv_cuda_rope_kv_append_dev(self.handle, _vp(d_qkv), batch, seq, n_q, n_kv, d_head, theta,
+                                                     _vp(d_pos), _vp(d_kc), _vp(d_vc), max_seq))
+
+    def gqa_attention_dev(self, d_q, q_stride, batch, seq_q, n_q, n_kv, d_head, d_kc, d_vc, max_seq, d_pos,
+                          causal, d_out):
+        _check(self.lib.yscv_cuda_gqa_attention_dev(self.handle, _vp(d_q), q_stride, batch, seq_q, n_q, n_kv, d_head,
+                                                    _vp(d_kc), _vp(d_vc), max_seq, _vp(d_pos), int(causal), _vp(d_out)))
+
+    def swiglu_dev(self, d_gate_up, rows, inter, d_out):
+        _check(self.lib.yscv_cuda_swiglu_dev(self.handle, _vp(d_gate_up), rows, inter, _vp(d_out)))
+
+    def f32_matmul_dev(self, d_w, d_x, m, n, k, d_out):
+        _check(self.lib.yscv_cuda_f32_matmul_dev(self.handle, _vp(d_w), _vp(d_x), m, n, k, _vp(d_out)))
+
+    def argmax_last_dev(self, d_logits, rows, vocab, d_out):
+        _check(self.lib.yscv_cuda_argmax_last_dev(self.handle, _vp(d_logits), rows, vocab, _vp(d_out)))
+
+    def advance_pos_dev(self, d_pos, by=1):
+        _check(self.lib.yscv_cuda_advance_pos_dev(self.handle, _vp(d_pos), by))
 
     def pack_int4_dev(self, d_weights: int, m_w, k, group_size, d_packed: int, d_scales: int):
         _check(self.lib.yscv_cuda_pack_int4_dev(self.handle, _vp(d_weights), m_w, k, group_size,

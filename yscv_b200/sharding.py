@@ -1,0 +1,48 @@
+"""Tensor-parallel partitioning of packed int4 weights (index arithmetic only).
+
+Packed layout: `packed` [n][k/2] bytes and `scales` [n][k/group] (one row per output
+channel, crates/yscv-kernels/src/ops/int4_matmul.rs:12-18), so
+
+* column-parallel (split the output channels): rank r owns the contiguous row slice
+  [r*n/G, (r+1)*n/G) of both arrays; no repacking, no collective when the consumer is
+  sharded the same way (attention heads, SwiGLU);
+* row-parallel (split K): rank r owns bytes [k0/2, k1/2) and scales [k0/g, k1/g) of
+  every row, k0 = r*k/G; needs (k/G) % group == 0 so that no group straddles two ranks.
+  Every rank produces an fp32 partial [m][n]; the partials are summed (all-reduce).
+
+Works on numpy arrays and torch tensors alike (plain slicing).
+"""
+from __future__ import annotations
+
+
+def row_range(n: int, rank: int, world: int) -> tuple[int, int]:
+    if n % world != 0:
+        raise ValueError(f"{n} output channels do not split evenly across {world} ranks")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def col_range(k: int, group: int, rank: int, world: int) -> tuple[int, int]:
+    if k % world != 0 or (k // world) % group != 0:
+        raise ValueError(f"k={k} cannot be split across {world} ranks on group-{group} boundaries")
+    per = k // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_rows(packed, scales, rank: int, world: int):
+    """Column-parallel shard: packed [n][k/2], scales [n][k/g] -> the rank's rows."""
+    r0, r1 = row_range(packed.shape[0], rank, world)
+    return packed[r0:r1], scales[r0:r1]
+
+
+def shard_cols(packed, scales, group: int, rank: int, world: int):
+    """Row-parallel shard: the rank's K slice of every row."""
+    k = packed.shape[1] * 2
+    k0, k1 = col_range(k, group, rank, world)
+    return packed[:, k0 // 2:k1 // 2], scales[:, k0 // group:k1 // group]
+
+
+def shard_activation_cols(act, group: int, rank: int, world: int):
+    """The K slice of the activations [m][k] that goes with shard_cols."""
+    k0, k1 = col_range(act.shape[-1], group, rank, world)
+    return act[..., k0:k1]
