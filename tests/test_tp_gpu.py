@@ -1,0 +1,66 @@
+"""Tensor-parallel decoder across 2 GPUs (NCCL) against the single-GPU decoder: same
+logits (relative Frobenius) and the same greedy tokens. Needs two B200s; skipped on a
+one-GPU box. Each rank is a child process; rank 0 also runs the TP=1 decoder."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = r'''
+import json, os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["YSCV_ROOT"])
+import yscv_b200
+from yscv_b200 import synth
+from yscv_b200.decoder import DecoderConfig, Int4Decoder
+rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+torch.cuda.set_device(local)
+cfg = DecoderConfig(layers=3, hidden=1024, mlp=2048, n_q=16, n_kv=4, head_dim=64, vocab=2000)
+B, P, steps = 2, 24, 12
+prompt = torch.from_numpy(np.stack([synth.uniform_int(7 + b, 9, P, 0, cfg.vocab - 1) for b in range(B)]).astype(np.int32)).cuda()
+stream = torch.cuda.Stream()
+ctx = yscv_b200.Context(local, stream=stream.cuda_stream)
+tp = Int4Decoder(ctx, cfg, B, P + steps + 2, stream, seed=5, tp_rank=rank, tp_size=world, process_group=dist.group.WORLD)
+lg = tp.prefill(prompt); stream.synchronize()
+tp.capture_decode_step()
+toks = tp.decode(steps); stream.synchronize()
+out = {"status": ctx.device_status()}
+if rank == 0:
+    one = Int4Decoder(ctx, cfg, B, P + steps + 2, stream, seed=5)
+    lg1 = one.prefill(prompt); stream.synchronize()
+    one.capture_decode_step()
+    toks1 = one.decode(steps); stream.synchronize()
+    out["rel"] = float(torch.linalg.norm(lg - lg1) / torch.linalg.norm(lg1))
+    out["tokens_equal"] = bool(torch.equal(toks, toks1))
+    print("RESULT " + json.dumps(out), flush=True)
+    one.close()
+tp.close()
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def test_tp2_matches_tp1(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    script = tmp_path / "tp_worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, YSCV_ROOT=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29611", str(script)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    import json
+    line = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    res = json.loads(line[len("RESULT "):])
+    assert res["status"] == 0
+    assert res["rel"] < 1e-5, res       # fp32 partial sums in a different order
+    assert res["tokens_equal"], res

@@ -189,6 +189,16 @@ class Int4Decoder:
         ctx.advance_pos_dev(self.pos.data_ptr(), seq)
         return logits
 
+    def close(self):
+        """Drop the captured graph and every device buffer. With tensor parallelism call this
+        before the process group is destroyed: a graph that holds NCCL nodes must go first."""
+        self.stream.synchronize()
+        self.graph = None
+        self._bufs.clear()
+        self.kcache, self.vcache = [], []
+        self.wqkv, self.wo, self.wgu, self.wdown = [], [], [], []
+        torch.cuda.synchronize()
+
     # ---- the llm-bench loop: prefill, then greedy decode with the KV cache -------------
     def reset(self):
         with torch.cuda.stream(self.stream):

@@ -1,0 +1,126 @@
+"""Decode benchmark of the random-init int4 decoder, the counterpart of
+apps/llm-bench (apps/llm-bench/src/main.rs:491-586): warm-up passes, one timed prefill,
+N timed single-token greedy steps with the KV cache, one JSON summary line with the
+same keys (prompt_tokens, decode_tokens, prefill_ms, decode_total_ms,
+decode_tokens_per_sec).
+
+    python -m yscv_b200.llm_bench --model tinyllama --batch 1 --prompt-len 128 --max-tokens 256
+    torchrun --nproc-per-node 8 -m yscv_b200.llm_bench --model llama70b --prompt-len 2048 --max-tokens 128
+
+Under torchrun the linears are tensor-parallel across the ranks (NCCL all-reduce after
+the row-parallel ones); prompts are uniform token ids from the seeded generator.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import Context, synth
+from .decoder import LLAMA3_70B, TINYLLAMA_1B, Int4Decoder
+
+MODELS = {"tinyllama": (TINYLLAMA_1B, 3), "llama70b": (LLAMA3_70B, 4)}
+
+
+def weight_bytes_per_token(cfg, layers, tp):
+    d = cfg.head_dim
+    per_layer = (cfg.n_q + 2 * cfg.n_kv) * d * cfg.hidden + cfg.hidden * cfg.n_q * d + 3 * cfg.mlp * cfg.hidden
+    int4 = per_layer * layers * (0.5 + 4.0 / cfg.group_size) / tp
+    return int4 + cfg.vocab * cfg.hidden * 4  # + fp32 LM head (replicated)
+
+
+def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, layers=None, use_graph=True):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    pg = None
+    if world > 1:
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        pg = dist.group.WORLD
+    torch.cuda.set_device(local)
+    cfg, seed = MODELS[model]
+    stream = torch.cuda.Stream()
+    ctx = Context(local, stream=stream.cuda_stream)
+    n_layers = layers or cfg.layers
+    dec = Int4Decoder(ctx, cfg, batch, prompt_len + max_tokens + 2, stream, seed=seed, tp_rank=rank, tp_size=world,
+                      process_group=pg, layers=n_layers)
+    import numpy as np
+    prompt = np.stack([synth.uniform_int(seed + b, 9, prompt_len, 0, cfg.vocab - 1) for b in range(batch)])
+    d_prompt = torch.from_numpy(prompt.astype(np.int32)).cuda()
+    for _ in range(warmup):  # stateless warm-up with the full prompt, cache restored afterwards
+        dec.reset()
+        dec.prefill(d_prompt)
+    stream.synchronize()
+    dec.reset()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        dec.prefill(d_prompt)
+        e1.record(stream)
+    stream.synchronize()
+    if use_graph:
+        dec.capture_decode_step()
+    l0 = ctx.launch_count()
+    with torch.cuda.stream(stream):
+        e1.record(stream)
+    toks = dec.decode(max_tokens, use_graph=use_graph)
+    with torch.cuda.stream(stream):
+        e2.record(stream)
+    stream.synchronize()
+    prefill_ms, decode_ms = e0.elapsed_time(e1) if False else None, e1.elapsed_time(e2)
+    # the prefill was timed before e1 was re-recorded: measure it again from a fresh pair
+    dec.reset()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        p0.record(stream)
+        dec.prefill(d_prompt)
+        p1.record(stream)
+    stream.synchronize()
+    prefill_ms = p0.elapsed_time(p1)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([prefill_ms, decode_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        prefill_ms, decode_ms = float(t[0]), float(t[1])
+    tps = batch * max_tokens * 1000.0 / decode_ms
+    wb = weight_bytes_per_token(cfg, n_layers, world)
+    summary = {
+        "model": f"{model} (random-init int4, group {cfg.group_size}, {n_layers} layers)",
+        "gpus": world, "batch": batch, "prompt_tokens": prompt_len, "decode_tokens": max_tokens,
+        "prefill_ms": prefill_ms, "decode_total_ms": decode_ms, "decode_tokens_per_sec": tps,
+        "ms_per_step": decode_ms / max_tokens,
+        "weight_bytes_per_step_per_gpu": wb,
+        "weight_stream_gbs_per_gpu": wb / (decode_ms / max_tokens * 1e-3) / 1e9,
+        "cuda_graph": bool(use_graph),
+        "first_tokens": toks[:8, 0].cpu().tolist(),
+        "device_status": ctx.device_status(),
+    }
+    dec.close()
+    return summary
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="tinyllama", choices=sorted(MODELS))
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--prompt-len", type=int, default=128)
+    ap.add_argument("--max-tokens", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=None, help="truncate the stack (default: the model's depth)")
+    ap.add_argument("--no-graph", action="store_true")
+    a = ap.parse_args()
+    s = run(a.model, a.batch, a.prompt_len, a.max_tokens, a.warmup, a.layers, not a.no_graph)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(s), flush=True)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
