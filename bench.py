@@ -344,6 +344,11 @@ def run_cuda(args):
                          f"split across {threads} threads; single_thread_value from {c1} calls on 1 thread "
                          "(the reference kernel is single-threaded)"}
 
+    # ---- the other two quantities of BASELINE's metric, measured beside the headline ----
+    other = None
+    if world == 1 and not args.no_extras:
+        other = extra_metrics(ctx, stream, dev)
+
     if rank == 0:
         line = {
             "metric": "w4_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
@@ -358,6 +363,7 @@ def run_cuda(args):
             "kernels_per_call": launches / calls,
             "roofline": roofline,
             "cpu_baseline": cpu,
+            "other_metrics": other,
             "sanity_rel_err_vs_torch_fp32": check,
         }
         print(json.dumps(line), flush=True)
@@ -367,9 +373,48 @@ def run_cuda(args):
         dist.destroy_process_group()
 
 
+def extra_metrics(ctx, stream, dev):
+    """int8 GEMM TOPS on BASELINE configs[2] (QLinearMatMul 2048x4096x4096, uint8 in/out) and
+    configs[0] (MatMulInteger 64x1024x1024), and decode tokens/s of the TinyLlama-1.1B-shape
+    int4 decoder (configs[3], batch 1, 128-token prompt, 128 greedy steps)."""
+    import torch
+    from yscv_b200.llm_bench import run as llm_run
+    out = {}
+    with torch.cuda.stream(stream):
+        for name, (m, k, n), reps in (("qlinear_matmul_2048x4096x4096", (2048, 4096, 4096), 50),
+                                      ("matmul_integer_64x1024x1024", (64, 1024, 1024), 200)):
+            a = torch.randint(0, 256, (m, k), dtype=torch.uint8, device=dev)
+            b = torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev)
+            pk = ctx.pack_i8_b_dev(b.data_ptr(), k, n)
+            o8 = torch.empty(m, n, dtype=torch.uint8, device=dev)
+            o32 = torch.empty(m, n, dtype=torch.int32, device=dev)
+            rq = ctx.requant(1e-4, 128.0, 0, 255, a_unsigned=True, a_zp=128)
+            if name.startswith("qlinear"):
+                f = lambda: ctx.qlinear_matmul_dev(a.data_ptr(), pk, m, rq, o8.data_ptr())
+            else:
+                f = lambda: ctx.matmul_integer_dev(a.data_ptr(), True, 128, pk, m, o32.data_ptr())
+            for _ in range(5):
+                f()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                f()
+            e1.record(stream)
+            stream.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            out[name] = {"us_per_call": us, "tops": 2.0 * m * k * n / us / 1e6, "kernel": ctx.last_kernel(),
+                         "frac_of_nominal_4500_tops": 2.0 * m * k * n / us / 1e6 / 4500.0}
+            pk.free()
+    stream.synchronize()
+    d = llm_run("tinyllama", batch=1, prompt_len=128, max_tokens=128, warmup=1)
+    out["int4_decoder_tinyllama_b1"] = {k: d[k] for k in ("decode_tokens_per_sec", "ms_per_step", "prefill_ms",
+                                                            "weight_stream_gbs_per_gpu")}
+    return out
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel,
 # from the ncu capture summarised under profiles/ (None until captured).
-NCU_DRAM_BYTES_PER_LAUNCH = None
+NCU_DRAM_BYTES_PER_LAUNCH = 36_747_520  # 36.745 MB read + 2.8 KB written (profiles/int4_gemv_fast_m1_k4096_n14336.md)
 
 
 def main():
@@ -379,6 +424,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the int8 GEMM and decoder side measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -103,6 +103,40 @@ def test_operators(tctx, oracle):
         assert np.max(np.abs(lg.cpu().numpy() - xs @ emb.T)) < 1e-4
         assert am.cpu().numpy().tolist() == [999, 999, 17]
         assert [oracle.argmax_last(tie[i]) for i in range(3)] == [999, 999, 17]
+        wide = synth.normal(8, 0, 2 * 32000, 1.0).reshape(2, 32000)
+        wide[0, [100, 31999]] = 9.0     # tie across partial blocks: the last index wins
+        wide[1, [7, 15000, 15001]] = 9.0
+        dwide = dev(wide)
+        am2 = torch.empty(2, dtype=torch.int32, device="cuda")
+        ctx.argmax_last_dev(dwide.data_ptr(), 2, 32000, am2.data_ptr())
+        s.synchronize()
+        assert am2.cpu().numpy().tolist() == [31999, 15001]
+
+
+def test_split_attention_long_cache(tctx, oracle):
+    """Decode attention over a long cache takes the split-key kernel; same result."""
+    import torch
+    ctx, s = tctx
+    B, nq, nkv, d, max_seq, filled = 2, 8, 2, 128, 1500, 1203
+    with torch.cuda.stream(s):
+        k = synth.normal(31, 0, B * filled * nkv * d, 1.0).reshape(B, filled, nkv * d)
+        v = synth.normal(31, 1, B * filled * nkv * d, 1.0).reshape(B, filled, nkv * d)
+        kc = torch.zeros(B, max_seq, nkv * d, device="cuda")
+        vc = torch.zeros_like(kc)
+        kc[:, :filled] = dev(k)
+        vc[:, :filled] = dev(v)
+        q = synth.normal(31, 2, B * nq * d, 1.0).reshape(B, nq * d)
+        dq = dev(q)
+        pos = torch.full((1,), filled - 1, dtype=torch.int32, device="cuda")
+        out = torch.empty(B, nq * d, device="cuda")
+        ctx.gqa_attention_dev(dq.data_ptr(), nq * d, B, 1, nq, nkv, d, kc.data_ptr(), vc.data_ptr(), max_seq,
+                              pos.data_ptr(), True, out.data_ptr())
+        s.synchronize()
+        assert "split" in ctx.last_kernel()
+        got = out.cpu().numpy()
+        for b in range(B):
+            want = oracle.gqa_attention(q[b], k[b].ravel(), v[b].ravel(), 1, 1, filled, nq, nkv, d, True)
+            assert np.max(np.abs(got[b] - want)) < 2e-5
 
 
 def export_weights(dec):

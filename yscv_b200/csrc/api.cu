@@ -1,5 +1,6 @@
 // C ABI of the library (see include/yscv_cuda.h): argument validation, host
 // staging for the drop-in entry points, dispatch to the kernels.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -62,7 +63,14 @@ static int int4_matmul_dev(yscv_cuda_ctx *ctx, const uint8_t *d_packed, const fl
         float *o = d_out + m0 * n;
         const bool aligned = ((reinterpret_cast<uintptr_t>(d_packed) | reinterpret_cast<uintptr_t>(d_scales) |
                                reinterpret_cast<uintptr_t>(a)) & 15) == 0;
-        if (aligned && int4_gemv_fast_supported(mc, n, k, gs)) {
+        // small matrices are latency-bound: the light warp-per-row kernel starts faster than
+        // the TMA pipeline (threshold in packed bytes, YSCV_CUDA_SMALL_GEMV_BYTES overrides it)
+        static const size_t small_bytes = [] {
+            const char *e = getenv("YSCV_CUDA_SMALL_GEMV_BYTES");
+            return e ? (size_t)strtoull(e, nullptr, 10) : (size_t)0;
+        }();
+        const bool small = mc <= 4 && n * k / 2 <= small_bytes && gs % 32 == 0 && k % 32 == 0;
+        if (!small && aligned && int4_gemv_fast_supported(mc, n, k, gs)) {
             rc = ctx->scratch.reserve(int4_gemv_scratch_bytes(16, k));
             if (rc) return rc;
             rc = int4_gemv_fast(ctx, d_packed, d_scales, a, o, mc, n, k, ctx->scratch.ptr);
@@ -155,6 +163,7 @@ void yscv_cuda_ctx_destroy(yscv_cuda_ctx *ctx) {
     ctx->out0.release();
     ctx->out1.release();
     ctx->scratch.release();
+    ctx->scratch_attn.release();
     if (ctx->d_status) cudaFree(ctx->d_status);
     for (auto &ev : ctx->prof_events) {
         cudaEventDestroy(ev.first);

@@ -61,6 +61,7 @@ struct yscv_cuda_ctx {
     yscv::DeviceBuffer in0, in1, in2, out0, out1;
     // scratch for kernels that need global memory beyond their operands
     yscv::DeviceBuffer scratch;
+    yscv::DeviceBuffer scratch_attn;  // partial outputs of the split attention
 };
 
 struct yscv_cuda_int4_weight {

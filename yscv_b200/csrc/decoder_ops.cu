@@ -91,19 +91,22 @@ add_rms_norm_kernel(const float *x, const float *__restrict__ delta,
 __global__ void rope_kv_append_kernel(float *__restrict__ qkv, int seq, int n_q, int n_kv, int d,
                                       float theta, const int32_t *__restrict__ pos,
                                       float *__restrict__ kc, float *__restrict__ vc, int max_seq) {
+    __shared__ float cs_tab[128], sn_tab[128];  // d/2 <= 128
     const int row = blockIdx.x, b = row / seq, s = row % seq;
     const int p = *pos + s;
     const int half = d / 2;
     const int row_w = (n_q + 2 * n_kv) * d;
     float *r = qkv + (size_t)row * row_w;
     const float fp = (float)p;
-    // q and k heads: one thread per (head, i < half)
+    // the angle of pair i is the same for every head: one table per row
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float inv_freq = 1.0f / powf(theta, 2.0f * (float)i / (float)d);
+        sincosf(inv_freq * fp, &sn_tab[i], &cs_tab[i]);
+    }
+    __syncthreads();
     for (int idx = threadIdx.x; idx < (n_q + n_kv) * half; idx += blockDim.x) {
         const int h = idx / half, i = idx % half;
-        const float inv_freq = 1.0f / powf(theta, 2.0f * (float)i / (float)d);
-        const float angle = inv_freq * fp;
-        float sn, cs;
-        sincosf(angle, &sn, &cs);
+        const float cs = cs_tab[i], sn = sn_tab[i];
         float *v = r + (size_t)h * d;
         const float x0 = v[i], x1 = v[i + half];
         const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
@@ -169,6 +172,101 @@ gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n
         float acc = 0.0f;
         for (int sk = 0; sk < limit; ++sk) acc = fmaf(scores[sk] * inv, vb[(size_t)sk * n_kv * d + i], acc);
         orow[i] = acc;
+    }
+}
+
+// Decode-shaped attention (one query position per sequence) with the keys split across
+// blocks so that a long cache fills the machine: block (split, q head, b) handles keys
+// [split*chunk, ...), leaves an unnormalised partial output, its running max and its
+// exp-sum in `part`; attention_combine_kernel merges the splits (the usual
+// max-rescaling of a split softmax).
+__global__ void __launch_bounds__(128)
+gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int n_kv, int d,
+                        const float *__restrict__ kc, const float *__restrict__ vc, int max_seq,
+                        const int32_t *__restrict__ pos, int chunk, float *__restrict__ part) {
+    // chunk == blockDim.x == 128: one key per thread in the score phase
+    extern __shared__ float sm[];
+    float *scores = sm;            // chunk
+    float *qs = sm + chunk;        // d
+    float *acc2 = qs + d;          // d   (second half of the threads in the V phase)
+    __shared__ float red[4];
+    const int split = blockIdx.x, qh = blockIdx.y, b = blockIdx.z, n_splits = gridDim.x;
+    const int kv_h = qh / (n_q / n_kv);
+    int limit = *pos + 1;
+    limit = limit > max_seq ? max_seq : limit;
+    const int k0 = split * chunk, k1 = min(limit, k0 + chunk);
+    float *po = part + (((size_t)b * n_q + qh) * n_splits + split) * (d + 2);
+    if (k0 >= k1) {  // nothing for this split yet: neutral element of the merge
+        for (int i = threadIdx.x; i < d; i += blockDim.x) po[i] = 0.0f;
+        if (threadIdx.x == 0) { po[d] = -INFINITY; po[d + 1] = 0.0f; }
+        return;
+    }
+    const int nk = k1 - k0;
+    const float scale = 1.0f / sqrtf((float)d);
+    const float *qrow = q + (size_t)b * q_stride + (size_t)qh * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = qrow[i];
+    __syncthreads();
+    const float *kb = kc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const float *vb = vc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    // scores: thread j owns key k0 + j and walks its row with 128-bit loads
+    float sc = -INFINITY;
+    if ((int)threadIdx.x < nk) {
+        const float4 *kr = reinterpret_cast<const float4 *>(kb + (size_t)(k0 + threadIdx.x) * n_kv * d);
+        const float4 *q4 = reinterpret_cast<const float4 *>(qs);
+        float dot = 0.0f;
+#pragma unroll 4
+        for (int i = 0; i < d / 4; ++i) {
+            const float4 kv = __ldg(kr + i), qv = q4[i];
+            dot = fmaf(qv.x, kv.x, dot);
+            dot = fmaf(qv.y, kv.y, dot);
+            dot = fmaf(qv.z, kv.z, dot);
+            dot = fmaf(qv.w, kv.w, dot);
+        }
+        sc = dot * scale;
+    }
+    const float mx = block_max(sc, red);
+    const float e = ((int)threadIdx.x < nk) ? expf(sc - mx) : 0.0f;
+    scores[threadIdx.x] = e;
+    const float se = block_sum(e, red);  // (its barriers also publish `scores`)
+    // weighted V: the two halves of the block take alternate keys, d threads each (d <= 64),
+    // or all threads take every key (d == 128)
+    const int groups = blockDim.x / d >= 2 ? 2 : 1;
+    const int gi = threadIdx.x / d, i = threadIdx.x % d;
+    float acc = 0.0f;
+    if (gi < groups) {
+#pragma unroll 4
+        for (int j = gi; j < nk; j += groups) acc = fmaf(scores[j], __ldg(vb + (size_t)(k0 + j) * n_kv * d + i), acc);
+    }
+    if (groups == 2) {
+        if (gi == 1) acc2[i] = acc;
+        __syncthreads();
+        if (gi == 0) po[i] = acc + acc2[i];
+    } else if (gi == 0) {
+        po[i] = acc;
+    }
+    if (threadIdx.x == 0) { po[d] = mx; po[d + 1] = se; }
+}
+
+__global__ void attention_combine_kernel(const float *__restrict__ part, int n_splits, int d,
+                                         float *__restrict__ out) {
+    // block per (q head, b); out row [b][n_q*d]
+    const size_t hb = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+    const float *p = part + hb * n_splits * (d + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[(size_t)s * (d + 2) + d]);
+    float L = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float m = p[(size_t)s * (d + 2) + d];
+        if (m > -INFINITY) L += expf(m - M) * p[(size_t)s * (d + 2) + d + 1];
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float m = p[(size_t)s * (d + 2) + d];
+            if (m > -INFINITY) acc = fmaf(expf(m - M), p[(size_t)s * (d + 2) + i], acc);
+        }
+        out[hb * d + i] = acc * inv;
     }
 }
 
@@ -255,6 +353,53 @@ argmax_last_kernel(const float *__restrict__ logits, int vocab, int32_t *__restr
     if (threadIdx.x == 0) out[blockIdx.x] = bi[0] < 0 ? 0 : bi[0];
 }
 
+// two-stage variant for wide vocabularies: 64 blocks per row leave (value, index) partials,
+// the single-block kernel above then reduces those (indices carried along)
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float *__restrict__ logits, int vocab, float *__restrict__ pv,
+                      int32_t *__restrict__ pi) {
+    __shared__ float bv[256];
+    __shared__ int bi[256];
+    const int row = blockIdx.y, nb = gridDim.x;
+    const int per = (vocab + nb - 1) / nb;
+    const int lo = blockIdx.x * per, hi = min(vocab, lo + per);
+    const float *r = logits + (size_t)row * vocab;
+    float best = -INFINITY;
+    int idx = -1;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = r[i];
+        if (idx < 0 || !(v < best)) { best = v; idx = i; }
+    }
+    bv[threadIdx.x] = best;
+    bi[threadIdx.x] = idx;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float a = bv[threadIdx.x], b = bv[threadIdx.x + s];
+            const int ia = bi[threadIdx.x], ib = bi[threadIdx.x + s];
+            if (ib >= 0 && (ia < 0 || b > a || (b == a && ib > ia))) { bv[threadIdx.x] = b; bi[threadIdx.x] = ib; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { pv[row * nb + blockIdx.x] = bv[0]; pi[row * nb + blockIdx.x] = bi[0]; }
+}
+
+__global__ void __launch_bounds__(64)
+argmax_final_kernel(const float *__restrict__ pv, const int32_t *__restrict__ pi, int nb,
+                    int32_t *__restrict__ out) {
+    // partials are in increasing index order: scan them in order, later wins ties
+    if (threadIdx.x != 0) return;
+    const int row = blockIdx.x;
+    float best = -INFINITY;
+    int idx = -1;
+    for (int j = 0; j < nb; ++j) {
+        const int i = pi[row * nb + j];
+        const float v = pv[row * nb + j];
+        if (i >= 0 && (idx < 0 || !(v < best))) { best = v; idx = i; }
+    }
+    out[row] = idx < 0 ? 0 : idx;
+}
+
 __global__ void advance_pos_kernel(int32_t *pos, int by) { *pos += by; }
 
 }  // namespace yscv
@@ -313,6 +458,25 @@ int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_s
     if (!d_q || !d_kcache || !d_vcache || !d_pos || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
     if (n_kv == 0 || n_q % n_kv != 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "n_q must be a multiple of n_kv");
     if (batch * seq_q == 0) return YSCV_CUDA_OK;
+    if (seq_q == 1 && causal && max_seq > 128) {
+        // decode over a long cache: split the keys across blocks, then merge
+        if (d_head % 4 != 0 || d_head > 128)
+            return fail(YSCV_CUDA_ERR_UNSUPPORTED, "d_head %zu not supported by the decode attention", d_head);
+        const int chunk = 128;
+        const int n_splits = (int)((max_seq + chunk - 1) / chunk);
+        const size_t need = batch * n_q * (size_t)n_splits * (d_head + 2) * sizeof(float);
+        int rc = ctx->scratch_attn.reserve(need);
+        if (rc) return rc;
+        float *part = reinterpret_cast<float *>(ctx->scratch_attn.ptr);
+        dim3 grid((unsigned)n_splits, (unsigned)n_q, (unsigned)batch);
+        gqa_decode_split_kernel<<<grid, 128, (chunk + 2 * d_head) * sizeof(float), ctx->stream>>>(
+            d_q, (int)q_stride, (int)n_q, (int)n_kv, (int)d_head, d_kcache, d_vcache, (int)max_seq, d_pos, chunk, part);
+        YSCV_CUDA_TRY(cudaGetLastError());
+        ctx->launches++;
+        attention_combine_kernel<<<dim3((unsigned)n_q, (unsigned)batch), 128, 0, ctx->stream>>>(part, n_splits,
+                                                                                               (int)d_head, d_out);
+        DEC_EPILOGUE(ctx, "gqa_attention(split-k)");
+    }
     const size_t smem = (max_seq + d_head) * sizeof(float);
     if (smem > 200 * 1024) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "max_seq %zu too long for the attention kernel", max_seq);
     static int attr_set[16] = {0};
@@ -360,6 +524,18 @@ int yscv_cuda_argmax_last_dev(yscv_cuda_ctx *ctx, const float *d_logits, size_t 
     if (!d_logits || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
     if (rows == 0) return YSCV_CUDA_OK;
     if (vocab == 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "empty vocabulary");
+    if (vocab >= 8192) {
+        const int nb = 64;
+        int rc = ctx->scratch_attn.reserve(rows * nb * 8);
+        if (rc) return rc;
+        float *pv = reinterpret_cast<float *>(ctx->scratch_attn.ptr);
+        int32_t *pi = reinterpret_cast<int32_t *>(pv + rows * nb);
+        argmax_partial_kernel<<<dim3(nb, (unsigned)rows), 256, 0, ctx->stream>>>(d_logits, (int)vocab, pv, pi);
+        YSCV_CUDA_TRY(cudaGetLastError());
+        ctx->launches++;
+        argmax_final_kernel<<<(unsigned)rows, 64, 0, ctx->stream>>>(pv, pi, nb, d_out);
+        DEC_EPILOGUE(ctx, "argmax_last(two-stage)");
+    }
     argmax_last_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(d_logits, (int)vocab, d_out);
     DEC_EPILOGUE(ctx, "argmax_last");
 }

@@ -397,40 +397,49 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
     // byte offset of the digit blob relative to the stage base (per-stage copy) or to `dig`
     const uint32_t b_off = FUSEQ ? 0u : (uint32_t)(g.w_bytes + g.s_bytes);
 
-    if (tid == 0) {
+    // ---------------- producer: one thread drives the TMA ring ----------------
+    // (The first ring of stages is issued after the block-wide sync on purpose: put in
+    // flight any earlier, ~200 KB of weight traffic per SM queues in front of the consumers'
+    // activation loads and delays the quantisation prologue by about 2 us.)
+    const bool is_producer = (warp == FAST_CONSUMER_WARPS) && (lane == 0);
+    const uint32_t tx = (uint32_t)(g.w_bytes + g.s_bytes + (FUSEQ ? 0 : g.q.blob_bytes));
+    int p_slot = 0, p_ks = 0, p_rb = 0;
+    uint32_t p_phase = 0;
+    auto issue_stage = [&]() {
+        const uint32_t st = smem_base + (uint32_t)p_slot * g.stage_bytes;
+        const uint32_t full = bar_full + p_slot * 8;
+        const int row0 = r0 + p_rb * rb_rows;
+        mbar_expect_tx(full, tx);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+            tma_load_2d(st + a * (rb_rows * 128), &tm_w, p_ks * (GS * 16) + a * 128, row0, full);
+        tma_load_2d(st + g.w_bytes, &tm_s, p_ks * GS, row0, full);
+        if constexpr (!FUSEQ)
+            bulk_load(st + b_off, blobs + (size_t)p_ks * g.q.blob_bytes, g.q.blob_bytes, full);
+        if (++p_slot == g.stages) { p_slot = 0; p_phase ^= 1u; }
+        if (++p_ks == k_stages) { p_ks = 0; ++p_rb; }
+    };
+    const int first_wave = total < g.stages ? total : g.stages;
+    if (is_producer) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_w));
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_s));
         for (int i = 0; i < g.stages; ++i) {
             mbar_init(bar_full + i * 8, 1);
             mbar_init(bar_empty + i * 8, FAST_CONSUMER_WARPS);
         }
         mbar_fence_init();
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     __syncthreads();
     TRACE(1);
 
     if (warp == FAST_CONSUMER_WARPS) {
-        // ---------------- producer: one thread drives the TMA ring ----------------
         if (lane == 0) {
-            const uint32_t tx = (uint32_t)(g.w_bytes + g.s_bytes + (FUSEQ ? 0 : g.q.blob_bytes));
-            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_w));
-            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_s));
-            int slot = 0, ks = 0, rb = 0;
-            uint32_t phase = 0;
+            for (int it = 0; it < first_wave; ++it) issue_stage();
             bool alive = true;
-            for (int it = 0; it < total && alive; ++it) {
-                if (it >= g.stages) alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
-                if (!alive) break;
-                const uint32_t st = smem_base + (uint32_t)slot * g.stage_bytes;
-                const uint32_t full = bar_full + slot * 8;
-                const int row0 = r0 + rb * rb_rows;
-                mbar_expect_tx(full, tx);
-#pragma unroll
-                for (int a = 0; a < ATOMS; ++a)
-                    tma_load_2d(st + a * (rb_rows * 128), &tm_w, ks * (GS * 16) + a * 128, row0, full);
-                tma_load_2d(st + g.w_bytes, &tm_s, ks * GS, row0, full);
-                if constexpr (!FUSEQ)
-                    bulk_load(st + b_off, blobs + (size_t)ks * g.q.blob_bytes, g.q.blob_bytes, full);
-                if (++slot == g.stages) { slot = 0; phase ^= 1u; }
-                if (++ks == k_stages) { ks = 0; ++rb; }
+            for (int it = first_wave; it < total && alive; ++it) {
+                alive = mbar_wait(bar_empty + p_slot * 8, p_phase ^ 1u, status);
+                if (alive) issue_stage();
             }
             // A consumer that gave up leaves copies unobserved: wait (bounded) for every
             // stage this thread armed before the CTA may exit.
