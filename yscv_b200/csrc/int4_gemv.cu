@@ -179,13 +179,20 @@ static QuantLayout quant_layout(int mp, int gs) {
 // shared memory. `src` (this lane's 8 floats) is null for padding rows (m >= M),
 // which produce zeros. All 32 lanes of the warp must call this together; lanes
 // whose item is out of range pass valid = false.
+template <bool SMEM_SRC = false>
 __device__ __forceinline__ void quantize_group(const float *__restrict__ src, unsigned char *blobs,
                                                const QuantLayout &q, int Gabs, int m, int t,
                                                bool valid) {
     float v[8];
     if (src && valid) {
-        const float4 x = __ldg(reinterpret_cast<const float4 *>(src));
-        const float4 y = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        float4 x, y;
+        if constexpr (SMEM_SRC) {  // staged in shared memory by the producer
+            x = *reinterpret_cast<const float4 *>(src);
+            y = *(reinterpret_cast<const float4 *>(src) + 1);
+        } else {
+            x = __ldg(reinterpret_cast<const float4 *>(src));
+            y = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        }
         v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
         v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
     } else {
@@ -343,6 +350,7 @@ struct FastGeom {
     int tiles;        // 16-row tiles per row block (1..TP2)
     int stages;       // ring depth
     int w_bytes, s_bytes, stage_bytes;
+    int act_bytes;    // > 0: the producer stages the activations [M][K] in shared memory first
     QuantLayout q;
 };
 
@@ -393,14 +401,18 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar_full = smem_base + ring_bytes + 16 * 8 * 32 * 4;
     const uint32_t bar_empty = bar_full + 8 * 8;
-    unsigned char *dig = smem + ring_bytes + 16 * 8 * 32 * 4 + 2 * 8 * 8;  // FUSEQ: resident blobs
+    const uint32_t bar_act = bar_empty + 8 * 8;
+    unsigned char *dig = smem + ring_bytes + 16 * 8 * 32 * 4 + 2 * 8 * 8 + 16;  // FUSEQ: resident blobs
+    float *act_s = reinterpret_cast<float *>(dig + (size_t)(K / (32 * GS)) * g.q.blob_bytes);
     // byte offset of the digit blob relative to the stage base (per-stage copy) or to `dig`
     const uint32_t b_off = FUSEQ ? 0u : (uint32_t)(g.w_bytes + g.s_bytes);
 
     // ---------------- producer: one thread drives the TMA ring ----------------
-    // (The first ring of stages is issued after the block-wide sync on purpose: put in
-    // flight any earlier, ~200 KB of weight traffic per SM queues in front of the consumers'
-    // activation loads and delays the quantisation prologue by about 2 us.)
+    // With the activations staged by TMA (act_bytes > 0) they are the first copy in the
+    // queue and the first ring of weight stages follows immediately, before the block-wide
+    // sync. Without that staging the ring is issued after the sync on purpose: ~200 KB of
+    // weight traffic per SM in front of the consumers' own activation loads delays the
+    // quantisation prologue by about 2 us.
     const bool is_producer = (warp == FAST_CONSUMER_WARPS) && (lane == 0);
     const uint32_t tx = (uint32_t)(g.w_bytes + g.s_bytes + (FUSEQ ? 0 : g.q.blob_bytes));
     int p_slot = 0, p_ks = 0, p_rb = 0;
@@ -427,15 +439,22 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
             mbar_init(bar_full + i * 8, 1);
             mbar_init(bar_empty + i * 8, FAST_CONSUMER_WARPS);
         }
+        mbar_init(bar_act, 1);
         mbar_fence_init();
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        if (FUSEQ && g.act_bytes > 0) {
+            mbar_expect_tx(bar_act, (uint32_t)g.act_bytes);
+            bulk_load(smem_u32(act_s), act, (uint32_t)g.act_bytes, bar_act);
+            for (int it = 0; it < first_wave; ++it) issue_stage();
+        }
     }
     __syncthreads();
     TRACE(1);
 
     if (warp == FAST_CONSUMER_WARPS) {
         if (lane == 0) {
-            for (int it = 0; it < first_wave; ++it) issue_stage();
+            if (!(FUSEQ && g.act_bytes > 0))
+                for (int it = 0; it < first_wave; ++it) issue_stage();
             bool alive = true;
             for (int it = first_wave; it < total && alive; ++it) {
                 alive = mbar_wait(bar_empty + p_slot * 8, p_phase ^ 1u, status);
@@ -457,12 +476,18 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
         const int items = (K / 32) * slots;
         constexpr int QUADS = FAST_CONSUMER_WARPS * 8;
         const int rounds = (items + QUADS - 1) / QUADS;
+        const bool staged = g.act_bytes > 0;
+        bool act_ok = true;
+        if (staged) act_ok = mbar_wait(bar_act, 0, status);
         for (int r = 0; r < rounds; ++r) {
             const int item = r * QUADS + (tid >> 2);
             const bool valid = item < items;
             const int Gabs = valid ? item % (K / 32) : 0, m = valid ? item / (K / 32) : 0;
-            quantize_group(m < M ? act + (size_t)m * K + Gabs * 32 + 8 * t : nullptr, dig, g.q, Gabs,
-                           m, t, valid);
+            const size_t off = (size_t)m * K + Gabs * 32 + 8 * t;
+            if (staged)
+                quantize_group<true>(m < M && act_ok ? act_s + off : nullptr, dig, g.q, Gabs, m, t, valid);
+            else
+                quantize_group<false>(m < M ? act + off : nullptr, dig, g.q, Gabs, m, t, valid);
         }
         named_bar_sync(1, FAST_CONSUMER_WARPS * 32);
     }
@@ -658,12 +683,15 @@ static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scale
     g.w_bytes = rb_rows * GS * 16;
     g.s_bytes = rb_rows * GS * 4;
     const int digit_bytes = FUSEQ ? (K / (32 * GS)) * q.blob_bytes : 0;
+    // stage the activations through TMA when they are small (M <= 2) and 16-byte aligned
+    g.act_bytes = (FUSEQ && MP <= 2 && (size_t)M * K * 4 <= 32 * 1024 &&
+                   (reinterpret_cast<uintptr_t>(act) & 15) == 0) ? M * K * 4 : 0;
     g.stage_bytes = ((g.w_bytes + g.s_bytes + (FUSEQ ? 0 : q.blob_bytes) + 1023) / 1024) * 1024;
     const int red_bytes = 16 * 8 * 32 * 4;
-    const int bar_bytes = 2 * 8 * 8;
-    const int budget = 227 * 1024 - red_bytes - bar_bytes - digit_bytes - 1024;
+    const int bar_bytes = 2 * 8 * 8 + 16;
+    const int budget = 227 * 1024 - red_bytes - bar_bytes - digit_bytes - g.act_bytes - 1024;
     g.stages = max(2, min(8, budget / g.stage_bytes));
-    const int smem = g.stages * g.stage_bytes + red_bytes + bar_bytes + digit_bytes;
+    const int smem = g.stages * g.stage_bytes + red_bytes + bar_bytes + digit_bytes + g.act_bytes;
     // tensor maps: weights as bytes [N][K/2], box [rb_rows][128] with the 128-byte swizzle;
     // scales as f32 [N][K/32], box [rb_rows][GS] with the swizzle that matches its width
     CUtensorMap tm_w, tm_s;
