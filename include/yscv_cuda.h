@@ -72,6 +72,12 @@ const char *yscv_cuda_last_error(void);
 const char *yscv_cuda_last_kernel(const yscv_cuda_ctx *ctx);
 /* Number of kernels this library has launched on the context so far. */
 uint64_t yscv_cuda_ctx_launch_count(const yscv_cuda_ctx *ctx);
+/* int4 matmuls with more than 16 activation rows run on the bf16 tensor-core path
+ * (relative Frobenius error ~3e-3 against the fp32 kernel, bound 2e-2). exact != 0 keeps
+ * the fp32-exact decode kernel for them, 16 rows per pass (slower, error ~1e-6): the
+ * counterpart of choosing packed_int4_gemm_scalar over a SIMD variant
+ * (crates/yscv-kernels/src/ops/int4_matmul.rs:548-605). */
+int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact);
 /* Per-kernel timing, the counterpart of YSCV_RUNNER_PROFILE
  * (crates/yscv-onnx/src/runner/profile.rs:1-120): while enabled, the dominant
  * kernel of every call is bracketed by CUDA events on the context's stream.

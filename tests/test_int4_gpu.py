@@ -9,6 +9,11 @@ from yscv_b200 import synth
 pytestmark = pytest.mark.gpu
 
 REL_TOL = 1e-4  # max|diff| / max|ref|, the definition kernel_bench uses (kernel_bench.rs:97-103)
+FRO_TOL = 2e-2  # relative Frobenius error allowed for the bf16 tensor-core prefill GEMM (m > 16)
+
+
+def fro_err(got, want):
+    return float(np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30))
 
 
 def rel_err(got, want):
@@ -45,6 +50,11 @@ def test_gemm_reference_cases(ctx, oracle):
         act = oracle.lcg_f32(0x200 + m, m * k)
         want = oracle.int4_gemm(packed, scales, act, m, n, k, g)
         got = ctx.packed_int4_gemm(packed, scales, act, m, n, k, g)
+        if m > 16:  # bf16 tensor-core path, then the exact one
+            assert fro_err(got, want) <= FRO_TOL, m
+            ctx.set_int4_prefill_exact(True)
+            got = ctx.packed_int4_gemm(packed, scales, act, m, n, k, g)
+            ctx.set_int4_prefill_exact(False)
         assert np.max(np.abs(got - want)) <= 1e-3, m
 
 
@@ -71,7 +81,34 @@ def test_odd_shapes(ctx, oracle, m, n, k, g):
     want = oracle.exec_matmul_int4(packed, scales, act, m, n, k, g)
     got = ctx.packed_int4_gemm(packed, scales, act, m, n, k, g)
     assert got.shape == (m, n)
+    if "prefill" in ctx.last_kernel():
+        assert fro_err(got, want) <= FRO_TOL
+        ctx.set_int4_prefill_exact(True)
+        got = ctx.packed_int4_gemm(packed, scales, act, m, n, k, g)
+        ctx.set_int4_prefill_exact(False)
     assert rel_err(got, want) <= REL_TOL, (ctx.last_kernel(), rel_err(got, want))
+
+
+# ---- prefill shapes: tcgen05 bf16 GEMM, relative Frobenius error <= 2e-2 ----------
+
+@pytest.mark.parametrize("m,n,k", [(17, 128, 64), (128, 2560, 2048), (200, 1000, 1024), (333, 130, 4096),
+                                   (512, 4096, 512), (1024, 300, 256), (2048, 1024, 2048)])
+def test_prefill_gemm(ctx, oracle, m, n, k):
+    g = 32
+    packed, scales = make_weights(oracle, 21, n, k, g)
+    act = synth.normal(22, 1, m * k, 1.0)
+    want = oracle.exec_matmul_int4(packed, scales, act, m, n, k, g, threads=8)
+    got = ctx.packed_int4_gemm(packed, scales, act, m, n, k, g)
+    assert "prefill" in ctx.last_kernel()
+    e = fro_err(got, want)
+    assert e <= FRO_TOL, e
+    assert e > 1e-6          # it really is the bf16 path
+    assert ctx.device_status() == 0
+    # every row is as good as the whole: no tile is left out or duplicated
+    rows = np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)
+    assert np.max(rows) <= FRO_TOL, int(np.argmax(rows))
+    cols = np.linalg.norm(got - want, axis=0) / np.maximum(np.linalg.norm(want, axis=0), 1e-30)
+    assert np.max(cols) <= 5 * FRO_TOL, int(np.argmax(cols))
 
 
 def test_kernel_selection(ctx, oracle):

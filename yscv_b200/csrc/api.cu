@@ -57,6 +57,16 @@ static int int4_matmul_dev(yscv_cuda_ctx *ctx, const uint8_t *d_packed, const fl
     int rc = check_int4_shape(n, k, gs);
     if (rc) return rc;
     if (m == 0) return YSCV_CUDA_OK;
+    // prefill shapes: dequantise to bf16 in shared memory, tcgen05 MMA, fp32 accumulate
+    // (yscv_cuda_ctx_set_int4_prefill_exact keeps the fp32-exact kernel, 16 rows per pass)
+    const bool exact_prefill = ctx->prefill_exact;
+    const bool all_aligned = ((reinterpret_cast<uintptr_t>(d_packed) | reinterpret_cast<uintptr_t>(d_scales) |
+                               reinterpret_cast<uintptr_t>(d_act)) & 15) == 0;
+    if (!exact_prefill && all_aligned && int4_prefill_supported(m, n, k, gs)) {
+        rc = ctx->scratch.reserve(int4_prefill_scratch_bytes(m, k));
+        if (rc) return rc;
+        return int4_prefill_gemm(ctx, d_packed, d_scales, d_act, d_out, m, n, k, ctx->scratch.ptr);
+    }
     for (size_t m0 = 0; m0 < m; m0 += 16) {
         const size_t mc = m - m0 < 16 ? m - m0 : 16;
         const float *a = d_act + m0 * k;
@@ -206,6 +216,12 @@ int yscv_cuda_ctx_profile_read(yscv_cuda_ctx *ctx, uint64_t *launches, double *t
     *launches = ctx->prof_used;
     *total_ms = sum;
     ctx->prof_used = 0;
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    ctx->prefill_exact = exact != 0;
     return YSCV_CUDA_OK;
 }
 

@@ -51,6 +51,7 @@ struct yscv_cuda_ctx {
     int *d_status = nullptr;   // device status word
     uint64_t launches = 0;
     const char *last_kernel = "none";
+    bool prefill_exact = false;  // int4 matmul with m > 16: fp32-exact kernel instead of bf16 MMA
     // optional per-kernel event timing (yscv_cuda_ctx_profile_*)
     bool profiling = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;

@@ -1,0 +1,368 @@
+// Prefill-shaped (M > 16) packed-int4 x fp32 matmul on the 5th-generation tensor
+// cores: weights are dequantised to bf16 in shared memory and multiplied with bf16
+// activations by tcgen05.mma.kind::f16 with fp32 accumulators in TMEM.
+//
+// Replaces packed_int4_gemm_dispatch for large M
+// (crates/yscv-kernels/src/ops/int4_matmul.rs:387-435, 548-605) with the same operands:
+// weights [N][K/2] nibbles + scales [N][K/32], activations [M][K] f32, output [M][N] f32.
+// Accuracy contract: bf16 rounding of q*scale and of the activations, fp32 accumulate;
+// relative Frobenius error ~3e-3 against the fp32 scalar kernel (bound 2e-2).
+//
+// Orientation: the weight rows are the MMA's M side (128 output channels per CTA
+// tile), the tokens its N side (a tile of BT tokens, NT tiles per pass), so a short
+// prefill still fills the instruction and every weight tile is dequantised once per
+// NT*BT tokens.
+//
+// Kernel: persistent, 320 threads:
+//   warp 0      TMA producer: per 64-k block the packed nibbles [128 rows][32 B] and the
+//               bf16 activation tiles [BT tokens][64 k] (128-byte swizzle)
+//   warp 1      allocates TMEM, issues the MMAs (4 per block and token tile), commits
+//               stages, A buffers and finished accumulators
+//   warps 2-5   dequantise: thread r owns weight row r of the tile; 8 nibbles become four
+//               bf16x2 with 3 shifts + 4 lop3 (0x4300 | nibble^8 = 136 + q exactly), then
+//               subtract 136 and multiply by the group scale; one 16-byte store per word
+//               into the swizzled A tile (double-buffered)
+//   warps 6-9   epilogue: tcgen05.ld, coalesced fp32 stores out[token][n]
+// The nibble pairs come out as k = (0,4),(1,5),(2,6),(3,7) of each group of 8; the
+// activation pre-pass writes its bf16 copy in the same order, so no permutation is
+// needed in the loop. All mbarrier waits are bounded.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "kernels.cuh"
+#include "tma.cuh"
+
+namespace yscv {
+
+constexpr int PG_BM = 128;      // weight rows per tile
+constexpr int PG_BK = 64;       // k per block: 64 bf16 = one 128-byte swizzle row
+constexpr int PG_THREADS = 320;
+
+struct PGParams {
+    int M, N, K;
+    int BT, NT;          // tokens per MMA tile (multiple of 16, <= 256), tiles per pass
+    int n_tiles, t_chunks, k_blocks;
+    int stages, stage_bytes;
+};
+
+__device__ __forceinline__ void pg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void pg_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ uint64_t pg_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void pg_mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void pg_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void pg_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// fp32 activations -> bf16, k order inside every group of 8 permuted to 0,4,1,5,2,6,3,7
+__global__ void act_to_bf16_kernel(const float *__restrict__ act, __nv_bfloat16 *__restrict__ out,
+                                   size_t groups8) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < groups8;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(act) + 2 * i);
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(act) + 2 * i + 1);
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, b.x);  // k 0,4
+        __nv_bfloat162 p1 = __floats2bfloat162_rn(a.y, b.y);  // k 1,5
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(a.z, b.z);  // k 2,6
+        __nv_bfloat162 p3 = __floats2bfloat162_rn(a.w, b.w);  // k 3,7
+        uint4 v;
+        v.x = *reinterpret_cast<uint32_t *>(&p0);
+        v.y = *reinterpret_cast<uint32_t *>(&p1);
+        v.z = *reinterpret_cast<uint32_t *>(&p2);
+        v.w = *reinterpret_cast<uint32_t *>(&p3);
+        reinterpret_cast<uint4 *>(out)[i] = v;
+    }
+}
+
+__global__ void __launch_bounds__(PG_THREADS, 1)
+int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
+                         const float *__restrict__ scales, float *__restrict__ out, PGParams p,
+                         int *__restrict__ status) {
+    constexpr int W_BYTES = PG_BM * 32;            // packed nibbles of one k block: 4 KB
+    constexpr int A_TILE = PG_BM * PG_BK * 2;      // dequantised bf16 tile: 16 KB
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t smem_base = smem_u32(smem);
+    // [A tile 0][A tile 1][stages x {act tiles NT*BT*128 B | packed 4 KB}][barriers][tmem slot]
+    const uint32_t a_tiles = smem_base;
+    const uint32_t ring = smem_base + 2 * A_TILE;
+    const int act_bytes = p.NT * p.BT * 128;
+    const uint32_t bars = ring + (uint32_t)p.stages * p.stage_bytes;
+    const uint32_t bar_full = bars, bar_empty = bars + 64, bar_afull = bars + 128, bar_aempty = bars + 144;
+    const uint32_t bar_tfull = bars + 160, bar_tempty = bars + 176;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 2 * A_TILE + (size_t)p.stages * p.stage_bytes + 192);
+    const int tiles = p.n_tiles * p.t_chunks;
+    const int acc_cols = p.NT * p.BT;              // TMEM columns of one accumulator buffer (<= 256)
+
+    if (tid == 0) {
+        for (int i = 0; i < p.stages; ++i) {
+            mbar_init(bar_full + i * 8, 1);
+            mbar_init(bar_empty + i * 8, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_afull + i * 8, 4);    // one arrival per dequant warp
+            mbar_init(bar_aempty + i * 8, 1);
+            mbar_init(bar_tfull + i * 8, 1);
+            mbar_init(bar_tempty + i * 8, 4);   // one arrival per epilogue warp
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    pg_fence_before();
+    __syncthreads();
+    pg_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int slot = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+                const int nt_i = t % p.n_tiles, tc = t / p.n_tiles;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
+                    if (!alive) break;
+                    const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
+                    const uint32_t full = bar_full + slot * 8;
+                    mbar_expect_tx(full, (uint32_t)(act_bytes + W_BYTES));
+                    for (int j = 0; j < p.NT; ++j)
+                        tma_load_2d(st + j * (p.BT * 128), &tm_a, kb * PG_BK, tc * acc_cols + j * p.BT, full);
+                    tma_load_2d(st + act_bytes, &tm_w, kb * 32, nt_i * PG_BM, full);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // D fp32, A and B bf16, both K-major, N = BT, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BT >> 3) << 17) |
+                                   ((uint32_t)(PG_BM >> 4) << 24);
+            int slot = 0, abuf = 0, tbuf = 0;
+            uint32_t phase = 0, aphase = 0, tphase = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+                alive = mbar_wait(bar_tempty + tbuf * 8, tphase ^ 1u, status);
+                if (!alive) break;
+                pg_fence_after();
+                const uint32_t tacc = tmem_base + (uint32_t)tbuf * 256;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    alive = mbar_wait(bar_full + slot * 8, phase, status) &&
+                            mbar_wait(bar_afull + abuf * 8, aphase, status);
+                    if (!alive) break;
+                    pg_fence_after();
+                    const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
+                    const uint64_t da = pg_desc_sw128(a_tiles + abuf * A_TILE);
+                    for (int j = 0; j < p.NT; ++j) {
+                        const uint64_t db = pg_desc_sw128(st + j * (p.BT * 128));
+#pragma unroll
+                        for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
+                            pg_mma_bf16(tacc + j * p.BT, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
+                                        (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    pg_commit(bar_empty + slot * 8);
+                    pg_commit(bar_aempty + abuf * 8);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                    if (++abuf == 2) { abuf = 0; aphase ^= 1u; }
+                }
+                if (!alive) break;
+                pg_commit(bar_tfull + tbuf * 8);
+                if (++tbuf == 2) { tbuf = 0; tphase ^= 1u; }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- dequantise: thread r = weight row r of the tile ----------------
+        const int r = (warp - 2) * 32 + lane;
+        const int groups = p.K / 32;
+        int slot = 0, abuf = 0;
+        uint32_t phase = 0, aphase = 0;
+        bool alive = true;
+        for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+            const int nt_i = t % p.n_tiles;
+            const int row = nt_i * PG_BM + r;
+            const float *srow = scales + (size_t)(row < p.N ? row : 0) * groups;
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                alive = mbar_wait(bar_full + slot * 8, phase, status) &&
+                        mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
+                if (!alive) break;
+                const unsigned char *st = smem + 2 * A_TILE + (size_t)slot * p.stage_bytes + act_bytes;
+                const uint4 w0 = *reinterpret_cast<const uint4 *>(st + r * 32);
+                const uint4 w1 = *reinterpret_cast<const uint4 *>(st + r * 32 + 16);
+                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const float2 sc = (row < p.N) ? __ldg(reinterpret_cast<const float2 *>(srow + kb * 2))
+                                              : make_float2(0.0f, 0.0f);
+                const __nv_bfloat162 s0 = __float2bfloat162_rn(sc.x), s1 = __float2bfloat162_rn(sc.y);
+                const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
+                unsigned char *arow = smem + (size_t)abuf * A_TILE + (size_t)r * 128;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t w = words[i];
+                    uint32_t x[4];
+                    // 0x4300 | (nibble ^ 8) is the bf16 value 136 + q, exactly
+                    asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[0]) : "r"(w));
+                    asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[1]) : "r"(w >> 4));
+                    asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[2]) : "r"(w >> 8));
+                    asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[3]) : "r"(w >> 12));
+                    const __nv_bfloat162 s = (i < 4) ? s0 : s1;
+                    uint4 o;
+                    uint32_t *ov = &o.x;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&x[j]);
+                        v = __hmul2(__hsub2(v, bias), s);
+                        ov[j] = *reinterpret_cast<uint32_t *>(&v);
+                    }
+                    // 16-byte chunk i of row r sits at chunk i ^ (r & 7) (128-byte swizzle)
+                    *reinterpret_cast<uint4 *>(arow + ((i ^ (r & 7)) << 4)) = o;
+                }
+                // make the generic-proxy writes visible to the tensor core's async proxy
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_afull + abuf * 8);
+                if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                if (++abuf == 2) { abuf = 0; aphase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 6..9 own TMEM lanes 32*(warp%4).. ----------------
+        const int q = warp & 3;
+        int tbuf = 0;
+        uint32_t tphase = 0;
+        bool alive = true;
+        for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+            const int nt_i = t % p.n_tiles, tc = t / p.n_tiles;
+            alive = mbar_wait(bar_tfull + tbuf * 8, tphase, status);
+            if (!alive) break;
+            pg_fence_after();
+            const int n = nt_i * PG_BM + q * 32 + lane;           // output channel of this lane
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)tbuf * 256;
+#pragma unroll 1
+            for (int c0 = 0; c0 < acc_cols; c0 += 32) {
+                uint32_t rr[32];
+                pg_tmem_ld32(taddr + c0, rr);
+                const int tok0 = tc * acc_cols + c0;
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (tok0 + j < p.M) out[(size_t)(tok0 + j) * p.N + n] = __uint_as_float(rr[j]);
+                }
+            }
+            pg_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + tbuf * 8);
+            if (++tbuf == 2) { tbuf = 0; tphase ^= 1u; }
+        }
+    }
+
+    pg_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        pg_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+size_t int4_prefill_scratch_bytes(size_t m, size_t k) { return m * k * 2 + 256; }
+
+bool int4_prefill_supported(size_t m, size_t n, size_t k, size_t gs) {
+    return tensor_map_encoder() != nullptr && gs == 32 && k % 64 == 0 && m > 16 && n >= 1 &&
+           m < (1u << 30) && n < (1u << 30) && k < (1u << 30);
+}
+
+int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, const float *act,
+                      float *out, size_t m, size_t n, size_t k, void *scratch) {
+    PGParams p = {};
+    p.M = (int)m;
+    p.N = (int)n;
+    p.K = (int)k;
+    // token tiling: up to 256 tokens per pass, as two MMA tiles of up to 128
+    const int m16 = (int)((m + 15) / 16 * 16);
+    if (m16 <= 128) {
+        p.BT = m16;
+        p.NT = 1;
+    } else {
+        p.BT = 128;
+        p.NT = 2;
+    }
+    const int acc_cols = p.BT * p.NT;
+    p.n_tiles = (p.N + PG_BM - 1) / PG_BM;
+    p.t_chunks = (p.M + acc_cols - 1) / acc_cols;
+    p.k_blocks = p.K / PG_BK;
+    p.stage_bytes = ((p.NT * p.BT * 128 + PG_BM * 32 + 1023) / 1024) * 1024;
+    p.stages = (227 * 1024 - 2 * PG_BM * PG_BK * 2 - 1024) / p.stage_bytes;
+    if (p.stages > 8) p.stages = 8;
+    const int smem = 2 * PG_BM * PG_BK * 2 + p.stages * p.stage_bytes + 256;
+
+    __nv_bfloat16 *abf = reinterpret_cast<__nv_bfloat16 *>(scratch);
+    const size_t groups8 = m * k / 8;
+    const unsigned cb = (unsigned)((groups8 + 255) / 256 < 8192 ? (groups8 + 255) / 256 : 8192);
+    act_to_bf16_kernel<<<cb, 256, 0, ctx->stream>>>(act, abf, groups8);
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+
+    CUtensorMap tm_w, tm_a;
+    int rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, n, k / 2, k / 2, PG_BM, 32,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, m, k, k * 2, (uint32_t)p.BT, PG_BK,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    static int smem_set[16] = {0};
+    if (ctx->device >= 16 || !smem_set[ctx->device]) {
+        YSCV_CUDA_TRY(cudaFuncSetAttribute(int4_prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           227 * 1024));
+        if (ctx->device < 16) smem_set[ctx->device] = 1;
+    }
+    const int tiles = p.n_tiles * p.t_chunks;
+    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    ctx->prof_begin();
+    int4_prefill_gemm_kernel<<<grid, PG_THREADS, smem, ctx->stream>>>(tm_w, tm_a, scales, out, p, ctx->d_status);
+    ctx->prof_end();
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    ctx->last_kernel = "int4_prefill_gemm(tcgen05,bf16)";
+    return YSCV_CUDA_OK;
+}
+
+}  // namespace yscv
