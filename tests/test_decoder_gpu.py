@@ -146,9 +146,15 @@ def export_weights(dec):
     return full
 
 
-def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logit_tol):
+def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logit_tol, exact_prefill=True):
+    """exact_prefill: the prompt pass uses the fp32-exact int4 kernel (tokens must then match the
+    oracle except at rounding-level ties); otherwise the bf16 tensor-core GEMM, whose logits
+    may differ by up to 2e-2 (relative Frobenius) and whose tokens may differ only where the
+    oracle's own top-2 margin is inside that noise."""
     import torch
     ctx, s = tctx
+    ctx.set_int4_prefill_exact(exact_prefill)
+    flip_margin = 1e-4 if exact_prefill else 5e-2
     dec = Int4Decoder.with_full_weights(ctx, cfg, batch, prompt_len + steps + 1, s, seed=seed, layers=n_layers)
     from oracle_decoder import OracleDecoder
     ref = OracleDecoder(oracle, cfg, n_layers, export_weights(dec), dec.embedding.cpu().numpy(),
@@ -160,13 +166,30 @@ def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logi
     want_logits, want_next = ref.forward(prompt, prompt_len)
     got_logits = logits.cpu().numpy()
     rel = np.linalg.norm(got_logits - want_logits) / np.linalg.norm(want_logits)
+    ctx.set_int4_prefill_exact(False)
     assert rel < logit_tol, rel
-    assert np.array_equal(dec.next_tokens.cpu().numpy(), want_next)  # token chosen by the prefill
+    if exact_prefill:
+        assert np.array_equal(dec.next_tokens.cpu().numpy(), want_next)  # token chosen by the prefill
+    else:
+        assert rel > 1e-6  # the prompt pass really took the bf16 path
+    if not exact_prefill:
+        # the KV cache now carries bf16-level noise: follow the GPU's tokens and require the
+        # logits of every decode step to stay within the same bound
+        toks = dec.next_tokens.cpu().numpy().astype(np.int32)
+        for i in range(steps):
+            with torch.cuda.stream(s):
+                lg = dec.forward(dec.next_tokens, 1)
+            s.synchronize()
+            wl, _ = ref.forward(toks.reshape(batch, 1), 1)
+            r = np.linalg.norm(lg.cpu().numpy() - wl) / np.linalg.norm(wl)
+            assert r < 1.5 * logit_tol, (i, r)
+            toks = dec.next_tokens.cpu().numpy().astype(np.int32)
+        return rel
     dec.capture_decode_step()
     got = dec.decode(steps)                        # [steps, batch], enqueued on the decoder's stream
     s.synchronize()
     got = got.cpu().numpy()
-    toks = want_next
+    toks = dec.next_tokens.cpu().numpy().astype(np.int32) if not exact_prefill else want_next
     mism = 0
     for i in range(steps):
         lg, nxt = ref.forward(toks.reshape(batch, 1), 1)
@@ -174,10 +197,10 @@ def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logi
             if got[i, b] != nxt[b]:
                 # a flip is only acceptable when the oracle's own top-2 margin is at rounding level
                 srt = np.sort(lg[b])
-                assert srt[-1] - srt[-2] < 1e-4 * max(1.0, abs(srt[-1])), (i, b, srt[-1] - srt[-2])
+                assert srt[-1] - srt[-2] < flip_margin * max(1.0, abs(srt[-1])), (i, b, srt[-1] - srt[-2])
                 mism += 1
         toks = got[i].astype(np.int32)  # follow the GPU's token so one tie cannot derail the rest
-    assert mism <= 1
+    assert mism <= (1 if exact_prefill else steps * batch // 4)
     return rel
 
 
@@ -190,6 +213,12 @@ def test_tinyllama_shape_greedy_tokens(tctx, oracle):
     # BASELINE config 4 shape, seed 3; 4 of the 22 layers keep the CPU oracle in seconds,
     # the full depth runs in bench/decoder measurements
     run_parity(tctx, oracle, TINYLLAMA_1B, 4, batch=1, prompt_len=128, steps=32, seed=3, logit_tol=1e-4)
+
+
+def test_tinyllama_shape_bf16_prefill(tctx, oracle):
+    # same decoder with the prompt pass on the tensor-core GEMM: logits within 2e-2
+    run_parity(tctx, oracle, TINYLLAMA_1B, 4, batch=1, prompt_len=128, steps=16, seed=3, logit_tol=2e-2,
+               exact_prefill=False)
 
 
 def test_graph_replay_equals_eager(tctx):
