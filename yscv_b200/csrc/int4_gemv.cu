@@ -183,6 +183,31 @@ template <bool SMEM_SRC = false>
 __device__ __forceinline__ void quantize_group(const float *__restrict__ src, unsigned char *blobs,
                                                const QuantLayout &q, int Gabs, int m, int t,
                                                bool valid) {
+    if (!src) {
+        // padding row (m >= M): all digits, the scale factor and the correction are zero.
+        // A warp's eight quads belong to the same row (K/32 is a multiple of 8), so the whole
+        // warp takes this branch together and skips the shuffles below.
+        if (!valid) return;
+        const int ks = Gabs / q.gs, G = Gabs % q.gs;
+        unsigned char *blob = blobs + (size_t)ks * q.blob_bytes;
+        if (q.mp <= 2) {
+            uint2 *frag = reinterpret_cast<uint2 *>(blob);
+            const int C = q.ms;
+            if (4 * m < C)
+                for (int c = 0; c < 4; ++c) frag[((G * C + 4 * m + c) * 4 + t) * 2] = make_uint2(0u, 0u);
+            for (int col = t; col < C; col += 4) {
+                frag[((G * C + col) * 4 + 2 * m) * 2 + 1] = make_uint2(0u, 0u);
+                frag[((G * C + col) * 4 + 2 * m + 1) * 2 + 1] = make_uint2(0u, 0u);
+            }
+        } else {
+            if (m < q.ms) {
+                reinterpret_cast<uint4 *>(blob)[(G * q.ms + m) * 4 + t] = make_uint4(0u, 0u, 0u, 0u);
+                reinterpret_cast<uint2 *>(blob + q.off_h1)[(G * q.ms + m) * 4 + t] = make_uint2(0u, 0u);
+            }
+            if (t == 0 && m < q.mc) reinterpret_cast<int2 *>(blob + q.off_meta)[G * q.mc + m] = make_int2(0, 0);
+        }
+        return;
+    }
     float v[8];
     if (src && valid) {
         float4 x, y;
@@ -508,14 +533,25 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
     // scale tile: 16-byte chunk j of a row sits at chunk j ^ phase (TMA 64B / 32B swizzle)
     const uint32_t s_phase = (GS == 16) ? ((rowA >> 1) & 3) : ((rowA >> 2) & 1);
     const uint32_t s_row = g.w_bytes + (uint32_t)rowA * (GS * 4);
-    const int fc = COLS ? g.q.ms : 0;  // columns stored per group (columns form)
-    const int mslot = (MP < 8) ? min(gq, g.q.ms - 1) : gq;
+    // the digit-blob layout is a pure function of (MP, GS): keep it in compile-time constants
+    // so that every per-group offset below folds into an immediate (see quant_layout())
+    constexpr int Q_MS = COLS ? (MP == 1 ? 4 : 8) : (MP < 8 ? MP + 1 : MP);
+    constexpr int Q_MC = COLS ? 4 : (MP <= 8 ? 8 : 16);
+    constexpr int Q_OFF_H1 = COLS ? 0 : GS * Q_MS * 4 * 16;
+    constexpr int Q_OFF_META = COLS ? 0 : Q_OFF_H1 + GS * Q_MS * 4 * 8;
+    constexpr int fc = COLS ? Q_MS : 1;  // columns stored per group (columns form)
+    const int mslot = (MP < 8) ? min(gq, Q_MS - 1) : gq;
     const uint32_t f_off = COLS ? b_off + (uint32_t)((G0 * fc + (gq & (fc - 1))) * 4 + t) * 16
-                                : b_off + (uint32_t)((G0 * g.q.ms + mslot) * 4 + t) * 16;
-    const uint32_t h1_off = b_off + g.q.off_h1 + (uint32_t)((G0 * g.q.ms + mslot) * 4 + t) * 8;
-    const uint32_t mt_off = b_off + g.q.off_meta + (uint32_t)(G0 * g.q.mc + 2 * t) * 8;
-    const uint32_t f_step = COLS ? fc * 4 * 16 : g.q.ms * 4 * 16;  // bytes per group
-    const uint32_t h1_step = g.q.ms * 4 * 8, mt_step = g.q.mc * 8;
+                                : b_off + (uint32_t)((G0 * Q_MS + mslot) * 4 + t) * 16;
+    const uint32_t h1_off = b_off + Q_OFF_H1 + (uint32_t)((G0 * Q_MS + mslot) * 4 + t) * 8;
+    const uint32_t mt_off = b_off + Q_OFF_META + (uint32_t)(G0 * Q_MC + 2 * t) * 8;
+    constexpr uint32_t f_step = COLS ? fc * 4 * 16 : Q_MS * 4 * 16;  // bytes per group
+    constexpr uint32_t h1_step = Q_MS * 4 * 8, mt_step = Q_MC * 8;
+    // 16-byte chunk offsets of this thread's scale groups (four groups per chunk)
+    uint32_t s_ch[(GPW + 3) / 4];
+#pragma unroll
+    for (int c = 0; c < (GPW + 3) / 4; ++c)
+        s_ch[c] = s_row + (((((uint32_t)(G0 + 4 * c)) >> 2) ^ s_phase) << 4);
     const int mul_hi = (t & 1) ? 1 : 65536;  // columns form: plane weight of this thread's c0
 
     float acc[NACC];
@@ -537,9 +573,8 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
             if constexpr (GPW % 4 == 0) {
 #pragma unroll
                 for (int gi = 0; gi < GPW; gi += 4) {
-                    const uint32_t ch = ((((uint32_t)(G0 + gi) >> 2) ^ s_phase) << 4);
-                    const uint4 x = lds128(st, s_row + ch);
-                    const uint4 y = lds128(st, s_row + 8 * (GS * 4) + ch);
+                    const uint4 x = lds128(st, s_ch[gi / 4]);
+                    const uint4 y = lds128(st, s_ch[gi / 4] + 8 * (GS * 4));
                     sA[gi] = __uint_as_float(x.x); sA[gi + 1] = __uint_as_float(x.y);
                     sA[gi + 2] = __uint_as_float(x.z); sA[gi + 3] = __uint_as_float(x.w);
                     sB[gi] = __uint_as_float(y.x); sB[gi + 1] = __uint_as_float(y.y);
