@@ -36,6 +36,34 @@ struct DeviceBuffer {
 
 }  // namespace yscv
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// A kernel launched through launch_pdl() may be scheduled while its predecessor in the
+// stream is still draining. It must call pdl_wait() before it reads anything a predecessor
+// wrote or writes anything a predecessor may still read; pdl_trigger() lets its own
+// successor be scheduled early. Both are no-ops for a normally launched kernel.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+namespace yscv {
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+}  // namespace yscv
+#endif
+
 // Device status codes written by bounded waits inside kernels.
 enum : int {
     YSCV_DEV_OK = 0,

@@ -48,6 +48,8 @@ __device__ __forceinline__ float block_max(float v, float *red) {
 
 __global__ void embedding_kernel(const float *__restrict__ w, const int32_t *__restrict__ tokens,
                                  float *__restrict__ out, int vocab, int dim) {
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x;
     int tok = tokens[row];
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
@@ -61,6 +63,8 @@ __global__ void __launch_bounds__(256)
 add_rms_norm_kernel(const float *x, const float *__restrict__ delta,
                     const float *__restrict__ gamma, float eps, int hidden,
                     float *x_out, float *__restrict__ normed) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float red[8];
     const size_t base = (size_t)blockIdx.x * hidden;
     float ss = 0.0f;
@@ -91,6 +95,8 @@ add_rms_norm_kernel(const float *x, const float *__restrict__ delta,
 __global__ void rope_kv_append_kernel(float *__restrict__ qkv, int seq, int n_q, int n_kv, int d,
                                       float theta, const int32_t *__restrict__ pos,
                                       float *__restrict__ kc, float *__restrict__ vc, int max_seq) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float cs_tab[128], sn_tab[128];  // d/2 <= 128
     const int row = blockIdx.x, b = row / seq, s = row % seq;
     const int p = *pos + s;
@@ -131,6 +137,8 @@ __global__ void __launch_bounds__(128)
 gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n_q, int n_kv, int d,
                      const float *__restrict__ kc, const float *__restrict__ vc, int max_seq,
                      const int32_t *__restrict__ pos, int causal, float *__restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ float sm[];
     float *scores = sm;           // max_seq
     float *qs = sm + max_seq;     // d
@@ -184,6 +192,8 @@ __global__ void __launch_bounds__(128)
 gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int n_kv, int d,
                         const float *__restrict__ kc, const float *__restrict__ vc, int max_seq,
                         const int32_t *__restrict__ pos, int chunk, float *__restrict__ part) {
+    pdl_wait();
+    pdl_trigger();
     // chunk == blockDim.x == 128: one key per thread in the score phase
     extern __shared__ float sm[];
     float *scores = sm;            // chunk
@@ -249,6 +259,8 @@ gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int 
 
 __global__ void attention_combine_kernel(const float *__restrict__ part, int n_splits, int d,
                                          float *__restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     // block per (q head, b); out row [b][n_q*d]
     const size_t hb = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
     const float *p = part + hb * n_splits * (d + 2);
@@ -273,6 +285,8 @@ __global__ void attention_combine_kernel(const float *__restrict__ part, int n_s
 // gate_up rows: [gate (inter) | up (inter)] -> out = silu(gate) * up
 __global__ void swiglu_kernel(const float *__restrict__ gu, float *__restrict__ out, size_t rows,
                               int inter) {
+    pdl_wait();
+    pdl_trigger();
     const size_t total = rows * (size_t)inter;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
@@ -289,6 +303,8 @@ template <int MT>
 __global__ void __launch_bounds__(256)
 f32_matmul_kernel(const float *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
                   int m0, int M, int N, int K) {
+    pdl_wait();
+    pdl_trigger();
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
     const int mt = min(MT, M - m0);
@@ -323,6 +339,8 @@ f32_matmul_kernel(const float *__restrict__ w, const float *__restrict__ x, floa
 // greedy token per row: the LAST index among equal maxima (Iterator::max_by)
 __global__ void __launch_bounds__(256)
 argmax_last_kernel(const float *__restrict__ logits, int vocab, int32_t *__restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float bv[256];
     __shared__ int bi[256];
     const float *row = logits + (size_t)blockIdx.x * vocab;
@@ -358,6 +376,8 @@ argmax_last_kernel(const float *__restrict__ logits, int vocab, int32_t *__restr
 __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float *__restrict__ logits, int vocab, float *__restrict__ pv,
                       int32_t *__restrict__ pi) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float bv[256];
     __shared__ int bi[256];
     const int row = blockIdx.y, nb = gridDim.x;
@@ -387,6 +407,8 @@ argmax_partial_kernel(const float *__restrict__ logits, int vocab, float *__rest
 __global__ void __launch_bounds__(64)
 argmax_final_kernel(const float *__restrict__ pv, const int32_t *__restrict__ pi, int nb,
                     int32_t *__restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     // partials are in increasing index order: scan them in order, later wins ties
     if (threadIdx.x != 0) return;
     const int row = blockIdx.x;
@@ -423,7 +445,7 @@ int yscv_cuda_embedding_dev(yscv_cuda_ctx *ctx, const float *d_weight, size_t vo
     if (!d_weight || !d_tokens || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
     if (dim % 4 != 0) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "embedding dim must be a multiple of 4");
     if (rows == 0) return YSCV_CUDA_OK;
-    embedding_kernel<<<(unsigned)rows, 128, 0, ctx->stream>>>(d_weight, d_tokens, d_out, (int)vocab, (int)dim);
+    YSCV_CUDA_TRY(launch_pdl(embedding_kernel, dim3((unsigned)rows), dim3(128), 0, ctx->stream, d_weight, d_tokens, d_out, (int)vocab, (int)dim));
     DEC_EPILOGUE(ctx, "embedding");
 }
 
@@ -433,8 +455,8 @@ int yscv_cuda_add_rms_norm_dev(yscv_cuda_ctx *ctx, const float *d_x, const float
     DEC_PROLOGUE(ctx);
     if (!d_x || !d_gamma || !d_normed) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
     if (rows == 0) return YSCV_CUDA_OK;
-    add_rms_norm_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(d_x, d_delta, d_gamma, eps, (int)hidden,
-                                                                 d_x_out, d_normed);
+    YSCV_CUDA_TRY(launch_pdl(add_rms_norm_kernel, dim3((unsigned)rows), dim3(256), 0, ctx->stream, d_x, d_delta, d_gamma, eps, (int)hidden,
+                                                                 d_x_out, d_normed));
     DEC_EPILOGUE(ctx, "add_rms_norm");
 }
 
@@ -445,8 +467,7 @@ int yscv_cuda_rope_kv_append_dev(yscv_cuda_ctx *ctx, float *d_qkv, size_t batch,
     if (!d_qkv || !d_pos || !d_kcache || !d_vcache) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
     if (d_head % 2 != 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "d_head must be even for RoPE");
     if (batch * seq == 0) return YSCV_CUDA_OK;
-    rope_kv_append_kernel<<<(unsigned)(batch * seq), 128, 0, ctx->stream>>>(
-        d_qkv, (int)seq, (int)n_q, (int)n_kv, (int)d_head, theta, d_pos, d_kcache, d_vcache, (int)max_seq);
+    YSCV_CUDA_TRY(launch_pdl(rope_kv_append_kernel, dim3((unsigned)(batch * seq)), dim3(128), 0, ctx->stream, d_qkv, (int)seq, (int)n_q, (int)n_kv, (int)d_head, theta, d_pos, d_kcache, d_vcache, (int)max_seq));
     DEC_EPILOGUE(ctx, "rope_kv_append");
 }
 
@@ -469,12 +490,11 @@ int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_s
         if (rc) return rc;
         float *part = reinterpret_cast<float *>(ctx->scratch_attn.ptr);
         dim3 grid((unsigned)n_splits, (unsigned)n_q, (unsigned)batch);
-        gqa_decode_split_kernel<<<grid, 128, (chunk + 2 * d_head) * sizeof(float), ctx->stream>>>(
-            d_q, (int)q_stride, (int)n_q, (int)n_kv, (int)d_head, d_kcache, d_vcache, (int)max_seq, d_pos, chunk, part);
+        YSCV_CUDA_TRY(launch_pdl(gqa_decode_split_kernel, dim3(grid), dim3(128), (chunk + 2 * d_head) * sizeof(float), ctx->stream, d_q, (int)q_stride, (int)n_q, (int)n_kv, (int)d_head, d_kcache, d_vcache, (int)max_seq, d_pos, chunk, part));
         YSCV_CUDA_TRY(cudaGetLastError());
         ctx->launches++;
-        attention_combine_kernel<<<dim3((unsigned)n_q, (unsigned)batch), 128, 0, ctx->stream>>>(part, n_splits,
-                                                                                               (int)d_head, d_out);
+        YSCV_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3(dim3((unsigned)n_q, (unsigned)batch)), dim3(128), 0, ctx->stream, part, n_splits,
+                                                                                               (int)d_head, d_out));
         DEC_EPILOGUE(ctx, "gqa_attention(split-k)");
     }
     const size_t smem = (max_seq + d_head) * sizeof(float);
@@ -485,9 +505,9 @@ int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_s
         if (ctx->device < 16) attr_set[ctx->device] = 1;
     }
     dim3 grid((unsigned)seq_q, (unsigned)n_q, (unsigned)batch);
-    gqa_attention_kernel<<<grid, 128, smem, ctx->stream>>>(d_q, (int)q_stride, (int)seq_q, (int)n_q, (int)n_kv,
+    YSCV_CUDA_TRY(launch_pdl(gqa_attention_kernel, dim3(grid), dim3(128), smem, ctx->stream, d_q, (int)q_stride, (int)seq_q, (int)n_q, (int)n_kv,
                                                            (int)d_head, d_kcache, d_vcache, (int)max_seq,
-                                                           d_pos, causal, d_out);
+                                                           d_pos, causal, d_out));
     DEC_EPILOGUE(ctx, "gqa_attention");
 }
 
@@ -498,7 +518,7 @@ int yscv_cuda_swiglu_dev(yscv_cuda_ctx *ctx, const float *d_gate_up, size_t rows
     if (rows * inter == 0) return YSCV_CUDA_OK;
     const size_t total = rows * inter;
     const unsigned blocks = (unsigned)((total + 255) / 256 < 65535 ? (total + 255) / 256 : 65535);
-    swiglu_kernel<<<blocks, 256, 0, ctx->stream>>>(d_gate_up, d_out, rows, (int)inter);
+    YSCV_CUDA_TRY(launch_pdl(swiglu_kernel, dim3(blocks), dim3(256), 0, ctx->stream, d_gate_up, d_out, rows, (int)inter));
     DEC_EPILOGUE(ctx, "swiglu");
 }
 
@@ -510,7 +530,7 @@ int yscv_cuda_f32_matmul_dev(yscv_cuda_ctx *ctx, const float *d_w, const float *
     if (m * n == 0) return YSCV_CUDA_OK;
     const unsigned blocks = (unsigned)((n + 7) / 8 < (size_t)(16 * ctx->sm_count) ? (n + 7) / 8 : 16 * ctx->sm_count);
     for (size_t m0 = 0; m0 < m; m0 += 4) {
-        f32_matmul_kernel<4><<<blocks, 256, 0, ctx->stream>>>(d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k);
+        YSCV_CUDA_TRY(launch_pdl(f32_matmul_kernel<4>, dim3(blocks), dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k));
         YSCV_CUDA_TRY(cudaGetLastError());
         ctx->launches++;
     }
@@ -530,20 +550,20 @@ int yscv_cuda_argmax_last_dev(yscv_cuda_ctx *ctx, const float *d_logits, size_t 
         if (rc) return rc;
         float *pv = reinterpret_cast<float *>(ctx->scratch_attn.ptr);
         int32_t *pi = reinterpret_cast<int32_t *>(pv + rows * nb);
-        argmax_partial_kernel<<<dim3(nb, (unsigned)rows), 256, 0, ctx->stream>>>(d_logits, (int)vocab, pv, pi);
+        YSCV_CUDA_TRY(launch_pdl(argmax_partial_kernel, dim3(dim3(nb, (unsigned)rows)), dim3(256), 0, ctx->stream, d_logits, (int)vocab, pv, pi));
         YSCV_CUDA_TRY(cudaGetLastError());
         ctx->launches++;
-        argmax_final_kernel<<<(unsigned)rows, 64, 0, ctx->stream>>>(pv, pi, nb, d_out);
+        YSCV_CUDA_TRY(launch_pdl(argmax_final_kernel, dim3((unsigned)rows), dim3(64), 0, ctx->stream, pv, pi, nb, d_out));
         DEC_EPILOGUE(ctx, "argmax_last(two-stage)");
     }
-    argmax_last_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(d_logits, (int)vocab, d_out);
+    YSCV_CUDA_TRY(launch_pdl(argmax_last_kernel, dim3((unsigned)rows), dim3(256), 0, ctx->stream, d_logits, (int)vocab, d_out));
     DEC_EPILOGUE(ctx, "argmax_last");
 }
 
 int yscv_cuda_advance_pos_dev(yscv_cuda_ctx *ctx, int32_t *d_pos, int by) {
     DEC_PROLOGUE(ctx);
     if (!d_pos) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
-    advance_pos_kernel<<<1, 1, 0, ctx->stream>>>(d_pos, by);
+    YSCV_CUDA_TRY(launch_pdl(advance_pos_kernel, dim3(1), dim3(1), 0, ctx->stream, d_pos, by));
     DEC_EPILOGUE(ctx, "advance_pos");
 }
 

@@ -412,6 +412,8 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, t = lane & 3;
     TRACE(0);
+    // let the next kernel of the stream be scheduled as soon as SMs free up
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
     // N * gridDim.x < 2^31 is checked on the host: 32-bit division is enough
     const int r0 = (int)(((unsigned)N * blockIdx.x) / gridDim.x);
@@ -468,6 +470,7 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
         mbar_fence_init();
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         if (FUSEQ && g.act_bytes > 0) {
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");  // activations come from a predecessor
             mbar_expect_tx(bar_act, (uint32_t)g.act_bytes);
             bulk_load(smem_u32(act_s), act, (uint32_t)g.act_bytes, bar_act);
             for (int it = 0; it < first_wave; ++it) issue_stage();
@@ -475,6 +478,9 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
     }
     __syncthreads();
     TRACE(1);
+    // everything below reads a predecessor's output (activations / digit blobs) or writes
+    // memory a predecessor may still be reading (the output)
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     if (warp == FAST_CONSUMER_WARPS) {
         if (lane == 0) {
@@ -745,8 +751,20 @@ static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scale
         if (ctx->device < 16) smem_set[ctx->device] = 1;
     }
     ctx->prof_begin();
-    kern<<<grid, FAST_THREADS, smem, ctx->stream>>>(tm_w, tm_s, blobs, act, out, M, N, K, g,
-                                                    ctx->d_status);
+    // Programmatic dependent launch: this grid may be scheduled while the previous kernel of
+    // the stream drains; it touches nothing a predecessor may have written (activations,
+    // digit blobs) or may still read (the output) before griddepcontrol.wait.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(FAST_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tm_w, tm_s, blobs, act, out, M, N, K, g, ctx->d_status));
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
