@@ -27,6 +27,7 @@ B, P, steps = 2, 24, 12
 prompt = torch.from_numpy(np.stack([synth.uniform_int(7 + b, 9, P, 0, cfg.vocab - 1) for b in range(B)]).astype(np.int32)).cuda()
 stream = torch.cuda.Stream()
 ctx = yscv_b200.Context(local, stream=stream.cuda_stream)
+ctx.set_int4_prefill_exact(True)   # strict comparison: the bf16 prompt pass rounds differently per K split
 tp = Int4Decoder(ctx, cfg, B, P + steps + 2, stream, seed=5, tp_rank=rank, tp_size=world, process_group=dist.group.WORLD)
 lg = tp.prefill(prompt); stream.synchronize()
 tp.capture_decode_step()

@@ -31,7 +31,8 @@ def weight_bytes_per_token(cfg, layers, tp):
     return int4 + cfg.vocab * cfg.hidden * 4  # + fp32 LM head (replicated)
 
 
-def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, layers=None, use_graph=True):
+def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, layers=None, use_graph=True,
+        exact_prefill=False):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -45,6 +46,7 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
     cfg, seed = MODELS[model]
     stream = torch.cuda.Stream()
     ctx = Context(local, stream=stream.cuda_stream)
+    ctx.set_int4_prefill_exact(exact_prefill)
     n_layers = layers or cfg.layers
     dec = Int4Decoder(ctx, cfg, batch, prompt_len + max_tokens + 2, stream, seed=seed, tp_rank=rank, tp_size=world,
                       process_group=pg, layers=n_layers)
@@ -95,7 +97,7 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
         "ms_per_step": decode_ms / max_tokens,
         "weight_bytes_per_step_per_gpu": wb,
         "weight_stream_gbs_per_gpu": wb / (decode_ms / max_tokens * 1e-3) / 1e9,
-        "cuda_graph": bool(use_graph),
+        "cuda_graph": bool(use_graph), "prefill": "fp32-exact" if exact_prefill else "bf16 tensor-core",
         "first_tokens": toks[:8, 0].cpu().tolist(),
         "device_status": ctx.device_status(),
     }
@@ -112,8 +114,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--layers", type=int, default=None, help="truncate the stack (default: the model's depth)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--exact-prefill", action="store_true",
+                    help="prompt pass on the fp32-exact int4 kernel (token-for-token comparable across TP degrees)")
     a = ap.parse_args()
-    s = run(a.model, a.batch, a.prompt_len, a.max_tokens, a.warmup, a.layers, not a.no_graph)
+    s = run(a.model, a.batch, a.prompt_len, a.max_tokens, a.warmup, a.layers, not a.no_graph, a.exact_prefill)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(s), flush=True)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
