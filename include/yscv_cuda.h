@@ -263,6 +263,46 @@ int yscv_cuda_argmax_last_dev(yscv_cuda_ctx *ctx, const float *d_logits, size_t 
 /* *d_pos += by, on the stream (position_offset += 1, apps/llm-bench/src/main.rs:536) */
 int yscv_cuda_advance_pos_dev(yscv_cuda_ctx *ctx, int32_t *d_pos, int by);
 
+/* ---- one decode step in one launch ---------------------------------------------------
+ * No single counterpart in the reference: one iteration of the llm-bench decode loop
+ * (apps/llm-bench/src/main.rs:491-561) runs the whole ONNX graph, i.e. per layer the
+ * operators above in this order: RMSNorm, int4 MatMul (fused q|k|v rows), RoPE + KvCache
+ * append, grouped-query attention (causal), int4 MatMul (output) + residual, RMSNorm,
+ * int4 MatMul (gate|up rows), SiLU(gate)*up, int4 MatMul (down) + residual. A decode plan
+ * runs that sequence for ONE sequence (batch 1) as a single persistent cooperative kernel.
+ * Requirements (else YSCV_CUDA_ERR_UNSUPPORTED): group size 32; every K a multiple of 512;
+ * sm_count <= rows <= 128 * sm_count per matrix; n_q <= sm_count; head_dim a multiple of 8
+ * that divides 512, at most 256; max_seq small enough for one CTA per head (about 10^4).
+ * The plan borrows the weights and caches (they must outlive it) and copies the gammas. */
+typedef struct yscv_cuda_decode_plan yscv_cuda_decode_plan;
+
+typedef struct yscv_cuda_decode_layer {
+    const yscv_cuda_int4_weight *qkv;      /* [(n_q + 2 n_kv) * d_head][hidden] */
+    const yscv_cuda_int4_weight *o;        /* [hidden][n_q * d_head] */
+    const yscv_cuda_int4_weight *gate_up;  /* [2 * inter][hidden]: gate rows, then up rows */
+    const yscv_cuda_int4_weight *down;     /* [hidden][inter] */
+    const float *d_gamma_attn;             /* [hidden] */
+    const float *d_gamma_mlp;              /* [hidden] */
+    float *d_kcache;                       /* [max_seq][n_kv][d_head], f32 */
+    float *d_vcache;
+} yscv_cuda_decode_layer;
+
+int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_decode_layer *layers,
+                                 size_t n_layers, size_t hidden, size_t inter, size_t n_q,
+                                 size_t n_kv, size_t d_head, size_t max_seq, float eps,
+                                 float rope_theta, yscv_cuda_decode_plan **out);
+
+/* x = embedding[*d_token], then every layer at position *d_pos (appending to the caches at
+ * that position); leaves the residual stream after the last layer, before the final norm,
+ * in d_x [hidden]. Asynchronous on the context's stream. A device-side wait that runs out
+ * sets the context's status word (yscv_cuda_ctx_device_status) and the plan must then be
+ * rebuilt. */
+int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
+                                   const float *d_embedding, size_t vocab, const int32_t *d_token,
+                                   const int32_t *d_pos, float *d_x);
+
+void yscv_cuda_decode_plan_free(yscv_cuda_decode_plan *plan);
+
 #ifdef __cplusplus
 }
 #endif

@@ -146,7 +146,8 @@ def export_weights(dec):
     return full
 
 
-def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logit_tol, exact_prefill=True):
+def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logit_tol, exact_prefill=True,
+               fused_step=True):
     """exact_prefill: the prompt pass uses the fp32-exact int4 kernel (tokens must then match the
     oracle except at rounding-level ties); otherwise the bf16 tensor-core GEMM, whose logits
     may differ by up to 2e-2 (relative Frobenius) and whose tokens may differ only where the
@@ -155,7 +156,9 @@ def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logi
     ctx, s = tctx
     ctx.set_int4_prefill_exact(exact_prefill)
     flip_margin = 1e-4 if exact_prefill else 5e-2
-    dec = Int4Decoder.with_full_weights(ctx, cfg, batch, prompt_len + steps + 1, s, seed=seed, layers=n_layers)
+    dec = Int4Decoder.with_full_weights(ctx, cfg, batch, prompt_len + steps + 1, s, seed=seed, layers=n_layers,
+                                        fused_step=fused_step)
+    assert (dec.plan is not None) == (fused_step and batch == 1)
     from oracle_decoder import OracleDecoder
     ref = OracleDecoder(oracle, cfg, n_layers, export_weights(dec), dec.embedding.cpu().numpy(),
                         dec.lm_head.cpu().numpy(), batch)
@@ -209,10 +212,54 @@ def test_small_decoder_matches_oracle(tctx, oracle):
     run_parity(tctx, oracle, cfg, 3, batch=2, prompt_len=20, steps=12, seed=3, logit_tol=1e-4)
 
 
+def test_small_decoder_fused_step_matches_oracle(tctx, oracle):
+    # batch 1: every decode step is one launch of the persistent step kernel
+    cfg = DecoderConfig(layers=3, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
+    run_parity(tctx, oracle, cfg, 3, batch=1, prompt_len=20, steps=12, seed=4, logit_tol=1e-4)
+    ctx, _ = tctx
+    assert ctx.device_status() == 0
+
+
+def test_fused_step_logits_match_operator_chain(tctx):
+    """The one-launch step against the chain of separate operator launches, same weights, same
+    cache contents: logits of every step within 1e-5 (relative), same tokens."""
+    import torch
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=2, hidden=1024, mlp=2560, n_q=16, n_kv=4, head_dim=64, vocab=2000)
+    prompt = dev(synth.uniform_int(21, 9, 24, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    ctx.set_int4_prefill_exact(True)
+    logs, toks = [], []
+    for fused in (False, True):
+        dec = Int4Decoder(ctx, cfg, 1, 64, s, seed=12, fused_step=fused)
+        assert (dec.plan is not None) == fused
+        dec.prefill(prompt)
+        lg, tk = [], []
+        for _ in range(10):
+            with torch.cuda.stream(s):
+                out = dec.forward(dec.next_tokens, 1)
+            s.synchronize()
+            lg.append(out.cpu().numpy().copy())
+            tk.append(int(dec.next_tokens.cpu().numpy()[0]))
+        logs.append(lg)
+        toks.append(tk)
+        dec.close()
+    ctx.set_int4_prefill_exact(False)
+    assert toks[0] == toks[1]
+    for a, b in zip(*logs):
+        assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
+    assert ctx.device_status() == 0
+
+
 def test_tinyllama_shape_greedy_tokens(tctx, oracle):
     # BASELINE config 4 shape, seed 3; 4 of the 22 layers keep the CPU oracle in seconds,
     # the full depth runs in bench/decoder measurements
     run_parity(tctx, oracle, TINYLLAMA_1B, 4, batch=1, prompt_len=128, steps=32, seed=3, logit_tol=1e-4)
+
+
+def test_tinyllama_shape_operator_chain(tctx, oracle):
+    # the same comparison with the single-token steps as separate operator launches
+    run_parity(tctx, oracle, TINYLLAMA_1B, 2, batch=1, prompt_len=64, steps=8, seed=3, logit_tol=1e-4,
+               fused_step=False)
 
 
 def test_tinyllama_shape_bf16_prefill(tctx, oracle):

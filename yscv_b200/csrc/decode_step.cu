@@ -1,0 +1,714 @@
+// One launch = one single-token decode step (batch 1) through every layer of a Llama-shaped
+// int4 decoder.
+//
+// The reference runs a decode step as a chain of ONNX nodes (apps/llm-bench/src/main.rs:491-561
+// drives crates/yscv-onnx/src/runner: the packed-int4 MatMul of linear.rs:223-278, RMSNorm
+// norm.rs:1497-1518, rotate-half RoPE rope.rs:24-117, the KV-cache append kv_cache.rs:118-254,
+// grouped-query attention linear.rs:552-646, SiLU activation.rs:1000-1005). At batch 1 every
+// linear moves a few MB, so on this GPU a chain of separate launches spends its time between
+// kernels, not in them. Here the whole stack is one persistent cooperative kernel, one CTA per
+// SM:
+//
+//   * one producer thread per CTA walks the layers' four weight matrices (qkv, output, gate+up,
+//     down) in order and streams this CTA's rows of each through a TMA ring; the weights are
+//     constants, so the ring keeps filling across operator boundaries and never waits for an
+//     activation;
+//   * 16 consumer warps run the operators: residual add + RMSNorm (or SwiGLU) fused into the
+//     staging of the activation vector, its conversion to block-fixed-point digit planes, the
+//     integer-MMA dot products of the M = 1 decode GEMV (same arithmetic as int4_gemv.cu), the
+//     residual add fused into the store of the output and down projections, and RoPE + cache
+//     append + attention with one CTA per query head;
+//   * operators that need another CTA's output are separated by a grid-wide barrier (a counter
+//     in global memory, bounded spin, abort flag), five per layer.
+//
+// Limits (checked when the plan is built): group size 32, K % 512 == 0, at most 128 weight rows
+// per CTA and matrix, head_dim <= 256, the whole context of a head handled by one CTA.
+#include <cmath>
+#include <cstring>
+
+#include "common.cuh"
+#include "int4_digits.cuh"
+#include "kernels.cuh"
+#include "tma.cuh"
+
+namespace yscv {
+
+constexpr int DS_CONSUMER_WARPS = 16;
+constexpr int DS_CONSUMERS = DS_CONSUMER_WARPS * 32;
+constexpr int DS_THREADS = DS_CONSUMERS + 32;  // + the producer warp
+constexpr int DS_GS = 16;                      // groups of 32 k per stage
+constexpr int DS_RED_BYTES = 4096;             // K slices x tiles x 2 accumulators x 32 lanes, f32
+constexpr int DS_BAR_BYTES = 256;
+constexpr int DS_MAX_STAGES = 8;
+constexpr int DS_BLOB_BYTES = DS_GS * 4 * 4 * 16;  // digit blob of one stage (M = 1, columns form)
+constexpr int DS_SPIN_LIMIT = 1 << 21;
+
+// One int4 linear as the kernel sees it (array in global memory).
+struct alignas(64) StepMat {
+    CUtensorMap tm_w;  // weights as bytes [n][k/2], box [tiles*16][128], 128-byte swizzle
+    CUtensorMap tm_s;  // scales as f32 [n][k/32], box [tiles*16][16], 64-byte swizzle
+    int n, k, tiles, k_stages;
+    int pad[12];
+};
+
+struct StepParams {
+    const StepMat *mats;      // [layers][4]: qkv, output, gate+up, down
+    const float *gamma;       // [layers][2][hidden]
+    float *const *kcache;     // [layers] -> [max_seq][n_kv][d_head]
+    float *const *vcache;
+    const float *embedding;   // [vocab][hidden]
+    const int32_t *token;
+    const int32_t *pos;
+    float *x;                 // [hidden] residual stream, result of the step
+    float *qkv, *attn, *gu;   // scratch between operators
+    unsigned int *sync;       // [0] barrier arrivals, [1] CTAs that left, [2] abort flag
+    int *status;
+    int layers, hidden, inter, n_q, n_kv, d_head, max_seq, vocab;
+    float eps, theta;
+    int stages, slot_bytes, dig_bytes, act_floats;
+};
+
+#ifdef YSCV_TRACE
+// debugging aid (not built by default): per-CTA timestamps of the first four layers
+__device__ unsigned long long g_step_trace[148 * 64];
+extern "C" int yscv_step_trace_read(unsigned long long *dst) {
+    return (int)cudaMemcpyFromSymbol(dst, g_step_trace, sizeof(g_step_trace));
+}
+#define STRACE(slot)                                                                    \
+    do {                                                                                \
+        if (threadIdx.x == 0 && (slot) < 64) {                                          \
+            unsigned long long _t;                                                      \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                      \
+            g_step_trace[blockIdx.x * 64 + (slot)] = _t;                                \
+        }                                                                               \
+    } while (0)
+#else
+#define STRACE(slot) do { } while (0)
+#endif
+
+// ---- consumer-side helpers (the 512 consumer threads only; named barrier 1) ---------------
+
+__device__ __forceinline__ void cons_sync() { named_bar_sync(1, DS_CONSUMERS); }
+
+__device__ __forceinline__ float cons_sum(float v, float *misc) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    cons_sync();  // misc may still be read from the previous reduction
+    if ((threadIdx.x & 31) == 0) misc[threadIdx.x >> 5] = v;
+    cons_sync();
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < DS_CONSUMER_WARPS; ++i) t += misc[i];
+    return t;
+}
+
+__device__ __forceinline__ float cons_max(float v, float *misc) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    cons_sync();
+    if ((threadIdx.x & 31) == 0) misc[threadIdx.x >> 5] = v;
+    cons_sync();
+    float t = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < DS_CONSUMER_WARPS; ++i) t = fmaxf(t, misc[i]);
+    return t;
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Grid-wide barrier of the consumers. `epoch` counts the barriers of this launch (the same in
+// every thread). A CTA that waits longer than the limit raises the abort flag; from then on
+// every barrier of every CTA falls through, the kernel runs to its end and the host finds the
+// status word set.
+__device__ __forceinline__ void grid_barrier(const StepParams &p, unsigned int &epoch) {
+    ++epoch;
+    cons_sync();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(&p.sync[0], 1u);
+        const unsigned int target = epoch * gridDim.x;
+        int spins = 0;
+        while (ld_acquire_u32(&p.sync[0]) < target) {
+            if (ld_acquire_u32(&p.sync[2]) != 0u) break;
+            if (++spins > DS_SPIN_LIMIT) {
+                atomicExch(&p.sync[2], 1u);
+                *p.status = YSCV_DEV_FLAG_TIMEOUT;
+                break;
+            }
+        }
+        __threadfence();
+    }
+    cons_sync();
+}
+
+// The activation vector is in act_s: turn it into the digit planes of every K stage.
+__device__ __forceinline__ void quantize_activation(const float *act_s, unsigned char *dig, int K) {
+    const QuantLayout q = quant_layout(1, DS_GS);
+    const int tid = threadIdx.x, t = tid & 3;
+    const int items = (K / 32) * 2;  // row 0 and the all-zero padding row of the columns form
+    const int rounds = (items + DS_CONSUMERS / 4 - 1) / (DS_CONSUMERS / 4);
+    for (int r = 0; r < rounds; ++r) {
+        const int item = r * (DS_CONSUMERS / 4) + (tid >> 2);
+        const bool valid = item < items;
+        const int Gabs = valid ? item % (K / 32) : 0, m = valid ? item / (K / 32) : 0;
+        quantize_group<true>(m < 1 ? act_s + Gabs * 32 + 8 * t : nullptr, dig, q, Gabs, m, t, valid);
+    }
+    cons_sync();
+}
+
+struct RingPos {
+    int slot;
+    uint32_t phase;
+};
+
+// The M = 1 GEMV of one matrix over this CTA's rows [r0, r1): walks the matrix's K stages in
+// the ring, combines the K slices in a fixed order and stores (or adds into) out[row].
+// Same fragment arithmetic as int4_gemv_fast_kernel<1, 16, TP2, true>.
+template <int TP2>
+__device__ __forceinline__ void consume_matrix(const StepParams &p, const unsigned char *smem,
+                                               uint32_t bar_full, uint32_t bar_empty, float *red,
+                                               const unsigned char *dig, RingPos &c, int tiles,
+                                               int k_stages, int r0, int r1, float *out,
+                                               bool accumulate, bool &dead) {
+    constexpr int GS = DS_GS;
+    constexpr int KSL = (16 / TP2 < GS) ? 16 / TP2 : GS;
+    constexpr int GPW = GS / KSL;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, t = lane & 3;
+    const int rb_rows = tiles * 16;
+    const uint32_t w_bytes = (uint32_t)rb_rows * GS * 16;
+    const int tile = warp % TP2, kslice = warp / TP2;
+    const bool active = (tile < tiles) && (kslice < KSL);
+    const int G0 = kslice * GPW;
+    const int rowA = tile * 16 + gq;
+    uint32_t w_off[GPW];
+#pragma unroll
+    for (int gi = 0; gi < GPW; ++gi) {
+        const int G = G0 + gi;
+        w_off[gi] = (uint32_t)(G >> 3) * (rb_rows * 128) + (uint32_t)rowA * 128 +
+                    ((((uint32_t)G & 7u) ^ (uint32_t)(rowA & 7)) << 4) + t * 4;
+    }
+    const uint32_t s_phase = (rowA >> 1) & 3;
+    const uint32_t s_row = w_bytes + (uint32_t)rowA * (GS * 4);
+    const uint32_t f_off = (uint32_t)((G0 * 4 + (gq & 3)) * 4 + t) * 16;
+    constexpr uint32_t f_step = 4 * 4 * 16;
+    uint32_t s_ch[(GPW + 3) / 4];
+#pragma unroll
+    for (int cc = 0; cc < (GPW + 3) / 4; ++cc)
+        s_ch[cc] = s_row + (((((uint32_t)(G0 + 4 * cc)) >> 2) ^ s_phase) << 4);
+    const int mul_hi = (t & 1) ? 1 : 65536;
+    float acc[2] = {0.0f, 0.0f};
+
+    for (int ks = 0; ks < k_stages; ++ks) {
+        if (!dead) dead = !mbar_wait(bar_full + c.slot * 8, c.phase, p.status);
+        if (active && !dead) {
+            const unsigned char *st = smem + (size_t)c.slot * p.slot_bytes;
+            const unsigned char *db = dig + (size_t)ks * DS_BLOB_BYTES;
+            float sA[GPW], sB[GPW];
+            if constexpr (GPW % 4 == 0) {
+#pragma unroll
+                for (int gi = 0; gi < GPW; gi += 4) {
+                    const uint4 x = lds128(st, s_ch[gi / 4]);
+                    const uint4 y = lds128(st, s_ch[gi / 4] + 8 * (GS * 4));
+                    sA[gi] = __uint_as_float(x.x); sA[gi + 1] = __uint_as_float(x.y);
+                    sA[gi + 2] = __uint_as_float(x.z); sA[gi + 3] = __uint_as_float(x.w);
+                    sB[gi] = __uint_as_float(y.x); sB[gi + 1] = __uint_as_float(y.y);
+                    sB[gi + 2] = __uint_as_float(y.z); sB[gi + 3] = __uint_as_float(y.w);
+                }
+            } else {
+#pragma unroll
+                for (int gi = 0; gi < GPW; ++gi) {
+                    const uint32_t G = (uint32_t)(G0 + gi);
+                    const uint32_t o = (((G >> 2) ^ s_phase) << 4) + (G & 3u) * 4;
+                    sA[gi] = lds_f32(st, s_row + o);
+                    sB[gi] = lds_f32(st, s_row + 8 * (GS * 4) + o);
+                }
+            }
+#pragma unroll
+            for (int gi = 0; gi < GPW; ++gi) {
+                const uint32_t wA = lds32(st, w_off[gi]), wB = lds32(st, w_off[gi] + 1024);
+                uint32_t a[4];
+                a[0] = nib_u8(wA);
+                a[1] = nib_u8(wB);
+                a[2] = nib_u8(wA >> 4);
+                a[3] = nib_u8(wB >> 4);
+                const uint4 f = lds128(db, f_off + gi * f_step);
+                int cfrag[4];
+                mma_u8s8(cfrag, a, f.x, f.y, 0, 0, 0, 0);
+                const int vA = cfrag[0] * mul_hi + (cfrag[1] * 256 + (int)f.w);
+                const int vB = cfrag[2] * mul_hi + (cfrag[3] * 256 + (int)f.w);
+                const float as = __uint_as_float(f.z);
+                acc[0] = fmaf(sA[gi] * as, (float)vA, acc[0]);
+                acc[1] = fmaf(sB[gi] * as, (float)vB, acc[1]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + c.slot * 8);
+        if (++c.slot == p.stages) { c.slot = 0; c.phase ^= 1u; }
+    }
+    if (active) {
+        red[((kslice * tiles + tile) * 2 + 0) * 32 + lane] = acc[0];
+        red[((kslice * tiles + tile) * 2 + 1) * 32 + lane] = acc[1];
+    }
+    cons_sync();
+    // element (tile, half, gq): sum over the K slices and the thread pair t = 0, 1
+    for (int i = tid; i < tiles * 16; i += DS_CONSUMERS) {
+        const int q8 = i & 7, half = (i >> 3) & 1, tl = i >> 4;
+        float v = 0.0f;
+        for (int ks = 0; ks < KSL; ++ks) {
+            const float *pp = red + ((ks * tiles + tl) * 2 + half) * 32 + q8 * 4;
+            v += pp[0] + pp[1];
+        }
+        const int row = r0 + tl * 16 + q8 + half * 8;
+        if (row < r1) out[row] = accumulate ? __ldcg(out + row) + v : v;
+    }
+    cons_sync();  // `red` is reused by the next matrix
+}
+
+// RoPE of this head's q and of its KV head's new k, cache append (by the first query head of
+// each KV group), then attention of the one query over positions 0 .. pos.
+__device__ __forceinline__ void attention_head(const StepParams &p, int layer, int h, float *scratch,
+                                               float *misc) {
+    const int tid = threadIdx.x;
+    const int d = p.d_head, half = d / 2;
+    const int grp = p.n_q / p.n_kv, kvh = h / grp;
+    int pos = *p.pos;
+    pos = pos < 0 ? 0 : (pos >= p.max_seq ? p.max_seq - 1 : pos);
+    float *qs = scratch, *kcur = qs + d, *vcur = kcur + d, *partial = vcur + d;  // partial: [512/d][d]
+    float *scores = partial + DS_CONSUMERS;                                      // [max_seq]
+    float *kc = p.kcache[layer], *vc = p.vcache[layer];
+    const bool owner = (h % grp) == 0;
+    if (tid < d) {
+        const bool is_k = tid >= half;
+        const int i = is_k ? tid - half : tid;
+        const float inv_freq = 1.0f / powf(p.theta, 2.0f * (float)i / (float)d);
+        float sn, cs;
+        sincosf(inv_freq * (float)pos, &sn, &cs);
+        const float *src = p.qkv + (size_t)(is_k ? p.n_q + kvh : h) * d;
+        const float x0 = __ldcg(src + i), x1 = __ldcg(src + i + half);
+        const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
+        float *dst = is_k ? kcur : qs;
+        dst[i] = y0;
+        dst[i + half] = y1;
+        if (is_k && owner) {
+            float *cd = kc + ((size_t)pos * p.n_kv + kvh) * d;
+            cd[i] = y0;
+            cd[i + half] = y1;
+        }
+    } else if (tid < 2 * d) {
+        const int i = tid - d;
+        const float v = __ldcg(p.qkv + (size_t)(p.n_q + p.n_kv + kvh) * d + i);
+        vcur[i] = v;
+        if (owner) vc[((size_t)pos * p.n_kv + kvh) * d + i] = v;
+    }
+    cons_sync();
+    const float scale = 1.0f / sqrtf((float)d);
+    const int limit = pos + 1;
+    float mx = -INFINITY;
+    for (int key = tid; key < limit; key += DS_CONSUMERS) {
+        float dot = 0.0f;
+        const float4 *q4 = reinterpret_cast<const float4 *>(qs);
+        if (key < pos) {
+            const float4 *kr = reinterpret_cast<const float4 *>(kc + ((size_t)key * p.n_kv + kvh) * d);
+#pragma unroll 4
+            for (int i = 0; i < d / 4; ++i) {
+                const float4 kv = __ldg(kr + i), qv = q4[i];
+                dot = fmaf(qv.x, kv.x, dot);
+                dot = fmaf(qv.y, kv.y, dot);
+                dot = fmaf(qv.z, kv.z, dot);
+                dot = fmaf(qv.w, kv.w, dot);
+            }
+        } else {
+            const float4 *kr = reinterpret_cast<const float4 *>(kcur);
+            for (int i = 0; i < d / 4; ++i) {
+                const float4 kv = kr[i], qv = q4[i];
+                dot = fmaf(qv.x, kv.x, dot);
+                dot = fmaf(qv.y, kv.y, dot);
+                dot = fmaf(qv.z, kv.z, dot);
+                dot = fmaf(qv.w, kv.w, dot);
+            }
+        }
+        const float sc = dot * scale;
+        scores[key] = sc;
+        mx = fmaxf(mx, sc);
+    }
+    mx = cons_max(mx, misc);
+    float se = 0.0f;
+    for (int key = tid; key < limit; key += DS_CONSUMERS) {
+        const float e = expf(scores[key] - mx);
+        scores[key] = e;
+        se += e;
+    }
+    se = cons_sum(se, misc);  // (its barriers also publish `scores`)
+    const float inv = se > 0.0f ? 1.0f / se : 0.0f;
+    const int nparts = DS_CONSUMERS / d, part = tid / d, dd = tid % d;
+    float acc = 0.0f;
+    if (part < nparts) {
+        for (int key = part; key < limit; key += nparts) {
+            const float v = key < pos ? __ldg(vc + ((size_t)key * p.n_kv + kvh) * d + dd) : vcur[dd];
+            acc = fmaf(scores[key], v, acc);
+        }
+        partial[part * d + dd] = acc;
+    }
+    cons_sync();
+    if (tid < d) {
+        float v = 0.0f;
+        for (int pt = 0; pt < nparts; ++pt) v += partial[pt * d + tid];
+        p.attn[(size_t)h * d + tid] = v * inv;
+    }
+    cons_sync();  // scratch is reused
+}
+
+__global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t ring_bytes = (uint32_t)p.stages * p.slot_bytes;
+    float *red = reinterpret_cast<float *>(smem + ring_bytes);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_full = smem_base + ring_bytes + DS_RED_BYTES;
+    const uint32_t bar_empty = bar_full + 8 * DS_MAX_STAGES;
+    unsigned char *dig = smem + ring_bytes + DS_RED_BYTES + DS_BAR_BYTES;
+    float *act_s = reinterpret_cast<float *>(dig + p.dig_bytes);
+    float *misc = act_s + p.act_floats;  // 32 floats
+    const int nmat = p.layers * 4;
+
+    if (tid == DS_CONSUMERS) {
+        for (int i = 0; i < p.stages; ++i) {
+            mbar_init(bar_full + i * 8, 1);
+            mbar_init(bar_empty + i * 8, DS_CONSUMER_WARPS);
+        }
+        mbar_fence_init();
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    // ---------------- producer: the weight stream of every layer, in order ----------------
+    if (warp == DS_CONSUMER_WARPS) {
+        if (lane == 0) {
+            int slot = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int mi = 0; mi < nmat && alive; ++mi) {
+                const StepMat *m = p.mats + mi;
+                const int n = m->n, tiles = m->tiles, k_stages = m->k_stages;
+                const int r0 = (int)(((unsigned)n * blockIdx.x) / gridDim.x);
+                const int rb_rows = tiles * 16;
+                const uint32_t tx = (uint32_t)rb_rows * (DS_GS * 16 + DS_GS * 4);
+                for (int ks = 0; ks < k_stages && alive; ++ks) {
+                    // a fresh barrier passes the wait on the opposite parity at once
+                    alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, p.status);
+                    if (!alive) break;
+                    const uint32_t st = smem_base + (uint32_t)slot * p.slot_bytes;
+                    const uint32_t full = bar_full + slot * 8;
+                    mbar_expect_tx(full, tx);
+                    tma_load_2d(st, &m->tm_w, ks * (DS_GS * 16), r0, full);
+                    tma_load_2d(st + rb_rows * 128, &m->tm_w, ks * (DS_GS * 16) + 128, r0, full);
+                    tma_load_2d(st + rb_rows * 256, &m->tm_s, ks * DS_GS, r0, full);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                }
+            }
+            // a consumer that gave up leaves copies unobserved: wait (bounded) for every slot
+            if (!alive)
+                for (int i = 0; i < p.stages; ++i) mbar_wait(bar_full + i * 8, 0, nullptr);
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    unsigned int epoch = 0;
+    RingPos c = {0, 0u};
+    bool dead = false;
+    const int H = p.hidden, I = p.inter;
+
+    auto gemv = [&](int mi, float *out, bool accumulate) {
+        const StepMat *m = p.mats + mi;
+        const int n = m->n, tiles = m->tiles, k_stages = m->k_stages;
+        const int r0 = (int)(((unsigned)n * blockIdx.x) / gridDim.x);
+        const int r1 = (int)(((unsigned)n * (blockIdx.x + 1)) / gridDim.x);
+        if (tiles <= 2)
+            consume_matrix<2>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, r0, r1, out, accumulate, dead);
+        else
+            consume_matrix<8>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, r0, r1, out, accumulate, dead);
+    };
+    // act_s = RMSNorm(x) * gamma
+    auto stage_norm = [&](const float *gamma) {
+        float ss = 0.0f;
+        for (int i = tid; i < H; i += DS_CONSUMERS) {
+            const float v = __ldcg(p.x + i);
+            act_s[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+        const float total = cons_sum(ss, misc);
+        const float inv = 1.0f / sqrtf(total / (float)H + p.eps);
+        for (int i = tid; i < H; i += DS_CONSUMERS) act_s[i] = (act_s[i] * inv) * gamma[i];
+        cons_sync();
+    };
+
+    // x = embedding[token]
+    {
+        int tok = *p.token;
+        tok = tok < 0 ? 0 : (tok >= p.vocab ? p.vocab - 1 : tok);
+        const int i0 = (int)(((unsigned)H * blockIdx.x) / gridDim.x);
+        const int i1 = (int)(((unsigned)H * (blockIdx.x + 1)) / gridDim.x);
+        for (int i = i0 + tid; i < i1; i += DS_CONSUMERS) p.x[i] = p.embedding[(size_t)tok * H + i];
+    }
+    grid_barrier(p, epoch);
+
+    for (int l = 0; l < p.layers; ++l) {
+        const float *g1 = p.gamma + (size_t)(2 * l) * H, *g2 = g1 + H;
+        const int ts = l * 16;  // trace slots of this layer (debug builds)
+        STRACE(ts + 0);
+        // attention block: norm -> qkv
+        stage_norm(g1);
+        STRACE(ts + 1);
+        quantize_activation(act_s, dig, H);
+        STRACE(ts + 2);
+        gemv(4 * l + 0, p.qkv, false);
+        STRACE(ts + 3);
+        grid_barrier(p, epoch);
+        STRACE(ts + 4);
+        // RoPE, cache append, attention: one CTA per query head
+        if ((int)blockIdx.x < p.n_q) attention_head(p, l, blockIdx.x, reinterpret_cast<float *>(dig), misc);
+        STRACE(ts + 5);
+        grid_barrier(p, epoch);
+        STRACE(ts + 6);
+        // output projection, residual add in the store
+        for (int i = tid; i < p.n_q * p.d_head; i += DS_CONSUMERS) act_s[i] = __ldcg(p.attn + i);
+        cons_sync();
+        quantize_activation(act_s, dig, p.n_q * p.d_head);
+        STRACE(ts + 7);
+        gemv(4 * l + 1, p.x, true);
+        STRACE(ts + 8);
+        grid_barrier(p, epoch);
+        STRACE(ts + 9);
+        // MLP: norm -> gate+up -> SwiGLU -> down, residual add in the store
+        stage_norm(g2);
+        quantize_activation(act_s, dig, H);
+        STRACE(ts + 10);
+        gemv(4 * l + 2, p.gu, false);
+        STRACE(ts + 11);
+        grid_barrier(p, epoch);
+        STRACE(ts + 12);
+        for (int i = tid; i < I; i += DS_CONSUMERS) {
+            const float g = __ldcg(p.gu + i), u = __ldcg(p.gu + I + i);
+            const float s = 1.0f / (1.0f + expf(-g));
+            act_s[i] = (g * s) * u;
+        }
+        cons_sync();
+        quantize_activation(act_s, dig, I);
+        STRACE(ts + 13);
+        gemv(4 * l + 3, p.x, true);
+        STRACE(ts + 14);
+        grid_barrier(p, epoch);
+        STRACE(ts + 15);
+    }
+
+    // the last CTA to leave resets the barrier words for the next launch
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int prev = atomicAdd(&p.sync[1], 1u);
+        if (prev == gridDim.x - 1) {
+            p.sync[0] = 0u;
+            p.sync[1] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace yscv
+
+// ---------------------------------------------------------------------------
+// Host side: the plan and its C ABI
+// ---------------------------------------------------------------------------
+
+struct yscv_cuda_decode_plan {
+    int device = 0;
+    yscv::StepParams params = {};
+    int smem = 0;
+    void *d_mats = nullptr, *d_gamma = nullptr, *d_kptr = nullptr, *d_vptr = nullptr;
+    void *d_scratch = nullptr, *d_sync = nullptr;
+};
+
+extern "C" void yscv_cuda_decode_plan_free(yscv_cuda_decode_plan *plan) {
+    if (!plan) return;
+    cudaSetDevice(plan->device);
+    cudaFree(plan->d_mats);
+    cudaFree(plan->d_gamma);
+    cudaFree(plan->d_kptr);
+    cudaFree(plan->d_vptr);
+    cudaFree(plan->d_scratch);
+    cudaFree(plan->d_sync);
+    delete plan;
+}
+
+extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_decode_layer *layers,
+                                            size_t n_layers, size_t hidden, size_t inter, size_t n_q,
+                                            size_t n_kv, size_t d_head, size_t max_seq, float eps,
+                                            float rope_theta, yscv_cuda_decode_plan **out) {
+    using namespace yscv;
+    if (!ctx || !layers || !out || n_layers == 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    *out = nullptr;
+    if (tensor_map_encoder() == nullptr) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "no tensor-map encoder in this driver");
+    const int grid = ctx->sm_count;
+    if (n_kv == 0 || n_q % n_kv != 0 || d_head == 0 || d_head % 8 != 0 || 2 * d_head > (size_t)DS_CONSUMERS ||
+        DS_CONSUMERS % d_head != 0 || n_q > (size_t)grid)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: n_q=%zu n_kv=%zu d_head=%zu not supported on %d SMs",
+                    n_q, n_kv, d_head, grid);
+    const size_t qkv_rows = (n_q + 2 * n_kv) * d_head, attn_w = n_q * d_head;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    auto *plan = new yscv_cuda_decode_plan();
+    plan->device = ctx->device;
+    auto bail = [&](int rc) {
+        yscv_cuda_decode_plan_free(plan);
+        return rc;
+    };
+    // every matrix: shape, geometry, tensor maps
+    std::vector<StepMat> mats(n_layers * 4);
+    size_t k_max = 0;
+    int slot_bytes = 0;
+    for (size_t l = 0; l < n_layers; ++l) {
+        const yscv_cuda_int4_weight *w[4] = {layers[l].qkv, layers[l].o, layers[l].gate_up, layers[l].down};
+        const size_t want_n[4] = {qkv_rows, hidden, 2 * inter, hidden};
+        const size_t want_k[4] = {hidden, attn_w, hidden, inter};
+        if (!layers[l].d_gamma_attn || !layers[l].d_gamma_mlp || !layers[l].d_kcache || !layers[l].d_vcache)
+            return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: layer %zu has a null pointer", l));
+        for (int j = 0; j < 4; ++j) {
+            if (!w[j]) return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: layer %zu has a null weight", l));
+            if (w[j]->m_w != want_n[j] || w[j]->k != want_k[j] || w[j]->group_size != 32)
+                return bail(fail(YSCV_CUDA_ERR_BAD_ARG,
+                                 "decode plan: layer %zu matrix %d is [%zu][%zu] group %zu, expected [%zu][%zu] group 32",
+                                 l, j, w[j]->m_w, w[j]->k, w[j]->group_size, want_n[j], want_k[j]));
+            const size_t n = w[j]->m_w, k = w[j]->k;
+            const size_t rows_per_cta = (n + grid - 1) / grid;
+            if (k % 512 != 0 || n < (size_t)grid || rows_per_cta > 128 ||
+                ((reinterpret_cast<uintptr_t>(w[j]->d_packed) | reinterpret_cast<uintptr_t>(w[j]->d_scales)) & 15))
+                return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED,
+                                 "decode plan: matrix [%zu][%zu] needs k %% 512 == 0, %d <= n <= %d and 16-byte alignment",
+                                 n, k, grid, 128 * grid));
+            StepMat &m = mats[l * 4 + j];
+            memset(&m, 0, sizeof(m));
+            m.n = (int)n;
+            m.k = (int)k;
+            m.tiles = (int)((rows_per_cta + 15) / 16);
+            m.k_stages = (int)(k / 512);
+            const uint32_t rb_rows = (uint32_t)m.tiles * 16;
+            int rc = encode_2d(&m.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[j]->d_packed, n, k / 2, k / 2, rb_rows,
+                               128, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc) return bail(rc);
+            rc = encode_2d(&m.tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, w[j]->d_scales, n, k / 32, k / 8, rb_rows,
+                           DS_GS, CU_TENSOR_MAP_SWIZZLE_64B);
+            if (rc) return bail(rc);
+            k_max = k > k_max ? k : k_max;
+            const int sb = (int)rb_rows * (DS_GS * 16 + DS_GS * 4);
+            slot_bytes = sb > slot_bytes ? sb : slot_bytes;
+        }
+    }
+    slot_bytes = ((slot_bytes + 1023) / 1024) * 1024;
+    StepParams &p = plan->params;
+    p.dig_bytes = (int)(k_max / 512) * DS_BLOB_BYTES;
+    p.act_floats = (int)k_max;
+    // the attention scratch (q, k, v of the head, partial sums, scores) lives in the digit +
+    // activation area between the GEMVs
+    const size_t attn_scratch = (3 * d_head + DS_CONSUMERS + max_seq) * sizeof(float);
+    if (attn_scratch > (size_t)p.dig_bytes + k_max * 4)
+        return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: max_seq=%zu does not fit one CTA per head", max_seq));
+    const int fixed = DS_RED_BYTES + DS_BAR_BYTES + p.dig_bytes + (int)k_max * 4 + 128;
+    const int budget = 227 * 1024 - fixed - 1024;
+    p.stages = budget / slot_bytes;
+    if (p.stages > DS_MAX_STAGES) p.stages = DS_MAX_STAGES;
+    if (p.stages < 2) return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: k=%zu leaves no room for the weight ring", k_max));
+    p.slot_bytes = slot_bytes;
+    plan->smem = p.stages * slot_bytes + fixed;
+
+    // device copies: matrices, gammas, cache pointers, scratch, barrier words
+    std::vector<float *> kptr(n_layers), vptr(n_layers);
+    for (size_t l = 0; l < n_layers; ++l) { kptr[l] = layers[l].d_kcache; vptr[l] = layers[l].d_vcache; }
+    const size_t scratch_floats = qkv_rows + attn_w + 2 * inter;
+#define PLAN_TRY(expr)                                                                       \
+    do {                                                                                     \
+        cudaError_t _e = (expr);                                                             \
+        if (_e != cudaSuccess)                                                               \
+            return bail(fail(YSCV_CUDA_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e))); \
+    } while (0)
+    PLAN_TRY(cudaMalloc(&plan->d_mats, mats.size() * sizeof(StepMat)));
+    PLAN_TRY(cudaMalloc(&plan->d_gamma, n_layers * 2 * hidden * sizeof(float)));
+    PLAN_TRY(cudaMalloc(&plan->d_kptr, n_layers * sizeof(float *)));
+    PLAN_TRY(cudaMalloc(&plan->d_vptr, n_layers * sizeof(float *)));
+    PLAN_TRY(cudaMalloc(&plan->d_scratch, scratch_floats * sizeof(float)));
+    PLAN_TRY(cudaMalloc(&plan->d_sync, 4 * sizeof(unsigned int)));
+    PLAN_TRY(cudaMemcpyAsync(plan->d_mats, mats.data(), mats.size() * sizeof(StepMat), cudaMemcpyHostToDevice, ctx->stream));
+    PLAN_TRY(cudaMemcpyAsync(plan->d_kptr, kptr.data(), n_layers * sizeof(float *), cudaMemcpyHostToDevice, ctx->stream));
+    PLAN_TRY(cudaMemcpyAsync(plan->d_vptr, vptr.data(), n_layers * sizeof(float *), cudaMemcpyHostToDevice, ctx->stream));
+    PLAN_TRY(cudaMemsetAsync(plan->d_sync, 0, 4 * sizeof(unsigned int), ctx->stream));
+    for (size_t l = 0; l < n_layers; ++l) {
+        float *g = reinterpret_cast<float *>(plan->d_gamma) + l * 2 * hidden;
+        PLAN_TRY(cudaMemcpyAsync(g, layers[l].d_gamma_attn, hidden * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        PLAN_TRY(cudaMemcpyAsync(g + hidden, layers[l].d_gamma_mlp, hidden * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    PLAN_TRY(cudaStreamSynchronize(ctx->stream));  // the host vectors go out of scope
+    PLAN_TRY(cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan->smem));
+    int per_sm = 0;
+    PLAN_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, DS_THREADS, plan->smem));
+    if (per_sm < 1) return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: the step kernel does not fit an SM"));
+#undef PLAN_TRY
+    p.mats = reinterpret_cast<const StepMat *>(plan->d_mats);
+    p.gamma = reinterpret_cast<const float *>(plan->d_gamma);
+    p.kcache = reinterpret_cast<float *const *>(plan->d_kptr);
+    p.vcache = reinterpret_cast<float *const *>(plan->d_vptr);
+    float *s = reinterpret_cast<float *>(plan->d_scratch);
+    p.qkv = s;
+    p.attn = s + qkv_rows;
+    p.gu = p.attn + attn_w;
+    p.sync = reinterpret_cast<unsigned int *>(plan->d_sync);
+    p.status = ctx->d_status;
+    p.layers = (int)n_layers;
+    p.hidden = (int)hidden;
+    p.inter = (int)inter;
+    p.n_q = (int)n_q;
+    p.n_kv = (int)n_kv;
+    p.d_head = (int)d_head;
+    p.max_seq = (int)max_seq;
+    p.eps = eps;
+    p.theta = rope_theta;
+    *out = plan;
+    return YSCV_CUDA_OK;
+}
+
+extern "C" int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
+                                              const float *d_embedding, size_t vocab, const int32_t *d_token,
+                                              const int32_t *d_pos, float *d_x) {
+    using namespace yscv;
+    if (!ctx || !plan || !d_embedding || !d_token || !d_pos || !d_x || vocab == 0)
+        return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (plan->device != ctx->device) return fail(YSCV_CUDA_ERR_BAD_ARG, "plan belongs to device %d", plan->device);
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    StepParams p = plan->params;
+    p.embedding = d_embedding;
+    p.vocab = (int)vocab;
+    p.token = d_token;
+    p.pos = d_pos;
+    p.x = d_x;
+    p.status = ctx->d_status;
+    // the CTAs wait on one another: cooperative launch, one CTA per SM
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctx->sm_count);
+    cfg.blockDim = dim3(DS_THREADS);
+    cfg.dynamicSmemBytes = plan->smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ctx->prof_begin();
+    YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_step_kernel, p));
+    ctx->prof_end();
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    ctx->last_kernel = "decode_step(persistent,tma,imma)";
+    return YSCV_CUDA_OK;
+}

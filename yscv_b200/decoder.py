@@ -21,7 +21,7 @@ from dataclasses import dataclass
 import torch
 
 from . import sharding
-from .lib import Context
+from .lib import Context, YscvCudaError
 
 
 @dataclass(frozen=True)
@@ -54,7 +54,7 @@ class Int4Linear:
 class Int4Decoder:
     def __init__(self, ctx: Context, cfg: DecoderConfig, batch: int, max_seq: int, stream: torch.cuda.Stream,
                  seed: int = 3, tp_rank: int = 0, tp_size: int = 1, process_group=None,
-                 layers: int | None = None):
+                 layers: int | None = None, fused_step: bool = True):
         assert cfg.n_q % tp_size == 0 and cfg.n_kv % tp_size == 0 and cfg.mlp % (tp_size * cfg.group_size) == 0
         self.ctx, self.cfg, self.batch, self.max_seq, self.stream = ctx, cfg, batch, max_seq, stream
         self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
@@ -73,6 +73,20 @@ class Int4Decoder:
         self._bufs = {}
         self.graph = None
         stream.synchronize()
+        # batch 1 on one GPU: the whole single-token step as one persistent kernel, when the
+        # shapes allow it (the library says which do)
+        self.plan = None
+        if fused_step and batch == 1 and tp_size == 1:
+            try:
+                self.plan = ctx.decode_plan(
+                    [dict(qkv=self.wqkv[l].handle, o=self.wo[l].handle, gate_up=self.wgu[l].handle,
+                          down=self.wdown[l].handle, gamma_attn=self.gamma.data_ptr(),
+                          gamma_mlp=self.gamma.data_ptr(), kcache=self.kcache[l].data_ptr(),
+                          vcache=self.vcache[l].data_ptr()) for l in range(self.n_layers)],
+                    cfg.hidden, cfg.mlp, cfg.n_q, cfg.n_kv, cfg.head_dim, max_seq, cfg.eps, cfg.rope_theta)
+            except YscvCudaError as e:
+                if e.status != -3:  # anything but "unsupported shape" is a real failure
+                    raise
 
     # ---- weights -------------------------------------------------------------------
     def _normal(self, tag: int, rows: int, cols: int) -> torch.Tensor:
@@ -161,9 +175,14 @@ class Int4Decoder:
         gu = self._buf("gu", rows, 2 * self.mlp_l)
         act = self._buf("act", rows, self.mlp_l)
         down = self._buf("down", rows, H)
-        ctx.embedding_dev(self.embedding.data_ptr(), c.vocab, H, tokens.data_ptr(), rows, x.data_ptr())
+        fused = self.plan is not None and seq == 1
+        if fused:
+            self.plan.step_dev(self.embedding.data_ptr(), c.vocab, tokens.data_ptr(), self.pos.data_ptr(),
+                               x.data_ptr())
+        else:
+            ctx.embedding_dev(self.embedding.data_ptr(), c.vocab, H, tokens.data_ptr(), rows, x.data_ptr())
         delta = 0
-        for l in range(self.n_layers):
+        for l in range(0 if fused else self.n_layers):
             ctx.add_rms_norm_dev(x.data_ptr(), delta, self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
             ctx.int4_matmul_dev(self.wqkv[l].handle, h.data_ptr(), qkv.data_ptr(), rows)
             ctx.rope_kv_append_dev(qkv.data_ptr(), B, seq, self.nq_l, self.nkv_l, d, c.rope_theta, self.pos.data_ptr(),
@@ -194,6 +213,9 @@ class Int4Decoder:
         before the process group is destroyed: a graph that holds NCCL nodes must go first."""
         self.stream.synchronize()
         self.graph = None
+        if self.plan is not None:
+            self.plan.free()
+            self.plan = None
         self._bufs.clear()
         self.kcache, self.vcache = [], []
         self.wqkv, self.wo, self.wgu, self.wdown = [], [], [], []

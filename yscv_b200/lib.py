@@ -73,6 +73,10 @@ SIGNATURES = {
     "yscv_cuda_f32_matmul_dev": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp]),
     "yscv_cuda_argmax_last_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
     "yscv_cuda_advance_pos_dev": (C.c_int, [_vp, _vp, C.c_int]),
+    "yscv_cuda_decode_plan_create": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, C.c_float, C.c_float,
+                                               C.POINTER(_vp)]),
+    "yscv_cuda_decode_plan_step_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "yscv_cuda_decode_plan_free": (None, [_vp]),
 }
 
 
@@ -81,6 +85,12 @@ class Requant(C.Structure):
     _fields_ = [("a_is_unsigned", C.c_int), ("a_zero_point", C.c_int32), ("composite", C.c_float),
                 ("y_zero_point", C.c_float), ("qmin", C.c_int32), ("qmax", C.c_int32),
                 ("round_mode", C.c_int)]
+
+
+class DecodeLayer(C.Structure):
+    """yscv_cuda_decode_layer."""
+    _fields_ = [("qkv", _vp), ("o", _vp), ("gate_up", _vp), ("down", _vp), ("d_gamma_attn", _vp),
+                ("d_gamma_mlp", _vp), ("d_kcache", _vp), ("d_vcache", _vp)]
 
 
 def load_library():
@@ -151,6 +161,28 @@ class I8B:
         if self.handle:
             load_library().yscv_cuda_i8b_free(self.handle)
             self.handle = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class DecodePlan:
+    """yscv_cuda_decode_plan: one launch per single-token decode step (batch 1)."""
+
+    def __init__(self, ctx: "Context", handle: int):
+        self.ctx, self.handle = ctx, handle
+
+    def step_dev(self, d_embedding: int, vocab: int, d_token: int, d_pos: int, d_x: int):
+        _check(self.ctx.lib.yscv_cuda_decode_plan_step_dev(self.ctx.handle, self.handle, _vp(d_embedding), vocab,
+                                                           _vp(d_token), _vp(d_pos), _vp(d_x)))
+
+    def free(self):
+        if self.handle:
+            self.ctx.lib.yscv_cuda_decode_plan_free(self.handle)
+            self.handle = None
 
     def __del__(self):
         try:
@@ -350,6 +382,20 @@ class Context:
 
     def advance_pos_dev(self, d_pos, by=1):
         _check(self.lib.yscv_cuda_advance_pos_dev(self.handle, _vp(d_pos), by))
+
+    def decode_plan(self, layers, hidden, inter, n_q, n_kv, d_head, max_seq, eps, rope_theta) -> DecodePlan:
+        """layers: list of dicts with Int4Weight `qkv`, `o`, `gate_up`, `down` and device
+        pointers `gamma_attn`, `gamma_mlp`, `kcache`, `vcache`."""
+        arr = (DecodeLayer * len(layers))()
+        for dst, l in zip(arr, layers):
+            dst.qkv, dst.o, dst.gate_up, dst.down = (l["qkv"].handle, l["o"].handle, l["gate_up"].handle,
+                                                     l["down"].handle)
+            dst.d_gamma_attn, dst.d_gamma_mlp = l["gamma_attn"], l["gamma_mlp"]
+            dst.d_kcache, dst.d_vcache = l["kcache"], l["vcache"]
+        h = _vp()
+        _check(self.lib.yscv_cuda_decode_plan_create(self.handle, C.cast(arr, _vp), len(layers), hidden, inter, n_q,
+                                                     n_kv, d_head, max_seq, eps, rope_theta, C.byref(h)))
+        return DecodePlan(self, h.value)
 
     def pack_int4_dev(self, d_weights: int, m_w, k, group_size, d_packed: int, d_scales: int):
         _check(self.lib.yscv_cuda_pack_int4_dev(self.handle, _vp(d_weights), m_w, k, group_size,
