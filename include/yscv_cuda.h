@@ -271,8 +271,8 @@ int yscv_cuda_advance_pos_dev(yscv_cuda_ctx *ctx, int32_t *d_pos, int by);
  * int4 MatMul (gate|up rows), SiLU(gate)*up, int4 MatMul (down) + residual. A decode plan
  * runs that sequence for ONE sequence (batch 1) as a single persistent cooperative kernel.
  * Requirements (else YSCV_CUDA_ERR_UNSUPPORTED): group size 32; every K a multiple of 512;
- * sm_count <= rows <= 128 * sm_count per matrix; n_q <= sm_count; head_dim a multiple of 8
- * that divides 512, at most 256; max_seq small enough for one CTA per head (about 10^4).
+ * sm_count <= rows <= 128 * sm_count per matrix; n_q <= sm_count; head_dim a multiple of 16
+ * that divides 512, at most 128; max_seq small enough for one CTA per head (about 10^4).
  * The plan borrows the weights and caches (they must outlive it) and copies the gammas. */
 typedef struct yscv_cuda_decode_plan yscv_cuda_decode_plan;
 

@@ -22,7 +22,8 @@
 //     in global memory, bounded spin, abort flag), five per layer.
 //
 // Limits (checked when the plan is built): group size 32, K % 512 == 0, at most 128 weight rows
-// per CTA and matrix, head_dim <= 256, the whole context of a head handled by one CTA.
+// per CTA and matrix, head_dim <= 128, the whole context of a head handled by one CTA.
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 
@@ -60,12 +61,17 @@ struct StepParams {
     const int32_t *token;
     const int32_t *pos;
     float *x;                 // [hidden] residual stream, result of the step
-    float *qkv, *attn, *gu;   // scratch between operators
+    float *qkv, *attn, *gu;   // scratch between operators; attn = [n_q][splits][d_head + 2]
+    int splits;               // CTAs per query head in the attention phase
     unsigned int *sync;       // [0] barrier arrivals, [1] CTAs that left, [2] abort flag
     int *status;
     int layers, hidden, inter, n_q, n_kv, d_head, max_seq, vocab;
     float eps, theta;
     int stages, slot_bytes, dig_bytes, act_floats;
+    // shape of the four matrices of a layer (the same in every layer): rows, 16-row tiles per
+    // CTA, K stages; kept here so that no thread waits on global memory to learn them
+    int mat_n[4], mat_tiles[4], mat_ks[4];
+    int mat_kps[4];  // K stages per ring slot: a matrix with few rows per CTA packs several
 };
 
 #ifdef YSCV_TRACE
@@ -76,14 +82,16 @@ extern "C" int yscv_step_trace_read(unsigned long long *dst) {
 }
 #define STRACE(slot)                                                                    \
     do {                                                                                \
-        if (threadIdx.x == 0 && (slot) < 64) {                                          \
+        if (threadIdx.x == 0 && (slot) >= 0 && (slot) < 64) {                                          \
             unsigned long long _t;                                                      \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                      \
             g_step_trace[blockIdx.x * 64 + (slot)] = _t;                                \
         }                                                                               \
     } while (0)
+#define ATRACE(slot) do { if (layer == 2) STRACE(48 + (slot)); } while (0)
 #else
 #define STRACE(slot) do { } while (0)
+#define ATRACE(slot) do { } while (0)
 #endif
 
 // ---- consumer-side helpers (the 512 consumer threads only; named barrier 1) ---------------
@@ -128,28 +136,32 @@ __device__ __forceinline__ void grid_barrier(const StepParams &p, unsigned int &
     ++epoch;
     cons_sync();
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(&p.sync[0], 1u);
+        // release: the CTA's writes (ordered before this thread by the bar.sync above) become
+        // visible before the arrival; the acquire load that sees the last arrival orders
+        // everything after the barrier behind all CTAs' writes
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(p.sync) : "memory");
         const unsigned int target = epoch * gridDim.x;
         int spins = 0;
         while (ld_acquire_u32(&p.sync[0]) < target) {
-            if (ld_acquire_u32(&p.sync[2]) != 0u) break;
-            if (++spins > DS_SPIN_LIMIT) {
+            ++spins;
+            if ((spins & 63) == 0 && ld_acquire_u32(&p.sync[2]) != 0u) break;
+            if (spins > DS_SPIN_LIMIT) {
                 atomicExch(&p.sync[2], 1u);
                 *p.status = YSCV_DEV_FLAG_TIMEOUT;
                 break;
             }
         }
-        __threadfence();
     }
     cons_sync();
 }
 
 // The activation vector is in act_s: turn it into the digit planes of every K stage.
-__device__ __forceinline__ void quantize_activation(const float *act_s, unsigned char *dig, int K) {
+// The all-zero padding row of the columns form (`pad`) never changes: it is written once per
+// launch, for the longest K, and nothing else touches the digit area afterwards.
+__device__ __forceinline__ void quantize_activation(const float *act_s, unsigned char *dig, int K, bool pad) {
     const QuantLayout q = quant_layout(1, DS_GS);
     const int tid = threadIdx.x, t = tid & 3;
-    const int items = (K / 32) * 2;  // row 0 and the all-zero padding row of the columns form
+    const int items = (K / 32) * (pad ? 2 : 1);
     const int rounds = (items + DS_CONSUMERS / 4 - 1) / (DS_CONSUMERS / 4);
     for (int r = 0; r < rounds; ++r) {
         const int item = r * (DS_CONSUMERS / 4) + (tid >> 2);
@@ -172,7 +184,7 @@ template <int TP2>
 __device__ __forceinline__ void consume_matrix(const StepParams &p, const unsigned char *smem,
                                                uint32_t bar_full, uint32_t bar_empty, float *red,
                                                const unsigned char *dig, RingPos &c, int tiles,
-                                               int k_stages, int r0, int r1, float *out,
+                                               int k_stages, int kps, int r0, int r1, float *out,
                                                bool accumulate, bool &dead) {
     constexpr int GS = DS_GS;
     constexpr int KSL = (16 / TP2 < GS) ? 16 / TP2 : GS;
@@ -202,48 +214,57 @@ __device__ __forceinline__ void consume_matrix(const StepParams &p, const unsign
         s_ch[cc] = s_row + (((((uint32_t)(G0 + 4 * cc)) >> 2) ^ s_phase) << 4);
     const int mul_hi = (t & 1) ? 1 : 65536;
     float acc[2] = {0.0f, 0.0f};
+    // the thread that will store output row `my_row` fetches the residual value now, not after
+    // the K loop
+    const int my_row = r0 + (tid >> 4) * 16 + (tid & 7) + ((tid >> 3) & 1) * 8;
+    float resid = 0.0f;
+    if (accumulate && tid < tiles * 16 && my_row < r1) resid = __ldcg(out + my_row);
 
-    for (int ks = 0; ks < k_stages; ++ks) {
+    const uint32_t sub_bytes = (uint32_t)rb_rows * (GS * 16 + GS * 4);  // one K stage inside a slot
+    for (int ks0 = 0; ks0 < k_stages; ks0 += kps) {
         if (!dead) dead = !mbar_wait(bar_full + c.slot * 8, c.phase, p.status);
+        const int nsub = min(kps, k_stages - ks0);
         if (active && !dead) {
-            const unsigned char *st = smem + (size_t)c.slot * p.slot_bytes;
-            const unsigned char *db = dig + (size_t)ks * DS_BLOB_BYTES;
-            float sA[GPW], sB[GPW];
-            if constexpr (GPW % 4 == 0) {
+            for (int j = 0; j < nsub; ++j) {
+                const unsigned char *st = smem + (size_t)c.slot * p.slot_bytes + (size_t)j * sub_bytes;
+                const unsigned char *db = dig + (size_t)(ks0 + j) * DS_BLOB_BYTES;
+                float sA[GPW], sB[GPW];
+                if constexpr (GPW % 4 == 0) {
 #pragma unroll
-                for (int gi = 0; gi < GPW; gi += 4) {
-                    const uint4 x = lds128(st, s_ch[gi / 4]);
-                    const uint4 y = lds128(st, s_ch[gi / 4] + 8 * (GS * 4));
-                    sA[gi] = __uint_as_float(x.x); sA[gi + 1] = __uint_as_float(x.y);
-                    sA[gi + 2] = __uint_as_float(x.z); sA[gi + 3] = __uint_as_float(x.w);
-                    sB[gi] = __uint_as_float(y.x); sB[gi + 1] = __uint_as_float(y.y);
-                    sB[gi + 2] = __uint_as_float(y.z); sB[gi + 3] = __uint_as_float(y.w);
+                    for (int gi = 0; gi < GPW; gi += 4) {
+                        const uint4 x = lds128(st, s_ch[gi / 4]);
+                        const uint4 y = lds128(st, s_ch[gi / 4] + 8 * (GS * 4));
+                        sA[gi] = __uint_as_float(x.x); sA[gi + 1] = __uint_as_float(x.y);
+                        sA[gi + 2] = __uint_as_float(x.z); sA[gi + 3] = __uint_as_float(x.w);
+                        sB[gi] = __uint_as_float(y.x); sB[gi + 1] = __uint_as_float(y.y);
+                        sB[gi + 2] = __uint_as_float(y.z); sB[gi + 3] = __uint_as_float(y.w);
+                    }
+                } else {
+#pragma unroll
+                    for (int gi = 0; gi < GPW; ++gi) {
+                        const uint32_t G = (uint32_t)(G0 + gi);
+                        const uint32_t o = (((G >> 2) ^ s_phase) << 4) + (G & 3u) * 4;
+                        sA[gi] = lds_f32(st, s_row + o);
+                        sB[gi] = lds_f32(st, s_row + 8 * (GS * 4) + o);
+                    }
                 }
-            } else {
 #pragma unroll
                 for (int gi = 0; gi < GPW; ++gi) {
-                    const uint32_t G = (uint32_t)(G0 + gi);
-                    const uint32_t o = (((G >> 2) ^ s_phase) << 4) + (G & 3u) * 4;
-                    sA[gi] = lds_f32(st, s_row + o);
-                    sB[gi] = lds_f32(st, s_row + 8 * (GS * 4) + o);
+                    const uint32_t wA = lds32(st, w_off[gi]), wB = lds32(st, w_off[gi] + 1024);
+                    uint32_t a[4];
+                    a[0] = nib_u8(wA);
+                    a[1] = nib_u8(wB);
+                    a[2] = nib_u8(wA >> 4);
+                    a[3] = nib_u8(wB >> 4);
+                    const uint4 f = lds128(db, f_off + gi * f_step);
+                    int cfrag[4];
+                    mma_u8s8(cfrag, a, f.x, f.y, 0, 0, 0, 0);
+                    const int vA = cfrag[0] * mul_hi + (cfrag[1] * 256 + (int)f.w);
+                    const int vB = cfrag[2] * mul_hi + (cfrag[3] * 256 + (int)f.w);
+                    const float as = __uint_as_float(f.z);
+                    acc[0] = fmaf(sA[gi] * as, (float)vA, acc[0]);
+                    acc[1] = fmaf(sB[gi] * as, (float)vB, acc[1]);
                 }
-            }
-#pragma unroll
-            for (int gi = 0; gi < GPW; ++gi) {
-                const uint32_t wA = lds32(st, w_off[gi]), wB = lds32(st, w_off[gi] + 1024);
-                uint32_t a[4];
-                a[0] = nib_u8(wA);
-                a[1] = nib_u8(wB);
-                a[2] = nib_u8(wA >> 4);
-                a[3] = nib_u8(wB >> 4);
-                const uint4 f = lds128(db, f_off + gi * f_step);
-                int cfrag[4];
-                mma_u8s8(cfrag, a, f.x, f.y, 0, 0, 0, 0);
-                const int vA = cfrag[0] * mul_hi + (cfrag[1] * 256 + (int)f.w);
-                const int vB = cfrag[2] * mul_hi + (cfrag[3] * 256 + (int)f.w);
-                const float as = __uint_as_float(f.z);
-                acc[0] = fmaf(sA[gi] * as, (float)vA, acc[0]);
-                acc[1] = fmaf(sB[gi] * as, (float)vB, acc[1]);
             }
         }
         __syncwarp();
@@ -256,110 +277,176 @@ __device__ __forceinline__ void consume_matrix(const StepParams &p, const unsign
     }
     cons_sync();
     // element (tile, half, gq): sum over the K slices and the thread pair t = 0, 1
-    for (int i = tid; i < tiles * 16; i += DS_CONSUMERS) {
-        const int q8 = i & 7, half = (i >> 3) & 1, tl = i >> 4;
+    if (tid < tiles * 16) {   // tiles <= 8: at most 128 rows, one per thread
+        const int q8 = tid & 7, half = (tid >> 3) & 1, tl = tid >> 4;
         float v = 0.0f;
         for (int ks = 0; ks < KSL; ++ks) {
             const float *pp = red + ((ks * tiles + tl) * 2 + half) * 32 + q8 * 4;
             v += pp[0] + pp[1];
         }
-        const int row = r0 + tl * 16 + q8 + half * 8;
-        if (row < r1) out[row] = accumulate ? __ldcg(out + row) + v : v;
+        if (my_row < r1) out[my_row] = accumulate ? resid + v : v;
     }
     cons_sync();  // `red` is reused by the next matrix
 }
 
-// RoPE of this head's q and of its KV head's new k, cache append (by the first query head of
-// each KV group), then attention of the one query over positions 0 .. pos.
-__device__ __forceinline__ void attention_head(const StepParams &p, int layer, int h, float *scratch,
-                                               float *misc) {
+// Attention of the one query of head h over positions 0 .. pos, the keys dealt in contiguous
+// chunks to p.splits CTAs per head: RoPE of the head's q and of its KV head's new k, cache
+// append (one CTA per KV head), then this CTA's chunk of scores, a local softmax and the
+// unnormalised weighted V sum. It leaves {acc[d], max, exp-sum}; the output projection
+// merges the splits while it stages its activations. The phase is a chain of short steps
+// that each wait on global memory, so every load that does not depend on an earlier step
+// (the head's q/k/v, up to 128 cached key rows, the value rows) is issued before anything
+// else; rows past the current position are fetched speculatively (the cache holds max_seq
+// rows) and never used.
+__device__ __forceinline__ void attention_head(const StepParams &p, int layer, int h, int split, int pos,
+                                               float *kc, float *vc, const float *rope_cs,
+                                               float *scratch, float *misc) {
     const int tid = threadIdx.x;
     const int d = p.d_head, half = d / 2;
     const int grp = p.n_q / p.n_kv, kvh = h / grp;
-    int pos = *p.pos;
-    pos = pos < 0 ? 0 : (pos >= p.max_seq ? p.max_seq - 1 : pos);
-    float *qs = scratch, *kcur = qs + d, *vcur = kcur + d, *partial = vcur + d;  // partial: [512/d][d]
-    float *scores = partial + DS_CONSUMERS;                                      // [max_seq]
-    float *kc = p.kcache[layer], *vc = p.vcache[layer];
-    const bool owner = (h % grp) == 0;
+    float *qs = scratch, *kcur = qs + d, *vcur = kcur + d, *partial = vcur + d;  // partial: [512/(d/4)][d]
+    float *scores = partial + 4 * DS_CONSUMERS;                                  // [max_seq]
+    const size_t kv_stride = (size_t)p.n_kv * d;
+    const float *kbase = kc + (size_t)kvh * d, *vbase = vc + (size_t)kvh * d;
+    const int limit = pos + 1;
+    const int chunk = (limit + p.splits - 1) / p.splits;
+    const int k0 = split * chunk, k1 = min(limit, k0 + chunk);   // this CTA's keys
+    float *po = p.attn + ((size_t)h * p.splits + split) * (d + 2);
+    if (k0 >= k1) {  // nothing for this split yet: the neutral element of the merge
+        for (int i = tid; i < d; i += DS_CONSUMERS) po[i] = 0.0f;
+        if (tid == 0) { po[d] = -INFINITY; po[d + 1] = 0.0f; }
+        return;
+    }
+    const bool has_new = (pos >= k0 && pos < k1);          // the split that sees the new position
+    const bool owner = has_new && (h % grp) == 0;          // ... of the first head of the group appends
+    ATRACE(0);
+
+    // ---- loads ----
+    constexpr int KQ = 8;   // float4 per thread of a key row: d/16 <= 8
+    constexpr int NV = 4;   // value rows prefetched per thread
+    const int kq = tid >> 2, sub = tid & 3, q4n = d / 16;       // 4 threads per key row
+    const int vec = d / 4, nparts = DS_CONSUMERS / vec, part = tid / vec, c4 = tid % vec;
+    float4 kreg[KQ], vreg[NV];
+#pragma unroll
+    for (int j = 0; j < KQ; ++j)
+        kreg[j] = (j < q4n && k0 + kq < p.max_seq)
+                      ? __ldg(reinterpret_cast<const float4 *>(kbase + (size_t)(k0 + kq) * kv_stride + sub * (d / 4)) + j)
+                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int key = k0 + part + j * nparts;
+        vreg[j] = key < p.max_seq ? __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)key * kv_stride) + c4)
+                                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float x0 = 0.0f, x1 = 0.0f;
+    const bool is_k = tid >= half;
+    const int ri = is_k ? tid - half : tid;
     if (tid < d) {
-        const bool is_k = tid >= half;
-        const int i = is_k ? tid - half : tid;
-        const float inv_freq = 1.0f / powf(p.theta, 2.0f * (float)i / (float)d);
-        float sn, cs;
-        sincosf(inv_freq * (float)pos, &sn, &cs);
         const float *src = p.qkv + (size_t)(is_k ? p.n_q + kvh : h) * d;
-        const float x0 = __ldcg(src + i), x1 = __ldcg(src + i + half);
+        x0 = __ldcg(src + ri);
+        x1 = __ldcg(src + ri + half);
+    } else if (tid < 2 * d) {
+        x0 = __ldcg(p.qkv + (size_t)(p.n_q + p.n_kv + kvh) * d + (tid - d));
+    }
+    ATRACE(1);
+
+    // ---- RoPE, append ----
+    if (tid < d) {
+        const float cs = rope_cs[2 * ri], sn = rope_cs[2 * ri + 1];  // the same for every layer
         const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
         float *dst = is_k ? kcur : qs;
-        dst[i] = y0;
-        dst[i + half] = y1;
+        dst[ri] = y0;
+        dst[ri + half] = y1;
         if (is_k && owner) {
             float *cd = kc + ((size_t)pos * p.n_kv + kvh) * d;
-            cd[i] = y0;
-            cd[i + half] = y1;
+            cd[ri] = y0;
+            cd[ri + half] = y1;
         }
     } else if (tid < 2 * d) {
-        const int i = tid - d;
-        const float v = __ldcg(p.qkv + (size_t)(p.n_q + p.n_kv + kvh) * d + i);
-        vcur[i] = v;
-        if (owner) vc[((size_t)pos * p.n_kv + kvh) * d + i] = v;
+        vcur[tid - d] = x0;
+        if (owner) vc[((size_t)pos * p.n_kv + kvh) * d + (tid - d)] = x0;
     }
     cons_sync();
+    ATRACE(2);
+
+    // ---- scores: four threads per key, a quarter of the row each ----
     const float scale = 1.0f / sqrtf((float)d);
-    const int limit = pos + 1;
+    const int nk = k1 - k0;
+    const float4 *q4 = reinterpret_cast<const float4 *>(qs + sub * (d / 4));
     float mx = -INFINITY;
-    for (int key = tid; key < limit; key += DS_CONSUMERS) {
+    for (int kk = kq, pass = 0; kk < ((nk + 127) & ~127); kk += DS_CONSUMERS / 4, ++pass) {
+        const int key = k0 + kk;
         float dot = 0.0f;
-        const float4 *q4 = reinterpret_cast<const float4 *>(qs);
-        if (key < pos) {
-            const float4 *kr = reinterpret_cast<const float4 *>(kc + ((size_t)key * p.n_kv + kvh) * d);
-#pragma unroll 4
-            for (int i = 0; i < d / 4; ++i) {
-                const float4 kv = __ldg(kr + i), qv = q4[i];
-                dot = fmaf(qv.x, kv.x, dot);
-                dot = fmaf(qv.y, kv.y, dot);
-                dot = fmaf(qv.z, kv.z, dot);
-                dot = fmaf(qv.w, kv.w, dot);
-            }
-        } else {
-            const float4 *kr = reinterpret_cast<const float4 *>(kcur);
-            for (int i = 0; i < d / 4; ++i) {
-                const float4 kv = kr[i], qv = q4[i];
-                dot = fmaf(qv.x, kv.x, dot);
-                dot = fmaf(qv.y, kv.y, dot);
-                dot = fmaf(qv.z, kv.z, dot);
-                dot = fmaf(qv.w, kv.w, dot);
+        if (kk < nk) {
+            const float4 *kcur4 = reinterpret_cast<const float4 *>(kcur + sub * (d / 4));
+            const float4 *krow = reinterpret_cast<const float4 *>(kbase + (size_t)key * kv_stride + sub * (d / 4));
+#pragma unroll
+            for (int j = 0; j < KQ; ++j) {
+                if (j < q4n) {
+                    const float4 kv = key == pos ? kcur4[j] : (pass == 0 ? kreg[j] : __ldg(krow + j));
+                    const float4 qv = q4[j];
+                    dot = fmaf(qv.x, kv.x, dot);
+                    dot = fmaf(qv.y, kv.y, dot);
+                    dot = fmaf(qv.z, kv.z, dot);
+                    dot = fmaf(qv.w, kv.w, dot);
+                }
             }
         }
-        const float sc = dot * scale;
-        scores[key] = sc;
-        mx = fmaxf(mx, sc);
+        // every lane takes part in the shuffles (the loop bound is a multiple of 128 keys)
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        if (kk < nk) {
+            const float sc = dot * scale;
+            if (sub == 0) scores[kk] = sc;
+            mx = fmaxf(mx, sc);
+        }
     }
+    ATRACE(3);
     mx = cons_max(mx, misc);
     float se = 0.0f;
-    for (int key = tid; key < limit; key += DS_CONSUMERS) {
-        const float e = expf(scores[key] - mx);
-        scores[key] = e;
+    for (int kk = tid; kk < nk; kk += DS_CONSUMERS) {
+        const float e = expf(scores[kk] - mx);
+        scores[kk] = e;
         se += e;
     }
     se = cons_sum(se, misc);  // (its barriers also publish `scores`)
-    const float inv = se > 0.0f ? 1.0f / se : 0.0f;
-    const int nparts = DS_CONSUMERS / d, part = tid / d, dd = tid % d;
-    float acc = 0.0f;
-    if (part < nparts) {
-        for (int key = part; key < limit; key += nparts) {
-            const float v = key < pos ? __ldg(vc + ((size_t)key * p.n_kv + kvh) * d + dd) : vcur[dd];
-            acc = fmaf(scores[key], v, acc);
+    ATRACE(4);
+
+    // ---- weighted V: d/4 threads per key row, the keys dealt round-robin to 512/(d/4) parts ----
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float4 vcur4 = *(reinterpret_cast<const float4 *>(vcur) + c4);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int kk = part + j * nparts;
+        if (kk < nk) {
+            const float4 v = k0 + kk == pos ? vcur4 : vreg[j];
+            const float w = scores[kk];
+            acc.x = fmaf(w, v.x, acc.x);
+            acc.y = fmaf(w, v.y, acc.y);
+            acc.z = fmaf(w, v.z, acc.z);
+            acc.w = fmaf(w, v.w, acc.w);
         }
-        partial[part * d + dd] = acc;
     }
+#pragma unroll 4
+    for (int kk = part + NV * nparts; kk < nk; kk += nparts) {
+        const float4 v = k0 + kk == pos ? vcur4
+                                        : __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)(k0 + kk) * kv_stride) + c4);
+        const float w = scores[kk];
+        acc.x = fmaf(w, v.x, acc.x);
+        acc.y = fmaf(w, v.y, acc.y);
+        acc.z = fmaf(w, v.z, acc.z);
+        acc.w = fmaf(w, v.w, acc.w);
+    }
+    *(reinterpret_cast<float4 *>(partial + (size_t)part * d) + c4) = acc;
+    ATRACE(5);
     cons_sync();
     if (tid < d) {
         float v = 0.0f;
         for (int pt = 0; pt < nparts; ++pt) v += partial[pt * d + tid];
-        p.attn[(size_t)h * d + tid] = v * inv;
+        po[tid] = v;
     }
+    if (tid == 0) { po[d] = mx; po[d + 1] = se; }
+    ATRACE(6);
     cons_sync();  // scratch is reused
 }
 
@@ -374,6 +461,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     unsigned char *dig = smem + ring_bytes + DS_RED_BYTES + DS_BAR_BYTES;
     float *act_s = reinterpret_cast<float *>(dig + p.dig_bytes);
     float *misc = act_s + p.act_floats;  // 32 floats
+    float *rope_cs = misc + 32;          // [d_head/2] x {cos, sin} of this step's position
+    float **cache_ptr = reinterpret_cast<float **>(rope_cs + p.d_head);  // [layers] x {k, v}
     const int nmat = p.layers * 4;
 
     if (tid == DS_CONSUMERS) {
@@ -394,20 +483,25 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
             bool alive = true;
             for (int mi = 0; mi < nmat && alive; ++mi) {
                 const StepMat *m = p.mats + mi;
-                const int n = m->n, tiles = m->tiles, k_stages = m->k_stages;
+                const int n = p.mat_n[mi & 3], tiles = p.mat_tiles[mi & 3], k_stages = p.mat_ks[mi & 3];
                 const int r0 = (int)(((unsigned)n * blockIdx.x) / gridDim.x);
                 const int rb_rows = tiles * 16;
-                const uint32_t tx = (uint32_t)rb_rows * (DS_GS * 16 + DS_GS * 4);
-                for (int ks = 0; ks < k_stages && alive; ++ks) {
+                const int kps = p.mat_kps[mi & 3];
+                const uint32_t sub_bytes = (uint32_t)rb_rows * (DS_GS * 16 + DS_GS * 4);
+                for (int ks0 = 0; ks0 < k_stages && alive; ks0 += kps) {
                     // a fresh barrier passes the wait on the opposite parity at once
                     alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, p.status);
                     if (!alive) break;
-                    const uint32_t st = smem_base + (uint32_t)slot * p.slot_bytes;
+                    const int nsub = min(kps, k_stages - ks0);
                     const uint32_t full = bar_full + slot * 8;
-                    mbar_expect_tx(full, tx);
-                    tma_load_2d(st, &m->tm_w, ks * (DS_GS * 16), r0, full);
-                    tma_load_2d(st + rb_rows * 128, &m->tm_w, ks * (DS_GS * 16) + 128, r0, full);
-                    tma_load_2d(st + rb_rows * 256, &m->tm_s, ks * DS_GS, r0, full);
+                    mbar_expect_tx(full, (uint32_t)nsub * sub_bytes);
+                    for (int j = 0; j < nsub; ++j) {
+                        const uint32_t st = smem_base + (uint32_t)slot * p.slot_bytes + (uint32_t)j * sub_bytes;
+                        const int ks = ks0 + j;
+                        tma_load_2d(st, &m->tm_w, ks * (DS_GS * 16), r0, full);
+                        tma_load_2d(st + rb_rows * 128, &m->tm_w, ks * (DS_GS * 16) + 128, r0, full);
+                        tma_load_2d(st + rb_rows * 256, &m->tm_s, ks * DS_GS, r0, full);
+                    }
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
             }
@@ -425,29 +519,59 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     const int H = p.hidden, I = p.inter;
 
     auto gemv = [&](int mi, float *out, bool accumulate) {
-        const StepMat *m = p.mats + mi;
-        const int n = m->n, tiles = m->tiles, k_stages = m->k_stages;
+        const int n = p.mat_n[mi & 3], tiles = p.mat_tiles[mi & 3], k_stages = p.mat_ks[mi & 3];
+        const int kps = p.mat_kps[mi & 3];
         const int r0 = (int)(((unsigned)n * blockIdx.x) / gridDim.x);
         const int r1 = (int)(((unsigned)n * (blockIdx.x + 1)) / gridDim.x);
         if (tiles <= 2)
-            consume_matrix<2>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, r0, r1, out, accumulate, dead);
+            consume_matrix<2>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, accumulate, dead);
         else
-            consume_matrix<8>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, r0, r1, out, accumulate, dead);
+            consume_matrix<8>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, accumulate, dead);
     };
     // act_s = RMSNorm(x) * gamma
     auto stage_norm = [&](const float *gamma) {
+        // H <= 8 * 512 keeps a thread's elements and gammas in registers across the reduction
+        float xv[8], gv[8];
         float ss = 0.0f;
-        for (int i = tid; i < H; i += DS_CONSUMERS) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = tid + j * DS_CONSUMERS;
+            xv[j] = i < H ? __ldcg(p.x + i) : 0.0f;
+            gv[j] = i < H ? __ldg(gamma + i) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(xv[j], xv[j], ss);
+        for (int i = tid + 8 * DS_CONSUMERS; i < H; i += DS_CONSUMERS) {
             const float v = __ldcg(p.x + i);
-            act_s[i] = v;
             ss = fmaf(v, v, ss);
         }
         const float total = cons_sum(ss, misc);
         const float inv = 1.0f / sqrtf(total / (float)H + p.eps);
-        for (int i = tid; i < H; i += DS_CONSUMERS) act_s[i] = (act_s[i] * inv) * gamma[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = tid + j * DS_CONSUMERS;
+            if (i < H) act_s[i] = (xv[j] * inv) * gv[j];
+        }
+        for (int i = tid + 8 * DS_CONSUMERS; i < H; i += DS_CONSUMERS) act_s[i] = (__ldcg(p.x + i) * inv) * gamma[i];
         cons_sync();
     };
 
+    // per-launch constants: the position, its rotary factors, the cache pointers; the padding
+    // row of the digit planes
+    int pos = *p.pos;
+    pos = pos < 0 ? 0 : (pos >= p.max_seq ? p.max_seq - 1 : pos);
+    if (tid < p.d_head / 2) {
+        const float inv_freq = 1.0f / powf(p.theta, 2.0f * (float)tid / (float)p.d_head);
+        sincosf(inv_freq * (float)pos, &rope_cs[2 * tid + 1], &rope_cs[2 * tid]);
+    }
+    for (int i = tid; i < 2 * p.layers; i += DS_CONSUMERS)
+        cache_ptr[i] = (i & 1) ? p.vcache[i >> 1] : p.kcache[i >> 1];
+    {
+        const QuantLayout q = quant_layout(1, DS_GS);
+        const int groups = p.dig_bytes / (4 * 4 * 16);
+        for (int item = tid >> 2; item < groups; item += DS_CONSUMERS / 4)
+            quantize_group<true>(nullptr, dig, q, item, 1, tid & 3, true);
+    }
     // x = embedding[token]
     {
         int tok = *p.token;
@@ -460,26 +584,52 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
 
     for (int l = 0; l < p.layers; ++l) {
         const float *g1 = p.gamma + (size_t)(2 * l) * H, *g2 = g1 + H;
-        const int ts = l * 16;  // trace slots of this layer (debug builds)
+        const int ts = l < 3 ? l * 16 : -100;  // trace slots of this layer (debug builds)
         STRACE(ts + 0);
         // attention block: norm -> qkv
         stage_norm(g1);
         STRACE(ts + 1);
-        quantize_activation(act_s, dig, H);
+        quantize_activation(act_s, dig, H, false);
         STRACE(ts + 2);
         gemv(4 * l + 0, p.qkv, false);
         STRACE(ts + 3);
         grid_barrier(p, epoch);
         STRACE(ts + 4);
         // RoPE, cache append, attention: one CTA per query head
-        if ((int)blockIdx.x < p.n_q) attention_head(p, l, blockIdx.x, reinterpret_cast<float *>(dig), misc);
+        if ((int)blockIdx.x < p.n_q * p.splits)
+            attention_head(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
+                           cache_ptr[2 * l + 1], rope_cs, act_s, misc);
         STRACE(ts + 5);
         grid_barrier(p, epoch);
         STRACE(ts + 6);
-        // output projection, residual add in the store
-        for (int i = tid; i < p.n_q * p.d_head; i += DS_CONSUMERS) act_s[i] = __ldcg(p.attn + i);
+        // output projection, residual add in the store; its activation vector is the merge of
+        // the attention splits (the usual max-rescaling of a split softmax)
+#pragma unroll 4
+        for (int i = tid; i < p.n_q * p.d_head; i += DS_CONSUMERS) {
+            const int hh = i / p.d_head, dd = i - hh * p.d_head;
+            const float *pp = p.attn + (size_t)hh * p.splits * (p.d_head + 2);
+            float a[4], m[4], e[4];  // splits <= 4
+#pragma unroll
+            for (int sp = 0; sp < 4; ++sp) {
+                const bool on = sp < p.splits;
+                a[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + dd) : 0.0f;
+                m[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + p.d_head) : -INFINITY;
+                e[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + p.d_head + 1) : 0.0f;
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 4; ++sp) M = fmaxf(M, m[sp]);
+            float L = 0.0f, v = 0.0f;
+#pragma unroll
+            for (int sp = 0; sp < 4; ++sp) {
+                const float w = m[sp] > -INFINITY ? expf(m[sp] - M) : 0.0f;
+                L = fmaf(w, e[sp], L);
+                v = fmaf(w, a[sp], v);
+            }
+            act_s[i] = L > 0.0f ? v / L : 0.0f;
+        }
         cons_sync();
-        quantize_activation(act_s, dig, p.n_q * p.d_head);
+        quantize_activation(act_s, dig, p.n_q * p.d_head, false);
         STRACE(ts + 7);
         gemv(4 * l + 1, p.x, true);
         STRACE(ts + 8);
@@ -487,19 +637,29 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         STRACE(ts + 9);
         // MLP: norm -> gate+up -> SwiGLU -> down, residual add in the store
         stage_norm(g2);
-        quantize_activation(act_s, dig, H);
+        quantize_activation(act_s, dig, H, false);
         STRACE(ts + 10);
         gemv(4 * l + 2, p.gu, false);
         STRACE(ts + 11);
         grid_barrier(p, epoch);
         STRACE(ts + 12);
-        for (int i = tid; i < I; i += DS_CONSUMERS) {
-            const float g = __ldcg(p.gu + i), u = __ldcg(p.gu + I + i);
-            const float s = 1.0f / (1.0f + expf(-g));
-            act_s[i] = (g * s) * u;
+        for (int i0 = tid; i0 < I; i0 += 12 * DS_CONSUMERS) {
+            float g[12], u[12];
+#pragma unroll
+            for (int j = 0; j < 12; ++j) {  // up to 24 loads in flight per thread
+                const int i = i0 + j * DS_CONSUMERS;
+                g[j] = i < I ? __ldcg(p.gu + i) : 0.0f;
+                u[j] = i < I ? __ldcg(p.gu + I + i) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 12; ++j) {
+                const int i = i0 + j * DS_CONSUMERS;
+                const float sg = 1.0f / (1.0f + expf(-g[j]));
+                if (i < I) act_s[i] = (g[j] * sg) * u[j];
+            }
         }
         cons_sync();
-        quantize_activation(act_s, dig, I);
+        quantize_activation(act_s, dig, I, false);
         STRACE(ts + 13);
         gemv(4 * l + 3, p.x, true);
         STRACE(ts + 14);
@@ -554,7 +714,7 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     *out = nullptr;
     if (tensor_map_encoder() == nullptr) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "no tensor-map encoder in this driver");
     const int grid = ctx->sm_count;
-    if (n_kv == 0 || n_q % n_kv != 0 || d_head == 0 || d_head % 8 != 0 || 2 * d_head > (size_t)DS_CONSUMERS ||
+    if (n_kv == 0 || n_q % n_kv != 0 || d_head == 0 || d_head % 16 != 0 || d_head > 128 ||
         DS_CONSUMERS % d_head != 0 || n_q > (size_t)grid)
         return fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: n_q=%zu n_kv=%zu d_head=%zu not supported on %d SMs",
                     n_q, n_kv, d_head, grid);
@@ -610,13 +770,17 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     slot_bytes = ((slot_bytes + 1023) / 1024) * 1024;
     StepParams &p = plan->params;
     p.dig_bytes = (int)(k_max / 512) * DS_BLOB_BYTES;
-    p.act_floats = (int)k_max;
-    // the attention scratch (q, k, v of the head, partial sums, scores) lives in the digit +
-    // activation area between the GEMVs
-    const size_t attn_scratch = (3 * d_head + DS_CONSUMERS + max_seq) * sizeof(float);
-    if (attn_scratch > (size_t)p.dig_bytes + k_max * 4)
+    // the attention scratch (q, k, v of the head, partial sums, scores) lives in the activation
+    // area between the GEMVs: widen that area if it needs more
+    const size_t attn_scratch = (3 * d_head + 4 * DS_CONSUMERS + max_seq) * sizeof(float);
+    size_t act_floats = k_max;
+    if (attn_scratch > act_floats * 4) act_floats = (attn_scratch + 3) / 4;
+    act_floats = (act_floats + 3) / 4 * 4;
+    if (act_floats * 4 > 96 * 1024)
         return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: max_seq=%zu does not fit one CTA per head", max_seq));
-    const int fixed = DS_RED_BYTES + DS_BAR_BYTES + p.dig_bytes + (int)k_max * 4 + 128;
+    p.act_floats = (int)act_floats;
+    const int tables = 128 + (int)d_head * 4 + (int)n_layers * 2 * 8 + 16;  // misc, rotary factors, cache pointers
+    const int fixed = DS_RED_BYTES + DS_BAR_BYTES + p.dig_bytes + p.act_floats * 4 + tables;
     const int budget = 227 * 1024 - fixed - 1024;
     p.stages = budget / slot_bytes;
     if (p.stages > DS_MAX_STAGES) p.stages = DS_MAX_STAGES;
@@ -627,7 +791,9 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     // device copies: matrices, gammas, cache pointers, scratch, barrier words
     std::vector<float *> kptr(n_layers), vptr(n_layers);
     for (size_t l = 0; l < n_layers; ++l) { kptr[l] = layers[l].d_kcache; vptr[l] = layers[l].d_vcache; }
-    const size_t scratch_floats = qkv_rows + attn_w + 2 * inter;
+    const int splits = (int)std::min<size_t>(4, (size_t)grid / n_q);
+    const size_t attn_floats = n_q * splits * (d_head + 2);
+    const size_t scratch_floats = qkv_rows + attn_floats + 2 * inter;
 #define PLAN_TRY(expr)                                                                       \
     do {                                                                                     \
         cudaError_t _e = (expr);                                                             \
@@ -662,7 +828,8 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     float *s = reinterpret_cast<float *>(plan->d_scratch);
     p.qkv = s;
     p.attn = s + qkv_rows;
-    p.gu = p.attn + attn_w;
+    p.gu = p.attn + attn_floats;
+    p.splits = splits;
     p.sync = reinterpret_cast<unsigned int *>(plan->d_sync);
     p.status = ctx->d_status;
     p.layers = (int)n_layers;
@@ -674,6 +841,13 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     p.max_seq = (int)max_seq;
     p.eps = eps;
     p.theta = rope_theta;
+    for (int j = 0; j < 4; ++j) {
+        p.mat_n[j] = mats[j].n;
+        p.mat_tiles[j] = mats[j].tiles;
+        p.mat_ks[j] = mats[j].k_stages;
+        const int sub = mats[j].tiles * 16 * (DS_GS * 16 + DS_GS * 4);
+        p.mat_kps[j] = std::max(1, std::min(slot_bytes / sub, 8));
+    }
     *out = plan;
     return YSCV_CUDA_OK;
 }

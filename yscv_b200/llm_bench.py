@@ -98,6 +98,7 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
         "weight_bytes_per_step_per_gpu": wb,
         "weight_stream_gbs_per_gpu": wb / (decode_ms / max_tokens * 1e-3) / 1e9,
         "cuda_graph": bool(use_graph), "prefill": "fp32-exact" if exact_prefill else "bf16 tensor-core",
+        "decode_step": "one persistent kernel per token" if dec.plan is not None else "operator chain",
         "first_tokens": toks[:8, 0].cpu().tolist(),
         "device_status": ctx.device_status(),
     }
