@@ -149,6 +149,16 @@ int yscv_cuda_int4_matmul_dev_static(yscv_cuda_ctx *ctx, const uint8_t *d_packed
                                      size_t group_size, const float *d_activation,
                                      float *d_output, size_t m);
 
+/* Weights exported as ONNX MatMulNBits (bits = 4, block_size = group) hold unsigned nibbles with
+ * an implicit zero point of 8 in the same [N][K/2] layout, low nibble = even k; the reference
+ * has no such import (its int4 weights live in a side-table, crates/yscv-onnx/src/quantize/
+ * packed_int4.rs:28-39). byte ^ 0x88 turns them into this library's two's-complement nibbles;
+ * scales are unchanged. src == dst is allowed. The host form is a load-time format conversion
+ * and makes no CUDA call. */
+int yscv_cuda_int4_from_matmulnbits(const uint8_t *src, uint8_t *dst, size_t bytes);
+int yscv_cuda_int4_from_matmulnbits_dev(yscv_cuda_ctx *ctx, const uint8_t *d_src, uint8_t *d_dst,
+                                        size_t bytes);
+
 /* pack_int4_symmetric_per_group on device memory: d_weights [m_w,k] f32. */
 int yscv_cuda_pack_int4_dev(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w,
                             size_t k, size_t group_size, uint8_t *d_packed,
@@ -170,6 +180,13 @@ int yscv_cuda_pack_i8_b_for_matmul(yscv_cuda_ctx *ctx, const int8_t *b, size_t k
 int yscv_cuda_pack_i8_b_dev(yscv_cuda_ctx *ctx, const int8_t *d_b, size_t k, size_t n,
                             yscv_cuda_i8b **out);
 void yscv_cuda_i8b_free(yscv_cuda_i8b *b);
+/* Zero point of B (the b_zero_point input of MatMulInteger / QLinearMatMul, a scalar:
+ * crates/yscv-onnx/src/runner/linear.rs:440-446, 651-660), default 0. The reference leaves
+ * its integer path when any zero point is non-zero and computes in fp32 (linear.rs:701-735);
+ * here the product stays exact: sum_k (a - a_zp)(b - b_zp) = acc - a_zp * colsum(B)[n]
+ * - b_zp * rowsum(A)[m] + k * a_zp * b_zp in the epilogue (one extra pass over A). Weights
+ * stored as uint8 with zero point z are given as int8 (byte ^ 0x80) with zero point z - 128. */
+int yscv_cuda_i8b_set_zero_point(yscv_cuda_i8b *b, int32_t b_zero_point);
 size_t yscv_cuda_i8b_k(const yscv_cuda_i8b *b); /* PackedI8B::k() */
 size_t yscv_cuda_i8b_n(const yscv_cuda_i8b *b); /* PackedI8B::n() */
 
@@ -262,6 +279,35 @@ int yscv_cuda_argmax_last_dev(yscv_cuda_ctx *ctx, const float *d_logits, size_t 
 
 /* *d_pos += by, on the stream (position_offset += 1, apps/llm-bench/src/main.rs:536) */
 int yscv_cuda_advance_pos_dev(yscv_cuda_ctx *ctx, int32_t *d_pos, int by);
+
+/* ---- int8 GEMM with the i8 requant epilogues of the quantized convolution path ----------
+ * The pointwise (1x1) QLinearConv of the reference is an int8 GEMM over NHWC pixels,
+ * A [m = pixels][k = c_in] i8, B [k][n = c_out] i8, followed by a requant pass
+ * (crates/yscv-onnx/src/runner/conv/quantized.rs:340-500). Both are fused here.
+ *
+ * per-channel: int8_matmul_prepacked_dispatch + requant_i8_per_channel_dispatch
+ * (crates/yscv-kernels/src/ops/int8_requant.rs:537-556):
+ *   out[m,n] = clamp(round_ties_even((float)(acc[m,n] + corr[n]) * composite[n] + y_zp), -128, 127)
+ * with the add wrapping as in the reference; corr[n] is what the caller folds together
+ * there (bias[n] - x_zp * sum_k w[k,n]), composite[n] = x_scale * w_scale[n] / y_scale. */
+int yscv_cuda_int8_matmul_requant_per_channel_dev(yscv_cuda_ctx *ctx, const int8_t *d_a,
+                                                  const yscv_cuda_i8b *b, size_t m,
+                                                  const int32_t *d_corr, const float *d_composite,
+                                                  float y_zero_point, int8_t *d_out);
+int yscv_cuda_int8_matmul_requant_per_channel(yscv_cuda_ctx *ctx, const int8_t *a,
+                                              const yscv_cuda_i8b *b, size_t m, const int32_t *corr,
+                                              const float *composite, float y_zero_point,
+                                              int8_t *out);
+
+/* per-tensor: int8_matmul_prepacked_dispatch + requant_i32_row_to_i8_dispatch
+ * (int8_requant.rs:81-138, 143-169): optional bias[n] (wrapping add; may be NULL), scalar
+ * composite, saturate to [-128,127], optional ReLU after the saturation. */
+int yscv_cuda_int8_matmul_requant_i8_dev(yscv_cuda_ctx *ctx, const int8_t *d_a, const yscv_cuda_i8b *b,
+                                         size_t m, const int32_t *d_bias, float composite,
+                                         float y_zero_point, int relu, int8_t *d_out);
+int yscv_cuda_int8_matmul_requant_i8(yscv_cuda_ctx *ctx, const int8_t *a, const yscv_cuda_i8b *b,
+                                     size_t m, const int32_t *bias, float composite,
+                                     float y_zero_point, int relu, int8_t *out);
 
 /* ---- one decode step in one launch ---------------------------------------------------
  * No single counterpart in the reference: one iteration of the llm-bench decode loop

@@ -104,6 +104,14 @@ def int8_fixtures(o):
         # requant_scalar (int8_matmul.rs): separate multiply and add, ties to even, clamp
         out[f"{name}/q_u8"] = o.requant_range(acc, float(comp), 128.0, 0, 255).astype(np.uint8)
         out[f"{name}/q_i8"] = o.requant_range(acc, float(comp), -3.0, -128, 127).astype(np.int8)
+        if zp == 0 and not unsigned:
+            # pointwise QLinearConv epilogue (int8_requant.rs:537-556): per-channel composite and
+            # correction (bias - x_zp * colsum, here any int32 vector)
+            corr = (o.lcg_i8(seed + 2, n).astype(np.int32) * 37)
+            comp_pc = (comp * (np.float32(1.0) + np.float32(0.125) * (np.arange(n) % 5).astype(np.float32))).astype(np.float32)
+            out[f"{name}/corr"] = corr
+            out[f"{name}/composite_pc"] = comp_pc
+            out[f"{name}/q_pc"] = o.requant_i8_per_channel(acc.ravel(), corr, comp_pc, 4.0, n).reshape(m, n)
     return out
 
 

@@ -32,6 +32,17 @@ def test_binding_covers_header_exactly():
     yscv_b200.load_library()
 
 
+def test_matmulnbits_nibbles_become_twos_complement(oracle):
+    # (q_u - 8) for every unsigned nibble pair equals the sign-extended nibbles of byte ^ 0x88
+    import numpy as np
+    src = np.arange(256, dtype=np.uint8)
+    got = yscv_b200.int4_from_matmulnbits(src)
+    assert np.array_equal(got, src ^ 0x88)
+    for u, s in zip(src.tolist(), got.tolist()):
+        assert oracle.lib.yo_unpack_low(s) == (u & 15) - 8
+        assert oracle.lib.yo_unpack_high(s) == (u >> 4) - 8
+
+
 def test_no_fallback_without_device():
     # On a machine without a B200 the library must refuse, not compute on the CPU.
     import torch

@@ -64,6 +64,9 @@ def test_oracle_reproduces_int8(oracle, name):
         if np.max(np.abs(c["acc"])) < 2 ** 24:
             assert np.array_equal(got.astype(np.int64), c["acc"].astype(np.int64))
     comp = float(c["composite"][0])
+    if "q_pc" in c:
+        got = oracle.requant_i8_per_channel(c["acc"].ravel(), c["corr"], c["composite_pc"], 4.0, n).reshape(m, n)
+        assert np.array_equal(got, c["q_pc"])
     assert np.array_equal(oracle.requant_range(c["acc"], comp, 128.0, 0, 255), c["q_u8"].astype(np.int32))
     assert np.array_equal(oracle.requant_range(c["acc"], comp, -3.0, -128, 127), c["q_i8"].astype(np.int32))
 
@@ -123,6 +126,9 @@ def test_cuda_int8_matches_golden(ctx, name):
             assert np.array_equal(np.asarray(ctx.int8_matmul_prepacked(c["a"], pk, m)).reshape(m, n), c["acc"])
         got = ctx.matmul_integer(c["a"], pk, m, a_zp=zp)
         assert np.array_equal(np.asarray(got).reshape(m, n), c["acc"])
+        if "q_pc" in c:
+            got = ctx.int8_matmul_requant_per_channel(c["a"], pk, m, c["corr"], c["composite_pc"], 4.0)
+            assert np.array_equal(got, c["q_pc"])
         comp = float(c["composite"][0])
         rq = ctx.requant(comp, 128.0, 0, 255, a_unsigned=bool(unsigned), a_zp=zp)
         got = ctx.qlinear_matmul(c["a"], pk, m, rq)

@@ -245,3 +245,23 @@ def test_bad_arguments(ctx):
     with pytest.raises(yscv_b200.YscvCudaError):
         ctx.packed_int4_gemv(z8, zf, zf, 0, 32, 32)       # no rows
     assert ctx.packed_int4_gemm(z8, zf, np.zeros(0, np.float32), 0, 2, 32, 32).shape == (0, 2)
+
+
+def test_matmulnbits_import_on_device(ctx, oracle):
+    """Weights given as MatMulNBits bytes (zero point 8): converted on the device, then the same GEMV."""
+    import torch
+    n, k, g = 296, 512, 32
+    w = oracle.lcg_f32(0x4B1D, n * k)
+    packed, scales = oracle.pack_int4(w, n, k, g)
+    nbits = packed ^ 0x88                      # what an exporter would have written
+    torch.cuda.synchronize()
+    d_src = torch.from_numpy(nbits).cuda()
+    d_dst = torch.empty_like(d_src)
+    torch.cuda.synchronize()
+    ctx.int4_from_matmulnbits_dev(d_src.data_ptr(), d_dst.data_ptr(), d_src.numel())
+    ctx.synchronize()
+    assert np.array_equal(d_dst.cpu().numpy(), packed)
+    act = oracle.lcg_f32(0x77, k)
+    got = ctx.packed_int4_gemv(d_dst.cpu().numpy(), scales, act, n, k, g)
+    want = oracle.int4_gemv(packed, scales, act, n, k, g)
+    assert np.max(np.abs(got - want)) / np.max(np.abs(want)) <= 1e-4

@@ -176,3 +176,116 @@ def test_bad_arguments(ctx):
     assert e.value.status == -1
     assert ctx.int8_matmul_prepacked(np.zeros(0, np.int8), packed, 0).shape == (0, 4)
     packed.free()
+
+
+# ---- the i8 requant epilogues of the pointwise QLinearConv path ---------------------------
+# crates/yscv-onnx/src/runner/conv/quantized.rs:340-500 = int8 GEMM over NHWC pixels, then
+# requant_i8_per_channel (int8_requant.rs:537-556) or requant_i32_row_to_i8 (:81-169)
+
+def conv_case(m, k, n, seed):
+    a = synth.uniform_int(seed, 0, m * k, -128, 127).astype(np.int8)      # activations, NHWC pixels
+    b = synth.uniform_int(seed, 1, k * n, -127, 127).astype(np.int8)      # weights [c_in][c_out]
+    x_zp = int(synth.uniform_int(seed, 2, 1, -20, 20)[0])
+    bias = synth.uniform_int(seed, 3, n, -5000, 5000).astype(np.int32)
+    colsum = b.reshape(k, n).astype(np.int64).sum(axis=0)
+    corr = (bias.astype(np.int64) - x_zp * colsum).astype(np.int32)       # what the reference folds together
+    w_scale = (0.002 + 0.001 * (np.arange(n) % 7)).astype(np.float32)
+    composite = (np.float32(0.05) * w_scale / np.float32(0.11)).astype(np.float32)
+    return a, b, corr, composite, bias
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 4, 1), (49, 32, 24), (196, 96, 33), (784, 128, 256), (3136, 64, 130),
+                                   (1000, 257, 512)])
+def test_pointwise_conv_per_channel_requant(ctx, oracle, m, k, n):
+    a, b, corr, composite, _ = conv_case(m, k, n, 40 + m)
+    packed = ctx.pack_i8_b(b, k, n)
+    got = ctx.int8_matmul_requant_per_channel(a, packed, m, corr, composite, -3.0)
+    acc = oracle.int8_matmul(a, b, m, k, n)
+    want = oracle.requant_i8_per_channel(acc.ravel(), corr, composite, -3.0, n).reshape(m, n)
+    assert np.array_equal(got, want), ctx.last_kernel()
+    assert ctx.device_status() == 0
+    packed.free()
+
+
+def test_per_channel_requant_wraps_like_the_reference(ctx, oracle):
+    # acc + corr overflows i32: the reference's wrapping_add turns it negative, saturating low
+    m, k, n = 4, 64, 40
+    a = np.full(m * k, 127, np.int8)
+    b = np.full(k * n, 127, np.int8)
+    corr = np.full(n, 2**31 - 1, np.int32)
+    corr[::2] = -7
+    composite = np.full(n, 1e-4, np.float32)
+    packed = ctx.pack_i8_b(b, k, n)
+    got = ctx.int8_matmul_requant_per_channel(a, packed, m, corr, composite, 0.0)
+    acc = oracle.int8_matmul(a, b, m, k, n)
+    want = oracle.requant_i8_per_channel(acc.ravel(), corr, composite, 0.0, n).reshape(m, n)
+    assert np.array_equal(got, want)
+    assert got[0, 1] == -128 and got[0, 0] > 0
+    packed.free()
+
+
+@pytest.mark.parametrize("relu,with_bias", [(False, False), (False, True), (True, True), (True, False)])
+def test_pointwise_conv_per_tensor_requant(ctx, oracle, relu, with_bias):
+    m, k, n = 300, 96, 72
+    a, b, _, _, bias = conv_case(m, k, n, 77)
+    packed = ctx.pack_i8_b(b, k, n)
+    got = ctx.int8_matmul_requant_i8(a, packed, m, bias if with_bias else None, 3.1e-4, 2.0, relu=relu)
+    acc = oracle.int8_matmul(a, b, m, k, n)
+    want = oracle.requant_i8(acc.ravel(), bias if with_bias else None, 3.1e-4, 2.0, relu, n).reshape(m, n)
+    assert np.array_equal(got, want)
+    if relu:
+        assert got.min() >= 0
+    packed.free()
+
+
+def test_per_channel_requant_device_pointers(ctx, oracle):
+    import torch
+    m, k, n = 512, 256, 384
+    a, b, corr, composite, _ = conv_case(m, k, n, 5)
+    packed = ctx.pack_i8_b(b, k, n)
+    torch.cuda.synchronize()
+    da, dc, dp = (torch.from_numpy(x).cuda() for x in (a, corr, composite))
+    out = torch.empty(m, n, dtype=torch.int8, device="cuda")
+    torch.cuda.synchronize()
+    ctx.int8_matmul_requant_per_channel_dev(da.data_ptr(), packed, m, dc.data_ptr(), dp.data_ptr(), 1.0,
+                                            out.data_ptr())
+    ctx.synchronize()
+    acc = oracle.int8_matmul(a, b, m, k, n)
+    want = oracle.requant_i8_per_channel(acc.ravel(), corr, composite, 1.0, n).reshape(m, n)
+    assert np.array_equal(out.cpu().numpy(), want)
+    packed.free()
+
+
+# ---- a zero point on B: exact, where the reference would leave its integer path -------------
+# (crates/yscv-onnx/src/runner/linear.rs:701-735 computes (a - a_zp)(b - b_zp) in fp32 then)
+
+@pytest.mark.parametrize("m,k,n,a_unsigned,a_zp,b_zp", [(3, 8, 3, False, 0, 5), (64, 1024, 1024, True, 128, -3),
+                                                        (130, 200, 72, True, 7, 11), (257, 333, 65, False, -9, -128),
+                                                        (512, 2048, 512, True, 255, 127)])
+def test_matmul_integer_with_b_zero_point(ctx, oracle, m, k, n, a_unsigned, a_zp, b_zp):
+    if a_unsigned:
+        a = synth.uniform_int(9, 0, m * k, 0, 255).astype(np.uint8)
+    else:
+        a = synth.uniform_int(9, 0, m * k, -128, 127).astype(np.int8)
+    b = synth.uniform_int(9, 1, k * n, -128, 127).astype(np.int8)
+    packed = ctx.pack_i8_b(b, k, n)
+    packed.set_zero_point(b_zp)
+    want = ((a.astype(np.int64).reshape(m, k) - a_zp) @ (b.astype(np.int64).reshape(k, n) - b_zp))
+    assert np.abs(want).max() < 2**31
+    got = ctx.matmul_integer(a, packed, m, a_zp=a_zp)
+    assert np.array_equal(got.astype(np.int64), want), ctx.last_kernel()
+    # the float-typed MatMulInteger of the runner agrees wherever fp32 is exact
+    if np.abs(want).max() < 2**24 and m * k * n < 2**22:
+        ref = oracle.runner_matmul_integer(a.astype(np.float32), b.astype(np.float32), m, k, n, float(a_zp), float(b_zp))
+        assert np.array_equal(ref.astype(np.int64), want)
+    # QLinearMatMul on top of it: exact accumulator, then the requant contract
+    comp = float(np.float32(0.4) / np.float32(max(1.0, np.abs(want).max() / 100.0)))
+    rq = ctx.requant(comp, 128.0, 0, 255, a_unsigned=a_unsigned, a_zp=a_zp)
+    got_q = ctx.qlinear_matmul(a, packed, m, rq)
+    want_q = oracle.requant_range(want.astype(np.int32), comp, 128.0, 0, 255).astype(np.uint8)
+    assert np.array_equal(got_q, want_q)
+    packed.set_zero_point(0)
+    assert np.array_equal(ctx.matmul_integer(a, packed, m, a_zp=a_zp).astype(np.int64),
+                          (a.astype(np.int64).reshape(m, k) - a_zp) @ b.astype(np.int64).reshape(k, n))
+    assert ctx.device_status() == 0
+    packed.free()

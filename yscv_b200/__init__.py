@@ -11,6 +11,8 @@ from .lib import (  # noqa: F401
     Requant,
     Int4Weight,
     YscvCudaError,
+    DecodePlan,
+    int4_from_matmulnbits,
     load_library,
     library_path,
 )

@@ -174,6 +174,7 @@ void yscv_cuda_ctx_destroy(yscv_cuda_ctx *ctx) {
     ctx->out1.release();
     ctx->scratch.release();
     ctx->scratch_attn.release();
+    ctx->rowsum.release();
     if (ctx->d_status) cudaFree(ctx->d_status);
     for (auto &ev : ctx->prof_events) {
         cudaEventDestroy(ev.first);
@@ -262,6 +263,20 @@ int yscv_cuda_packed_int4_gemv(yscv_cuda_ctx *ctx, const uint8_t *weight_packed,
                                size_t m_w, size_t k, size_t group_size) {
     return yscv_cuda_packed_int4_gemm(ctx, weight_packed, scales, activation, output, 1, m_w, k,
                                       group_size);
+}
+
+int yscv_cuda_int4_from_matmulnbits_dev(yscv_cuda_ctx *ctx, const uint8_t *d_src, uint8_t *d_dst,
+                                        size_t bytes) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    if (bytes && (!d_src || !d_dst)) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    return int4_from_matmulnbits(ctx, d_src, d_dst, bytes);
+}
+
+int yscv_cuda_int4_from_matmulnbits(const uint8_t *src, uint8_t *dst, size_t bytes) {
+    if (bytes && (!src || !dst)) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    for (size_t i = 0; i < bytes; ++i) dst[i] = (uint8_t)(src[i] ^ 0x88u);
+    return YSCV_CUDA_OK;
 }
 
 int yscv_cuda_pack_int4_dev(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w, size_t k,
@@ -456,6 +471,14 @@ void yscv_cuda_i8b_free(yscv_cuda_i8b *b) {
     delete b;
 }
 
+int yscv_cuda_i8b_set_zero_point(yscv_cuda_i8b *b, int32_t b_zero_point) {
+    if (!b) return fail(YSCV_CUDA_ERR_BAD_ARG, "null handle");
+    if (b_zero_point < -128 || b_zero_point > 127)
+        return fail(YSCV_CUDA_ERR_BAD_ARG, "b_zero_point %d is not an int8 value", (int)b_zero_point);
+    b->b_zp = (int)b_zero_point;
+    return YSCV_CUDA_OK;
+}
+
 size_t yscv_cuda_i8b_k(const yscv_cuda_i8b *b) { return b ? b->k : 0; }
 size_t yscv_cuda_i8b_n(const yscv_cuda_i8b *b) { return b ? b->n : 0; }
 
@@ -530,6 +553,71 @@ int yscv_cuda_qlinear_matmul(yscv_cuda_ctx *ctx, const void *a, const yscv_cuda_
                              const yscv_cuda_requant *rq, void *out) {
     if (!rq) return fail(YSCV_CUDA_ERR_BAD_ARG, "requant parameters are null");
     return i8_gemm_host(ctx, a, b, m, out, 1, 0, 0, rq);
+}
+
+// ---- int8 GEMM + the i8 requant epilogues of the convolution path ----
+
+static int i8_requant_i8_dev(yscv_cuda_ctx *ctx, const int8_t *d_a, const yscv_cuda_i8b *b, size_t m,
+                             const int32_t *d_corr, const float *d_comp_pc, float composite, float y_zp,
+                             int relu, int8_t *d_out) {
+    if (!ctx || !b) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (!d_a || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (m == 0) return YSCV_CUDA_OK;
+    if (m >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "dimension too large");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    return int8_gemm(ctx, d_a, b, m, d_out, 0, 0, 1, composite, y_zp, -128, 127, 0, d_corr, d_comp_pc, relu);
+}
+
+int yscv_cuda_int8_matmul_requant_per_channel_dev(yscv_cuda_ctx *ctx, const int8_t *d_a,
+                                                  const yscv_cuda_i8b *b, size_t m, const int32_t *d_corr,
+                                                  const float *d_composite, float y_zero_point,
+                                                  int8_t *d_out) {
+    if (!d_corr || !d_composite) return fail(YSCV_CUDA_ERR_BAD_ARG, "null per-channel vector");
+    return i8_requant_i8_dev(ctx, d_a, b, m, d_corr, d_composite, 0.0f, y_zero_point, 0, d_out);
+}
+
+int yscv_cuda_int8_matmul_requant_i8_dev(yscv_cuda_ctx *ctx, const int8_t *d_a, const yscv_cuda_i8b *b,
+                                         size_t m, const int32_t *d_bias, float composite,
+                                         float y_zero_point, int relu, int8_t *d_out) {
+    return i8_requant_i8_dev(ctx, d_a, b, m, d_bias, nullptr, composite, y_zero_point, relu, d_out);
+}
+
+// host operands: A, the per-channel vectors and the output are staged through the context
+static int i8_requant_i8_host(yscv_cuda_ctx *ctx, const int8_t *a, const yscv_cuda_i8b *b, size_t m,
+                              const int32_t *corr, const float *comp_pc, float composite, float y_zp,
+                              int relu, int8_t *out) {
+    if (!ctx || !b) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (!a || !out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (m == 0) return YSCV_CUDA_OK;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    const size_t ab = m * b->k, ob = m * b->n, vb = b->n * 4;
+    int rc;
+    if ((rc = ctx->in0.reserve(ab)) || (rc = ctx->out0.reserve(ob)) || (rc = ctx->in1.reserve(vb)) ||
+        (rc = ctx->in2.reserve(vb)))
+        return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in0.ptr, a, ab, cudaMemcpyHostToDevice, ctx->stream));
+    if (corr) YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in1.ptr, corr, vb, cudaMemcpyHostToDevice, ctx->stream));
+    if (comp_pc) YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in2.ptr, comp_pc, vb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = i8_requant_i8_dev(ctx, (const int8_t *)ctx->in0.ptr, b, m, corr ? (const int32_t *)ctx->in1.ptr : nullptr,
+                           comp_pc ? (const float *)ctx->in2.ptr : nullptr, composite, y_zp, relu,
+                           (int8_t *)ctx->out0.ptr);
+    if (rc) return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(out, ctx->out0.ptr, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_int8_matmul_requant_per_channel(yscv_cuda_ctx *ctx, const int8_t *a, const yscv_cuda_i8b *b,
+                                              size_t m, const int32_t *corr, const float *composite,
+                                              float y_zero_point, int8_t *out) {
+    if (!corr || !composite) return fail(YSCV_CUDA_ERR_BAD_ARG, "null per-channel vector");
+    return i8_requant_i8_host(ctx, a, b, m, corr, composite, 0.0f, y_zero_point, 0, out);
+}
+
+int yscv_cuda_int8_matmul_requant_i8(yscv_cuda_ctx *ctx, const int8_t *a, const yscv_cuda_i8b *b, size_t m,
+                                     const int32_t *bias, float composite, float y_zero_point, int relu,
+                                     int8_t *out) {
+    return i8_requant_i8_host(ctx, a, b, m, bias, nullptr, composite, y_zero_point, relu, out);
 }
 
 int yscv_cuda_matmul_integer_dev(yscv_cuda_ctx *ctx, const void *d_a, int a_is_unsigned,

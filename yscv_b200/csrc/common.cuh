@@ -91,6 +91,7 @@ struct yscv_cuda_ctx {
     // scratch for kernels that need global memory beyond their operands
     yscv::DeviceBuffer scratch;
     yscv::DeviceBuffer scratch_attn;  // partial outputs of the split attention
+    yscv::DeviceBuffer rowsum;        // row sums of A (int8 GEMM with a zero point on B)
 };
 
 struct yscv_cuda_int4_weight {
@@ -108,4 +109,5 @@ struct yscv_cuda_i8b {
     int32_t *d_colsum = nullptr;
     size_t k = 0, n = 0, kp = 0;
     int device = 0;
+    int b_zp = 0;  // zero point of B (yscv_cuda_i8b_set_zero_point)
 };

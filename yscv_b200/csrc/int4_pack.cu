@@ -56,4 +56,22 @@ int pack_int4(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w, size_t k, 
     return YSCV_CUDA_OK;
 }
 
+// MatMulNBits (4 bits, zero point 8) bytes -> two's-complement nibbles: every nibble q_u in
+// [0,15] stands for q_u - 8, whose two's-complement nibble is q_u ^ 8.
+__global__ void nbits_xor_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, size_t bytes) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < bytes; i += stride)
+        dst[i] = src[i] ^ 0x88u;
+}
+
+int int4_from_matmulnbits(yscv_cuda_ctx *ctx, const uint8_t *d_src, uint8_t *d_dst, size_t bytes) {
+    if (bytes == 0) return YSCV_CUDA_OK;
+    const size_t want = (bytes + 255) / 256;
+    const int blocks = (int)(want < (size_t)(32 * ctx->sm_count) ? want : (size_t)(32 * ctx->sm_count));
+    nbits_xor_kernel<<<blocks, 256, 0, ctx->stream>>>(d_src, d_dst, bytes);
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    return YSCV_CUDA_OK;
+}
+
 }  // namespace yscv

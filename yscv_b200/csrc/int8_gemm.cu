@@ -47,6 +47,17 @@ struct G8Params {
     int qmin, qmax;
     int round_mode;         // 0: ties to even, 1: half away from zero
     long long ldc;          // elements per output row
+    // requantised output only, all optional: corr[n] is added to the accumulator (wrapping, as
+    // the reference's per-channel requant does with bias - x_zp * colsum), comp_pc[n] replaces
+    // the scalar composite, relu clamps negative outputs to zero after the saturation
+    const int32_t *corr;
+    const float *comp_pc;
+    int relu;
+    // zero point of B: (a - a_zp)(b - b_zp) summed over k = acc - a_zp * colsum[n]
+    //                  - b_zp * rowsum[m] + k_true * a_zp * b_zp, all modulo 2^32
+    int b_zp;
+    const int32_t *rowsum;  // row sums of A over k (only when b_zp != 0)
+    int k_true;
 };
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -207,6 +218,11 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             tc_fence_after();
             const int row = mb * G8_BM + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)abuf * BN;
+            // what the zero point of B adds to every element of this row
+            int row_term = 0;
+            if (p.b_zp != 0 && row < p.M)
+                row_term = (int)((uint32_t)p.k_true * (uint32_t)p.a_zp * (uint32_t)p.b_zp -
+                                 (uint32_t)p.b_zp * (uint32_t)__ldg(p.rowsum + row));
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -219,16 +235,16 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) {
                                 int4 v;
-                                v.x = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j);
-                                v.y = (int)r[j + 1] - p.a_zp * __ldg(colsum + col0 + j + 1);
-                                v.z = (int)r[j + 2] - p.a_zp * __ldg(colsum + col0 + j + 2);
-                                v.w = (int)r[j + 3] - p.a_zp * __ldg(colsum + col0 + j + 3);
+                                v.x = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
+                                v.y = (int)r[j + 1] - p.a_zp * __ldg(colsum + col0 + j + 1) + row_term;
+                                v.z = (int)r[j + 2] - p.a_zp * __ldg(colsum + col0 + j + 2) + row_term;
+                                v.w = (int)r[j + 3] - p.a_zp * __ldg(colsum + col0 + j + 3) + row_term;
                                 *reinterpret_cast<int4 *>(o + j) = v;
                             }
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N) o[j] = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j);
+                                if (col0 + j < p.N) o[j] = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
                         }
                     } else {
                         uint8_t *o = reinterpret_cast<uint8_t *>(out) + (size_t)row * p.ldc + col0;
@@ -236,11 +252,15 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int cc = (col0 + j < p.N) ? col0 + j : col0;
-                            const int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc);
+                            int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc) + row_term;
+                            float comp = p.composite;
+                            if (p.corr) acc = (int)((uint32_t)acc + (uint32_t)__ldg(p.corr + cc));
+                            if (p.comp_pc) comp = __ldg(p.comp_pc + cc);
                             // separate multiply and add: the CPU kernel does not fuse them
-                            const float v = __fadd_rn(__fmul_rn((float)acc, p.composite), p.y_zp);
+                            const float v = __fadd_rn(__fmul_rn((float)acc, comp), p.y_zp);
                             const float rr = p.round_mode ? roundf(v) : rintf(v);
-                            const int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
+                            int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
+                            if (p.relu && qv < 0) qv = 0;
                             if ((j & 3) == 0) packed[j >> 2] = 0;
                             packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
                         }
@@ -292,6 +312,20 @@ pack_i8_b_kernel(const int8_t *__restrict__ b, int8_t *__restrict__ bt, int32_t 
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if (lane == 0) colsum[n] = s;
+}
+
+// row sums of A over k (one warp per row), the bytes read as u8 or i8
+__global__ void __launch_bounds__(256)
+rowsum_a_kernel(const uint8_t *__restrict__ a, int32_t *__restrict__ rowsum, int M, int K, int is_unsigned) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const uint8_t *r = a + (size_t)row * K;
+    int s = 0;
+    for (int k = lane; k < K; k += 32) s += is_unsigned ? (int)r[k] : (int)(int8_t)r[k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) rowsum[row] = s;
 }
 
 // pads A [M][K] to [M][Kp] when K is not a multiple of 16 (TMA row pitch)
@@ -355,8 +389,11 @@ static int launch_g8(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const yscv
 // d_a: [m][k] bytes (i8, or u8 when a_unsigned). mode 0: d_out int32 [m][n]; mode 1: bytes [m][n].
 int int8_gemm(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_t m, void *d_out,
               int a_unsigned, int a_zp, int mode, float composite, float y_zp, int qmin, int qmax,
-              int round_mode) {
+              int round_mode, const int32_t *d_corr, const float *d_comp_pc, int relu) {
     G8Params p = {};
+    p.corr = d_corr;
+    p.comp_pc = d_comp_pc;
+    p.relu = relu;
     p.a_unsigned = a_unsigned;
     p.a_zp = a_zp;
     p.mode = mode;
@@ -366,6 +403,18 @@ int int8_gemm(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_
     p.qmax = qmax;
     p.round_mode = round_mode;
     p.ldc = (long long)b->n;
+    p.b_zp = b->b_zp;
+    p.k_true = (int)b->k;
+    if (b->b_zp != 0) {
+        int rc = ctx->rowsum.reserve(m * sizeof(int32_t));
+        if (rc) return rc;
+        rowsum_a_kernel<<<(unsigned)((m + 7) / 8), 256, 0, ctx->stream>>>(
+            reinterpret_cast<const uint8_t *>(d_a), reinterpret_cast<int32_t *>(ctx->rowsum.ptr), (int)m,
+            (int)b->k, a_unsigned);
+        YSCV_CUDA_TRY(cudaGetLastError());
+        ctx->launches++;
+        p.rowsum = reinterpret_cast<const int32_t *>(ctx->rowsum.ptr);
+    }
     const void *a = d_a;
     size_t lda = b->k;
     if (b->k != b->kp || (reinterpret_cast<uintptr_t>(d_a) & 15)) {

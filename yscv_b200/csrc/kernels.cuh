@@ -26,11 +26,14 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
 int pack_int4(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w, size_t k, size_t gs,
               uint8_t *d_packed, float *d_scales);
 
+int int4_from_matmulnbits(yscv_cuda_ctx *ctx, const uint8_t *d_src, uint8_t *d_dst, size_t bytes);
+
 // int8_gemm.cu
 int pack_i8_b(yscv_cuda_ctx *ctx, const int8_t *d_b, size_t k, size_t n, int8_t *d_bt,
               int32_t *d_colsum, size_t kp);
 int int8_gemm(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_t m, void *d_out,
               int a_unsigned, int a_zp, int mode, float composite, float y_zp, int qmin, int qmax,
-              int round_mode);
+              int round_mode, const int32_t *d_corr = nullptr, const float *d_comp_pc = nullptr,
+              int relu = 0);
 
 }  // namespace yscv

@@ -73,6 +73,13 @@ SIGNATURES = {
     "yscv_cuda_f32_matmul_dev": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp]),
     "yscv_cuda_argmax_last_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
     "yscv_cuda_advance_pos_dev": (C.c_int, [_vp, _vp, C.c_int]),
+    "yscv_cuda_i8b_set_zero_point": (C.c_int, [_vp, C.c_int32]),
+    "yscv_cuda_int4_from_matmulnbits": (C.c_int, [_vp, _vp, _sz]),
+    "yscv_cuda_int4_from_matmulnbits_dev": (C.c_int, [_vp, _vp, _vp, _sz]),
+    "yscv_cuda_int8_matmul_requant_per_channel_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, C.c_float, _vp]),
+    "yscv_cuda_int8_matmul_requant_per_channel": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, C.c_float, _vp]),
+    "yscv_cuda_int8_matmul_requant_i8_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, C.c_float, C.c_float, C.c_int, _vp]),
+    "yscv_cuda_int8_matmul_requant_i8": (C.c_int, [_vp, _vp, _vp, _sz, _vp, C.c_float, C.c_float, C.c_int, _vp]),
     "yscv_cuda_decode_plan_create": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, C.c_float, C.c_float,
                                                C.POINTER(_vp)]),
     "yscv_cuda_decode_plan_step_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp]),
@@ -157,6 +164,10 @@ class I8B:
         self.k = int(lib.yscv_cuda_i8b_k(handle))
         self.n = int(lib.yscv_cuda_i8b_n(handle))
 
+    def set_zero_point(self, b_zp: int):
+        """b_zero_point of MatMulInteger / QLinearMatMul for this weight (default 0)."""
+        _check(load_library().yscv_cuda_i8b_set_zero_point(self.handle, int(b_zp)))
+
     def free(self):
         if self.handle:
             load_library().yscv_cuda_i8b_free(self.handle)
@@ -167,6 +178,14 @@ class I8B:
             self.free()
         except Exception:
             pass
+
+
+def int4_from_matmulnbits(src) -> np.ndarray:
+    """MatMulNBits bytes (unsigned nibbles, zero point 8) -> two's-complement nibbles; host only."""
+    a = _host(src, np.uint8)
+    out = np.empty_like(a)
+    _check(load_library().yscv_cuda_int4_from_matmulnbits(_ptr(a), _ptr(out), a.size))
+    return out
 
 
 class DecodePlan:
@@ -335,6 +354,33 @@ class Context:
     def qlinear_matmul_dev(self, d_a: int, b: "I8B", m, rq: "Requant", d_out: int):
         _check(self.lib.yscv_cuda_qlinear_matmul_dev(self.handle, _vp(d_a), b.handle, m, C.byref(rq), _vp(d_out)))
 
+    def int8_matmul_requant_per_channel(self, a, b: "I8B", m, corr, composite, y_zp):
+        """i8 A [m,k] host -> i8 [m,n]; corr int32 [n], composite f32 [n]."""
+        a8, cr, cp = _host(a, np.int8), _host(corr, np.int32), _host(composite, np.float32)
+        out = np.empty((m, b.n), dtype=np.int8)
+        _check(self.lib.yscv_cuda_int8_matmul_requant_per_channel(self.handle, _ptr(a8), b.handle, m, _ptr(cr),
+                                                                   _ptr(cp), y_zp, _ptr(out)))
+        return out
+
+    def int8_matmul_requant_per_channel_dev(self, d_a: int, b: "I8B", m, d_corr: int, d_composite: int, y_zp,
+                                            d_out: int):
+        _check(self.lib.yscv_cuda_int8_matmul_requant_per_channel_dev(self.handle, _vp(d_a), b.handle, m,
+                                                                       _vp(d_corr), _vp(d_composite), y_zp,
+                                                                       _vp(d_out)))
+
+    def int8_matmul_requant_i8(self, a, b: "I8B", m, bias, composite, y_zp, relu=False):
+        a8 = _host(a, np.int8)
+        bs = None if bias is None else _host(bias, np.int32)
+        out = np.empty((m, b.n), dtype=np.int8)
+        _check(self.lib.yscv_cuda_int8_matmul_requant_i8(self.handle, _ptr(a8), b.handle, m,
+                                                          None if bs is None else _ptr(bs), composite, y_zp,
+                                                          int(relu), _ptr(out)))
+        return out
+
+    def int8_matmul_requant_i8_dev(self, d_a: int, b: "I8B", m, d_bias, composite, y_zp, relu, d_out: int):
+        _check(self.lib.yscv_cuda_int8_matmul_requant_i8_dev(self.handle, _vp(d_a), b.handle, m, _vp(d_bias or 0),
+                                                              composite, y_zp, int(relu), _vp(d_out)))
+
     def matmul_integer(self, a, b: "I8B", m, a_zp=0):
         a = np.ascontiguousarray(a)
         assert a.dtype in (np.uint8, np.int8)
@@ -396,6 +442,9 @@ class Context:
         _check(self.lib.yscv_cuda_decode_plan_create(self.handle, C.cast(arr, _vp), len(layers), hidden, inter, n_q,
                                                      n_kv, d_head, max_seq, eps, rope_theta, C.byref(h)))
         return DecodePlan(self, h.value)
+
+    def int4_from_matmulnbits_dev(self, d_src: int, d_dst: int, nbytes: int):
+        _check(self.lib.yscv_cuda_int4_from_matmulnbits_dev(self.handle, _vp(d_src), _vp(d_dst), nbytes))
 
     def pack_int4_dev(self, d_weights: int, m_w, k, group_size, d_packed: int, d_scales: int):
         _check(self.lib.yscv_cuda_pack_int4_dev(self.handle, _vp(d_weights), m_w, k, group_size,
