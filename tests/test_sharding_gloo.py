@@ -43,7 +43,23 @@ def _worker(rank, world, port, q):
         t = torch.from_numpy(part.copy())
         dist.all_reduce(t)
         err = float(np.max(np.abs(t.numpy() - full)) / np.max(np.abs(full)))
-        q.put((rank, col_ok, err))
+        # int8 QLinearMatMul, N-sharded: own columns of B and of the per-channel vectors,
+        # all-gather the requantised bytes
+        mi, ki, ni = 5, 48, 32
+        a8 = synth.uniform_int(9, 2, mi * ki, -128, 127).astype(np.int8)
+        b8 = synth.uniform_int(9, 3, ki * ni, -127, 127).astype(np.int8).reshape(ki, ni)
+        corr = synth.uniform_int(9, 4, ni, -500, 500).astype(np.int32)
+        comp = (0.001 * (1 + np.arange(ni) % 3)).astype(np.float32)
+        full_q = o.requant_i8_per_channel(o.int8_matmul(a8, b8, mi, ki, ni).ravel(), corr, comp, 1.0, ni).reshape(mi, ni)
+        bs = np.ascontiguousarray(sharding.shard_i8_b_cols(b8, rank, world))
+        acc = o.int8_matmul(a8, bs, mi, ki, ni // world)
+        mine = o.requant_i8_per_channel(acc.ravel(), np.ascontiguousarray(sharding.shard_channel_vector(corr, rank, world)),
+                                        np.ascontiguousarray(sharding.shard_channel_vector(comp, rank, world)), 1.0,
+                                        ni // world).reshape(mi, ni // world)
+        parts = [torch.empty(mi, ni // world, dtype=torch.int8) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(mine))
+        i8_ok = np.array_equal(sharding.assemble_cols(torch.stack(parts)).numpy(), full_q)
+        q.put((rank, col_ok and i8_ok, err))
     finally:
         dist.destroy_process_group()
 

@@ -65,3 +65,20 @@ def test_tp2_matches_tp1(tmp_path):
     assert res["status"] == 0
     assert res["rel"] < 1e-5, res       # fp32 partial sums in a different order
     assert res["tokens_equal"], res
+
+
+def test_int8_n_shard_matches_unsharded():
+    """QLinearMatMul with the output channels split over 2 GPUs: the all-gathered bytes equal
+    the single-GPU result bit for bit."""
+    import json
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29613", "-m", "yscv_b200.int8_shard_bench",
+           "--rows", "512", "--inner", "1024", "--cols", "1536", "--iters", "5"]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240, cwd=str(ROOT))
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    res = json.loads([l for l in proc.stdout.splitlines() if l.startswith("{")][-1])
+    assert res["bit_exact_vs_unsharded"] and res["device_status"] == 0 and res["gpus"] == 2

@@ -10,6 +10,11 @@ channel, crates/yscv-kernels/src/ops/int4_matmul.rs:12-18), so
   every row, k0 = r*k/G; needs (k/G) % group == 0 so that no group straddles two ranks.
   Every rank produces an fp32 partial [m][n]; the partials are summed (all-reduce).
 
+int8 QLinearMatMul / MatMulInteger (B [k][n] row-major, per-tensor or per-channel requant):
+split the output channels; rank r owns the columns [r*n/G, (r+1)*n/G) of B and the matching
+slice of every per-channel vector, A is replicated, the requant is per element, so the
+ranks' byte outputs [m][n/G] are independent and are all-gathered.
+
 Works on numpy arrays and torch tensors alike (plain slicing).
 """
 from __future__ import annotations
@@ -46,3 +51,26 @@ def shard_activation_cols(act, group: int, rank: int, world: int):
     """The K slice of the activations [m][k] that goes with shard_cols."""
     k0, k1 = col_range(act.shape[-1], group, rank, world)
     return act[..., k0:k1]
+
+
+def shard_i8_b_cols(b, rank: int, world: int):
+    """N-shard of an int8 weight b [k][n]: the rank's output channels (a strided view)."""
+    n0, n1 = row_range(b.shape[1], rank, world)
+    return b[:, n0:n1]
+
+
+def shard_channel_vector(v, rank: int, world: int):
+    """The rank's slice of a per-output-channel vector (composite, correction, bias)."""
+    n0, n1 = row_range(v.shape[0], rank, world)
+    return v[n0:n1]
+
+
+def assemble_cols(parts):
+    """[G][m][n/G] gathered outputs -> [m][n] (torch tensors or numpy arrays)."""
+    if hasattr(parts, "permute"):
+        g, m, w = parts.shape
+        return parts.permute(1, 0, 2).reshape(m, g * w)
+    import numpy as np
+    parts = np.asarray(parts)
+    g, m, w = parts.shape
+    return parts.transpose(1, 0, 2).reshape(m, g * w)
