@@ -143,6 +143,33 @@ def time_cpu(oracle, copies, m, threads, steps, warmup, max_copies=None):
     return algorithmic_bytes(m) * calls / dt / 1e9, dt / steps * 1e3, calls
 
 
+def cpu_int8_baselines(oracle, threads):
+    """The reference's int8 GEMM (AVX-512-VNNI restatement, prepacked B) on the host cores:
+    BASELINE configs[0] in full and a bounded row sample of configs[2]; one thread (what the
+    reference kernel does) and rows split over `threads` threads."""
+    import numpy as np
+    out = {}
+    rng = np.random.default_rng(2)
+    for name, (m, k, n), sample_m in (("matmul_integer_64x1024x1024", (64, 1024, 1024), 64),
+                                      ("qlinear_matmul_2048x4096x4096", (2048, 4096, 4096), 256)):
+        a = rng.integers(-128, 128, size=(sample_m, k), dtype=np.int8)
+        b = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+        bt = oracle.transpose_b_i8(b, k, n)
+        ops = 2.0 * sample_m * k * n
+        res = {"sample": f"{sample_m} of {m} rows of A, prepacked B, i32 accumulate (the requant pass is not timed)"}
+        for label, t, rows, reps in (("threads", threads, sample_m, 3), ("one_thread", 1, min(sample_m, 64), 2)):
+            aa = np.ascontiguousarray(a[:rows])
+            oracle.int8_matmul_prepacked(aa, bt, rows, k, n, simd=True, threads=t)
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                oracle.int8_matmul_prepacked(aa, bt, rows, k, n, simd=True, threads=t)
+            dt = (time.perf_counter() - t0) / reps
+            res[f"tops_{label}"] = 2.0 * rows * k * n / dt / 1e12
+        res["cores"] = threads
+        out[name] = res
+    return out
+
+
 def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
@@ -355,6 +382,9 @@ def run_cuda(args):
     other = None
     if world == 1 and not args.no_extras:
         other = extra_metrics(ctx, stream, dev)
+        if cpu is not None:
+            for name, res in cpu_int8_baselines(oracle, threads).items():
+                other[name]["cpu_baseline"] = res
 
     if rank == 0:
         line = {

@@ -4,7 +4,7 @@ same kind plus the BASELINE configurations, a parity gate before every timing, a
 same derived figures (weight bandwidth N*K/2 / t for the GEMV, kernel_bench.rs:317-324;
 2*M*N*K / t for the GEMMs, :389-396), median and min over the timed iterations (:54-69).
 
-    python -m yscv_b200.kernel_bench [--section int8|int4_gemv|int4_gemm] [--only SUBSTR]
+    python -m yscv_b200.kernel_bench [--section int8|conv1x1|int4_gemv|int4_gemm] [--only SUBSTR]
                                      [--iters N] [--copies C]
 
 The parity gate recomputes a random sample of outputs on the GPU in float64 from the raw
@@ -33,6 +33,16 @@ INT8_SHAPES = [
     ("M-sweep 256x2048x2048", 256, 2048, 2048),
     ("square 4096x4096x4096", 4096, 4096, 4096),
     ("square 8192x8192x8192", 8192, 8192, 8192),
+]
+
+# pointwise (1x1) QLinearConv as a GEMM over NHWC pixels: (label, pixels, c_in, c_out)
+CONV1X1_SHAPES = [
+    ("56x56  64->256", 3136, 64, 256),
+    ("28x28 128->512", 784, 128, 512),
+    ("14x14 256->1024", 196, 256, 1024),
+    ("7x7  512->2048", 49, 512, 2048),
+    ("8 x 56x56 64->256", 25088, 64, 256),
+    ("8 x 14x14 1024->256", 1568, 1024, 256),
 ]
 
 INT4_GEMV_SHAPES = [  # (label, N, K); timed at M = 1, 4, 16
@@ -105,6 +115,37 @@ def bench_int8(ctx, stream, dev, iters, only):
         ops = 2.0 * m * k * n
         print(f"  {label:46s} i32: med {med:9.2f} us min {mn:9.2f} us {ops / mn / 1e6:8.1f} TOPS | "
               f"requant-u8: min {mnq:9.2f} us {ops / mnq / 1e6:8.1f} TOPS  [{ctx.last_kernel()}]  parity: bit-exact")
+        pk.free()
+
+
+def bench_conv1x1(ctx, stream, dev, iters, only):
+    print("\n== INT8 pointwise QLinearConv (GEMM + per-channel i8 requant in the epilogue) ==")
+    for label, m, k, n in CONV1X1_SHAPES:
+        if only and only not in label:
+            continue
+        with torch.cuda.stream(stream):
+            g = torch.Generator(device=dev)
+            g.manual_seed(0xC0)
+            a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev, generator=g)
+            b = torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev, generator=g)
+            corr = torch.randint(-4000, 4000, (n,), dtype=torch.int32, device=dev, generator=g)
+            comp = (0.0005 + 0.0001 * (torch.arange(n, device=dev) % 7)).float()
+            pk = ctx.pack_i8_b_dev(b.data_ptr(), k, n)
+            out = torch.empty(m, n, dtype=torch.int8, device=dev)
+            ctx.int8_matmul_requant_per_channel_dev(a.data_ptr(), pk, m, corr.data_ptr(), comp.data_ptr(), -2.0,
+                                                    out.data_ptr())
+            # gate: exact accumulator (float64 is exact here), then the requant contract in fp32
+            acc = (a.double() @ b.double()).to(torch.int32) + corr
+            want = torch.clamp(torch.round(acc.float() * comp + (-2.0)), -128, 127).to(torch.int8)
+            bad = int((out != want).sum())
+        stream.synchronize()
+        assert bad == 0, f"{label}: {bad} outputs differ"
+        med, mn = time_us(stream, lambda: ctx.int8_matmul_requant_per_channel_dev(
+            a.data_ptr(), pk, m, corr.data_ptr(), comp.data_ptr(), -2.0, out.data_ptr()), iters)
+        ops = 2.0 * m * k * n
+        byts = m * k + k * n + m * n
+        print(f"  {label:22s} [{m}x{k}x{n}]: med {med:8.2f} us min {mn:8.2f} us {ops / mn / 1e6:8.1f} TOPS "
+              f"{byts / mn / 1e3:7.1f} GB/s  [{ctx.last_kernel()}]  parity: bit-exact")
         pk.free()
 
 
@@ -186,7 +227,7 @@ def bench_int4_gemm(ctx, stream, dev, iters, only):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--section", choices=["int8", "int4_gemv", "int4_gemm"], default=None)
+    ap.add_argument("--section", choices=["int8", "conv1x1", "int4_gemv", "int4_gemm"], default=None)
     ap.add_argument("--only", default=None, help="substring of the shape label")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--copies", type=int, default=16)
@@ -196,6 +237,8 @@ def main():
     ctx = Context(0, stream=stream.cuda_stream)
     if a.section in (None, "int8"):
         bench_int8(ctx, stream, dev, a.iters, a.only)
+    if a.section in (None, "conv1x1"):
+        bench_conv1x1(ctx, stream, dev, a.iters, a.only)
     if a.section in (None, "int4_gemv"):
         bench_int4_gemv(ctx, stream, dev, a.iters, a.only, a.copies)
     if a.section in (None, "int4_gemm"):
