@@ -250,6 +250,40 @@ def test_fused_step_logits_match_operator_chain(tctx):
     assert ctx.device_status() == 0
 
 
+def test_fused_step_long_context_and_limits(tctx):
+    """More than 128 keys per attention split (the loops past the prefetched rows), the last
+    cache slot, and shapes the plan refuses."""
+    import torch
+    import yscv_b200
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=2, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
+    P, steps = 700, 4   # 148 // 8 -> 4 splits per head: 175+ keys each
+    prompt = dev(synth.uniform_int(33, 9, P, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    logs = []
+    for fused in (False, True):
+        dec = Int4Decoder(ctx, cfg, 1, P + steps, s, seed=14, fused_step=fused)   # the last step fills the cache
+        assert (dec.plan is not None) == fused
+        dec.prefill(prompt)
+        lg = []
+        for _ in range(steps):
+            with torch.cuda.stream(s):
+                out = dec.forward(dec.next_tokens, 1)
+            s.synchronize()
+            lg.append(out.cpu().numpy().copy())
+        logs.append(lg)
+        dec.close()
+    for a, b in zip(*logs):
+        assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
+    assert ctx.device_status() == 0
+    # K not a multiple of 512, fewer rows than SMs, too many heads: refused when the plan is built
+    for bad in (DecoderConfig(layers=1, hidden=768, mlp=1024, n_q=12, n_kv=4, head_dim=64, vocab=100),
+                DecoderConfig(layers=1, hidden=512, mlp=1024, n_q=2, n_kv=1, head_dim=32, vocab=100),
+                DecoderConfig(layers=1, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=100, group_size=64)):
+        dec = Int4Decoder(ctx, bad, 1, 32, s, seed=1)
+        assert dec.plan is None
+        dec.close()
+
+
 def test_tinyllama_shape_greedy_tokens(tctx, oracle):
     # BASELINE config 4 shape, seed 3; 4 of the 22 layers keep the CPU oracle in seconds,
     # the full depth runs in bench/decoder measurements

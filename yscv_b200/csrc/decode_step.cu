@@ -738,10 +738,13 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
             return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: layer %zu has a null pointer", l));
         for (int j = 0; j < 4; ++j) {
             if (!w[j]) return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: layer %zu has a null weight", l));
-            if (w[j]->m_w != want_n[j] || w[j]->k != want_k[j] || w[j]->group_size != 32)
+            if (w[j]->m_w != want_n[j] || w[j]->k != want_k[j])
                 return bail(fail(YSCV_CUDA_ERR_BAD_ARG,
-                                 "decode plan: layer %zu matrix %d is [%zu][%zu] group %zu, expected [%zu][%zu] group 32",
-                                 l, j, w[j]->m_w, w[j]->k, w[j]->group_size, want_n[j], want_k[j]));
+                                 "decode plan: layer %zu matrix %d is [%zu][%zu], expected [%zu][%zu]",
+                                 l, j, w[j]->m_w, w[j]->k, want_n[j], want_k[j]));
+            if (w[j]->group_size != 32)
+                return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: group size %zu (only 32)",
+                                 w[j]->group_size));
             const size_t n = w[j]->m_w, k = w[j]->k;
             const size_t rows_per_cta = (n + grid - 1) / grid;
             if (k % 512 != 0 || n < (size_t)grid || rows_per_cta > 128 ||
