@@ -25,6 +25,7 @@
 // per CTA and matrix, head_dim <= 128, the whole context of a head handled by one CTA.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -43,6 +44,7 @@ constexpr int DS_BAR_BYTES = 256;
 constexpr int DS_MAX_STAGES = 8;
 constexpr int DS_BLOB_BYTES = DS_GS * 4 * 4 * 16;  // digit blob of one stage (M = 1, columns form)
 constexpr int DS_SPIN_LIMIT = 1 << 21;
+constexpr int DS_DEFAULT_VARIANT = 7;  // pairing, sixteen slices, merge table; the relaxed poll measured slower
 
 // One int4 linear as the kernel sees it (array in global memory).
 struct alignas(64) StepMat {
@@ -72,6 +74,14 @@ struct StepParams {
     // CTA, K stages; kept here so that no thread waits on global memory to learn them
     int mat_n[4], mat_tiles[4], mat_ks[4];
     int mat_kps[4];  // K stages per ring slot: a matrix with few rows per CTA packs several
+    // gate/up pairing: a CTA owns the intermediate indices [i0, i1) and streams gate rows
+    // [i0, i1) and up rows [inter + i0, inter + i1) as the two halves of its slab, so that
+    // silu(gate) * up is formed in the store of that GEMV (gu then holds [inter] values)
+    int pair_gu;     // 0: gate_up rows split like any matrix, SwiGLU while staging the down GEMV
+    int gu_half_tiles;
+    int one_tile_16;  // 1: a one-tile slab is split over 16 K slices (all warps) instead of 8
+    int merge_table;  // 1: the split-merge weights go through a shared-memory table
+    int relaxed_poll; // 1: the barrier polls with relaxed loads and fences once
 };
 
 #ifdef YSCV_TRACE
@@ -128,6 +138,12 @@ __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int *p) {
     return v;
 }
 
+__device__ __forceinline__ unsigned int ld_relaxed_u32(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // Grid-wide barrier of the consumers. `epoch` counts the barriers of this launch (the same in
 // every thread). A CTA that waits longer than the limit raises the abort flag; from then on
 // every barrier of every CTA falls through, the kernel runs to its end and the host finds the
@@ -142,7 +158,7 @@ __device__ __forceinline__ void grid_barrier(const StepParams &p, unsigned int &
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(p.sync) : "memory");
         const unsigned int target = epoch * gridDim.x;
         int spins = 0;
-        while (ld_acquire_u32(&p.sync[0]) < target) {
+        while ((p.relaxed_poll ? ld_relaxed_u32(&p.sync[0]) : ld_acquire_u32(&p.sync[0])) < target) {
             ++spins;
             if ((spins & 63) == 0 && ld_acquire_u32(&p.sync[2]) != 0u) break;
             if (spins > DS_SPIN_LIMIT) {
@@ -151,6 +167,7 @@ __device__ __forceinline__ void grid_barrier(const StepParams &p, unsigned int &
                 break;
             }
         }
+        if (p.relaxed_poll) asm volatile("fence.acq_rel.gpu;\n" ::: "memory");
     }
     cons_sync();
 }
@@ -185,7 +202,10 @@ __device__ __forceinline__ void consume_matrix(const StepParams &p, const unsign
                                                uint32_t bar_full, uint32_t bar_empty, float *red,
                                                const unsigned char *dig, RingPos &c, int tiles,
                                                int k_stages, int kps, int r0, int r1, float *out,
-                                               bool accumulate, bool &dead) {
+                                               int store, bool &dead) {
+    // store: 0 out[row] = v; 1 out[row] += v; 2 the slab is gate tiles then up tiles of the
+    // intermediate indices [r0, r1): out[i] = silu(gate_i) * up_i
+    const bool accumulate = store == 1;
     constexpr int GS = DS_GS;
     constexpr int KSL = (16 / TP2 < GS) ? 16 / TP2 : GS;
     constexpr int GPW = GS / KSL;
@@ -277,7 +297,21 @@ __device__ __forceinline__ void consume_matrix(const StepParams &p, const unsign
     }
     cons_sync();
     // element (tile, half, gq): sum over the K slices and the thread pair t = 0, 1
-    if (tid < tiles * 16) {   // tiles <= 8: at most 128 rows, one per thread
+    if (store == 2) {
+        const int th = tiles / 2;
+        if (tid < th * 16) {
+            const int q8 = tid & 7, half = (tid >> 3) & 1, tl = tid >> 4;
+            float g = 0.0f, u = 0.0f;
+            for (int ks = 0; ks < KSL; ++ks) {
+                const float *pg = red + ((ks * tiles + tl) * 2 + half) * 32 + q8 * 4;
+                const float *pu = red + ((ks * tiles + tl + th) * 2 + half) * 32 + q8 * 4;
+                g += pg[0] + pg[1];
+                u += pu[0] + pu[1];
+            }
+            const float sg = 1.0f / (1.0f + expf(-g));
+            if (my_row < r1) out[my_row] = (g * sg) * u;
+        }
+    } else if (tid < tiles * 16) {   // tiles <= 8: at most 128 rows, one per thread
         const int q8 = tid & 7, half = (tid >> 3) & 1, tl = tid >> 4;
         float v = 0.0f;
         for (int ks = 0; ks < KSL; ++ks) {
@@ -463,6 +497,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     float *misc = act_s + p.act_floats;  // 32 floats
     float *rope_cs = misc + 32;          // [d_head/2] x {cos, sin} of this step's position
     float **cache_ptr = reinterpret_cast<float **>(rope_cs + p.d_head);  // [layers] x {k, v}
+    float *wtab = reinterpret_cast<float *>(cache_ptr + 2 * p.layers);   // [n_q][4] split-merge weights
     const int nmat = p.layers * 4;
 
     if (tid == DS_CONSUMERS) {
@@ -483,7 +518,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
             bool alive = true;
             for (int mi = 0; mi < nmat && alive; ++mi) {
                 const StepMat *m = p.mats + mi;
-                const int n = p.mat_n[mi & 3], tiles = p.mat_tiles[mi & 3], k_stages = p.mat_ks[mi & 3];
+                const bool paired = (mi & 3) == 2 && p.pair_gu;
+                const int n = paired ? p.inter : p.mat_n[mi & 3];
+                const int tiles = p.mat_tiles[mi & 3], k_stages = p.mat_ks[mi & 3];
                 const int r0 = (int)(((unsigned)n * blockIdx.x) / gridDim.x);
                 const int rb_rows = tiles * 16;
                 const int kps = p.mat_kps[mi & 3];
@@ -498,9 +535,20 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
                     for (int j = 0; j < nsub; ++j) {
                         const uint32_t st = smem_base + (uint32_t)slot * p.slot_bytes + (uint32_t)j * sub_bytes;
                         const int ks = ks0 + j;
-                        tma_load_2d(st, &m->tm_w, ks * (DS_GS * 16), r0, full);
-                        tma_load_2d(st + rb_rows * 128, &m->tm_w, ks * (DS_GS * 16) + 128, r0, full);
-                        tma_load_2d(st + rb_rows * 256, &m->tm_s, ks * DS_GS, r0, full);
+                        if (paired) {
+                            // two boxes of half the slab each: gate rows, then the matching up rows
+                            const int hr = p.gu_half_tiles * 16;
+                            for (int h = 0; h < 2; ++h) {
+                                const int row = h * p.inter + r0;
+                                tma_load_2d(st + h * hr * 128, &m->tm_w, ks * (DS_GS * 16), row, full);
+                                tma_load_2d(st + rb_rows * 128 + h * hr * 128, &m->tm_w, ks * (DS_GS * 16) + 128, row, full);
+                                tma_load_2d(st + rb_rows * 256 + h * hr * (DS_GS * 4), &m->tm_s, ks * DS_GS, row, full);
+                            }
+                        } else {
+                            tma_load_2d(st, &m->tm_w, ks * (DS_GS * 16), r0, full);
+                            tma_load_2d(st + rb_rows * 128, &m->tm_w, ks * (DS_GS * 16) + 128, r0, full);
+                            tma_load_2d(st + rb_rows * 256, &m->tm_s, ks * DS_GS, r0, full);
+                        }
                     }
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
@@ -518,15 +566,19 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     bool dead = false;
     const int H = p.hidden, I = p.inter;
 
-    auto gemv = [&](int mi, float *out, bool accumulate) {
-        const int n = p.mat_n[mi & 3], tiles = p.mat_tiles[mi & 3], k_stages = p.mat_ks[mi & 3];
-        const int kps = p.mat_kps[mi & 3];
-        const int r0 = (int)(((unsigned)n * blockIdx.x) / gridDim.x);
-        const int r1 = (int)(((unsigned)n * (blockIdx.x + 1)) / gridDim.x);
-        if (tiles <= 2)
-            consume_matrix<2>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, accumulate, dead);
+    auto gemv = [&](int mi, float *out, int store) {
+        const int j = mi & 3;
+        const int tiles = p.mat_tiles[j], k_stages = p.mat_ks[j], kps = p.mat_kps[j];
+        // rows of the matrix, or (paired gate/up) intermediate indices
+        const unsigned n = (j == 2 && p.pair_gu) ? (unsigned)p.inter : (unsigned)p.mat_n[j];
+        const int r0 = (int)((n * blockIdx.x) / gridDim.x);
+        const int r1 = (int)((n * (blockIdx.x + 1)) / gridDim.x);
+        if (tiles == 1 && p.one_tile_16)
+            consume_matrix<1>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, store, dead);
+        else if (tiles <= 2)
+            consume_matrix<2>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, store, dead);
         else
-            consume_matrix<8>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, accumulate, dead);
+            consume_matrix<8>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, store, dead);
     };
     // act_s = RMSNorm(x) * gamma
     auto stage_norm = [&](const float *gamma) {
@@ -591,7 +643,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         STRACE(ts + 1);
         quantize_activation(act_s, dig, H, false);
         STRACE(ts + 2);
-        gemv(4 * l + 0, p.qkv, false);
+        gemv(4 * l + 0, p.qkv, 0);
         STRACE(ts + 3);
         grid_barrier(p, epoch);
         STRACE(ts + 4);
@@ -604,34 +656,78 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         STRACE(ts + 6);
         // output projection, residual add in the store; its activation vector is the merge of
         // the attention splits (the usual max-rescaling of a split softmax)
+        if (p.merge_table) {
+            // per (head, split): weight exp(m - M) / L once, through shared memory
+            if (tid < p.n_q) {
+                const float *pp = p.attn + (size_t)tid * p.splits * (p.d_head + 2) + p.d_head;
+                float m[4], e[4];
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp) {
+                    const bool on = sp < p.splits;
+                    m[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2)) : -INFINITY;
+                    e[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + 1) : 0.0f;
+                }
+                float M = -INFINITY, L = 0.0f, w[4];
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp) M = fmaxf(M, m[sp]);
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp) {
+                    w[sp] = m[sp] > -INFINITY ? expf(m[sp] - M) : 0.0f;
+                    L = fmaf(w[sp], e[sp], L);
+                }
+                const float invL = L > 0.0f ? 1.0f / L : 0.0f;
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp) wtab[tid * 4 + sp] = w[sp] * invL;
+            }
+            float a[8][4];  // n_q * d_head <= 8 * 512 elements per thread in registers
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = tid + j * DS_CONSUMERS;
+                const int hh = i / p.d_head, dd = i - hh * p.d_head;
+                const float *pp = p.attn + (size_t)hh * p.splits * (p.d_head + 2) + dd;
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp)
+                    a[j][sp] = (i < p.n_q * p.d_head && sp < p.splits) ? __ldcg(pp + (size_t)sp * (p.d_head + 2)) : 0.0f;
+            }
+            cons_sync();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = tid + j * DS_CONSUMERS;
+                if (i < p.n_q * p.d_head) {
+                    const float *w = wtab + (i / p.d_head) * 4;
+                    act_s[i] = fmaf(w[3], a[j][3], fmaf(w[2], a[j][2], fmaf(w[1], a[j][1], w[0] * a[j][0])));
+                }
+            }
+        } else {
 #pragma unroll 4
-        for (int i = tid; i < p.n_q * p.d_head; i += DS_CONSUMERS) {
-            const int hh = i / p.d_head, dd = i - hh * p.d_head;
-            const float *pp = p.attn + (size_t)hh * p.splits * (p.d_head + 2);
-            float a[4], m[4], e[4];  // splits <= 4
+            for (int i = tid; i < p.n_q * p.d_head; i += DS_CONSUMERS) {
+                const int hh = i / p.d_head, dd = i - hh * p.d_head;
+                const float *pp = p.attn + (size_t)hh * p.splits * (p.d_head + 2);
+                float a[4], m[4], e[4];  // splits <= 4
 #pragma unroll
-            for (int sp = 0; sp < 4; ++sp) {
-                const bool on = sp < p.splits;
-                a[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + dd) : 0.0f;
-                m[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + p.d_head) : -INFINITY;
-                e[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + p.d_head + 1) : 0.0f;
+                for (int sp = 0; sp < 4; ++sp) {
+                    const bool on = sp < p.splits;
+                    a[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + dd) : 0.0f;
+                    m[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + p.d_head) : -INFINITY;
+                    e[sp] = on ? __ldcg(pp + (size_t)sp * (p.d_head + 2) + p.d_head + 1) : 0.0f;
+                }
+                float M = -INFINITY;
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp) M = fmaxf(M, m[sp]);
+                float L = 0.0f, v = 0.0f;
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp) {
+                    const float w = m[sp] > -INFINITY ? expf(m[sp] - M) : 0.0f;
+                    L = fmaf(w, e[sp], L);
+                    v = fmaf(w, a[sp], v);
+                }
+                act_s[i] = L > 0.0f ? v / L : 0.0f;
             }
-            float M = -INFINITY;
-#pragma unroll
-            for (int sp = 0; sp < 4; ++sp) M = fmaxf(M, m[sp]);
-            float L = 0.0f, v = 0.0f;
-#pragma unroll
-            for (int sp = 0; sp < 4; ++sp) {
-                const float w = m[sp] > -INFINITY ? expf(m[sp] - M) : 0.0f;
-                L = fmaf(w, e[sp], L);
-                v = fmaf(w, a[sp], v);
-            }
-            act_s[i] = L > 0.0f ? v / L : 0.0f;
         }
         cons_sync();
         quantize_activation(act_s, dig, p.n_q * p.d_head, false);
         STRACE(ts + 7);
-        gemv(4 * l + 1, p.x, true);
+        gemv(4 * l + 1, p.x, 1);
         STRACE(ts + 8);
         grid_barrier(p, epoch);
         STRACE(ts + 9);
@@ -639,29 +735,34 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         stage_norm(g2);
         quantize_activation(act_s, dig, H, false);
         STRACE(ts + 10);
-        gemv(4 * l + 2, p.gu, false);
+        gemv(4 * l + 2, p.gu, p.pair_gu ? 2 : 0);
         STRACE(ts + 11);
         grid_barrier(p, epoch);
         STRACE(ts + 12);
-        for (int i0 = tid; i0 < I; i0 += 12 * DS_CONSUMERS) {
-            float g[12], u[12];
+        if (p.pair_gu) {
+#pragma unroll 4
+            for (int i = tid; i < I; i += DS_CONSUMERS) act_s[i] = __ldcg(p.gu + i);
+        } else {
+            for (int i0 = tid; i0 < I; i0 += 12 * DS_CONSUMERS) {
+                float g[12], u[12];
 #pragma unroll
-            for (int j = 0; j < 12; ++j) {  // up to 24 loads in flight per thread
-                const int i = i0 + j * DS_CONSUMERS;
-                g[j] = i < I ? __ldcg(p.gu + i) : 0.0f;
-                u[j] = i < I ? __ldcg(p.gu + I + i) : 0.0f;
-            }
+                for (int j = 0; j < 12; ++j) {  // up to 24 loads in flight per thread
+                    const int i = i0 + j * DS_CONSUMERS;
+                    g[j] = i < I ? __ldcg(p.gu + i) : 0.0f;
+                    u[j] = i < I ? __ldcg(p.gu + I + i) : 0.0f;
+                }
 #pragma unroll
-            for (int j = 0; j < 12; ++j) {
-                const int i = i0 + j * DS_CONSUMERS;
-                const float sg = 1.0f / (1.0f + expf(-g[j]));
-                if (i < I) act_s[i] = (g[j] * sg) * u[j];
+                for (int j = 0; j < 12; ++j) {
+                    const int i = i0 + j * DS_CONSUMERS;
+                    const float sg = 1.0f / (1.0f + expf(-g[j]));
+                    if (i < I) act_s[i] = (g[j] * sg) * u[j];
+                }
             }
         }
         cons_sync();
         quantize_activation(act_s, dig, I, false);
         STRACE(ts + 13);
-        gemv(4 * l + 3, p.x, true);
+        gemv(4 * l + 3, p.x, 1);
         STRACE(ts + 14);
         grid_barrier(p, epoch);
         STRACE(ts + 15);
@@ -726,6 +827,13 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
         yscv_cuda_decode_plan_free(plan);
         return rc;
     };
+    // kernel variants (YSCV_CUDA_STEP_VARIANT, a bit mask read when the plan is built):
+    // 1 gate/up pairing, 2 sixteen K slices for one-tile slabs, 4 merge-weight table,
+    // 8 relaxed barrier polling
+    const char *venv = getenv("YSCV_CUDA_STEP_VARIANT");
+    const int variant = venv ? atoi(venv) : DS_DEFAULT_VARIANT;
+    const int half_tiles = (int)(((inter + grid - 1) / grid + 15) / 16);
+    const bool pair_gu = (variant & 1) && 2 * half_tiles <= 8;
     // every matrix: shape, geometry, tensor maps
     std::vector<StepMat> mats(n_layers * 4);
     size_t k_max = 0;
@@ -758,13 +866,19 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
             m.k = (int)k;
             m.tiles = (int)((rows_per_cta + 15) / 16);
             m.k_stages = (int)(k / 512);
-            const uint32_t rb_rows = (uint32_t)m.tiles * 16;
-            int rc = encode_2d(&m.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[j]->d_packed, n, k / 2, k / 2, rb_rows,
+            uint32_t box_rows = (uint32_t)m.tiles * 16;
+            if (j == 2 && pair_gu) {
+                // gate rows and the matching up rows: two boxes of half_tiles * 16 rows
+                m.tiles = 2 * half_tiles;
+                box_rows = (uint32_t)half_tiles * 16;
+            }
+            int rc = encode_2d(&m.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[j]->d_packed, n, k / 2, k / 2, box_rows,
                                128, CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc) return bail(rc);
-            rc = encode_2d(&m.tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, w[j]->d_scales, n, k / 32, k / 8, rb_rows,
+            rc = encode_2d(&m.tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, w[j]->d_scales, n, k / 32, k / 8, box_rows,
                            DS_GS, CU_TENSOR_MAP_SWIZZLE_64B);
             if (rc) return bail(rc);
+            const uint32_t rb_rows = (uint32_t)m.tiles * 16;
             k_max = k > k_max ? k : k_max;
             const int sb = (int)rb_rows * (DS_GS * 16 + DS_GS * 4);
             slot_bytes = sb > slot_bytes ? sb : slot_bytes;
@@ -782,7 +896,8 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     if (act_floats * 4 > 96 * 1024)
         return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: max_seq=%zu does not fit one CTA per head", max_seq));
     p.act_floats = (int)act_floats;
-    const int tables = 128 + (int)d_head * 4 + (int)n_layers * 2 * 8 + 16;  // misc, rotary factors, cache pointers
+    // misc, rotary factors, cache pointers, split-merge weights
+    const int tables = 128 + (int)d_head * 4 + (int)n_layers * 2 * 8 + (int)n_q * 16 + 16;
     const int fixed = DS_RED_BYTES + DS_BAR_BYTES + p.dig_bytes + p.act_floats * 4 + tables;
     const int budget = 227 * 1024 - fixed - 1024;
     p.stages = budget / slot_bytes;
@@ -844,6 +959,11 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     p.max_seq = (int)max_seq;
     p.eps = eps;
     p.theta = rope_theta;
+    p.pair_gu = pair_gu ? 1 : 0;
+    p.gu_half_tiles = half_tiles;
+    p.one_tile_16 = (variant & 2) ? 1 : 0;
+    p.merge_table = (variant & 4) ? 1 : 0;
+    p.relaxed_poll = (variant & 8) ? 1 : 0;
     for (int j = 0; j < 4; ++j) {
         p.mat_n[j] = mats[j].n;
         p.mat_tiles[j] = mats[j].tiles;

@@ -313,6 +313,7 @@ f32_matmul_kernel(const float *__restrict__ w, const float *__restrict__ x, floa
         float acc[MT];
 #pragma unroll
         for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
+#pragma unroll 4
         for (int c = lane; c < K / 4; c += 32) {
             const float4 wv = __ldg(wr + c);
 #pragma unroll
