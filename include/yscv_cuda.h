@@ -317,8 +317,10 @@ int yscv_cuda_int8_matmul_requant_i8(yscv_cuda_ctx *ctx, const int8_t *a, const 
  * int4 MatMul (gate|up rows), SiLU(gate)*up, int4 MatMul (down) + residual. A decode plan
  * runs that sequence for ONE sequence (batch 1) as a single persistent cooperative kernel.
  * Requirements (else YSCV_CUDA_ERR_UNSUPPORTED): group size 32; every K a multiple of 512;
- * sm_count <= rows <= 128 * sm_count per matrix; n_q <= sm_count; head_dim a multiple of 16
- * that divides 512, at most 128; max_seq small enough for one CTA per head (about 10^4).
+ * at least sm_count rows per matrix; hidden and n_q * d_head at most 8192; inter above 8192
+ * only while the down projection has at most 128 rows per SM (hidden <= 128 * sm_count);
+ * n_q <= sm_count; head_dim a multiple of 16 that divides 512, at most 128; max_seq small
+ * enough for the scores of one head chunk in shared memory (about 2 * 10^4).
  * The plan borrows the weights and caches (they must outlive it) and copies the gammas. */
 typedef struct yscv_cuda_decode_plan yscv_cuda_decode_plan;
 

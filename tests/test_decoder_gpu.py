@@ -250,6 +250,78 @@ def test_fused_step_logits_match_operator_chain(tctx):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("env", [
+    {"YSCV_CUDA_STEP_MAX_TILES": "2", "YSCV_CUDA_STEP_KCHUNK": "1024"},                                  # default variant
+    {"YSCV_CUDA_STEP_MAX_TILES": "2", "YSCV_CUDA_STEP_KCHUNK": "1024", "YSCV_CUDA_STEP_VARIANT": "0"},   # plain
+    {"YSCV_CUDA_STEP_MAX_TILES": "4", "YSCV_CUDA_STEP_KCHUNK": "1536", "YSCV_CUDA_STEP_VARIANT": "5"},
+])
+def test_fused_step_row_blocks_and_k_chunks(tctx, env):
+    """Small shapes pushed through the paths large models take: several row blocks per CTA
+    (gate/up) and a down projection longer than one K chunk, by shrinking the plan's limits."""
+    import os
+    import torch
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=2, hidden=1024, mlp=2560, n_q=16, n_kv=4, head_dim=64, vocab=2000)
+    prompt = dev(synth.uniform_int(23, 9, 40, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    ctx.set_int4_prefill_exact(True)
+    logs, toks = [], []
+    try:
+        for fused in (False, True):
+            if fused:
+                os.environ.update(env)
+            dec = Int4Decoder(ctx, cfg, 1, 64, s, seed=15, fused_step=fused)
+            assert (dec.plan is not None) == fused
+            dec.prefill(prompt)
+            lg, tk = [], []
+            for _ in range(6):
+                with torch.cuda.stream(s):
+                    out = dec.forward(dec.next_tokens, 1)
+                s.synchronize()
+                lg.append(out.cpu().numpy().copy())
+                tk.append(int(dec.next_tokens.cpu().numpy()[0]))
+            logs.append(lg)
+            toks.append(tk)
+            dec.close()
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+        ctx.set_int4_prefill_exact(False)
+    assert toks[0] == toks[1]
+    for a, b in zip(*logs):
+        assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
+    assert ctx.device_status() == 0
+
+
+def test_fused_step_llama70b_layer_shape(tctx):
+    """One layer of BASELINE config 5's shape (hidden 8192, MLP 28672, 64/8 heads of 128; small
+    vocabulary): four row blocks in gate/up, a down projection of 3.5 K chunks, two CTAs per
+    head. The one-launch step against the operator chain."""
+    import torch
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=1, hidden=8192, mlp=28672, n_q=64, n_kv=8, head_dim=128, vocab=4096,
+                        rope_theta=500000.0)
+    prompt = dev(synth.uniform_int(29, 9, 200, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    logs, toks = [], []
+    for fused in (False, True):
+        dec = Int4Decoder(ctx, cfg, 1, 256, s, seed=16, fused_step=fused)
+        assert (dec.plan is not None) == fused
+        dec.prefill(prompt)
+        lg, tk = [], []
+        for _ in range(3):
+            with torch.cuda.stream(s):
+                out = dec.forward(dec.next_tokens, 1)
+            s.synchronize()
+            lg.append(out.cpu().numpy().copy())
+            tk.append(int(dec.next_tokens.cpu().numpy()[0]))
+        logs.append(lg)
+        toks.append(tk)
+        dec.close()
+    assert toks[0] == toks[1]
+    for a, b in zip(*logs):
+        assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
+    assert ctx.device_status() == 0
+
+
 def test_fused_step_long_context_and_limits(tctx):
     """More than 128 keys per attention split (the loops past the prefetched rows), the last
     cache slot, and shapes the plan refuses."""

@@ -21,8 +21,12 @@
 //   * operators that need another CTA's output are separated by a grid-wide barrier (a counter
 //     in global memory, bounded spin, abort flag), five per layer.
 //
-// Limits (checked when the plan is built): group size 32, K % 512 == 0, at most 128 weight rows
-// per CTA and matrix, head_dim <= 128, the whole context of a head handled by one CTA.
+// A CTA's rows of a matrix are walked in row blocks of at most 8 tiles of 16 rows; the digit
+// planes of at most 8192 activations are resident at a time, so a longer down projection is
+// walked in K chunks (stage a chunk, consume its stages, keep the accumulators).
+//
+// Limits (checked when the plan is built): group size 32, K % 512 == 0, hidden and
+// n_q * head_dim <= 8192, head_dim <= 128, at most 4 CTAs per query head.
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
@@ -74,6 +78,9 @@ struct StepParams {
     // CTA, K stages; kept here so that no thread waits on global memory to learn them
     int mat_n[4], mat_tiles[4], mat_ks[4];
     int mat_kps[4];  // K stages per ring slot: a matrix with few rows per CTA packs several
+    int mat_nrb[4];  // row blocks a CTA walks per matrix (each of mat_tiles tiles)
+    int kc_stages;   // K stages whose digit planes fit the digit area at once (a K chunk); only
+                     // the down projection may be longer than one chunk
     // gate/up pairing: a CTA owns the intermediate indices [i0, i1) and streams gate rows
     // [i0, i1) and up rows [inter + i0, inter + i1) as the two halves of its slab, so that
     // silu(gate) * up is formed in the store of that GEMV (gu then holds [inter] values)
@@ -194,18 +201,17 @@ struct RingPos {
     uint32_t phase;
 };
 
-// The M = 1 GEMV of one matrix over this CTA's rows [r0, r1): walks the matrix's K stages in
-// the ring, combines the K slices in a fixed order and stores (or adds into) out[row].
-// Same fragment arithmetic as int4_gemv_fast_kernel<1, 16, TP2, true>.
+// The M = 1 GEMV of one row block of a matrix: consume_stages walks K stages [ks_begin, ks_end)
+// of the block in the ring and adds into the two accumulators of the thread; finish_rows
+// combines the K slices in a fixed order and stores. Same fragment arithmetic as
+// int4_gemv_fast_kernel<1, 16, TP2, true>. `dig_stage0` is the K stage whose digit planes sit
+// at the start of the digit area (the first stage of the current K chunk).
 template <int TP2>
-__device__ __forceinline__ void consume_matrix(const StepParams &p, const unsigned char *smem,
-                                               uint32_t bar_full, uint32_t bar_empty, float *red,
+__device__ __forceinline__ void consume_stages(const StepParams &p, const unsigned char *smem,
+                                               uint32_t bar_full, uint32_t bar_empty,
                                                const unsigned char *dig, RingPos &c, int tiles,
-                                               int k_stages, int kps, int r0, int r1, float *out,
-                                               int store, bool &dead) {
-    // store: 0 out[row] = v; 1 out[row] += v; 2 the slab is gate tiles then up tiles of the
-    // intermediate indices [r0, r1): out[i] = silu(gate_i) * up_i
-    const bool accumulate = store == 1;
+                                               int ks_begin, int ks_end, int kps, int dig_stage0,
+                                               float (&acc)[2], bool &dead) {
     constexpr int GS = DS_GS;
     constexpr int KSL = (16 / TP2 < GS) ? 16 / TP2 : GS;
     constexpr int GPW = GS / KSL;
@@ -233,21 +239,15 @@ __device__ __forceinline__ void consume_matrix(const StepParams &p, const unsign
     for (int cc = 0; cc < (GPW + 3) / 4; ++cc)
         s_ch[cc] = s_row + (((((uint32_t)(G0 + 4 * cc)) >> 2) ^ s_phase) << 4);
     const int mul_hi = (t & 1) ? 1 : 65536;
-    float acc[2] = {0.0f, 0.0f};
-    // the thread that will store output row `my_row` fetches the residual value now, not after
-    // the K loop
-    const int my_row = r0 + (tid >> 4) * 16 + (tid & 7) + ((tid >> 3) & 1) * 8;
-    float resid = 0.0f;
-    if (accumulate && tid < tiles * 16 && my_row < r1) resid = __ldcg(out + my_row);
 
     const uint32_t sub_bytes = (uint32_t)rb_rows * (GS * 16 + GS * 4);  // one K stage inside a slot
-    for (int ks0 = 0; ks0 < k_stages; ks0 += kps) {
+    for (int ks0 = ks_begin; ks0 < ks_end; ks0 += kps) {
         if (!dead) dead = !mbar_wait(bar_full + c.slot * 8, c.phase, p.status);
-        const int nsub = min(kps, k_stages - ks0);
+        const int nsub = min(kps, ks_end - ks0);
         if (active && !dead) {
             for (int j = 0; j < nsub; ++j) {
                 const unsigned char *st = smem + (size_t)c.slot * p.slot_bytes + (size_t)j * sub_bytes;
-                const unsigned char *db = dig + (size_t)(ks0 + j) * DS_BLOB_BYTES;
+                const unsigned char *db = dig + (size_t)(ks0 + j - dig_stage0) * DS_BLOB_BYTES;
                 float sA[GPW], sB[GPW];
                 if constexpr (GPW % 4 == 0) {
 #pragma unroll
@@ -291,11 +291,25 @@ __device__ __forceinline__ void consume_matrix(const StepParams &p, const unsign
         if (lane == 0) mbar_arrive(bar_empty + c.slot * 8);
         if (++c.slot == p.stages) { c.slot = 0; c.phase ^= 1u; }
     }
+}
+
+// store: 0 out[row] = v; 1 out[row] = resid + v (resid fetched by the caller before the K loop);
+// 2 the block is gate tiles then up tiles of intermediate indices: out[i] = silu(gate_i) * up_i.
+// Rows (indices) of the block start at row_base; nothing at or past r1 is written.
+template <int TP2>
+__device__ __forceinline__ void finish_rows(float *red, int tiles, int row_base, int r1, float *out,
+                                            int store, const float (&acc)[2], float resid) {
+    constexpr int GS = DS_GS;
+    constexpr int KSL = (16 / TP2 < GS) ? 16 / TP2 : GS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tile = warp % TP2, kslice = warp / TP2;
+    const bool active = (tile < tiles) && (kslice < KSL);
     if (active) {
         red[((kslice * tiles + tile) * 2 + 0) * 32 + lane] = acc[0];
         red[((kslice * tiles + tile) * 2 + 1) * 32 + lane] = acc[1];
     }
     cons_sync();
+    const int my_row = row_base + (tid >> 4) * 16 + (tid & 7) + ((tid >> 3) & 1) * 8;
     // element (tile, half, gq): sum over the K slices and the thread pair t = 0, 1
     if (store == 2) {
         const int th = tiles / 2;
@@ -318,9 +332,9 @@ __device__ __forceinline__ void consume_matrix(const StepParams &p, const unsign
             const float *pp = red + ((ks * tiles + tl) * 2 + half) * 32 + q8 * 4;
             v += pp[0] + pp[1];
         }
-        if (my_row < r1) out[my_row] = accumulate ? resid + v : v;
+        if (my_row < r1) out[my_row] = store == 1 ? resid + v : v;
     }
-    cons_sync();  // `red` is reused by the next matrix
+    cons_sync();  // `red` is reused by the next block
 }
 
 // Attention of the one query of head h over positions 0 .. pos, the keys dealt in contiguous
@@ -518,39 +532,49 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
             bool alive = true;
             for (int mi = 0; mi < nmat && alive; ++mi) {
                 const StepMat *m = p.mats + mi;
-                const bool paired = (mi & 3) == 2 && p.pair_gu;
-                const int n = paired ? p.inter : p.mat_n[mi & 3];
-                const int tiles = p.mat_tiles[mi & 3], k_stages = p.mat_ks[mi & 3];
+                const int j = mi & 3;
+                const bool paired = j == 2 && p.pair_gu;
+                const int n = paired ? p.inter : p.mat_n[j];
+                const int tiles = p.mat_tiles[j], k_stages = p.mat_ks[j], n_rb = p.mat_nrb[j];
                 const int r0 = (int)(((unsigned)n * blockIdx.x) / gridDim.x);
                 const int rb_rows = tiles * 16;
-                const int kps = p.mat_kps[mi & 3];
+                const int block_rows = (paired ? tiles / 2 : tiles) * 16;
+                const int kps = p.mat_kps[j];
                 const uint32_t sub_bytes = (uint32_t)rb_rows * (DS_GS * 16 + DS_GS * 4);
-                for (int ks0 = 0; ks0 < k_stages && alive; ks0 += kps) {
-                    // a fresh barrier passes the wait on the opposite parity at once
-                    alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, p.status);
-                    if (!alive) break;
-                    const int nsub = min(kps, k_stages - ks0);
-                    const uint32_t full = bar_full + slot * 8;
-                    mbar_expect_tx(full, (uint32_t)nsub * sub_bytes);
-                    for (int j = 0; j < nsub; ++j) {
-                        const uint32_t st = smem_base + (uint32_t)slot * p.slot_bytes + (uint32_t)j * sub_bytes;
-                        const int ks = ks0 + j;
-                        if (paired) {
-                            // two boxes of half the slab each: gate rows, then the matching up rows
-                            const int hr = p.gu_half_tiles * 16;
-                            for (int h = 0; h < 2; ++h) {
-                                const int row = h * p.inter + r0;
-                                tma_load_2d(st + h * hr * 128, &m->tm_w, ks * (DS_GS * 16), row, full);
-                                tma_load_2d(st + rb_rows * 128 + h * hr * 128, &m->tm_w, ks * (DS_GS * 16) + 128, row, full);
-                                tma_load_2d(st + rb_rows * 256 + h * hr * (DS_GS * 4), &m->tm_s, ks * DS_GS, row, full);
+                // the consumers' order: K chunk, row block, K stage
+                for (int cs = 0; cs < k_stages && alive; cs += p.kc_stages) {
+                    const int ce = min(k_stages, cs + p.kc_stages);
+                    for (int rb = 0; rb < n_rb && alive; ++rb) {
+                        const int row0 = r0 + rb * block_rows;
+                        for (int ks0 = cs; ks0 < ce && alive; ks0 += kps) {
+                            // a fresh barrier passes the wait on the opposite parity at once
+                            alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, p.status);
+                            if (!alive) break;
+                            const int nsub = min(kps, ce - ks0);
+                            const uint32_t full = bar_full + slot * 8;
+                            mbar_expect_tx(full, (uint32_t)nsub * sub_bytes);
+                            for (int q = 0; q < nsub; ++q) {
+                                const uint32_t st = smem_base + (uint32_t)slot * p.slot_bytes + (uint32_t)q * sub_bytes;
+                                const int ks = ks0 + q;
+                                if (paired) {
+                                    // two boxes of half the block each: gate rows, then the matching up rows
+                                    for (int h = 0; h < 2; ++h) {
+                                        const int row = h * p.inter + row0;
+                                        tma_load_2d(st + h * block_rows * 128, &m->tm_w, ks * (DS_GS * 16), row, full);
+                                        tma_load_2d(st + rb_rows * 128 + h * block_rows * 128, &m->tm_w,
+                                                    ks * (DS_GS * 16) + 128, row, full);
+                                        tma_load_2d(st + rb_rows * 256 + h * block_rows * (DS_GS * 4), &m->tm_s,
+                                                    ks * DS_GS, row, full);
+                                    }
+                                } else {
+                                    tma_load_2d(st, &m->tm_w, ks * (DS_GS * 16), row0, full);
+                                    tma_load_2d(st + rb_rows * 128, &m->tm_w, ks * (DS_GS * 16) + 128, row0, full);
+                                    tma_load_2d(st + rb_rows * 256, &m->tm_s, ks * DS_GS, row0, full);
+                                }
                             }
-                        } else {
-                            tma_load_2d(st, &m->tm_w, ks * (DS_GS * 16), r0, full);
-                            tma_load_2d(st + rb_rows * 128, &m->tm_w, ks * (DS_GS * 16) + 128, r0, full);
-                            tma_load_2d(st + rb_rows * 256, &m->tm_s, ks * DS_GS, r0, full);
+                            if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                         }
                     }
-                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
             }
             // a consumer that gave up leaves copies unobserved: wait (bounded) for every slot
@@ -566,19 +590,44 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     bool dead = false;
     const int H = p.hidden, I = p.inter;
 
-    auto gemv = [&](int mi, float *out, int store) {
+    // One matrix: for every K chunk, `stage_chunk(k0, klen)` leaves the activations of that
+    // chunk in act_s and their digit planes in `dig`; then every row block of the CTA walks the
+    // chunk's stages. (More than one chunk only with a single row block: the accumulators then
+    // live across the chunks.)
+    auto gemv = [&](int mi, float *out, int store, auto &&stage_chunk) {
         const int j = mi & 3;
-        const int tiles = p.mat_tiles[j], k_stages = p.mat_ks[j], kps = p.mat_kps[j];
+        const int tiles = p.mat_tiles[j], k_stages = p.mat_ks[j], kps = p.mat_kps[j], n_rb = p.mat_nrb[j];
         // rows of the matrix, or (paired gate/up) intermediate indices
         const unsigned n = (j == 2 && p.pair_gu) ? (unsigned)p.inter : (unsigned)p.mat_n[j];
         const int r0 = (int)((n * blockIdx.x) / gridDim.x);
         const int r1 = (int)((n * (blockIdx.x + 1)) / gridDim.x);
-        if (tiles == 1 && p.one_tile_16)
-            consume_matrix<1>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, store, dead);
-        else if (tiles <= 2)
-            consume_matrix<2>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, store, dead);
-        else
-            consume_matrix<8>(p, smem, bar_full, bar_empty, red, dig, c, tiles, k_stages, kps, r0, r1, out, store, dead);
+        const int block_rows = (store == 2 ? tiles / 2 : tiles) * 16;
+        float acc[2] = {0.0f, 0.0f};
+        for (int cs = 0; cs < k_stages; cs += p.kc_stages) {
+            const int ce = min(k_stages, cs + p.kc_stages);
+            stage_chunk(cs * (DS_GS * 32), (ce - cs) * (DS_GS * 32));
+            for (int rb = 0; rb < n_rb; ++rb) {
+                const int row_base = r0 + rb * block_rows;
+                const bool last = ce == k_stages;
+                // the thread that will store a row fetches its residual value before the K loop
+                float resid = 0.0f;
+                if (store == 1 && last && tid < tiles * 16) {
+                    const int my_row = row_base + (tid >> 4) * 16 + (tid & 7) + ((tid >> 3) & 1) * 8;
+                    if (my_row < r1) resid = __ldcg(out + my_row);
+                }
+                if (n_rb > 1) { acc[0] = 0.0f; acc[1] = 0.0f; }
+                if (tiles == 1 && p.one_tile_16) {
+                    consume_stages<1>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
+                    if (last) finish_rows<1>(red, tiles, row_base, r1, out, store, acc, resid);
+                } else if (tiles <= 2) {
+                    consume_stages<2>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
+                    if (last) finish_rows<2>(red, tiles, row_base, r1, out, store, acc, resid);
+                } else {
+                    consume_stages<8>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
+                    if (last) finish_rows<8>(red, tiles, row_base, r1, out, store, acc, resid);
+                }
+            }
+        }
     };
     // act_s = RMSNorm(x) * gamma
     auto stage_norm = [&](const float *gamma) {
@@ -634,28 +683,14 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     }
     grid_barrier(p, epoch);
 
-    for (int l = 0; l < p.layers; ++l) {
-        const float *g1 = p.gamma + (size_t)(2 * l) * H, *g2 = g1 + H;
-        const int ts = l < 3 ? l * 16 : -100;  // trace slots of this layer (debug builds)
-        STRACE(ts + 0);
-        // attention block: norm -> qkv
-        stage_norm(g1);
-        STRACE(ts + 1);
+    // activation staging of the three kinds of GEMV input (each ends with the digit planes)
+    auto stage_normed = [&](const float *gamma) {
+        stage_norm(gamma);
         quantize_activation(act_s, dig, H, false);
-        STRACE(ts + 2);
-        gemv(4 * l + 0, p.qkv, 0);
-        STRACE(ts + 3);
-        grid_barrier(p, epoch);
-        STRACE(ts + 4);
-        // RoPE, cache append, attention: one CTA per query head
-        if ((int)blockIdx.x < p.n_q * p.splits)
-            attention_head(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
-                           cache_ptr[2 * l + 1], rope_cs, act_s, misc);
-        STRACE(ts + 5);
-        grid_barrier(p, epoch);
-        STRACE(ts + 6);
-        // output projection, residual add in the store; its activation vector is the merge of
-        // the attention splits (the usual max-rescaling of a split softmax)
+    };
+    // merge of the attention splits (the usual max-rescaling of a split softmax)
+    auto stage_attention = [&]() {
+        const int AW = p.n_q * p.d_head;
         if (p.merge_table) {
             // per (head, split): weight exp(m - M) / L once, through shared memory
             if (tid < p.n_q) {
@@ -679,28 +714,31 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
 #pragma unroll
                 for (int sp = 0; sp < 4; ++sp) wtab[tid * 4 + sp] = w[sp] * invL;
             }
-            float a[8][4];  // n_q * d_head <= 8 * 512 elements per thread in registers
+            // 4 x 512 elements per pass, their partial sums in registers across the barrier
+            for (int base = 0; base < AW; base += 4 * DS_CONSUMERS) {
+                float a[4][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int i = tid + j * DS_CONSUMERS;
-                const int hh = i / p.d_head, dd = i - hh * p.d_head;
-                const float *pp = p.attn + (size_t)hh * p.splits * (p.d_head + 2) + dd;
+                for (int j = 0; j < 4; ++j) {
+                    const int i = base + tid + j * DS_CONSUMERS;
+                    const int hh = i / p.d_head, dd = i - hh * p.d_head;
+                    const float *pp = p.attn + (size_t)hh * p.splits * (p.d_head + 2) + dd;
 #pragma unroll
-                for (int sp = 0; sp < 4; ++sp)
-                    a[j][sp] = (i < p.n_q * p.d_head && sp < p.splits) ? __ldcg(pp + (size_t)sp * (p.d_head + 2)) : 0.0f;
-            }
-            cons_sync();
+                    for (int sp = 0; sp < 4; ++sp)
+                        a[j][sp] = (i < AW && sp < p.splits) ? __ldcg(pp + (size_t)sp * (p.d_head + 2)) : 0.0f;
+                }
+                if (base == 0) cons_sync();  // the weight table is complete
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int i = tid + j * DS_CONSUMERS;
-                if (i < p.n_q * p.d_head) {
-                    const float *w = wtab + (i / p.d_head) * 4;
-                    act_s[i] = fmaf(w[3], a[j][3], fmaf(w[2], a[j][2], fmaf(w[1], a[j][1], w[0] * a[j][0])));
+                for (int j = 0; j < 4; ++j) {
+                    const int i = base + tid + j * DS_CONSUMERS;
+                    if (i < AW) {
+                        const float *w = wtab + (i / p.d_head) * 4;
+                        act_s[i] = fmaf(w[3], a[j][3], fmaf(w[2], a[j][2], fmaf(w[1], a[j][1], w[0] * a[j][0])));
+                    }
                 }
             }
         } else {
 #pragma unroll 4
-            for (int i = tid; i < p.n_q * p.d_head; i += DS_CONSUMERS) {
+            for (int i = tid; i < AW; i += DS_CONSUMERS) {
                 const int hh = i / p.d_head, dd = i - hh * p.d_head;
                 const float *pp = p.attn + (size_t)hh * p.splits * (p.d_head + 2);
                 float a[4], m[4], e[4];  // splits <= 4
@@ -725,44 +763,62 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
             }
         }
         cons_sync();
-        quantize_activation(act_s, dig, p.n_q * p.d_head, false);
-        STRACE(ts + 7);
-        gemv(4 * l + 1, p.x, 1);
-        STRACE(ts + 8);
-        grid_barrier(p, epoch);
-        STRACE(ts + 9);
-        // MLP: norm -> gate+up -> SwiGLU -> down, residual add in the store
-        stage_norm(g2);
-        quantize_activation(act_s, dig, H, false);
-        STRACE(ts + 10);
-        gemv(4 * l + 2, p.gu, p.pair_gu ? 2 : 0);
-        STRACE(ts + 11);
-        grid_barrier(p, epoch);
-        STRACE(ts + 12);
+        quantize_activation(act_s, dig, AW, false);
+    };
+    // the MLP activations [k0, k0 + klen): already silu(gate) * up (paired), or formed here
+    auto stage_mlp = [&](int k0, int klen) {
+        if (k0 > 0) cons_sync();  // every warp is done with the previous chunk's act_s and planes
         if (p.pair_gu) {
 #pragma unroll 4
-            for (int i = tid; i < I; i += DS_CONSUMERS) act_s[i] = __ldcg(p.gu + i);
+            for (int i = tid; i < klen; i += DS_CONSUMERS) act_s[i] = __ldcg(p.gu + k0 + i);
         } else {
-            for (int i0 = tid; i0 < I; i0 += 12 * DS_CONSUMERS) {
+            for (int i0 = tid; i0 < klen; i0 += 12 * DS_CONSUMERS) {
                 float g[12], u[12];
 #pragma unroll
                 for (int j = 0; j < 12; ++j) {  // up to 24 loads in flight per thread
                     const int i = i0 + j * DS_CONSUMERS;
-                    g[j] = i < I ? __ldcg(p.gu + i) : 0.0f;
-                    u[j] = i < I ? __ldcg(p.gu + I + i) : 0.0f;
+                    g[j] = i < klen ? __ldcg(p.gu + k0 + i) : 0.0f;
+                    u[j] = i < klen ? __ldcg(p.gu + I + k0 + i) : 0.0f;
                 }
 #pragma unroll
                 for (int j = 0; j < 12; ++j) {
                     const int i = i0 + j * DS_CONSUMERS;
                     const float sg = 1.0f / (1.0f + expf(-g[j]));
-                    if (i < I) act_s[i] = (g[j] * sg) * u[j];
+                    if (i < klen) act_s[i] = (g[j] * sg) * u[j];
                 }
             }
         }
         cons_sync();
-        quantize_activation(act_s, dig, I, false);
-        STRACE(ts + 13);
-        gemv(4 * l + 3, p.x, 1);
+        quantize_activation(act_s, dig, klen, false);
+    };
+
+    for (int l = 0; l < p.layers; ++l) {
+        const float *g1 = p.gamma + (size_t)(2 * l) * H, *g2 = g1 + H;
+        [[maybe_unused]] const int ts = l < 3 ? l * 16 : -100;  // trace slots of this layer (debug builds)
+        STRACE(ts + 0);
+        // attention block: norm -> qkv
+        gemv(4 * l + 0, p.qkv, 0, [&](int, int) { stage_normed(g1); });
+        STRACE(ts + 3);
+        grid_barrier(p, epoch);
+        STRACE(ts + 4);
+        // RoPE, cache append, attention: a few CTAs per query head
+        if ((int)blockIdx.x < p.n_q * p.splits)
+            attention_head(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
+                           cache_ptr[2 * l + 1], rope_cs, act_s, misc);
+        STRACE(ts + 5);
+        grid_barrier(p, epoch);
+        STRACE(ts + 6);
+        // output projection, residual add in the store
+        gemv(4 * l + 1, p.x, 1, [&](int, int) { stage_attention(); });
+        STRACE(ts + 8);
+        grid_barrier(p, epoch);
+        STRACE(ts + 9);
+        // MLP: norm -> gate+up -> SwiGLU -> down, residual add in the store
+        gemv(4 * l + 2, p.gu, p.pair_gu ? 2 : 0, [&](int, int) { stage_normed(g2); });
+        STRACE(ts + 11);
+        grid_barrier(p, epoch);
+        STRACE(ts + 12);
+        gemv(4 * l + 3, p.x, 1, stage_mlp);
         STRACE(ts + 14);
         grid_barrier(p, epoch);
         STRACE(ts + 15);
@@ -832,8 +888,23 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     // 8 relaxed barrier polling
     const char *venv = getenv("YSCV_CUDA_STEP_VARIANT");
     const int variant = venv ? atoi(venv) : DS_DEFAULT_VARIANT;
-    const int half_tiles = (int)(((inter + grid - 1) / grid + 15) / 16);
-    const bool pair_gu = (variant & 1) && 2 * half_tiles <= 8;
+    // geometry limits, overridable so that small test shapes reach the row-block and K-chunk
+    // paths: tiles per row block (YSCV_CUDA_STEP_MAX_TILES, 2..8, even), k per chunk
+    // (YSCV_CUDA_STEP_KCHUNK, a multiple of 512)
+    const char *tenv = getenv("YSCV_CUDA_STEP_MAX_TILES"), *kenv = getenv("YSCV_CUDA_STEP_KCHUNK");
+    int max_tiles = tenv ? atoi(tenv) : 8;
+    max_tiles = max_tiles < 2 ? 2 : (max_tiles > 8 ? 8 : max_tiles & ~1);
+    int kc_limit = kenv ? atoi(kenv) / 512 : 16;   // 16 stages = 8192 k = 64 KB of digit planes
+    kc_limit = kc_limit < 1 ? 1 : (kc_limit > 16 ? 16 : kc_limit);
+    // rows (or paired indices) per CTA -> row blocks of at most `cap` tiles, balanced
+    auto blocks_of = [&](size_t per_cta, int cap, int *tiles_out) {
+        const int n_rb = (int)((per_cta + (size_t)cap * 16 - 1) / ((size_t)cap * 16));
+        const size_t per_block = (per_cta + n_rb - 1) / n_rb;
+        *tiles_out = (int)((per_block + 15) / 16);
+        return n_rb;
+    };
+    const bool pair_gu = (variant & 1) != 0;
+    int nrb[4] = {1, 1, 1, 1}, tl[4] = {1, 1, 1, 1};
     // every matrix: shape, geometry, tensor maps
     std::vector<StepMat> mats(n_layers * 4);
     size_t k_max = 0;
@@ -854,24 +925,28 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
                 return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: group size %zu (only 32)",
                                  w[j]->group_size));
             const size_t n = w[j]->m_w, k = w[j]->k;
-            const size_t rows_per_cta = (n + grid - 1) / grid;
-            if (k % 512 != 0 || n < (size_t)grid || rows_per_cta > 128 ||
+            if (k % 512 != 0 || n < (size_t)grid ||
                 ((reinterpret_cast<uintptr_t>(w[j]->d_packed) | reinterpret_cast<uintptr_t>(w[j]->d_scales)) & 15))
                 return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED,
-                                 "decode plan: matrix [%zu][%zu] needs k %% 512 == 0, %d <= n <= %d and 16-byte alignment",
-                                 n, k, grid, 128 * grid));
+                                 "decode plan: matrix [%zu][%zu] needs k %% 512 == 0, n >= %d and 16-byte alignment",
+                                 n, k, grid));
             StepMat &m = mats[l * 4 + j];
             memset(&m, 0, sizeof(m));
             m.n = (int)n;
             m.k = (int)k;
-            m.tiles = (int)((rows_per_cta + 15) / 16);
             m.k_stages = (int)(k / 512);
-            uint32_t box_rows = (uint32_t)m.tiles * 16;
+            uint32_t box_rows;
             if (j == 2 && pair_gu) {
-                // gate rows and the matching up rows: two boxes of half_tiles * 16 rows
-                m.tiles = 2 * half_tiles;
-                box_rows = (uint32_t)half_tiles * 16;
+                // gate rows and the matching up rows: two boxes of half the block each
+                int half = 1;
+                nrb[j] = blocks_of((inter + grid - 1) / grid, max_tiles / 2, &half);
+                m.tiles = 2 * half;
+                box_rows = (uint32_t)half * 16;
+            } else {
+                nrb[j] = blocks_of((n + grid - 1) / grid, max_tiles, &m.tiles);
+                box_rows = (uint32_t)m.tiles * 16;
             }
+            tl[j] = m.tiles;
             int rc = encode_2d(&m.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[j]->d_packed, n, k / 2, k / 2, box_rows,
                                128, CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc) return bail(rc);
@@ -886,11 +961,20 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     }
     slot_bytes = ((slot_bytes + 1023) / 1024) * 1024;
     StepParams &p = plan->params;
-    p.dig_bytes = (int)(k_max / 512) * DS_BLOB_BYTES;
+    // K chunk: the digit planes and activations of one chunk are resident at a time; only the
+    // down projection may span several chunks, and then with a single row block
+    const int kc_stages = std::min<int>((int)(k_max / 512), kc_limit);
+    if (hidden / 512 > (size_t)kc_stages || attn_w / 512 > (size_t)kc_stages ||
+        (inter / 512 > (size_t)kc_stages && nrb[3] != 1))
+        return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED,
+                         "decode plan: hidden=%zu / n_q*d_head=%zu exceed one K chunk of %d, or the down projection "
+                         "needs both several chunks and several row blocks", hidden, attn_w, kc_stages * 512));
+    p.kc_stages = kc_stages;
+    p.dig_bytes = kc_stages * DS_BLOB_BYTES;
     // the attention scratch (q, k, v of the head, partial sums, scores) lives in the activation
     // area between the GEMVs: widen that area if it needs more
     const size_t attn_scratch = (3 * d_head + 4 * DS_CONSUMERS + max_seq) * sizeof(float);
-    size_t act_floats = k_max;
+    size_t act_floats = (size_t)kc_stages * 512;
     if (attn_scratch > act_floats * 4) act_floats = (attn_scratch + 3) / 4;
     act_floats = (act_floats + 3) / 4 * 4;
     if (act_floats * 4 > 96 * 1024)
@@ -960,7 +1044,7 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     p.eps = eps;
     p.theta = rope_theta;
     p.pair_gu = pair_gu ? 1 : 0;
-    p.gu_half_tiles = half_tiles;
+    p.gu_half_tiles = tl[2] / 2;
     p.one_tile_16 = (variant & 2) ? 1 : 0;
     p.merge_table = (variant & 4) ? 1 : 0;
     p.relaxed_poll = (variant & 8) ? 1 : 0;
@@ -970,6 +1054,7 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
         p.mat_ks[j] = mats[j].k_stages;
         const int sub = mats[j].tiles * 16 * (DS_GS * 16 + DS_GS * 4);
         p.mat_kps[j] = std::max(1, std::min(slot_bytes / sub, 8));
+        p.mat_nrb[j] = nrb[j];
     }
     *out = plan;
     return YSCV_CUDA_OK;

@@ -218,6 +218,7 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             tc_fence_after();
             const int row = mb * G8_BM + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)abuf * BN;
+            const bool general = p.corr != nullptr || p.comp_pc != nullptr || p.relu != 0 || p.b_zp != 0;
             // what the zero point of B adds to every element of this row
             int row_term = 0;
             if (p.b_zp != 0 && row < p.M)
@@ -249,20 +250,35 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     } else {
                         uint8_t *o = reinterpret_cast<uint8_t *>(out) + (size_t)row * p.ldc + col0;
                         uint32_t packed[8];
+                        if (general) {
+                            // per-channel vectors, bias, ReLU or a zero point on B
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int cc = (col0 + j < p.N) ? col0 + j : col0;
-                            int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc) + row_term;
-                            float comp = p.composite;
-                            if (p.corr) acc = (int)((uint32_t)acc + (uint32_t)__ldg(p.corr + cc));
-                            if (p.comp_pc) comp = __ldg(p.comp_pc + cc);
-                            // separate multiply and add: the CPU kernel does not fuse them
-                            const float v = __fadd_rn(__fmul_rn((float)acc, comp), p.y_zp);
-                            const float rr = p.round_mode ? roundf(v) : rintf(v);
-                            int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
-                            if (p.relu && qv < 0) qv = 0;
-                            if ((j & 3) == 0) packed[j >> 2] = 0;
-                            packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
+                            for (int j = 0; j < 32; ++j) {
+                                const int cc = (col0 + j < p.N) ? col0 + j : col0;
+                                int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc) + row_term;
+                                float comp = p.composite;
+                                if (p.corr) acc = (int)((uint32_t)acc + (uint32_t)__ldg(p.corr + cc));
+                                if (p.comp_pc) comp = __ldg(p.comp_pc + cc);
+                                // separate multiply and add: the CPU kernel does not fuse them
+                                const float v = __fadd_rn(__fmul_rn((float)acc, comp), p.y_zp);
+                                const float rr = p.round_mode ? roundf(v) : rintf(v);
+                                int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
+                                if (p.relu && qv < 0) qv = 0;
+                                if ((j & 3) == 0) packed[j >> 2] = 0;
+                                packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const int cc = (col0 + j < p.N) ? col0 + j : col0;
+                                const int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc);
+                                // separate multiply and add: the CPU kernel does not fuse them
+                                const float v = __fadd_rn(__fmul_rn((float)acc, p.composite), p.y_zp);
+                                const float rr = p.round_mode ? roundf(v) : rintf(v);
+                                const int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
+                                if ((j & 3) == 0) packed[j >> 2] = 0;
+                                packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
+                            }
                         }
                         if (col0 + 32 <= p.N && (p.ldc & 15) == 0) {
                             *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
