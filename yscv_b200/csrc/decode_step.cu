@@ -346,6 +346,7 @@ __device__ __forceinline__ void finish_rows(float *red, int tiles, int row_base,
 // (the head's q/k/v, up to 128 cached key rows, the value rows) is issued before anything
 // else; rows past the current position are fetched speculatively (the cache holds max_seq
 // rows) and never used.
+template <int VB>   // value rows whose loads are in flight together past the prefetched ones
 __device__ __forceinline__ void attention_head(const StepParams &p, int layer, int h, int split, int pos,
                                                float *kc, float *vc, const float *rope_cs,
                                                float *scratch, float *misc) {
@@ -422,22 +423,41 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
     const int nk = k1 - k0;
     const float4 *q4 = reinterpret_cast<const float4 *>(qs + sub * (d / 4));
     float mx = -INFINITY;
+    auto quarter_dot = [&](const float4 (&kv)[KQ]) {
+        float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < KQ; ++j) {
+            if (j < q4n) {
+                const float4 qv = q4[j];
+                d0 = fmaf(qv.x, kv[j].x, d0);
+                d1 = fmaf(qv.y, kv[j].y, d1);
+                d2 = fmaf(qv.z, kv[j].z, d2);
+                d3 = fmaf(qv.w, kv[j].w, d3);
+            }
+        }
+        return (d0 + d1) + (d2 + d3);
+    };
+    // the new position's key comes from shared memory: patch it into the prefetched registers
+    // or load it in its pass
+    if (k0 + kq == pos) {
+        const float4 *kcur4 = reinterpret_cast<const float4 *>(kcur + sub * (d / 4));
+#pragma unroll
+        for (int j = 0; j < KQ; ++j) kreg[j] = j < q4n ? kcur4[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
     for (int kk = kq, pass = 0; kk < ((nk + 127) & ~127); kk += DS_CONSUMERS / 4, ++pass) {
         const int key = k0 + kk;
         float dot = 0.0f;
         if (kk < nk) {
-            const float4 *kcur4 = reinterpret_cast<const float4 *>(kcur + sub * (d / 4));
-            const float4 *krow = reinterpret_cast<const float4 *>(kbase + (size_t)key * kv_stride + sub * (d / 4));
+            if (pass == 0) {
+                dot = quarter_dot(kreg);
+            } else {
+                // all of the row quarter's loads first, then the arithmetic
+                const float4 *krow = key == pos ? reinterpret_cast<const float4 *>(kcur + sub * (d / 4))
+                                                : reinterpret_cast<const float4 *>(kbase + (size_t)key * kv_stride + sub * (d / 4));
+                float4 kv[KQ];
 #pragma unroll
-            for (int j = 0; j < KQ; ++j) {
-                if (j < q4n) {
-                    const float4 kv = key == pos ? kcur4[j] : (pass == 0 ? kreg[j] : __ldg(krow + j));
-                    const float4 qv = q4[j];
-                    dot = fmaf(qv.x, kv.x, dot);
-                    dot = fmaf(qv.y, kv.y, dot);
-                    dot = fmaf(qv.z, kv.z, dot);
-                    dot = fmaf(qv.w, kv.w, dot);
-                }
+                for (int j = 0; j < KQ; ++j) kv[j] = j < q4n ? krow[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                dot = quarter_dot(kv);
             }
         }
         // every lane takes part in the shuffles (the loop bound is a multiple of 128 keys)
@@ -475,15 +495,25 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
             acc.w = fmaf(w, v.w, acc.w);
         }
     }
-#pragma unroll 8
-    for (int kk = part + NV * nparts; kk < nk; kk += nparts) {
-        const float4 v = k0 + kk == pos ? vcur4
-                                        : __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)(k0 + kk) * kv_stride) + c4);
-        const float w = scores[kk];
-        acc.x = fmaf(w, v.x, acc.x);
-        acc.y = fmaf(w, v.y, acc.y);
-        acc.z = fmaf(w, v.z, acc.z);
-        acc.w = fmaf(w, v.w, acc.w);
+    // the rest of the part's keys, VB rows' loads in flight at a time
+    for (int kb = part + NV * nparts; kb < nk; kb += VB * nparts) {
+        float4 v[VB];
+#pragma unroll
+        for (int j = 0; j < VB; ++j) {
+            const int kk = kb + j * nparts;
+            v[j] = (kk < nk && k0 + kk != pos)
+                       ? __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)(k0 + kk) * kv_stride) + c4)
+                       : vcur4;
+        }
+#pragma unroll
+        for (int j = 0; j < VB; ++j) {
+            const int kk = kb + j * nparts;
+            const float w = kk < nk ? scores[kk] : 0.0f;
+            acc.x = fmaf(w, v[j].x, acc.x);
+            acc.y = fmaf(w, v[j].y, acc.y);
+            acc.z = fmaf(w, v[j].z, acc.z);
+            acc.w = fmaf(w, v[j].w, acc.w);
+        }
     }
     *(reinterpret_cast<float4 *>(partial + (size_t)part * d) + c4) = acc;
     ATRACE(5);
@@ -813,7 +843,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         STRACE(ts + 4);
         // RoPE, cache append, attention: a few CTAs per query head
         if ((int)blockIdx.x < p.n_q * p.splits)
-            attention_head(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
+            attention_head<SIMPLE ? 4 : 8>(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
                            cache_ptr[2 * l + 1], rope_cs, act_s, misc);
         STRACE(ts + 5);
         grid_barrier(p, epoch);
