@@ -254,6 +254,8 @@ def test_fused_step_logits_match_operator_chain(tctx):
     {"YSCV_CUDA_STEP_MAX_TILES": "2", "YSCV_CUDA_STEP_KCHUNK": "1024"},                                  # default variant
     {"YSCV_CUDA_STEP_MAX_TILES": "2", "YSCV_CUDA_STEP_KCHUNK": "1024", "YSCV_CUDA_STEP_VARIANT": "0"},   # plain
     {"YSCV_CUDA_STEP_MAX_TILES": "4", "YSCV_CUDA_STEP_KCHUNK": "1536", "YSCV_CUDA_STEP_VARIANT": "5"},
+    {"YSCV_CUDA_STEP_ATTN": "1"},                                  # attention per KV head and key chunk + merge phase
+    {"YSCV_CUDA_STEP_ATTN": "1", "YSCV_CUDA_STEP_MAX_TILES": "2"},
 ])
 def test_fused_step_row_blocks_and_k_chunks(tctx, env):
     """Small shapes pushed through the paths large models take: several row blocks per CTA
@@ -287,6 +289,32 @@ def test_fused_step_row_blocks_and_k_chunks(tctx, env):
             os.environ.pop(k, None)
         ctx.set_int4_prefill_exact(False)
     assert toks[0] == toks[1]
+    for a, b in zip(*logs):
+        assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
+    assert ctx.device_status() == 0
+
+
+def test_fused_step_grouped_attention_long_cache(tctx):
+    """A cache long enough that the plan picks attention per KV head and key chunk by itself,
+    with more than 128 keys per chunk (the passes past the prefetched rows)."""
+    import torch
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=2, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
+    P, steps = 4300, 3
+    prompt = dev(synth.uniform_int(35, 9, P, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    logs = []
+    for fused in (False, True):
+        dec = Int4Decoder(ctx, cfg, 1, P + steps + 1, s, seed=17, fused_step=fused)
+        assert (dec.plan is not None) == fused
+        dec.prefill(prompt)
+        lg = []
+        for _ in range(steps):
+            with torch.cuda.stream(s):
+                out = dec.forward(dec.next_tokens, 1)
+            s.synchronize()
+            lg.append(out.cpu().numpy().copy())
+        logs.append(lg)
+        dec.close()
     for a, b in zip(*logs):
         assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
     assert ctx.device_status() == 0
@@ -329,12 +357,18 @@ def test_fused_step_long_context_and_limits(tctx):
     import yscv_b200
     ctx, s = tctx
     cfg = DecoderConfig(layers=2, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
+    import os
     P, steps = 700, 4   # 148 // 8 -> 4 splits per head: 175+ keys each
     prompt = dev(synth.uniform_int(33, 9, P, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
     logs = []
-    for fused in (False, True):
-        dec = Int4Decoder(ctx, cfg, 1, P + steps, s, seed=14, fused_step=fused)   # the last step fills the cache
-        assert (dec.plan is not None) == fused
+    for fused in (False, True, "grouped"):
+        if fused == "grouped":   # 32 chunks per KV head; with 5000 cache slots more than 128 keys per chunk
+            os.environ["YSCV_CUDA_STEP_ATTN"] = "1"
+        try:
+            dec = Int4Decoder(ctx, cfg, 1, P + steps, s, seed=14, fused_step=bool(fused))   # the last step fills the cache
+        finally:
+            os.environ.pop("YSCV_CUDA_STEP_ATTN", None)
+        assert (dec.plan is not None) == bool(fused)
         dec.prefill(prompt)
         lg = []
         for _ in range(steps):
@@ -344,8 +378,9 @@ def test_fused_step_long_context_and_limits(tctx):
             lg.append(out.cpu().numpy().copy())
         logs.append(lg)
         dec.close()
-    for a, b in zip(*logs):
+    for a, b, c in zip(*logs):
         assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
+        assert np.linalg.norm(a - c) / np.linalg.norm(a) < 1e-5
     assert ctx.device_status() == 0
     # K not a multiple of 512, fewer rows than SMs, too many heads: refused when the plan is built
     for bad in (DecoderConfig(layers=1, hidden=768, mlp=1024, n_q=12, n_kv=4, head_dim=64, vocab=100),

@@ -69,6 +69,11 @@ struct StepParams {
     float *x;                 // [hidden] residual stream, result of the step
     float *qkv, *attn, *gu;   // scratch between operators; attn = [n_q][splits][d_head + 2]
     int splits;               // CTAs per query head in the attention phase
+    // grouped attention (long contexts): one CTA per (KV head, key chunk) serves all the query
+    // heads of the group from one pass over the chunk's keys and values; a short second phase
+    // merges the g_splits chunks of every head into attn_out [n_q][d_head]
+    int attn_grouped, g_splits, g_chunk_cap;
+    float *attn_out;
     unsigned int *sync;       // [0] barrier arrivals, [1] CTAs that left, [2] abort flag
     int *status;
     int layers, hidden, inter, n_q, n_kv, d_head, max_seq, vocab;
@@ -337,6 +342,217 @@ __device__ __forceinline__ void finish_rows(float *red, int tiles, int row_base,
     cons_sync();  // `red` is reused by the next block
 }
 
+// Grouped attention, phase 1. CTA (kvh, split): RoPE of the group's queries and of the new key,
+// cache append (the split that holds the new position), scores of all the group's query heads
+// against this split's keys (the key row quarter a thread holds serves every head), a local
+// softmax per head, the unnormalised weighted value sums. Leaves {acc[d], max, exp-sum} per
+// (query head, split) in p.attn. Scratch: q [grp][d], new k and v [d] each, partial sums
+// [parts][grp][d], 32 floats, scores [grp][chunk_cap].
+__device__ __forceinline__ void attention_group(const StepParams &p, int kvh, int split, int pos,
+                                                float *kc, float *vc, const float *rope_cs,
+                                                float *scratch) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int d = p.d_head, half = d / 2;
+    const int grp = p.n_q / p.n_kv, S = p.g_splits, cap = p.g_chunk_cap;
+    const int vecs = d / 4, parts = DS_CONSUMERS / (grp * vecs);
+    float *qs = scratch, *kcur = qs + grp * d, *vcur = kcur + d, *partial = vcur + d;
+    float *wred = partial + parts * grp * d, *scores = wred + 32;
+    const size_t kv_stride = (size_t)p.n_kv * d;
+    const float *kbase = kc + (size_t)kvh * d, *vbase = vc + (size_t)kvh * d;
+    const int limit = pos + 1;
+    const int chunk = (limit + S - 1) / S;
+    const int k0 = split * chunk, k1 = min(limit, k0 + chunk);
+    const int h0 = kvh * grp;   // first query head of the group
+    if (k0 >= k1) {  // nothing for this split yet: the neutral element of the merge
+        for (int i = tid; i < grp * (d + 2); i += DS_CONSUMERS) {
+            const int hh = i / (d + 2), j = i - hh * (d + 2);
+            p.attn[((size_t)(h0 + hh) * S + split) * (d + 2) + j] = j == d ? -INFINITY : 0.0f;
+        }
+        return;
+    }
+    const int nk = k1 - k0;
+    const bool has_new = pos >= k0 && pos < k1;
+
+    // ---- loads: the first 128 key rows of the chunk (a quarter row per thread), q, new k, v ----
+    constexpr int KQ = 8;
+    const int kq = tid >> 2, sub = tid & 3, q4n = d / 16;
+    float4 kreg[KQ];
+#pragma unroll
+    for (int j = 0; j < KQ; ++j)
+        kreg[j] = (j < q4n && k0 + kq < p.max_seq)
+                      ? __ldg(reinterpret_cast<const float4 *>(kbase + (size_t)(k0 + kq) * kv_stride + sub * (d / 4)) + j)
+                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    // one rotary pair per thread: the group's queries (grp * d/2 pairs), then the new key
+    for (int i = tid; i < (grp + 1) * half; i += DS_CONSUMERS) {
+        const int hh = i / half, ri = i - hh * half;
+        const bool is_k = hh == grp;
+        const float *src = p.qkv + (size_t)(is_k ? p.n_q + kvh : h0 + hh) * d;
+        const float x0 = __ldcg(src + ri), x1 = __ldcg(src + ri + half);
+        const float cs = rope_cs[2 * ri], sn = rope_cs[2 * ri + 1];
+        const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
+        float *dst = is_k ? kcur : qs + hh * d;
+        dst[ri] = y0;
+        dst[ri + half] = y1;
+        if (is_k && has_new) {
+            float *cd = kc + ((size_t)pos * p.n_kv + kvh) * d;
+            cd[ri] = y0;
+            cd[ri + half] = y1;
+        }
+    }
+    for (int i = tid; i < d; i += DS_CONSUMERS) {
+        const float v = __ldcg(p.qkv + (size_t)(p.n_q + p.n_kv + kvh) * d + i);
+        vcur[i] = v;
+        if (has_new) vc[((size_t)pos * p.n_kv + kvh) * d + i] = v;
+    }
+    cons_sync();
+
+    // ---- scores: four threads per key; the quarter row in registers serves every query head ----
+    const float scale = 1.0f / sqrtf((float)d);
+    if (k0 + kq == pos) {
+        const float4 *kcur4 = reinterpret_cast<const float4 *>(kcur + sub * (d / 4));
+#pragma unroll
+        for (int j = 0; j < KQ; ++j) kreg[j] = j < q4n ? kcur4[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    for (int kk = kq, pass = 0; kk < ((nk + 127) & ~127); kk += DS_CONSUMERS / 4, ++pass) {
+        const int key = k0 + kk;
+        if (pass > 0 && kk < nk) {
+            const float4 *krow = key == pos ? reinterpret_cast<const float4 *>(kcur + sub * (d / 4))
+                                            : reinterpret_cast<const float4 *>(kbase + (size_t)key * kv_stride + sub * (d / 4));
+#pragma unroll
+            for (int j = 0; j < KQ; ++j) kreg[j] = j < q4n ? krow[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        for (int hh = 0; hh < grp; ++hh) {
+            const float4 *q4 = reinterpret_cast<const float4 *>(qs + hh * d + sub * (d / 4));
+            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < KQ; ++j) {
+                if (j < q4n) {
+                    const float4 qv = q4[j];
+                    d0 = fmaf(qv.x, kreg[j].x, d0);
+                    d1 = fmaf(qv.y, kreg[j].y, d1);
+                    d2 = fmaf(qv.z, kreg[j].z, d2);
+                    d3 = fmaf(qv.w, kreg[j].w, d3);
+                }
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+            // every lane takes part in the shuffles (the loop bound is a multiple of 128 keys)
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            if (kk < nk && sub == 0) scores[hh * cap + kk] = dot * scale;
+        }
+    }
+    cons_sync();
+
+    // ---- softmax per head: 16 / grp warps per head ----
+    const int wph = DS_CONSUMER_WARPS / grp, hh_w = warp / wph, wi = warp - hh_w * wph;
+    float *sc = scores + hh_w * cap;
+    float mx = -INFINITY;
+    for (int kk = wi * 32 + lane; kk < nk; kk += wph * 32) mx = fmaxf(mx, sc[kk]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) wred[warp] = mx;
+    cons_sync();
+    mx = -INFINITY;
+    for (int i = 0; i < wph; ++i) mx = fmaxf(mx, wred[hh_w * wph + i]);
+    cons_sync();
+    float se = 0.0f;
+    for (int kk = wi * 32 + lane; kk < nk; kk += wph * 32) {
+        const float e = expf(sc[kk] - mx);
+        sc[kk] = e;
+        se += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+    if (lane == 0) wred[warp] = se;
+    cons_sync();  // (also publishes the exponentials)
+    if (wi == 0 && lane == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < wph; ++i) t += wred[hh_w * wph + i];
+        float *po = p.attn + ((size_t)(h0 + hh_w) * S + split) * (d + 2);
+        po[d] = mx;
+        po[d + 1] = t;
+    }
+
+    // ---- weighted values: thread (part, head, float4 column); the group's heads re-read the
+    // same value rows, which the L1 serves ----
+    const int c4 = tid % vecs, hv = (tid / vecs) % grp, part = tid / (vecs * grp);
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (part < parts) {
+        const float *w = scores + hv * cap;
+        const float4 vcur4 = *(reinterpret_cast<const float4 *>(vcur) + c4);
+        for (int kb = part; kb < nk; kb += 8 * parts) {
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int kk = kb + j * parts;
+                v[j] = (kk < nk && k0 + kk != pos)
+                           ? __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)(k0 + kk) * kv_stride) + c4)
+                           : vcur4;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int kk = kb + j * parts;
+                const float ww = kk < nk ? w[kk] : 0.0f;
+                acc.x = fmaf(ww, v[j].x, acc.x);
+                acc.y = fmaf(ww, v[j].y, acc.y);
+                acc.z = fmaf(ww, v[j].z, acc.z);
+                acc.w = fmaf(ww, v[j].w, acc.w);
+            }
+        }
+        *(reinterpret_cast<float4 *>(partial + ((size_t)part * grp + hv) * d) + c4) = acc;
+    }
+    cons_sync();
+    for (int i = tid; i < grp * d; i += DS_CONSUMERS) {
+        const int hh = i / d, dd = i - hh * d;
+        float v = 0.0f;
+        for (int pt = 0; pt < parts; ++pt) v += partial[((size_t)pt * grp + hh) * d + dd];
+        p.attn[((size_t)(h0 + hh) * S + split) * (d + 2) + dd] = v;
+    }
+    cons_sync();  // scratch is reused
+}
+
+// Grouped attention, phase 2: CTA h merges the g_splits (<= 32) partial results of query head h
+// (the usual max-rescaling of a split softmax) into attn_out[h][d_head]. The 512 threads form
+// 512 / d_head groups that take the splits round-robin, every load of a thread in flight at once.
+__device__ __forceinline__ void attention_merge(const StepParams &p, int h, float *scratch, float *misc) {
+    const int tid = threadIdx.x, d = p.d_head, S = p.g_splits;
+    const int G = DS_CONSUMERS / d, g = tid / d, dd = tid - g * d;   // d divides 512
+    const float *pp = p.attn + (size_t)h * S * (d + 2);
+    float m[8], e[8], a[8];   // ceil(32 / G) <= 8 for d_head <= 128
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int sp = g + j * G;
+        const bool on = sp < S;
+        m[j] = on ? __ldcg(pp + (size_t)sp * (d + 2) + d) : -INFINITY;
+        e[j] = on ? __ldcg(pp + (size_t)sp * (d + 2) + d + 1) : 0.0f;
+        a[j] = on ? __ldcg(pp + (size_t)sp * (d + 2) + dd) : 0.0f;
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) M = fmaxf(M, m[j]);
+    M = cons_max(M, misc);
+    float L = 0.0f, v = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float w = m[j] > -INFINITY ? expf(m[j] - M) : 0.0f;
+        L = fmaf(w, e[j], L);
+        v = fmaf(w, a[j], v);
+    }
+    // scratch: [G][d] partial sums, then [G] partial exp-sums
+    scratch[g * d + dd] = v;
+    if (dd == 0) scratch[G * d + g] = L;
+    cons_sync();
+    if (tid < d) {
+        float vs = 0.0f, Ls = 0.0f;
+        for (int i = 0; i < G; ++i) {
+            vs += scratch[i * d + tid];
+            Ls += scratch[G * d + i];
+        }
+        p.attn_out[(size_t)h * d + tid] = Ls > 0.0f ? vs / Ls : 0.0f;
+    }
+    cons_sync();  // scratch is reused
+}
+
 // Attention of the one query of head h over positions 0 .. pos, the keys dealt in contiguous
 // chunks to p.splits CTAs per head: RoPE of the head's q and of its KV head's new k, cache
 // append (one CTA per KV head), then this CTA's chunk of scores, a local softmax and the
@@ -528,8 +744,9 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
     cons_sync();  // scratch is reused
 }
 
-// SIMPLE: every matrix is one row block and one K chunk per CTA (small models); the loops over
-// blocks and chunks then fold away at compile time, which is worth 7 % of a TinyLlama step.
+// SIMPLE: every matrix is one row block and one K chunk per CTA and attention runs per query
+// head (small models, short contexts); the loops over blocks and chunks then fold away at
+// compile time, which is worth 7 % of a TinyLlama step.
 template <bool SIMPLE>
 __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -731,7 +948,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     // merge of the attention splits (the usual max-rescaling of a split softmax)
     auto stage_attention = [&]() {
         const int AW = p.n_q * p.d_head;
-        if (p.merge_table) {
+        if (!SIMPLE && p.attn_grouped) {
+#pragma unroll 4
+            for (int i = tid; i < AW; i += DS_CONSUMERS) act_s[i] = __ldcg(p.attn_out + i);
+        } else if (p.merge_table) {
             // per (head, split): weight exp(m - M) / L once, through shared memory
             if (tid < p.n_q) {
                 const float *pp = p.attn + (size_t)tid * p.splits * (p.d_head + 2) + p.d_head;
@@ -841,10 +1061,18 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         STRACE(ts + 3);
         grid_barrier(p, epoch);
         STRACE(ts + 4);
-        // RoPE, cache append, attention: a few CTAs per query head
-        if ((int)blockIdx.x < p.n_q * p.splits)
+        // RoPE, cache append, attention: a few CTAs per query head, or (long contexts) one CTA
+        // per KV head and key chunk followed by a merge phase
+        if (!SIMPLE && p.attn_grouped) {
+            if ((int)blockIdx.x < p.n_kv * p.g_splits)
+                attention_group(p, blockIdx.x / p.g_splits, blockIdx.x % p.g_splits, pos, cache_ptr[2 * l],
+                                cache_ptr[2 * l + 1], rope_cs, act_s);
+            grid_barrier(p, epoch);
+            if ((int)blockIdx.x < p.n_q) attention_merge(p, blockIdx.x, act_s, misc);
+        } else if ((int)blockIdx.x < p.n_q * p.splits) {
             attention_head<SIMPLE ? 4 : 8>(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
                            cache_ptr[2 * l + 1], rope_cs, act_s, misc);
+        }
         STRACE(ts + 5);
         grid_barrier(p, epoch);
         STRACE(ts + 6);
@@ -1012,9 +1240,22 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
                          "needs both several chunks and several row blocks", hidden, attn_w, kc_stages * 512));
     p.kc_stages = kc_stages;
     p.dig_bytes = kc_stages * DS_BLOB_BYTES;
-    // the attention scratch (q, k, v of the head, partial sums, scores) lives in the activation
-    // area between the GEMVs: widen that area if it needs more
-    const size_t attn_scratch = (3 * d_head + 4 * DS_CONSUMERS + max_seq) * sizeof(float);
+    // attention form: per query head with up to 4 key chunks, or (long contexts, or
+    // YSCV_CUDA_STEP_ATTN=1) per KV head with up to 32 key chunks and a merge phase
+    const int splits = (int)std::min<size_t>(4, (size_t)grid / n_q);
+    const size_t grp = n_q / n_kv;
+    const bool group_ok = (grp & (grp - 1)) == 0 && grp <= 16 && grp * d_head <= 2048 &&
+                          DS_CONSUMERS % (grp * d_head / 4) == 0;
+    const char *aenv = getenv("YSCV_CUDA_STEP_ATTN");
+    const bool grouped = group_ok && (aenv ? atoi(aenv) != 0 : (max_seq + splits - 1) / splits > 256);
+    const int g_splits = (int)std::max<size_t>(1, std::min<size_t>(32, (size_t)grid / n_kv));
+    const int g_cap = (int)(((max_seq + g_splits - 1) / g_splits + 3) / 4 * 4);
+    // the attention scratch lives in the activation area between the GEMVs: widen that area if
+    // it needs more
+    const size_t g_parts = DS_CONSUMERS / (grp * d_head / 4 ? grp * d_head / 4 : 1);
+    const size_t attn_scratch =
+        grouped ? (grp * d_head + 2 * d_head + g_parts * grp * d_head + 32 + grp * (size_t)g_cap) * sizeof(float)
+                : (3 * d_head + 4 * DS_CONSUMERS + max_seq) * sizeof(float);
     size_t act_floats = (size_t)kc_stages * 512;
     if (attn_scratch > act_floats * 4) act_floats = (attn_scratch + 3) / 4;
     act_floats = (act_floats + 3) / 4 * 4;
@@ -1034,9 +1275,8 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     // device copies: matrices, gammas, cache pointers, scratch, barrier words
     std::vector<float *> kptr(n_layers), vptr(n_layers);
     for (size_t l = 0; l < n_layers; ++l) { kptr[l] = layers[l].d_kcache; vptr[l] = layers[l].d_vcache; }
-    const int splits = (int)std::min<size_t>(4, (size_t)grid / n_q);
-    const size_t attn_floats = n_q * splits * (d_head + 2);
-    const size_t scratch_floats = qkv_rows + attn_floats + 2 * inter;
+    const size_t attn_floats = n_q * (size_t)(grouped ? g_splits : splits) * (d_head + 2);
+    const size_t scratch_floats = qkv_rows + attn_floats + 2 * inter + attn_w;
 #define PLAN_TRY(expr)                                                                       \
     do {                                                                                     \
         cudaError_t _e = (expr);                                                             \
@@ -1059,7 +1299,8 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
         PLAN_TRY(cudaMemcpyAsync(g + hidden, layers[l].d_gamma_mlp, hidden * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     }
     PLAN_TRY(cudaStreamSynchronize(ctx->stream));  // the host vectors go out of scope
-    plan->simple = nrb[0] == 1 && nrb[1] == 1 && nrb[2] == 1 && nrb[3] == 1 && (int)(k_max / 512) <= kc_stages;
+    plan->simple = nrb[0] == 1 && nrb[1] == 1 && nrb[2] == 1 && nrb[3] == 1 && (int)(k_max / 512) <= kc_stages &&
+                   !grouped;
     auto kern = plan->simple ? decode_step_kernel<true> : decode_step_kernel<false>;
     PLAN_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan->smem));
     int per_sm = 0;
@@ -1074,7 +1315,11 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     p.qkv = s;
     p.attn = s + qkv_rows;
     p.gu = p.attn + attn_floats;
+    p.attn_out = p.gu + 2 * inter;
     p.splits = splits;
+    p.attn_grouped = grouped ? 1 : 0;
+    p.g_splits = g_splits;
+    p.g_chunk_cap = g_cap;
     p.sync = reinterpret_cast<unsigned int *>(plan->d_sync);
     p.status = ctx->d_status;
     p.layers = (int)n_layers;
