@@ -349,6 +349,15 @@ int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_pl
                                    const float *d_embedding, size_t vocab, const int32_t *d_token,
                                    const int32_t *d_pos, float *d_x);
 
+/* The same step followed, in the same launch, by what llm-bench does after the graph
+ * (apps/llm-bench/src/main.rs:536-543): the final RMSNorm (d_final_gamma [hidden]), the fp32 LM
+ * head d_lm_head [vocab][hidden] -> d_logits [vocab], the greedy token (last index among equal
+ * maxima) written to *d_token, and *d_pos += 1. d_x receives the residual stream as above. */
+int yscv_cuda_decode_plan_step_token_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
+                                         const float *d_embedding, size_t vocab, int32_t *d_token,
+                                         int32_t *d_pos, const float *d_final_gamma,
+                                         const float *d_lm_head, float *d_x, float *d_logits);
+
 void yscv_cuda_decode_plan_free(yscv_cuda_decode_plan *plan);
 
 #ifdef __cplusplus

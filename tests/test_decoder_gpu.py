@@ -294,6 +294,41 @@ def test_fused_step_row_blocks_and_k_chunks(tctx, env):
     assert ctx.device_status() == 0
 
 
+def test_decode_plan_step_without_tail(tctx):
+    """yscv_cuda_decode_plan_step_dev (layers only) leaves the same residual stream as the
+    full step, touches neither the token nor the position, and the operator tail on top of it
+    gives the same logits."""
+    import torch
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=2, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=777)
+    prompt = dev(synth.uniform_int(41, 9, 18, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    decs = [Int4Decoder(ctx, cfg, 1, 32, s, seed=19) for _ in range(2)]
+    for d_ in decs:
+        d_.prefill(prompt)
+    a, b = decs
+    with torch.cuda.stream(s):
+        logits = a.forward(a.next_tokens, 1).clone()           # full step
+        xa = a._buf("x", 1, cfg.hidden).clone()
+        tok_before, pos_before = b.next_tokens.clone(), b.pos.clone()
+        xb = torch.empty(1, cfg.hidden, device="cuda")
+        b.plan.step_dev(b.embedding.data_ptr(), cfg.vocab, b.next_tokens.data_ptr(), b.pos.data_ptr(), xb.data_ptr())
+        h = torch.empty_like(xb)
+        lg = torch.empty(1, cfg.vocab, device="cuda")
+        ctx.add_rms_norm_dev(xb.data_ptr(), 0, b.gamma.data_ptr(), cfg.eps, 1, cfg.hidden, xb.data_ptr(), h.data_ptr())
+        ctx.f32_matmul_dev(b.lm_head.data_ptr(), h.data_ptr(), 1, cfg.vocab, cfg.hidden, lg.data_ptr())
+    s.synchronize()
+    assert torch.equal(xa, xb)
+    assert torch.equal(b.next_tokens, tok_before) and torch.equal(b.pos, pos_before)
+    assert int(a.pos.item()) == int(pos_before.item()) + 1
+    rel = float(torch.linalg.norm(lg - logits) / torch.linalg.norm(logits))
+    assert rel < 1e-5, rel
+    mx = logits[0].max()
+    assert float(logits[0, int(a.next_tokens.item())]) == float(mx)   # the greedy token is a maximum
+    for d_ in decs:
+        d_.close()
+    assert ctx.device_status() == 0
+
+
 def test_fused_step_grouped_attention_long_cache(tctx):
     """A cache long enough that the plan picks attention per KV head and key chunk by itself,
     with more than 128 keys per chunk (the passes past the prefetched rows)."""

@@ -74,6 +74,14 @@ struct StepParams {
     // merges the g_splits chunks of every head into attn_out [n_q][d_head]
     int attn_grouped, g_splits, g_chunk_cap;
     float *attn_out;
+    // optional tail (tail != 0): final RMSNorm, fp32 LM head [vocab][hidden] -> logits [vocab],
+    // greedy argmax (last index among equal maxima) into *token_out, *pos_out = position + 1
+    int tail;
+    const float *final_gamma, *lm_head;
+    float *logits;
+    float *best_val;          // [gridDim.x] per-CTA maxima
+    int *best_idx;
+    int32_t *token_out, *pos_out;
     unsigned int *sync;       // [0] barrier arrivals, [1] CTAs that left, [2] abort flag
     int *status;
     int layers, hidden, inter, n_q, n_kv, d_head, max_seq, vocab;
@@ -1092,6 +1100,67 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         STRACE(ts + 15);
     }
 
+    // ---- optional tail: final norm, LM head, greedy token ----
+    if (p.tail) {
+        stage_norm(p.final_gamma);   // act_s = the normalised last hidden state
+        const int v0 = (int)(((unsigned long long)p.vocab * blockIdx.x) / gridDim.x);
+        const int v1 = (int)(((unsigned long long)p.vocab * (blockIdx.x + 1)) / gridDim.x);
+        // one warp per vocabulary row, the same summation order as f32_matmul_kernel
+        float best = -INFINITY;
+        int besti = -1;
+        const float4 *x4 = reinterpret_cast<const float4 *>(act_s);
+        for (int row = v0 + warp; row < v1; row += DS_CONSUMER_WARPS) {
+            const float4 *wr = reinterpret_cast<const float4 *>(p.lm_head + (size_t)row * H);
+            float acc = 0.0f;
+#pragma unroll 4
+            for (int cidx = lane; cidx < H / 4; cidx += 32) {
+                const float4 wv = __ldg(wr + cidx), xv = x4[cidx];
+                acc = fmaf(wv.x, xv.x, acc);
+                acc = fmaf(wv.y, xv.y, acc);
+                acc = fmaf(wv.z, xv.z, acc);
+                acc = fmaf(wv.w, xv.w, acc);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) p.logits[row] = acc;
+            if (besti < 0 || !(acc < best)) { best = acc; besti = row; }  // later index wins ties
+        }
+        // CTA maximum: rows ascend within a warp, warps interleave rows -> compare (value, index)
+        float *bv = misc;
+        int *bi = reinterpret_cast<int *>(misc + 16);
+        cons_sync();
+        if (lane == 0) { bv[warp] = best; bi[warp] = besti; }
+        cons_sync();
+        if (tid == 0) {
+            float b = -INFINITY;
+            int ib = -1;
+            for (int i = 0; i < DS_CONSUMER_WARPS; ++i)
+                if (bi[i] >= 0 && (ib < 0 || bv[i] > b || (bv[i] == b && bi[i] > ib))) { b = bv[i]; ib = bi[i]; }
+            p.best_val[blockIdx.x] = b;
+            p.best_idx[blockIdx.x] = ib;
+        }
+        grid_barrier(p, epoch);
+        if (blockIdx.x == 0 && warp == 0) {
+            float b = -INFINITY;
+            int ib = -1;
+            for (int i = lane; i < (int)gridDim.x; i += 32) {
+                const float v = __ldcg(p.best_val + i);
+                const int iv = __ldcg(p.best_idx + i);
+                if (iv >= 0 && (ib < 0 || v > b || (v == b && iv > ib))) { b = v; ib = iv; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float v = __shfl_xor_sync(0xffffffffu, b, o);
+                const int iv = __shfl_xor_sync(0xffffffffu, ib, o);
+                if (iv >= 0 && (ib < 0 || v > b || (v == b && iv > ib))) { b = v; ib = iv; }
+            }
+            if (lane == 0) {
+                *p.token_out = ib < 0 ? 0 : ib;
+                *p.pos_out = pos + 1;
+            }
+        }
+    }
+
     // the last CTA to leave resets the barrier words for the next launch
     if (tid == 0) {
         __threadfence();
@@ -1276,7 +1345,7 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     std::vector<float *> kptr(n_layers), vptr(n_layers);
     for (size_t l = 0; l < n_layers; ++l) { kptr[l] = layers[l].d_kcache; vptr[l] = layers[l].d_vcache; }
     const size_t attn_floats = n_q * (size_t)(grouped ? g_splits : splits) * (d_head + 2);
-    const size_t scratch_floats = qkv_rows + attn_floats + 2 * inter + attn_w;
+    const size_t scratch_floats = qkv_rows + attn_floats + 2 * inter + attn_w + 2 * (size_t)grid;
 #define PLAN_TRY(expr)                                                                       \
     do {                                                                                     \
         cudaError_t _e = (expr);                                                             \
@@ -1316,6 +1385,8 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     p.attn = s + qkv_rows;
     p.gu = p.attn + attn_floats;
     p.attn_out = p.gu + 2 * inter;
+    p.best_val = p.attn_out + attn_w;
+    p.best_idx = reinterpret_cast<int *>(p.best_val + grid);
     p.splits = splits;
     p.attn_grouped = grouped ? 1 : 0;
     p.g_splits = g_splits;
@@ -1348,20 +1419,8 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     return YSCV_CUDA_OK;
 }
 
-extern "C" int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
-                                              const float *d_embedding, size_t vocab, const int32_t *d_token,
-                                              const int32_t *d_pos, float *d_x) {
+static int launch_step(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan, yscv::StepParams &p) {
     using namespace yscv;
-    if (!ctx || !plan || !d_embedding || !d_token || !d_pos || !d_x || vocab == 0)
-        return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
-    if (plan->device != ctx->device) return fail(YSCV_CUDA_ERR_BAD_ARG, "plan belongs to device %d", plan->device);
-    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
-    StepParams p = plan->params;
-    p.embedding = d_embedding;
-    p.vocab = (int)vocab;
-    p.token = d_token;
-    p.pos = d_pos;
-    p.x = d_x;
     p.status = ctx->d_status;
     // the CTAs wait on one another: cooperative launch, one CTA per SM
     cudaLaunchConfig_t cfg = {};
@@ -1382,6 +1441,52 @@ extern "C" int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cud
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
-    ctx->last_kernel = "decode_step(persistent,tma,imma)";
+    ctx->last_kernel = p.tail ? "decode_step(persistent,tma,imma,+lm_head)" : "decode_step(persistent,tma,imma)";
     return YSCV_CUDA_OK;
+}
+
+extern "C" int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
+                                              const float *d_embedding, size_t vocab, const int32_t *d_token,
+                                              const int32_t *d_pos, float *d_x) {
+    using namespace yscv;
+    if (!ctx || !plan || !d_embedding || !d_token || !d_pos || !d_x || vocab == 0)
+        return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (plan->device != ctx->device) return fail(YSCV_CUDA_ERR_BAD_ARG, "plan belongs to device %d", plan->device);
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    StepParams p = plan->params;
+    p.embedding = d_embedding;
+    p.vocab = (int)vocab;
+    p.token = d_token;
+    p.pos = d_pos;
+    p.x = d_x;
+    p.tail = 0;
+    return launch_step(ctx, plan, p);
+}
+
+extern "C" int yscv_cuda_decode_plan_step_token_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
+                                                    const float *d_embedding, size_t vocab, int32_t *d_token,
+                                                    int32_t *d_pos, const float *d_final_gamma,
+                                                    const float *d_lm_head, float *d_x, float *d_logits) {
+    using namespace yscv;
+    if (!ctx || !plan || !d_embedding || !d_token || !d_pos || !d_x || !d_final_gamma || !d_lm_head ||
+        !d_logits || vocab == 0)
+        return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (plan->device != ctx->device) return fail(YSCV_CUDA_ERR_BAD_ARG, "plan belongs to device %d", plan->device);
+    if (vocab >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "vocabulary too large");
+    if ((reinterpret_cast<uintptr_t>(d_lm_head) & 15) != 0)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "the LM head must be 16-byte aligned");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    StepParams p = plan->params;
+    p.embedding = d_embedding;
+    p.vocab = (int)vocab;
+    p.token = d_token;
+    p.pos = d_pos;
+    p.x = d_x;
+    p.tail = 1;
+    p.final_gamma = d_final_gamma;
+    p.lm_head = d_lm_head;
+    p.logits = d_logits;
+    p.token_out = d_token;
+    p.pos_out = d_pos;
+    return launch_step(ctx, plan, p);
 }

@@ -177,12 +177,17 @@ class Int4Decoder:
         down = self._buf("down", rows, H)
         fused = self.plan is not None and seq == 1
         if fused:
-            self.plan.step_dev(self.embedding.data_ptr(), c.vocab, tokens.data_ptr(), self.pos.data_ptr(),
-                               x.data_ptr())
-        else:
-            ctx.embedding_dev(self.embedding.data_ptr(), c.vocab, H, tokens.data_ptr(), rows, x.data_ptr())
+            # the whole step in one launch: layers, final norm, LM head, greedy token, position
+            logits = self._buf("logits", B, c.vocab)
+            if tokens.data_ptr() != self.next_tokens.data_ptr():
+                self.next_tokens.copy_(tokens)
+            self.plan.step_token_dev(self.embedding.data_ptr(), c.vocab, self.next_tokens.data_ptr(),
+                                     self.pos.data_ptr(), self.gamma.data_ptr(), self.lm_head.data_ptr(),
+                                     x.data_ptr(), logits.data_ptr())
+            return logits
+        ctx.embedding_dev(self.embedding.data_ptr(), c.vocab, H, tokens.data_ptr(), rows, x.data_ptr())
         delta = 0
-        for l in range(0 if fused else self.n_layers):
+        for l in range(self.n_layers):
             ctx.add_rms_norm_dev(x.data_ptr(), delta, self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
             ctx.int4_matmul_dev(self.wqkv[l].handle, h.data_ptr(), qkv.data_ptr(), rows)
             ctx.rope_kv_append_dev(qkv.data_ptr(), B, seq, self.nq_l, self.nkv_l, d, c.rope_theta, self.pos.data_ptr(),

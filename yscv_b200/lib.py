@@ -83,6 +83,7 @@ SIGNATURES = {
     "yscv_cuda_decode_plan_create": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, C.c_float, C.c_float,
                                                C.POINTER(_vp)]),
     "yscv_cuda_decode_plan_step_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "yscv_cuda_decode_plan_step_token_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp]),
     "yscv_cuda_decode_plan_free": (None, [_vp]),
 }
 
@@ -197,6 +198,13 @@ class DecodePlan:
     def step_dev(self, d_embedding: int, vocab: int, d_token: int, d_pos: int, d_x: int):
         _check(self.ctx.lib.yscv_cuda_decode_plan_step_dev(self.ctx.handle, self.handle, _vp(d_embedding), vocab,
                                                            _vp(d_token), _vp(d_pos), _vp(d_x)))
+
+    def step_token_dev(self, d_embedding: int, vocab: int, d_token: int, d_pos: int, d_final_gamma: int,
+                       d_lm_head: int, d_x: int, d_logits: int):
+        """The step plus final norm, fp32 LM head, greedy token into *d_token and *d_pos += 1."""
+        _check(self.ctx.lib.yscv_cuda_decode_plan_step_token_dev(
+            self.ctx.handle, self.handle, _vp(d_embedding), vocab, _vp(d_token), _vp(d_pos), _vp(d_final_gamma),
+            _vp(d_lm_head), _vp(d_x), _vp(d_logits)))
 
     def free(self):
         if self.handle:
