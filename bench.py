@@ -413,7 +413,8 @@ def run_cuda(args):
 def extra_metrics(ctx, stream, dev):
     """int8 GEMM TOPS on BASELINE configs[2] (QLinearMatMul 2048x4096x4096, uint8 in/out) and
     configs[0] (MatMulInteger 64x1024x1024), and decode tokens/s of the TinyLlama-1.1B-shape
-    int4 decoder (configs[3], batch 1, 128-token prompt, 128 greedy steps)."""
+    int4 decoder (configs[3], batch 1, 128-token prompt, 128 greedy steps) and of the
+    Llama-3-70B-shape one (configs[4], batch 1, 2048-token prompt, 32 greedy steps)."""
     import torch
     from yscv_b200.llm_bench import run as llm_run
     out = {}
@@ -444,8 +445,15 @@ def extra_metrics(ctx, stream, dev):
             pk.free()
     stream.synchronize()
     d = llm_run("tinyllama", batch=1, prompt_len=128, max_tokens=128, warmup=1)
-    out["int4_decoder_tinyllama_b1"] = {k: d[k] for k in ("decode_tokens_per_sec", "ms_per_step", "prefill_ms",
-                                                            "weight_stream_gbs_per_gpu")}
+    keys = ("decode_tokens_per_sec", "ms_per_step", "prefill_ms", "weight_stream_gbs_per_gpu", "decode_step")
+    out["int4_decoder_tinyllama_b1"] = {k: d[k] for k in keys}
+    # configs[4]: Llama-3-70B shape on this one GPU (47 GB of weights), prompt 2048, 32 greedy steps
+    try:
+        torch.cuda.empty_cache()
+        d = llm_run("llama70b", batch=1, prompt_len=2048, max_tokens=32, warmup=0)
+        out["int4_decoder_llama70b_b1"] = {k: d[k] for k in keys}
+    except Exception as e:  # e.g. not enough free memory on a shared GPU: report, do not fail the bench
+        out["int4_decoder_llama70b_b1"] = {"error": f"{type(e).__name__}: {e}"[:200]}
     return out
 
 
