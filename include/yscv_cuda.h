@@ -20,8 +20,21 @@
  *  - There is no CPU fallback anywhere. Shapes a kernel cannot take are
  *    rejected with YSCV_CUDA_ERR_UNSUPPORTED.
  *  - A context owns one CUDA stream (or borrows the caller's); calls on one
- *    context are serialised by the caller. Handles are immutable after
- *    creation and may be shared between contexts of the same device.
+ *    context are serialised by the caller (the library takes no lock per call);
+ *    different contexts may be used from different threads at the same time:
+ *    the only process-wide state (per-kernel attributes set once, the operator
+ *    counters, the table behind a yscv_cuda_registry) is guarded inside. Handles
+ *    are immutable after creation and may be shared between contexts of the
+ *    same device.
+ *  - "_dev" entry points only enqueue work, with one exception: the first call
+ *    for a shape larger than any seen before may grow the context's scratch
+ *    buffers (a cudaFree and a cudaMalloc, which synchronise the device and are
+ *    not allowed inside a stream capture). Run one call of every shape before
+ *    capturing a CUDA graph.
+ *  - Pointers given to "_dev" entry points must be aligned as the natural
+ *    vector width of the operand asks (16 bytes for f32 rows read with 128-bit
+ *    loads); a pointer that is not is rejected with YSCV_CUDA_ERR_UNSUPPORTED or
+ *    takes a scalar path, it never faults.
  *
  * Layouts (identical to the reference's)
  *  - packed int4 weights: [N rows][K/2 bytes], one row per output channel,
@@ -63,8 +76,9 @@ int yscv_cuda_ctx_create(int device, yscv_cuda_ctx **out);
 int yscv_cuda_ctx_create_on_stream(int device, void *cuda_stream, yscv_cuda_ctx **out);
 void yscv_cuda_ctx_destroy(yscv_cuda_ctx *ctx);
 int yscv_cuda_ctx_synchronize(yscv_cuda_ctx *ctx);
-/* Reads and clears the device-side status word that bounded waits inside the
- * kernels set when they give up (0 = none). */
+/* Reads and clears the device-side status word (0 = none): 1 a bounded wait on a copy
+ * barrier ran out, 2 a bounded wait on another CTA or another GPU ran out, 3 a sequence
+ * position outside [0, max_seq) was given to a cache append (nothing was appended). */
 int yscv_cuda_ctx_device_status(yscv_cuda_ctx *ctx, int *status);
 const char *yscv_cuda_last_error(void);
 /* Counterpart of runtime_dispatch_report() (crates/yscv-kernels/src/core.rs:30-137):
@@ -72,6 +86,27 @@ const char *yscv_cuda_last_error(void);
 const char *yscv_cuda_last_kernel(const yscv_cuda_ctx *ctx);
 /* Number of kernels this library has launched on the context so far. */
 uint64_t yscv_cuda_ctx_launch_count(const yscv_cuda_ctx *ctx);
+/* runtime_dispatch_report() (crates/yscv-kernels/src/core.rs:111-137) for this context: the
+ * device, and for the last int4 and the last int8 call the kernel variant with its tile
+ * geometry and the shape it was chosen for. The string belongs to the calling thread and is
+ * valid until its next call. */
+const char *yscv_cuda_dispatch_report(const yscv_cuda_ctx *ctx);
+/* Process-wide operator counters, the counterpart of QuantRuntimeStats
+ * (crates/yscv-onnx/src/runner/quant_stats.rs:21-92): how many calls each kernel family
+ * served since the last reset. cpu_fallbacks is always 0: this library has no CPU path. */
+typedef struct {
+    uint64_t int4_gemv_calls;      /* m <= 16 passes on the integer-MMA decode kernel */
+    uint64_t int4_gemm_calls;      /* m > 16 calls on the tensor-core prefill GEMM */
+    uint64_t int4_generic_calls;   /* passes on the warp-per-row kernel (odd group / k / alignment) */
+    uint64_t int8_gemm_calls;      /* every int8 GEMM launch, whatever the epilogue */
+    uint64_t qlinear_matmul_calls;
+    uint64_t matmul_integer_calls;
+    uint64_t requant_calls;        /* stand-alone requant passes */
+    uint64_t decode_step_calls;    /* one-launch decode steps */
+    uint64_t cpu_fallbacks;
+} yscv_cuda_quant_stats;
+void yscv_cuda_quant_stats_read(yscv_cuda_quant_stats *out);
+void yscv_cuda_quant_stats_reset(void);
 /* int4 matmuls with more than 16 activation rows run on the bf16 tensor-core path
  * (relative Frobenius error ~3e-3 against the fp32 kernel, bound 2e-2). exact != 0 keeps
  * the fp32-exact decode kernel for them, 16 rows per pass (slower, error ~1e-6): the
@@ -80,7 +115,9 @@ uint64_t yscv_cuda_ctx_launch_count(const yscv_cuda_ctx *ctx);
 int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact);
 /* Per-kernel timing, the counterpart of YSCV_RUNNER_PROFILE
  * (crates/yscv-onnx/src/runner/profile.rs:1-120): while enabled, the dominant
- * kernel of every call is bracketed by CUDA events on the context's stream.
+ * kernel of every call is bracketed by CUDA events on the context's stream
+ * (the first 4096 launches after a read; the events are created by _enable,
+ * so that no launch path ever allocates).
  * _read synchronises, returns the number of bracketed launches and their summed
  * device time, and resets the counters. */
 int yscv_cuda_ctx_profile_enable(yscv_cuda_ctx *ctx, int enable);
@@ -88,7 +125,12 @@ int yscv_cuda_ctx_profile_read(yscv_cuda_ctx *ctx, uint64_t *launches, double *t
 
 /* ---- int4 block-quantized GEMV / GEMM: host drop-ins --------------------- */
 
-/* packed_int4_gemv_dispatch (crates/yscv-kernels/src/ops/int4_matmul.rs:310-377) */
+/* packed_int4_gemv_dispatch (crates/yscv-kernels/src/ops/int4_matmul.rs:310-377).
+ * Non-finite activations: the kernels for m <= 16 turn each group of 32 activations into
+ * block-fixed-point integers first, so a group that holds a NaN or an infinity yields NaN for
+ * every output row, where the reference's fp32 loop (int4_matmul.rs:61-80) yields NaN or, when
+ * every weight that meets the infinity is non-zero and of one sign, an infinity of that sign.
+ * Both are non-finite; finite inputs are unaffected. */
 int yscv_cuda_packed_int4_gemv(yscv_cuda_ctx *ctx, const uint8_t *weight_packed,
                                const float *scales, const float *activation,
                                float *output, size_t m_w, size_t k, size_t group_size);
@@ -158,6 +200,47 @@ int yscv_cuda_int4_matmul_dev_static(yscv_cuda_ctx *ctx, const uint8_t *d_packed
 int yscv_cuda_int4_from_matmulnbits(const uint8_t *src, uint8_t *dst, size_t bytes);
 int yscv_cuda_int4_from_matmulnbits_dev(yscv_cuda_ctx *ctx, const uint8_t *d_src, uint8_t *d_dst,
                                         size_t bytes);
+
+/* The inverse: this library's nibbles as MatMulNBits expects them (q + 8, zero point 8). The
+ * same bit flip; named for the direction. */
+int yscv_cuda_int4_to_matmulnbits(const uint8_t *src, uint8_t *dst, size_t bytes);
+
+/* One weight of quantize_matmul_weights_int4_packed
+ * (crates/yscv-onnx/src/quantize/packed_int4.rs:50-128): an fp32 initializer [dim0][dim1] in
+ * the layout its node implies is transposed to [N][K] where needed, packed and kept resident.
+ * The reference's rules hold: an odd or zero group_size is an error (YSCV_CUDA_ERR_BAD_ARG,
+ * packed_int4.rs:54-58); a weight with k % group_size != 0 or k * n < 32 is silently skipped
+ * (packed_int4.rs:102-104): the call returns 0 and leaves *out NULL, and the caller keeps
+ * the fp32 weight. Unlike the reference's exec_gemm (runner/linear.rs:3-10), which never
+ * consults the side table, handles made from Gemm weights are usable like any other. */
+enum {
+    YSCV_CUDA_WEIGHT_MATMUL_KN = 0, /* MatMul: [K][N] */
+    YSCV_CUDA_WEIGHT_GEMM_NK = 1,   /* Gemm, transB = 1: [N][K], packed as it is */
+    YSCV_CUDA_WEIGHT_GEMM_KN = 2    /* Gemm, transB = 0: [K][N] */
+};
+int yscv_cuda_int4_weight_from_f32(yscv_cuda_ctx *ctx, const float *weight, size_t dim0, size_t dim1,
+                                   int layout, size_t group_size, yscv_cuda_int4_weight **out);
+/* PackedInt4Weight's fields (packed_int4.rs:28-39) of a resident weight, and its bytes back
+ * in host memory: packed [m_w * k / 2], scales [m_w * k / group_size]. */
+size_t yscv_cuda_int4_weight_rows(const yscv_cuda_int4_weight *w);
+size_t yscv_cuda_int4_weight_k(const yscv_cuda_int4_weight *w);
+size_t yscv_cuda_int4_weight_group_size(const yscv_cuda_int4_weight *w);
+int yscv_cuda_int4_weight_download(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w, uint8_t *packed,
+                                   float *scales);
+
+/* A byte container for one packed int4 weight. No counterpart in the reference, which keeps
+ * packed int4 in memory only (packed_int4.rs:28-39) and re-quantises the fp32 model at every
+ * start. Layout, little endian: 64-byte header {"YSCVINT4", u32 version = 1, u32 group_size,
+ * u64 m_w, u64 k, u64 packed_bytes, u64 scale_count, 16 reserved bytes}, the packed bytes
+ * padded with zeros to a multiple of 16, the f32 scales. _read validates the header and
+ * returns views into `src`; host only, no CUDA call. */
+size_t yscv_cuda_int4_container_size(size_t m_w, size_t k, size_t group_size);
+int yscv_cuda_int4_container_write(const uint8_t *packed, const float *scales, size_t m_w, size_t k,
+                                   size_t group_size, uint8_t *dst, size_t capacity, size_t *written);
+int yscv_cuda_int4_container_read(const uint8_t *src, size_t len, size_t *m_w, size_t *k, size_t *group_size,
+                                  const uint8_t **packed, const float **scales);
+int yscv_cuda_int4_weight_from_container(yscv_cuda_ctx *ctx, const uint8_t *src, size_t len,
+                                         yscv_cuda_int4_weight **out);
 
 /* pack_int4_symmetric_per_group on device memory: d_weights [m_w,k] f32. */
 int yscv_cuda_pack_int4_dev(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w,
@@ -230,6 +313,45 @@ int yscv_cuda_matmul_integer_dev(yscv_cuda_ctx *ctx, const void *d_a, int a_is_u
                                  int32_t a_zero_point, const yscv_cuda_i8b *b, size_t m,
                                  int32_t *d_out);
 
+/* requant_i32_row_to_i8_dispatch (crates/yscv-kernels/src/ops/int8_requant.rs:81-169) as a
+ * pass of its own: acc [len] i32, len a multiple of the channel count c, optional bias [c]
+ * (wrapping add), out[i] = clamp(round_ties_even((float)(acc[i] + bias[i % c]) * composite +
+ * y_zero_point), -128, 127), ReLU after the saturation. The GEMM entry points above fuse the
+ * same arithmetic behind the tensor cores; this one serves accumulators made elsewhere. */
+int yscv_cuda_requant_i32_row_to_i8(yscv_cuda_ctx *ctx, const int32_t *acc, const int32_t *bias, float composite,
+                                    float y_zero_point, int relu, int8_t *out, size_t len, size_t c);
+int yscv_cuda_requant_i32_row_to_i8_dev(yscv_cuda_ctx *ctx, const int32_t *d_acc, const int32_t *d_bias,
+                                        float composite, float y_zero_point, int relu, int8_t *d_out,
+                                        size_t len, size_t c);
+
+/* ---- resident weights keyed by initializer name ----------------------------------------
+ * The runner's side tables: env.packed_int4_weights.get(&node.inputs[1])
+ * (crates/yscv-onnx/src/runner/linear.rs:228) and prepacked_i8_weights / prepacked_i8_b(name)
+ * (crates/yscv-onnx/src/plan/build.rs:1417-1454, crates/yscv-onnx/src/runner/tensor_env.rs:178-183),
+ * filled once at load time. _put takes ownership of the handle (a second _put under the same
+ * name frees the first, like HashMap::insert); _get returns NULL for a name that is absent;
+ * _destroy frees every handle. Lookups may run concurrently from any thread. */
+typedef struct yscv_cuda_registry yscv_cuda_registry;
+int yscv_cuda_registry_create(yscv_cuda_registry **out);
+void yscv_cuda_registry_destroy(yscv_cuda_registry *reg);
+int yscv_cuda_registry_put_int4(yscv_cuda_registry *reg, const char *name, yscv_cuda_int4_weight *w);
+int yscv_cuda_registry_put_i8b(yscv_cuda_registry *reg, const char *name, yscv_cuda_i8b *b);
+const yscv_cuda_int4_weight *yscv_cuda_registry_get_int4(const yscv_cuda_registry *reg, const char *name);
+const yscv_cuda_i8b *yscv_cuda_registry_get_i8b(const yscv_cuda_registry *reg, const char *name);
+size_t yscv_cuda_registry_len(const yscv_cuda_registry *reg);
+/* The load-time hooks in one call each: quantize_matmul_weights_int4_packed for one weight
+ * (*packed = 0 when the reference's rules skip it) and the QLinearMatMul / MatMulInteger
+ * prepack of build_runtime_index (*prepacked = 0 when should_prepack_i8_b says no). */
+int yscv_cuda_registry_register_matmul_weight(yscv_cuda_ctx *ctx, yscv_cuda_registry *reg, const char *name,
+                                              const float *weight, size_t dim0, size_t dim1, int layout,
+                                              size_t group_size, int *packed);
+int yscv_cuda_registry_register_i8_weight(yscv_cuda_ctx *ctx, yscv_cuda_registry *reg, const char *name,
+                                          const int8_t *b, size_t k, size_t n, int *prepacked);
+/* should_prepack_i8_b (crates/yscv-onnx/src/plan/build.rs:1371-1377) and
+ * should_use_prepacked_i8_b (crates/yscv-onnx/src/runner/layout.rs:6-11), unchanged. */
+int yscv_cuda_should_prepack_i8_b(size_t k, size_t n);
+int yscv_cuda_should_use_prepacked_i8_b(size_t m, size_t k, size_t n);
+
 /* ---- fp32 operators between the quantized linears of a decoder step ---------- */
 /* All take device pointers and are asynchronous on the context's stream. The sequence
  * position (*d_pos) and the token ids live in device memory, so that a whole decode
@@ -248,7 +370,9 @@ int yscv_cuda_add_rms_norm_dev(yscv_cuda_ctx *ctx, const float *d_x, const float
 /* apply_rotary_embedding (crates/yscv-kernels/src/ops/rope.rs:24-117, rotate-half) on the
  * q and k parts of fused qkv rows [q | k | v] at positions *d_pos + s, fused with the
  * KvCache append (crates/yscv-onnx/src/runner/kv_cache.rs:118-254, f32 storage):
- * caches are [batch][max_seq][n_kv][d_head]. q is rotated in place. */
+ * caches are [batch][max_seq][n_kv][d_head]. q is rotated in place. d_head even, d_head +
+ * (int8 form) n_kv * d_head floats must fit 48 KB of shared memory. A position outside
+ * [0, max_seq) appends nothing and sets the context's status word to 3. */
 int yscv_cuda_rope_kv_append_dev(yscv_cuda_ctx *ctx, float *d_qkv, size_t batch, size_t seq,
                                  size_t n_q, size_t n_kv, size_t d_head, float theta,
                                  const int32_t *d_pos, float *d_kcache, float *d_vcache,
@@ -261,6 +385,22 @@ int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_s
                                 size_t seq_q, size_t n_q, size_t n_kv, size_t d_head,
                                 const float *d_kcache, const float *d_vcache, size_t max_seq,
                                 const int32_t *d_pos, int causal, float *d_out);
+
+/* The same two operators over a cache stored as KvDtype::I8
+ * (crates/yscv-onnx/src/runner/kv_cache.rs:8-90): every appended row (one token's
+ * n_kv * d_head keys, or values, of one layer) is stored as int8 with one f32 scale,
+ * scale = abs_max / 127 (1.0 when abs_max <= f32::EPSILON), q = clamp(round_half_away(v *
+ * (1 / scale)), -127, 127); reads dequantise on the fly, (float)q * scale. Caches are int8
+ * [batch][max_seq][n_kv][d_head], scale tables f32 [batch][max_seq]. */
+int yscv_cuda_rope_kv_append_i8_dev(yscv_cuda_ctx *ctx, float *d_qkv, size_t batch, size_t seq, size_t n_q,
+                                    size_t n_kv, size_t d_head, float theta, const int32_t *d_pos,
+                                    int8_t *d_kcache, float *d_kscale, int8_t *d_vcache, float *d_vscale,
+                                    size_t max_seq);
+int yscv_cuda_gqa_attention_i8_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_stride, size_t batch,
+                                   size_t seq_q, size_t n_q, size_t n_kv, size_t d_head,
+                                   const int8_t *d_kcache, const float *d_kscale, const int8_t *d_vcache,
+                                   const float *d_vscale, size_t max_seq, const int32_t *d_pos, int causal,
+                                   float *d_out);
 
 /* SwiGLU on fused rows [gate | up] with the scalar SiLU of
  * crates/yscv-kernels/src/ops/simd/activation.rs:1000-1005: out = gate/(1+exp(-gate)) * up */
@@ -340,11 +480,64 @@ int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_decode_laye
                                  size_t n_kv, size_t d_head, size_t max_seq, float eps,
                                  float rope_theta, yscv_cuda_decode_plan **out);
 
+/* Tensor-parallel decode steps. No counterpart in the reference (it has no multi-GPU
+ * inference: crates/yscv-model/src/distributed.rs:27). One process per GPU; rank r of a group
+ * of `world` (2..8) GPUs of one machine holds the column-parallel shard of qkv and gate|up
+ * (its heads, its intermediate channels) and the row-parallel shard of the output and down
+ * projections (its K slice), as yscv_b200/sharding.py cuts them. _create allocates this
+ * rank's exchange region (2 * world * max_rows 8-byte words; max_rows >= hidden) and writes
+ * its IPC handle; the host gathers every rank's handle (YSCV_CUDA_TP_HANDLE_BYTES each, in
+ * rank order) and gives them to _connect, which maps the peers' regions. A plan built with
+ * the connected group then exchanges the partial sums of the row-parallel GEMVs inside the
+ * step kernel: plain 8-byte stores {f32 value, 32-bit tag} into every peer's region over
+ * NVLink, a bounded poll of the own region, sums in rank order (identical bits on every
+ * rank). Every rank must run the same sequence of steps; destroy the plan and the group on
+ * every rank only after all of them have finished their last step. */
+typedef struct yscv_cuda_tp_comm yscv_cuda_tp_comm;
+#define YSCV_CUDA_TP_HANDLE_BYTES 64
+int yscv_cuda_tp_comm_create(yscv_cuda_ctx *ctx, int rank, int world, size_t max_rows,
+                             yscv_cuda_tp_comm **out, uint8_t handle_out[YSCV_CUDA_TP_HANDLE_BYTES]);
+int yscv_cuda_tp_comm_connect(yscv_cuda_tp_comm *comm, const uint8_t *handles /* world x 64 bytes */);
+void yscv_cuda_tp_comm_destroy(yscv_cuda_tp_comm *comm);
+/* Test form of _connect: the peers' regions are stand-ins in this GPU's memory that nobody
+ * ever writes, so every wait for a peer runs out. Used to exercise the give-up path of the
+ * bounded waits on one GPU (with a short spin_limit below). */
+int yscv_cuda_tp_comm_connect_unanswered(yscv_cuda_tp_comm *comm);
+
+/* Optional settings of a plan; a NULL pointer or a zeroed struct with variant =
+ * attention_form = -1 means the defaults. The geometry fields exist so that tests can push
+ * small shapes down the paths large models take. */
+typedef struct yscv_cuda_decode_options {
+    int variant;        /* -1: default. Bit mask: 1 gate/up rows paired (SwiGLU in the store),
+                           2 sixteen K slices for one-tile slabs, 4 split-merge weight table,
+                           8 relaxed barrier polling */
+    int max_tiles;      /* 0: default (8). 16-row tiles per row block, 2..8, even */
+    int k_chunk;        /* 0: default (8192). k per resident chunk of digit planes, multiple of 512 */
+    int attention_form; /* -1: chosen from max_seq. 0: CTAs per query head; 1: per KV head and key chunk */
+    int spin_limit;     /* 0: default (2^21 probes, about a second). Probes after which a wait
+                           for another CTA or another GPU gives up */
+    const yscv_cuda_tp_comm *tp; /* NULL: one GPU. Else this rank's connected group; the layer
+                                    weights and n_q, n_kv, inter are then the rank's shards */
+} yscv_cuda_decode_options;
+int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cuda_decode_layer *layers,
+                                    size_t n_layers, size_t hidden, size_t inter, size_t n_q,
+                                    size_t n_kv, size_t d_head, size_t max_seq, float eps,
+                                    float rope_theta, const yscv_cuda_decode_options *opt,
+                                    yscv_cuda_decode_plan **out);
+
+/* Synchronises the stream and reports whether a bounded wait ran out in any step of this plan
+ * so far: YSCV_CUDA_ERR_TIMEOUT if so. From then on the plan is poisoned: every later step
+ * call returns YSCV_CUDA_ERR_TIMEOUT without launching (steps enqueued before the check still
+ * fall through all their waits and set the context's status word to 2 again). Rebuild the
+ * plan (and, for a tensor-parallel one, the group on every rank). */
+int yscv_cuda_decode_plan_check(yscv_cuda_ctx *ctx, yscv_cuda_decode_plan *plan);
+
 /* x = embedding[*d_token], then every layer at position *d_pos (appending to the caches at
  * that position); leaves the residual stream after the last layer, before the final norm,
  * in d_x [hidden]. Asynchronous on the context's stream. A device-side wait that runs out
  * sets the context's status word (yscv_cuda_ctx_device_status) and the plan must then be
- * rebuilt. */
+ * rebuilt (yscv_cuda_decode_plan_check). A position outside [0, max_seq) computes and
+ * appends nothing and sets the status word to 3. */
 int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
                                    const float *d_embedding, size_t vocab, const int32_t *d_token,
                                    const int32_t *d_pos, float *d_x);
@@ -357,6 +550,18 @@ int yscv_cuda_decode_plan_step_token_dev(yscv_cuda_ctx *ctx, const yscv_cuda_dec
                                          const float *d_embedding, size_t vocab, int32_t *d_token,
                                          int32_t *d_pos, const float *d_final_gamma,
                                          const float *d_lm_head, float *d_x, float *d_logits);
+
+/* The same with the LM head split by rows across the ranks of a tensor-parallel plan: this
+ * rank holds rows [lm_row0, lm_row0 + lm_rows) of the LM head in d_lm_head_rows
+ * [lm_rows][hidden] and writes only those entries of d_logits [vocab]; the ranks exchange
+ * their best (value, index) inside the kernel and every rank writes the same greedy token.
+ * (The plain entry point above, given a tensor-parallel plan, computes every row on every
+ * rank.) */
+int yscv_cuda_decode_plan_step_token_shard_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
+                                               const float *d_embedding, size_t vocab, int32_t *d_token,
+                                               int32_t *d_pos, const float *d_final_gamma,
+                                               const float *d_lm_head_rows, size_t lm_row0, size_t lm_rows,
+                                               float *d_x, float *d_logits);
 
 void yscv_cuda_decode_plan_free(yscv_cuda_decode_plan *plan);
 

@@ -57,6 +57,8 @@ class Oracle:
             "yo_rope": [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _f],
             "yo_gqa_attention": [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, C.c_int, _vp],
             "yo_silu": [_vp, _sz, _vp],
+            "yo_kv_append_i8": [_vp, _sz, _sz, _vp, _vp],
+            "yo_kv_dequantise_i8": [_vp, _vp, _sz, _sz, _vp],
             "yo_lcg_f32": [C.c_uint64, _sz, _vp],
             "yo_lcg_i8": [C.c_uint64, _sz, _vp],
             "ysb_int4_gemv": [_vp, _vp, _vp, _vp, _sz, _sz, _sz],
@@ -213,6 +215,22 @@ class Oracle:
         out = np.empty(batch * sq * n_q * d, np.float32)
         self.lib.yo_gqa_attention(self._p(q), self._p(k), self._p(v), batch, sq, sk, n_q, n_kv, d,
                                   int(causal), self._p(out))
+        return out
+
+    def kv_append_i8(self, rows):
+        """rows f32 [n, kv_dim] -> (int8 [n, kv_dim], scales f32 [n]) as KvDtype::I8 stores them."""
+        rows = np.ascontiguousarray(rows, np.float32)
+        n, kv_dim = rows.shape
+        data = np.empty((n, kv_dim), np.int8)
+        scales = np.empty(n, np.float32)
+        self.lib.yo_kv_append_i8(self._p(rows), n, kv_dim, self._p(data), self._p(scales))
+        return data, scales
+
+    def kv_dequantise_i8(self, data, scales):
+        data = np.ascontiguousarray(data, np.int8)
+        scales = np.ascontiguousarray(scales, np.float32)
+        out = np.empty(data.shape, np.float32)
+        self.lib.yo_kv_dequantise_i8(self._p(data), self._p(scales), data.shape[0], data.shape[1], self._p(out))
         return out
 
     def silu(self, x):

@@ -15,6 +15,7 @@
  */
 #include "yscv_oracle.h"
 
+#include <float.h>
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
@@ -180,6 +181,35 @@ void yo_requant_i8(const int32_t *acc, size_t len, const int32_t *bias,
             if (relu && q < 0) q = 0;
             out[p * c + ch] = q;
         }
+}
+
+void yo_kv_append_i8(const float *src, size_t rows, size_t kv_dim, int8_t *data,
+                     float *scales) {
+    for (size_t r = 0; r < rows; ++r) {
+        const float *row = src + r * kv_dim;
+        float abs_max = 0.0f;
+        for (size_t i = 0; i < kv_dim; ++i) {
+            float a = fabsf(row[i]);
+            if (a > abs_max) abs_max = a; /* f32::max ignores a NaN operand */
+        }
+        float scale = abs_max <= FLT_EPSILON ? 1.0f : abs_max / 127.0f;
+        float inv = 1.0f / scale;
+        scales[r] = scale;
+        for (size_t i = 0; i < kv_dim; ++i) {
+            float v = row[i] * inv;
+            float q = roundf(v); /* f32::round: half away from zero */
+            if (q < -127.0f) q = -127.0f;
+            if (q > 127.0f) q = 127.0f;
+            data[r * kv_dim + i] = (v != v) ? (int8_t)0 : (int8_t)q; /* NaN as i8 == 0 */
+        }
+    }
+}
+
+void yo_kv_dequantise_i8(const int8_t *data, const float *scales, size_t rows,
+                         size_t kv_dim, float *out) {
+    for (size_t r = 0; r < rows; ++r)
+        for (size_t i = 0; i < kv_dim; ++i)
+            out[r * kv_dim + i] = (float)data[r * kv_dim + i] * scales[r];
 }
 
 void yo_requant_range(const int32_t *acc, size_t len, float composite, float y_zp,

@@ -96,6 +96,15 @@ void yo_quantize_linear_u8(const float *data, size_t len, float scale,
 void yo_quantize_tensor_symmetric(const float *data, size_t len, float scale,
                                   int8_t *out);
 
+/* crates/yscv-onnx/src/runner/kv_cache.rs:44-60  LayerStorage::append, KvDtype::I8:
+ * per row abs_max; scale = abs_max <= EPSILON ? 1.0 : abs_max / 127.0; inv = 1.0 / scale;
+ * q = clamp(round_half_away(v * inv), -127, 127). One scale per row. */
+void yo_kv_append_i8(const float *src, size_t rows, size_t kv_dim, int8_t *data,
+                     float *scales);
+/* crates/yscv-onnx/src/runner/kv_cache.rs:63-78  dequantise_to_vec: (q as f32) * scale */
+void yo_kv_dequantise_i8(const int8_t *data, const float *scales, size_t rows,
+                         size_t kv_dim, float *out);
+
 /* ---- runner-level operator semantics ----------------------------------- */
 
 /* crates/yscv-onnx/src/runner/linear.rs:453-492: QLinearMatMul fast path as the

@@ -6,11 +6,14 @@ import numpy as np
 
 
 class OracleDecoder:
-    def __init__(self, oracle, cfg, n_layers, weights, embedding, lm_head, batch, threads=8):
+    def __init__(self, oracle, cfg, n_layers, weights, embedding, lm_head, batch, threads=8, kv_int8=False):
         """weights[l][name] = (packed uint8 [n,k/2], scales f32 [n,k/g]) for
         name in q,k,v,o,gate,up,down (unsharded)."""
         self.o, self.cfg, self.n_layers, self.w = oracle, cfg, n_layers, weights
         self.emb, self.lm_head, self.batch, self.threads = embedding, lm_head, batch, threads
+        # KvDtype::I8 (kv_cache.rs:8-90): rows are quantised when appended and dequantised when
+        # read, so the cache below holds the dequantised values
+        self.kv_int8 = kv_int8
         self.k = [[np.zeros((0, cfg.n_kv * cfg.head_dim), np.float32) for _ in range(batch)] for _ in range(n_layers)]
         self.v = [[np.zeros((0, cfg.n_kv * cfg.head_dim), np.float32) for _ in range(batch)] for _ in range(n_layers)]
         self.pos = 0
@@ -35,8 +38,12 @@ class OracleDecoder:
             for b in range(B):
                 sl = slice(b * seq, (b + 1) * seq)
                 qb, kb = o.rope(q[sl].ravel(), k[sl].ravel(), c.n_q, c.n_kv, d, seq, self.pos, c.rope_theta)
-                self.k[l][b] = np.concatenate([self.k[l][b], kb.reshape(seq, -1)])
-                self.v[l][b] = np.concatenate([self.v[l][b], v[sl]])
+                new_k, new_v = kb.reshape(seq, -1), v[sl]
+                if self.kv_int8:
+                    new_k = o.kv_dequantise_i8(*o.kv_append_i8(new_k))
+                    new_v = o.kv_dequantise_i8(*o.kv_append_i8(new_v))
+                self.k[l][b] = np.concatenate([self.k[l][b], new_k])
+                self.v[l][b] = np.concatenate([self.v[l][b], new_v])
                 sk = self.k[l][b].shape[0]
                 attn[sl] = o.gqa_attention(qb, self.k[l][b].ravel(), self.v[l][b].ravel(), 1, seq, sk, c.n_q, c.n_kv,
                                            d, True).reshape(seq, -1)

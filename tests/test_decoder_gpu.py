@@ -147,7 +147,7 @@ def export_weights(dec):
 
 
 def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logit_tol, exact_prefill=True,
-               fused_step=True):
+               fused_step=True, kv_int8=False):
     """exact_prefill: the prompt pass uses the fp32-exact int4 kernel (tokens must then match the
     oracle except at rounding-level ties); otherwise the bf16 tensor-core GEMM, whose logits
     may differ by up to 2e-2 (relative Frobenius) and whose tokens may differ only where the
@@ -157,11 +157,11 @@ def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logi
     ctx.set_int4_prefill_exact(exact_prefill)
     flip_margin = 1e-4 if exact_prefill else 5e-2
     dec = Int4Decoder.with_full_weights(ctx, cfg, batch, prompt_len + steps + 1, s, seed=seed, layers=n_layers,
-                                        fused_step=fused_step)
-    assert (dec.plan is not None) == (fused_step and batch == 1)
+                                        fused_step=fused_step, kv_int8=kv_int8)
+    assert (dec.plan is not None) == (fused_step and batch == 1 and not kv_int8)
     from oracle_decoder import OracleDecoder
     ref = OracleDecoder(oracle, cfg, n_layers, export_weights(dec), dec.embedding.cpu().numpy(),
-                        dec.lm_head.cpu().numpy(), batch)
+                        dec.lm_head.cpu().numpy(), batch, kv_int8=kv_int8)
     prompt = np.stack([synth.uniform_int(seed + b, 9, prompt_len, 0, cfg.vocab - 1) for b in range(batch)]).astype(np.int32)
     d_prompt = dev(prompt)
     logits = dec.prefill(d_prompt)
@@ -250,17 +250,16 @@ def test_fused_step_logits_match_operator_chain(tctx):
     assert ctx.device_status() == 0
 
 
-@pytest.mark.parametrize("env", [
-    {"YSCV_CUDA_STEP_MAX_TILES": "2", "YSCV_CUDA_STEP_KCHUNK": "1024"},                                  # default variant
-    {"YSCV_CUDA_STEP_MAX_TILES": "2", "YSCV_CUDA_STEP_KCHUNK": "1024", "YSCV_CUDA_STEP_VARIANT": "0"},   # plain
-    {"YSCV_CUDA_STEP_MAX_TILES": "4", "YSCV_CUDA_STEP_KCHUNK": "1536", "YSCV_CUDA_STEP_VARIANT": "5"},
-    {"YSCV_CUDA_STEP_ATTN": "1"},                                  # attention per KV head and key chunk + merge phase
-    {"YSCV_CUDA_STEP_ATTN": "1", "YSCV_CUDA_STEP_MAX_TILES": "2"},
+@pytest.mark.parametrize("opts", [
+    dict(max_tiles=2, k_chunk=1024),                    # default variant
+    dict(max_tiles=2, k_chunk=1024, variant=0),         # plain
+    dict(max_tiles=4, k_chunk=1536, variant=5),
+    dict(attention_form=1),                             # attention per KV head and key chunk + merge phase
+    dict(attention_form=1, max_tiles=2),
 ])
-def test_fused_step_row_blocks_and_k_chunks(tctx, env):
+def test_fused_step_row_blocks_and_k_chunks(tctx, opts):
     """Small shapes pushed through the paths large models take: several row blocks per CTA
     (gate/up) and a down projection longer than one K chunk, by shrinking the plan's limits."""
-    import os
     import torch
     ctx, s = tctx
     cfg = DecoderConfig(layers=2, hidden=1024, mlp=2560, n_q=16, n_kv=4, head_dim=64, vocab=2000)
@@ -269,9 +268,7 @@ def test_fused_step_row_blocks_and_k_chunks(tctx, env):
     logs, toks = [], []
     try:
         for fused in (False, True):
-            if fused:
-                os.environ.update(env)
-            dec = Int4Decoder(ctx, cfg, 1, 64, s, seed=15, fused_step=fused)
+            dec = Int4Decoder(ctx, cfg, 1, 64, s, seed=15, fused_step=fused, plan_options=opts if fused else None)
             assert (dec.plan is not None) == fused
             dec.prefill(prompt)
             lg, tk = [], []
@@ -285,8 +282,6 @@ def test_fused_step_row_blocks_and_k_chunks(tctx, env):
             toks.append(tk)
             dec.close()
     finally:
-        for k in env:
-            os.environ.pop(k, None)
         ctx.set_int4_prefill_exact(False)
     assert toks[0] == toks[1]
     for a, b in zip(*logs):
@@ -392,17 +387,13 @@ def test_fused_step_long_context_and_limits(tctx):
     import yscv_b200
     ctx, s = tctx
     cfg = DecoderConfig(layers=2, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
-    import os
     P, steps = 700, 4   # 148 // 8 -> 4 splits per head: 175+ keys each
     prompt = dev(synth.uniform_int(33, 9, P, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
     logs = []
     for fused in (False, True, "grouped"):
-        if fused == "grouped":   # 32 chunks per KV head; with 5000 cache slots more than 128 keys per chunk
-            os.environ["YSCV_CUDA_STEP_ATTN"] = "1"
-        try:
-            dec = Int4Decoder(ctx, cfg, 1, P + steps, s, seed=14, fused_step=bool(fused))   # the last step fills the cache
-        finally:
-            os.environ.pop("YSCV_CUDA_STEP_ATTN", None)
+        # "grouped": 32 chunks per KV head; the last step fills the cache
+        dec = Int4Decoder(ctx, cfg, 1, P + steps, s, seed=14, fused_step=bool(fused),
+                          plan_options=dict(attention_form=1) if fused == "grouped" else None)
         assert (dec.plan is not None) == bool(fused)
         dec.prefill(prompt)
         lg = []
@@ -427,9 +418,195 @@ def test_fused_step_long_context_and_limits(tctx):
 
 
 def test_tinyllama_shape_greedy_tokens(tctx, oracle):
-    # BASELINE config 4 shape, seed 3; 4 of the 22 layers keep the CPU oracle in seconds,
-    # the full depth runs in bench/decoder measurements
-    run_parity(tctx, oracle, TINYLLAMA_1B, 4, batch=1, prompt_len=128, steps=32, seed=3, logit_tol=1e-4)
+    # BASELINE config 4 at full depth: 22 layers, prompt 128, seed 3, 32 greedy steps, every
+    # decode step one launch of the step kernel, against the CPU oracle decoder
+    run_parity(tctx, oracle, TINYLLAMA_1B, 22, batch=1, prompt_len=128, steps=32, seed=3, logit_tol=1e-4)
+
+
+def test_tinyllama_shape_batch8(tctx, oracle):
+    # BASELINE config 4, batch 8 (independent sequences, prompt seed + b): operator chain
+    run_parity(tctx, oracle, TINYLLAMA_1B, 2, batch=8, prompt_len=32, steps=8, seed=3, logit_tol=1e-4)
+
+
+LLAMA70B_LAYER = DecoderConfig(layers=2, hidden=8192, mlp=28672, n_q=64, n_kv=8, head_dim=128, vocab=16032,
+                               rope_theta=500000.0)
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_llama70b_shape_two_layers_match_oracle(tctx, oracle, fused):
+    """BASELINE config 5's layer shape (hidden 8192, MLP 28672, 64/8 heads of 128, RoPE base
+    5e5), truncated to 2 layers and an eighth of the vocabulary so that the CPU oracle finishes
+    in seconds: logits of the prompt pass and 8 greedy tokens against the oracle decoder, for
+    the one-launch step (four row blocks in gate/up, a K-chunked down projection, two CTAs
+    per head) and for the operator chain."""
+    run_parity(tctx, oracle, LLAMA70B_LAYER, 2, batch=1, prompt_len=24, steps=8, seed=4, logit_tol=1e-4,
+               fused_step=fused)
+    ctx, _ = tctx
+    assert ctx.device_status() == 0
+
+
+def test_int8_kv_cache_matches_oracle(tctx, oracle):
+    """KvDtype::I8 (kv_cache.rs:8-90): rows quantised at append time, dequantised in the
+    attention; logits and tokens against the oracle decoder with the same cache format, at
+    batch 1 and 3, with a prompt pass (block per query) and decode steps (split keys)."""
+    cfg = DecoderConfig(layers=3, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
+    run_parity(tctx, oracle, cfg, 3, batch=3, prompt_len=20, steps=10, seed=6, logit_tol=1e-4, kv_int8=True)
+    cfg = DecoderConfig(layers=2, hidden=1024, mlp=2048, n_q=8, n_kv=2, head_dim=128, vocab=1500)
+    run_parity(tctx, oracle, cfg, 2, batch=1, prompt_len=150, steps=6, seed=7, logit_tol=1e-4, kv_int8=True)
+    ctx, _ = tctx
+    assert ctx.device_status() == 0
+
+
+def test_int8_kv_cache_bytes(tctx, oracle):
+    """The cache rows themselves: int8 values and scales bit-identical to the reference's append."""
+    import torch
+    ctx, s = tctx
+    B, seq, n_q, n_kv, d, max_seq = 2, 5, 4, 2, 64, 16
+    rng = np.random.default_rng(12)
+    qkv = rng.normal(0, 1, (B * seq, (n_q + 2 * n_kv) * d)).astype(np.float32)
+    qkv[3, n_q * d:(n_q + n_kv) * d] = 0.0    # an all-zero key row: scale falls to 1.0
+    d_qkv = dev(qkv.copy())
+    kc = torch.zeros(B, max_seq, n_kv * d, dtype=torch.int8, device="cuda")
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros(B, max_seq, device="cuda")
+    vs = torch.zeros_like(ks)
+    pos = dev(np.array([2], np.int32))
+    with torch.cuda.stream(s):
+        ctx.rope_kv_append_i8_dev(d_qkv.data_ptr(), B, seq, n_q, n_kv, d, 10000.0, pos.data_ptr(), kc.data_ptr(),
+                                  ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), max_seq)
+    s.synchronize()
+    for b in range(B):
+        rows = qkv[b * seq:(b + 1) * seq]
+        _, k_rot = oracle.rope(rows[:, :n_q * d].ravel(), rows[:, n_q * d:(n_q + n_kv) * d].ravel(), n_q, n_kv, d,
+                               seq, 2, 10000.0)
+        kq, ksc = oracle.kv_append_i8(k_rot.reshape(seq, -1))
+        vq, vsc = oracle.kv_append_i8(rows[:, (n_q + n_kv) * d:])
+        assert np.array_equal(vc[b, 2:2 + seq].cpu().numpy(), vq) and np.array_equal(vs[b, 2:2 + seq].cpu().numpy(), vsc)
+        got_k, got_ks = kc[b, 2:2 + seq].cpu().numpy(), ks[b, 2:2 + seq].cpu().numpy()
+        # the rotated keys come from sincosf on the GPU and libm on the CPU: a value on a rounding
+        # boundary may land one step apart
+        assert np.max(np.abs(got_k.astype(np.int32) - kq.astype(np.int32))) <= 1
+        assert np.mean(got_k != kq) < 0.01
+        np.testing.assert_allclose(got_ks, ksc, rtol=1e-6)
+        assert not kc[b, :2].any() and not kc[b, 2 + seq:].any()
+    assert ctx.device_status() == 0
+
+
+def test_position_outside_the_cache_is_reported(tctx):
+    """pos >= max_seq: both decode paths leave the caches alone and set status 3."""
+    import torch
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=2, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
+    prompt = dev(synth.uniform_int(35, 9, 8, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    for fused in (True, False):
+        dec = Int4Decoder(ctx, cfg, 1, 9, s, seed=2, fused_step=fused)   # room for the prompt and one step
+        dec.prefill(prompt)
+        with torch.cuda.stream(s):
+            dec.forward(dec.next_tokens, 1)          # position 8: the last slot
+        s.synchronize()
+        assert ctx.device_status() == 0
+        before = [c.clone() for c in dec.kcache + dec.vcache]
+        with torch.cuda.stream(s):
+            dec.forward(dec.next_tokens, 1)          # position 9 == max_seq
+        s.synchronize()
+        assert ctx.device_status() == 3
+        assert all(torch.equal(a, b) for a, b in zip(before, dec.kcache + dec.vcache))
+        assert ctx.device_status() == 0              # reading cleared it
+        dec.close()
+
+
+def test_eager_steps_equal_graph_replay_wide_vocabulary(tctx):
+    """Operator chain without a graph (kernels chained by programmatic dependent launch, the
+    two-stage arg-max of a vocabulary >= 8192, the position bump) against the replayed graph."""
+    import torch
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=2, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=9000)
+    prompt = dev(np.stack([synth.uniform_int(45 + b, 9, 12, 0, cfg.vocab - 1) for b in range(2)]).astype(np.int32))
+    outs = []
+    for use_graph in (False, True):
+        dec = Int4Decoder(ctx, cfg, 2, 48, s, seed=21)
+        dec.prefill(prompt)
+        if use_graph:
+            dec.capture_decode_step()
+        toks = dec.decode(24, use_graph=use_graph)
+        s.synchronize()
+        outs.append(toks.cpu().numpy())
+        assert int(dec.pos.cpu().numpy()[0]) == 12 + 24
+        dec.close()
+    assert np.array_equal(outs[0], outs[1])
+    assert ctx.device_status() == 0
+
+
+def test_bounded_wait_gives_up_and_the_context_survives(tctx):
+    """The give-up path of the step kernel's waits, without hanging anything: a tensor-parallel
+    plan of two ranks whose peer never answers (its exchange region is a stand-in nobody
+    writes) and a short spin limit. The first wait for the peer runs out, the kernel raises its
+    abort flag, falls through every later wait and returns; the status word says 2, the plan is
+    poisoned, and a fresh plan on the same context works."""
+    import torch
+    import yscv_b200
+    ctx, s = tctx
+    full = DecoderConfig(layers=2, hidden=1024, mlp=2048, n_q=16, n_kv=4, head_dim=64, vocab=2000)
+    dec = Int4Decoder(ctx, full, 1, 32, s, seed=8, fused_step=False)
+    # rank 0's shards of a 2-rank group, cut from the unsharded decoder's weights
+    from yscv_b200 import sharding
+    comm = yscv_b200.TpComm(ctx, 0, 2, full.hidden)
+    comm.connect_unanswered()
+    g, d = full.group_size, full.head_dim
+    keep, layers = [], []
+    for l in range(2):
+        def rows(w, r0, r1):
+            return w.packed[r0:r1], w.scales[r0:r1]
+        q, k, v = (full.n_q * d, full.n_kv * d, full.n_kv * d)
+        parts = [rows(dec.wqkv[l], 0, q // 2), rows(dec.wqkv[l], q, q + k // 2), rows(dec.wqkv[l], q + k, q + k + v // 2)]
+        qkv = (torch.cat([p for p, _ in parts]).contiguous(), torch.cat([sc for _, sc in parts]).contiguous())
+        o = tuple(t.contiguous() for t in sharding.shard_cols(dec.wo[l].packed, dec.wo[l].scales, g, 0, 2))
+        parts = [rows(dec.wgu[l], 0, full.mlp // 2), rows(dec.wgu[l], full.mlp, full.mlp + full.mlp // 2)]
+        gu = (torch.cat([p for p, _ in parts]).contiguous(), torch.cat([sc for _, sc in parts]).contiguous())
+        dn = tuple(t.contiguous() for t in sharding.shard_cols(dec.wdown[l].packed, dec.wdown[l].scales, g, 0, 2))
+        keep += [qkv, o, gu, dn]
+        hs = [ctx.int4_weight_wrap(p.data_ptr(), sc.data_ptr(), p.shape[0], p.shape[1] * 2, g) for p, sc in (qkv, o, gu, dn)]
+        keep += hs
+        kc = torch.zeros(32, full.n_kv // 2, d, device="cuda")
+        vc = torch.zeros_like(kc)
+        keep += [kc, vc]
+        layers.append(dict(qkv=hs[0], o=hs[1], gate_up=hs[2], down=hs[3], gamma_attn=dec.gamma.data_ptr(),
+                           gamma_mlp=dec.gamma.data_ptr(), kcache=kc.data_ptr(), vcache=vc.data_ptr()))
+    plan = ctx.decode_plan(layers, full.hidden, full.mlp // 2, full.n_q // 2, full.n_kv // 2, d, 32, full.eps,
+                           full.rope_theta, tp=comm, spin_limit=2000)
+    tok = dev(np.array([5], np.int32))
+    pos = dev(np.array([0], np.int32))
+    x = torch.zeros(full.hidden, device="cuda")
+    logits = torch.zeros(full.vocab, device="cuda")
+    with torch.cuda.stream(s):
+        plan.step_token_shard_dev(dec.embedding.data_ptr(), full.vocab, tok.data_ptr(), pos.data_ptr(),
+                                  dec.gamma.data_ptr(), dec.lm_head.data_ptr(), 0, full.vocab // 2, x.data_ptr(),
+                                  logits.data_ptr())
+    s.synchronize()                                   # the kernel returned
+    assert ctx.device_status() == 2                   # YSCV_DEV_FLAG_TIMEOUT
+    with pytest.raises(yscv_b200.YscvCudaError) as e:
+        plan.check()
+    assert e.value.status == -4
+    with pytest.raises(yscv_b200.YscvCudaError) as e:  # poisoned: refuses to launch again
+        plan.step_dev(dec.embedding.data_ptr(), full.vocab, tok.data_ptr(), pos.data_ptr(), x.data_ptr())
+    assert e.value.status == -4
+    plan.free()
+    comm.close()
+    dec.close()
+    # the context is intact: a fresh one-GPU plan runs and agrees with the operator chain
+    cfg = DecoderConfig(layers=2, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
+    prompt = dev(synth.uniform_int(3, 0, 12, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    logs = []
+    for fused in (False, True):
+        d2 = Int4Decoder(ctx, cfg, 1, 32, s, seed=3, fused_step=fused)
+        d2.prefill(prompt)
+        with torch.cuda.stream(s):
+            lg = d2.forward(d2.next_tokens, 1)
+        s.synchronize()
+        logs.append(lg.cpu().numpy().copy())
+        d2.close()
+    assert np.linalg.norm(logs[0] - logs[1]) / np.linalg.norm(logs[0]) < 1e-5
+    assert ctx.device_status() == 0
 
 
 def test_tinyllama_shape_operator_chain(tctx, oracle):

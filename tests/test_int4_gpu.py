@@ -179,6 +179,22 @@ def test_extreme_activations(ctx, oracle):
     act[100] = np.nan
     got = ctx.packed_int4_gemv(packed, scales, act, n, k, g)
     assert np.all(np.isnan(got)), "a NaN activation reaches every output, as in fp32"
+    # an infinite activation: the reference's fp32 loop (int4_matmul.rs:61-80) gives q * inf, i.e.
+    # +-inf per row, or NaN where a zero nibble or infinities of both signs meet it; the integer
+    # path cannot tell these apart and gives NaN for the whole group. Both are non-finite on
+    # every row (documented in the header); the fp32 kernel for odd group sizes follows the
+    # reference exactly.
+    act[100] = np.inf
+    want = oracle.int4_gemv(packed, scales, act, n, k, g)
+    got = ctx.packed_int4_gemv(packed, scales, act, n, k, g)
+    assert not np.any(np.isfinite(want)) and not np.any(np.isfinite(got))
+    p16, s16 = oracle.pack_int4(synth.normal(5, 0, n * 48, 0.02), n, 48, 16)   # group 16: fp32 kernel
+    a48 = synth.normal(6, 2, 48, 1.0)
+    a48[5] = -np.inf
+    want = oracle.int4_gemv(p16, s16, a48, n, 48, 16)
+    got = ctx.packed_int4_gemv(p16, s16, a48, n, 48, 16)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(got[~np.isnan(want)], want[~np.isnan(want)])
 
 
 # ---- device-resident form -------------------------------------------------------

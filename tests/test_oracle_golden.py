@@ -253,3 +253,30 @@ def test_decoder_primitives(oracle):
     vv = oracle.lcg_f32(9, 3 * 1 * 4)
     o = oracle.gqa_attention(qq, kk, vv, 1, 1, 3, 2, 1, 4, False)
     assert np.allclose(o.reshape(2, 4), vv.reshape(3, 4).mean(axis=0), atol=1e-6)
+
+
+def test_kv_cache_int8_reference_cases(oracle):
+    # crates/yscv-onnx/src/runner/kv_cache.rs:318-357: the round trip stays within one
+    # quantisation step of each row's own scale (abs_max / 127)
+    k = np.array([[-3.0, -2.5, -1.0, 0.0, 0.5, 1.5, 2.0, 2.8],
+                  [0.1, 0.2, 0.3, 0.4, 0.5, 0.6, 0.7, 0.8]], np.float32)
+    v = np.array([[10.0, 20.0, -30.0, 40.0, -50.0, 60.0, -70.0, 80.0],
+                  [1.0, -1.0, 2.0, -2.0, 3.0, -3.0, 4.0, -4.0]], np.float32)
+    for rows, maxima in ((k, (3.0, 0.8)), (v, (80.0, 4.0))):
+        q, s = oracle.kv_append_i8(rows)
+        back = oracle.kv_dequantise_i8(q, s)
+        for r, mx in enumerate(maxima):
+            assert s[r] == np.float32(mx) / np.float32(127.0)
+            assert np.all(np.abs(back[r] - rows[r]) <= mx / 127.0)
+        assert q.min() >= -127 and q.max() <= 127
+        assert np.all(np.abs(q).max(axis=1) == 127)   # the row maximum maps to +-127
+    # kv_cache.rs:360-375: a constant row of 5.0 comes back within 0.05
+    q, s = oracle.kv_append_i8(np.full((1, 4), 5.0, np.float32))
+    assert abs(float(oracle.kv_dequantise_i8(q, s)[0, 0]) - 5.0) < 0.05
+    # a row at or below f32::EPSILON keeps scale 1.0 (kv_cache.rs:50-54) and rounds to zero
+    q, s = oracle.kv_append_i8(np.full((1, 4), 1e-8, np.float32))
+    assert s[0] == 1.0 and not q.any()
+    # f32::round is half away from zero: 0.5 steps of the scale
+    row = np.array([[127.0, 0.5, -0.5, 1.5, -2.5]], np.float32)
+    q, s = oracle.kv_append_i8(row)
+    assert s[0] == 1.0 and q.tolist() == [[127, 1, -1, 2, -3]]

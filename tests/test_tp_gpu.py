@@ -1,6 +1,8 @@
-"""Tensor-parallel decoder across 2 GPUs (NCCL) against the single-GPU decoder: same
-logits (relative Frobenius) and the same greedy tokens. Needs two B200s; skipped on a
-one-GPU box. Each rank is a child process; rank 0 also runs the TP=1 decoder."""
+"""Tensor-parallel decoder across 2 GPUs against the single-GPU decoder: same logits
+(relative Frobenius) and the same greedy tokens, for the operator chain (NCCL all-reduce,
+batch 2) and for the one-launch decode step whose kernels exchange their partial sums
+through peer memory (batch 1). Needs two B200s; skipped on a one-GPU box. Each rank is a
+child process; rank 0 also runs the TP=1 decoder."""
 import os
 import subprocess
 import sys
@@ -44,6 +46,43 @@ if rank == 0:
     one.close()
 tp.close()
 dist.barrier()
+
+# ---- batch 1: the one-launch step on both ranks, partial sums exchanged inside the kernel ----
+P1, steps1 = 40, 16
+prompt1 = prompt[:1, :].contiguous()
+prompt1 = torch.cat([prompt1, prompt1], dim=1)[:, :P1].contiguous()
+ftp = Int4Decoder(ctx, cfg, 1, P1 + steps1 + 2, stream, seed=5, tp_rank=rank, tp_size=world, process_group=dist.group.WORLD)
+assert ftp.plan is not None, "the tensor-parallel decode plan was not built"
+ftp.prefill(prompt1); stream.synchronize()
+with torch.cuda.stream(stream):
+    first = ftp.forward(ftp.next_tokens, 1).clone()     # one eager step: this rank's slice of the logits
+stream.synchronize()
+ftp.capture_decode_step()
+ftoks = ftp.decode(steps1); stream.synchronize()
+ftp.plan.check()
+parts = [torch.empty_like(first) for _ in range(world)]
+dist.all_gather(parts, first)
+V = cfg.vocab // world
+full_logits = torch.cat([parts[r][0, r * V:(r + 1) * V] for r in range(world)])
+allt = [torch.empty_like(ftoks) for _ in range(world)]
+dist.all_gather(allt, ftoks.contiguous())
+out2 = {"status": ctx.device_status(), "ranks_agree": bool(all(torch.equal(allt[0], t) for t in allt)),
+        "kernel": ctx.last_kernel()}
+if rank == 0:
+    one = Int4Decoder(ctx, cfg, 1, P1 + steps1 + 2, stream, seed=5)
+    assert one.plan is not None
+    one.prefill(prompt1); stream.synchronize()
+    with torch.cuda.stream(stream):
+        lg1 = one.forward(one.next_tokens, 1).clone()
+    stream.synchronize()
+    one.capture_decode_step()
+    toks1 = one.decode(steps1); stream.synchronize()
+    out2["rel"] = float(torch.linalg.norm(full_logits - lg1[0]) / torch.linalg.norm(lg1[0]))
+    out2["tokens_equal"] = bool(torch.equal(ftoks, toks1))
+    print("RESULT2 " + json.dumps(out2), flush=True)
+    one.close()
+ftp.close()
+dist.barrier()
 dist.destroy_process_group()
 '''
 
@@ -64,6 +103,12 @@ def test_tp2_matches_tp1(tmp_path):
     res = json.loads(line[len("RESULT "):])
     assert res["status"] == 0
     assert res["rel"] < 1e-5, res       # fp32 partial sums in a different order
+    assert res["tokens_equal"], res
+    line = [l for l in proc.stdout.splitlines() if l.startswith("RESULT2 ")][-1]
+    res = json.loads(line[len("RESULT2 "):])
+    assert res["status"] == 0 and res["ranks_agree"], res
+    assert "decode_step" in res["kernel"], res
+    assert res["rel"] < 1e-5, res
     assert res["tokens_equal"], res
 
 

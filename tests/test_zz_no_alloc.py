@@ -36,6 +36,31 @@ def test_static_scratch_matches_regular_entry_point(ctx, oracle, m, n, k):
     w.free()
 
 
+def test_static_scratch_allocates_nothing(oracle):
+    """A context that never reserved any scratch of its own: the free device memory reported
+    by the driver is the same before and after calls through the allocation-free entry point."""
+    import torch
+    m, n, k, g = 8, 2048, 4096, 32
+    packed, scales = oracle.pack_int4(synth.normal(75, 0, n * k, 0.02), n, k, g)
+    d_p, d_s = torch.from_numpy(packed).cuda(), torch.from_numpy(scales).cuda()
+    d_a = torch.from_numpy(synth.normal(76, 1, m * k, 1.0)).cuda()
+    out = torch.empty(m * n, dtype=torch.float32, device="cuda")
+    fresh = yscv_b200.Context(0)
+    # first call: looks up the built-in array's address and loads the kernels it needs
+    fresh.int4_matmul_dev_static(d_p.data_ptr(), d_s.data_ptr(), n, k, g, d_a.data_ptr(), out.data_ptr(), m)
+    fresh.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        fresh.int4_matmul_dev_static(d_p.data_ptr(), d_s.data_ptr(), n, k, g, d_a.data_ptr(), out.data_ptr(), m)
+    fresh.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    want = oracle.exec_matmul_int4(packed, scales, synth.normal(76, 1, m * k, 1.0), m, n, k, g).ravel()
+    assert np.max(np.abs(out.cpu().numpy() - want)) / np.max(np.abs(want)) <= 1e-4
+    assert fresh.device_status() == 0
+    fresh.close()
+
+
 def test_static_scratch_rejects_what_it_cannot_hold(ctx):
     import torch
     buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")

@@ -12,7 +12,14 @@ from .lib import (  # noqa: F401
     Int4Weight,
     YscvCudaError,
     DecodePlan,
+    Registry,
+    TpComm,
+    int4_container_read,
+    int4_container_write,
     int4_from_matmulnbits,
+    int4_to_matmulnbits,
+    quant_stats,
+    quant_stats_reset,
     load_library,
     library_path,
 )

@@ -16,7 +16,7 @@ LIB_PATH = PKG_DIR / "libyscv_cuda.so"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC",
     "-diag-suppress", "177",
 ]
 
@@ -38,16 +38,43 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not is_stale():
         return LIB_PATH
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH), *map(str, sources())]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
+    # one object per source file, compiled side by side (no device symbol crosses a file), then
+    # one link step; the objects live in a scratch directory outside the tree
+    import tempfile
+    from concurrent.futures import ThreadPoolExecutor
+    objdir = Path(tempfile.gettempdir()) / "yscv_b200_obj"
+    objdir.mkdir(exist_ok=True)
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.hpp")) + sorted((PKG_DIR.parent / "include").glob("*.h"))
+    newest_header = max((p.stat().st_mtime for p in headers), default=0.0)
+
+    def compile_one(src: Path):
+        obj = objdir / (src.stem + ".o")
+        if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, newest_header):
+            return obj, None
+        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        return obj, subprocess.run(cmd, capture_output=True, text=True)
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        results = list(pool.map(compile_one, sources()))
+    failed = False
+    for obj, proc in results:
+        if proc is None:
+            continue
+        if proc.returncode != 0:
+            sys.stderr.write(proc.stdout + proc.stderr)
+            failed = True
+        elif verbose:
+            sys.stderr.write(proc.stderr)
+    if failed:
+        raise RuntimeError("nvcc failed building libyscv_cuda.so")
+    link = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC",
+            "-o", str(LIB_PATH), *[str(o) for o, _ in results]]
+    proc = subprocess.run(link, capture_output=True, text=True)
     if proc.returncode != 0:
         sys.stderr.write(proc.stdout + proc.stderr)
-        raise RuntimeError("nvcc failed building libyscv_cuda.so")
-    if verbose:
-        sys.stderr.write(proc.stderr)
+        raise RuntimeError("nvcc failed linking libyscv_cuda.so")
     return LIB_PATH
 
 

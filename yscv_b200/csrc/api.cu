@@ -2,6 +2,7 @@
 // staging for the drop-in entry points, dispatch to the kernels.
 #include <cstdlib>
 #include <cstring>
+#include <set>
 
 #include "common.cuh"
 #include "kernels.cuh"
@@ -21,6 +22,21 @@ int fail(int status, const char *fmt, ...) {
     va_end(ap);
     last_error() = buf;
     return status;
+}
+
+int ensure_dynamic_smem(const void *kernel, int device, int bytes) {
+    static std::mutex mu;
+    static std::set<std::pair<const void *, int>> done;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.count({kernel, device})) return YSCV_CUDA_OK;
+    YSCV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done.insert({kernel, device});
+    return YSCV_CUDA_OK;
+}
+
+OpCounters &op_counters() {
+    static OpCounters c;
+    return c;
 }
 
 int DeviceBuffer::reserve(size_t want) {
@@ -65,6 +81,10 @@ static int int4_matmul_dev(yscv_cuda_ctx *ctx, const uint8_t *d_packed, const fl
     if (!exact_prefill && all_aligned && int4_prefill_supported(m, n, k, gs)) {
         rc = ctx->scratch.reserve(int4_prefill_scratch_bytes(m, k));
         if (rc) return rc;
+        op_counters().int4_gemm_calls++;
+        snprintf(ctx->report_int4, sizeof(ctx->report_int4),
+                 "int4_prefill_gemm m=%zu n=%zu k=%zu: tcgen05 bf16, 128-row weight tiles, dequant in shared memory",
+                 m, n, k);
         return int4_prefill_gemm(ctx, d_packed, d_scales, d_act, d_out, m, n, k, ctx->scratch.ptr);
     }
     for (size_t m0 = 0; m0 < m; m0 += 16) {
@@ -73,19 +93,16 @@ static int int4_matmul_dev(yscv_cuda_ctx *ctx, const uint8_t *d_packed, const fl
         float *o = d_out + m0 * n;
         const bool aligned = ((reinterpret_cast<uintptr_t>(d_packed) | reinterpret_cast<uintptr_t>(d_scales) |
                                reinterpret_cast<uintptr_t>(a)) & 15) == 0;
-        // small matrices are latency-bound: the light warp-per-row kernel starts faster than
-        // the TMA pipeline (threshold in packed bytes, YSCV_CUDA_SMALL_GEMV_BYTES overrides it)
-        static const size_t small_bytes = [] {
-            const char *e = getenv("YSCV_CUDA_SMALL_GEMV_BYTES");
-            return e ? (size_t)strtoull(e, nullptr, 10) : (size_t)0;
-        }();
-        const bool small = mc <= 4 && n * k / 2 <= small_bytes && gs % 32 == 0 && k % 32 == 0;
-        if (!small && aligned && int4_gemv_fast_supported(mc, n, k, gs)) {
+        if (aligned && int4_gemv_fast_supported(mc, n, k, gs)) {
             rc = ctx->scratch.reserve(int4_gemv_scratch_bytes(16, k));
             if (rc) return rc;
             rc = int4_gemv_fast(ctx, d_packed, d_scales, a, o, mc, n, k, ctx->scratch.ptr);
+            op_counters().int4_gemv_calls++;
         } else {
             rc = int4_gemv_generic(ctx, d_packed, d_scales, a, o, mc, n, k, gs);
+            op_counters().int4_generic_calls++;
+            snprintf(ctx->report_int4, sizeof(ctx->report_int4),
+                     "int4_gemv_generic m=%zu n=%zu k=%zu group=%zu: warp per row, fp32 FMAs", mc, n, k, gs);
         }
         if (rc) return rc;
     }
@@ -94,13 +111,10 @@ static int int4_matmul_dev(yscv_cuda_ctx *ctx, const uint8_t *d_packed, const fl
 
 }  // namespace yscv
 
+// The event pairs are created by yscv_cuda_ctx_profile_enable, never here: a launch path
+// must not allocate (launches past the pool are simply not bracketed).
 void yscv_cuda_ctx::prof_begin() {
-    if (!profiling) return;
-    if (prof_used == prof_events.size()) {
-        cudaEvent_t a, b;
-        if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
-        prof_events.emplace_back(a, b);
-    }
+    if (!profiling || prof_used >= prof_events.size()) return;
     cudaEventRecord(prof_events[prof_used].first, stream);
 }
 
@@ -175,6 +189,8 @@ void yscv_cuda_ctx_destroy(yscv_cuda_ctx *ctx) {
     ctx->scratch.release();
     ctx->scratch_attn.release();
     ctx->rowsum.release();
+    ctx->tmp_bt.release();
+    ctx->tmp_colsum.release();
     if (ctx->d_status) cudaFree(ctx->d_status);
     for (auto &ev : ctx->prof_events) {
         cudaEventDestroy(ev.first);
@@ -201,6 +217,19 @@ int yscv_cuda_ctx_device_status(yscv_cuda_ctx *ctx, int *status) {
 
 int yscv_cuda_ctx_profile_enable(yscv_cuda_ctx *ctx, int enable) {
     if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    if (enable) {
+        YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+        while (ctx->prof_events.size() < 4096) {
+            cudaEvent_t a, b;
+            YSCV_CUDA_TRY(cudaEventCreate(&a));
+            cudaError_t e = cudaEventCreate(&b);
+            if (e != cudaSuccess) {
+                cudaEventDestroy(a);
+                return fail(YSCV_CUDA_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e));
+            }
+            ctx->prof_events.emplace_back(a, b);
+        }
+    }
     ctx->profiling = enable != 0;
     return YSCV_CUDA_OK;
 }
@@ -489,7 +518,9 @@ static int i8_gemm_dev(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b 
     if (m == 0) return YSCV_CUDA_OK;
     if (m >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "dimension too large");
     YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    op_counters().int8_gemm_calls++;
     if (rq) {
+        op_counters().qlinear_matmul_calls++;
         if (rq->qmin > rq->qmax || rq->qmin < -128 || rq->qmax > 255 || rq->qmax - rq->qmin > 255)
             return fail(YSCV_CUDA_ERR_BAD_ARG, "requant range [%d,%d] does not fit one byte", rq->qmin, rq->qmax);
         return int8_gemm(ctx, d_a, b, m, d_out, rq->a_is_unsigned, rq->a_zero_point, 1, rq->composite,
@@ -535,12 +566,27 @@ int yscv_cuda_int8_matmul(yscv_cuda_ctx *ctx, const int8_t *a, const int8_t *b, 
         memset(out, 0, m * n * sizeof(int32_t));
         return YSCV_CUDA_OK;
     }
-    yscv_cuda_i8b *packed = nullptr;
-    int rc = yscv_cuda_pack_i8_b_for_matmul(ctx, b, k, n, &packed);
+    int rc = check_i8_shape(k, n);
     if (rc) return rc;
-    rc = yscv_cuda_int8_matmul_prepacked(ctx, a, packed, m, out);
-    yscv_cuda_i8b_free(packed);
-    return rc;
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    // B^T and its column sums live in buffers the context keeps (grow-only): no allocation
+    // per call once the largest shape has been seen
+    const size_t kp = (k + 15) / 16 * 16;
+    if ((rc = ctx->in1.reserve(k * n)) || (rc = ctx->tmp_bt.reserve(n * kp)) ||
+        (rc = ctx->tmp_colsum.reserve(n * sizeof(int32_t))))
+        return rc;
+    YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in1.ptr, b, k * n, cudaMemcpyHostToDevice, ctx->stream));
+    rc = pack_i8_b(ctx, (const int8_t *)ctx->in1.ptr, k, n, (int8_t *)ctx->tmp_bt.ptr,
+                   (int32_t *)ctx->tmp_colsum.ptr, kp);
+    if (rc) return rc;
+    yscv_cuda_i8b view;
+    view.d_bt = (int8_t *)ctx->tmp_bt.ptr;
+    view.d_colsum = (int32_t *)ctx->tmp_colsum.ptr;
+    view.k = k;
+    view.n = n;
+    view.kp = kp;
+    view.device = ctx->device;
+    return yscv_cuda_int8_matmul_prepacked(ctx, a, &view, m, out);
 }
 
 int yscv_cuda_qlinear_matmul_dev(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_t m,
@@ -565,6 +611,7 @@ static int i8_requant_i8_dev(yscv_cuda_ctx *ctx, const int8_t *d_a, const yscv_c
     if (m == 0) return YSCV_CUDA_OK;
     if (m >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "dimension too large");
     YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    op_counters().int8_gemm_calls++;
     return int8_gemm(ctx, d_a, b, m, d_out, 0, 0, 1, composite, y_zp, -128, 127, 0, d_corr, d_comp_pc, relu);
 }
 
@@ -623,11 +670,13 @@ int yscv_cuda_int8_matmul_requant_i8(yscv_cuda_ctx *ctx, const int8_t *a, const 
 int yscv_cuda_matmul_integer_dev(yscv_cuda_ctx *ctx, const void *d_a, int a_is_unsigned,
                                  int32_t a_zero_point, const yscv_cuda_i8b *b, size_t m,
                                  int32_t *d_out) {
+    op_counters().matmul_integer_calls++;
     return i8_gemm_dev(ctx, d_a, b, m, d_out, a_is_unsigned, a_zero_point, nullptr);
 }
 
 int yscv_cuda_matmul_integer(yscv_cuda_ctx *ctx, const void *a, int a_is_unsigned, int32_t a_zero_point,
                              const yscv_cuda_i8b *b, size_t m, int32_t *out) {
+    op_counters().matmul_integer_calls++;
     return i8_gemm_host(ctx, a, b, m, out, sizeof(int32_t), a_is_unsigned, a_zero_point, nullptr);
 }
 

@@ -4,8 +4,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 #include <string>
 #include <utility>
 #include <vector>
@@ -26,6 +28,20 @@ int fail(int status, const char *fmt, ...);
                                 cudaGetErrorString(_e), __FILE__, __LINE__);        \
     } while (0)
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device); safe to call
+// from several threads.
+int ensure_dynamic_smem(const void *kernel, int device, int bytes);
+
+// Process-wide operator counters, the counterpart of the reference's QuantRuntimeStats
+// (crates/yscv-onnx/src/runner/quant_stats.rs:21-92): bumped by the entry points, read and
+// reset through yscv_cuda_quant_stats / yscv_cuda_reset_quant_stats.
+struct OpCounters {
+    std::atomic<uint64_t> int4_gemv_calls{0}, int4_gemm_calls{0}, int4_generic_calls{0};
+    std::atomic<uint64_t> int8_gemm_calls{0}, qlinear_matmul_calls{0}, matmul_integer_calls{0};
+    std::atomic<uint64_t> requant_calls{0}, decode_step_calls{0};
+};
+OpCounters &op_counters();
+
 // Grow-only device buffer owned by a context.
 struct DeviceBuffer {
     void *ptr = nullptr;
@@ -41,6 +57,10 @@ struct DeviceBuffer {
 // stream is still draining. It must call pdl_wait() before it reads anything a predecessor
 // wrote or writes anything a predecessor may still read; pdl_trigger() lets its own
 // successor be scheduled early. Both are no-ops for a normally launched kernel.
+// EVERY kernel launched through launch_pdl() MUST execute pdl_wait() on all paths, even one
+// that touches nothing a predecessor wrote: a kernel that skips it can retire while its
+// predecessor (which triggered early) is still running, and the next kernel's wait would then
+// cover only the skipping kernel, not that predecessor.
 #ifdef __CUDACC__
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
@@ -69,6 +89,7 @@ enum : int {
     YSCV_DEV_OK = 0,
     YSCV_DEV_MBARRIER_TIMEOUT = 1,
     YSCV_DEV_FLAG_TIMEOUT = 2,
+    YSCV_DEV_POS_OVERFLOW = 3,  // the sequence position is outside [0, max_seq): nothing was appended
 };
 
 struct yscv_cuda_ctx {
@@ -92,6 +113,10 @@ struct yscv_cuda_ctx {
     yscv::DeviceBuffer scratch;
     yscv::DeviceBuffer scratch_attn;  // partial outputs of the split attention
     yscv::DeviceBuffer rowsum;        // row sums of A (int8 GEMM with a zero point on B)
+    yscv::DeviceBuffer tmp_bt, tmp_colsum;  // B^T and column sums of the non-prepacked int8 entry point
+    // variant / tile report of the last int4 and int8 dispatch (yscv_cuda_dispatch_report)
+    char report_int4[160] = "none";
+    char report_int8[160] = "none";
 };
 
 struct yscv_cuda_int4_weight {
@@ -110,4 +135,17 @@ struct yscv_cuda_i8b {
     size_t k = 0, n = 0, kp = 0;
     int device = 0;
     int b_zp = 0;  // zero point of B (yscv_cuda_i8b_set_zero_point)
+};
+
+// One rank's view of a tensor-parallel group: its own exchange region and every peer's,
+// mapped through CUDA IPC (tp_comm.cu).
+struct yscv_cuda_tp_comm {
+    int device = 0, rank = 0, world = 1;
+    size_t cap_rows = 0, bytes = 0;
+    void *local = nullptr;        // this rank's region (cudaMalloc)
+    void *peer[8] = {};           // every rank's region as mapped in this process (peer[rank] == local)
+    bool opened[8] = {};          // mapped with cudaIpcOpenMemHandle, to be closed
+    void *standin = nullptr;      // test form: local stand-ins for the peers' regions that nobody writes
+    unsigned int *d_seq = nullptr;  // steps run so far (tags of the exchanges)
+    bool connected = false;
 };

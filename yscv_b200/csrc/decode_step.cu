@@ -102,27 +102,22 @@ struct StepParams {
     int one_tile_16;  // 1: a one-tile slab is split over 16 K slices (all warps) instead of 8
     int merge_table;  // 1: the split-merge weights go through a shared-memory table
     int relaxed_poll; // 1: the barrier polls with relaxed loads and fences once
+    int spin_limit;   // probes after which a waiting CTA gives up (grid barrier, peer slots)
+    // tensor parallelism (tp_size > 1): this launch is one rank of tp_size identical launches on
+    // tp_size GPUs. The weights handed to the plan are this rank's shards (n_q, n_kv, inter are
+    // the local counts); the output and down projections then produce partial sums over K, which
+    // the ranks exchange through tp_peer[r], rank r's exchange region mapped into this process
+    // (peer memory over NVLink; tp_peer[tp_rank] is the local one):
+    //   slot word (parity, source rank, row) = {f32 partial sum, 32-bit tag} as one 64-bit store,
+    //   written into every peer's region by the thread that owns the row, who then polls its own
+    //   region until all tp_size - 1 words carry this exchange's tag and adds them in rank order.
+    // No multicast, no atomics, no collective library inside the step.
+    int tp_rank, tp_size, tp_cap;          // tp_cap: rows per (parity, source) slot array
+    unsigned long long *tp_peer[8];
+    unsigned int *tp_seq;                  // steps this plan has run (device word, local)
+    int lm_row0, lm_rows;                  // this rank's rows of the LM head (all of them when tp_size == 1)
 };
 
-#ifdef YSCV_TRACE
-// debugging aid (not built by default): per-CTA timestamps of the first four layers
-__device__ unsigned long long g_step_trace[148 * 64];
-extern "C" int yscv_step_trace_read(unsigned long long *dst) {
-    return (int)cudaMemcpyFromSymbol(dst, g_step_trace, sizeof(g_step_trace));
-}
-#define STRACE(slot)                                                                    \
-    do {                                                                                \
-        if (threadIdx.x == 0 && (slot) >= 0 && (slot) < 64) {                                          \
-            unsigned long long _t;                                                      \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                      \
-            g_step_trace[blockIdx.x * 64 + (slot)] = _t;                                \
-        }                                                                               \
-    } while (0)
-#define ATRACE(slot) do { if (layer == 2) STRACE(48 + (slot)); } while (0)
-#else
-#define STRACE(slot) do { } while (0)
-#define ATRACE(slot) do { } while (0)
-#endif
 
 // ---- consumer-side helpers (the 512 consumer threads only; named barrier 1) ---------------
 
@@ -164,6 +159,66 @@ __device__ __forceinline__ unsigned int ld_relaxed_u32(const unsigned int *p) {
     return v;
 }
 
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;\n" ::"l"(p), "l"(v) : "memory");
+}
+
+// Slot index of exchange word (parity, source rank, row); slots past the row arrays hold the
+// greedy-token exchange: (parity, source rank, {value, index}).
+__device__ __forceinline__ size_t tp_slot(const StepParams &p, int parity, int src, int row) {
+    return ((size_t)(parity * p.tp_size + src)) * p.tp_cap + row;
+}
+__device__ __forceinline__ size_t tp_arg_slot(const StepParams &p, int parity, int src, int which) {
+    return (size_t)2 * p.tp_size * p.tp_cap + (size_t)((parity * p.tp_size + src) * 2 + which);
+}
+
+// Polls one word of the local exchange region until it carries `tag`. Bounded: after
+// p.spin_limit probes the abort flag and the status word are set and whatever is there is
+// returned; a raised abort flag ends the wait early.
+__device__ __forceinline__ unsigned int tp_wait_word(const StepParams &p, const unsigned long long *src,
+                                                     unsigned int tag) {
+    unsigned long long w = ld_relaxed_sys_u64(src);
+    int spins = 0;
+    while ((unsigned int)(w >> 32) != tag) {
+        ++spins;
+        if ((spins & 63) == 0 && ld_acquire_u32(&p.sync[2]) != 0u) {
+            *p.status = YSCV_DEV_FLAG_TIMEOUT;
+            break;
+        }
+        if (spins > p.spin_limit) {
+            atomicExch(&p.sync[2], 1u);
+            *p.status = YSCV_DEV_FLAG_TIMEOUT;
+            break;
+        }
+        w = ld_relaxed_sys_u64(src);
+    }
+    return (unsigned int)w;
+}
+
+// All-reduce of one element of a row-parallel GEMV across the ranks, by the thread that owns
+// the row: publish this rank's partial sum in every peer's region, then add the ranks'
+// partials in rank order (the same order, hence the same bits, on every rank).
+__device__ __forceinline__ float tp_reduce_row(const StepParams &p, int row, float v, unsigned int tag,
+                                               int parity) {
+    const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    const size_t mine = tp_slot(p, parity, p.tp_rank, row);
+    for (int r = 0; r < p.tp_size; ++r)
+        if (r != p.tp_rank) st_relaxed_sys_u64(p.tp_peer[r] + mine, word);
+    const unsigned long long *local = p.tp_peer[p.tp_rank];
+    float sum = 0.0f;
+    for (int r = 0; r < p.tp_size; ++r) {
+        const float part = r == p.tp_rank ? v : __uint_as_float(tp_wait_word(p, local + tp_slot(p, parity, r, row), tag));
+        sum = r == 0 ? part : sum + part;
+    }
+    return sum;
+}
+
 // Grid-wide barrier of the consumers. `epoch` counts the barriers of this launch (the same in
 // every thread). A CTA that waits longer than the limit raises the abort flag; from then on
 // every barrier of every CTA falls through, the kernel runs to its end and the host finds the
@@ -180,8 +235,13 @@ __device__ __forceinline__ void grid_barrier(const StepParams &p, unsigned int &
         int spins = 0;
         while ((p.relaxed_poll ? ld_relaxed_u32(&p.sync[0]) : ld_acquire_u32(&p.sync[0])) < target) {
             ++spins;
-            if ((spins & 63) == 0 && ld_acquire_u32(&p.sync[2]) != 0u) break;
-            if (spins > DS_SPIN_LIMIT) {
+            if ((spins & 63) == 0 && ld_acquire_u32(&p.sync[2]) != 0u) {
+                // another CTA gave up (in this launch or an earlier one of the same plan): the
+                // step's result is void, say so again in case the status word was read and cleared
+                *p.status = YSCV_DEV_FLAG_TIMEOUT;
+                break;
+            }
+            if (spins > p.spin_limit) {
                 atomicExch(&p.sync[2], 1u);
                 *p.status = YSCV_DEV_FLAG_TIMEOUT;
                 break;
@@ -310,8 +370,9 @@ __device__ __forceinline__ void consume_stages(const StepParams &p, const unsign
 // 2 the block is gate tiles then up tiles of intermediate indices: out[i] = silu(gate_i) * up_i.
 // Rows (indices) of the block start at row_base; nothing at or past r1 is written.
 template <int TP2>
-__device__ __forceinline__ void finish_rows(float *red, int tiles, int row_base, int r1, float *out,
-                                            int store, const float (&acc)[2], float resid) {
+__device__ __forceinline__ void finish_rows(const StepParams &p, float *red, int tiles, int row_base, int r1,
+                                            float *out, int store, const float (&acc)[2], float resid,
+                                            unsigned int tp_tag, int tp_parity) {
     constexpr int GS = DS_GS;
     constexpr int KSL = (16 / TP2 < GS) ? 16 / TP2 : GS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -345,7 +406,11 @@ __device__ __forceinline__ void finish_rows(float *red, int tiles, int row_base,
             const float *pp = red + ((ks * tiles + tl) * 2 + half) * 32 + q8 * 4;
             v += pp[0] + pp[1];
         }
-        if (my_row < r1) out[my_row] = store == 1 ? resid + v : v;
+        // store 1 under tensor parallelism: v is this rank's partial sum over its K slice
+        if (my_row < r1) {
+            if (store == 1 && p.tp_size > 1) v = tp_reduce_row(p, my_row, v, tp_tag, tp_parity);
+            out[my_row] = store == 1 ? resid + v : v;
+        }
     }
     cons_sync();  // `red` is reused by the next block
 }
@@ -592,7 +657,6 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
     }
     const bool has_new = (pos >= k0 && pos < k1);          // the split that sees the new position
     const bool owner = has_new && (h % grp) == 0;          // ... of the first head of the group appends
-    ATRACE(0);
 
     // ---- loads ----
     constexpr int KQ = 8;   // float4 per thread of a key row: d/16 <= 8
@@ -621,7 +685,6 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
     } else if (tid < 2 * d) {
         x0 = __ldcg(p.qkv + (size_t)(p.n_q + p.n_kv + kvh) * d + (tid - d));
     }
-    ATRACE(1);
 
     // ---- RoPE, append ----
     if (tid < d) {
@@ -640,7 +703,6 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
         if (owner) vc[((size_t)pos * p.n_kv + kvh) * d + (tid - d)] = x0;
     }
     cons_sync();
-    ATRACE(2);
 
     // ---- scores: four threads per key, a quarter of the row each ----
     const float scale = 1.0f / sqrtf((float)d);
@@ -693,7 +755,6 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
             mx = fmaxf(mx, sc);
         }
     }
-    ATRACE(3);
     mx = cons_max(mx, misc);
     float se = 0.0f;
     for (int kk = tid; kk < nk; kk += DS_CONSUMERS) {
@@ -702,7 +763,6 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
         se += e;
     }
     se = cons_sum(se, misc);  // (its barriers also publish `scores`)
-    ATRACE(4);
 
     // ---- weighted V: d/4 threads per key row, the keys dealt round-robin to 512/(d/4) parts ----
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -740,7 +800,6 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
         }
     }
     *(reinterpret_cast<float4 *>(partial + (size_t)part * d) + c4) = acc;
-    ATRACE(5);
     cons_sync();
     if (tid < d) {
         float v = 0.0f;
@@ -748,7 +807,6 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
         po[tid] = v;
     }
     if (tid == 0) { po[d] = mx; po[d + 1] = se; }
-    ATRACE(6);
     cons_sync();  // scratch is reused
 }
 
@@ -771,6 +829,16 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     float **cache_ptr = reinterpret_cast<float **>(rope_cs + p.d_head);  // [layers] x {k, v}
     float *wtab = reinterpret_cast<float *>(cache_ptr + 2 * p.layers);   // [n_q][4] split-merge weights
     const int nmat = p.layers * 4;
+
+    // A position outside the cache: nothing is appended, nothing is computed, the status word
+    // says so (every thread of every CTA takes the same way out, before any barrier).
+    {
+        const int pos_in = *p.pos;
+        if (pos_in < 0 || pos_in >= p.max_seq) {
+            if (blockIdx.x == 0 && tid == 0) *p.status = YSCV_DEV_POS_OVERFLOW;
+            return;
+        }
+    }
 
     if (tid == DS_CONSUMERS) {
         for (int i = 0; i < p.stages; ++i) {
@@ -847,6 +915,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     RingPos c = {0, 0u};
     bool dead = false;
     const int H = p.hidden, I = p.inter;
+    // exchanges of this launch are tagged tp_tag_base + 1 ... + 2 * layers (the row-parallel
+    // GEMVs) and + 2 * layers + 1 (the greedy token)
+    const unsigned int tp_seq = p.tp_size > 1 ? *p.tp_seq : 0u;
+    const unsigned int tp_tag_base = tp_seq * (unsigned int)(2 * p.layers + 1);
+    int tp_ar = 0;
 
     // One matrix: for every K chunk, `stage_chunk(k0, klen)` leaves the activations of that
     // chunk in act_s and their digit planes in `dig`; then every row block of the CTA walks the
@@ -862,6 +935,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         const int r0 = (int)((n * blockIdx.x) / gridDim.x);
         const int r1 = (int)((n * (blockIdx.x + 1)) / gridDim.x);
         const int block_rows = (store == 2 ? tiles / 2 : tiles) * 16;
+        // row-parallel GEMV under tensor parallelism: the tag of this exchange (never 0, the
+        // value of untouched slots) and its slot parity (two exchanges per layer: consecutive
+        // ones alternate, also across launches)
+        const unsigned int tp_tag = tp_tag_base + (unsigned int)tp_ar + 1u;
         float acc[2] = {0.0f, 0.0f};
         for (int cs = 0; cs < k_stages; cs += kc) {
             const int ce = min(k_stages, cs + kc);
@@ -878,19 +955,20 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
                 if (n_rb > 1) { acc[0] = 0.0f; acc[1] = 0.0f; }
                 if (tiles == 1 && p.one_tile_16) {
                     consume_stages<1>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
-                    if (last) finish_rows<1>(red, tiles, row_base, r1, out, store, acc, resid);
+                    if (last) finish_rows<1>(p, red, tiles, row_base, r1, out, store, acc, resid, tp_tag, tp_ar & 1);
                 } else if (tiles <= 2) {
                     consume_stages<2>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
-                    if (last) finish_rows<2>(red, tiles, row_base, r1, out, store, acc, resid);
+                    if (last) finish_rows<2>(p, red, tiles, row_base, r1, out, store, acc, resid, tp_tag, tp_ar & 1);
                 } else if (!SIMPLE && tiles <= 4) {   // (small models have no 3- or 4-tile slab)
                     consume_stages<4>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
-                    if (last) finish_rows<4>(red, tiles, row_base, r1, out, store, acc, resid);
+                    if (last) finish_rows<4>(p, red, tiles, row_base, r1, out, store, acc, resid, tp_tag, tp_ar & 1);
                 } else {
                     consume_stages<8>(p, smem, bar_full, bar_empty, dig, c, tiles, cs, ce, kps, cs, acc, dead);
-                    if (last) finish_rows<8>(red, tiles, row_base, r1, out, store, acc, resid);
+                    if (last) finish_rows<8>(p, red, tiles, row_base, r1, out, store, acc, resid, tp_tag, tp_ar & 1);
                 }
             }
         }
+        if (store == 1) ++tp_ar;
     };
     // act_s = RMSNorm(x) * gamma
     auto stage_norm = [&](const float *gamma) {
@@ -924,8 +1002,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
 
     // per-launch constants: the position, its rotary factors, the cache pointers; the padding
     // row of the digit planes
-    int pos = *p.pos;
-    pos = pos < 0 ? 0 : (pos >= p.max_seq ? p.max_seq - 1 : pos);
+    const int pos = *p.pos;   // inside [0, max_seq): checked at the top
     if (tid < p.d_head / 2) {
         const float inv_freq = 1.0f / powf(p.theta, 2.0f * (float)tid / (float)p.d_head);
         sincosf(inv_freq * (float)pos, &rope_cs[2 * tid + 1], &rope_cs[2 * tid]);
@@ -1062,13 +1139,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
 
     for (int l = 0; l < p.layers; ++l) {
         const float *g1 = p.gamma + (size_t)(2 * l) * H, *g2 = g1 + H;
-        [[maybe_unused]] const int ts = l < 3 ? l * 16 : -100;  // trace slots of this layer (debug builds)
-        STRACE(ts + 0);
         // attention block: norm -> qkv
         gemv(4 * l + 0, p.qkv, 0, [&](int, int) { stage_normed(g1); });
-        STRACE(ts + 3);
         grid_barrier(p, epoch);
-        STRACE(ts + 4);
         // RoPE, cache append, attention: a few CTAs per query head, or (long contexts) one CTA
         // per KV head and key chunk followed by a merge phase
         if (!SIMPLE && p.attn_grouped) {
@@ -1081,36 +1154,29 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
             attention_head<SIMPLE ? 4 : 8>(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
                            cache_ptr[2 * l + 1], rope_cs, act_s, misc);
         }
-        STRACE(ts + 5);
         grid_barrier(p, epoch);
-        STRACE(ts + 6);
         // output projection, residual add in the store
         gemv(4 * l + 1, p.x, 1, [&](int, int) { stage_attention(); });
-        STRACE(ts + 8);
         grid_barrier(p, epoch);
-        STRACE(ts + 9);
         // MLP: norm -> gate+up -> SwiGLU -> down, residual add in the store
         gemv(4 * l + 2, p.gu, p.pair_gu ? 2 : 0, [&](int, int) { stage_normed(g2); });
-        STRACE(ts + 11);
         grid_barrier(p, epoch);
-        STRACE(ts + 12);
         gemv(4 * l + 3, p.x, 1, stage_mlp);
-        STRACE(ts + 14);
         grid_barrier(p, epoch);
-        STRACE(ts + 15);
     }
 
     // ---- optional tail: final norm, LM head, greedy token ----
     if (p.tail) {
         stage_norm(p.final_gamma);   // act_s = the normalised last hidden state
-        const int v0 = (int)(((unsigned long long)p.vocab * blockIdx.x) / gridDim.x);
-        const int v1 = (int)(((unsigned long long)p.vocab * (blockIdx.x + 1)) / gridDim.x);
+        // this rank's rows of the LM head (all of them on one GPU); tokens are global indices
+        const int v0 = p.lm_row0 + (int)(((unsigned long long)p.lm_rows * blockIdx.x) / gridDim.x);
+        const int v1 = p.lm_row0 + (int)(((unsigned long long)p.lm_rows * (blockIdx.x + 1)) / gridDim.x);
         // one warp per vocabulary row, the same summation order as f32_matmul_kernel
         float best = -INFINITY;
         int besti = -1;
         const float4 *x4 = reinterpret_cast<const float4 *>(act_s);
         for (int row = v0 + warp; row < v1; row += DS_CONSUMER_WARPS) {
-            const float4 *wr = reinterpret_cast<const float4 *>(p.lm_head + (size_t)row * H);
+            const float4 *wr = reinterpret_cast<const float4 *>(p.lm_head + (size_t)(row - p.lm_row0) * H);
             float acc = 0.0f;
 #pragma unroll 4
             for (int cidx = lane; cidx < H / 4; cidx += 32) {
@@ -1155,6 +1221,33 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
                 if (iv >= 0 && (ib < 0 || v > b || (v == b && iv > ib))) { b = v; ib = iv; }
             }
             if (lane == 0) {
+                if (p.tp_size > 1) {
+                    // exchange the ranks' best (value, index): same slots-and-tags scheme as the
+                    // row-parallel GEMVs, parity by step; every rank reduces in rank order with
+                    // the same tie rule (the larger index wins), so every rank picks the same token
+                    const unsigned int tag = tp_tag_base + (unsigned int)(2 * p.layers) + 1u;
+                    const int par = (int)(tp_seq & 1u);
+                    const unsigned long long wv = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(b);
+                    const unsigned long long wi = ((unsigned long long)tag << 32) | (unsigned long long)(unsigned int)ib;
+                    for (int r = 0; r < p.tp_size; ++r) {
+                        if (r == p.tp_rank) continue;
+                        st_relaxed_sys_u64(p.tp_peer[r] + tp_arg_slot(p, par, p.tp_rank, 0), wv);
+                        st_relaxed_sys_u64(p.tp_peer[r] + tp_arg_slot(p, par, p.tp_rank, 1), wi);
+                    }
+                    const unsigned long long *local = p.tp_peer[p.tp_rank];
+                    float gb = -INFINITY;
+                    int gi = -1;
+                    for (int r = 0; r < p.tp_size; ++r) {
+                        float v = b;
+                        int iv = ib;
+                        if (r != p.tp_rank) {
+                            v = __uint_as_float(tp_wait_word(p, local + tp_arg_slot(p, par, r, 0), tag));
+                            iv = (int)tp_wait_word(p, local + tp_arg_slot(p, par, r, 1), tag);
+                        }
+                        if (iv >= 0 && (gi < 0 || v > gb || (v == gb && iv > gi))) { gb = v; gi = iv; }
+                    }
+                    ib = gi;
+                }
                 *p.token_out = ib < 0 ? 0 : ib;
                 *p.pos_out = pos + 1;
             }
@@ -1168,6 +1261,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         if (prev == gridDim.x - 1) {
             p.sync[0] = 0u;
             p.sync[1] = 0u;
+            if (p.tp_size > 1) *p.tp_seq = tp_seq + 1u;  // the next launch's exchanges get fresh tags
             __threadfence();
         }
     }
@@ -1186,6 +1280,8 @@ struct yscv_cuda_decode_plan {
     bool simple = false;
     void *d_mats = nullptr, *d_gamma = nullptr, *d_kptr = nullptr, *d_vptr = nullptr;
     void *d_scratch = nullptr, *d_sync = nullptr;
+    bool poisoned = false;   // a bounded wait ran out in a step of this plan (yscv_cuda_decode_plan_check)
+    int tp_rank = 0, tp_size = 1;
 };
 
 extern "C" void yscv_cuda_decode_plan_free(yscv_cuda_decode_plan *plan) {
@@ -1204,6 +1300,15 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
                                             size_t n_layers, size_t hidden, size_t inter, size_t n_q,
                                             size_t n_kv, size_t d_head, size_t max_seq, float eps,
                                             float rope_theta, yscv_cuda_decode_plan **out) {
+    return yscv_cuda_decode_plan_create_ex(ctx, layers, n_layers, hidden, inter, n_q, n_kv, d_head, max_seq, eps,
+                                           rope_theta, nullptr, out);
+}
+
+extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cuda_decode_layer *layers,
+                                               size_t n_layers, size_t hidden, size_t inter, size_t n_q,
+                                               size_t n_kv, size_t d_head, size_t max_seq, float eps,
+                                               float rope_theta, const yscv_cuda_decode_options *opt,
+                                               yscv_cuda_decode_plan **out) {
     using namespace yscv;
     if (!ctx || !layers || !out || n_layers == 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
     *out = nullptr;
@@ -1221,19 +1326,20 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
         yscv_cuda_decode_plan_free(plan);
         return rc;
     };
-    // kernel variants (YSCV_CUDA_STEP_VARIANT, a bit mask read when the plan is built):
-    // 1 gate/up pairing, 2 sixteen K slices for one-tile slabs, 4 merge-weight table,
-    // 8 relaxed barrier polling
-    const char *venv = getenv("YSCV_CUDA_STEP_VARIANT");
-    const int variant = venv ? atoi(venv) : DS_DEFAULT_VARIANT;
+    // kernel variants (options: a bit mask): 1 gate/up pairing, 2 sixteen K slices for one-tile
+    // slabs, 4 merge-weight table, 8 relaxed barrier polling
+    const int variant = (opt && opt->variant >= 0) ? opt->variant : DS_DEFAULT_VARIANT;
     // geometry limits, overridable so that small test shapes reach the row-block and K-chunk
-    // paths: tiles per row block (YSCV_CUDA_STEP_MAX_TILES, 2..8, even), k per chunk
-    // (YSCV_CUDA_STEP_KCHUNK, a multiple of 512)
-    const char *tenv = getenv("YSCV_CUDA_STEP_MAX_TILES"), *kenv = getenv("YSCV_CUDA_STEP_KCHUNK");
-    int max_tiles = tenv ? atoi(tenv) : 8;
+    // paths: tiles per row block (2..8, even), k per chunk (a multiple of 512)
+    int max_tiles = (opt && opt->max_tiles > 0) ? opt->max_tiles : 8;
     max_tiles = max_tiles < 2 ? 2 : (max_tiles > 8 ? 8 : max_tiles & ~1);
-    int kc_limit = kenv ? atoi(kenv) / 512 : 16;   // 16 stages = 8192 k = 64 KB of digit planes
+    int kc_limit = (opt && opt->k_chunk > 0) ? opt->k_chunk / 512 : 16;   // 16 stages = 8192 k = 64 KB of digit planes
     kc_limit = kc_limit < 1 ? 1 : (kc_limit > 16 ? 16 : kc_limit);
+    const yscv_cuda_tp_comm *tp = opt ? opt->tp : nullptr;
+    if (tp && (tp->device != ctx->device || !tp->connected))
+        return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: the exchange region is not connected on device %d", ctx->device));
+    if (tp && tp->cap_rows < hidden)
+        return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: the exchange region holds %zu rows, hidden is %zu", tp->cap_rows, hidden));
     // rows (or paired indices) per CTA -> row blocks of at most `cap` tiles, balanced
     auto blocks_of = [&](size_t per_cta, int cap, int *tiles_out) {
         const int n_rb = (int)((per_cta + (size_t)cap * 16 - 1) / ((size_t)cap * 16));
@@ -1253,6 +1359,9 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
         const size_t want_k[4] = {hidden, attn_w, hidden, inter};
         if (!layers[l].d_gamma_attn || !layers[l].d_gamma_mlp || !layers[l].d_kcache || !layers[l].d_vcache)
             return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: layer %zu has a null pointer", l));
+        // key and value rows are read with 128-bit loads
+        if ((reinterpret_cast<uintptr_t>(layers[l].d_kcache) | reinterpret_cast<uintptr_t>(layers[l].d_vcache)) & 15)
+            return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: the caches of layer %zu must be 16-byte aligned", l));
         for (int j = 0; j < 4; ++j) {
             if (!w[j]) return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: layer %zu has a null weight", l));
             if (w[j]->m_w != want_n[j] || w[j]->k != want_k[j])
@@ -1315,8 +1424,8 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     const size_t grp = n_q / n_kv;
     const bool group_ok = (grp & (grp - 1)) == 0 && grp <= 16 && grp * d_head <= 2048 &&
                           DS_CONSUMERS % (grp * d_head / 4) == 0;
-    const char *aenv = getenv("YSCV_CUDA_STEP_ATTN");
-    const bool grouped = group_ok && (aenv ? atoi(aenv) != 0 : (max_seq + splits - 1) / splits > 256);
+    const int attn_form = opt ? opt->attention_form : -1;
+    const bool grouped = group_ok && (attn_form >= 0 ? attn_form != 0 : (max_seq + splits - 1) / splits > 256);
     const int g_splits = (int)std::max<size_t>(1, std::min<size_t>(32, (size_t)grid / n_kv));
     const int g_cap = (int)(((max_seq + g_splits - 1) / g_splits + 3) / 4 * 4);
     // the attention scratch lives in the activation area between the GEMVs: widen that area if
@@ -1407,6 +1516,18 @@ extern "C" int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_
     p.one_tile_16 = (variant & 2) ? 1 : 0;
     p.merge_table = (variant & 4) ? 1 : 0;
     p.relaxed_poll = (variant & 8) ? 1 : 0;
+    p.spin_limit = (opt && opt->spin_limit > 0) ? opt->spin_limit : DS_SPIN_LIMIT;
+    p.tp_rank = 0;
+    p.tp_size = 1;
+    if (tp) {
+        p.tp_rank = tp->rank;
+        p.tp_size = tp->world;
+        p.tp_cap = (int)tp->cap_rows;
+        for (int r = 0; r < tp->world; ++r) p.tp_peer[r] = reinterpret_cast<unsigned long long *>(tp->peer[r]);
+        p.tp_seq = tp->d_seq;
+        plan->tp_rank = tp->rank;
+        plan->tp_size = tp->world;
+    }
     for (int j = 0; j < 4; ++j) {
         p.mat_n[j] = mats[j].n;
         p.mat_tiles[j] = mats[j].tiles;
@@ -1445,21 +1566,78 @@ static int launch_step(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan, ys
     return YSCV_CUDA_OK;
 }
 
-extern "C" int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
-                                              const float *d_embedding, size_t vocab, const int32_t *d_token,
-                                              const int32_t *d_pos, float *d_x) {
+extern "C" int yscv_cuda_decode_plan_check(yscv_cuda_ctx *ctx, yscv_cuda_decode_plan *plan) {
+    using namespace yscv;
+    if (!ctx || !plan) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (plan->poisoned) return fail(YSCV_CUDA_ERR_TIMEOUT, "a bounded wait ran out in an earlier step of this plan: rebuild it");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    unsigned int words[4] = {0, 0, 0, 0};
+    YSCV_CUDA_TRY(cudaMemcpyAsync(words, plan->d_sync, sizeof(words), cudaMemcpyDeviceToHost, ctx->stream));
+    YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    if (words[2] != 0u) {
+        plan->poisoned = true;
+        return fail(YSCV_CUDA_ERR_TIMEOUT, "a bounded wait ran out in a step of this plan: its results are void, rebuild it");
+    }
+    return YSCV_CUDA_OK;
+}
+
+static int step_common(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan, const float *d_embedding, size_t vocab,
+                       const int32_t *d_token, const int32_t *d_pos, float *d_x, yscv::StepParams &p) {
     using namespace yscv;
     if (!ctx || !plan || !d_embedding || !d_token || !d_pos || !d_x || vocab == 0)
         return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
     if (plan->device != ctx->device) return fail(YSCV_CUDA_ERR_BAD_ARG, "plan belongs to device %d", plan->device);
+    if (plan->poisoned)
+        return fail(YSCV_CUDA_ERR_TIMEOUT, "a bounded wait ran out in an earlier step of this plan: rebuild it");
+    if (vocab >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "vocabulary too large");
     YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
-    StepParams p = plan->params;
+    p = plan->params;
     p.embedding = d_embedding;
     p.vocab = (int)vocab;
     p.token = d_token;
     p.pos = d_pos;
     p.x = d_x;
     p.tail = 0;
+    p.lm_row0 = 0;
+    p.lm_rows = (int)vocab;
+    op_counters().decode_step_calls++;
+    return YSCV_CUDA_OK;
+}
+
+extern "C" int yscv_cuda_decode_plan_step_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
+                                              const float *d_embedding, size_t vocab, const int32_t *d_token,
+                                              const int32_t *d_pos, float *d_x) {
+    yscv::StepParams p;
+    int rc = step_common(ctx, plan, d_embedding, vocab, d_token, d_pos, d_x, p);
+    if (rc) return rc;
+    return launch_step(ctx, plan, p);
+}
+
+extern "C" int yscv_cuda_decode_plan_step_token_shard_dev(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan,
+                                                          const float *d_embedding, size_t vocab, int32_t *d_token,
+                                                          int32_t *d_pos, const float *d_final_gamma,
+                                                          const float *d_lm_head_rows, size_t lm_row0,
+                                                          size_t lm_rows, float *d_x, float *d_logits) {
+    using namespace yscv;
+    if (!d_final_gamma || !d_lm_head_rows || !d_logits) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (lm_rows == 0 || lm_row0 + lm_rows > vocab)
+        return fail(YSCV_CUDA_ERR_BAD_ARG, "LM head rows [%zu, %zu) are not inside the vocabulary of %zu", lm_row0,
+                    lm_row0 + lm_rows, vocab);
+    if ((reinterpret_cast<uintptr_t>(d_lm_head_rows) & 15) != 0)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "the LM head must be 16-byte aligned");
+    StepParams p;
+    int rc = step_common(ctx, plan, d_embedding, vocab, d_token, d_pos, d_x, p);
+    if (rc) return rc;
+    if (p.tp_size == 1 && lm_rows != vocab)
+        return fail(YSCV_CUDA_ERR_BAD_ARG, "a plan for one GPU needs every row of the LM head");
+    p.tail = 1;
+    p.final_gamma = d_final_gamma;
+    p.lm_head = d_lm_head_rows;
+    p.lm_row0 = (int)lm_row0;
+    p.lm_rows = (int)lm_rows;
+    p.logits = d_logits;
+    p.token_out = d_token;
+    p.pos_out = d_pos;
     return launch_step(ctx, plan, p);
 }
 
@@ -1467,26 +1645,6 @@ extern "C" int yscv_cuda_decode_plan_step_token_dev(yscv_cuda_ctx *ctx, const ys
                                                     const float *d_embedding, size_t vocab, int32_t *d_token,
                                                     int32_t *d_pos, const float *d_final_gamma,
                                                     const float *d_lm_head, float *d_x, float *d_logits) {
-    using namespace yscv;
-    if (!ctx || !plan || !d_embedding || !d_token || !d_pos || !d_x || !d_final_gamma || !d_lm_head ||
-        !d_logits || vocab == 0)
-        return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
-    if (plan->device != ctx->device) return fail(YSCV_CUDA_ERR_BAD_ARG, "plan belongs to device %d", plan->device);
-    if (vocab >= (1u << 30)) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "vocabulary too large");
-    if ((reinterpret_cast<uintptr_t>(d_lm_head) & 15) != 0)
-        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "the LM head must be 16-byte aligned");
-    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
-    StepParams p = plan->params;
-    p.embedding = d_embedding;
-    p.vocab = (int)vocab;
-    p.token = d_token;
-    p.pos = d_pos;
-    p.x = d_x;
-    p.tail = 1;
-    p.final_gamma = d_final_gamma;
-    p.lm_head = d_lm_head;
-    p.logits = d_logits;
-    p.token_out = d_token;
-    p.pos_out = d_pos;
-    return launch_step(ctx, plan, p);
+    return yscv_cuda_decode_plan_step_token_shard_dev(ctx, plan, d_embedding, vocab, d_token, d_pos, d_final_gamma,
+                                                      d_lm_head, 0, vocab, d_x, d_logits);
 }

@@ -90,17 +90,59 @@ add_rms_norm_kernel(const float *x, const float *__restrict__ delta,
     }
 }
 
+// Element access to a KV cache row: f32 storage, or per-row symmetric int8 with one f32
+// scale per row (KvDtype::I8 of crates/yscv-onnx/src/runner/kv_cache.rs:8-90; a row is one
+// token's n_kv*d values of one layer). Reads dequantise on the fly: (float)q * scale.
+template <typename KV>
+__device__ __forceinline__ float kv_get(const KV *row, int i, float scale);
+template <>
+__device__ __forceinline__ float kv_get<float>(const float *row, int i, float) { return row[i]; }
+template <>
+__device__ __forceinline__ float kv_get<int8_t>(const int8_t *row, int i, float scale) {
+    return __fmul_rn((float)row[i], scale);
+}
+
+// LayerStorage::append for KvDtype::I8 (kv_cache.rs:44-60) on one row held in `src` (global or
+// shared memory): scale = abs_max / 127 (1.0 when abs_max <= f32::EPSILON), inv = 1 / scale,
+// q = clamp(round_half_away(v * inv), -127, 127). Every thread of the block calls it.
+__device__ __forceinline__ void kv_quantize_row(const float *src, int len, int8_t *dst, float *scale_out,
+                                                float *red) {
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) amax = fmaxf(amax, fabsf(src[i]));
+    amax = block_max(amax, red);
+    const float scale = (amax <= 1.1920929e-07f) ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (threadIdx.x == 0) *scale_out = scale;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+        const float x = __fmul_rn(src[i], inv);
+        // NaN -> 0, as Rust's saturating float-to-int cast does
+        dst[i] = (x != x) ? (int8_t)0 : (int8_t)(int)fminf(fmaxf(roundf(x), -127.0f), 127.0f);
+    }
+    __syncthreads();  // `red` and `src` may be reused by the caller
+}
+
 // qkv rows: [q (n_q*d) | k (n_kv*d) | v (n_kv*d)], row r = b*seq + s at position *pos + s.
-// Rotates q in place, writes rotated k and v into the cache at [b][position][head][d].
+// Rotates q in place, writes rotated k and v into the cache at [b][position][head][d]
+// (f32), or quantised per row with their scales at [b][position] (int8). A position outside
+// [0, max_seq) appends nothing and raises YSCV_DEV_POS_OVERFLOW in the status word.
+// Dynamic shared memory: d floats of rotary factors (+ n_kv*d floats of rotated keys, int8).
+template <typename KV>
 __global__ void rope_kv_append_kernel(float *__restrict__ qkv, int seq, int n_q, int n_kv, int d,
                                       float theta, const int32_t *__restrict__ pos,
-                                      float *__restrict__ kc, float *__restrict__ vc, int max_seq) {
+                                      KV *__restrict__ kc, KV *__restrict__ vc,
+                                      float *__restrict__ kscale, float *__restrict__ vscale,
+                                      int max_seq, int *__restrict__ status) {
     pdl_wait();
     pdl_trigger();
-    __shared__ float cs_tab[128], sn_tab[128];  // d/2 <= 128
+    constexpr bool I8 = sizeof(KV) == 1;
+    extern __shared__ float rsm[];
+    __shared__ float red[8];
+    const int half = d / 2;
+    float *cs_tab = rsm, *sn_tab = rsm + half, *krow = rsm + d;
     const int row = blockIdx.x, b = row / seq, s = row % seq;
     const int p = *pos + s;
-    const int half = d / 2;
+    const bool in_range = p >= 0 && p < max_seq;
+    if (!in_range && threadIdx.x == 0) *status = YSCV_DEV_POS_OVERFLOW;
     const int row_w = (n_q + 2 * n_kv) * d;
     float *r = qkv + (size_t)row * row_w;
     const float fp = (float)p;
@@ -119,26 +161,39 @@ __global__ void rope_kv_append_kernel(float *__restrict__ qkv, int seq, int n_q,
         if (h < n_q) {
             v[i] = y0;
             v[i + half] = y1;
-        } else if (p < max_seq) {
-            float *dst = kc + (((size_t)b * max_seq + p) * n_kv + (h - n_q)) * d;
+        } else if constexpr (I8) {
+            krow[(h - n_q) * d + i] = y0;
+            krow[(h - n_q) * d + i + half] = y1;
+        } else if (in_range) {
+            float *dst = reinterpret_cast<float *>(kc) + (((size_t)b * max_seq + p) * n_kv + (h - n_q)) * d;
             dst[i] = y0;
             dst[i + half] = y1;
         }
     }
-    if (p < max_seq) {
-        const float *vsrc = r + (size_t)(n_q + n_kv) * d;
-        float *vdst = vc + ((size_t)b * max_seq + p) * n_kv * d;
+    const float *vsrc = r + (size_t)(n_q + n_kv) * d;
+    if constexpr (I8) {
+        __syncthreads();
+        if (in_range) {  // (uniform across the block)
+            const size_t slot = (size_t)b * max_seq + p;
+            kv_quantize_row(krow, n_kv * d, reinterpret_cast<int8_t *>(kc) + slot * n_kv * d, kscale + slot, red);
+            kv_quantize_row(vsrc, n_kv * d, reinterpret_cast<int8_t *>(vc) + slot * n_kv * d, vscale + slot, red);
+        }
+    } else if (in_range) {
+        float *vdst = reinterpret_cast<float *>(vc) + ((size_t)b * max_seq + p) * n_kv * d;
         for (int i = threadIdx.x; i < n_kv * d; i += blockDim.x) vdst[i] = vsrc[i];
     }
 }
 
 // One block per (b, q head, sq). Keys 0 .. *pos + sq (causal) or *pos + seq_q - 1.
+template <typename KV>
 __global__ void __launch_bounds__(128)
 gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n_q, int n_kv, int d,
-                     const float *__restrict__ kc, const float *__restrict__ vc, int max_seq,
+                     const KV *__restrict__ kc, const KV *__restrict__ vc,
+                     const float *__restrict__ kscale, const float *__restrict__ vscale, int max_seq,
                      const int32_t *__restrict__ pos, int causal, float *__restrict__ out) {
     pdl_wait();
     pdl_trigger();
+    constexpr bool I8 = sizeof(KV) == 1;
     extern __shared__ float sm[];
     float *scores = sm;           // max_seq
     float *qs = sm + max_seq;     // d
@@ -146,20 +201,23 @@ gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n
     const int sq = blockIdx.x, qh = blockIdx.y, b = blockIdx.z;
     const int kv_h = qh / (n_q / n_kv);
     int limit = *pos + (causal ? sq + 1 : seq_q);
-    limit = limit > max_seq ? max_seq : limit;
+    limit = limit > max_seq ? max_seq : (limit < 0 ? 0 : limit);
     const float scale = 1.0f / sqrtf((float)d);
     const float *qrow = q + ((size_t)b * seq_q + sq) * q_stride + (size_t)qh * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = qrow[i];
     __syncthreads();
-    const float *kb = kc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
-    const float *vb = vc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const KV *kb = kc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const KV *vb = vc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const float *ksc = I8 ? kscale + (size_t)b * max_seq : nullptr;
+    const float *vsc = I8 ? vscale + (size_t)b * max_seq : nullptr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float mx = -INFINITY;
     // a warp per key: lanes stride over d (coalesced), shuffle-reduce
     for (int sk = warp; sk < limit; sk += 4) {
-        const float *kr = kb + (size_t)sk * n_kv * d;
+        const KV *kr = kb + (size_t)sk * n_kv * d;
+        const float rs = I8 ? ksc[sk] : 1.0f;
         float dot = 0.0f;
-        for (int i = lane; i < d; i += 32) dot = fmaf(qs[i], kr[i], dot);
+        for (int i = lane; i < d; i += 32) dot = fmaf(qs[i], kv_get<KV>(kr, i, rs), dot);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         const float sc = dot * scale;
@@ -178,7 +236,8 @@ gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n
     float *orow = out + ((size_t)b * seq_q + sq) * (size_t)n_q * d + (size_t)qh * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.0f;
-        for (int sk = 0; sk < limit; ++sk) acc = fmaf(scores[sk] * inv, vb[(size_t)sk * n_kv * d + i], acc);
+        for (int sk = 0; sk < limit; ++sk)
+            acc = fmaf(scores[sk] * inv, kv_get<KV>(vb + (size_t)sk * n_kv * d, i, I8 ? vsc[sk] : 1.0f), acc);
         orow[i] = acc;
     }
 }
@@ -188,12 +247,15 @@ gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n
 // [split*chunk, ...), leaves an unnormalised partial output, its running max and its
 // exp-sum in `part`; attention_combine_kernel merges the splits (the usual
 // max-rescaling of a split softmax).
+template <typename KV>
 __global__ void __launch_bounds__(128)
 gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int n_kv, int d,
-                        const float *__restrict__ kc, const float *__restrict__ vc, int max_seq,
+                        const KV *__restrict__ kc, const KV *__restrict__ vc,
+                        const float *__restrict__ kscale, const float *__restrict__ vscale, int max_seq,
                         const int32_t *__restrict__ pos, int chunk, float *__restrict__ part) {
     pdl_wait();
     pdl_trigger();
+    constexpr bool I8 = sizeof(KV) == 1;
     // chunk == blockDim.x == 128: one key per thread in the score phase
     extern __shared__ float sm[];
     float *scores = sm;            // chunk
@@ -203,7 +265,7 @@ gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int 
     const int split = blockIdx.x, qh = blockIdx.y, b = blockIdx.z, n_splits = gridDim.x;
     const int kv_h = qh / (n_q / n_kv);
     int limit = *pos + 1;
-    limit = limit > max_seq ? max_seq : limit;
+    limit = limit > max_seq ? max_seq : (limit < 0 ? 0 : limit);
     const int k0 = split * chunk, k1 = min(limit, k0 + chunk);
     float *po = part + (((size_t)b * n_q + qh) * n_splits + split) * (d + 2);
     if (k0 >= k1) {  // nothing for this split yet: neutral element of the merge
@@ -216,28 +278,48 @@ gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int 
     const float *qrow = q + (size_t)b * q_stride + (size_t)qh * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = qrow[i];
     __syncthreads();
-    const float *kb = kc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
-    const float *vb = vc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
-    // scores: thread j owns key k0 + j and walks its row with 128-bit loads
+    const KV *kb = kc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const KV *vb = vc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const float *ksc = I8 ? kscale + (size_t)b * max_seq : nullptr;
+    const float *vsc = I8 ? vscale + (size_t)b * max_seq : nullptr;
+    // scores: thread j owns key k0 + j and walks its row with wide loads
     float sc = -INFINITY;
     if ((int)threadIdx.x < nk) {
-        const float4 *kr = reinterpret_cast<const float4 *>(kb + (size_t)(k0 + threadIdx.x) * n_kv * d);
         const float4 *q4 = reinterpret_cast<const float4 *>(qs);
         float dot = 0.0f;
+        if constexpr (I8) {
+            // four int8 per 32-bit load (rows are 4-byte aligned: d % 4 == 0)
+            const int *kr = reinterpret_cast<const int *>(kb + (size_t)(k0 + threadIdx.x) * n_kv * d);
+            const float rs = ksc[k0 + threadIdx.x];
 #pragma unroll 4
-        for (int i = 0; i < d / 4; ++i) {
-            const float4 kv = __ldg(kr + i), qv = q4[i];
-            dot = fmaf(qv.x, kv.x, dot);
-            dot = fmaf(qv.y, kv.y, dot);
-            dot = fmaf(qv.z, kv.z, dot);
-            dot = fmaf(qv.w, kv.w, dot);
+            for (int i = 0; i < d / 4; ++i) {
+                const int w = __ldg(kr + i);
+                const float4 qv = q4[i];
+                dot = fmaf(qv.x, __fmul_rn((float)(int8_t)(w & 255), rs), dot);
+                dot = fmaf(qv.y, __fmul_rn((float)(int8_t)((w >> 8) & 255), rs), dot);
+                dot = fmaf(qv.z, __fmul_rn((float)(int8_t)((w >> 16) & 255), rs), dot);
+                dot = fmaf(qv.w, __fmul_rn((float)(int8_t)((w >> 24) & 255), rs), dot);
+            }
+        } else {
+            const float4 *kr = reinterpret_cast<const float4 *>(kb + (size_t)(k0 + threadIdx.x) * n_kv * d);
+#pragma unroll 4
+            for (int i = 0; i < d / 4; ++i) {
+                const float4 kv = __ldg(kr + i), qv = q4[i];
+                dot = fmaf(qv.x, kv.x, dot);
+                dot = fmaf(qv.y, kv.y, dot);
+                dot = fmaf(qv.z, kv.z, dot);
+                dot = fmaf(qv.w, kv.w, dot);
+            }
         }
         sc = dot * scale;
     }
     const float mx = block_max(sc, red);
-    const float e = ((int)threadIdx.x < nk) ? expf(sc - mx) : 0.0f;
+    float e = ((int)threadIdx.x < nk) ? expf(sc - mx) : 0.0f;
+    const float se = block_sum(e, red);
+    // int8 values: fold the row scale of the value row into its weight once
+    if (I8 && (int)threadIdx.x < nk) e = e * vsc[k0 + threadIdx.x];
     scores[threadIdx.x] = e;
-    const float se = block_sum(e, red);  // (its barriers also publish `scores`)
+    __syncthreads();
     // weighted V: the two halves of the block take alternate keys, d threads each (d <= 64),
     // or all threads take every key (d == 128)
     const int groups = blockDim.x / d >= 2 ? 2 : 1;
@@ -245,7 +327,10 @@ gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int 
     float acc = 0.0f;
     if (gi < groups) {
 #pragma unroll 4
-        for (int j = gi; j < nk; j += groups) acc = fmaf(scores[j], __ldg(vb + (size_t)(k0 + j) * n_kv * d + i), acc);
+        for (int j = gi; j < nk; j += groups) {
+            const KV *vr = vb + (size_t)(k0 + j) * n_kv * d;
+            acc = fmaf(scores[j], I8 ? (float)vr[i] : kv_get<KV>(vr, i, 1.0f), acc);
+        }
     }
     if (groups == 2) {
         if (gi == 1) acc2[i] = acc;
@@ -423,7 +508,11 @@ argmax_final_kernel(const float *__restrict__ pv, const int32_t *__restrict__ pi
     out[row] = idx < 0 ? 0 : idx;
 }
 
-__global__ void advance_pos_kernel(int32_t *pos, int by) { *pos += by; }
+__global__ void advance_pos_kernel(int32_t *pos, int by) {
+    pdl_wait();  // the predecessor may still read *pos, and its own predecessors must be covered
+    pdl_trigger();
+    *pos += by;
+}
 
 }  // namespace yscv
 
@@ -445,6 +534,8 @@ int yscv_cuda_embedding_dev(yscv_cuda_ctx *ctx, const float *d_weight, size_t vo
     DEC_PROLOGUE(ctx);
     if (!d_weight || !d_tokens || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
     if (dim % 4 != 0) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "embedding dim must be a multiple of 4");
+    if ((reinterpret_cast<uintptr_t>(d_weight) | reinterpret_cast<uintptr_t>(d_out)) & 15)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "embedding table and output must be 16-byte aligned");
     if (rows == 0) return YSCV_CUDA_OK;
     YSCV_CUDA_TRY(launch_pdl(embedding_kernel, dim3((unsigned)rows), dim3(128), 0, ctx->stream, d_weight, d_tokens, d_out, (int)vocab, (int)dim));
     DEC_EPILOGUE(ctx, "embedding");
@@ -461,29 +552,70 @@ int yscv_cuda_add_rms_norm_dev(yscv_cuda_ctx *ctx, const float *d_x, const float
     DEC_EPILOGUE(ctx, "add_rms_norm");
 }
 
+}  // extern "C"
+
+template <typename KV>
+static int rope_kv_append_impl(yscv_cuda_ctx *ctx, float *d_qkv, size_t batch, size_t seq, size_t n_q,
+                               size_t n_kv, size_t d_head, float theta, const int32_t *d_pos,
+                               KV *d_kcache, KV *d_vcache, float *d_kscale, float *d_vscale,
+                               size_t max_seq) {
+    DEC_PROLOGUE(ctx);
+    if (!d_qkv || !d_pos || !d_kcache || !d_vcache) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (sizeof(KV) == 1 && (!d_kscale || !d_vscale)) return fail(YSCV_CUDA_ERR_BAD_ARG, "null scale table");
+    if (d_head == 0 || d_head % 2 != 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "d_head must be even for RoPE");
+    if (n_kv == 0 || max_seq == 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "n_kv and max_seq must be positive");
+    if (batch * seq == 0) return YSCV_CUDA_OK;
+    const size_t smem = (d_head + (sizeof(KV) == 1 ? n_kv * d_head : 0)) * sizeof(float);
+    if (smem > 48 * 1024)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "RoPE tables for d_head=%zu, n_kv=%zu do not fit shared memory", d_head, n_kv);
+    YSCV_CUDA_TRY(launch_pdl(rope_kv_append_kernel<KV>, dim3((unsigned)(batch * seq)), dim3(128), smem, ctx->stream,
+                             d_qkv, (int)seq, (int)n_q, (int)n_kv, (int)d_head, theta, d_pos, d_kcache, d_vcache,
+                             d_kscale, d_vscale, (int)max_seq, ctx->d_status));
+    DEC_EPILOGUE(ctx, sizeof(KV) == 1 ? "rope_kv_append(int8 cache)" : "rope_kv_append");
+}
+
+template <typename KV>
+static int gqa_attention_impl(yscv_cuda_ctx *ctx, const float *d_q, size_t q_stride, size_t batch,
+                              size_t seq_q, size_t n_q, size_t n_kv, size_t d_head, const KV *d_kcache,
+                              const KV *d_vcache, const float *d_kscale, const float *d_vscale,
+                              size_t max_seq, const int32_t *d_pos, int causal, float *d_out);
+
+extern "C" {
+
 int yscv_cuda_rope_kv_append_dev(yscv_cuda_ctx *ctx, float *d_qkv, size_t batch, size_t seq, size_t n_q,
                                  size_t n_kv, size_t d_head, float theta, const int32_t *d_pos,
                                  float *d_kcache, float *d_vcache, size_t max_seq) {
-    DEC_PROLOGUE(ctx);
-    if (!d_qkv || !d_pos || !d_kcache || !d_vcache) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
-    if (d_head % 2 != 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "d_head must be even for RoPE");
-    if (batch * seq == 0) return YSCV_CUDA_OK;
-    YSCV_CUDA_TRY(launch_pdl(rope_kv_append_kernel, dim3((unsigned)(batch * seq)), dim3(128), 0, ctx->stream, d_qkv, (int)seq, (int)n_q, (int)n_kv, (int)d_head, theta, d_pos, d_kcache, d_vcache, (int)max_seq));
-    DEC_EPILOGUE(ctx, "rope_kv_append");
+    return rope_kv_append_impl<float>(ctx, d_qkv, batch, seq, n_q, n_kv, d_head, theta, d_pos, d_kcache, d_vcache,
+                                      nullptr, nullptr, max_seq);
 }
 
-int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_stride, size_t batch,
-                                size_t seq_q, size_t n_q, size_t n_kv, size_t d_head,
-                                const float *d_kcache, const float *d_vcache, size_t max_seq,
-                                const int32_t *d_pos, int causal, float *d_out) {
+int yscv_cuda_rope_kv_append_i8_dev(yscv_cuda_ctx *ctx, float *d_qkv, size_t batch, size_t seq, size_t n_q,
+                                    size_t n_kv, size_t d_head, float theta, const int32_t *d_pos,
+                                    int8_t *d_kcache, float *d_kscale, int8_t *d_vcache, float *d_vscale,
+                                    size_t max_seq) {
+    return rope_kv_append_impl<int8_t>(ctx, d_qkv, batch, seq, n_q, n_kv, d_head, theta, d_pos, d_kcache, d_vcache,
+                                       d_kscale, d_vscale, max_seq);
+}
+
+}  // extern "C"
+
+template <typename KV>
+static int gqa_attention_impl(yscv_cuda_ctx *ctx, const float *d_q, size_t q_stride, size_t batch,
+                              size_t seq_q, size_t n_q, size_t n_kv, size_t d_head, const KV *d_kcache,
+                              const KV *d_vcache, const float *d_kscale, const float *d_vscale,
+                              size_t max_seq, const int32_t *d_pos, int causal, float *d_out) {
     DEC_PROLOGUE(ctx);
     if (!d_q || !d_kcache || !d_vcache || !d_pos || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (sizeof(KV) == 1 && (!d_kscale || !d_vscale)) return fail(YSCV_CUDA_ERR_BAD_ARG, "null scale table");
     if (n_kv == 0 || n_q % n_kv != 0) return fail(YSCV_CUDA_ERR_BAD_ARG, "n_q must be a multiple of n_kv");
     if (batch * seq_q == 0) return YSCV_CUDA_OK;
     if (seq_q == 1 && causal && max_seq > 128) {
         // decode over a long cache: split the keys across blocks, then merge
         if (d_head % 4 != 0 || d_head > 128)
             return fail(YSCV_CUDA_ERR_UNSUPPORTED, "d_head %zu not supported by the decode attention", d_head);
+        // 128-bit (f32) / 32-bit (int8) loads of key rows and of the staged query
+        if ((reinterpret_cast<uintptr_t>(d_kcache) & (sizeof(KV) == 1 ? 3 : 15)) != 0)
+            return fail(YSCV_CUDA_ERR_UNSUPPORTED, "the key cache must be %d-byte aligned", sizeof(KV) == 1 ? 4 : 16);
         const int chunk = 128;
         const int n_splits = (int)((max_seq + chunk - 1) / chunk);
         const size_t need = batch * n_q * (size_t)n_splits * (d_head + 2) * sizeof(float);
@@ -491,25 +623,45 @@ int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_s
         if (rc) return rc;
         float *part = reinterpret_cast<float *>(ctx->scratch_attn.ptr);
         dim3 grid((unsigned)n_splits, (unsigned)n_q, (unsigned)batch);
-        YSCV_CUDA_TRY(launch_pdl(gqa_decode_split_kernel, dim3(grid), dim3(128), (chunk + 2 * d_head) * sizeof(float), ctx->stream, d_q, (int)q_stride, (int)n_q, (int)n_kv, (int)d_head, d_kcache, d_vcache, (int)max_seq, d_pos, chunk, part));
+        YSCV_CUDA_TRY(launch_pdl(gqa_decode_split_kernel<KV>, dim3(grid), dim3(128), (chunk + 2 * d_head) * sizeof(float),
+                                 ctx->stream, d_q, (int)q_stride, (int)n_q, (int)n_kv, (int)d_head, d_kcache, d_vcache,
+                                 d_kscale, d_vscale, (int)max_seq, d_pos, chunk, part));
         YSCV_CUDA_TRY(cudaGetLastError());
         ctx->launches++;
         YSCV_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3(dim3((unsigned)n_q, (unsigned)batch)), dim3(128), 0, ctx->stream, part, n_splits,
                                                                                                (int)d_head, d_out));
-        DEC_EPILOGUE(ctx, "gqa_attention(split-k)");
+        DEC_EPILOGUE(ctx, sizeof(KV) == 1 ? "gqa_attention(split-k,int8 cache)" : "gqa_attention(split-k)");
     }
     const size_t smem = (max_seq + d_head) * sizeof(float);
     if (smem > 200 * 1024) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "max_seq %zu too long for the attention kernel", max_seq);
-    static int attr_set[16] = {0};
-    if (smem > 48 * 1024 && (ctx->device >= 16 || !attr_set[ctx->device])) {
-        YSCV_CUDA_TRY(cudaFuncSetAttribute(gqa_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        if (ctx->device < 16) attr_set[ctx->device] = 1;
+    if (smem > 48 * 1024) {
+        int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(gqa_attention_kernel<KV>), ctx->device, 200 * 1024);
+        if (arc) return arc;
     }
     dim3 grid((unsigned)seq_q, (unsigned)n_q, (unsigned)batch);
-    YSCV_CUDA_TRY(launch_pdl(gqa_attention_kernel, dim3(grid), dim3(128), smem, ctx->stream, d_q, (int)q_stride, (int)seq_q, (int)n_q, (int)n_kv,
-                                                           (int)d_head, d_kcache, d_vcache, (int)max_seq,
-                                                           d_pos, causal, d_out));
-    DEC_EPILOGUE(ctx, "gqa_attention");
+    YSCV_CUDA_TRY(launch_pdl(gqa_attention_kernel<KV>, dim3(grid), dim3(128), smem, ctx->stream, d_q, (int)q_stride, (int)seq_q,
+                             (int)n_q, (int)n_kv, (int)d_head, d_kcache, d_vcache, d_kscale, d_vscale, (int)max_seq,
+                             d_pos, causal, d_out));
+    DEC_EPILOGUE(ctx, sizeof(KV) == 1 ? "gqa_attention(int8 cache)" : "gqa_attention");
+}
+
+extern "C" {
+
+int yscv_cuda_gqa_attention_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_stride, size_t batch,
+                                size_t seq_q, size_t n_q, size_t n_kv, size_t d_head,
+                                const float *d_kcache, const float *d_vcache, size_t max_seq,
+                                const int32_t *d_pos, int causal, float *d_out) {
+    return gqa_attention_impl<float>(ctx, d_q, q_stride, batch, seq_q, n_q, n_kv, d_head, d_kcache, d_vcache, nullptr,
+                                     nullptr, max_seq, d_pos, causal, d_out);
+}
+
+int yscv_cuda_gqa_attention_i8_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t q_stride, size_t batch,
+                                   size_t seq_q, size_t n_q, size_t n_kv, size_t d_head,
+                                   const int8_t *d_kcache, const float *d_kscale, const int8_t *d_vcache,
+                                   const float *d_vscale, size_t max_seq, const int32_t *d_pos, int causal,
+                                   float *d_out) {
+    return gqa_attention_impl<int8_t>(ctx, d_q, q_stride, batch, seq_q, n_q, n_kv, d_head, d_kcache, d_vcache, d_kscale,
+                                      d_vscale, max_seq, d_pos, causal, d_out);
 }
 
 int yscv_cuda_swiglu_dev(yscv_cuda_ctx *ctx, const float *d_gate_up, size_t rows, size_t inter,
@@ -528,10 +680,17 @@ int yscv_cuda_f32_matmul_dev(yscv_cuda_ctx *ctx, const float *d_w, const float *
     DEC_PROLOGUE(ctx);
     if (!d_w || !d_x || !d_out) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
     if (k % 4 != 0) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "k must be a multiple of 4");
+    if ((reinterpret_cast<uintptr_t>(d_w) | reinterpret_cast<uintptr_t>(d_x)) & 15)
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "weights and activations must be 16-byte aligned");
     if (m * n == 0) return YSCV_CUDA_OK;
     const unsigned blocks = (unsigned)((n + 7) / 8 < (size_t)(16 * ctx->sm_count) ? (n + 7) / 8 : 16 * ctx->sm_count);
-    for (size_t m0 = 0; m0 < m; m0 += 4) {
-        YSCV_CUDA_TRY(launch_pdl(f32_matmul_kernel<4>, dim3(blocks), dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k));
+    // one pass over the weights per 4 (or, for wide batches, 16) activation rows
+    const size_t mt = m > 8 ? 16 : 4;
+    for (size_t m0 = 0; m0 < m; m0 += mt) {
+        if (mt == 16)
+            YSCV_CUDA_TRY(launch_pdl(f32_matmul_kernel<16>, dim3(blocks), dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k));
+        else
+            YSCV_CUDA_TRY(launch_pdl(f32_matmul_kernel<4>, dim3(blocks), dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k));
         YSCV_CUDA_TRY(cudaGetLastError());
         ctx->launches++;
     }

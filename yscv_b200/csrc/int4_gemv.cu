@@ -136,23 +136,6 @@ act_quant_kernel(const float *__restrict__ act, unsigned char *__restrict__ blob
 // Fast kernel
 // ---------------------------------------------------------------------------
 
-#ifdef YSCV_TRACE
-// debugging aid (not built by default): per-CTA timestamps of the consumer warp 0
-__device__ unsigned long long g_trace[148 * 32];
-extern "C" int yscv_trace_read(unsigned long long *dst) {
-    return (int)cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace));
-}
-#define TRACE(slot)                                                                     \
-    do {                                                                                \
-        if (tid == 0 && (slot) < 32) {                                                  \
-            unsigned long long _t;                                                      \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                      \
-            g_trace[blockIdx.x * 32 + (slot)] = _t;                                     \
-        }                                                                               \
-    } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#endif
 
 struct FastGeom {
     int tiles;        // 16-row tiles per row block (1..TP2)
@@ -194,7 +177,6 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, t = lane & 3;
-    TRACE(0);
     // let the next kernel of the stream be scheduled as soon as SMs free up
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
@@ -260,7 +242,6 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
         }
     }
     __syncthreads();
-    TRACE(1);
     // everything below reads a predecessor's output (activations / digit blobs) or writes
     // memory a predecessor may still be reading (the output)
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
@@ -353,7 +334,6 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
                         // still need this warp) but stop waiting and computing
     for (int it = 0; it < total; ++it) {
         if (!dead) dead = !mbar_wait(bar_full + c_slot * 8, c_phase, status);
-        TRACE(2 + 2 * it);
         if (active && !dead) {
             const unsigned char *st = smem + (size_t)c_slot * g.stage_bytes;
             // digit blob of this K stage: inside the stage, or in the resident copy
@@ -420,7 +400,6 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
         }
         // this warp is done reading the stage: hand the slot back to the producer
         __syncwarp();
-        TRACE(3 + 2 * it);
         if (lane == 0) mbar_arrive(bar_empty + c_slot * 8);
         if (++c_slot == g.stages) { c_slot = 0; c_phase ^= 1u; }
         if (++c_ks == k_stages) {
@@ -461,7 +440,6 @@ int4_gemv_fast_kernel(const __grid_constant__ CUtensorMap tm_w,
                 }
             }
             ++c_rb;
-            TRACE(30);
             if (c_rb < n_rb) named_bar_sync(1, FAST_CONSUMER_WARPS * 32);  // `red` is reused
         }
     }
@@ -527,12 +505,12 @@ static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scale
                    GS == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     if (rc) return rc;
     auto kern = int4_gemv_fast_kernel<MP, GS, TP2, FUSEQ>;
-    static int smem_set[16] = {0};  // per device: opt-in shared memory size already raised
-    if (ctx->device >= 16 || !smem_set[ctx->device]) {
-        YSCV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           227 * 1024));
-        if (ctx->device < 16) smem_set[ctx->device] = 1;
-    }
+    rc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
+    if (rc) return rc;
+    snprintf(ctx->report_int4, sizeof(ctx->report_int4),
+             "int4_gemv_fast m=%d(pad %d) n=%d k=%d: %d-row blocks, %d groups/stage, %d stages, %s, grid %d",
+             M, MP, N, K, rb_rows, GS, g.stages, FUSEQ ? "activations quantised in the kernel" : "digit planes from scratch",
+             grid);
     ctx->prof_begin();
     // Programmatic dependent launch: this grid may be scheduled while the previous kernel of
     // the stream drains; it touches nothing a predecessor may have written (activations,
@@ -609,6 +587,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[YSCV_STATIC_SCRA
 // In host code `g_static_scratch` is only a stand-in for the device array, never an
 // address a kernel may be given; the real address is looked up once per device.
 static void *g_static_scratch_ptr[64] = {nullptr};
+static std::mutex g_static_scratch_mutex;
 
 // the scratch-using variant only: digit planes are always produced by act_quant_kernel
 template <int MP, int GS>
@@ -655,13 +634,17 @@ extern "C" int yscv_cuda_int4_matmul_dev_static(yscv_cuda_ctx *ctx, const uint8_
         return fail(YSCV_CUDA_ERR_UNSUPPORTED, "scratch need exceeds the built-in array");
     if (ctx->device < 0 || ctx->device >= 64) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "device index");
     YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
-    if (!g_static_scratch_ptr[ctx->device]) {
-        // first call on this device: resolve the device address of the array
-        void *ptr = nullptr;
-        YSCV_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
-        g_static_scratch_ptr[ctx->device] = ptr;
+    unsigned char *blobs = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (!g_static_scratch_ptr[ctx->device]) {
+            // first call on this device: resolve the device address of the array
+            void *ptr = nullptr;
+            YSCV_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+            g_static_scratch_ptr[ctx->device] = ptr;
+        }
+        blobs = reinterpret_cast<unsigned char *>(g_static_scratch_ptr[ctx->device]);
     }
-    unsigned char *blobs = reinterpret_cast<unsigned char *>(g_static_scratch_ptr[ctx->device]);
     const int M = (int)m, N = (int)n, K = (int)k;
     const int MP = padded_m(M);
     const int GS = stage_groups(MP, K);

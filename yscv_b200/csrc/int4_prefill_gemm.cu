@@ -348,11 +348,9 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, m, k, k * 2, (uint32_t)p.BT, PG_BK,
                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    static int smem_set[16] = {0};
-    if (ctx->device >= 16 || !smem_set[ctx->device]) {
-        YSCV_CUDA_TRY(cudaFuncSetAttribute(int4_prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           227 * 1024));
-        if (ctx->device < 16) smem_set[ctx->device] = 1;
+    {
+        const int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(int4_prefill_gemm_kernel), ctx->device, 227 * 1024);
+        if (arc) return arc;
     }
     const int tiles = p.n_tiles * p.t_chunks;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;

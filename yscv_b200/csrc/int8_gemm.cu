@@ -219,6 +219,9 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int row = mb * G8_BM + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)abuf * BN;
             const bool general = p.corr != nullptr || p.comp_pc != nullptr || p.relu != 0 || p.b_zp != 0;
+            // 16-byte vector stores need a 16-byte aligned output (rows then stay aligned through
+            // the pitch conditions below); anything else takes scalar stores
+            const bool out_vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
             // what the zero point of B adds to every element of this row
             int row_term = 0;
             if (p.b_zp != 0 && row < p.M)
@@ -232,7 +235,7 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if (row < p.M && col0 < p.N) {
                     if (p.mode == 0) {
                         int32_t *o = reinterpret_cast<int32_t *>(out) + (size_t)row * p.ldc + col0;
-                        if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
+                        if (col0 + 32 <= p.N && (p.ldc & 3) == 0 && out_vec_ok) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) {
                                 int4 v;
@@ -280,7 +283,7 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                 packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
                             }
                         }
-                        if (col0 + 32 <= p.N && (p.ldc & 15) == 0) {
+                        if (col0 + 32 <= p.N && (p.ldc & 15) == 0 && out_vec_ok) {
                             *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                             *reinterpret_cast<uint4 *>(o + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                         } else {
@@ -387,13 +390,14 @@ static int launch_g8(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const yscv
                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     auto kern = int8_gemm_tc_kernel<BN>;
-    static int smem_set[16] = {0};
-    if (ctx->device >= 16 || !smem_set[ctx->device]) {
-        YSCV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        if (ctx->device < 16) smem_set[ctx->device] = 1;
-    }
+    rc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
+    if (rc) return rc;
     const int tiles = p.m_blocks * p.n_blocks;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    snprintf(ctx->report_int8, sizeof(ctx->report_int8),
+             "int8_gemm_tc m=%d n=%d k=%d: tcgen05 kind::i8, CTA tile %dx%d, %d stages of %d KB, %d tiles on %d CTAs, %s",
+             p.M, p.N, p.K, G8_BM, BN, p.stages, stage_bytes / 1024, tiles, grid,
+             p.mode == 0 ? "int32 out" : "requantised bytes out");
     ctx->prof_begin();
     kern<<<grid, G8_THREADS, smem, ctx->stream>>>(tm_a, tm_b, b->d_colsum, d_out, p, ctx->d_status);
     ctx->prof_end();

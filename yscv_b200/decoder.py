@@ -8,11 +8,17 @@ attention, output linear, SwiGLU MLP, fp32 LM head, greedy argmax-last) from the
 library's entry points, so the int4 kernels can be measured in the loop they exist
 for. Every tensor operation is a call into libyscv_cuda.so; torch supplies device
 memory, the stream, the CUDA graph that replays a decode step, and (tensor
-parallel) the NCCL all-reduce after the row-parallel linears.
+parallel) the rendezvous between the ranks and the NCCL all-reduce of the prompt pass.
 
 Tensor parallel layout (tp_size ranks): q/k/v heads, gate and up rows are split
 across ranks (column-parallel, no collective); the output and down projections are
-split along K (row-parallel) and their fp32 partial sums are all-reduced.
+split along K (row-parallel) and their fp32 partial sums are summed across the ranks:
+by `ncclAllReduce` in the operator chain (prompt pass, batch > 1), and inside the
+one-launch decode step by the kernel itself (peer stores into exchange regions the
+ranks map through CUDA IPC, sums in rank order), where the LM head is split by rows too.
+
+`kv_int8=True` stores the KV cache as the reference's KvDtype::I8
+(crates/yscv-onnx/src/runner/kv_cache.rs:8-90): int8 rows with one f32 scale per token.
 """
 from __future__ import annotations
 
@@ -21,7 +27,7 @@ from dataclasses import dataclass
 import torch
 
 from . import sharding
-from .lib import Context, YscvCudaError
+from .lib import Context, TpComm, YscvCudaError, TP_HANDLE_BYTES
 
 
 @dataclass(frozen=True)
@@ -54,7 +60,8 @@ class Int4Linear:
 class Int4Decoder:
     def __init__(self, ctx: Context, cfg: DecoderConfig, batch: int, max_seq: int, stream: torch.cuda.Stream,
                  seed: int = 3, tp_rank: int = 0, tp_size: int = 1, process_group=None,
-                 layers: int | None = None, fused_step: bool = True):
+                 layers: int | None = None, fused_step: bool = True, kv_int8: bool = False,
+                 plan_options: dict | None = None):
         assert cfg.n_q % tp_size == 0 and cfg.n_kv % tp_size == 0 and cfg.mlp % (tp_size * cfg.group_size) == 0
         self.ctx, self.cfg, self.batch, self.max_seq, self.stream = ctx, cfg, batch, max_seq, stream
         self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
@@ -66,27 +73,61 @@ class Int4Decoder:
         with torch.cuda.stream(stream):
             self._build_weights()
             d, B = cfg.head_dim, batch
-            self.kcache = [torch.zeros(B, max_seq, self.nkv_l, d, device=self.dev) for _ in range(self.n_layers)]
-            self.vcache = [torch.zeros(B, max_seq, self.nkv_l, d, device=self.dev) for _ in range(self.n_layers)]
+            self.kv_int8 = kv_int8
+            kv_dtype = torch.int8 if kv_int8 else torch.float32
+            self.kcache = [torch.zeros(B, max_seq, self.nkv_l, d, dtype=kv_dtype, device=self.dev) for _ in range(self.n_layers)]
+            self.vcache = [torch.zeros(B, max_seq, self.nkv_l, d, dtype=kv_dtype, device=self.dev) for _ in range(self.n_layers)]
+            if kv_int8:  # one scale per cached row (token), keys and values apart
+                self.kscale = [torch.zeros(B, max_seq, device=self.dev) for _ in range(self.n_layers)]
+                self.vscale = [torch.zeros(B, max_seq, device=self.dev) for _ in range(self.n_layers)]
             self.pos = torch.zeros(1, dtype=torch.int32, device=self.dev)
             self.next_tokens = torch.zeros(B, dtype=torch.int32, device=self.dev)
         self._bufs = {}
         self.graph = None
         stream.synchronize()
-        # batch 1 on one GPU: the whole single-token step as one persistent kernel, when the
-        # shapes allow it (the library says which do)
+        # batch 1: the whole single-token step as one persistent kernel per GPU, when the
+        # shapes allow it (the library says which do). With tensor parallelism the ranks'
+        # kernels exchange their partial sums through exchange regions mapped with CUDA IPC;
+        # the handles travel through the process group, and every rank must agree on whether
+        # the plan exists.
         self.plan = None
-        if fused_step and batch == 1 and tp_size == 1:
+        self.tp_comm = None
+        self.lm_row0, self.lm_rows = 0, cfg.vocab
+        if fused_step and batch == 1 and not kv_int8:
             try:
+                if tp_size > 1:
+                    self._connect_tp()
+                    assert cfg.vocab % tp_size == 0
+                    self.lm_rows = cfg.vocab // tp_size
+                    self.lm_row0 = tp_rank * self.lm_rows
                 self.plan = ctx.decode_plan(
                     [dict(qkv=self.wqkv[l].handle, o=self.wo[l].handle, gate_up=self.wgu[l].handle,
                           down=self.wdown[l].handle, gamma_attn=self.gamma.data_ptr(),
                           gamma_mlp=self.gamma.data_ptr(), kcache=self.kcache[l].data_ptr(),
                           vcache=self.vcache[l].data_ptr()) for l in range(self.n_layers)],
-                    cfg.hidden, cfg.mlp, cfg.n_q, cfg.n_kv, cfg.head_dim, max_seq, cfg.eps, cfg.rope_theta)
+                    cfg.hidden, self.mlp_l, self.nq_l, self.nkv_l, cfg.head_dim, max_seq, cfg.eps, cfg.rope_theta,
+                    tp=self.tp_comm, **(plan_options or {}))
             except YscvCudaError as e:
                 if e.status != -3:  # anything but "unsupported shape" is a real failure
                     raise
+            if tp_size > 1:
+                import torch.distributed as dist
+                ok = torch.tensor([1 if self.plan is not None else 0], device=self.dev)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.pg)
+                if int(ok.item()) == 0 and self.plan is not None:
+                    self.plan.free()
+                    self.plan = None
+
+    def _connect_tp(self):
+        """Create this rank's exchange region, gather every rank's IPC handle, map the peers."""
+        import numpy as np
+        import torch.distributed as dist
+        self.tp_comm = TpComm(self.ctx, self.tp_rank, self.tp_size, self.cfg.hidden)
+        mine = torch.from_numpy(self.tp_comm.handle_bytes.copy()).to(self.dev)
+        gathered = [torch.empty_like(mine) for _ in range(self.tp_size)]
+        dist.all_gather(gathered, mine, group=self.pg)
+        self.tp_comm.connect(np.stack([g.cpu().numpy() for g in gathered]))
+        dist.barrier(group=self.pg)  # every region is mapped everywhere before anyone stores into one
 
     # ---- weights -------------------------------------------------------------------
     def _normal(self, tag: int, rows: int, cols: int) -> torch.Tensor:
@@ -181,19 +222,30 @@ class Int4Decoder:
             logits = self._buf("logits", B, c.vocab)
             if tokens.data_ptr() != self.next_tokens.data_ptr():
                 self.next_tokens.copy_(tokens)
-            self.plan.step_token_dev(self.embedding.data_ptr(), c.vocab, self.next_tokens.data_ptr(),
-                                     self.pos.data_ptr(), self.gamma.data_ptr(), self.lm_head.data_ptr(),
-                                     x.data_ptr(), logits.data_ptr())
+            # (tensor parallel: this rank's rows of the LM head; `logits` then holds only those)
+            self.plan.step_token_shard_dev(self.embedding.data_ptr(), c.vocab, self.next_tokens.data_ptr(),
+                                           self.pos.data_ptr(), self.gamma.data_ptr(),
+                                           self.lm_head.data_ptr() + self.lm_row0 * H * 4, self.lm_row0, self.lm_rows,
+                                           x.data_ptr(), logits.data_ptr())
             return logits
         ctx.embedding_dev(self.embedding.data_ptr(), c.vocab, H, tokens.data_ptr(), rows, x.data_ptr())
         delta = 0
         for l in range(self.n_layers):
             ctx.add_rms_norm_dev(x.data_ptr(), delta, self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
             ctx.int4_matmul_dev(self.wqkv[l].handle, h.data_ptr(), qkv.data_ptr(), rows)
-            ctx.rope_kv_append_dev(qkv.data_ptr(), B, seq, self.nq_l, self.nkv_l, d, c.rope_theta, self.pos.data_ptr(),
-                                   self.kcache[l].data_ptr(), self.vcache[l].data_ptr(), self.max_seq)
-            ctx.gqa_attention_dev(qkv.data_ptr(), qkv_w, B, seq, self.nq_l, self.nkv_l, d, self.kcache[l].data_ptr(),
-                                  self.vcache[l].data_ptr(), self.max_seq, self.pos.data_ptr(), True, attn.data_ptr())
+            if self.kv_int8:
+                ctx.rope_kv_append_i8_dev(qkv.data_ptr(), B, seq, self.nq_l, self.nkv_l, d, c.rope_theta,
+                                          self.pos.data_ptr(), self.kcache[l].data_ptr(), self.kscale[l].data_ptr(),
+                                          self.vcache[l].data_ptr(), self.vscale[l].data_ptr(), self.max_seq)
+                ctx.gqa_attention_i8_dev(qkv.data_ptr(), qkv_w, B, seq, self.nq_l, self.nkv_l, d,
+                                         self.kcache[l].data_ptr(), self.kscale[l].data_ptr(),
+                                         self.vcache[l].data_ptr(), self.vscale[l].data_ptr(), self.max_seq,
+                                         self.pos.data_ptr(), True, attn.data_ptr())
+            else:
+                ctx.rope_kv_append_dev(qkv.data_ptr(), B, seq, self.nq_l, self.nkv_l, d, c.rope_theta, self.pos.data_ptr(),
+                                       self.kcache[l].data_ptr(), self.vcache[l].data_ptr(), self.max_seq)
+                ctx.gqa_attention_dev(qkv.data_ptr(), qkv_w, B, seq, self.nq_l, self.nkv_l, d, self.kcache[l].data_ptr(),
+                                      self.vcache[l].data_ptr(), self.max_seq, self.pos.data_ptr(), True, attn.data_ptr())
             ctx.int4_matmul_dev(self.wo[l].handle, attn.data_ptr(), o.data_ptr(), rows)
             self._all_reduce(o)
             ctx.add_rms_norm_dev(x.data_ptr(), o.data_ptr(), self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
@@ -205,10 +257,7 @@ class Int4Decoder:
         ctx.add_rms_norm_dev(x.data_ptr(), delta, self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
         last = h if seq == 1 else h.view(B, seq, H)[:, seq - 1, :].contiguous()
         logits = self._buf("logits", B, c.vocab)
-        if B <= 8:
-            ctx.f32_matmul_dev(self.lm_head.data_ptr(), last.data_ptr(), B, c.vocab, H, logits.data_ptr())
-        else:
-            torch.matmul(last, self.lm_head.t(), out=logits)  # plain library GEMM for a wide batch
+        ctx.f32_matmul_dev(self.lm_head.data_ptr(), last.data_ptr(), B, c.vocab, H, logits.data_ptr())
         ctx.argmax_last_dev(logits.data_ptr(), B, c.vocab, self.next_tokens.data_ptr())
         ctx.advance_pos_dev(self.pos.data_ptr(), seq)
         return logits
@@ -221,6 +270,13 @@ class Int4Decoder:
         if self.plan is not None:
             self.plan.free()
             self.plan = None
+        if self.tp_comm is not None:
+            # no rank may unmap a region a peer's kernel could still be storing into
+            import torch.distributed as dist
+            torch.cuda.synchronize()
+            dist.barrier(group=self.pg)
+            self.tp_comm.close()
+            self.tp_comm = None
         self._bufs.clear()
         self.kcache, self.vcache = [], []
         self.wqkv, self.wo, self.wgu, self.wdown = [], [], [], []

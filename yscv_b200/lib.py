@@ -85,7 +85,51 @@ SIGNATURES = {
     "yscv_cuda_decode_plan_step_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp]),
     "yscv_cuda_decode_plan_step_token_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp]),
     "yscv_cuda_decode_plan_free": (None, [_vp]),
+    "yscv_cuda_decode_plan_create_ex": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, C.c_float, C.c_float,
+                                                  _vp, C.POINTER(_vp)]),
+    "yscv_cuda_decode_plan_check": (C.c_int, [_vp, _vp]),
+    "yscv_cuda_decode_plan_step_token_shard_dev": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp, _sz, _sz, _vp,
+                                                             _vp]),
+    "yscv_cuda_tp_comm_create": (C.c_int, [_vp, C.c_int, C.c_int, _sz, C.POINTER(_vp), _vp]),
+    "yscv_cuda_tp_comm_connect": (C.c_int, [_vp, _vp]),
+    "yscv_cuda_tp_comm_connect_unanswered": (C.c_int, [_vp]),
+    "yscv_cuda_tp_comm_destroy": (None, [_vp]),
+    "yscv_cuda_dispatch_report": (C.c_char_p, [_vp]),
+    "yscv_cuda_quant_stats_read": (None, [_vp]),
+    "yscv_cuda_quant_stats_reset": (None, []),
+    "yscv_cuda_int4_to_matmulnbits": (C.c_int, [_vp, _vp, _sz]),
+    "yscv_cuda_int4_weight_from_f32": (C.c_int, [_vp, _vp, _sz, _sz, C.c_int, _sz, C.POINTER(_vp)]),
+    "yscv_cuda_int4_weight_rows": (_sz, [_vp]),
+    "yscv_cuda_int4_weight_k": (_sz, [_vp]),
+    "yscv_cuda_int4_weight_group_size": (_sz, [_vp]),
+    "yscv_cuda_int4_weight_download": (C.c_int, [_vp, _vp, _vp, _vp]),
+    "yscv_cuda_int4_container_size": (_sz, [_sz, _sz, _sz]),
+    "yscv_cuda_int4_container_write": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _vp, _sz, C.POINTER(_sz)]),
+    "yscv_cuda_int4_container_read": (C.c_int, [_vp, _sz, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz),
+                                                C.POINTER(_vp), C.POINTER(_vp)]),
+    "yscv_cuda_int4_weight_from_container": (C.c_int, [_vp, _vp, _sz, C.POINTER(_vp)]),
+    "yscv_cuda_requant_i32_row_to_i8": (C.c_int, [_vp, _vp, _vp, C.c_float, C.c_float, C.c_int, _vp, _sz, _sz]),
+    "yscv_cuda_requant_i32_row_to_i8_dev": (C.c_int, [_vp, _vp, _vp, C.c_float, C.c_float, C.c_int, _vp, _sz, _sz]),
+    "yscv_cuda_registry_create": (C.c_int, [C.POINTER(_vp)]),
+    "yscv_cuda_registry_destroy": (None, [_vp]),
+    "yscv_cuda_registry_put_int4": (C.c_int, [_vp, C.c_char_p, _vp]),
+    "yscv_cuda_registry_put_i8b": (C.c_int, [_vp, C.c_char_p, _vp]),
+    "yscv_cuda_registry_get_int4": (_vp, [_vp, C.c_char_p]),
+    "yscv_cuda_registry_get_i8b": (_vp, [_vp, C.c_char_p]),
+    "yscv_cuda_registry_len": (_sz, [_vp]),
+    "yscv_cuda_registry_register_matmul_weight": (C.c_int, [_vp, _vp, C.c_char_p, _vp, _sz, _sz, C.c_int, _sz,
+                                                            C.POINTER(C.c_int)]),
+    "yscv_cuda_registry_register_i8_weight": (C.c_int, [_vp, _vp, C.c_char_p, _vp, _sz, _sz, C.POINTER(C.c_int)]),
+    "yscv_cuda_should_prepack_i8_b": (C.c_int, [_sz, _sz]),
+    "yscv_cuda_should_use_prepacked_i8_b": (C.c_int, [_sz, _sz, _sz]),
+    "yscv_cuda_rope_kv_append_i8_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _vp, _vp, _vp, _vp,
+                                                  _vp, _sz]),
+    "yscv_cuda_gqa_attention_i8_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _sz, _vp,
+                                                 C.c_int, _vp]),
 }
+
+WEIGHT_MATMUL_KN, WEIGHT_GEMM_NK, WEIGHT_GEMM_KN = 0, 1, 2
+TP_HANDLE_BYTES = 64
 
 
 class Requant(C.Structure):
@@ -93,6 +137,19 @@ class Requant(C.Structure):
     _fields_ = [("a_is_unsigned", C.c_int), ("a_zero_point", C.c_int32), ("composite", C.c_float),
                 ("y_zero_point", C.c_float), ("qmin", C.c_int32), ("qmax", C.c_int32),
                 ("round_mode", C.c_int)]
+
+
+class QuantStats(C.Structure):
+    """yscv_cuda_quant_stats."""
+    _fields_ = [(n, C.c_uint64) for n in ("int4_gemv_calls", "int4_gemm_calls", "int4_generic_calls",
+                                          "int8_gemm_calls", "qlinear_matmul_calls", "matmul_integer_calls",
+                                          "requant_calls", "decode_step_calls", "cpu_fallbacks")]
+
+
+class DecodeOptions(C.Structure):
+    """yscv_cuda_decode_options."""
+    _fields_ = [("variant", C.c_int), ("max_tiles", C.c_int), ("k_chunk", C.c_int), ("attention_form", C.c_int),
+                ("spin_limit", C.c_int), ("tp", _vp)]
 
 
 class DecodeLayer(C.Structure):
@@ -140,14 +197,16 @@ def _ptr(a) -> int:
 class Int4Weight:
     """PackedInt4Weight resident in HBM (owning or wrapping device memory)."""
 
+    borrowed = False  # a view of a handle a Registry owns
+
     def __init__(self, handle: int, m_w: int, k: int, group_size: int):
         self.handle = handle
         self.m_w, self.k, self.group_size = m_w, k, group_size
 
     def free(self):
-        if self.handle:
+        if self.handle and not self.borrowed:
             load_library().yscv_cuda_int4_weight_free(self.handle)
-            self.handle = 0
+        self.handle = 0
 
     def __del__(self):
         try:
@@ -158,6 +217,8 @@ class Int4Weight:
 
 class I8B:
     """PackedI8B resident in HBM."""
+
+    borrowed = False  # a view of a handle a Registry owns
 
     def __init__(self, handle: int):
         self.handle = handle
@@ -170,9 +231,9 @@ class I8B:
         _check(load_library().yscv_cuda_i8b_set_zero_point(self.handle, int(b_zp)))
 
     def free(self):
-        if self.handle:
+        if self.handle and not self.borrowed:
             load_library().yscv_cuda_i8b_free(self.handle)
-            self.handle = 0
+        self.handle = 0
 
     def __del__(self):
         try:
@@ -187,6 +248,155 @@ def int4_from_matmulnbits(src) -> np.ndarray:
     out = np.empty_like(a)
     _check(load_library().yscv_cuda_int4_from_matmulnbits(_ptr(a), _ptr(out), a.size))
     return out
+
+
+def quant_stats() -> dict:
+    """Process-wide operator counters since the last reset."""
+    st = QuantStats()
+    load_library().yscv_cuda_quant_stats_read(C.byref(st))
+    return {n: int(getattr(st, n)) for n, _ in QuantStats._fields_}
+
+
+def quant_stats_reset():
+    load_library().yscv_cuda_quant_stats_reset()
+
+
+def int4_to_matmulnbits(src) -> np.ndarray:
+    """Two's-complement nibbles -> MatMulNBits bytes (unsigned nibbles, zero point 8); host only."""
+    a = _host(src, np.uint8)
+    out = np.empty_like(a)
+    _check(load_library().yscv_cuda_int4_to_matmulnbits(_ptr(a), _ptr(out), a.size))
+    return out
+
+
+def int4_container_write(packed, scales, m_w: int, k: int, group_size: int) -> bytes:
+    """Serialise one packed int4 weight (header + packed bytes + scales)."""
+    lib = load_library()
+    p8, sc = _host(packed, np.uint8), _host(scales, np.float32)
+    size = int(lib.yscv_cuda_int4_container_size(m_w, k, group_size))
+    buf = np.empty(max(size, 64), dtype=np.uint8)
+    written = _sz(0)
+    _check(lib.yscv_cuda_int4_container_write(_ptr(p8), _ptr(sc), m_w, k, group_size, _ptr(buf), buf.size,
+                                              C.byref(written)))
+    return buf[:written.value].tobytes()
+
+
+def int4_container_read(blob: bytes):
+    """-> (packed uint8 [m_w*k/2], scales f32, m_w, k, group_size); validates the header."""
+    lib = load_library()
+    src = np.frombuffer(blob, dtype=np.uint8)
+    m_w, k, g = _sz(0), _sz(0), _sz(0)
+    pp, sp = _vp(), _vp()
+    _check(lib.yscv_cuda_int4_container_read(_ptr(src) if src.size else None, src.size, C.byref(m_w), C.byref(k),
+                                             C.byref(g), C.byref(pp), C.byref(sp)))
+    base = src.ctypes.data
+    p_off, s_off = pp.value - base, sp.value - base
+    n_p, n_s = m_w.value * k.value // 2, m_w.value * (k.value // g.value)
+    packed = src[p_off:p_off + n_p].copy()
+    scales = np.frombuffer(blob, dtype=np.float32, count=n_s, offset=s_off).copy()
+    return packed, scales, m_w.value, k.value, g.value
+
+
+class Registry:
+    """yscv_cuda_registry: resident weights keyed by initializer name."""
+
+    def __init__(self):
+        self.lib = load_library()
+        h = _vp()
+        _check(self.lib.yscv_cuda_registry_create(C.byref(h)))
+        self.handle = h.value
+
+    def put_int4(self, name: str, w: "Int4Weight"):
+        """The table takes the handle over (the wrapper no longer frees it)."""
+        _check(self.lib.yscv_cuda_registry_put_int4(self.handle, name.encode(), w.handle))
+        w.handle = 0
+
+    def put_i8b(self, name: str, b: "I8B"):
+        _check(self.lib.yscv_cuda_registry_put_i8b(self.handle, name.encode(), b.handle))
+        b.handle = 0
+
+    def get_int4(self, name: str):
+        """A borrowed Int4Weight view (never freed by the wrapper), or None."""
+        h = self.lib.yscv_cuda_registry_get_int4(self.handle, name.encode())
+        if not h:
+            return None
+        w = Int4Weight(h, int(self.lib.yscv_cuda_int4_weight_rows(h)), int(self.lib.yscv_cuda_int4_weight_k(h)),
+                       int(self.lib.yscv_cuda_int4_weight_group_size(h)))
+        w.borrowed = True
+        return w
+
+    def get_i8b(self, name: str):
+        h = self.lib.yscv_cuda_registry_get_i8b(self.handle, name.encode())
+        if not h:
+            return None
+        b = I8B(h)
+        b.borrowed = True
+        return b
+
+    def register_matmul_weight(self, ctx: "Context", name: str, weight, layout: int, group_size: int) -> bool:
+        """One weight of quantize_matmul_weights_int4_packed; False when the rules skip it."""
+        w = _host(weight, np.float32)
+        assert w.ndim == 2
+        packed = C.c_int(0)
+        _check(self.lib.yscv_cuda_registry_register_matmul_weight(ctx.handle, self.handle, name.encode(), _ptr(w),
+                                                                  w.shape[0], w.shape[1], layout, group_size,
+                                                                  C.byref(packed)))
+        return bool(packed.value)
+
+    def register_i8_weight(self, ctx: "Context", name: str, b) -> bool:
+        """Load-time prepack of a QLinearMatMul / MatMulInteger weight b [k][n]; False when the gate says no."""
+        b8 = _host(b, np.int8)
+        done = C.c_int(0)
+        _check(self.lib.yscv_cuda_registry_register_i8_weight(ctx.handle, self.handle, name.encode(), _ptr(b8),
+                                                              b8.shape[0], b8.shape[1], C.byref(done)))
+        return bool(done.value)
+
+    def __len__(self):
+        return int(self.lib.yscv_cuda_registry_len(self.handle))
+
+    def close(self):
+        if self.handle:
+            self.lib.yscv_cuda_registry_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class TpComm:
+    """yscv_cuda_tp_comm: this rank's exchange region and the peers' mapped ones."""
+
+    def __init__(self, ctx: "Context", rank: int, world: int, max_rows: int):
+        self.lib, self.rank, self.world = ctx.lib, rank, world
+        h = _vp()
+        self.handle_bytes = np.zeros(TP_HANDLE_BYTES, dtype=np.uint8)
+        _check(self.lib.yscv_cuda_tp_comm_create(ctx.handle, rank, world, max_rows, C.byref(h),
+                                                 _ptr(self.handle_bytes)))
+        self.handle = h.value
+
+    def connect(self, all_handles: np.ndarray):
+        """all_handles: uint8 [world, 64], every rank's handle in rank order."""
+        a = _host(all_handles, np.uint8)
+        assert a.size == self.world * TP_HANDLE_BYTES
+        _check(self.lib.yscv_cuda_tp_comm_connect(self.handle, _ptr(a)))
+
+    def connect_unanswered(self):
+        """Test form: peers that never answer (every wait for them runs out)."""
+        _check(self.lib.yscv_cuda_tp_comm_connect_unanswered(self.handle))
+
+    def close(self):
+        if self.handle:
+            self.lib.yscv_cuda_tp_comm_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class DecodePlan:
@@ -205,6 +415,17 @@ class DecodePlan:
         _check(self.ctx.lib.yscv_cuda_decode_plan_step_token_dev(
             self.ctx.handle, self.handle, _vp(d_embedding), vocab, _vp(d_token), _vp(d_pos), _vp(d_final_gamma),
             _vp(d_lm_head), _vp(d_x), _vp(d_logits)))
+
+    def step_token_shard_dev(self, d_embedding: int, vocab: int, d_token: int, d_pos: int, d_final_gamma: int,
+                             d_lm_head_rows: int, lm_row0: int, lm_rows: int, d_x: int, d_logits: int):
+        """Tensor-parallel form: this rank's rows of the LM head, the token agreed between the ranks."""
+        _check(self.ctx.lib.yscv_cuda_decode_plan_step_token_shard_dev(
+            self.ctx.handle, self.handle, _vp(d_embedding), vocab, _vp(d_token), _vp(d_pos), _vp(d_final_gamma),
+            _vp(d_lm_head_rows), lm_row0, lm_rows, _vp(d_x), _vp(d_logits)))
+
+    def check(self):
+        """Synchronises; raises YscvCudaError(-4) if a bounded wait ran out in a step of this plan."""
+        _check(self.ctx.lib.yscv_cuda_decode_plan_check(self.ctx.handle, self.handle))
 
     def free(self):
         if self.handle:
@@ -437,9 +658,60 @@ class Context:
     def advance_pos_dev(self, d_pos, by=1):
         _check(self.lib.yscv_cuda_advance_pos_dev(self.handle, _vp(d_pos), by))
 
-    def decode_plan(self, layers, hidden, inter, n_q, n_kv, d_head, max_seq, eps, rope_theta) -> DecodePlan:
+    def dispatch_report(self) -> str:
+        return self.lib.yscv_cuda_dispatch_report(self.handle).decode()
+
+    def int4_weight_from_f32(self, weight, layout: int, group_size: int):
+        """fp32 MatMul / Gemm weight -> resident packed int4, or None when the reference's rules skip it."""
+        w = _host(weight, np.float32)
+        assert w.ndim == 2
+        h = _vp()
+        _check(self.lib.yscv_cuda_int4_weight_from_f32(self.handle, _ptr(w), w.shape[0], w.shape[1], layout,
+                                                       group_size, C.byref(h)))
+        if not h.value:
+            return None
+        return Int4Weight(h.value, int(self.lib.yscv_cuda_int4_weight_rows(h.value)),
+                          int(self.lib.yscv_cuda_int4_weight_k(h.value)), group_size)
+
+    def int4_weight_download(self, w: Int4Weight):
+        packed = np.empty(w.m_w * w.k // 2, dtype=np.uint8)
+        scales = np.empty(w.m_w * (w.k // w.group_size), dtype=np.float32)
+        _check(self.lib.yscv_cuda_int4_weight_download(self.handle, w.handle, _ptr(packed), _ptr(scales)))
+        return packed, scales
+
+    def int4_weight_from_container(self, blob: bytes) -> Int4Weight:
+        src = np.frombuffer(blob, dtype=np.uint8)
+        h = _vp()
+        _check(self.lib.yscv_cuda_int4_weight_from_container(self.handle, _ptr(src) if src.size else None, src.size,
+                                                             C.byref(h)))
+        return Int4Weight(h.value, int(self.lib.yscv_cuda_int4_weight_rows(h.value)),
+                          int(self.lib.yscv_cuda_int4_weight_k(h.value)),
+                          int(self.lib.yscv_cuda_int4_weight_group_size(h.value)))
+
+    def requant_i32_row_to_i8(self, acc, bias, composite, y_zp, relu, c):
+        a = _host(acc, np.int32)
+        b = None if bias is None else _host(bias, np.int32)
+        out = np.empty(a.size, dtype=np.int8)
+        _check(self.lib.yscv_cuda_requant_i32_row_to_i8(self.handle, _ptr(a) if a.size else None,
+                                                         None if b is None else _ptr(b), composite, y_zp, int(relu),
+                                                         _ptr(out) if a.size else None, a.size, c))
+        return out
+
+    def rope_kv_append_i8_dev(self, d_qkv, batch, seq, n_q, n_kv, d_head, theta, d_pos, d_kc, d_ks, d_vc, d_vs, max_seq):
+        _check(self.lib.yscv_cuda_rope_kv_append_i8_dev(self.handle, _vp(d_qkv), batch, seq, n_q, n_kv, d_head, theta,
+                                                        _vp(d_pos), _vp(d_kc), _vp(d_ks), _vp(d_vc), _vp(d_vs), max_seq))
+
+    def gqa_attention_i8_dev(self, d_q, q_stride, batch, seq_q, n_q, n_kv, d_head, d_kc, d_ks, d_vc, d_vs, max_seq,
+                             d_pos, causal, d_out):
+        _check(self.lib.yscv_cuda_gqa_attention_i8_dev(self.handle, _vp(d_q), q_stride, batch, seq_q, n_q, n_kv, d_head,
+                                                       _vp(d_kc), _vp(d_ks), _vp(d_vc), _vp(d_vs), max_seq, _vp(d_pos),
+                                                       int(causal), _vp(d_out)))
+
+    def decode_plan(self, layers, hidden, inter, n_q, n_kv, d_head, max_seq, eps, rope_theta, *, variant=-1,
+                    max_tiles=0, k_chunk=0, attention_form=-1, spin_limit=0, tp: "TpComm | None" = None) -> DecodePlan:
         """layers: list of dicts with Int4Weight `qkv`, `o`, `gate_up`, `down` and device
-        pointers `gamma_attn`, `gamma_mlp`, `kcache`, `vcache`."""
+        pointers `gamma_attn`, `gamma_mlp`, `kcache`, `vcache`. The keyword arguments are the
+        fields of yscv_cuda_decode_options (defaults: the library's own choices)."""
         arr = (DecodeLayer * len(layers))()
         for dst, l in zip(arr, layers):
             dst.qkv, dst.o, dst.gate_up, dst.down = (l["qkv"].handle, l["o"].handle, l["gate_up"].handle,
@@ -447,8 +719,10 @@ class Context:
             dst.d_gamma_attn, dst.d_gamma_mlp = l["gamma_attn"], l["gamma_mlp"]
             dst.d_kcache, dst.d_vcache = l["kcache"], l["vcache"]
         h = _vp()
-        _check(self.lib.yscv_cuda_decode_plan_create(self.handle, C.cast(arr, _vp), len(layers), hidden, inter, n_q,
-                                                     n_kv, d_head, max_seq, eps, rope_theta, C.byref(h)))
+        opt = DecodeOptions(variant, max_tiles, k_chunk, attention_form, spin_limit, tp.handle if tp else None)
+        _check(self.lib.yscv_cuda_decode_plan_create_ex(self.handle, C.cast(arr, _vp), len(layers), hidden, inter,
+                                                        n_q, n_kv, d_head, max_seq, eps, rope_theta,
+                                                        C.cast(C.byref(opt), _vp), C.byref(h)))
         return DecodePlan(self, h.value)
 
     def int4_from_matmulnbits_dev(self, d_src: int, d_dst: int, nbytes: int):
