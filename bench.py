@@ -276,6 +276,10 @@ def run_cuda(args):
             sampler = ClockSampler(local) if sample_clocks else None
             if sampler:
                 sampler.start()
+                t_up = time.perf_counter()   # nvidia-smi takes a moment to print its first line
+                while not sampler.rows and time.perf_counter() - t_up < 3.0:
+                    one_step(m)
+                    stream.synchronize()
             for _ in range(warmup):
                 one_step(m)
             stream.synchronize()
@@ -291,7 +295,19 @@ def run_cuda(args):
             torch.cuda.synchronize()
             barrier()
             ms = e0.elapsed_time(e1)
-            clocks = sampler.stop(t_begin, time.perf_counter()) if sampler else None
+            t_end = time.perf_counter()
+            if sampler and not any(t_begin <= r[0] <= t_end for r in sampler.rows):
+                # the timed region was shorter than the sampling period: keep the same load
+                # running (untimed) until a few samples have landed and report those
+                t_begin = time.perf_counter()
+                while time.perf_counter() - t_begin < 0.25:
+                    one_step(m)
+                stream.synchronize()
+                t_end = time.perf_counter()
+                clocks = sampler.stop(t_begin, t_end)
+                clocks["window"] = "the same load continued right after the timed region (the region itself is shorter than the 20 ms sampling period)"
+            else:
+                clocks = sampler.stop(t_begin, t_end) if sampler else None
             launches = ctx.launch_count() - l0
         if world > 1:
             import torch.distributed as dist
@@ -380,11 +396,22 @@ def run_cuda(args):
 
     # ---- the other two quantities of BASELINE's metric, measured beside the headline ----
     other = None
-    if world == 1 and not args.no_extras:
-        other = extra_metrics(ctx, stream, dev)
-        if cpu is not None:
+    if not args.no_extras:
+        # release the headline's 590 MB of weights first: the 70B-shape decoder wants the room
+        weights.clear()
+        acts.clear()
+        outs.clear()
+        del p0, s0, h0
+        torch.cuda.empty_cache()
+        other = extra_metrics(ctx, stream, dev) if world == 1 else {}
+        if other is not None and cpu is not None:
             for name, res in cpu_int8_baselines(oracle, threads).items():
                 other[name]["cpu_baseline"] = res
+        sharded = sharded_metrics(world)      # every rank takes part
+        if rank == 0:
+            other.update(sharded)
+            if world == 1:  # the same run under the name earlier result files carry
+                other["int4_decoder_llama70b_b1"] = other["int4_decoder_llama70b_tp"]
 
     if rank == 0:
         line = {
@@ -413,8 +440,7 @@ def run_cuda(args):
 def extra_metrics(ctx, stream, dev):
     """int8 GEMM TOPS on BASELINE configs[2] (QLinearMatMul 2048x4096x4096, uint8 in/out) and
     configs[0] (MatMulInteger 64x1024x1024), and decode tokens/s of the TinyLlama-1.1B-shape
-    int4 decoder (configs[3], batch 1, 128-token prompt, 128 greedy steps) and of the
-    Llama-3-70B-shape one (configs[4], batch 1, 2048-token prompt, 32 greedy steps)."""
+    int4 decoder (configs[3], batch 1 / 8 / 32, 128-token prompt, 128 greedy steps)."""
     import torch
     from yscv_b200.llm_bench import run as llm_run
     out = {}
@@ -444,16 +470,44 @@ def extra_metrics(ctx, stream, dev):
                          "frac_of_nominal_4500_tops": 2.0 * m * k * n / us / 1e6 / 4500.0}
             pk.free()
     stream.synchronize()
-    d = llm_run("tinyllama", batch=1, prompt_len=128, max_tokens=128, warmup=1)
-    keys = ("decode_tokens_per_sec", "ms_per_step", "prefill_ms", "weight_stream_gbs_per_gpu", "decode_step")
-    out["int4_decoder_tinyllama_b1"] = {k: d[k] for k in keys}
-    # configs[4]: Llama-3-70B shape on this one GPU (47 GB of weights), prompt 2048, 32 greedy steps
+    for batch in (1, 8, 32):   # configs[3]: batch 1 / 8 / 32
+        d = llm_run("tinyllama", batch=batch, prompt_len=128, max_tokens=128, warmup=1)
+        out[f"int4_decoder_tinyllama_b{batch}"] = {k: d[k] for k in LLM_KEYS}
+        torch.cuda.empty_cache()
+    return out
+
+
+LLM_KEYS = ("decode_tokens_per_sec", "ms_per_step", "prefill_ms", "weight_stream_gbs_per_gpu", "decode_step",
+            "kv_cache", "device_status")
+
+
+def sharded_metrics(world):
+    """The workloads BASELINE shards across the GPUs of the job, run at tensor-parallel degree
+    = number of ranks (also 1): the Llama-3-70B-shape int4 decoder (configs[4]: batch 1, prompt
+    2048, 32 greedy steps; column-parallel qkv / gate / up, row-parallel output / down, the
+    partial sums exchanged inside the decode-step kernel) with its gate "greedy tokens equal the
+    one-GPU decoder's for 32 steps" on a 2-layer truncation, and QLinearMatMul configs[2]
+    sharded over output channels (bit-exact gate inside). Every rank calls this; rank 0 gets the
+    numbers."""
+    import torch
+    from yscv_b200 import int8_shard_bench
+    from yscv_b200.llm_bench import run as llm_run, tokens_match_single_gpu
+    out = {}
     try:
+        gate = tokens_match_single_gpu("llama70b", layers=2, prompt_len=64, steps=32)
         torch.cuda.empty_cache()
         d = llm_run("llama70b", batch=1, prompt_len=2048, max_tokens=32, warmup=0)
-        out["int4_decoder_llama70b_b1"] = {k: d[k] for k in keys}
+        res = {k: d[k] for k in LLM_KEYS}
+        res.update({"tensor_parallel": world, "tokens_equal_one_gpu_32_steps_2_layers": gate,
+                    "workload": "BASELINE configs[4]: batch 1, prompt 2048, 32 greedy steps, 80 layers"})
+        out["int4_decoder_llama70b_tp"] = res
     except Exception as e:  # e.g. not enough free memory on a shared GPU: report, do not fail the bench
-        out["int4_decoder_llama70b_b1"] = {"error": f"{type(e).__name__}: {e}"[:200]}
+        out["int4_decoder_llama70b_tp"] = {"error": f"{type(e).__name__}: {e}"[:300], "tensor_parallel": world}
+    torch.cuda.empty_cache()
+    try:
+        out["qlinear_matmul_nshard"] = int8_shard_bench.run(2048, 4096, 4096, iters=30)
+    except Exception as e:
+        out["qlinear_matmul_nshard"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     return out
 
 

@@ -22,13 +22,9 @@ import torch
 from . import Context, sharding
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--rows", type=int, default=2048, help="M")
-    ap.add_argument("--inner", type=int, default=4096, help="K")
-    ap.add_argument("--cols", type=int, default=4096, help="N")
-    ap.add_argument("--iters", type=int, default=50)
-    a = ap.parse_args()
+def run(m=2048, k=4096, n=4096, iters=50):
+    """One measurement inside an initialised job (or a single process). Returns the summary on
+    rank 0, None elsewhere; raises if the gathered output differs from the unsharded one."""
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     dev = torch.device("cuda", local)
@@ -36,10 +32,10 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
     stream = torch.cuda.Stream()
     ctx = Context(local, stream=stream.cuda_stream)
-    m, k, n = a.rows, a.inner, a.cols
     with torch.cuda.stream(stream):
         g = torch.Generator(device=dev)
         g.manual_seed(2)  # the same operands on every rank
@@ -79,7 +75,7 @@ def main():
         with torch.cuda.stream(stream):
             for _ in range(5):
                 fn()
-            for _ in range(a.iters):
+            for _ in range(iters):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
                 fn()
@@ -93,17 +89,34 @@ def main():
 
     t_compute = timed(compute)
     t_both = timed(lambda: (compute(), gather()))
+    out = None
     if rank == 0:
         ops = 2.0 * m * k * n
-        print(json.dumps({"workload": f"QLinearMatMul {m}x{k}x{n} u8 out, N-sharded", "gpus": world,
-                          "bit_exact_vs_unsharded": exact, "us_compute": t_compute, "us_with_all_gather": t_both,
-                          "tops_compute": ops / t_compute / 1e6, "tops_with_all_gather": ops / t_both / 1e6,
-                          "kernel": ctx.last_kernel(), "device_status": ctx.device_status()}), flush=True)
+        out = {"workload": f"QLinearMatMul {m}x{k}x{n} u8 out, N-sharded", "gpus": world,
+               "bit_exact_vs_unsharded": exact, "us_compute": t_compute, "us_with_all_gather": t_both,
+               "tops_compute": ops / t_compute / 1e6, "tops_with_all_gather": ops / t_both / 1e6,
+               "kernel": ctx.last_kernel(), "device_status": ctx.device_status()}
     pk.free()
+    ctx.close()
+    assert exact
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=2048, help="M")
+    ap.add_argument("--inner", type=int, default=4096, help="K")
+    ap.add_argument("--cols", type=int, default=4096, help="N")
+    ap.add_argument("--iters", type=int, default=50)
+    a = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    out = run(a.rows, a.inner, a.cols, a.iters)
+    if out is not None:
+        print(json.dumps(out), flush=True)
     if world > 1:
+        import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
-    assert exact
 
 
 if __name__ == "__main__":

@@ -7,8 +7,10 @@ decode_tokens_per_sec).
     python -m yscv_b200.llm_bench --model tinyllama --batch 1 --prompt-len 128 --max-tokens 256
     torchrun --nproc-per-node 8 -m yscv_b200.llm_bench --model llama70b --prompt-len 2048 --max-tokens 128
 
-Under torchrun the linears are tensor-parallel across the ranks (NCCL all-reduce after
-the row-parallel ones); prompts are uniform token ids from the seeded generator.
+Under torchrun the linears are tensor-parallel across the ranks: the prompt pass and
+batches above 1 sum the row-parallel partials with an NCCL all-reduce, the batch-1 decode
+step is one kernel launch per rank whose CTAs exchange the partials through peer memory.
+Prompts are uniform token ids from the seeded generator.
 """
 from __future__ import annotations
 
@@ -24,15 +26,15 @@ from .decoder import LLAMA3_70B, TINYLLAMA_1B, Int4Decoder
 MODELS = {"tinyllama": (TINYLLAMA_1B, 3), "llama70b": (LLAMA3_70B, 4)}
 
 
-def weight_bytes_per_token(cfg, layers, tp):
+def weight_bytes_per_token(cfg, layers, tp, lm_head_sharded=False):
     d = cfg.head_dim
     per_layer = (cfg.n_q + 2 * cfg.n_kv) * d * cfg.hidden + cfg.hidden * cfg.n_q * d + 3 * cfg.mlp * cfg.hidden
     int4 = per_layer * layers * (0.5 + 4.0 / cfg.group_size) / tp
-    return int4 + cfg.vocab * cfg.hidden * 4  # + fp32 LM head (replicated)
+    return int4 + cfg.vocab * cfg.hidden * 4 / (tp if lm_head_sharded else 1)  # + fp32 LM head
 
 
 def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, layers=None, use_graph=True,
-        exact_prefill=False):
+        exact_prefill=False, kv_int8=False, fused_step=True, return_tokens=False):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -49,7 +51,7 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
     ctx.set_int4_prefill_exact(exact_prefill)
     n_layers = layers or cfg.layers
     dec = Int4Decoder(ctx, cfg, batch, prompt_len + max_tokens + 2, stream, seed=seed, tp_rank=rank, tp_size=world,
-                      process_group=pg, layers=n_layers)
+                      process_group=pg, layers=n_layers, kv_int8=kv_int8, fused_step=fused_step)
     import numpy as np
     prompt = np.stack([synth.uniform_int(seed + b, 9, prompt_len, 0, cfg.vocab - 1) for b in range(batch)])
     d_prompt = torch.from_numpy(prompt.astype(np.int32)).cuda()
@@ -89,7 +91,9 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         prefill_ms, decode_ms = float(t[0]), float(t[1])
     tps = batch * max_tokens * 1000.0 / decode_ms
-    wb = weight_bytes_per_token(cfg, n_layers, world)
+    wb = weight_bytes_per_token(cfg, n_layers, world, lm_head_sharded=dec.plan is not None and world > 1)
+    if dec.plan is not None:
+        dec.plan.check()
     summary = {
         "model": f"{model} (random-init int4, group {cfg.group_size}, {n_layers} layers)",
         "gpus": world, "batch": batch, "prompt_tokens": prompt_len, "decode_tokens": max_tokens,
@@ -98,12 +102,47 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
         "weight_bytes_per_step_per_gpu": wb,
         "weight_stream_gbs_per_gpu": wb / (decode_ms / max_tokens * 1e-3) / 1e9,
         "cuda_graph": bool(use_graph), "prefill": "fp32-exact" if exact_prefill else "bf16 tensor-core",
-        "decode_step": "one persistent kernel per token" if dec.plan is not None else "operator chain",
+        "decode_step": ("one persistent kernel per token" + (" per GPU, partial sums exchanged through peer memory "
+                                                              "inside it" if world > 1 else ""))
+        if dec.plan is not None else ("operator chain" + (" + NCCL all-reduce" if world > 1 else "")),
+        "kv_cache": "int8 rows + f32 scale per token" if kv_int8 else "f32",
         "first_tokens": toks[:8, 0].cpu().tolist(),
         "device_status": ctx.device_status(),
     }
+    if return_tokens:
+        summary["tokens"] = toks.cpu().numpy().copy()
     dec.close()
+    ctx.close()
     return summary
+
+
+def tokens_match_single_gpu(model="llama70b", layers=2, prompt_len=64, steps=32):
+    """The tensor-parallel decoder of this job against the same decoder on one GPU, on a
+    truncation of `layers` layers with the prompt pass in the fp32-exact mode: identical greedy
+    tokens for `steps` steps (rank 0 runs the one-GPU decoder; returns None on other ranks)."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    tp = run(model, 1, prompt_len, steps, warmup=0, layers=layers, exact_prefill=True, return_tokens=True)
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    saved = {k: os.environ.get(k) for k in ("RANK", "WORLD_SIZE")}
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = "0", "1"
+    try:
+        # one GPU: the one-launch step against the operator chain; several GPUs: their
+        # one-launch steps against the one-launch step of a single GPU
+        one = run(model, 1, prompt_len, steps, warmup=0, layers=layers, exact_prefill=True, return_tokens=True,
+                  fused_step=world > 1)
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+    torch.cuda.empty_cache()
+    import numpy as np
+    return bool(np.array_equal(tp["tokens"], one["tokens"])) and tp["device_status"] == 0
 
 
 def main():
