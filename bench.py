@@ -296,6 +296,7 @@ def run_cuda(args):
             barrier()
             ms = e0.elapsed_time(e1)
             t_end = time.perf_counter()
+            launches = ctx.launch_count() - l0
             if sampler and not any(t_begin <= r[0] <= t_end for r in sampler.rows):
                 # the timed region was shorter than the sampling period: keep the same load
                 # running (untimed) until a few samples have landed and report those
@@ -308,7 +309,6 @@ def run_cuda(args):
                 clocks["window"] = "the same load continued right after the timed region (the region itself is shorter than the 20 ms sampling period)"
             else:
                 clocks = sampler.stop(t_begin, t_end) if sampler else None
-            launches = ctx.launch_count() - l0
         if world > 1:
             import torch.distributed as dist
             t = torch.tensor([ms], device=dev)

@@ -827,7 +827,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     float *misc = act_s + p.act_floats;  // 32 floats
     float *rope_cs = misc + 32;          // [d_head/2] x {cos, sin} of this step's position
     float **cache_ptr = reinterpret_cast<float **>(rope_cs + p.d_head);  // [layers] x {k, v}
-    float *wtab = reinterpret_cast<float *>(cache_ptr + 2 * p.layers);   // [n_q][4] split-merge weights
+    float *wtab = reinterpret_cast<float *>(cache_ptr + 2 * p.layers);   // [n_q][4 or 16] split-merge weights
     const int nmat = p.layers * 4;
 
     // A position outside the cache: nothing is appended, nothing is computed, the status word
@@ -1036,6 +1036,33 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         if (!SIMPLE && p.attn_grouped) {
 #pragma unroll 4
             for (int i = tid; i < AW; i += DS_CONSUMERS) act_s[i] = __ldcg(p.attn_out + i);
+        } else if (p.splits > 4) {
+            // many key chunks per head (few heads on this GPU, long context): per (head, chunk)
+            // the weight exp(m - M) / L once, through the shared-memory table [n_q][16]
+            if (tid < p.n_q) {
+                const float *pp = p.attn + (size_t)tid * p.splits * (p.d_head + 2) + p.d_head;
+                float M = -INFINITY;
+                for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, __ldcg(pp + (size_t)sp * (p.d_head + 2)));
+                float L = 0.0f;
+                for (int sp = 0; sp < p.splits; ++sp) {
+                    const float m = __ldcg(pp + (size_t)sp * (p.d_head + 2));
+                    const float w = m > -INFINITY ? expf(m - M) : 0.0f;
+                    L = fmaf(w, __ldcg(pp + (size_t)sp * (p.d_head + 2) + 1), L);
+                    wtab[tid * 16 + sp] = w;
+                }
+                const float invL = L > 0.0f ? 1.0f / L : 0.0f;
+                for (int sp = 0; sp < p.splits; ++sp) wtab[tid * 16 + sp] *= invL;
+            }
+            cons_sync();
+            for (int i = tid; i < AW; i += DS_CONSUMERS) {
+                const int hh = i / p.d_head, dd = i - hh * p.d_head;
+                const float *pp = p.attn + (size_t)hh * p.splits * (p.d_head + 2) + dd;
+                const float *w = wtab + hh * 16;
+                float acc = 0.0f;
+#pragma unroll 4
+                for (int sp = 0; sp < p.splits; ++sp) acc = fmaf(w[sp], __ldcg(pp + (size_t)sp * (p.d_head + 2)), acc);
+                act_s[i] = acc;
+            }
         } else if (p.merge_table) {
             // per (head, split): weight exp(m - M) / L once, through shared memory
             if (tid < p.n_q) {
@@ -1420,7 +1447,9 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     p.dig_bytes = kc_stages * DS_BLOB_BYTES;
     // attention form: per query head with up to 4 key chunks, or (long contexts, or
     // YSCV_CUDA_STEP_ATTN=1) per KV head with up to 32 key chunks and a merge phase
-    const int splits = (int)std::min<size_t>(4, (size_t)grid / n_q);
+    // key chunks (CTAs) per query head: up to 4, or up to 16 when this GPU has so few heads that
+    // 4 would leave most SMs idle (tensor-parallel shards)
+    const int splits = (int)std::min<size_t>(n_q * 4 * 2 <= (size_t)grid ? 16 : 4, (size_t)grid / n_q);
     const size_t grp = n_q / n_kv;
     const bool group_ok = (grp & (grp - 1)) == 0 && grp <= 16 && grp * d_head <= 2048 &&
                           DS_CONSUMERS % (grp * d_head / 4) == 0;
@@ -1441,7 +1470,7 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
         return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: max_seq=%zu does not fit one CTA per head", max_seq));
     p.act_floats = (int)act_floats;
     // misc, rotary factors, cache pointers, split-merge weights
-    const int tables = 128 + (int)d_head * 4 + (int)n_layers * 2 * 8 + (int)n_q * 16 + 16;
+    const int tables = 128 + (int)d_head * 4 + (int)n_layers * 2 * 8 + (int)n_q * 16 * (splits > 4 ? 4 : 1) + 16;
     const int fixed = DS_RED_BYTES + DS_BAR_BYTES + p.dig_bytes + p.act_floats * 4 + tables;
     const int budget = 227 * 1024 - fixed - 1024;
     p.stages = budget / slot_bytes;
