@@ -372,11 +372,25 @@ def run_cuda(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t.item())
     e2e_calls = e2e_steps * COPIES
+    # the same calls from pageable host memory (what a caller that never pinned its buffers gets)
+    a_pg, o_pg = np.array(a_np), np.empty_like(o_np)
+    for _, _, h in weights:
+        ctx.int4_matmul(h, a_pg, M_HEADLINE, out=o_pg)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for _, _, h in weights:
+            ctx.int4_matmul(h, a_pg, M_HEADLINE, out=o_pg)
+    torch.cuda.synchronize()
+    dt_pg = time.perf_counter() - t0
+    e2e_ok = bool(np.array_equal(o_pg, o_np))
     e2e = {"value": algorithmic_bytes(M_HEADLINE) * e2e_calls * world / dt / 1e9, "unit": "GB/s",
            "h2d_bytes_per_step": COPIES * M_HEADLINE * K * 4, "d2h_bytes_per_step": COPIES * M_HEADLINE * N * 4,
            "us_per_call": dt * 1e6 / e2e_calls,
+           "us_per_call_pageable_buffers": dt_pg * 1e6 / e2e_calls,
+           "pinned_equals_pageable_result": e2e_ok,
            "api": "yscv_cuda_int4_matmul (weights uploaded once at load time, pinned host activation "
-                  "in, pinned host output out, synchronised per call)"}
+                  "copied in, output written by the kernel into the caller's pinned buffer, synchronised per call; "
+                  "pageable buffers go through a staging copy each way)"}
 
     # ---- CPU baseline beside it (rank 0, N=1 only): bounded sample ----
     cpu = None

@@ -113,6 +113,13 @@ void yscv_cuda_quant_stats_reset(void);
  * counterpart of choosing packed_int4_gemm_scalar over a SIMD variant
  * (crates/yscv-kernels/src/ops/int4_matmul.rs:548-605). */
 int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact);
+/* Kernel-selection switch of the int8 GEMM, like the reference's environment gates on its
+ * int8 paths (crates/yscv-onnx/src/runner/quant_stats.rs:68-71): enable != 0 lets shapes with
+ * enough 256 x 256 tiles run on CTA pairs (tcgen05 cta_group::2, two SMs per tile, each staging
+ * half of both operands); 0 (the default) keeps the one-CTA kernel everywhere, which measured
+ * faster on every shape tried: the tensor pipe, not shared memory, bounds this GEMM. The
+ * results are identical (integer arithmetic), only the speed differs. */
+int yscv_cuda_ctx_set_int8_cta_pairs(yscv_cuda_ctx *ctx, int enable);
 /* Per-kernel timing, the counterpart of YSCV_RUNNER_PROFILE
  * (crates/yscv-onnx/src/runner/profile.rs:1-120): while enabled, the dominant
  * kernel of every call is bracketed by CUDA events on the context's stream

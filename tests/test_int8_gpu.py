@@ -289,3 +289,32 @@ def test_matmul_integer_with_b_zero_point(ctx, oracle, m, k, n, a_unsigned, a_zp
                           (a.astype(np.int64).reshape(m, k) - a_zp) @ b.astype(np.int64).reshape(k, n))
     assert ctx.device_status() == 0
     packed.free()
+
+
+@pytest.mark.parametrize("m,k,n", [(2048, 1024, 2560), (1500, 300, 2304), (4096, 256, 4096)])
+def test_cta_pair_kernel_is_bit_identical(ctx, oracle, m, k, n):
+    """The cta_group::2 kernel (two CTAs per 256 x 256 tile, off by default) against the one-CTA
+    kernel and, on a row sample, the oracle: int32 and requantised outputs, ragged M, K not a
+    multiple of the stage, more tiles than CTA pairs."""
+    import torch
+    rng = np.random.default_rng(17)
+    a = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+    b = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    pk = ctx.pack_i8_b(b, k, n)
+    rq = ctx.requant(3e-4, 128.0, 0, 255, a_unsigned=True, a_zp=128)
+    outs = {}
+    try:
+        for pairs in (False, True):
+            ctx.set_int8_cta_pairs(pairs)
+            q = ctx.qlinear_matmul(a, pk, m, rq)
+            assert ("cta_group::2" in ctx.last_kernel()) == pairs
+            outs[pairs] = (q, ctx.matmul_integer(a, pk, m, a_zp=128))
+    finally:
+        ctx.set_int8_cta_pairs(False)
+    assert np.array_equal(outs[False][0], outs[True][0]) and np.array_equal(outs[False][1], outs[True][1])
+    rows = rng.choice(m, size=16, replace=False)
+    acc = oracle.int8_matmul((a[rows] ^ 0x80).view(np.int8), b, len(rows), k, n)
+    assert np.array_equal(outs[True][1][rows], acc)
+    assert np.array_equal(outs[True][0][rows], oracle.requant_range(acc, 3e-4, 128.0, 0, 255).astype(np.uint8))
+    pk.free()
+    assert ctx.device_status() == 0

@@ -255,6 +255,12 @@ int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact) {
     return YSCV_CUDA_OK;
 }
 
+int yscv_cuda_ctx_set_int8_cta_pairs(yscv_cuda_ctx *ctx, int enable) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    ctx->int8_pairs = enable != 0;
+    return YSCV_CUDA_OK;
+}
+
 const char *yscv_cuda_last_kernel(const yscv_cuda_ctx *ctx) { return ctx ? ctx->last_kernel : "none"; }
 
 uint64_t yscv_cuda_ctx_launch_count(const yscv_cuda_ctx *ctx) { return ctx ? ctx->launches : 0; }
@@ -413,6 +419,18 @@ int yscv_cuda_int4_matmul_dev(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w
                            d_output, m);
 }
 
+// Device alias of a host buffer the kernels may write directly (page-locked and mapped into the
+// device's address space: cudaHostAlloc / cudaHostRegister memory under unified addressing),
+// or null for pageable memory.
+static void *mapped_alias(const void *host) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, host) != cudaSuccess) {
+        cudaGetLastError();  // (older runtimes report pageable memory as an error)
+        return nullptr;
+    }
+    return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
+}
+
 int yscv_cuda_int4_matmul(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
                           const float *activation, float *output, size_t m) {
     if (!ctx || !w) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
@@ -421,12 +439,22 @@ int yscv_cuda_int4_matmul(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
     YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
     const size_t ab = m * w->k * sizeof(float), ob = m * w->m_w * sizeof(float);
     int rc;
-    if ((rc = ctx->in2.reserve(ab)) || (rc = ctx->out0.reserve(ob))) return rc;
+    if ((rc = ctx->in2.reserve(ab))) return rc;
+    // A page-locked output buffer is written by the kernel itself (posted writes over PCIe, no
+    // copy-engine pass behind the kernel); a pageable one goes through the staging buffer. The
+    // activations are always copied in: every CTA reads all of them, which must not cross PCIe
+    // 148 times.
+    float *d_out = m <= 16 ? static_cast<float *>(mapped_alias(output)) : nullptr;
+    const bool direct = d_out != nullptr && (reinterpret_cast<uintptr_t>(d_out) & 15) == 0;
+    if (!direct) {
+        if ((rc = ctx->out0.reserve(ob))) return rc;
+        d_out = (float *)ctx->out0.ptr;
+    }
     YSCV_CUDA_TRY(cudaMemcpyAsync(ctx->in2.ptr, activation, ab, cudaMemcpyHostToDevice, ctx->stream));
     rc = int4_matmul_dev(ctx, w->d_packed, w->d_scales, w->m_w, w->k, w->group_size,
-                         (const float *)ctx->in2.ptr, (float *)ctx->out0.ptr, m);
+                         (const float *)ctx->in2.ptr, d_out, m);
     if (rc) return rc;
-    YSCV_CUDA_TRY(cudaMemcpyAsync(output, ctx->out0.ptr, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!direct) YSCV_CUDA_TRY(cudaMemcpyAsync(output, ctx->out0.ptr, ob, cudaMemcpyDeviceToHost, ctx->stream));
     YSCV_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     return YSCV_CUDA_OK;
 }

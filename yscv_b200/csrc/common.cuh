@@ -101,6 +101,7 @@ struct yscv_cuda_ctx {
     uint64_t launches = 0;
     const char *last_kernel = "none";
     bool prefill_exact = false;  // int4 matmul with m > 16: fp32-exact kernel instead of bf16 MMA
+    bool int8_pairs = false;     // int8 GEMM: CTA-pair kernel (cta_group::2) where the shape has enough tiles; measured slower, off by default
     // optional per-kernel event timing (yscv_cuda_ctx_profile_*)
     bool profiling = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;

@@ -110,6 +110,90 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+// Epilogue of one accumulator row: the thread owns output row `row`, whose BN int32 sums sit in
+// TMEM at `taddr` (this warp's lane group, the tile's first column); columns nb * BN ... of the
+// output. Subtracts the zero-point terms, then stores int32 or requantises and stores bytes.
+template <int BN>
+__device__ __forceinline__ void epilogue_row(const G8Params &p, const int32_t *__restrict__ colsum,
+                                             void *__restrict__ out, int row, uint32_t taddr, int nb) {
+    const bool general = p.corr != nullptr || p.comp_pc != nullptr || p.relu != 0 || p.b_zp != 0;
+    // 16-byte vector stores need a 16-byte aligned output (rows then stay aligned through
+    // the pitch conditions below); anything else takes scalar stores
+    const bool out_vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    // what the zero point of B adds to every element of this row
+    int row_term = 0;
+    if (p.b_zp != 0 && row < p.M)
+        row_term = (int)((uint32_t)p.k_true * (uint32_t)p.a_zp * (uint32_t)p.b_zp -
+                         (uint32_t)p.b_zp * (uint32_t)__ldg(p.rowsum + row));
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        const int col0 = nb * BN + c0;
+        if (row < p.M && col0 < p.N) {
+            if (p.mode == 0) {
+                int32_t *o = reinterpret_cast<int32_t *>(out) + (size_t)row * p.ldc + col0;
+                if (col0 + 32 <= p.N && (p.ldc & 3) == 0 && out_vec_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        int4 v;
+                        v.x = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
+                        v.y = (int)r[j + 1] - p.a_zp * __ldg(colsum + col0 + j + 1) + row_term;
+                        v.z = (int)r[j + 2] - p.a_zp * __ldg(colsum + col0 + j + 2) + row_term;
+                        v.w = (int)r[j + 3] - p.a_zp * __ldg(colsum + col0 + j + 3) + row_term;
+                        *reinterpret_cast<int4 *>(o + j) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) o[j] = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
+                }
+            } else {
+                uint8_t *o = reinterpret_cast<uint8_t *>(out) + (size_t)row * p.ldc + col0;
+                uint32_t packed[8];
+                if (general) {
+                    // per-channel vectors, bias, ReLU or a zero point on B
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int cc = (col0 + j < p.N) ? col0 + j : col0;
+                        int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc) + row_term;
+                        float comp = p.composite;
+                        if (p.corr) acc = (int)((uint32_t)acc + (uint32_t)__ldg(p.corr + cc));
+                        if (p.comp_pc) comp = __ldg(p.comp_pc + cc);
+                        // separate multiply and add: the CPU kernel does not fuse them
+                        const float v = __fadd_rn(__fmul_rn((float)acc, comp), p.y_zp);
+                        const float rr = p.round_mode ? roundf(v) : rintf(v);
+                        int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
+                        if (p.relu && qv < 0) qv = 0;
+                        if ((j & 3) == 0) packed[j >> 2] = 0;
+                        packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int cc = (col0 + j < p.N) ? col0 + j : col0;
+                        const int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc);
+                        // separate multiply and add: the CPU kernel does not fuse them
+                        const float v = __fadd_rn(__fmul_rn((float)acc, p.composite), p.y_zp);
+                        const float rr = p.round_mode ? roundf(v) : rintf(v);
+                        const int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
+                        if ((j & 3) == 0) packed[j >> 2] = 0;
+                        packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
+                    }
+                }
+                if (col0 + 32 <= p.N && (p.ldc & 15) == 0 && out_vec_ok) {
+                    *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    *reinterpret_cast<uint4 *>(o + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) o[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
+                }
+            }
+        }
+    }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(G8_THREADS, 1)
 int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -218,82 +302,7 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             tc_fence_after();
             const int row = mb * G8_BM + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)abuf * BN;
-            const bool general = p.corr != nullptr || p.comp_pc != nullptr || p.relu != 0 || p.b_zp != 0;
-            // 16-byte vector stores need a 16-byte aligned output (rows then stay aligned through
-            // the pitch conditions below); anything else takes scalar stores
-            const bool out_vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-            // what the zero point of B adds to every element of this row
-            int row_term = 0;
-            if (p.b_zp != 0 && row < p.M)
-                row_term = (int)((uint32_t)p.k_true * (uint32_t)p.a_zp * (uint32_t)p.b_zp -
-                                 (uint32_t)p.b_zp * (uint32_t)__ldg(p.rowsum + row));
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(taddr + c0, r);
-                const int col0 = nb * BN + c0;
-                if (row < p.M && col0 < p.N) {
-                    if (p.mode == 0) {
-                        int32_t *o = reinterpret_cast<int32_t *>(out) + (size_t)row * p.ldc + col0;
-                        if (col0 + 32 <= p.N && (p.ldc & 3) == 0 && out_vec_ok) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                int4 v;
-                                v.x = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
-                                v.y = (int)r[j + 1] - p.a_zp * __ldg(colsum + col0 + j + 1) + row_term;
-                                v.z = (int)r[j + 2] - p.a_zp * __ldg(colsum + col0 + j + 2) + row_term;
-                                v.w = (int)r[j + 3] - p.a_zp * __ldg(colsum + col0 + j + 3) + row_term;
-                                *reinterpret_cast<int4 *>(o + j) = v;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N) o[j] = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
-                        }
-                    } else {
-                        uint8_t *o = reinterpret_cast<uint8_t *>(out) + (size_t)row * p.ldc + col0;
-                        uint32_t packed[8];
-                        if (general) {
-                            // per-channel vectors, bias, ReLU or a zero point on B
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int cc = (col0 + j < p.N) ? col0 + j : col0;
-                                int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc) + row_term;
-                                float comp = p.composite;
-                                if (p.corr) acc = (int)((uint32_t)acc + (uint32_t)__ldg(p.corr + cc));
-                                if (p.comp_pc) comp = __ldg(p.comp_pc + cc);
-                                // separate multiply and add: the CPU kernel does not fuse them
-                                const float v = __fadd_rn(__fmul_rn((float)acc, comp), p.y_zp);
-                                const float rr = p.round_mode ? roundf(v) : rintf(v);
-                                int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
-                                if (p.relu && qv < 0) qv = 0;
-                                if ((j & 3) == 0) packed[j >> 2] = 0;
-                                packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int cc = (col0 + j < p.N) ? col0 + j : col0;
-                                const int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc);
-                                // separate multiply and add: the CPU kernel does not fuse them
-                                const float v = __fadd_rn(__fmul_rn((float)acc, p.composite), p.y_zp);
-                                const float rr = p.round_mode ? roundf(v) : rintf(v);
-                                const int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
-                                if ((j & 3) == 0) packed[j >> 2] = 0;
-                                packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
-                            }
-                        }
-                        if (col0 + 32 <= p.N && (p.ldc & 15) == 0 && out_vec_ok) {
-                            *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                            *reinterpret_cast<uint4 *>(o + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N) o[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
-                        }
-                    }
-                }
-            }
+            epilogue_row<BN>(p, colsum, out, row, taddr, nb);
             // all columns of this buffer have been read: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
@@ -308,6 +317,236 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * BN));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair kernel: tcgen05.mma.cta_group::2
+// ---------------------------------------------------------------------------
+//
+// Two CTAs on the two SMs of a TPC (a cluster of 2) share one 256 x 256 output tile. Per K
+// step each CTA stages its own 128 rows of A and its own 128 rows of the B^T tile (plain TMA
+// loads, no multicast); the leader CTA (cluster rank 0) issues one MMA of M = 256, N = 256 that
+// reads both CTAs' shared memory and accumulates rows 0..127 into its own TMEM and rows
+// 128..255 into the peer's. Against the one-CTA kernel a tensor core then reads 8 KB instead of
+// 12 KB of shared memory per instruction and each SM pulls 32 KB instead of 48 KB per K step
+// from L2 for the same flops: shared-memory bandwidth (TMA fill + MMA operand reads on one
+// 128 B/clk port) is what holds the one-CTA kernel at ~60 % of the tensor rate.
+//
+// Signalling (every barrier is a local mbarrier of the CTA that waits on it; remote arrivals
+// go through mapa + mbarrier.arrive.release.cluster; no multicast form is used anywhere):
+//   full[s]       own TMA loads of stage s landed                     (each CTA)
+//   peer_full[s]  leader only: the peer's relay thread saw the peer's full[s]
+//   empty[s]      leader: tcgen05.commit after the MMAs of stage s; peer: the leader's producer
+//                 forwards it once it has seen its own
+//   tfull[b]      leader: tcgen05.commit after the last K step; peer: forwarded by the leader's
+//                 first epilogue warp
+//   tempty[b]     leader only, 8 arrivals: the four epilogue warps of both CTAs drained buffer b
+// All waits are bounded; a wait that runs out sets the status word, the roles fall through to the
+// cluster-wide barrier at the end, and TMEM is released.
+constexpr int G8P_BN = 256;           // columns of the pair tile
+constexpr int G8P_STAGE = 2 * G8_BM * G8_BK;  // per CTA: 128 rows of A + 128 rows of B^T
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait on a barrier that a thread of the other CTA arrives on
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int *status) {
+    for (uint32_t i = 0; i < (1u << 22); ++i)
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (status) atomicExch(status, 1 /* YSCV_DEV_MBARRIER_TIMEOUT */);
+    return false;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(G8_THREADS, 1)
+int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                      const int32_t *__restrict__ colsum, void *__restrict__ out, G8Params p,
+                      int *__restrict__ status) {
+    constexpr int BN = G8P_BN;
+    constexpr int HALF_BYTES = G8_BM * G8_BK;   // 16 KB: one CTA's rows of A, or of B^T
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_rank();       // 0: leader (issues the MMAs), 1: peer
+    const uint32_t other = rank ^ 1u;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bars = smem_base + (uint32_t)p.stages * G8P_STAGE;
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * 8, bar_pfull = bars + 16 * 8;
+    const uint32_t bar_tfull = bars + 24 * 8, bar_tempty = bars + 26 * 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)p.stages * G8P_STAGE + 28 * 8);
+    const int tiles = p.m_blocks * p.n_blocks;   // pair tiles of 256 x 256
+
+    if (tid == 0) {
+        for (int i = 0; i < p.stages; ++i) {
+            mbar_init(bar_full + i * 8, 1);
+            mbar_init(bar_empty + i * 8, 1);
+            mbar_init(bar_pfull + i * 8, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tfull + i * 8, 1);
+            mbar_init(bar_tempty + i * 8, 8);  // four epilogue warps of each CTA
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        // 2 x 256 columns in each CTA of the pair; released after the cluster barrier at the end
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(2 * BN));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    cluster_sync_all();   // both CTAs' barriers exist before anyone arrives on a remote one
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs): own 128 rows of A, own 128 rows of B^T ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_a));
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_b));
+            int slot = 0, turn = 0;   // turn: how many times the ring has wrapped
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int t = pair; t < tiles && alive; t += n_pairs) {
+                const int mb = t % p.m_blocks, nb = t / p.m_blocks;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    // the leader's slot is freed by the MMA commit, the peer's by the leader's
+                    // forward of that same event (issued right below; never for a slot's first
+                    // use, which needs no freeing)
+                    alive = rank == 0 ? mbar_wait(bar_empty + slot * 8, phase ^ 1u, status)
+                                      : mbar_wait_cluster(bar_empty + slot * 8, phase ^ 1u, status);
+                    if (!alive) break;
+                    if (rank == 0 && turn > 0) mbar_arrive_remote(map_to_cta(bar_empty + slot * 8, other));
+                    const uint32_t st = smem_base + (uint32_t)slot * G8P_STAGE;
+                    const uint32_t full = bar_full + slot * 8;
+                    mbar_expect_tx(full, G8P_STAGE);
+                    tma_load_2d(st, &tm_a, kb * G8_BK, mb * 256 + (int)rank * G8_BM, full);
+                    tma_load_2d(st + HALF_BYTES, &tm_b, kb * G8_BK, nb * BN + (int)rank * G8_BM, full);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; ++turn; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---------------- MMA issuer (leader only) ----------------
+            const uint32_t idesc = (2u << 4) | ((p.a_unsigned ? 0u : 1u) << 7) | (1u << 10) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            int slot = 0, abuf = 0;
+            uint32_t phase = 0, aphase = 0;
+            bool alive = true;
+            for (int t = pair; t < tiles && alive; t += n_pairs) {
+                alive = mbar_wait_cluster(bar_tempty + abuf * 8, aphase ^ 1u, status);
+                if (!alive) break;
+                tc_fence_after();
+                const uint32_t tacc = tmem_base + (uint32_t)abuf * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    alive = mbar_wait(bar_full + slot * 8, phase, status) &&
+                            mbar_wait_cluster(bar_pfull + slot * 8, phase, status);
+                    if (!alive) break;
+                    tc_fence_after();
+                    const uint32_t st = smem_base + (uint32_t)slot * G8P_STAGE;
+                    const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + HALF_BYTES);
+#pragma unroll
+                    for (int j = 0; j < G8_BK / 32; ++j)
+                        umma_i8_pair(tacc, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc,
+                                     (kb > 0 || j > 0) ? 1u : 0u);
+                    umma_commit_pair(bar_empty + slot * 8);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                }
+                if (!alive) break;
+                umma_commit_pair(bar_tfull + abuf * 8);
+                if (++abuf == 2) { abuf = 0; aphase ^= 1u; }
+            }
+        } else if (lane == 0 && rank == 1) {
+            // ---------------- peer: tell the leader when this CTA's stage has landed ----------------
+            int slot = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int t = pair; t < tiles && alive; t += n_pairs) {
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    alive = mbar_wait(bar_full + slot * 8, phase, status);
+                    if (!alive) break;
+                    mbar_arrive_remote(map_to_cta(bar_pfull + slot * 8, 0));
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs): warps 2..5 own TMEM lanes 32*(warp%4).. ----------------
+        const int q = warp & 3;
+        int abuf = 0;
+        uint32_t aphase = 0;
+        bool alive = true;
+        const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
+        for (int t = pair; t < tiles && alive; t += n_pairs) {
+            const int mb = t % p.m_blocks, nb = t / p.m_blocks;
+            alive = rank == 0 ? mbar_wait(bar_tfull + abuf * 8, aphase, status)
+                              : mbar_wait_cluster(bar_tfull + abuf * 8, aphase, status);
+            if (!alive) break;
+            if (rank == 0 && q == 0 && lane == 0) mbar_arrive_remote(map_to_cta(bar_tfull + abuf * 8, other));
+            tc_fence_after();
+            const int row = mb * 256 + (int)rank * G8_BM + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)abuf * BN;
+            epilogue_row<BN>(p, colsum, out, row, taddr, nb);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_tempty + abuf * 8);
+            if (++abuf == 2) { abuf = 0; aphase ^= 1u; }
+        }
+    }
+
+    // ---------------- common exit ----------------
+    // Neither CTA may leave (or give its TMEM back) while the other can still read its shared
+    // memory or arrive on its barriers.
+    tc_fence_before();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * BN));
     }
 }
 
@@ -406,6 +645,56 @@ static int launch_g8(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const yscv
     return YSCV_CUDA_OK;
 }
 
+static int launch_g8_pair(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const yscv_cuda_i8b *b, size_t m,
+                          void *d_out, const G8Params &proto) {
+    G8Params p = proto;
+    p.M = (int)m;
+    p.N = (int)b->n;
+    p.K = (int)b->kp;
+    p.m_blocks = (p.M + 255) / 256;
+    p.n_blocks = (p.N + G8P_BN - 1) / G8P_BN;
+    p.k_blocks = (p.K + G8_BK - 1) / G8_BK;
+    p.stages = (227 * 1024 - 1024) / G8P_STAGE;
+    if (p.stages > 8) p.stages = 8;
+    const int smem = p.stages * G8P_STAGE + 256;
+    CUtensorMap tm_a, tm_b;
+    int rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d_a, m, b->kp, lda, G8_BM, G8_BK,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b->d_bt, b->n, b->kp, b->kp, G8_BM, G8_BK,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = ensure_dynamic_smem(reinterpret_cast<const void *>(int8_gemm_pair_kernel), ctx->device, 227 * 1024);
+    if (rc) return rc;
+    const int tiles = p.m_blocks * p.n_blocks;
+    const int max_pairs = ctx->sm_count / 2;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    snprintf(ctx->report_int8, sizeof(ctx->report_int8),
+             "int8_gemm_pair m=%d n=%d k=%d: tcgen05 kind::i8 cta_group::2, pair tile 256x%d, %d stages of %d KB per CTA, "
+             "%d tiles on %d CTA pairs, %s",
+             p.M, p.N, p.K, G8P_BN, p.stages, G8P_STAGE / 1024, tiles, pairs,
+             p.mode == 0 ? "int32 out" : "requantised bytes out");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(G8_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ctx->prof_begin();
+    YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, int8_gemm_pair_kernel, tm_a, tm_b, (const int32_t *)b->d_colsum, d_out, p,
+                                     ctx->d_status));
+    ctx->prof_end();
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    return YSCV_CUDA_OK;
+}
+
 // d_a: [m][k] bytes (i8, or u8 when a_unsigned). mode 0: d_out int32 [m][n]; mode 1: bytes [m][n].
 int int8_gemm(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_t m, void *d_out,
               int a_unsigned, int a_zp, int mode, float composite, float y_zp, int qmin, int qmax,
@@ -453,6 +742,12 @@ int int8_gemm(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_
     }
     // wide tiles when there are enough of them to fill the machine, else narrower ones
     const size_t tiles256 = ((m + G8_BM - 1) / G8_BM) * ((b->n + 255) / 256);
+    // CTA pairs (256 x 256 per pair) once there are enough pair tiles to occupy most pairs
+    const size_t pair_tiles = ((m + 255) / 256) * ((b->n + 255) / 256);
+    if (ctx->int8_pairs && b->n >= 256 && m >= 256 && pair_tiles * 10 >= (size_t)(ctx->sm_count / 2) * 8) {
+        ctx->last_kernel = "int8_gemm_pair(tcgen05,cta_group::2,256x256)";
+        return launch_g8_pair(ctx, a, lda, b, m, d_out, p);
+    }
     if (b->n >= 256 && tiles256 >= (size_t)ctx->sm_count) {
         ctx->last_kernel = "int8_gemm_tc(tcgen05,128x256)";
         return launch_g8<256>(ctx, a, lda, b, m, d_out, p);

@@ -41,6 +41,7 @@ SIGNATURES = {
     "yscv_cuda_last_kernel": (C.c_char_p, [_vp]),
     "yscv_cuda_ctx_launch_count": (C.c_uint64, [_vp]),
     "yscv_cuda_ctx_set_int4_prefill_exact": (C.c_int, [_vp, C.c_int]),
+    "yscv_cuda_ctx_set_int8_cta_pairs": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_enable": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_read": (C.c_int, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "yscv_cuda_int4_matmul": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
@@ -481,6 +482,10 @@ class Context:
     def set_int4_prefill_exact(self, exact: bool):
         """m > 16 int4 matmuls: fp32-exact kernel (True) or bf16 tensor-core GEMM (False, default)."""
         _check(self.lib.yscv_cuda_ctx_set_int4_prefill_exact(self.handle, int(exact)))
+
+    def set_int8_cta_pairs(self, on: bool):
+        """int8 GEMM: allow the CTA-pair kernel (cta_group::2) or keep the one-CTA kernel everywhere (default)."""
+        _check(self.lib.yscv_cuda_ctx_set_int8_cta_pairs(self.handle, int(on)))
 
     def profile_enable(self, on: bool):
         _check(self.lib.yscv_cuda_ctx_profile_enable(self.handle, int(on)))
