@@ -497,6 +497,69 @@ def test_int8_kv_cache_bytes(tctx, oracle):
     assert ctx.device_status() == 0
 
 
+def test_f32_matmul_wide_batch(tctx):
+    """The LM-head product for more than 8 rows (tiled kernel) against float64, ragged edges."""
+    import torch
+    ctx, s = tctx
+    rng = np.random.default_rng(31)
+    for m, n, k in [(9, 1000, 512), (32, 3207, 2048), (70, 130, 36)]:
+        w = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+        x = rng.normal(0, 1.0, (m, k)).astype(np.float32)
+        d_w, d_x = dev(w), dev(x)
+        out = torch.full((m, n), float("nan"), device="cuda")
+        with torch.cuda.stream(s):
+            ctx.f32_matmul_dev(d_w.data_ptr(), d_x.data_ptr(), m, n, k, out.data_ptr())
+        s.synchronize()
+        assert "tiled" in ctx.last_kernel()
+        want = x.astype(np.float64) @ w.astype(np.float64).T
+        got = out.cpu().numpy()
+        assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 1e-5, (m, n, k)
+    assert ctx.device_status() == 0
+
+
+def test_decode_attention_serves_whole_groups(tctx, oracle):
+    """Split-key decode attention over a long cache, f32 and int8, batch 3, groups of 4 and of
+    12 query heads per KV head (more than one pass of eight), a ragged last chunk."""
+    import torch
+    ctx, s = tctx
+    rng = np.random.default_rng(32)
+    for n_q, n_kv, d, seq in [(8, 2, 64, 300), (12, 1, 128, 131), (16, 2, 32, 257)]:
+        B, max_seq = 3, seq + 5
+        q = rng.normal(0, 1, (B, n_q * d)).astype(np.float32)
+        kf = rng.normal(0, 1, (B, max_seq, n_kv * d)).astype(np.float32)
+        vf = rng.normal(0, 1, (B, max_seq, n_kv * d)).astype(np.float32)
+        pos = dev(np.array([seq - 1], np.int32))
+        out = torch.empty(B, n_q * d, device="cuda")
+        d_q, d_k, d_v = dev(q), dev(kf), dev(vf)
+        with torch.cuda.stream(s):
+            ctx.gqa_attention_dev(d_q.data_ptr(), n_q * d, B, 1, n_q, n_kv, d, d_k.data_ptr(), d_v.data_ptr(),
+                                  max_seq, pos.data_ptr(), True, out.data_ptr())
+        s.synchronize()
+        assert "split-k" in ctx.last_kernel()
+        for b in range(B):
+            want = oracle.gqa_attention(q[b], kf[b, :seq].ravel(), vf[b, :seq].ravel(), 1, 1, seq, n_q, n_kv, d, False)
+            assert np.max(np.abs(out[b].cpu().numpy() - want)) < 2e-5 * max(1.0, np.max(np.abs(want)))
+        # the same cache quantised row by row
+        kq = np.empty((B, max_seq, n_kv * d), np.int8)
+        vq = np.empty_like(kq)
+        ksc = np.empty((B, max_seq), np.float32)
+        vsc = np.empty_like(ksc)
+        for b in range(B):
+            kq[b], ksc[b] = oracle.kv_append_i8(kf[b])
+            vq[b], vsc[b] = oracle.kv_append_i8(vf[b])
+        d_kq, d_ks, d_vq, d_vs = dev(kq), dev(ksc), dev(vq), dev(vsc)
+        with torch.cuda.stream(s):
+            ctx.gqa_attention_i8_dev(d_q.data_ptr(), n_q * d, B, 1, n_q, n_kv, d, d_kq.data_ptr(),
+                                     d_ks.data_ptr(), d_vq.data_ptr(), d_vs.data_ptr(), max_seq,
+                                     pos.data_ptr(), True, out.data_ptr())
+        s.synchronize()
+        for b in range(B):
+            kd, vd = oracle.kv_dequantise_i8(kq[b, :seq], ksc[b, :seq]), oracle.kv_dequantise_i8(vq[b, :seq], vsc[b, :seq])
+            want = oracle.gqa_attention(q[b], kd.ravel(), vd.ravel(), 1, 1, seq, n_q, n_kv, d, False)
+            assert np.max(np.abs(out[b].cpu().numpy() - want)) < 2e-5 * max(1.0, np.max(np.abs(want)))
+    assert ctx.device_status() == 0
+
+
 def test_position_outside_the_cache_is_reported(tctx):
     """pos >= max_seq: both decode paths leave the caches alone and set status 3."""
     import torch

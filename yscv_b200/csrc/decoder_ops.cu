@@ -243,10 +243,13 @@ gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n
 }
 
 // Decode-shaped attention (one query position per sequence) with the keys split across
-// blocks so that a long cache fills the machine: block (split, q head, b) handles keys
-// [split*chunk, ...), leaves an unnormalised partial output, its running max and its
-// exp-sum in `part`; attention_combine_kernel merges the splits (the usual
-// max-rescaling of a split softmax).
+// blocks so that a long cache fills the machine: block (split, kv head, b) handles keys
+// [split*chunk, ...) for ALL the query heads of its KV head's group from one pass over the
+// chunk's key and value rows (a row is read once per group, not once per query head), leaves
+// per query head an unnormalised partial output, its running max and its exp-sum in `part`;
+// attention_combine_kernel merges the splits (the usual max-rescaling of a split softmax).
+// Query heads are taken eight at a time. d % 16 == 0, d <= 128, blockDim.x == chunk == 128.
+// Dynamic shared memory: q [8][d], weights [8][chunk], partial sums [128 / (d/4)][8][d].
 template <typename KV>
 __global__ void __launch_bounds__(128)
 gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int n_kv, int d,
@@ -256,90 +259,139 @@ gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int 
     pdl_wait();
     pdl_trigger();
     constexpr bool I8 = sizeof(KV) == 1;
-    // chunk == blockDim.x == 128: one key per thread in the score phase
+    constexpr int HB = 8;   // query heads per pass
     extern __shared__ float sm[];
-    float *scores = sm;            // chunk
-    float *qs = sm + chunk;        // d
-    float *acc2 = qs + d;          // d   (second half of the threads in the V phase)
+    float *qs = sm;                    // [HB][d]
+    float *wts = qs + HB * d;          // [HB][chunk]
+    float *psum = wts + HB * chunk;    // [key groups][HB][d]
     __shared__ float red[4];
-    const int split = blockIdx.x, qh = blockIdx.y, b = blockIdx.z, n_splits = gridDim.x;
-    const int kv_h = qh / (n_q / n_kv);
+    const int tid = threadIdx.x;
+    const int split = blockIdx.x, kv_h = blockIdx.y, b = blockIdx.z, n_splits = gridDim.x;
+    const int grp = n_q / n_kv;
     int limit = *pos + 1;
     limit = limit > max_seq ? max_seq : (limit < 0 ? 0 : limit);
     const int k0 = split * chunk, k1 = min(limit, k0 + chunk);
-    float *po = part + (((size_t)b * n_q + qh) * n_splits + split) * (d + 2);
-    if (k0 >= k1) {  // nothing for this split yet: neutral element of the merge
-        for (int i = threadIdx.x; i < d; i += blockDim.x) po[i] = 0.0f;
-        if (threadIdx.x == 0) { po[d] = -INFINITY; po[d + 1] = 0.0f; }
-        return;
-    }
     const int nk = k1 - k0;
     const float scale = 1.0f / sqrtf((float)d);
-    const float *qrow = q + (size_t)b * q_stride + (size_t)qh * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = qrow[i];
-    __syncthreads();
     const KV *kb = kc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
     const KV *vb = vc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
     const float *ksc = I8 ? kscale + (size_t)b * max_seq : nullptr;
     const float *vsc = I8 ? vscale + (size_t)b * max_seq : nullptr;
-    // scores: thread j owns key k0 + j and walks its row with wide loads
-    float sc = -INFINITY;
-    if ((int)threadIdx.x < nk) {
-        const float4 *q4 = reinterpret_cast<const float4 *>(qs);
-        float dot = 0.0f;
-        if constexpr (I8) {
-            // four int8 per 32-bit load (rows are 4-byte aligned: d % 4 == 0)
-            const int *kr = reinterpret_cast<const int *>(kb + (size_t)(k0 + threadIdx.x) * n_kv * d);
-            const float rs = ksc[k0 + threadIdx.x];
-#pragma unroll 4
-            for (int i = 0; i < d / 4; ++i) {
-                const int w = __ldg(kr + i);
-                const float4 qv = q4[i];
-                dot = fmaf(qv.x, __fmul_rn((float)(int8_t)(w & 255), rs), dot);
-                dot = fmaf(qv.y, __fmul_rn((float)(int8_t)((w >> 8) & 255), rs), dot);
-                dot = fmaf(qv.z, __fmul_rn((float)(int8_t)((w >> 16) & 255), rs), dot);
-                dot = fmaf(qv.w, __fmul_rn((float)(int8_t)((w >> 24) & 255), rs), dot);
+    const int quads = d / 4, kgroups = blockDim.x / quads;      // V phase: thread = (key group, 4 dims)
+    const int vq = tid % quads, vg = tid / quads;
+    for (int h0 = 0; h0 < grp; h0 += HB) {
+        const int nh = min(HB, grp - h0);
+        const int qh0 = kv_h * grp + h0;
+        if (nk <= 0) {  // nothing for this split yet: the neutral element of the merge
+            for (int i = tid; i < nh * (d + 2); i += blockDim.x) {
+                const int hh = i / (d + 2), j = i - hh * (d + 2);
+                part[(((size_t)b * n_q + qh0 + hh) * n_splits + split) * (d + 2) + j] = j == d ? -INFINITY : 0.0f;
             }
-        } else {
-            const float4 *kr = reinterpret_cast<const float4 *>(kb + (size_t)(k0 + threadIdx.x) * n_kv * d);
-#pragma unroll 4
-            for (int i = 0; i < d / 4; ++i) {
-                const float4 kv = __ldg(kr + i), qv = q4[i];
-                dot = fmaf(qv.x, kv.x, dot);
-                dot = fmaf(qv.y, kv.y, dot);
-                dot = fmaf(qv.z, kv.z, dot);
-                dot = fmaf(qv.w, kv.w, dot);
-            }
+            continue;
         }
-        sc = dot * scale;
-    }
-    const float mx = block_max(sc, red);
-    float e = ((int)threadIdx.x < nk) ? expf(sc - mx) : 0.0f;
-    const float se = block_sum(e, red);
-    // int8 values: fold the row scale of the value row into its weight once
-    if (I8 && (int)threadIdx.x < nk) e = e * vsc[k0 + threadIdx.x];
-    scores[threadIdx.x] = e;
-    __syncthreads();
-    // weighted V: the two halves of the block take alternate keys, d threads each (d <= 64),
-    // or all threads take every key (d == 128)
-    const int groups = blockDim.x / d >= 2 ? 2 : 1;
-    const int gi = threadIdx.x / d, i = threadIdx.x % d;
-    float acc = 0.0f;
-    if (gi < groups) {
-#pragma unroll 4
-        for (int j = gi; j < nk; j += groups) {
-            const KV *vr = vb + (size_t)(k0 + j) * n_kv * d;
-            acc = fmaf(scores[j], I8 ? (float)vr[i] : kv_get<KV>(vr, i, 1.0f), acc);
-        }
-    }
-    if (groups == 2) {
-        if (gi == 1) acc2[i] = acc;
+        __syncthreads();   // the previous pass is done with the shared arrays
+        for (int i = tid; i < nh * d; i += blockDim.x)
+            qs[i] = q[(size_t)b * q_stride + (size_t)(qh0 + i / d) * d + (i % d)];
         __syncthreads();
-        if (gi == 0) po[i] = acc + acc2[i];
-    } else if (gi == 0) {
-        po[i] = acc;
+        // ---- scores: thread j owns key k0 + j, walks its row once, 16 elements at a time ----
+        float dot[HB];
+#pragma unroll
+        for (int h = 0; h < HB; ++h) dot[h] = 0.0f;
+        if (tid < nk) {
+            const KV *kr = kb + (size_t)(k0 + tid) * n_kv * d;
+            const float rs = I8 ? ksc[k0 + tid] : 1.0f;
+            for (int c = 0; c < d; c += 16) {
+                float kv[16];
+                if constexpr (I8) {
+                    const int4 w = __ldg(reinterpret_cast<const int4 *>(kr + c));
+                    const int ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int t = 0; t < 16; ++t)
+                        kv[t] = __fmul_rn((float)(int8_t)((ww[t >> 2] >> (8 * (t & 3))) & 255), rs);
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const float4 f = __ldg(reinterpret_cast<const float4 *>(kr + c) + t);
+                        kv[4 * t] = f.x; kv[4 * t + 1] = f.y; kv[4 * t + 2] = f.z; kv[4 * t + 3] = f.w;
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < HB; ++h) {
+                    if (h < nh) {
+                        const float *qh = qs + h * d + c;
+#pragma unroll
+                        for (int t = 0; t < 16; ++t) dot[h] = fmaf(qh[t], kv[t], dot[h]);
+                    }
+                }
+            }
+        }
+        // ---- per head: local softmax over the chunk; the weights go to shared memory ----
+        for (int h = 0; h < nh; ++h) {
+            const float sc = tid < nk ? dot[h] * scale : -INFINITY;
+            const float mx = block_max(sc, red);
+            float e = tid < nk ? expf(sc - mx) : 0.0f;
+            const float se = block_sum(e, red);
+            // int8 values: fold the row scale of the value row into its weight once
+            if (I8 && tid < nk) e = e * vsc[k0 + tid];
+            wts[h * chunk + tid] = e;
+            if (tid == 0) {
+                float *po = part + (((size_t)b * n_q + qh0 + h) * n_splits + split) * (d + 2);
+                po[d] = mx;
+                po[d + 1] = se;
+            }
+        }
+        __syncthreads();
+        // ---- weighted values: thread (key group vg, dims 4*vq..): a value row quad serves every head ----
+        float acc[HB][4];
+#pragma unroll
+        for (int h = 0; h < HB; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.0f;
+        if (vg < kgroups) {
+            // four value rows' loads in flight per thread, then the arithmetic
+            for (int j0 = vg; j0 < nk; j0 += 4 * kgroups) {
+                float v4[4][4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j0 + u * kgroups;
+                    const KV *vr = vb + (size_t)(k0 + (j < nk ? j : j0)) * n_kv * d;
+                    if constexpr (I8) {
+                        const int w = __ldg(reinterpret_cast<const int *>(vr) + vq);
+                        v4[u][0] = (float)(int8_t)(w & 255); v4[u][1] = (float)(int8_t)((w >> 8) & 255);
+                        v4[u][2] = (float)(int8_t)((w >> 16) & 255); v4[u][3] = (float)(int8_t)((w >> 24) & 255);
+                    } else {
+                        const float4 f = __ldg(reinterpret_cast<const float4 *>(vr) + vq);
+                        v4[u][0] = f.x; v4[u][1] = f.y; v4[u][2] = f.z; v4[u][3] = f.w;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j0 + u * kgroups;
+                    if (j >= nk) break;
+#pragma unroll
+                    for (int h = 0; h < HB; ++h) {
+                        if (h < nh) {
+                            const float w = wts[h * chunk + j];
+                            acc[h][0] = fmaf(w, v4[u][0], acc[h][0]);
+                            acc[h][1] = fmaf(w, v4[u][1], acc[h][1]);
+                            acc[h][2] = fmaf(w, v4[u][2], acc[h][2]);
+                            acc[h][3] = fmaf(w, v4[u][3], acc[h][3]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < HB; ++h)
+                if (h < nh)
+                    *reinterpret_cast<float4 *>(psum + ((size_t)vg * HB + h) * d + 4 * vq) =
+                        make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
+        }
+        __syncthreads();
+        for (int i = tid; i < nh * d; i += blockDim.x) {
+            const int h = i / d, dd = i - h * d;
+            float v = 0.0f;
+            for (int g = 0; g < kgroups; ++g) v += psum[((size_t)g * HB + h) * d + dd];
+            part[(((size_t)b * n_q + qh0 + h) * n_splits + split) * (d + 2) + dd] = v;
+        }
     }
-    if (threadIdx.x == 0) { po[d] = mx; po[d + 1] = se; }
 }
 
 __global__ void attention_combine_kernel(const float *__restrict__ part, int n_splits, int d,
@@ -418,6 +470,68 @@ f32_matmul_kernel(const float *__restrict__ w, const float *__restrict__ x, floa
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (lane == 0 && i < mt) out[(size_t)(m0 + i) * N + n] = v;
+        }
+    }
+}
+
+// The same product for a wide batch (m > 8): a shared-memory tiled SGEMM, 128 weight rows x 64
+// activation rows per block, K walked 32 at a time, every thread an 8 x 4 block of outputs.
+// The weights are read once from HBM per 64 activation rows.
+constexpr int FM_BN = 128, FM_BM = 64, FM_BK = 32;
+__global__ void __launch_bounds__(256)
+f32_matmul_tiled_kernel(const float *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
+                        int M, int N, int K) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float ws[FM_BK][FM_BN + 4];
+    __shared__ float xs[FM_BK][FM_BM + 4];
+    const int tid = threadIdx.x;
+    const int n0 = blockIdx.x * FM_BN, m0 = blockIdx.y * FM_BM;
+    const int tn = tid % 16, tm = tid / 16;      // outputs n0 + tn*8 .. +7, m0 + tm*4 .. +3
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += FM_BK) {
+        // stage the tiles transposed: [k][row]; rows / k past the edge are zero
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * 256, r = idx / 8, c = (idx % 8) * 4;   // 128 rows x 8 float4
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (n0 + r < N && k0 + c < K) v = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(n0 + r) * K + k0 + c));
+            ws[c][r] = v.x; ws[c + 1][r] = v.y; ws[c + 2][r] = v.z; ws[c + 3][r] = v.w;
+        }
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int idx = tid + it * 256, r = idx / 8, c = (idx % 8) * 4;   // 64 rows x 8 float4
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (m0 + r < M && k0 + c < K) v = __ldg(reinterpret_cast<const float4 *>(x + (size_t)(m0 + r) * K + k0 + c));
+            xs[c][r] = v.x; xs[c + 1][r] = v.y; xs[c + 2][r] = v.z; xs[c + 3][r] = v.w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < FM_BK; ++kk) {
+            const float4 wa = *reinterpret_cast<const float4 *>(&ws[kk][tn * 8]);
+            const float4 wb = *reinterpret_cast<const float4 *>(&ws[kk][tn * 8 + 4]);
+            const float4 xa = *reinterpret_cast<const float4 *>(&xs[kk][tm * 4]);
+            const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            const float xv[4] = {xa.x, xa.y, xa.z, xa.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + tm * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int n = n0 + tn * 8 + j;
+            if (n < N) out[(size_t)m * N + n] = acc[i][j];
         }
     }
 }
@@ -611,19 +725,22 @@ static int gqa_attention_impl(yscv_cuda_ctx *ctx, const float *d_q, size_t q_str
     if (batch * seq_q == 0) return YSCV_CUDA_OK;
     if (seq_q == 1 && causal && max_seq > 128) {
         // decode over a long cache: split the keys across blocks, then merge
-        if (d_head % 4 != 0 || d_head > 128)
+        if (d_head % 16 != 0 || d_head > 128)
             return fail(YSCV_CUDA_ERR_UNSUPPORTED, "d_head %zu not supported by the decode attention", d_head);
-        // 128-bit (f32) / 32-bit (int8) loads of key rows and of the staged query
-        if ((reinterpret_cast<uintptr_t>(d_kcache) & (sizeof(KV) == 1 ? 3 : 15)) != 0)
-            return fail(YSCV_CUDA_ERR_UNSUPPORTED, "the key cache must be %d-byte aligned", sizeof(KV) == 1 ? 4 : 16);
+        // key and value rows are read with 128-bit loads
+        if (((reinterpret_cast<uintptr_t>(d_kcache) | reinterpret_cast<uintptr_t>(d_vcache)) & 15) != 0)
+            return fail(YSCV_CUDA_ERR_UNSUPPORTED, "the key and value caches must be 16-byte aligned");
         const int chunk = 128;
         const int n_splits = (int)((max_seq + chunk - 1) / chunk);
         const size_t need = batch * n_q * (size_t)n_splits * (d_head + 2) * sizeof(float);
         int rc = ctx->scratch_attn.reserve(need);
         if (rc) return rc;
         float *part = reinterpret_cast<float *>(ctx->scratch_attn.ptr);
-        dim3 grid((unsigned)n_splits, (unsigned)n_q, (unsigned)batch);
-        YSCV_CUDA_TRY(launch_pdl(gqa_decode_split_kernel<KV>, dim3(grid), dim3(128), (chunk + 2 * d_head) * sizeof(float),
+        // one block per (key chunk, KV head, sequence): it serves every query head of the group
+        dim3 grid((unsigned)n_splits, (unsigned)n_kv, (unsigned)batch);
+        const size_t kgroups = 128 / (d_head / 4);
+        const size_t split_smem = (8 * d_head + 8 * chunk + kgroups * 8 * d_head) * sizeof(float);
+        YSCV_CUDA_TRY(launch_pdl(gqa_decode_split_kernel<KV>, dim3(grid), dim3(128), split_smem,
                                  ctx->stream, d_q, (int)q_stride, (int)n_q, (int)n_kv, (int)d_head, d_kcache, d_vcache,
                                  d_kscale, d_vscale, (int)max_seq, d_pos, chunk, part));
         YSCV_CUDA_TRY(cudaGetLastError());
@@ -684,13 +801,18 @@ int yscv_cuda_f32_matmul_dev(yscv_cuda_ctx *ctx, const float *d_w, const float *
         return fail(YSCV_CUDA_ERR_UNSUPPORTED, "weights and activations must be 16-byte aligned");
     if (m * n == 0) return YSCV_CUDA_OK;
     const unsigned blocks = (unsigned)((n + 7) / 8 < (size_t)(16 * ctx->sm_count) ? (n + 7) / 8 : 16 * ctx->sm_count);
-    // one pass over the weights per 4 (or, for wide batches, 16) activation rows
-    const size_t mt = m > 8 ? 16 : 4;
-    for (size_t m0 = 0; m0 < m; m0 += mt) {
-        if (mt == 16)
-            YSCV_CUDA_TRY(launch_pdl(f32_matmul_kernel<16>, dim3(blocks), dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k));
-        else
-            YSCV_CUDA_TRY(launch_pdl(f32_matmul_kernel<4>, dim3(blocks), dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k));
+    if (m > 8) {
+        // wide batch: tiled SGEMM, the weights cross HBM once per 64 activation rows
+        dim3 grid((unsigned)((n + FM_BN - 1) / FM_BN), (unsigned)((m + FM_BM - 1) / FM_BM));
+        YSCV_CUDA_TRY(launch_pdl(f32_matmul_tiled_kernel, grid, dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m, (int)n, (int)k));
+        YSCV_CUDA_TRY(cudaGetLastError());
+        ctx->launches++;
+        ctx->last_kernel = "f32_matmul(tiled)";
+        return YSCV_CUDA_OK;
+    }
+    // one pass over the weights per 4 activation rows
+    for (size_t m0 = 0; m0 < m; m0 += 4) {
+        YSCV_CUDA_TRY(launch_pdl(f32_matmul_kernel<4>, dim3(blocks), dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m0, (int)m, (int)n, (int)k));
         YSCV_CUDA_TRY(cudaGetLastError());
         ctx->launches++;
     }

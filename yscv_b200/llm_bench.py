@@ -34,7 +34,10 @@ def weight_bytes_per_token(cfg, layers, tp, lm_head_sharded=False):
 
 
 def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, layers=None, use_graph=True,
-        exact_prefill=False, kv_int8=False, fused_step=True, return_tokens=False):
+        exact_prefill=False, kv_int8=False, fused_step=True, return_tokens=False, synthetic_cache=False):
+    """synthetic_cache: skip the prompt pass and fill the KV cache of the first prompt_len
+    positions with seeded random rows instead (decode throughput does not depend on what the
+    cache holds; used where the prompt pass of a wide batch would take minutes)."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -55,17 +58,34 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
     import numpy as np
     prompt = np.stack([synth.uniform_int(seed + b, 9, prompt_len, 0, cfg.vocab - 1) for b in range(batch)])
     d_prompt = torch.from_numpy(prompt.astype(np.int32)).cuda()
-    for _ in range(warmup):  # stateless warm-up with the full prompt, cache restored afterwards
-        dec.reset()
-        dec.prefill(d_prompt)
-    stream.synchronize()
-    dec.reset()
     e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        dec.prefill(d_prompt)
-        e1.record(stream)
-    stream.synchronize()
+    if synthetic_cache:
+        with torch.cuda.stream(stream):
+            gen = torch.Generator(device=dec.dev)
+            gen.manual_seed(seed + 77)
+            for l in range(n_layers):
+                for cache, scale in ((dec.kcache[l], dec.kscale[l] if kv_int8 else None),
+                                     (dec.vcache[l], dec.vscale[l] if kv_int8 else None)):
+                    if kv_int8:
+                        cache[:, :prompt_len].copy_(torch.randint(-127, 128, cache[:, :prompt_len].shape, device=dec.dev,
+                                                                  generator=gen, dtype=torch.int8))
+                        scale[:, :prompt_len].fill_(1.0 / 127.0)
+                    else:
+                        cache[:, :prompt_len].normal_(0.0, 1.0, generator=gen)
+            dec.pos.fill_(prompt_len)
+            dec.next_tokens.copy_(d_prompt[:, -1])
+        stream.synchronize()
+    else:
+        for _ in range(warmup):  # stateless warm-up with the full prompt, cache restored afterwards
+            dec.reset()
+            dec.prefill(d_prompt)
+        stream.synchronize()
+        dec.reset()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            dec.prefill(d_prompt)
+            e1.record(stream)
+        stream.synchronize()
     if use_graph:
         dec.capture_decode_step()
     l0 = ctx.launch_count()
@@ -77,19 +97,21 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
     stream.synchronize()
     prefill_ms, decode_ms = e0.elapsed_time(e1) if False else None, e1.elapsed_time(e2)
     # the prefill was timed before e1 was re-recorded: measure it again from a fresh pair
-    dec.reset()
-    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        p0.record(stream)
-        dec.prefill(d_prompt)
-        p1.record(stream)
-    stream.synchronize()
-    prefill_ms = p0.elapsed_time(p1)
+    prefill_ms = None
+    if not synthetic_cache:
+        dec.reset()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            p0.record(stream)
+            dec.prefill(d_prompt)
+            p1.record(stream)
+        stream.synchronize()
+        prefill_ms = p0.elapsed_time(p1)
     if world > 1:
         import torch.distributed as dist
-        t = torch.tensor([prefill_ms, decode_ms], device="cuda")
+        t = torch.tensor([prefill_ms or 0.0, decode_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        prefill_ms, decode_ms = float(t[0]), float(t[1])
+        prefill_ms, decode_ms = (float(t[0]) if prefill_ms is not None else None), float(t[1])
     tps = batch * max_tokens * 1000.0 / decode_ms
     wb = weight_bytes_per_token(cfg, n_layers, world, lm_head_sharded=dec.plan is not None and world > 1)
     if dec.plan is not None:
@@ -105,7 +127,8 @@ def run(model="tinyllama", batch=1, prompt_len=128, max_tokens=256, warmup=1, la
         "decode_step": ("one persistent kernel per token" + (" per GPU, partial sums exchanged through peer memory "
                                                               "inside it" if world > 1 else ""))
         if dec.plan is not None else ("operator chain" + (" + NCCL all-reduce" if world > 1 else "")),
-        "kv_cache": "int8 rows + f32 scale per token" if kv_int8 else "f32",
+        "kv_cache": ("int8 rows + f32 scale per token" if kv_int8 else "f32") +
+                    (", first prompt_len positions filled with random rows instead of a prompt pass" if synthetic_cache else ""),
         "first_tokens": toks[:8, 0].cpu().tolist(),
         "device_status": ctx.device_status(),
     }
@@ -154,10 +177,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--layers", type=int, default=None, help="truncate the stack (default: the model's depth)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--kv-int8", action="store_true", help="KV cache as int8 rows with one f32 scale per token")
+    ap.add_argument("--synthetic-cache", action="store_true",
+                    help="no prompt pass: random cache contents for the first prompt-len positions")
     ap.add_argument("--exact-prefill", action="store_true",
                     help="prompt pass on the fp32-exact int4 kernel (token-for-token comparable across TP degrees)")
     a = ap.parse_args()
-    s = run(a.model, a.batch, a.prompt_len, a.max_tokens, a.warmup, a.layers, not a.no_graph, a.exact_prefill)
+    s = run(a.model, a.batch, a.prompt_len, a.max_tokens, a.warmup, a.layers, not a.no_graph, a.exact_prefill,
+            kv_int8=a.kv_int8, synthetic_cache=a.synthetic_cache)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(s), flush=True)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
