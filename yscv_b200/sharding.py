@@ -74,3 +74,41 @@ def assemble_cols(parts):
     parts = np.asarray(parts)
     g, m, w = parts.shape
     return parts.transpose(1, 0, 2).reshape(m, g * w)
+
+
+# ---- the exchange inside the tensor-parallel decode step ----------------------------------
+# Host-side statement of the slot / tag arithmetic of csrc/decode_step.cu, so that it can be
+# checked without a GPU. A step of `layers` layers has 2 * layers row-parallel GEMVs (output
+# and down projection of every layer) followed by one greedy-token exchange. Every exchange
+# writes {value, tag} words into slot (parity, source rank, row) of every peer's region.
+
+def exchanges_per_step(layers: int) -> int:
+    return 2 * layers + 1
+
+
+def exchange_tag(step: int, layers: int, exchange: int) -> int:
+    """32-bit tag of exchange number `exchange` (0 .. 2*layers) of decode step `step`; never 0,
+    the value of a slot nobody has written yet."""
+    tag = (step * exchanges_per_step(layers) + exchange + 1) & 0xFFFFFFFF
+    return tag
+
+
+def exchange_parity(step: int, layers: int, exchange: int) -> int:
+    """Which of the two slot sets an exchange uses: the GEMV exchanges alternate (there is an
+    even number of them per step, so the alternation continues across steps); the token
+    exchange has slots of its own and alternates by step."""
+    return (exchange & 1) if exchange < 2 * layers else (step & 1)
+
+
+def exchange_slot(parity: int, src_rank: int, row: int, world: int, rows_cap: int) -> int:
+    """Word index of (parity, source rank, row) in a rank's exchange region."""
+    return (parity * world + src_rank) * rows_cap + row
+
+
+def sum_in_rank_order(partials):
+    """What every rank computes from the world's partial sums: p0 + p1 + ... in rank order,
+    hence bit-identical on every rank."""
+    total = partials[0].copy()
+    for p in partials[1:]:
+        total = total + p
+    return total
