@@ -90,7 +90,7 @@ def sample_idx(rows, cols, count, dev):
     return r, c
 
 
-def bench_int8(ctx, stream, dev, iters, only):
+def bench_int8(ctx, stream, dev, iters, only, calibrate=False):
     print("\n== INT8 GEMM (tcgen05, i32 accumulate; QLinearMatMul = + requant to u8) ==")
     for label, m, k, n in INT8_SHAPES:
         if only and only not in label:
@@ -115,6 +115,17 @@ def bench_int8(ctx, stream, dev, iters, only):
         ops = 2.0 * m * k * n
         print(f"  {label:46s} i32: med {med:9.2f} us min {mn:9.2f} us {ops / mn / 1e6:8.1f} TOPS | "
               f"requant-u8: min {mnq:9.2f} us {ops / mnq / 1e6:8.1f} TOPS  [{ctx.last_kernel()}]  parity: bit-exact")
+        if calibrate and m % 8 == 0 and k % 8 == 0 and n % 8 == 0 and m > 16:
+            # CALIBRATION ONLY: what the vendor's own int8 GEMM (cuBLASLt through torch._int_mm)
+            # reaches on this shape and this GPU, the practical ceiling of the int8 tensor pipe.
+            # Never part of the library's code path.
+            with torch.cuda.stream(stream):
+                a8 = (a.to(torch.int16) - 128).to(torch.int8)
+                lib = torch._int_mm(a8, b)
+                same = bool(torch.equal(lib, o32))
+            lmed, lmn = time_us(stream, lambda: torch._int_mm(a8, b), iters)
+            print(f"  {'':46s} calibration, library int8 GEMM (cuBLASLt, i32 out): min {lmn:9.2f} us "
+                  f"{ops / lmn / 1e6:8.1f} TOPS  same result: {same}")
         pk.free()
 
 
@@ -231,12 +242,15 @@ def main():
     ap.add_argument("--only", default=None, help="substring of the shape label")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--copies", type=int, default=16)
+    ap.add_argument("--calibrate-int8", action="store_true",
+                    help="also time the vendor library's int8 GEMM on every int8 shape (calibration of the "
+                         "tensor-pipe ceiling only)")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     stream = torch.cuda.Stream()
     ctx = Context(0, stream=stream.cuda_stream)
     if a.section in (None, "int8"):
-        bench_int8(ctx, stream, dev, a.iters, a.only)
+        bench_int8(ctx, stream, dev, a.iters, a.only, a.calibrate_int8)
     if a.section in (None, "conv1x1"):
         bench_conv1x1(ctx, stream, dev, a.iters, a.only)
     if a.section in (None, "int4_gemv"):
