@@ -120,6 +120,13 @@ int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact);
  * faster on every shape tried: the tensor pipe, not shared memory, bounds this GEMM. The
  * results are identical (integer arithmetic), only the speed differs. */
 int yscv_cuda_ctx_set_int8_cta_pairs(yscv_cuda_ctx *ctx, int enable);
+/* Second switch of the int8 GEMM, on by default: when the output tiles occupy at most half of
+ * the SMs and K >= 8192, the K loops are cut into equal runs over all CTAs and the int32 partial
+ * sums are added by the CTA that owns the tile (workspace of 128 KB per SM in the context,
+ * allocated by the first call that needs it; the waits on the partial sums are bounded and report
+ * status 2). Integer sums do not depend on the order, so the results are identical with the
+ * switch off; 0 keeps whole tiles per CTA. */
+int yscv_cuda_ctx_set_int8_tail_split(yscv_cuda_ctx *ctx, int enable);
 /* Per-kernel timing, the counterpart of YSCV_RUNNER_PROFILE
  * (crates/yscv-onnx/src/runner/profile.rs:1-120): while enabled, the dominant
  * kernel of every call is bracketed by CUDA events on the context's stream

@@ -318,3 +318,38 @@ def test_cta_pair_kernel_is_bit_identical(ctx, oracle, m, k, n):
     assert np.array_equal(outs[True][0][rows], oracle.requant_range(acc, 3e-4, 128.0, 0, 255).astype(np.uint8))
     pk.free()
     assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("m,k,n,splits", [(64, 11008, 4096, True), (300, 8200, 700, True),
+                                          (130, 16384, 1100, True), (2048, 4096, 4096, False)])
+def test_tail_split_is_bit_identical(ctx, oracle, m, k, n, splits):
+    """Shapes with far fewer tiles than SMs and K >= 8192 have their K loops cut over all CTAs and
+    their int32 partial sums added by the owning CTA: aligned, ragged M / N / K, more than two
+    parts per tile; config 3 keeps whole tiles. Outputs equal those of whole tiles per CTA and, on
+    a row sample, the oracle; repeated calls reuse the workspace under a new epoch."""
+    rng = np.random.default_rng(23)
+    a = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+    b = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    pk = ctx.pack_i8_b(b, k, n)
+    rq = ctx.requant(2e-4, 128.0, 0, 255, a_unsigned=True, a_zp=128)
+    outs = {}
+    try:
+        for split in (False, True, True):
+            ctx.set_int8_tail_split(split)
+            q = ctx.qlinear_matmul(a, pk, m, rq)
+            report = ctx.dispatch_report()
+            if not split:
+                assert "tail split" not in report
+            else:
+                assert ("tail split" in report) == splits, report
+            outs[split] = (q, ctx.matmul_integer(a, pk, m, a_zp=128))
+            if split:
+                assert np.array_equal(outs[False][0], q) and np.array_equal(outs[False][1], outs[True][1])
+    finally:
+        ctx.set_int8_tail_split(True)
+    rows = rng.choice(m, size=8, replace=False)
+    acc = oracle.int8_matmul((a[rows] ^ 0x80).view(np.int8), b, len(rows), k, n)
+    assert np.array_equal(outs[True][1][rows], acc)
+    assert np.array_equal(outs[True][0][rows], oracle.requant_range(acc, 2e-4, 128.0, 0, 255).astype(np.uint8))
+    pk.free()
+    assert ctx.device_status() == 0

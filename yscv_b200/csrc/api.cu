@@ -190,6 +190,8 @@ void yscv_cuda_ctx_destroy(yscv_cuda_ctx *ctx) {
     ctx->scratch_attn.release();
     ctx->rowsum.release();
     ctx->tmp_bt.release();
+    ctx->gemm_ws.release();
+    ctx->gemm_flags.release();
     ctx->tmp_colsum.release();
     if (ctx->d_status) cudaFree(ctx->d_status);
     for (auto &ev : ctx->prof_events) {
@@ -258,6 +260,12 @@ int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact) {
 int yscv_cuda_ctx_set_int8_cta_pairs(yscv_cuda_ctx *ctx, int enable) {
     if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
     ctx->int8_pairs = enable != 0;
+    return YSCV_CUDA_OK;
+}
+
+int yscv_cuda_ctx_set_int8_tail_split(yscv_cuda_ctx *ctx, int enable) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    ctx->int8_tail_split = enable != 0;
     return YSCV_CUDA_OK;
 }
 

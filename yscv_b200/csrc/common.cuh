@@ -115,9 +115,14 @@ struct yscv_cuda_ctx {
     yscv::DeviceBuffer scratch_attn;  // partial outputs of the split attention
     yscv::DeviceBuffer rowsum;        // row sums of A (int8 GEMM with a zero point on B)
     yscv::DeviceBuffer tmp_bt, tmp_colsum;  // B^T and column sums of the non-prepacked int8 entry point
+    // int8 GEMM with a split tail: one slot of partial sums per CTA, four flags per CTA; every
+    // launch that splits publishes a new epoch in the flags, so they are never reset
+    yscv::DeviceBuffer gemm_ws, gemm_flags;
+    int gemm_epoch = 0;
+    bool int8_tail_split = true;
     // variant / tile report of the last int4 and int8 dispatch (yscv_cuda_dispatch_report)
     char report_int4[160] = "none";
-    char report_int8[160] = "none";
+    char report_int8[224] = "none";
 };
 
 struct yscv_cuda_int4_weight {

@@ -13,16 +13,18 @@
 // prefill still fills the instruction and every weight tile is dequantised once per
 // NT*BT tokens.
 //
-// Kernel: persistent, 320 threads:
+// Kernel: persistent, 448 threads:
 //   warp 0      TMA producer: per 64-k block the packed nibbles [128 rows][32 B] and the
-//               bf16 activation tiles [BT tokens][64 k] (128-byte swizzle)
-//   warp 1      allocates TMEM, issues the MMAs (4 per block and token tile), commits
+//               bf16 activation tile [BT tokens][64 k] (128-byte swizzle)
+//   warp 1      allocates TMEM, issues the MMAs (4 per block, N = BT up to 256), commits
 //               stages, A buffers and finished accumulators
-//   warps 2-5   dequantise: thread r owns weight row r of the tile; 8 nibbles become four
-//               bf16x2 with 3 shifts + 4 lop3 (0x4300 | nibble^8 = 136 + q exactly), then
-//               subtract 136 and multiply by the group scale; one 16-byte store per word
+//   warps 2-9   dequantise: two threads per weight row of the tile, one per 32-k group
+//               (consecutive lanes read consecutive 16-byte pieces of the packed tile: no bank
+//               conflicts); 8 nibbles become four bf16x2 with 3 shifts + 4 lop3
+//               (0x4300 | nibble^8 = 136 + q exactly), then subtract 136 and multiply by the
+//               group scale, which was fetched one k block ahead; one 16-byte store per word
 //               into the swizzled A tile (double-buffered)
-//   warps 6-9   epilogue: tcgen05.ld, coalesced fp32 stores out[token][n]
+//   warps 10-13 epilogue: tcgen05.ld, coalesced fp32 stores out[token][n]
 // The nibble pairs come out as k = (0,4),(1,5),(2,6),(3,7) of each group of 8; the
 // activation pre-pass writes its bf16 copy in the same order, so no permutation is
 // needed in the loop. All mbarrier waits are bounded.
@@ -36,7 +38,8 @@ namespace yscv {
 
 constexpr int PG_BM = 128;      // weight rows per tile
 constexpr int PG_BK = 64;       // k per block: 64 bf16 = one 128-byte swizzle row
-constexpr int PG_THREADS = 320;
+constexpr int PG_THREADS = 448;
+constexpr int PG_DEQ_WARPS = 8;
 
 struct PGParams {
     int M, N, K;
@@ -135,7 +138,7 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
             mbar_init(bar_empty + i * 8, 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar_afull + i * 8, 4);    // one arrival per dequant warp
+            mbar_init(bar_afull + i * 8, PG_DEQ_WARPS);  // one arrival per dequant warp
             mbar_init(bar_aempty + i * 8, 1);
             mbar_init(bar_tfull + i * 8, 1);
             mbar_init(bar_tempty + i * 8, 4);   // one arrival per epilogue warp
@@ -211,32 +214,34 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                 if (++tbuf == 2) { tbuf = 0; tphase ^= 1u; }
             }
         }
-    } else if (warp < 6) {
-        // ---------------- dequantise: thread r = weight row r of the tile ----------------
-        const int r = (warp - 2) * 32 + lane;
+    } else if (warp < 2 + PG_DEQ_WARPS) {
+        // ------- dequantise: lanes 2i, 2i+1 share weight row (warp - 2) * 16 + i, one group each -------
+        const int r = (warp - 2) * 16 + (lane >> 1), half = lane & 1;
         const int groups = p.K / 32;
         int slot = 0, abuf = 0;
         uint32_t phase = 0, aphase = 0;
         bool alive = true;
+        const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
         for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
             const int nt_i = t % p.n_tiles;
             const int row = nt_i * PG_BM + r;
-            const float *srow = scales + (size_t)(row < p.N ? row : 0) * groups;
+            const float *srow = scales + (size_t)(row < p.N ? row : 0) * groups + half;
+            const bool live_row = row < p.N;
+            float sc_next = live_row ? __ldg(srow) : 0.0f;
             for (int kb = 0; kb < p.k_blocks; ++kb) {
+                const float sc = sc_next;
+                // the next block's scale travels while this block is converted
+                if (kb + 1 < p.k_blocks && live_row) sc_next = __ldg(srow + (kb + 1) * 2);
                 alive = mbar_wait(bar_full + slot * 8, phase, status) &&
                         mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
                 const unsigned char *st = smem + 2 * A_TILE + (size_t)slot * p.stage_bytes + act_bytes;
-                const uint4 w0 = *reinterpret_cast<const uint4 *>(st + r * 32);
-                const uint4 w1 = *reinterpret_cast<const uint4 *>(st + r * 32 + 16);
-                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                const float2 sc = (row < p.N) ? __ldg(reinterpret_cast<const float2 *>(srow + kb * 2))
-                                              : make_float2(0.0f, 0.0f);
-                const __nv_bfloat162 s0 = __float2bfloat162_rn(sc.x), s1 = __float2bfloat162_rn(sc.y);
-                const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
+                const uint4 w4 = *reinterpret_cast<const uint4 *>(st + r * 32 + half * 16);
+                const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+                const __nv_bfloat162 s = __float2bfloat162_rn(sc);
                 unsigned char *arow = smem + (size_t)abuf * A_TILE + (size_t)r * 128;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < 4; ++i) {
                     const uint32_t w = words[i];
                     uint32_t x[4];
                     // 0x4300 | (nibble ^ 8) is the bf16 value 136 + q, exactly
@@ -244,7 +249,6 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                     asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[1]) : "r"(w >> 4));
                     asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[2]) : "r"(w >> 8));
                     asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[3]) : "r"(w >> 12));
-                    const __nv_bfloat162 s = (i < 4) ? s0 : s1;
                     uint4 o;
                     uint32_t *ov = &o.x;
 #pragma unroll
@@ -253,8 +257,8 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                         v = __hmul2(__hsub2(v, bias), s);
                         ov[j] = *reinterpret_cast<uint32_t *>(&v);
                     }
-                    // 16-byte chunk i of row r sits at chunk i ^ (r & 7) (128-byte swizzle)
-                    *reinterpret_cast<uint4 *>(arow + ((i ^ (r & 7)) << 4)) = o;
+                    // 16-byte chunk c of row r sits at chunk c ^ (r & 7) (128-byte swizzle)
+                    *reinterpret_cast<uint4 *>(arow + (((half * 4 + i) ^ (r & 7)) << 4)) = o;
                 }
                 // make the generic-proxy writes visible to the tensor core's async proxy
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -265,7 +269,7 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
             }
         }
     } else {
-        // ---------------- epilogue: warps 6..9 own TMEM lanes 32*(warp%4).. ----------------
+        // ---------------- epilogue: warps 10..13 own TMEM lanes 32*(warp%4).. ----------------
         const int q = warp & 3;
         int tbuf = 0;
         uint32_t tphase = 0;
@@ -316,15 +320,10 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     p.M = (int)m;
     p.N = (int)n;
     p.K = (int)k;
-    // token tiling: up to 256 tokens per pass, as two MMA tiles of up to 128
+    // token tiling: up to 256 tokens per pass, one MMA tile (N = BT, a multiple of 16)
     const int m16 = (int)((m + 15) / 16 * 16);
-    if (m16 <= 128) {
-        p.BT = m16;
-        p.NT = 1;
-    } else {
-        p.BT = 128;
-        p.NT = 2;
-    }
+    p.BT = m16 <= 256 ? m16 : 256;
+    p.NT = 1;
     const int acc_cols = p.BT * p.NT;
     p.n_tiles = (p.N + PG_BM - 1) / PG_BM;
     p.t_chunks = (p.M + acc_cols - 1) / acc_cols;

@@ -58,7 +58,59 @@ struct G8Params {
     int b_zp;
     const int32_t *rowsum;  // row sums of A over k (only when b_zp != 0)
     int k_true;
+    // K split (one-CTA kernel, shapes with far fewer tiles than SMs and a long K): the K loops of
+    // the tiles from `tail_first` on are cut into runs of `tail_units` K blocks, one run per CTA,
+    // laid end to end over those tiles. The CTA that holds a tile's first K block owns the tile;
+    // the others leave their int32 partial sums in slot blockIdx.x of `ws` and publish `epoch`
+    // in ws_flag[4 * blockIdx.x + epilogue warp]. Integer addition is exact and commutative, so
+    // the result does not depend on the split. tail_first == tiles: no split.
+    int tail_first, tail_units;
+    int32_t *ws;
+    int *ws_flag;
+    int epoch;
 };
+
+// One piece of work of a CTA: K blocks [kb0, kb1) of output tile `tile`.
+struct G8Item {
+    int tile, kb0, kb1;
+};
+
+// The pieces of one CTA in the order every role walks them: its run of the split tiles (at most
+// one tile boundary inside a run, since a run is never longer than a tile's K loop), the part it
+// does not own first, then whole tiles.
+struct G8Walk {
+    int t, u, u1;
+    __device__ explicit G8Walk(const G8Params &p) {
+        const int tail_total = (p.m_blocks * p.n_blocks - p.tail_first) * p.k_blocks;
+        t = blockIdx.x;
+        u = min((int)blockIdx.x * p.tail_units, tail_total);
+        u1 = min(u + p.tail_units, tail_total);
+    }
+    __device__ bool next(const G8Params &p, G8Item &it) {
+        if (u < u1) {
+            const int tl = u / p.k_blocks, kb0 = u - tl * p.k_blocks;
+            const int n = min(u1 - u, p.k_blocks - kb0);
+            it.tile = p.tail_first + tl; it.kb0 = kb0; it.kb1 = kb0 + n;
+            u += n;
+            return true;
+        }
+        if (t < p.tail_first) {
+            it.tile = t; it.kb0 = 0; it.kb1 = p.k_blocks;
+            t += gridDim.x;
+            return true;
+        }
+        return false;
+    }
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int *p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int *p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ void tc_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -113,9 +165,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // Epilogue of one accumulator row: the thread owns output row `row`, whose BN int32 sums sit in
 // TMEM at `taddr` (this warp's lane group, the tile's first column); columns nb * BN ... of the
 // output. Subtracts the zero-point terms, then stores int32 or requantises and stores bytes.
+// [c_first, c_last]: CTAs whose partial sums of this tile (slots of p.ws, row `rt` of the tile) are
+// added first; empty range when the tile was not split.
 template <int BN>
 __device__ __forceinline__ void epilogue_row(const G8Params &p, const int32_t *__restrict__ colsum,
-                                             void *__restrict__ out, int row, uint32_t taddr, int nb) {
+                                             void *__restrict__ out, int row, uint32_t taddr, int nb,
+                                             int rt = 0, int c_first = 0, int c_last = -1) {
     const bool general = p.corr != nullptr || p.comp_pc != nullptr || p.relu != 0 || p.b_zp != 0;
     // 16-byte vector stores need a 16-byte aligned output (rows then stay aligned through
     // the pitch conditions below); anything else takes scalar stores
@@ -131,6 +186,23 @@ __device__ __forceinline__ void epilogue_row(const G8Params &p, const int32_t *_
         tmem_ld32(taddr + c0, r);
         const int col0 = nb * BN + c0;
         if (row < p.M && col0 < p.N) {
+            // partial sums: 16-byte piece (4 columns) j of row rt sits at piece index j * 128 + rt of
+            // the slot, so a warp reads 512 contiguous bytes; two slots are in flight at a time
+            for (int c = c_first; c <= c_last; c += 2) {
+                const bool two = c + 1 <= c_last;
+                const int4 *s0 = reinterpret_cast<const int4 *>(p.ws) + (size_t)c * (G8_BM * BN / 4) + (c0 / 4) * G8_BM + rt;
+                const int4 *s1 = s0 + (two ? G8_BM * BN / 4 : 0);
+                int4 v0[8], v1[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v0[j] = __ldcg(s0 + j * G8_BM);  // another CTA wrote them: L2, not L1
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v1[j] = two ? __ldcg(s1 + j * G8_BM) : make_int4(0, 0, 0, 0);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    r[4 * j] += (uint32_t)(v0[j].x + v1[j].x); r[4 * j + 1] += (uint32_t)(v0[j].y + v1[j].y);
+                    r[4 * j + 2] += (uint32_t)(v0[j].z + v1[j].z); r[4 * j + 3] += (uint32_t)(v0[j].w + v1[j].w);
+                }
+            }
             if (p.mode == 0) {
                 int32_t *o = reinterpret_cast<int32_t *>(out) + (size_t)row * p.ldc + col0;
                 if (col0 + 32 <= p.N && (p.ldc & 3) == 0 && out_vec_ok) {
@@ -194,6 +266,23 @@ __device__ __forceinline__ void epilogue_row(const G8Params &p, const int32_t *_
     }
 }
 
+// A non-owner's piece of a split tile: the raw int32 sums of row `rt` go to this CTA's slot.
+template <int BN>
+__device__ __forceinline__ void dump_row(const G8Params &p, int row, uint32_t taddr, int nb, int rt) {
+    int4 *dst = reinterpret_cast<int4 *>(p.ws) + (size_t)blockIdx.x * (G8_BM * BN / 4) + rt;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        if (row < p.M && nb * BN + c0 < p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                __stcg(dst + (c0 / 4 + j) * G8_BM,
+                       make_int4((int)r[4 * j], (int)r[4 * j + 1], (int)r[4 * j + 2], (int)r[4 * j + 3]));
+        }
+    }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(G8_THREADS, 1)
 int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -209,8 +298,6 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const uint32_t bar_full = bars, bar_empty = bars + 8 * 8;
     const uint32_t bar_tfull = bars + 16 * 8, bar_tempty = bars + 18 * 8;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)p.stages * STAGE_BYTES + 20 * 8);
-
-    const int tiles = p.m_blocks * p.n_blocks;
 
     if (tid == 0) {
         for (int i = 0; i < p.stages; ++i) {
@@ -243,9 +330,11 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             int slot = 0;
             uint32_t phase = 0;
             bool alive = true;
-            for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
-                const int mb = t % p.m_blocks, nb = t / p.m_blocks;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+            G8Walk walk(p);
+            G8Item it;
+            while (alive && walk.next(p, it)) {
+                const int mb = it.tile % p.m_blocks, nb = it.tile / p.m_blocks;
+                for (int kb = it.kb0; kb < it.kb1; ++kb) {
                     alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
                     if (!alive) break;
                     const uint32_t st = smem_base + (uint32_t)slot * STAGE_BYTES;
@@ -265,13 +354,15 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             int slot = 0, abuf = 0;
             uint32_t phase = 0, aphase = 0;
             bool alive = true;
-            for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+            G8Walk walk(p);
+            G8Item it;
+            while (alive && walk.next(p, it)) {
                 // the epilogue must have drained this accumulator buffer
                 alive = mbar_wait(bar_tempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)abuf * BN;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = it.kb0; kb < it.kb1; ++kb) {
                     alive = mbar_wait(bar_full + slot * 8, phase, status);
                     if (!alive) break;
                     tc_fence_after();
@@ -280,7 +371,7 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
                     for (int j = 0; j < G8_BK / 32; ++j)  // K = 32 per instruction: +32 bytes in the row
                         umma_i8(tacc, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc,
-                                (kb > 0 || j > 0) ? 1u : 0u);
+                                (kb > it.kb0 || j > 0) ? 1u : 0u);
                     umma_commit(bar_empty + slot * 8);  // stage free once these MMAs have read it
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
@@ -295,14 +386,42 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         int abuf = 0;
         uint32_t aphase = 0;
         bool alive = true;
-        for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
-            const int mb = t % p.m_blocks, nb = t / p.m_blocks;
+        G8Walk walk(p);
+        G8Item it;
+        while (alive && walk.next(p, it)) {
+            const int mb = it.tile % p.m_blocks, nb = it.tile / p.m_blocks;
             alive = mbar_wait(bar_tfull + abuf * 8, aphase, status);
             if (!alive) break;
             tc_fence_after();
-            const int row = mb * G8_BM + q * 32 + lane;
+            const int rt = q * 32 + lane;
+            const int row = mb * G8_BM + rt;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)abuf * BN;
-            epilogue_row<BN>(p, colsum, out, row, taddr, nb);
+            if (it.kb0 > 0) {
+                // a later part of a split tile: leave the partial sums for the tile's owner
+                dump_row<BN>(p, row, taddr, nb, rt);
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) st_release_gpu(p.ws_flag + 4 * blockIdx.x + q, p.epoch);
+            } else if (it.kb1 < p.k_blocks) {
+                // the first part of a split tile: this CTA owns it. The other parts belong to the
+                // CTAs that follow, which compute them at the start of their runs; wait (bounded)
+                // for the same warp of each, whose threads wrote the rows this warp reads.
+                const int u_end = (it.tile - p.tail_first + 1) * p.k_blocks - 1;
+                const int c_first = (int)blockIdx.x + 1, c_last = u_end / p.tail_units;
+                for (int c = c_first; c <= c_last && alive; ++c) {
+                    const int *f = p.ws_flag + 4 * c + q;
+                    bool seen = false;
+                    for (uint32_t i = 0; i < (1u << 22) && !seen; ++i) seen = ld_acquire_gpu(f) == p.epoch;
+                    if (!seen) {
+                        atomicExch(status, 2 /* YSCV_DEV_FLAG_TIMEOUT */);
+                        alive = false;
+                    }
+                }
+                alive = __all_sync(0xffffffffu, alive);
+                if (alive) epilogue_row<BN>(p, colsum, out, row, taddr, nb, rt, c_first, c_last);
+            } else {
+                epilogue_row<BN>(p, colsum, out, row, taddr, nb);
+            }
             // all columns of this buffer have been read: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
@@ -632,11 +751,40 @@ static int launch_g8(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const yscv
     rc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
     if (rc) return rc;
     const int tiles = p.m_blocks * p.n_blocks;
-    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    const int sms = ctx->sm_count;
+    int grid = tiles < sms ? tiles : sms;
+    p.tail_first = tiles;
+    p.tail_units = 0;
+    // Fewer tiles than half the SMs and a long K loop: cut the K loops into equal runs over all
+    // CTAs (see G8Params). The owners' fix-up costs about 4 us at the end of the kernel, which
+    // only K >= 8192 on a mostly idle machine pays back (64 x 11008 x 4096: 30.8 -> 22.6 us);
+    // with full waves of tiles the extra L2 traffic of the partial sums made every shape tried
+    // slower (config 3: 34.9 -> 41.1 us), so those keep whole tiles per CTA.
+    const int tail = tiles % sms;
+    const long long tail_blocks = (long long)tail * p.k_blocks;
+    if (ctx->int8_tail_split && tiles < sms && tail * 2 <= sms && p.k_blocks >= 64) {
+        int units = (int)((tail_blocks + sms - 1) / sms);
+        if (units < 4) units = 4;  // at most k_blocks / 4 + 1 parts per tile
+        const int ctas = (int)((tail_blocks + units - 1) / units);
+        rc = ctx->gemm_ws.reserve((size_t)sms * G8_BM * 256 * sizeof(int32_t));
+        if (rc) return rc;
+        if (!ctx->gemm_flags.ptr) {
+            rc = ctx->gemm_flags.reserve((size_t)sms * 4 * sizeof(int));
+            if (rc) return rc;
+            YSCV_CUDA_TRY(cudaMemsetAsync(ctx->gemm_flags.ptr, 0, (size_t)sms * 4 * sizeof(int), ctx->stream));
+        }
+        p.tail_first = tiles - tail;
+        p.tail_units = units;
+        p.ws = reinterpret_cast<int32_t *>(ctx->gemm_ws.ptr);
+        p.ws_flag = reinterpret_cast<int *>(ctx->gemm_flags.ptr);
+        p.epoch = ++ctx->gemm_epoch;
+        grid = p.tail_first > 0 ? sms : ctas;
+    }
     snprintf(ctx->report_int8, sizeof(ctx->report_int8),
-             "int8_gemm_tc m=%d n=%d k=%d: tcgen05 kind::i8, CTA tile %dx%d, %d stages of %d KB, %d tiles on %d CTAs, %s",
+             "int8_gemm_tc m=%d n=%d k=%d: tcgen05 kind::i8, CTA tile %dx%d, %d stages of %d KB, %d tiles on %d CTAs"
+             "%s, %s",
              p.M, p.N, p.K, G8_BM, BN, p.stages, stage_bytes / 1024, tiles, grid,
-             p.mode == 0 ? "int32 out" : "requantised bytes out");
+             p.tail_units ? " (tail split along K)" : "", p.mode == 0 ? "int32 out" : "requantised bytes out");
     ctx->prof_begin();
     kern<<<grid, G8_THREADS, smem, ctx->stream>>>(tm_a, tm_b, b->d_colsum, d_out, p, ctx->d_status);
     ctx->prof_end();

@@ -42,6 +42,7 @@ SIGNATURES = {
     "yscv_cuda_ctx_launch_count": (C.c_uint64, [_vp]),
     "yscv_cuda_ctx_set_int4_prefill_exact": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_set_int8_cta_pairs": (C.c_int, [_vp, C.c_int]),
+    "yscv_cuda_ctx_set_int8_tail_split": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_enable": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_read": (C.c_int, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "yscv_cuda_int4_matmul": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
@@ -486,6 +487,10 @@ class Context:
     def set_int8_cta_pairs(self, on: bool):
         """int8 GEMM: allow the CTA-pair kernel (cta_group::2) or keep the one-CTA kernel everywhere (default)."""
         _check(self.lib.yscv_cuda_ctx_set_int8_cta_pairs(self.handle, int(on)))
+
+    def set_int8_tail_split(self, on: bool):
+        """int8 GEMM: cut the K loops of the tiles beyond the last full wave over all CTAs (default) or not."""
+        _check(self.lib.yscv_cuda_ctx_set_int8_tail_split(self.handle, int(on)))
 
     def profile_enable(self, on: bool):
         _check(self.lib.yscv_cuda_ctx_profile_enable(self.handle, int(on)))
