@@ -1205,7 +1205,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         for (int row = v0 + warp; row < v1; row += DS_CONSUMER_WARPS) {
             const float4 *wr = reinterpret_cast<const float4 *>(p.lm_head + (size_t)(row - p.lm_row0) * H);
             float acc = 0.0f;
-#pragma unroll 4
+            // eight 16-byte loads in flight per lane (64 KB per SM): the row streams at the HBM
+            // rate; the additions keep their order
+#pragma unroll 8
             for (int cidx = lane; cidx < H / 4; cidx += 32) {
                 const float4 wv = __ldg(wr + cidx), xv = x4[cidx];
                 acc = fmaf(wv.x, xv.x, acc);
