@@ -485,8 +485,10 @@ typedef struct yscv_cuda_decode_layer {
     const yscv_cuda_int4_weight *down;     /* [hidden][inter] */
     const float *d_gamma_attn;             /* [hidden] */
     const float *d_gamma_mlp;              /* [hidden] */
-    float *d_kcache;                       /* [max_seq][n_kv][d_head], f32 */
-    float *d_vcache;
+    void *d_kcache;                        /* [max_seq][n_kv][d_head]: f32, or int8 with options.kv_int8 */
+    void *d_vcache;
+    float *d_kscale;                       /* int8 caches only: [max_seq] f32, one scale per cached row */
+    float *d_vscale;
 } yscv_cuda_decode_layer;
 
 int yscv_cuda_decode_plan_create(yscv_cuda_ctx *ctx, const yscv_cuda_decode_layer *layers,
@@ -532,6 +534,10 @@ typedef struct yscv_cuda_decode_options {
                            for another CTA or another GPU gives up */
     const yscv_cuda_tp_comm *tp; /* NULL: one GPU. Else this rank's connected group; the layer
                                     weights and n_q, n_kv, inter are then the rank's shards */
+    int kv_int8;        /* 0: f32 caches. 1: the caches are KvDtype::I8 as yscv_cuda_rope_kv_append_i8_dev
+                           writes them (int8 rows of n_kv * d_head with one f32 scale per row in
+                           d_kscale / d_vscale); d_head must be 64 or 128. Under tensor parallelism a
+                           row is this rank's KV heads only, so its scale differs from the one-GPU one */
 } yscv_cuda_decode_options;
 int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cuda_decode_layer *layers,
                                     size_t n_layers, size_t hidden, size_t inter, size_t n_q,

@@ -147,7 +147,7 @@ def export_weights(dec):
 
 
 def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logit_tol, exact_prefill=True,
-               fused_step=True, kv_int8=False):
+               fused_step=True, kv_int8=False, plan_options=None):
     """exact_prefill: the prompt pass uses the fp32-exact int4 kernel (tokens must then match the
     oracle except at rounding-level ties); otherwise the bf16 tensor-core GEMM, whose logits
     may differ by up to 2e-2 (relative Frobenius) and whose tokens may differ only where the
@@ -162,8 +162,8 @@ def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logi
         # last bits: the logits then agree to that step's share, not to fp32 rounding
         flip_margin = 1e-2
     dec = Int4Decoder.with_full_weights(ctx, cfg, batch, prompt_len + steps + 1, s, seed=seed, layers=n_layers,
-                                        fused_step=fused_step, kv_int8=kv_int8)
-    assert (dec.plan is not None) == (fused_step and batch == 1 and not kv_int8)
+                                        fused_step=fused_step, kv_int8=kv_int8, plan_options=plan_options)
+    assert (dec.plan is not None) == (fused_step and batch == 1)
     from oracle_decoder import OracleDecoder
     ref = OracleDecoder(oracle, cfg, n_layers, export_weights(dec), dec.embedding.cpu().numpy(),
                         dec.lm_head.cpu().numpy(), batch, kv_int8=kv_int8)
@@ -457,8 +457,58 @@ def test_int8_kv_cache_matches_oracle(tctx, oracle):
     cfg = DecoderConfig(layers=3, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
     run_parity(tctx, oracle, cfg, 3, batch=3, prompt_len=20, steps=10, seed=6, logit_tol=2e-3, kv_int8=True)
     cfg = DecoderConfig(layers=2, hidden=1024, mlp=2048, n_q=8, n_kv=2, head_dim=128, vocab=1500)
-    run_parity(tctx, oracle, cfg, 2, batch=1, prompt_len=150, steps=6, seed=7, logit_tol=2e-3, kv_int8=True)
+    run_parity(tctx, oracle, cfg, 2, batch=1, prompt_len=150, steps=6, seed=7, logit_tol=2e-3, kv_int8=True,
+               fused_step=False)
     ctx, _ = tctx
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("form", [0, 1])
+def test_int8_kv_cache_fused_step_matches_oracle(tctx, oracle, form):
+    """The one-launch step over KvDtype::I8 caches: the step kernel quantises the new position's
+    key and value rows (one scale over every KV head of the row) and dequantises the cached rows
+    in both of its attention forms (CTAs per query head; CTAs per KV head and key chunk plus a
+    merge), head sizes 64 and 128, against the oracle decoder with the same cache format. The
+    cache bytes the kernel appended are compared with the oracle's rows as well."""
+    opts = dict(attention_form=form)
+    cfg = DecoderConfig(layers=3, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
+    run_parity(tctx, oracle, cfg, 3, batch=1, prompt_len=20, steps=10, seed=8, logit_tol=2e-3, kv_int8=True,
+               plan_options=opts)
+    cfg = DecoderConfig(layers=2, hidden=1024, mlp=2048, n_q=8, n_kv=2, head_dim=128, vocab=1500)
+    run_parity(tctx, oracle, cfg, 2, batch=1, prompt_len=150, steps=6, seed=7, logit_tol=2e-3, kv_int8=True,
+               plan_options=opts)
+    ctx, _ = tctx
+    assert ctx.device_status() == 0
+
+
+def test_int8_kv_cache_fused_step_appends_the_same_rows_as_the_chain(tctx):
+    """After the same prompt and the same decode steps the int8 caches and their scales written
+    by the one-launch step equal those written by the operator chain, except where a value
+    sits on a rounding boundary of its row's grid (at most one step apart, in a handful of
+    places)."""
+    import torch
+    ctx, s = tctx
+    cfg = DecoderConfig(layers=2, hidden=1024, mlp=2048, n_q=8, n_kv=2, head_dim=128, vocab=1500)
+    prompt = dev(synth.uniform_int(5, 9, 40, 0, cfg.vocab - 1).astype(np.int32).reshape(1, -1))
+    caches = {}
+    ctx.set_int4_prefill_exact(True)
+    try:
+        for fused in (False, True):
+            dec = Int4Decoder(ctx, cfg, 1, 64, s, seed=11, fused_step=fused, kv_int8=True)
+            assert (dec.plan is not None) == fused
+            dec.prefill(prompt)
+            toks = dec.decode(8)
+            s.synchronize()
+            caches[fused] = ([c[0, :48].cpu().numpy().astype(np.int32) for c in dec.kcache + dec.vcache],
+                             [c[0, :48].cpu().numpy() for c in dec.kscale + dec.vscale], toks.cpu().numpy())
+            dec.close()
+    finally:
+        ctx.set_int4_prefill_exact(False)
+    assert np.array_equal(caches[False][2], caches[True][2])
+    for a, b in zip(caches[False][0], caches[True][0]):
+        assert np.abs(a - b).max() <= 1 and np.count_nonzero(a != b) <= a.size // 200
+    for a, b in zip(caches[False][1], caches[True][1]):
+        assert np.allclose(a, b, rtol=1e-5, atol=0)
     assert ctx.device_status() == 0
 
 

@@ -61,8 +61,9 @@ struct alignas(64) StepMat {
 struct StepParams {
     const StepMat *mats;      // [layers][4]: qkv, output, gate+up, down
     const float *gamma;       // [layers][2][hidden]
-    float *const *kcache;     // [layers] -> [max_seq][n_kv][d_head]
-    float *const *vcache;
+    float *const *kcache;     // [layers] -> [max_seq][n_kv][d_head] (f32, or int8 when kv_int8), then
+    float *const *vcache;     // (int8 only) [layers] -> [max_seq] f32 row scales
+    int kv_int8;
     const float *embedding;   // [vocab][hidden]
     const int32_t *token;
     const int32_t *pos;
@@ -810,6 +811,383 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
     cons_sync();  // scratch is reused
 }
 
+// ---- int8 KV cache (KvDtype::I8 of the reference, crates/yscv-onnx/src/runner/kv_cache.rs:44-90) ----
+//
+// A cached row is one token's n_kv * d_head keys (or values) of one layer as int8 with ONE f32
+// scale: scale = abs_max / 127 (1.0 when abs_max <= f32::EPSILON), q = clamp(round_half_away(v *
+// (1 / scale)), -127, 127), read back as (float)q * scale: the arithmetic of
+// rope_kv_append_kernel<int8_t>. The scale spans every KV head, so a CTA that needs the new
+// position's key or value rotates / fetches the whole row, whichever head it works on.
+
+__device__ __forceinline__ float4 s8x4_to_f4(uint32_t w) {
+    return make_float4((float)(int8_t)(w & 255u), (float)(int8_t)((w >> 8) & 255u),
+                       (float)(int8_t)((w >> 16) & 255u), (float)(int8_t)(w >> 24));
+}
+
+// Quantises `tmp[0 .. W)` (shared memory) as one cache row. Leaves the dequantised values of KV
+// head kvh in cur[d]; write == true also stores the row at position pos and its scale.
+__device__ __forceinline__ void quantise_row_i8(const StepParams &p, const float *tmp, float amax, int kvh, int pos,
+                                                int8_t *cache, float *scales, float *cur, bool write, float *misc) {
+    const int tid = threadIdx.x, d = p.d_head, W = p.n_kv * d;
+    amax = cons_max(amax, misc);   // (its barriers also publish tmp)
+    const float scale = (amax <= 1.1920929e-07f) ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float inv = __fdiv_rn(1.0f, scale);
+    for (int i = tid; i < W; i += DS_CONSUMERS) {
+        const float x = __fmul_rn(tmp[i], inv);
+        // NaN -> 0, as Rust's saturating float-to-int cast does
+        const int q = (x != x) ? 0 : (int)fminf(fmaxf(roundf(x), -127.0f), 127.0f);
+        if (write) cache[(size_t)pos * W + i] = (int8_t)q;
+        if (i / d == kvh) cur[i - kvh * d] = (float)q * scale;
+    }
+    if (write && tid == 0) scales[pos] = scale;
+    cons_sync();   // tmp is reused, cur is complete
+}
+
+// The new position's key and value rows: RoPE of every KV head's key, both rows quantised;
+// kcur / vcur receive what a reader of the cache would see for KV head kvh.
+__device__ __forceinline__ void append_rows_i8(const StepParams &p, int kvh, int pos, int8_t *kc8, float *ksc,
+                                               int8_t *vc8, float *vsc, const float *rope_cs, float *tmp,
+                                               float *misc, float *kcur, float *vcur, bool write) {
+    const int tid = threadIdx.x, d = p.d_head, half = d / 2, W = p.n_kv * d;
+    float amax = 0.0f;
+    for (int i = tid; i < p.n_kv * half; i += DS_CONSUMERS) {
+        const int hh = i / half, ri = i - hh * half;
+        const float *src = p.qkv + (size_t)(p.n_q + hh) * d;
+        const float x0 = __ldcg(src + ri), x1 = __ldcg(src + ri + half);
+        const float cs = rope_cs[2 * ri], sn = rope_cs[2 * ri + 1];
+        const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
+        tmp[hh * d + ri] = y0;
+        tmp[hh * d + ri + half] = y1;
+        amax = fmaxf(amax, fmaxf(fabsf(y0), fabsf(y1)));
+    }
+    quantise_row_i8(p, tmp, amax, kvh, pos, kc8, ksc, kcur, write, misc);
+    amax = 0.0f;
+    for (int i = tid; i < W; i += DS_CONSUMERS) {
+        const float v = __ldcg(p.qkv + (size_t)(p.n_q + p.n_kv) * d + i);
+        tmp[i] = v;
+        amax = fmaxf(amax, fabsf(v));
+    }
+    quantise_row_i8(p, tmp, amax, kvh, pos, vc8, vsc, vcur, write, misc);
+}
+
+// attention_head over an int8 cache. d_head is 64 or 128 (a quarter row is 16 or 32 bytes).
+template <int VB>
+__device__ __forceinline__ void attention_head_i8(const StepParams &p, int h, int split, int pos, int8_t *kc8,
+                                                  float *ksc, int8_t *vc8, float *vsc, const float *rope_cs,
+                                                  float *scratch, float *misc) {
+    const int tid = threadIdx.x;
+    const int d = p.d_head, half = d / 2;
+    const int grp = p.n_q / p.n_kv, kvh = h / grp;
+    float *qs = scratch, *kcur = qs + d, *vcur = kcur + d, *partial = vcur + d;  // partial: [512/(d/4)][d]
+    float *scores = partial + 4 * DS_CONSUMERS;                                  // [max_seq]
+    const size_t kv_stride = (size_t)p.n_kv * d;   // bytes per cached row
+    const int8_t *kbase = kc8 + (size_t)kvh * d, *vbase = vc8 + (size_t)kvh * d;
+    const int limit = pos + 1;
+    const int chunk = (limit + p.splits - 1) / p.splits;
+    const int k0 = split * chunk, k1 = min(limit, k0 + chunk);
+    float *po = p.attn + ((size_t)h * p.splits + split) * (d + 2);
+    if (k0 >= k1) {
+        for (int i = tid; i < d; i += DS_CONSUMERS) po[i] = 0.0f;
+        if (tid == 0) { po[d] = -INFINITY; po[d + 1] = 0.0f; }
+        return;
+    }
+    const bool has_new = (pos >= k0 && pos < k1);
+    const int nk = k1 - k0;
+    const int kq = tid >> 2, sub = tid & 3, n16 = d / 64;   // 4 threads per key row, 16-byte pieces per quarter
+    const int vec = d / 4, nparts = DS_CONSUMERS / vec, part = tid / vec, c4 = tid % vec;
+    // first pass of keys: loads in flight before anything else
+    uint4 k8[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+    float kscl = 0.0f;
+    if (kq < nk && k0 + kq != pos) {
+        const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)(k0 + kq) * kv_stride + sub * (d / 4));
+        k8[0] = __ldg(kr);
+        if (n16 > 1) k8[1] = __ldg(kr + 1);
+        kscl = __ldg(ksc + k0 + kq);
+    }
+    // the head's query, rotated
+    if (tid < half) {
+        const float *src = p.qkv + (size_t)h * d;
+        const float x0 = __ldcg(src + tid), x1 = __ldcg(src + tid + half);
+        const float cs = rope_cs[2 * tid], sn = rope_cs[2 * tid + 1];
+        qs[tid] = x0 * cs - x1 * sn;
+        qs[tid + half] = x0 * sn + x1 * cs;
+    }
+    if (has_new)   // (the same for every thread of the CTA) the first head's CTA stores the rows
+        append_rows_i8(p, kvh, pos, kc8, ksc, vc8, vsc, rope_cs, partial, misc, kcur, vcur, h == 0);
+    else
+        cons_sync();
+
+    // ---- scores ----
+    const float scale = 1.0f / sqrtf((float)d);
+    const float4 *q4 = reinterpret_cast<const float4 *>(qs + sub * (d / 4));
+    auto quarter_dot8 = [&](const uint4 (&kv)[2], float rs) {
+        float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (j < n16) {
+                const uint32_t w[4] = {kv[j].x, kv[j].y, kv[j].z, kv[j].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 kf = s8x4_to_f4(w[i]), qv = q4[j * 4 + i];
+                    d0 = fmaf(qv.x, kf.x, d0);
+                    d1 = fmaf(qv.y, kf.y, d1);
+                    d2 = fmaf(qv.z, kf.z, d2);
+                    d3 = fmaf(qv.w, kf.w, d3);
+                }
+            }
+        }
+        return ((d0 + d1) + (d2 + d3)) * rs;
+    };
+    float mx = -INFINITY;
+    for (int kk = kq, pass = 0; kk < ((nk + 127) & ~127); kk += DS_CONSUMERS / 4, ++pass) {
+        const int key = k0 + kk;
+        float dot = 0.0f;
+        if (kk < nk) {
+            if (key == pos) {
+                const float4 *kc4 = reinterpret_cast<const float4 *>(kcur + sub * (d / 4));
+                float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+                for (int j = 0; j < d / 16; ++j) {
+                    const float4 qv = q4[j], kf = kc4[j];
+                    d0 = fmaf(qv.x, kf.x, d0);
+                    d1 = fmaf(qv.y, kf.y, d1);
+                    d2 = fmaf(qv.z, kf.z, d2);
+                    d3 = fmaf(qv.w, kf.w, d3);
+                }
+                dot = (d0 + d1) + (d2 + d3);
+            } else {
+                if (pass > 0) {
+                    const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)key * kv_stride + sub * (d / 4));
+                    k8[0] = __ldg(kr);
+                    if (n16 > 1) k8[1] = __ldg(kr + 1);
+                    kscl = __ldg(ksc + key);
+                }
+                dot = quarter_dot8(k8, kscl);
+            }
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        if (kk < nk) {
+            const float sc = dot * scale;
+            if (sub == 0) scores[kk] = sc;
+            mx = fmaxf(mx, sc);
+        }
+    }
+    mx = cons_max(mx, misc);
+    float se = 0.0f;
+    for (int kk = tid; kk < nk; kk += DS_CONSUMERS) {
+        const float e = expf(scores[kk] - mx);
+        scores[kk] = e;
+        se += e;
+    }
+    se = cons_sum(se, misc);  // (its barriers also publish `scores`)
+
+    // ---- weighted V: d/4 threads per key row (4 bytes each), keys dealt round-robin to the parts ----
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float4 vcur4 = *(reinterpret_cast<const float4 *>(vcur) + c4);
+    for (int kb = part; kb < nk; kb += VB * nparts) {
+        uint32_t v[VB];
+        float vs[VB];
+#pragma unroll
+        for (int j = 0; j < VB; ++j) {
+            const int kk = kb + j * nparts;
+            const bool on = kk < nk && k0 + kk != pos;
+            v[j] = on ? __ldg(reinterpret_cast<const uint32_t *>(vbase + (size_t)(k0 + kk) * kv_stride) + c4) : 0u;
+            vs[j] = on ? __ldg(vsc + k0 + kk) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < VB; ++j) {
+            const int kk = kb + j * nparts;
+            if (kk < nk) {
+                const bool is_new = k0 + kk == pos;
+                const float4 vf = is_new ? vcur4 : s8x4_to_f4(v[j]);
+                const float w = scores[kk] * (is_new ? 1.0f : vs[j]);
+                acc.x = fmaf(w, vf.x, acc.x);
+                acc.y = fmaf(w, vf.y, acc.y);
+                acc.z = fmaf(w, vf.z, acc.z);
+                acc.w = fmaf(w, vf.w, acc.w);
+            }
+        }
+    }
+    *(reinterpret_cast<float4 *>(partial + (size_t)part * d) + c4) = acc;
+    cons_sync();
+    if (tid < d) {
+        float v = 0.0f;
+        for (int pt = 0; pt < nparts; ++pt) v += partial[pt * d + tid];
+        po[tid] = v;
+    }
+    if (tid == 0) { po[d] = mx; po[d + 1] = se; }
+    cons_sync();  // scratch is reused
+}
+
+// attention_group (phase 1 of the grouped form) over an int8 cache.
+__device__ __forceinline__ void attention_group_i8(const StepParams &p, int kvh, int split, int pos, int8_t *kc8,
+                                                   float *ksc, int8_t *vc8, float *vsc, const float *rope_cs,
+                                                   float *scratch, float *misc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int d = p.d_head, half = d / 2;
+    const int grp = p.n_q / p.n_kv, S = p.g_splits, cap = p.g_chunk_cap;
+    const int vecs = d / 4, parts = DS_CONSUMERS / (grp * vecs);
+    float *qs = scratch, *kcur = qs + grp * d, *vcur = kcur + d, *partial = vcur + d;
+    float *wred = partial + parts * grp * d, *scores = wred + 32;
+    const size_t kv_stride = (size_t)p.n_kv * d;
+    const int8_t *kbase = kc8 + (size_t)kvh * d, *vbase = vc8 + (size_t)kvh * d;
+    const int limit = pos + 1;
+    const int chunk = (limit + S - 1) / S;
+    const int k0 = split * chunk, k1 = min(limit, k0 + chunk);
+    const int h0 = kvh * grp;
+    if (k0 >= k1) {
+        for (int i = tid; i < grp * (d + 2); i += DS_CONSUMERS) {
+            const int hh = i / (d + 2), j = i - hh * (d + 2);
+            p.attn[((size_t)(h0 + hh) * S + split) * (d + 2) + j] = j == d ? -INFINITY : 0.0f;
+        }
+        return;
+    }
+    const int nk = k1 - k0;
+    const bool has_new = pos >= k0 && pos < k1;
+    const int kq = tid >> 2, sub = tid & 3, n16 = d / 64;
+    uint4 k8[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+    float kscl = 0.0f;
+    if (kq < nk && k0 + kq != pos) {
+        const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)(k0 + kq) * kv_stride + sub * (d / 4));
+        k8[0] = __ldg(kr);
+        if (n16 > 1) k8[1] = __ldg(kr + 1);
+        kscl = __ldg(ksc + k0 + kq);
+    }
+    // the group's queries, rotated
+    for (int i = tid; i < grp * half; i += DS_CONSUMERS) {
+        const int hh = i / half, ri = i - hh * half;
+        const float *src = p.qkv + (size_t)(h0 + hh) * d;
+        const float x0 = __ldcg(src + ri), x1 = __ldcg(src + ri + half);
+        const float cs = rope_cs[2 * ri], sn = rope_cs[2 * ri + 1];
+        qs[hh * d + ri] = x0 * cs - x1 * sn;
+        qs[hh * d + ri + half] = x0 * sn + x1 * cs;
+    }
+    if (has_new)   // the first KV head's CTA stores the rows
+        append_rows_i8(p, kvh, pos, kc8, ksc, vc8, vsc, rope_cs, partial, misc, kcur, vcur, kvh == 0);
+    else
+        cons_sync();
+
+    // ---- scores: four threads per key; the quarter row in registers serves every query head ----
+    const float scale = 1.0f / sqrtf((float)d);
+    for (int kk = kq, pass = 0; kk < ((nk + 127) & ~127); kk += DS_CONSUMERS / 4, ++pass) {
+        const int key = k0 + kk;
+        const bool is_new = key == pos;
+        float4 kf[8];   // the quarter row as floats (d/16 <= 8 float4)
+        float rs = 1.0f;
+        if (kk < nk) {
+            if (is_new) {
+                const float4 *kc4 = reinterpret_cast<const float4 *>(kcur + sub * (d / 4));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) kf[j] = j < d / 16 ? kc4[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            } else {
+                if (pass > 0) {
+                    const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)key * kv_stride + sub * (d / 4));
+                    k8[0] = __ldg(kr);
+                    if (n16 > 1) k8[1] = __ldg(kr + 1);
+                    kscl = __ldg(ksc + key);
+                }
+                rs = kscl;
+                const uint32_t w[8] = {k8[0].x, k8[0].y, k8[0].z, k8[0].w, k8[1].x, k8[1].y, k8[1].z, k8[1].w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) kf[j] = s8x4_to_f4(w[j]);   // (zeros past the quarter)
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) kf[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        for (int hh = 0; hh < grp; ++hh) {
+            const float4 *q4 = reinterpret_cast<const float4 *>(qs + hh * d + sub * (d / 4));
+            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < d / 16) {
+                    const float4 qv = q4[j];
+                    d0 = fmaf(qv.x, kf[j].x, d0);
+                    d1 = fmaf(qv.y, kf[j].y, d1);
+                    d2 = fmaf(qv.z, kf[j].z, d2);
+                    d3 = fmaf(qv.w, kf[j].w, d3);
+                }
+            }
+            float dot = ((d0 + d1) + (d2 + d3)) * rs;
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            if (kk < nk && sub == 0) scores[hh * cap + kk] = dot * scale;
+        }
+    }
+    cons_sync();
+
+    // ---- softmax per head: 16 / grp warps per head ----
+    const int wph = DS_CONSUMER_WARPS / grp, hh_w = warp / wph, wi = warp - hh_w * wph;
+    float *sc = scores + hh_w * cap;
+    float mx = -INFINITY;
+    for (int kk = wi * 32 + lane; kk < nk; kk += wph * 32) mx = fmaxf(mx, sc[kk]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) wred[warp] = mx;
+    cons_sync();
+    mx = -INFINITY;
+    for (int i = 0; i < wph; ++i) mx = fmaxf(mx, wred[hh_w * wph + i]);
+    cons_sync();
+    float se = 0.0f;
+    for (int kk = wi * 32 + lane; kk < nk; kk += wph * 32) {
+        const float e = expf(sc[kk] - mx);
+        sc[kk] = e;
+        se += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+    if (lane == 0) wred[warp] = se;
+    cons_sync();
+    if (wi == 0 && lane == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < wph; ++i) t += wred[hh_w * wph + i];
+        float *po = p.attn + ((size_t)(h0 + hh_w) * S + split) * (d + 2);
+        po[d] = mx;
+        po[d + 1] = t;
+    }
+
+    // ---- weighted values: thread (part, head, 4 columns) ----
+    const int c4 = tid % vecs, hv = (tid / vecs) % grp, part = tid / (vecs * grp);
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (part < parts) {
+        const float *w = scores + hv * cap;
+        const float4 vcur4 = *(reinterpret_cast<const float4 *>(vcur) + c4);
+        for (int kb = part; kb < nk; kb += 8 * parts) {
+            uint32_t v[8];
+            float vs[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int kk = kb + j * parts;
+                const bool on = kk < nk && k0 + kk != pos;
+                v[j] = on ? __ldg(reinterpret_cast<const uint32_t *>(vbase + (size_t)(k0 + kk) * kv_stride) + c4) : 0u;
+                vs[j] = on ? __ldg(vsc + k0 + kk) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int kk = kb + j * parts;
+                if (kk < nk) {
+                    const bool is_new = k0 + kk == pos;
+                    const float4 vf = is_new ? vcur4 : s8x4_to_f4(v[j]);
+                    const float ww = w[kk] * (is_new ? 1.0f : vs[j]);
+                    acc.x = fmaf(ww, vf.x, acc.x);
+                    acc.y = fmaf(ww, vf.y, acc.y);
+                    acc.z = fmaf(ww, vf.z, acc.z);
+                    acc.w = fmaf(ww, vf.w, acc.w);
+                }
+            }
+        }
+        *(reinterpret_cast<float4 *>(partial + ((size_t)part * grp + hv) * d) + c4) = acc;
+    }
+    cons_sync();
+    for (int i = tid; i < grp * d; i += DS_CONSUMERS) {
+        const int hh = i / d, dd = i - hh * d;
+        float v = 0.0f;
+        for (int pt = 0; pt < parts; ++pt) v += partial[((size_t)pt * grp + hh) * d + dd];
+        p.attn[((size_t)(h0 + hh) * S + split) * (d + 2) + dd] = v;
+    }
+    cons_sync();  // scratch is reused
+}
+
 // SIMPLE: every matrix is one row block and one K chunk per CTA and attention runs per query
 // head (small models, short contexts); the loops over blocks and chunks then fold away at
 // compile time, which is worth 7 % of a TinyLlama step.
@@ -1172,14 +1550,27 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
         // RoPE, cache append, attention: a few CTAs per query head, or (long contexts) one CTA
         // per KV head and key chunk followed by a merge phase
         if (!SIMPLE && p.attn_grouped) {
-            if ((int)blockIdx.x < p.n_kv * p.g_splits)
-                attention_group(p, blockIdx.x / p.g_splits, blockIdx.x % p.g_splits, pos, cache_ptr[2 * l],
-                                cache_ptr[2 * l + 1], rope_cs, act_s);
+            if ((int)blockIdx.x < p.n_kv * p.g_splits) {
+                if (p.kv_int8)
+                    attention_group_i8(p, blockIdx.x / p.g_splits, blockIdx.x % p.g_splits, pos,
+                                       reinterpret_cast<int8_t *>(cache_ptr[2 * l]), p.kcache[p.layers + l],
+                                       reinterpret_cast<int8_t *>(cache_ptr[2 * l + 1]), p.vcache[p.layers + l],
+                                       rope_cs, act_s, misc);
+                else
+                    attention_group(p, blockIdx.x / p.g_splits, blockIdx.x % p.g_splits, pos, cache_ptr[2 * l],
+                                    cache_ptr[2 * l + 1], rope_cs, act_s);
+            }
             grid_barrier(p, epoch);
             if ((int)blockIdx.x < p.n_q) attention_merge(p, blockIdx.x, act_s, misc);
         } else if ((int)blockIdx.x < p.n_q * p.splits) {
-            attention_head<SIMPLE ? 4 : 8>(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
-                           cache_ptr[2 * l + 1], rope_cs, act_s, misc);
+            if (p.kv_int8)
+                attention_head_i8<SIMPLE ? 4 : 8>(p, blockIdx.x / p.splits, blockIdx.x % p.splits, pos,
+                                                  reinterpret_cast<int8_t *>(cache_ptr[2 * l]), p.kcache[p.layers + l],
+                                                  reinterpret_cast<int8_t *>(cache_ptr[2 * l + 1]), p.vcache[p.layers + l],
+                                                  rope_cs, act_s, misc);
+            else
+                attention_head<SIMPLE ? 4 : 8>(p, l, blockIdx.x / p.splits, blockIdx.x % p.splits, pos, cache_ptr[2 * l],
+                                               cache_ptr[2 * l + 1], rope_cs, act_s, misc);
         }
         grid_barrier(p, epoch);
         // output projection, residual add in the store
@@ -1365,16 +1756,30 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     int kc_limit = (opt && opt->k_chunk > 0) ? opt->k_chunk / 512 : 16;   // 16 stages = 8192 k = 64 KB of digit planes
     kc_limit = kc_limit < 1 ? 1 : (kc_limit > 16 ? 16 : kc_limit);
     const yscv_cuda_tp_comm *tp = opt ? opt->tp : nullptr;
+    const bool kv_int8 = opt && opt->kv_int8 != 0;
     if (tp && (tp->device != ctx->device || !tp->connected))
         return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: the exchange region is not connected on device %d", ctx->device));
     if (tp && tp->cap_rows < hidden)
         return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: the exchange region holds %zu rows, hidden is %zu", tp->cap_rows, hidden));
+    if (kv_int8 && d_head != 64 && d_head != 128)
+        return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: int8 caches need d_head 64 or 128, got %zu", d_head));
+    if (kv_int8 && n_kv * d_head > 2048)
+        return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: int8 caches need n_kv * d_head <= 2048, got %zu", n_kv * d_head));
     // rows (or paired indices) per CTA -> row blocks of at most `cap` tiles, balanced
+    // (more blocks than the minimum when that wastes fewer padding rows: 388 rows are 5 blocks
+    // of 5 tiles = 400 rather than 4 blocks of 7 = 448)
     auto blocks_of = [&](size_t per_cta, int cap, int *tiles_out) {
-        const int n_rb = (int)((per_cta + (size_t)cap * 16 - 1) / ((size_t)cap * 16));
-        const size_t per_block = (per_cta + n_rb - 1) / n_rb;
-        *tiles_out = (int)((per_block + 15) / 16);
-        return n_rb;
+        const int n_min = (int)((per_cta + (size_t)cap * 16 - 1) / ((size_t)cap * 16));
+        int best_n = n_min, best_tiles = 0;
+        for (int n_rb = n_min; n_rb <= 2 * n_min; ++n_rb) {
+            const size_t per_block = (per_cta + n_rb - 1) / n_rb;
+            const int tiles = (int)((per_block + 15) / 16);
+            // a block costs its tiles plus about 0.4 tile for the reduction, the store and the ramp
+            if (best_tiles == 0 || n_rb * (5 * tiles + 2) < best_n * (5 * best_tiles + 2)) { best_n = n_rb; best_tiles = tiles; }
+            if (n_min == 1) break;   // one block stays one block (the single-block paths are faster)
+        }
+        *tiles_out = best_tiles;
+        return best_n;
     };
     const bool pair_gu = (variant & 1) != 0;
     int nrb[4] = {1, 1, 1, 1}, tl[4] = {1, 1, 1, 1};
@@ -1386,7 +1791,8 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
         const yscv_cuda_int4_weight *w[4] = {layers[l].qkv, layers[l].o, layers[l].gate_up, layers[l].down};
         const size_t want_n[4] = {qkv_rows, hidden, 2 * inter, hidden};
         const size_t want_k[4] = {hidden, attn_w, hidden, inter};
-        if (!layers[l].d_gamma_attn || !layers[l].d_gamma_mlp || !layers[l].d_kcache || !layers[l].d_vcache)
+        if (!layers[l].d_gamma_attn || !layers[l].d_gamma_mlp || !layers[l].d_kcache || !layers[l].d_vcache ||
+            (kv_int8 && (!layers[l].d_kscale || !layers[l].d_vscale)))
             return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: layer %zu has a null pointer", l));
         // key and value rows are read with 128-bit loads
         if ((reinterpret_cast<uintptr_t>(layers[l].d_kcache) | reinterpret_cast<uintptr_t>(layers[l].d_vcache)) & 15)
@@ -1482,8 +1888,14 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     plan->smem = p.stages * slot_bytes + fixed;
 
     // device copies: matrices, gammas, cache pointers, scratch, barrier words
-    std::vector<float *> kptr(n_layers), vptr(n_layers);
-    for (size_t l = 0; l < n_layers; ++l) { kptr[l] = layers[l].d_kcache; vptr[l] = layers[l].d_vcache; }
+    // cache pointers, then (int8 caches) the row-scale tables
+    std::vector<float *> kptr(2 * n_layers, nullptr), vptr(2 * n_layers, nullptr);
+    for (size_t l = 0; l < n_layers; ++l) {
+        kptr[l] = reinterpret_cast<float *>(layers[l].d_kcache);
+        vptr[l] = reinterpret_cast<float *>(layers[l].d_vcache);
+        kptr[n_layers + l] = layers[l].d_kscale;
+        vptr[n_layers + l] = layers[l].d_vscale;
+    }
     const size_t attn_floats = n_q * (size_t)(grouped ? g_splits : splits) * (d_head + 2);
     const size_t scratch_floats = qkv_rows + attn_floats + 2 * inter + attn_w + 2 * (size_t)grid;
 #define PLAN_TRY(expr)                                                                       \
@@ -1494,13 +1906,13 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     } while (0)
     PLAN_TRY(cudaMalloc(&plan->d_mats, mats.size() * sizeof(StepMat)));
     PLAN_TRY(cudaMalloc(&plan->d_gamma, n_layers * 2 * hidden * sizeof(float)));
-    PLAN_TRY(cudaMalloc(&plan->d_kptr, n_layers * sizeof(float *)));
-    PLAN_TRY(cudaMalloc(&plan->d_vptr, n_layers * sizeof(float *)));
+    PLAN_TRY(cudaMalloc(&plan->d_kptr, 2 * n_layers * sizeof(float *)));
+    PLAN_TRY(cudaMalloc(&plan->d_vptr, 2 * n_layers * sizeof(float *)));
     PLAN_TRY(cudaMalloc(&plan->d_scratch, scratch_floats * sizeof(float)));
     PLAN_TRY(cudaMalloc(&plan->d_sync, 4 * sizeof(unsigned int)));
     PLAN_TRY(cudaMemcpyAsync(plan->d_mats, mats.data(), mats.size() * sizeof(StepMat), cudaMemcpyHostToDevice, ctx->stream));
-    PLAN_TRY(cudaMemcpyAsync(plan->d_kptr, kptr.data(), n_layers * sizeof(float *), cudaMemcpyHostToDevice, ctx->stream));
-    PLAN_TRY(cudaMemcpyAsync(plan->d_vptr, vptr.data(), n_layers * sizeof(float *), cudaMemcpyHostToDevice, ctx->stream));
+    PLAN_TRY(cudaMemcpyAsync(plan->d_kptr, kptr.data(), 2 * n_layers * sizeof(float *), cudaMemcpyHostToDevice, ctx->stream));
+    PLAN_TRY(cudaMemcpyAsync(plan->d_vptr, vptr.data(), 2 * n_layers * sizeof(float *), cudaMemcpyHostToDevice, ctx->stream));
     PLAN_TRY(cudaMemsetAsync(plan->d_sync, 0, 4 * sizeof(unsigned int), ctx->stream));
     for (size_t l = 0; l < n_layers; ++l) {
         float *g = reinterpret_cast<float *>(plan->d_gamma) + l * 2 * hidden;
@@ -1520,6 +1932,7 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     p.gamma = reinterpret_cast<const float *>(plan->d_gamma);
     p.kcache = reinterpret_cast<float *const *>(plan->d_kptr);
     p.vcache = reinterpret_cast<float *const *>(plan->d_vptr);
+    p.kv_int8 = kv_int8 ? 1 : 0;
     float *s = reinterpret_cast<float *>(plan->d_scratch);
     p.qkv = s;
     p.attn = s + qkv_rows;

@@ -93,7 +93,7 @@ class Int4Decoder:
         self.plan = None
         self.tp_comm = None
         self.lm_row0, self.lm_rows = 0, cfg.vocab
-        if fused_step and batch == 1 and not kv_int8:
+        if fused_step and batch == 1:
             try:
                 if tp_size > 1:
                     self._connect_tp()
@@ -104,9 +104,11 @@ class Int4Decoder:
                     [dict(qkv=self.wqkv[l].handle, o=self.wo[l].handle, gate_up=self.wgu[l].handle,
                           down=self.wdown[l].handle, gamma_attn=self.gamma.data_ptr(),
                           gamma_mlp=self.gamma.data_ptr(), kcache=self.kcache[l].data_ptr(),
-                          vcache=self.vcache[l].data_ptr()) for l in range(self.n_layers)],
+                          vcache=self.vcache[l].data_ptr(),
+                          kscale=self.kscale[l].data_ptr() if kv_int8 else None,
+                          vscale=self.vscale[l].data_ptr() if kv_int8 else None) for l in range(self.n_layers)],
                     cfg.hidden, self.mlp_l, self.nq_l, self.nkv_l, cfg.head_dim, max_seq, cfg.eps, cfg.rope_theta,
-                    tp=self.tp_comm, **(plan_options or {}))
+                    tp=self.tp_comm, kv_int8=kv_int8, **(plan_options or {}))
             except YscvCudaError as e:
                 if e.status != -3:  # anything but "unsupported shape" is a real failure
                     raise

@@ -151,13 +151,13 @@ class QuantStats(C.Structure):
 class DecodeOptions(C.Structure):
     """yscv_cuda_decode_options."""
     _fields_ = [("variant", C.c_int), ("max_tiles", C.c_int), ("k_chunk", C.c_int), ("attention_form", C.c_int),
-                ("spin_limit", C.c_int), ("tp", _vp)]
+                ("spin_limit", C.c_int), ("tp", _vp), ("kv_int8", C.c_int)]
 
 
 class DecodeLayer(C.Structure):
     """yscv_cuda_decode_layer."""
     _fields_ = [("qkv", _vp), ("o", _vp), ("gate_up", _vp), ("down", _vp), ("d_gamma_attn", _vp),
-                ("d_gamma_mlp", _vp), ("d_kcache", _vp), ("d_vcache", _vp)]
+                ("d_gamma_mlp", _vp), ("d_kcache", _vp), ("d_vcache", _vp), ("d_kscale", _vp), ("d_vscale", _vp)]
 
 
 def load_library():
@@ -718,18 +718,22 @@ class Context:
                                                        int(causal), _vp(d_out)))
 
     def decode_plan(self, layers, hidden, inter, n_q, n_kv, d_head, max_seq, eps, rope_theta, *, variant=-1,
-                    max_tiles=0, k_chunk=0, attention_form=-1, spin_limit=0, tp: "TpComm | None" = None) -> DecodePlan:
+                    max_tiles=0, k_chunk=0, attention_form=-1, spin_limit=0, tp: "TpComm | None" = None,
+                    kv_int8=False) -> DecodePlan:
         """layers: list of dicts with Int4Weight `qkv`, `o`, `gate_up`, `down` and device
-        pointers `gamma_attn`, `gamma_mlp`, `kcache`, `vcache`. The keyword arguments are the
-        fields of yscv_cuda_decode_options (defaults: the library's own choices)."""
+        pointers `gamma_attn`, `gamma_mlp`, `kcache`, `vcache` (with kv_int8 also `kscale`,
+        `vscale`). The keyword arguments are the fields of yscv_cuda_decode_options (defaults: the
+        library's own choices)."""
         arr = (DecodeLayer * len(layers))()
         for dst, l in zip(arr, layers):
             dst.qkv, dst.o, dst.gate_up, dst.down = (l["qkv"].handle, l["o"].handle, l["gate_up"].handle,
                                                      l["down"].handle)
             dst.d_gamma_attn, dst.d_gamma_mlp = l["gamma_attn"], l["gamma_mlp"]
             dst.d_kcache, dst.d_vcache = l["kcache"], l["vcache"]
+            dst.d_kscale, dst.d_vscale = l.get("kscale"), l.get("vscale")
         h = _vp()
-        opt = DecodeOptions(variant, max_tiles, k_chunk, attention_form, spin_limit, tp.handle if tp else None)
+        opt = DecodeOptions(variant, max_tiles, k_chunk, attention_form, spin_limit, tp.handle if tp else None,
+                            1 if kv_int8 else 0)
         _check(self.lib.yscv_cuda_decode_plan_create_ex(self.handle, C.cast(arr, _vp), len(layers), hidden, inter,
                                                         n_q, n_kv, d_head, max_seq, eps, rope_theta,
                                                         C.cast(C.byref(opt), _vp), C.byref(h)))
