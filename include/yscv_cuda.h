@@ -538,6 +538,12 @@ typedef struct yscv_cuda_decode_options {
                            writes them (int8 rows of n_kv * d_head with one f32 scale per row in
                            d_kscale / d_vscale); d_head must be 64 or 128. Under tensor parallelism a
                            row is this rank's KV heads only, so its scale differs from the one-GPU one */
+    int batch;          /* 0 or 1: one sequence per step. 2..8: that many sequences per step, all at the
+                           same position (the batched decode of apps/llm-bench/src/main.rs:491-561):
+                           d_token, d_x, d_logits then hold one entry / row per sequence
+                           ([batch], [batch][hidden], [batch][vocab]) and the caches are
+                           [batch][max_seq][n_kv][d_head]. One GPU, f32 caches, hidden and
+                           n_q * d_head at most 2048 */
 } yscv_cuda_decode_options;
 int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cuda_decode_layer *layers,
                                     size_t n_layers, size_t hidden, size_t inter, size_t n_q,

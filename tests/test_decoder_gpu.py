@@ -163,7 +163,7 @@ def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logi
         flip_margin = 1e-2
     dec = Int4Decoder.with_full_weights(ctx, cfg, batch, prompt_len + steps + 1, s, seed=seed, layers=n_layers,
                                         fused_step=fused_step, kv_int8=kv_int8, plan_options=plan_options)
-    assert (dec.plan is not None) == (fused_step and batch == 1)
+    assert (dec.plan is not None) == (fused_step and (batch == 1 or (batch <= 8 and not kv_int8 and cfg.hidden <= 2048)))
     from oracle_decoder import OracleDecoder
     ref = OracleDecoder(oracle, cfg, n_layers, export_weights(dec), dec.embedding.cpu().numpy(),
                         dec.lm_head.cpu().numpy(), batch, kv_int8=kv_int8)
@@ -212,9 +212,26 @@ def run_parity(tctx, oracle, cfg, n_layers, batch, prompt_len, steps, seed, logi
     return rel
 
 
-def test_small_decoder_matches_oracle(tctx, oracle):
+@pytest.mark.parametrize("fused", [True, False])
+def test_small_decoder_matches_oracle(tctx, oracle, fused):
+    """Two sequences: the batch form of the one-launch step (two key chunks per head, rows 2..7
+    of the activation planes zero), and the operator chain."""
     cfg = DecoderConfig(layers=3, hidden=512, mlp=1024, n_q=8, n_kv=2, head_dim=64, vocab=1000)
-    run_parity(tctx, oracle, cfg, 3, batch=2, prompt_len=20, steps=12, seed=3, logit_tol=1e-4)
+    run_parity(tctx, oracle, cfg, 3, batch=2, prompt_len=20, steps=12, seed=3, logit_tol=1e-4, fused_step=fused)
+    ctx, _ = tctx
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("batch", [3, 5, 8])
+def test_small_decoder_batch_step_matches_oracle(tctx, oracle, batch):
+    """The batch form of the one-launch step at odd batch sizes and a full batch of 8, a shape
+    whose down projection is walked in K chunks (mlp 2560 > one chunk of 2048) and whose prompt
+    differs per sequence."""
+    cfg = DecoderConfig(layers=2, hidden=1024, mlp=2560, n_q=16, n_kv=4, head_dim=64, vocab=1200)
+    run_parity(tctx, oracle, cfg, 2, batch=batch, prompt_len=24, steps=8, seed=9, logit_tol=1e-4)
+    ctx, _ = tctx
+    assert "decode_step_batch" in ctx.last_kernel()
+    assert ctx.device_status() == 0
 
 
 def test_small_decoder_fused_step_matches_oracle(tctx, oracle):
@@ -428,9 +445,12 @@ def test_tinyllama_shape_greedy_tokens(tctx, oracle):
     run_parity(tctx, oracle, TINYLLAMA_1B, 22, batch=1, prompt_len=128, steps=32, seed=3, logit_tol=1e-4)
 
 
-def test_tinyllama_shape_batch8(tctx, oracle):
-    # BASELINE config 4, batch 8 (independent sequences, prompt seed + b): operator chain
-    run_parity(tctx, oracle, TINYLLAMA_1B, 2, batch=8, prompt_len=32, steps=8, seed=3, logit_tol=1e-4)
+@pytest.mark.parametrize("fused", [True, False])
+def test_tinyllama_shape_batch8(tctx, oracle, fused):
+    # BASELINE config 4, batch 8 (independent sequences, prompt seed + b): the batch form of the
+    # one-launch step, and the operator chain
+    run_parity(tctx, oracle, TINYLLAMA_1B, 2, batch=8, prompt_len=32, steps=8, seed=3, logit_tol=1e-4,
+               fused_step=fused)
 
 
 LLAMA70B_LAYER = DecoderConfig(layers=2, hidden=8192, mlp=28672, n_q=64, n_kv=8, head_dim=128, vocab=16032,

@@ -117,6 +117,10 @@ struct StepParams {
     unsigned long long *tp_peer[8];
     unsigned int *tp_seq;                  // steps this plan has run (device word, local)
     int lm_row0, lm_rows;                  // this rank's rows of the LM head (all of them when tp_size == 1)
+    // batch form (decode_step_batch_kernel): sequences per step, all at the same position. x, qkv,
+    // attn, gu, logits, best_val / best_idx and the token arrays then hold `batch` rows; the caches
+    // are [batch][max_seq][n_kv][d_head]
+    int batch, red_bytes;
 };
 
 
@@ -639,7 +643,11 @@ __device__ __forceinline__ void attention_merge(const StepParams &p, int h, floa
 template <int VB>   // value rows whose loads are in flight together past the prefetched ones
 __device__ __forceinline__ void attention_head(const StepParams &p, int layer, int h, int split, int pos,
                                                float *kc, float *vc, const float *rope_cs,
-                                               float *scratch, float *misc) {
+                                               float *scratch, float *misc, const float *qkv_base = nullptr,
+                                               float *attn_base = nullptr) {
+    // (batch form: the sequence's own q|k|v row, partial-result block and cache slices)
+    const float *const qkv_in = qkv_base ? qkv_base : p.qkv;
+    float *const attn_o = attn_base ? attn_base : p.attn;
     const int tid = threadIdx.x;
     const int d = p.d_head, half = d / 2;
     const int grp = p.n_q / p.n_kv, kvh = h / grp;
@@ -650,7 +658,7 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
     const int limit = pos + 1;
     const int chunk = (limit + p.splits - 1) / p.splits;
     const int k0 = split * chunk, k1 = min(limit, k0 + chunk);   // this CTA's keys
-    float *po = p.attn + ((size_t)h * p.splits + split) * (d + 2);
+    float *po = attn_o + ((size_t)h * p.splits + split) * (d + 2);
     if (k0 >= k1) {  // nothing for this split yet: the neutral element of the merge
         for (int i = tid; i < d; i += DS_CONSUMERS) po[i] = 0.0f;
         if (tid == 0) { po[d] = -INFINITY; po[d + 1] = 0.0f; }
@@ -680,11 +688,11 @@ __device__ __forceinline__ void attention_head(const StepParams &p, int layer, i
     const bool is_k = tid >= half;
     const int ri = is_k ? tid - half : tid;
     if (tid < d) {
-        const float *src = p.qkv + (size_t)(is_k ? p.n_q + kvh : h) * d;
+        const float *src = qkv_in + (size_t)(is_k ? p.n_q + kvh : h) * d;
         x0 = __ldcg(src + ri);
         x1 = __ldcg(src + ri + half);
     } else if (tid < 2 * d) {
-        x0 = __ldcg(p.qkv + (size_t)(p.n_q + p.n_kv + kvh) * d + (tid - d));
+        x0 = __ldcg(qkv_in + (size_t)(p.n_q + p.n_kv + kvh) * d + (tid - d));
     }
 
     // ---- RoPE, append ----
@@ -1687,6 +1695,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const StepPa
     }
 }
 
+#include "decode_step_batch.cuh"
+
 }  // namespace yscv
 
 // ---------------------------------------------------------------------------
@@ -1702,6 +1712,7 @@ struct yscv_cuda_decode_plan {
     void *d_scratch = nullptr, *d_sync = nullptr;
     bool poisoned = false;   // a bounded wait ran out in a step of this plan (yscv_cuda_decode_plan_check)
     int tp_rank = 0, tp_size = 1;
+    int batch = 1;           // > 1: decode_step_batch_kernel
 };
 
 extern "C" void yscv_cuda_decode_plan_free(yscv_cuda_decode_plan *plan) {
@@ -1748,15 +1759,26 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     };
     // kernel variants (options: a bit mask): 1 gate/up pairing, 2 sixteen K slices for one-tile
     // slabs, 4 merge-weight table, 8 relaxed barrier polling
-    const int variant = (opt && opt->variant >= 0) ? opt->variant : DS_DEFAULT_VARIANT;
+    // batch form: 2..8 sequences per step (always with paired gate/up rows)
+    const int batch = (opt && opt->batch > 1) ? opt->batch : 1;
+    const int variant = ((opt && opt->variant >= 0) ? opt->variant : DS_DEFAULT_VARIANT) | (batch > 1 ? 1 : 0);
     // geometry limits, overridable so that small test shapes reach the row-block and K-chunk
     // paths: tiles per row block (2..8, even), k per chunk (a multiple of 512)
     int max_tiles = (opt && opt->max_tiles > 0) ? opt->max_tiles : 8;
     max_tiles = max_tiles < 2 ? 2 : (max_tiles > 8 ? 8 : max_tiles & ~1);
     int kc_limit = (opt && opt->k_chunk > 0) ? opt->k_chunk / 512 : 16;   // 16 stages = 8192 k = 64 KB of digit planes
     kc_limit = kc_limit < 1 ? 1 : (kc_limit > 16 ? 16 : kc_limit);
+    if (batch > 1 && kc_limit > 4) kc_limit = 4;   // 32 activations per staging thread: chunks of 2048 k
     const yscv_cuda_tp_comm *tp = opt ? opt->tp : nullptr;
     const bool kv_int8 = opt && opt->kv_int8 != 0;
+    if (batch > DSB_ROWS)
+        return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: at most %d sequences per step, got %d", DSB_ROWS, batch));
+    if (batch > 1 && (tp || kv_int8))
+        return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: the batch form runs on one GPU with f32 caches"));
+    if (batch > 1 && (hidden > 2048 || n_q * d_head > 2048 || d_head % 8 != 0))
+        return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED,
+                         "decode plan: the batch form needs hidden and n_q * d_head <= 2048 (hidden=%zu, n_q*d_head=%zu)",
+                         hidden, n_q * d_head));
     if (tp && (tp->device != ctx->device || !tp->connected))
         return bail(fail(YSCV_CUDA_ERR_BAD_ARG, "decode plan: the exchange region is not connected on device %d", ctx->device));
     if (tp && tp->cap_rows < hidden)
@@ -1852,17 +1874,20 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
                          "decode plan: hidden=%zu / n_q*d_head=%zu exceed one K chunk of %d, or the down projection "
                          "needs both several chunks and several row blocks", hidden, attn_w, kc_stages * 512));
     p.kc_stages = kc_stages;
-    p.dig_bytes = kc_stages * DS_BLOB_BYTES;
+    p.dig_bytes = kc_stages * (batch > 1 ? DSB_BLOB_BYTES : DS_BLOB_BYTES);
+    p.batch = batch;
+    p.red_bytes = batch > 1 ? 2 * DS_RED_BYTES : DS_RED_BYTES;
     // attention form: per query head with up to 4 key chunks, or (long contexts, or
     // YSCV_CUDA_STEP_ATTN=1) per KV head with up to 32 key chunks and a merge phase
     // key chunks (CTAs) per query head: up to 4, or up to 16 when this GPU has so few heads that
     // 4 would leave most SMs idle (tensor-parallel shards)
-    const int splits = (int)std::min<size_t>(n_q * 4 * 2 <= (size_t)grid ? 16 : 4, (size_t)grid / n_q);
+    const int splits = batch > 1 ? (int)std::max<size_t>(1, std::min<size_t>(4, (size_t)grid / (n_q * batch)))
+                                 : (int)std::min<size_t>(n_q * 4 * 2 <= (size_t)grid ? 16 : 4, (size_t)grid / n_q);
     const size_t grp = n_q / n_kv;
     const bool group_ok = (grp & (grp - 1)) == 0 && grp <= 16 && grp * d_head <= 2048 &&
                           DS_CONSUMERS % (grp * d_head / 4) == 0;
     const int attn_form = opt ? opt->attention_form : -1;
-    const bool grouped = group_ok && (attn_form >= 0 ? attn_form != 0 : (max_seq + splits - 1) / splits > 256);
+    const bool grouped = batch == 1 && group_ok && (attn_form >= 0 ? attn_form != 0 : (max_seq + splits - 1) / splits > 256);
     const int g_splits = (int)std::max<size_t>(1, std::min<size_t>(32, (size_t)grid / n_kv));
     const int g_cap = (int)(((max_seq + g_splits - 1) / g_splits + 3) / 4 * 4);
     // the attention scratch lives in the activation area between the GEMVs: widen that area if
@@ -1873,13 +1898,20 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
                 : (3 * d_head + 4 * DS_CONSUMERS + max_seq) * sizeof(float);
     size_t act_floats = (size_t)kc_stages * 512;
     if (attn_scratch > act_floats * 4) act_floats = (attn_scratch + 3) / 4;
+    if (batch > 1) {
+        // the tail keeps the normalised rows [8][hidden] in the digit area and the scratch behind
+        // it, then the per-warp maxima [8][16] x {value, index} at the start of the scratch
+        const size_t rows_bytes = (size_t)DSB_ROWS * hidden * sizeof(float);
+        const size_t need = rows_bytes > (size_t)p.dig_bytes ? (rows_bytes - p.dig_bytes) / 4 : 0;
+        act_floats = std::max<size_t>(std::max<size_t>(act_floats, need), 2 * DSB_ROWS * DS_CONSUMER_WARPS);
+    }
     act_floats = (act_floats + 3) / 4 * 4;
     if (act_floats * 4 > 96 * 1024)
         return bail(fail(YSCV_CUDA_ERR_UNSUPPORTED, "decode plan: max_seq=%zu does not fit one CTA per head", max_seq));
     p.act_floats = (int)act_floats;
     // misc, rotary factors, cache pointers, split-merge weights
     const int tables = 128 + (int)d_head * 4 + (int)n_layers * 2 * 8 + (int)n_q * 16 * (splits > 4 ? 4 : 1) + 16;
-    const int fixed = DS_RED_BYTES + DS_BAR_BYTES + p.dig_bytes + p.act_floats * 4 + tables;
+    const int fixed = p.red_bytes + DS_BAR_BYTES + p.dig_bytes + p.act_floats * 4 + tables;
     const int budget = 227 * 1024 - fixed - 1024;
     p.stages = budget / slot_bytes;
     if (p.stages > DS_MAX_STAGES) p.stages = DS_MAX_STAGES;
@@ -1896,8 +1928,8 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
         kptr[n_layers + l] = layers[l].d_kscale;
         vptr[n_layers + l] = layers[l].d_vscale;
     }
-    const size_t attn_floats = n_q * (size_t)(grouped ? g_splits : splits) * (d_head + 2);
-    const size_t scratch_floats = qkv_rows + attn_floats + 2 * inter + attn_w + 2 * (size_t)grid;
+    const size_t attn_floats = (size_t)batch * n_q * (size_t)(grouped ? g_splits : splits) * (d_head + 2);
+    const size_t scratch_floats = (size_t)batch * (qkv_rows + 2 * inter + attn_w + 2 * (size_t)grid) + attn_floats;
 #define PLAN_TRY(expr)                                                                       \
     do {                                                                                     \
         cudaError_t _e = (expr);                                                             \
@@ -1920,9 +1952,10 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
         PLAN_TRY(cudaMemcpyAsync(g + hidden, layers[l].d_gamma_mlp, hidden * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     }
     PLAN_TRY(cudaStreamSynchronize(ctx->stream));  // the host vectors go out of scope
-    plan->simple = nrb[0] == 1 && nrb[1] == 1 && nrb[2] == 1 && nrb[3] == 1 && (int)(k_max / 512) <= kc_stages &&
-                   !grouped;
-    auto kern = plan->simple ? decode_step_kernel<true> : decode_step_kernel<false>;
+    plan->simple = batch == 1 && nrb[0] == 1 && nrb[1] == 1 && nrb[2] == 1 && nrb[3] == 1 &&
+                   (int)(k_max / 512) <= kc_stages && !grouped;
+    plan->batch = batch;
+    auto kern = batch > 1 ? decode_step_batch_kernel : (plan->simple ? decode_step_kernel<true> : decode_step_kernel<false>);
     PLAN_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan->smem));
     int per_sm = 0;
     PLAN_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DS_THREADS, plan->smem));
@@ -1935,11 +1968,11 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     p.kv_int8 = kv_int8 ? 1 : 0;
     float *s = reinterpret_cast<float *>(plan->d_scratch);
     p.qkv = s;
-    p.attn = s + qkv_rows;
+    p.attn = s + (size_t)batch * qkv_rows;
     p.gu = p.attn + attn_floats;
-    p.attn_out = p.gu + 2 * inter;
-    p.best_val = p.attn_out + attn_w;
-    p.best_idx = reinterpret_cast<int *>(p.best_val + grid);
+    p.attn_out = p.gu + (size_t)batch * 2 * inter;
+    p.best_val = p.attn_out + (size_t)batch * attn_w;
+    p.best_idx = reinterpret_cast<int *>(p.best_val + (size_t)batch * grid);
     p.splits = splits;
     p.attn_grouped = grouped ? 1 : 0;
     p.g_splits = g_splits;
@@ -1999,14 +2032,17 @@ static int launch_step(yscv_cuda_ctx *ctx, const yscv_cuda_decode_plan *plan, ys
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     ctx->prof_begin();
-    if (plan->simple)
+    if (plan->batch > 1)
+        YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_step_batch_kernel, p));
+    else if (plan->simple)
         YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_step_kernel<true>, p));
     else
         YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_step_kernel<false>, p));
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
-    ctx->last_kernel = p.tail ? "decode_step(persistent,tma,imma,+lm_head)" : "decode_step(persistent,tma,imma)";
+    ctx->last_kernel = plan->batch > 1 ? (p.tail ? "decode_step_batch(persistent,tma,imma,+lm_head)" : "decode_step_batch(persistent,tma,imma)")
+                                       : (p.tail ? "decode_step(persistent,tma,imma,+lm_head)" : "decode_step(persistent,tma,imma)");
     return YSCV_CUDA_OK;
 }
 

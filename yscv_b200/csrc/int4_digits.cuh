@@ -66,6 +66,10 @@ __host__ __device__ inline QuantLayout quant_layout(int mp, int gs) {
     return q;
 }
 
+__device__ __forceinline__ void quantize_group_values(const float (&v)[8], unsigned char *blobs,
+                                                      const struct QuantLayout &q, int Gabs, int m, int t,
+                                                      bool valid);
+
 // A quad (4 consecutive lanes) turns the 32 activations of (row m, group Gabs) into
 // digit planes and writes them into the blob of their K stage. Lane t of the quad
 // owns k = 8t..8t+7, which is exactly what fragment thread t needs, so the only
@@ -118,6 +122,15 @@ __device__ __forceinline__ void quantize_group(const float *__restrict__ src, un
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.0f;
     }
+    quantize_group_values(v, blobs, q, Gabs, m, t, valid);
+}
+
+// The same for eight activations the lane already holds in registers (k = 8t .. 8t+7 of group
+// Gabs, row m). All 32 lanes of the warp call it together; lanes without an item pass
+// valid = false (and any values).
+__device__ __forceinline__ void quantize_group_values(const float (&v)[8], unsigned char *blobs,
+                                                      const QuantLayout &q, int Gabs, int m, int t,
+                                                      bool valid) {
     float gmax = 0.0f;
     int nan = 0;
 #pragma unroll
@@ -157,9 +170,7 @@ __device__ __forceinline__ void quantize_group(const float *__restrict__ src, un
     if (!valid) return;
     const int ks = Gabs / q.gs, G = Gabs % q.gs;
     unsigned char *blob = blobs + (size_t)ks * q.blob_bytes;
-    const float as = src ? (bad ? __int_as_float(0x7fc00000)
-                                : __int_as_float((127 + e - 21) << 23))  // 2^(e-21)
-                         : 0.0f;
+    const float as = bad ? __int_as_float(0x7fc00000) : __int_as_float((127 + e - 21) << 23);  // 2^(e-21)
     const int ncorr = -8 * sum;
     if (q.mp <= 2) {
         uint2 *frag = reinterpret_cast<uint2 *>(blob);  // [G][col][t] x {b0,b1 | as,nc}

@@ -93,7 +93,8 @@ class Int4Decoder:
         self.plan = None
         self.tp_comm = None
         self.lm_row0, self.lm_rows = 0, cfg.vocab
-        if fused_step and batch == 1:
+        # batches of 2..8 sequences take the batch form of the same kernel (one GPU, f32 caches)
+        if fused_step and (batch == 1 or (batch <= 8 and tp_size == 1 and not kv_int8)):
             try:
                 if tp_size > 1:
                     self._connect_tp()
@@ -108,7 +109,7 @@ class Int4Decoder:
                           kscale=self.kscale[l].data_ptr() if kv_int8 else None,
                           vscale=self.vscale[l].data_ptr() if kv_int8 else None) for l in range(self.n_layers)],
                     cfg.hidden, self.mlp_l, self.nq_l, self.nkv_l, cfg.head_dim, max_seq, cfg.eps, cfg.rope_theta,
-                    tp=self.tp_comm, kv_int8=kv_int8, **(plan_options or {}))
+                    tp=self.tp_comm, kv_int8=kv_int8, batch=batch, **(plan_options or {}))
             except YscvCudaError as e:
                 if e.status != -3:  # anything but "unsupported shape" is a real failure
                     raise

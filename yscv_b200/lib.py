@@ -151,7 +151,7 @@ class QuantStats(C.Structure):
 class DecodeOptions(C.Structure):
     """yscv_cuda_decode_options."""
     _fields_ = [("variant", C.c_int), ("max_tiles", C.c_int), ("k_chunk", C.c_int), ("attention_form", C.c_int),
-                ("spin_limit", C.c_int), ("tp", _vp), ("kv_int8", C.c_int)]
+                ("spin_limit", C.c_int), ("tp", _vp), ("kv_int8", C.c_int), ("batch", C.c_int)]
 
 
 class DecodeLayer(C.Structure):
@@ -719,7 +719,7 @@ class Context:
 
     def decode_plan(self, layers, hidden, inter, n_q, n_kv, d_head, max_seq, eps, rope_theta, *, variant=-1,
                     max_tiles=0, k_chunk=0, attention_form=-1, spin_limit=0, tp: "TpComm | None" = None,
-                    kv_int8=False) -> DecodePlan:
+                    kv_int8=False, batch=1) -> DecodePlan:
         """layers: list of dicts with Int4Weight `qkv`, `o`, `gate_up`, `down` and device
         pointers `gamma_attn`, `gamma_mlp`, `kcache`, `vcache` (with kv_int8 also `kscale`,
         `vscale`). The keyword arguments are the fields of yscv_cuda_decode_options (defaults: the
@@ -733,7 +733,7 @@ class Context:
             dst.d_kscale, dst.d_vscale = l.get("kscale"), l.get("vscale")
         h = _vp()
         opt = DecodeOptions(variant, max_tiles, k_chunk, attention_form, spin_limit, tp.handle if tp else None,
-                            1 if kv_int8 else 0)
+                            1 if kv_int8 else 0, int(batch))
         _check(self.lib.yscv_cuda_decode_plan_create_ex(self.handle, C.cast(arr, _vp), len(layers), hidden, inter,
                                                         n_q, n_kv, d_head, max_seq, eps, rope_theta,
                                                         C.cast(C.byref(opt), _vp), C.byref(h)))
