@@ -149,21 +149,22 @@ __device__ __forceinline__ void quantize_group_values(const float (&v)[8], unsig
     e = max(e, -100);  // keeps 2^(21-e) finite for vanishing (or subnormal) groups
     const float up = __int_as_float((127 + 21 - e) << 23);  // 2^(21-e)
     int sum = 0;
-    uint32_t b0[3] = {0, 0, 0}, b1[3] = {0, 0, 0};  // per plane: k even / k odd digits
+    // The balanced digits d0, d1 (in [-128, 127]) and the remainder d2 of afix are the three low
+    // bytes of (afix + 0x8080) ^ 0x8080: adding 128 at a digit's position lets the carry into the
+    // next digit do the rounding, and flipping bit 7 turns the biased byte into two's complement.
+    uint32_t z[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int fx = bad ? 0 : __float2int_rn(v[i] * up);
         sum += fx;
-        const int d0 = ((fx + 128) & 255) - 128;
-        const int r1 = (fx - d0) >> 8;
-        const int d1 = ((r1 + 128) & 255) - 128;
-        const int d2 = (r1 - d1) >> 8;
-        const int sh = 8 * (i >> 1);
-        if (i & 1) {
-            b1[0] |= (uint32_t)(d0 & 255) << sh; b1[1] |= (uint32_t)(d1 & 255) << sh; b1[2] |= (uint32_t)(d2 & 255) << sh;
-        } else {
-            b0[0] |= (uint32_t)(d0 & 255) << sh; b0[1] |= (uint32_t)(d1 & 255) << sh; b0[2] |= (uint32_t)(d2 & 255) << sh;
-        }
+        z[i] = (uint32_t)(fx + 0x8080) ^ 0x8080u;
+    }
+    uint32_t b0[3], b1[3];  // per plane: the digits of k = 0,2,4,6 / k = 1,3,5,7, one per byte
+#pragma unroll
+    for (int pl = 0; pl < 3; ++pl) {
+        const uint32_t sel = (uint32_t)pl | ((uint32_t)(4 + pl) << 4);
+        b0[pl] = __byte_perm(__byte_perm(z[0], z[2], sel), __byte_perm(z[4], z[6], sel), 0x5410);
+        b1[pl] = __byte_perm(__byte_perm(z[1], z[3], sel), __byte_perm(z[5], z[7], sel), 0x5410);
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
