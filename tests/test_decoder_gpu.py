@@ -222,13 +222,15 @@ def test_small_decoder_matches_oracle(tctx, oracle, fused):
     assert ctx.device_status() == 0
 
 
-@pytest.mark.parametrize("batch", [3, 5, 8])
-def test_small_decoder_batch_step_matches_oracle(tctx, oracle, batch):
+@pytest.mark.parametrize("batch,form", [(3, -1), (5, 1), (8, -1), (8, 1)])
+def test_small_decoder_batch_step_matches_oracle(tctx, oracle, batch, form):
     """The batch form of the one-launch step at odd batch sizes and a full batch of 8, a shape
     whose down projection is walked in K chunks (mlp 2560 > one chunk of 2048) and whose prompt
-    differs per sequence."""
+    differs per sequence; attention per (sequence, query head, key chunk) (the default) and per
+    (sequence, KV head, key chunk)."""
     cfg = DecoderConfig(layers=2, hidden=1024, mlp=2560, n_q=16, n_kv=4, head_dim=64, vocab=1200)
-    run_parity(tctx, oracle, cfg, 2, batch=batch, prompt_len=24, steps=8, seed=9, logit_tol=1e-4)
+    run_parity(tctx, oracle, cfg, 2, batch=batch, prompt_len=24, steps=8, seed=9, logit_tol=1e-4,
+               plan_options=dict(attention_form=form))
     ctx, _ = tctx
     assert "decode_step_batch" in ctx.last_kernel()
     assert ctx.device_status() == 0

@@ -428,7 +428,11 @@ __device__ __forceinline__ void finish_rows(const StepParams &p, float *red, int
 // [parts][grp][d], 32 floats, scores [grp][chunk_cap].
 __device__ __forceinline__ void attention_group(const StepParams &p, int kvh, int split, int pos,
                                                 float *kc, float *vc, const float *rope_cs,
-                                                float *scratch) {
+                                                float *scratch, const float *qkv_base = nullptr,
+                                                float *attn_base = nullptr) {
+    // (batch form: the sequence's own q|k|v row, partial-result block and cache slices)
+    const float *const qkv_in = qkv_base ? qkv_base : p.qkv;
+    float *const attn_o = attn_base ? attn_base : p.attn;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int d = p.d_head, half = d / 2;
     const int grp = p.n_q / p.n_kv, S = p.g_splits, cap = p.g_chunk_cap;
@@ -444,7 +448,7 @@ __device__ __forceinline__ void attention_group(const StepParams &p, int kvh, in
     if (k0 >= k1) {  // nothing for this split yet: the neutral element of the merge
         for (int i = tid; i < grp * (d + 2); i += DS_CONSUMERS) {
             const int hh = i / (d + 2), j = i - hh * (d + 2);
-            p.attn[((size_t)(h0 + hh) * S + split) * (d + 2) + j] = j == d ? -INFINITY : 0.0f;
+            attn_o[((size_t)(h0 + hh) * S + split) * (d + 2) + j] = j == d ? -INFINITY : 0.0f;
         }
         return;
     }
@@ -464,7 +468,7 @@ __device__ __forceinline__ void attention_group(const StepParams &p, int kvh, in
     for (int i = tid; i < (grp + 1) * half; i += DS_CONSUMERS) {
         const int hh = i / half, ri = i - hh * half;
         const bool is_k = hh == grp;
-        const float *src = p.qkv + (size_t)(is_k ? p.n_q + kvh : h0 + hh) * d;
+        const float *src = qkv_in + (size_t)(is_k ? p.n_q + kvh : h0 + hh) * d;
         const float x0 = __ldcg(src + ri), x1 = __ldcg(src + ri + half);
         const float cs = rope_cs[2 * ri], sn = rope_cs[2 * ri + 1];
         const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
@@ -478,7 +482,7 @@ __device__ __forceinline__ void attention_group(const StepParams &p, int kvh, in
         }
     }
     for (int i = tid; i < d; i += DS_CONSUMERS) {
-        const float v = __ldcg(p.qkv + (size_t)(p.n_q + p.n_kv + kvh) * d + i);
+        const float v = __ldcg(qkv_in + (size_t)(p.n_q + p.n_kv + kvh) * d + i);
         vcur[i] = v;
         if (has_new) vc[((size_t)pos * p.n_kv + kvh) * d + i] = v;
     }
@@ -546,7 +550,7 @@ __device__ __forceinline__ void attention_group(const StepParams &p, int kvh, in
     if (wi == 0 && lane == 0) {
         float t = 0.0f;
         for (int i = 0; i < wph; ++i) t += wred[hh_w * wph + i];
-        float *po = p.attn + ((size_t)(h0 + hh_w) * S + split) * (d + 2);
+        float *po = attn_o + ((size_t)(h0 + hh_w) * S + split) * (d + 2);
         po[d] = mx;
         po[d + 1] = t;
     }
@@ -584,7 +588,7 @@ __device__ __forceinline__ void attention_group(const StepParams &p, int kvh, in
         const int hh = i / d, dd = i - hh * d;
         float v = 0.0f;
         for (int pt = 0; pt < parts; ++pt) v += partial[((size_t)pt * grp + hh) * d + dd];
-        p.attn[((size_t)(h0 + hh) * S + split) * (d + 2) + dd] = v;
+        attn_o[((size_t)(h0 + hh) * S + split) * (d + 2) + dd] = v;
     }
     cons_sync();  // scratch is reused
 }
@@ -1887,8 +1891,14 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     const bool group_ok = (grp & (grp - 1)) == 0 && grp <= 16 && grp * d_head <= 2048 &&
                           DS_CONSUMERS % (grp * d_head / 4) == 0;
     const int attn_form = opt ? opt->attention_form : -1;
-    const bool grouped = batch == 1 && group_ok && (attn_form >= 0 ? attn_form != 0 : (max_seq + splits - 1) / splits > 256);
-    const int g_splits = (int)std::max<size_t>(1, std::min<size_t>(32, (size_t)grid / n_kv));
+    // batch form: per (sequence, query head, key chunk) by default; per KV head and key chunk
+    // (one pass over a chunk's rows serves every query head of the group; the chunks are merged
+    // while the output projection stages its input, no merge phase) only on request: at the
+    // TinyLlama shape with 128-256 cached positions it measured 10 % slower per step
+    const bool grouped = batch > 1 ? (group_ok && attn_form == 1)
+                                   : group_ok && (attn_form >= 0 ? attn_form != 0 : (max_seq + splits - 1) / splits > 256);
+    const int g_splits = batch > 1 ? (int)std::max<size_t>(1, std::min<size_t>(4, (size_t)grid / (n_kv * batch)))
+                                   : (int)std::max<size_t>(1, std::min<size_t>(32, (size_t)grid / n_kv));
     const int g_cap = (int)(((max_seq + g_splits - 1) / g_splits + 3) / 4 * 4);
     // the attention scratch lives in the activation area between the GEMVs: widen that area if
     // it needs more
@@ -1973,7 +1983,7 @@ extern "C" int yscv_cuda_decode_plan_create_ex(yscv_cuda_ctx *ctx, const yscv_cu
     p.attn_out = p.gu + (size_t)batch * 2 * inter;
     p.best_val = p.attn_out + (size_t)batch * attn_w;
     p.best_idx = reinterpret_cast<int *>(p.best_val + (size_t)batch * grid);
-    p.splits = splits;
+    p.splits = (batch > 1 && grouped) ? g_splits : splits;   // (batch form: chunks per head in p.attn)
     p.attn_grouped = grouped ? 1 : 0;
     p.g_splits = g_splits;
     p.g_chunk_cap = g_cap;

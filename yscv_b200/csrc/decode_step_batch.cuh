@@ -418,18 +418,26 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_batch_kernel(const 
         dsb_quantize_rows(v, dig, klen, B);
     };
 
-    const int att_items = B * p.n_q * p.splits;
+    // attention work items over the CTAs: (sequence, KV head, key chunk) serving the whole group of
+    // query heads, or (sequence, query head, key chunk) where the group shape does not allow that
+    const int per_seq = (p.attn_grouped ? p.n_kv : p.n_q) * p.splits;
+    const int att_items = B * per_seq;
     for (int l = 0; l < p.layers; ++l) {
         const float *g1 = p.gamma + (size_t)(2 * l) * H, *g2 = g1 + H;
         gemv(4 * l + 0, p.qkv, qkv_w, 0, [&](int, int) { stage_normed(g1); });
         grid_barrier(p, epoch);
-        // RoPE, cache append, attention: work items (sequence, query head, key chunk) over the CTAs
+        // RoPE, cache append, attention
         for (int it = blockIdx.x; it < att_items; it += gridDim.x) {
-            const int b = it / (p.n_q * p.splits), hs = it - b * (p.n_q * p.splits);
+            const int b = it / per_seq, hs = it - b * per_seq;
             const size_t cache_off = (size_t)b * p.max_seq * p.n_kv * p.d_head;
-            attention_head<4>(p, l, hs / p.splits, hs % p.splits, pos, cache_ptr[2 * l] + cache_off,
-                              cache_ptr[2 * l + 1] + cache_off, rope_cs, act_s, misc,
-                              p.qkv + (size_t)b * qkv_w, p.attn + (size_t)b * p.n_q * p.splits * (p.d_head + 2));
+            const float *qkv_b = p.qkv + (size_t)b * qkv_w;
+            float *attn_b = p.attn + (size_t)b * p.n_q * p.splits * (p.d_head + 2);
+            if (p.attn_grouped)
+                attention_group(p, hs / p.splits, hs % p.splits, pos, cache_ptr[2 * l] + cache_off,
+                                cache_ptr[2 * l + 1] + cache_off, rope_cs, act_s, qkv_b, attn_b);
+            else
+                attention_head<4>(p, l, hs / p.splits, hs % p.splits, pos, cache_ptr[2 * l] + cache_off,
+                                  cache_ptr[2 * l + 1] + cache_off, rope_cs, act_s, misc, qkv_b, attn_b);
         }
         grid_barrier(p, epoch);
         gemv(4 * l + 1, p.x, H, 1, [&](int, int) { stage_attention(); });
