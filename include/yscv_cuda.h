@@ -469,7 +469,8 @@ int yscv_cuda_int8_matmul_requant_i8(yscv_cuda_ctx *ctx, const int8_t *a, const 
  * operators above in this order: RMSNorm, int4 MatMul (fused q|k|v rows), RoPE + KvCache
  * append, grouped-query attention (causal), int4 MatMul (output) + residual, RMSNorm,
  * int4 MatMul (gate|up rows), SiLU(gate)*up, int4 MatMul (down) + residual. A decode plan
- * runs that sequence for ONE sequence (batch 1) as a single persistent cooperative kernel.
+ * runs that sequence for one sequence (or, with options.batch, 2..8 sequences at the same
+ * position) as a single persistent cooperative kernel.
  * Requirements (else YSCV_CUDA_ERR_UNSUPPORTED): group size 32; every K a multiple of 512;
  * at least sm_count rows per matrix; hidden and n_q * d_head at most 8192; inter above 8192
  * only while the down projection has at most 128 rows per SM (hidden <= 128 * sm_count);

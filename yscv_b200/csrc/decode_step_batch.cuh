@@ -34,7 +34,8 @@ __device__ __forceinline__ void dsb_quantize_rows(const float (&v)[DSB_EPT / 8][
 #pragma unroll
     for (int j = 0; j < DSB_EPT / 8; ++j) {
         const int G = j * (DSB_TPR / 4) + quad;
-        quantize_group_values(v[j], dig, q, G < groups ? G : 0, row, t, G < groups && row < batch);
+        // (a warp stages one row: rows past the batch skip the arithmetic as a whole)
+        if (row < batch) quantize_group_values(v[j], dig, q, G < groups ? G : 0, row, t, G < groups);
     }
     cons_sync();
 }
