@@ -527,7 +527,7 @@ def sharded_metrics(world):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel,
 # from the ncu capture summarised under profiles/ (None until captured).
-NCU_DRAM_BYTES_PER_LAUNCH = 36_747_520  # 36.745 MB read + 2.8 KB written (profiles/int4_gemv_fast_m1_k4096_n14336.md)
+NCU_DRAM_BYTES_PER_LAUNCH = 36_762_880  # 36.763 MB read + 0 written: dram__bytes of one launch (profiles/int4_gemv_fast_m1_k4096_n14336.md)
 
 
 def main():

@@ -26,7 +26,9 @@
 // walked in K chunks (stage a chunk, consume its stages, keep the accumulators).
 //
 // Limits (checked when the plan is built): group size 32, K % 512 == 0, hidden and
-// n_q * head_dim <= 8192, head_dim <= 128, at most 4 CTAs per query head.
+// n_q * head_dim <= 8192, head_dim <= 128.
+//
+// decode_step_batch.cuh (included below) is the form for 2..8 sequences per step.
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
