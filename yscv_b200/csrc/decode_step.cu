@@ -218,10 +218,42 @@ __device__ __forceinline__ float tp_reduce_row(const StepParams &p, int row, flo
     for (int r = 0; r < p.tp_size; ++r)
         if (r != p.tp_rank) st_relaxed_sys_u64(p.tp_peer[r] + mine, word);
     const unsigned long long *local = p.tp_peer[p.tp_rank];
+    // Every pending peer's word is probed in the same round (the loads of a round are in flight
+    // together: one trip to L2 per round instead of one per peer). Bounded like tp_wait_word:
+    // after p.spin_limit rounds, or when another CTA has raised the abort flag, the status word
+    // is set and whatever is there is summed.
+    unsigned long long w[8];
+    unsigned int pending = 0u;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        w[r] = 0ull;
+        if (r < p.tp_size && r != p.tp_rank) pending |= 1u << r;
+    }
+    for (int spins = 0; pending != 0u; ++spins) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if ((pending >> r) & 1u) w[r] = ld_relaxed_sys_u64(local + tp_slot(p, parity, r, row));
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (((pending >> r) & 1u) && (unsigned int)(w[r] >> 32) == tag) pending &= ~(1u << r);
+        if (pending == 0u) break;
+        if ((spins & 63) == 63 && ld_acquire_u32(&p.sync[2]) != 0u) {
+            *p.status = YSCV_DEV_FLAG_TIMEOUT;
+            break;
+        }
+        if (spins > p.spin_limit) {
+            atomicExch(&p.sync[2], 1u);
+            *p.status = YSCV_DEV_FLAG_TIMEOUT;
+            break;
+        }
+    }
     float sum = 0.0f;
-    for (int r = 0; r < p.tp_size; ++r) {
-        const float part = r == p.tp_rank ? v : __uint_as_float(tp_wait_word(p, local + tp_slot(p, parity, r, row), tag));
-        sum = r == 0 ? part : sum + part;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        if (r < p.tp_size) {
+            const float part = r == p.tp_rank ? v : __uint_as_float((unsigned int)w[r]);
+            sum = r == 0 ? part : sum + part;
+        }
     }
     return sum;
 }
