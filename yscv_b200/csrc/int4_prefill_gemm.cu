@@ -8,10 +8,10 @@
 // Accuracy contract: bf16 rounding of q*scale and of the activations, fp32 accumulate;
 // relative Frobenius error ~3e-3 against the fp32 scalar kernel (bound 2e-2).
 //
-// Orientation: the weight rows are the MMA's M side (128 output channels per CTA
-// tile), the tokens its N side (a tile of BT tokens, NT tiles per pass), so a short
-// prefill still fills the instruction and every weight tile is dequantised once per
-// NT*BT tokens.
+// Orientation: the weight rows are the MMA's M side (128 output channels per MMA, one or
+// two such tiles per CTA tile), the tokens its N side (a tile of BT tokens, NT tiles per
+// pass), so a short prefill still fills the instruction and every weight tile is
+// dequantised once per NT*BT tokens.
 //
 // Kernel: persistent, 448 threads:
 //   warp 0      TMA producer: per 64-k block the packed nibbles [128 rows][32 B] and the
@@ -46,6 +46,7 @@ struct PGParams {
     int BT, NT;          // tokens per MMA tile (multiple of 16, <= 256), tiles per pass
     int n_tiles, t_chunks, k_blocks;
     int stages, stage_bytes;
+    int acc_bufs;        // accumulator buffers in TMEM: 2, or 1 when one buffer takes all 512 columns
 };
 
 __device__ __forceinline__ void pg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -112,25 +113,31 @@ __global__ void act_to_bf16_kernel(const float *__restrict__ act, __nv_bfloat16 
     }
 }
 
+// NA = 128-row weight tiles per CTA tile (1 or 2). With two, the activation tile of a k block is
+// fetched once for 256 weight rows: the kernel is bound by what the SMs pull through the crossbar
+// from L2 (with the dequantisation switched off and three quarters of the MMAs left out it still
+// takes 0.8 of its time), and the activation tile is nine tenths of that.
+template <int NA>
 __global__ void __launch_bounds__(PG_THREADS, 1)
 int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                          const float *__restrict__ scales, float *__restrict__ out, PGParams p,
                          int *__restrict__ status) {
-    constexpr int W_BYTES = PG_BM * 32;            // packed nibbles of one k block: 4 KB
-    constexpr int A_TILE = PG_BM * PG_BK * 2;      // dequantised bf16 tile: 16 KB
+    constexpr int W_BYTES = NA * PG_BM * 32;       // packed nibbles of one k block: 4 KB per 128 rows
+    constexpr int A_TILE = PG_BM * PG_BK * 2;      // dequantised bf16 tile of 128 rows: 16 KB
+    constexpr int A_BUF = NA * A_TILE;             // one buffer of dequantised tiles
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = smem_u32(smem);
-    // [A tile 0][A tile 1][stages x {act tiles NT*BT*128 B | packed 4 KB}][barriers][tmem slot]
+    // [A buffer 0][A buffer 1][stages x {act tiles NT*BT*128 B | packed nibbles}][barriers][tmem slot]
     const uint32_t a_tiles = smem_base;
-    const uint32_t ring = smem_base + 2 * A_TILE;
+    const uint32_t ring = smem_base + 2 * A_BUF;
     const int act_bytes = p.NT * p.BT * 128;
     const uint32_t bars = ring + (uint32_t)p.stages * p.stage_bytes;
     const uint32_t bar_full = bars, bar_empty = bars + 64, bar_afull = bars + 128, bar_aempty = bars + 144;
     const uint32_t bar_tfull = bars + 160, bar_tempty = bars + 176;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 2 * A_TILE + (size_t)p.stages * p.stage_bytes + 192);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 2 * A_BUF + (size_t)p.stages * p.stage_bytes + 192);
     const int tiles = p.n_tiles * p.t_chunks;
-    const int acc_cols = p.NT * p.BT;              // TMEM columns of one accumulator buffer (<= 256)
+    const int acc_cols = p.NT * p.BT;              // tokens per pass; NA * acc_cols TMEM columns per accumulator buffer (<= 256)
 
     if (tid == 0) {
         for (int i = 0; i < p.stages; ++i) {
@@ -171,7 +178,7 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                     mbar_expect_tx(full, (uint32_t)(act_bytes + W_BYTES));
                     for (int j = 0; j < p.NT; ++j)
                         tma_load_2d(st + j * (p.BT * 128), &tm_a, kb * PG_BK, tc * acc_cols + j * p.BT, full);
-                    tma_load_2d(st + act_bytes, &tm_w, kb * 32, nt_i * PG_BM, full);
+                    tma_load_2d(st + act_bytes, &tm_w, kb * 32, nt_i * (NA * PG_BM), full);
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
             }
@@ -196,13 +203,16 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                     if (!alive) break;
                     pg_fence_after();
                     const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
-                    const uint64_t da = pg_desc_sw128(a_tiles + abuf * A_TILE);
-                    for (int j = 0; j < p.NT; ++j) {
-                        const uint64_t db = pg_desc_sw128(st + j * (p.BT * 128));
 #pragma unroll
-                        for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
-                            pg_mma_bf16(tacc + j * p.BT, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
-                                        (kb > 0 || kk > 0) ? 1u : 0u);
+                    for (int a = 0; a < NA; ++a) {
+                        const uint64_t da = pg_desc_sw128(a_tiles + abuf * A_BUF + a * A_TILE);
+                        for (int j = 0; j < p.NT; ++j) {
+                            const uint64_t db = pg_desc_sw128(st + j * (p.BT * 128));
+#pragma unroll
+                            for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
+                                pg_mma_bf16(tacc + a * acc_cols + j * p.BT, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2),
+                                            idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        }
                     }
                     pg_commit(bar_empty + slot * 8);
                     pg_commit(bar_aempty + abuf * 8);
@@ -211,7 +221,7 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                 }
                 if (!alive) break;
                 pg_commit(bar_tfull + tbuf * 8);
-                if (++tbuf == 2) { tbuf = 0; tphase ^= 1u; }
+                if (++tbuf == p.acc_bufs) { tbuf = 0; tphase ^= 1u; }
             }
         }
     } else if (warp < 2 + PG_DEQ_WARPS) {
@@ -224,41 +234,55 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
         for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
             const int nt_i = t % p.n_tiles;
-            const int row = nt_i * PG_BM + r;
-            const float *srow = scales + (size_t)(row < p.N ? row : 0) * groups + half;
-            const bool live_row = row < p.N;
-            float sc_next = live_row ? __ldg(srow) : 0.0f;
+            // this thread's weight row in each of the NA tiles, its scale pointer, the scale of block 0
+            const float *srow[NA];
+            bool live_row[NA];
+            float sc_next[NA];
+#pragma unroll
+            for (int a = 0; a < NA; ++a) {
+                const int row = nt_i * (NA * PG_BM) + a * PG_BM + r;
+                live_row[a] = row < p.N;
+                srow[a] = scales + (size_t)(live_row[a] ? row : 0) * groups + half;
+                sc_next[a] = live_row[a] ? __ldg(srow[a]) : 0.0f;
+            }
             for (int kb = 0; kb < p.k_blocks; ++kb) {
-                const float sc = sc_next;
-                // the next block's scale travels while this block is converted
-                if (kb + 1 < p.k_blocks && live_row) sc_next = __ldg(srow + (kb + 1) * 2);
+                float sc[NA];
+#pragma unroll
+                for (int a = 0; a < NA; ++a) {
+                    sc[a] = sc_next[a];
+                    // the next block's scale travels while this block is converted
+                    if (kb + 1 < p.k_blocks && live_row[a]) sc_next[a] = __ldg(srow[a] + (kb + 1) * 2);
+                }
                 alive = mbar_wait(bar_full + slot * 8, phase, status) &&
                         mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
-                const unsigned char *st = smem + 2 * A_TILE + (size_t)slot * p.stage_bytes + act_bytes;
-                const uint4 w4 = *reinterpret_cast<const uint4 *>(st + r * 32 + half * 16);
-                const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
-                const __nv_bfloat162 s = __float2bfloat162_rn(sc);
-                unsigned char *arow = smem + (size_t)abuf * A_TILE + (size_t)r * 128;
+                const unsigned char *st = smem + 2 * A_BUF + (size_t)slot * p.stage_bytes + act_bytes;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t w = words[i];
-                    uint32_t x[4];
-                    // 0x4300 | (nibble ^ 8) is the bf16 value 136 + q, exactly
-                    asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[0]) : "r"(w));
-                    asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[1]) : "r"(w >> 4));
-                    asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[2]) : "r"(w >> 8));
-                    asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[3]) : "r"(w >> 12));
-                    uint4 o;
-                    uint32_t *ov = &o.x;
+                for (int a = 0; a < NA; ++a) {
+                    const uint4 w4 = *reinterpret_cast<const uint4 *>(st + (a * PG_BM + r) * 32 + half * 16);
+                    const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+                    const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[a]);
+                    unsigned char *arow = smem + (size_t)abuf * A_BUF + (size_t)a * A_TILE + (size_t)r * 128;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&x[j]);
-                        v = __hmul2(__hsub2(v, bias), s);
-                        ov[j] = *reinterpret_cast<uint32_t *>(&v);
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t w = words[i];
+                        uint32_t x[4];
+                        // 0x4300 | (nibble ^ 8) is the bf16 value 136 + q, exactly
+                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[0]) : "r"(w));
+                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[1]) : "r"(w >> 4));
+                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[2]) : "r"(w >> 8));
+                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[3]) : "r"(w >> 12));
+                        uint4 o;
+                        uint32_t *ov = &o.x;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&x[j]);
+                            v = __hmul2(__hsub2(v, bias), s2);
+                            ov[j] = *reinterpret_cast<uint32_t *>(&v);
+                        }
+                        // 16-byte chunk c of row r sits at chunk c ^ (r & 7) (128-byte swizzle)
+                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + i) ^ (r & 7)) << 4)) = o;
                     }
-                    // 16-byte chunk c of row r sits at chunk c ^ (r & 7) (128-byte swizzle)
-                    *reinterpret_cast<uint4 *>(arow + (((half * 4 + i) ^ (r & 7)) << 4)) = o;
                 }
                 // make the generic-proxy writes visible to the tensor core's async proxy
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -279,23 +303,26 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
             alive = mbar_wait(bar_tfull + tbuf * 8, tphase, status);
             if (!alive) break;
             pg_fence_after();
-            const int n = nt_i * PG_BM + q * 32 + lane;           // output channel of this lane
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)tbuf * 256;
 #pragma unroll 1
-            for (int c0 = 0; c0 < acc_cols; c0 += 32) {
-                uint32_t rr[32];
-                pg_tmem_ld32(taddr + c0, rr);
-                const int tok0 = tc * acc_cols + c0;
-                if (n < p.N) {
+            for (int a = 0; a < NA; ++a) {
+                const int n = nt_i * (NA * PG_BM) + a * PG_BM + q * 32 + lane;   // output channel of this lane
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)tbuf * 256 + (uint32_t)(a * acc_cols);
+#pragma unroll 1
+                for (int c0 = 0; c0 < acc_cols; c0 += 32) {
+                    uint32_t rr[32];
+                    pg_tmem_ld32(taddr + c0, rr);
+                    const int tok0 = tc * acc_cols + c0;
+                    if (n < p.N) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (tok0 + j < p.M) out[(size_t)(tok0 + j) * p.N + n] = __uint_as_float(rr[j]);
+                        for (int j = 0; j < 32; ++j)
+                            if (tok0 + j < p.M) out[(size_t)(tok0 + j) * p.N + n] = __uint_as_float(rr[j]);
+                    }
                 }
             }
             pg_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + tbuf * 8);
-            if (++tbuf == 2) { tbuf = 0; tphase ^= 1u; }
+            if (++tbuf == p.acc_bufs) { tbuf = 0; tphase ^= 1u; }
         }
     }
 
@@ -320,18 +347,28 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     p.M = (int)m;
     p.N = (int)n;
     p.K = (int)k;
-    // token tiling: up to 256 tokens per pass, one MMA tile (N = BT, a multiple of 16)
+    // Two 128-row weight tiles per CTA tile (256 rows x up to 256 tokens, the two accumulators
+    // filling all 512 TMEM columns, so the epilogue no longer overlaps the next tile) when that
+    // still gives every SM a tile: the activation tile, nine tenths of the L2 -> SM traffic, is
+    // then fetched once per 256 weight rows (2048 x 8192 x 8192: 918 -> 1121 TFLOP/s; 256 rows x
+    // 128 tokens with double-buffered accumulators measured 664: N = 128 MMAs read a third more
+    // shared memory per flop). Otherwise one weight tile x up to 256 tokens, accumulators
+    // double-buffered. One MMA tile per pass (N = BT, a multiple of 16).
     const int m16 = (int)((m + 15) / 16 * 16);
-    p.BT = m16 <= 256 ? m16 : 256;
+    const size_t tiles2 = ((n + 2 * PG_BM - 1) / (2 * PG_BM)) * ((m + 255) / 256);
+    const int NA = (m16 > 128 && tiles2 >= (size_t)ctx->sm_count) ? 2 : 1;
+    const int bt_max = 256;
+    p.BT = m16 <= bt_max ? m16 : bt_max;
     p.NT = 1;
     const int acc_cols = p.BT * p.NT;
-    p.n_tiles = (p.N + PG_BM - 1) / PG_BM;
+    p.acc_bufs = NA * acc_cols > 256 ? 1 : 2;
+    p.n_tiles = (p.N + NA * PG_BM - 1) / (NA * PG_BM);
     p.t_chunks = (p.M + acc_cols - 1) / acc_cols;
     p.k_blocks = p.K / PG_BK;
-    p.stage_bytes = ((p.NT * p.BT * 128 + PG_BM * 32 + 1023) / 1024) * 1024;
-    p.stages = (227 * 1024 - 2 * PG_BM * PG_BK * 2 - 1024) / p.stage_bytes;
+    p.stage_bytes = ((p.NT * p.BT * 128 + NA * PG_BM * 32 + 1023) / 1024) * 1024;
+    p.stages = (227 * 1024 - 2 * NA * PG_BM * PG_BK * 2 - 1024) / p.stage_bytes;
     if (p.stages > 8) p.stages = 8;
-    const int smem = 2 * PG_BM * PG_BK * 2 + p.stages * p.stage_bytes + 256;
+    const int smem = 2 * NA * PG_BM * PG_BK * 2 + p.stages * p.stage_bytes + 256;
 
     __nv_bfloat16 *abf = reinterpret_cast<__nv_bfloat16 *>(scratch);
     const size_t groups8 = m * k / 8;
@@ -341,20 +378,21 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     ctx->launches++;
 
     CUtensorMap tm_w, tm_a;
-    int rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, n, k / 2, k / 2, PG_BM, 32,
+    int rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, n, k / 2, k / 2, (uint32_t)(NA * PG_BM), 32,
                        CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, m, k, k * 2, (uint32_t)p.BT, PG_BK,
                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    auto kern = NA == 2 ? int4_prefill_gemm_kernel<2> : int4_prefill_gemm_kernel<1>;
     {
-        const int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(int4_prefill_gemm_kernel), ctx->device, 227 * 1024);
+        const int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
         if (arc) return arc;
     }
     const int tiles = p.n_tiles * p.t_chunks;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     ctx->prof_begin();
-    int4_prefill_gemm_kernel<<<grid, PG_THREADS, smem, ctx->stream>>>(tm_w, tm_a, scales, out, p, ctx->d_status);
+    kern<<<grid, PG_THREADS, smem, ctx->stream>>>(tm_w, tm_a, scales, out, p, ctx->d_status);
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
