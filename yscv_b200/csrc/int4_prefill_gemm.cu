@@ -47,6 +47,10 @@ struct PGParams {
     int n_tiles, t_chunks, k_blocks;
     int stages, stage_bytes;
     int acc_bufs;        // accumulator buffers in TMEM: 2, or 1 when one buffer takes all 512 columns
+    // K split (few tiles, e.g. a decode batch of 64 against 8192 weight rows): work item
+    // (tile, slice) covers k blocks [slice * kb_per, ...) and writes its fp32 partial sums into
+    // slice `slice` of a workspace [ksplit][M][N]; a second kernel adds the slices in order.
+    int ksplit, kb_per;
 };
 
 __device__ __forceinline__ void pg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -136,7 +140,7 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     const uint32_t bar_full = bars, bar_empty = bars + 64, bar_afull = bars + 128, bar_aempty = bars + 144;
     const uint32_t bar_tfull = bars + 160, bar_tempty = bars + 176;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 2 * A_BUF + (size_t)p.stages * p.stage_bytes + 192);
-    const int tiles = p.n_tiles * p.t_chunks;
+    const int tiles = p.n_tiles * p.t_chunks * p.ksplit;
     const int acc_cols = p.NT * p.BT;              // tokens per pass; NA * acc_cols TMEM columns per accumulator buffer (<= 256)
 
     if (tid == 0) {
@@ -169,8 +173,9 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
             uint32_t phase = 0;
             bool alive = true;
             for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
-                const int nt_i = t % p.n_tiles, tc = t / p.n_tiles;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                const int nt_i = t % p.n_tiles, ks = (t / p.n_tiles) % p.ksplit, tc = t / (p.n_tiles * p.ksplit);
+                const int kb0 = ks * p.kb_per, kb1 = min(p.k_blocks, kb0 + p.kb_per);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
                     if (!alive) break;
                     const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
@@ -197,7 +202,8 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                 if (!alive) break;
                 pg_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)tbuf * 256;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                const int kb0 = ((t / p.n_tiles) % p.ksplit) * p.kb_per, kb1 = min(p.k_blocks, kb0 + p.kb_per);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     alive = mbar_wait(bar_full + slot * 8, phase, status) &&
                             mbar_wait(bar_afull + abuf * 8, aphase, status);
                     if (!alive) break;
@@ -211,7 +217,7 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
 #pragma unroll
                             for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
                                 pg_mma_bf16(tacc + a * acc_cols + j * p.BT, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2),
-                                            idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                                            idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
                         }
                     }
                     pg_commit(bar_empty + slot * 8);
@@ -234,7 +240,8 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
         for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
             const int nt_i = t % p.n_tiles;
-            // this thread's weight row in each of the NA tiles, its scale pointer, the scale of block 0
+            const int kb0 = ((t / p.n_tiles) % p.ksplit) * p.kb_per, kb1 = min(p.k_blocks, kb0 + p.kb_per);
+            // this thread's weight row in each of the NA tiles, its scale pointer, the scale of the first block
             const float *srow[NA];
             bool live_row[NA];
             float sc_next[NA];
@@ -243,15 +250,15 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                 const int row = nt_i * (NA * PG_BM) + a * PG_BM + r;
                 live_row[a] = row < p.N;
                 srow[a] = scales + (size_t)(live_row[a] ? row : 0) * groups + half;
-                sc_next[a] = live_row[a] ? __ldg(srow[a]) : 0.0f;
+                sc_next[a] = live_row[a] ? __ldg(srow[a] + kb0 * 2) : 0.0f;
             }
-            for (int kb = 0; kb < p.k_blocks; ++kb) {
+            for (int kb = kb0; kb < kb1; ++kb) {
                 float sc[NA];
 #pragma unroll
                 for (int a = 0; a < NA; ++a) {
                     sc[a] = sc_next[a];
                     // the next block's scale travels while this block is converted
-                    if (kb + 1 < p.k_blocks && live_row[a]) sc_next[a] = __ldg(srow[a] + (kb + 1) * 2);
+                    if (kb + 1 < kb1 && live_row[a]) sc_next[a] = __ldg(srow[a] + (kb + 1) * 2);
                 }
                 alive = mbar_wait(bar_full + slot * 8, phase, status) &&
                         mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
@@ -299,7 +306,8 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         uint32_t tphase = 0;
         bool alive = true;
         for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
-            const int nt_i = t % p.n_tiles, tc = t / p.n_tiles;
+            const int nt_i = t % p.n_tiles, ks = (t / p.n_tiles) % p.ksplit, tc = t / (p.n_tiles * p.ksplit);
+            float *const o_base = out + (size_t)ks * p.M * p.N;   // (ksplit > 1: `out` is the workspace)
             alive = mbar_wait(bar_tfull + tbuf * 8, tphase, status);
             if (!alive) break;
             pg_fence_after();
@@ -315,7 +323,7 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                     if (n < p.N) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (tok0 + j < p.M) out[(size_t)(tok0 + j) * p.N + n] = __uint_as_float(rr[j]);
+                            if (tok0 + j < p.M) o_base[(size_t)(tok0 + j) * p.N + n] = __uint_as_float(rr[j]);
                     }
                 }
             }
@@ -334,6 +342,21 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     }
 }
 
+// out = slice 0 + slice 1 + ... of the K-split workspace, in that order
+__global__ void __launch_bounds__(256) add_kslices_kernel(const float4 *__restrict__ ws, float4 *__restrict__ out,
+                                                          size_t n4, int slices) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 a = ws[i];
+        for (int s = 1; s < slices; ++s) {
+            const float4 b = ws[(size_t)s * n4 + i];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        out[i] = a;
+    }
+}
+
 size_t int4_prefill_scratch_bytes(size_t m, size_t k) { return m * k * 2 + 256; }
 
 bool int4_prefill_supported(size_t m, size_t n, size_t k, size_t gs) {
@@ -344,6 +367,7 @@ bool int4_prefill_supported(size_t m, size_t n, size_t k, size_t gs) {
 int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, const float *act,
                       float *out, size_t m, size_t n, size_t k, void *scratch) {
     PGParams p = {};
+    int rc_ws = 0;
     p.M = (int)m;
     p.N = (int)n;
     p.K = (int)k;
@@ -369,6 +393,24 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     p.stages = (227 * 1024 - 2 * NA * PG_BM * PG_BK * 2 - 1024) / p.stage_bytes;
     if (p.stages > 8) p.stages = 8;
     const int smem = 2 * NA * PG_BM * PG_BK * 2 + p.stages * p.stage_bytes + 256;
+    // few tiles (a wide decode batch against a narrow matrix): split K so that most SMs get a piece
+    p.ksplit = 1;
+    {
+        const int base_tiles = p.n_tiles * p.t_chunks;
+        if (base_tiles * 2 <= ctx->sm_count && (m * n) % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+            int s = ctx->sm_count / base_tiles;
+            if (s > 8) s = 8;
+            while (s > 1 && p.k_blocks / s < 8) --s;   // at least 8 k blocks per piece
+            p.ksplit = s;
+        }
+    }
+    p.kb_per = (p.k_blocks + p.ksplit - 1) / p.ksplit;
+    float *kernel_out = out;
+    if (p.ksplit > 1) {
+        rc_ws = ctx->gemm_ws.reserve((size_t)p.ksplit * m * n * sizeof(float));
+        if (rc_ws) return rc_ws;
+        kernel_out = reinterpret_cast<float *>(ctx->gemm_ws.ptr);
+    }
 
     __nv_bfloat16 *abf = reinterpret_cast<__nv_bfloat16 *>(scratch);
     const size_t groups8 = m * k / 8;
@@ -389,13 +431,20 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
         const int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
         if (arc) return arc;
     }
-    const int tiles = p.n_tiles * p.t_chunks;
+    const int tiles = p.n_tiles * p.t_chunks * p.ksplit;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     ctx->prof_begin();
-    kern<<<grid, PG_THREADS, smem, ctx->stream>>>(tm_w, tm_a, scales, out, p, ctx->d_status);
+    kern<<<grid, PG_THREADS, smem, ctx->stream>>>(tm_w, tm_a, scales, kernel_out, p, ctx->d_status);
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
+    if (p.ksplit > 1) {
+        const size_t n4 = m * n / 4;
+        const unsigned blocks = (unsigned)((n4 + 255) / 256 < 1184 ? (n4 + 255) / 256 : 1184);
+        YSCV_CUDA_TRY(launch_pdl(add_kslices_kernel, dim3(blocks), dim3(256), 0, ctx->stream,
+                                 reinterpret_cast<const float4 *>(kernel_out), reinterpret_cast<float4 *>(out), n4, p.ksplit));
+        ctx->launches++;
+    }
     ctx->last_kernel = "int4_prefill_gemm(tcgen05,bf16)";
     return YSCV_CUDA_OK;
 }
