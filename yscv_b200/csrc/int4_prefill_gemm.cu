@@ -51,6 +51,10 @@ struct PGParams {
     // (tile, slice) covers k blocks [slice * kb_per, ...) and writes its fp32 partial sums into
     // slice `slice` of a workspace [ksplit][M][N]; a second kernel adds the slices in order.
     int ksplit, kb_per;
+    // k sub-blocks of 64 per ring stage and hand-over (1 or 2). With narrow token tiles a block's
+    // MMAs are short and a hand-over (dequantised tile -> MMA -> buffer back) costs ~1000 cycles
+    // whatever the work: two sub-blocks per hand-over halve their number. k_blocks, kb_per count stages.
+    int ksub;
 };
 
 __device__ __forceinline__ void pg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -128,14 +132,15 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                          int *__restrict__ status) {
     constexpr int W_BYTES = NA * PG_BM * 32;       // packed nibbles of one k block: 4 KB per 128 rows
     constexpr int A_TILE = PG_BM * PG_BK * 2;      // dequantised bf16 tile of 128 rows: 16 KB
-    constexpr int A_BUF = NA * A_TILE;             // one buffer of dequantised tiles
+    const int A_BUF = p.ksub * NA * A_TILE;        // one buffer of dequantised tiles: [sub-block][weight tile]
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = smem_u32(smem);
     // [A buffer 0][A buffer 1][stages x {act tiles NT*BT*128 B | packed nibbles}][barriers][tmem slot]
     const uint32_t a_tiles = smem_base;
     const uint32_t ring = smem_base + 2 * A_BUF;
-    const int act_bytes = p.NT * p.BT * 128;
+    const int act_bytes = p.NT * p.BT * 128;       // activation tile of one sub-block; a stage holds
+                                                   // [ksub activation tiles][ksub packed tiles]
     const uint32_t bars = ring + (uint32_t)p.stages * p.stage_bytes;
     const uint32_t bar_full = bars, bar_empty = bars + 64, bar_afull = bars + 128, bar_aempty = bars + 144;
     const uint32_t bar_tfull = bars + 160, bar_tempty = bars + 176;
@@ -180,10 +185,13 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                     if (!alive) break;
                     const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
                     const uint32_t full = bar_full + slot * 8;
-                    mbar_expect_tx(full, (uint32_t)(act_bytes + W_BYTES));
-                    for (int j = 0; j < p.NT; ++j)
-                        tma_load_2d(st + j * (p.BT * 128), &tm_a, kb * PG_BK, tc * acc_cols + j * p.BT, full);
-                    tma_load_2d(st + act_bytes, &tm_w, kb * 32, nt_i * (NA * PG_BM), full);
+                    mbar_expect_tx(full, (uint32_t)(p.ksub * (act_bytes + W_BYTES)));
+                    for (int sub = 0; sub < p.ksub; ++sub) {
+                        const int kx = kb * p.ksub + sub;   // 64-k block
+                        for (int j = 0; j < p.NT; ++j)
+                            tma_load_2d(st + sub * act_bytes + j * (p.BT * 128), &tm_a, kx * PG_BK, tc * acc_cols + j * p.BT, full);
+                        tma_load_2d(st + p.ksub * act_bytes + sub * W_BYTES, &tm_w, kx * 32, nt_i * (NA * PG_BM), full);
+                    }
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
             }
@@ -209,15 +217,17 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                     if (!alive) break;
                     pg_fence_after();
                     const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
+                    for (int sub = 0; sub < p.ksub; ++sub) {
 #pragma unroll
-                    for (int a = 0; a < NA; ++a) {
-                        const uint64_t da = pg_desc_sw128(a_tiles + abuf * A_BUF + a * A_TILE);
-                        for (int j = 0; j < p.NT; ++j) {
-                            const uint64_t db = pg_desc_sw128(st + j * (p.BT * 128));
+                        for (int a = 0; a < NA; ++a) {
+                            const uint64_t da = pg_desc_sw128(a_tiles + abuf * A_BUF + (sub * NA + a) * A_TILE);
+                            for (int j = 0; j < p.NT; ++j) {
+                                const uint64_t db = pg_desc_sw128(st + sub * act_bytes + j * (p.BT * 128));
 #pragma unroll
-                            for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
-                                pg_mma_bf16(tacc + a * acc_cols + j * p.BT, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2),
-                                            idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+                                for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
+                                    pg_mma_bf16(tacc + a * acc_cols + j * p.BT, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2),
+                                                idesc, (kb > kb0 || sub > 0 || kk > 0) ? 1u : 0u);
+                            }
                         }
                     }
                     pg_commit(bar_empty + slot * 8);
@@ -244,51 +254,62 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
             // this thread's weight row in each of the NA tiles, its scale pointer, the scale of the first block
             const float *srow[NA];
             bool live_row[NA];
-            float sc_next[NA];
+            float sc_next[2][NA];   // [sub-block][weight tile]
 #pragma unroll
             for (int a = 0; a < NA; ++a) {
                 const int row = nt_i * (NA * PG_BM) + a * PG_BM + r;
                 live_row[a] = row < p.N;
                 srow[a] = scales + (size_t)(live_row[a] ? row : 0) * groups + half;
-                sc_next[a] = live_row[a] ? __ldg(srow[a] + kb0 * 2) : 0.0f;
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub)
+                    sc_next[sub][a] = (live_row[a] && sub < p.ksub) ? __ldg(srow[a] + (kb0 * p.ksub + sub) * 2) : 0.0f;
             }
             for (int kb = kb0; kb < kb1; ++kb) {
-                float sc[NA];
+                float sc[2][NA];
 #pragma unroll
-                for (int a = 0; a < NA; ++a) {
-                    sc[a] = sc_next[a];
-                    // the next block's scale travels while this block is converted
-                    if (kb + 1 < kb1 && live_row[a]) sc_next[a] = __ldg(srow[a] + (kb + 1) * 2);
+                for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+                    for (int a = 0; a < NA; ++a) {
+                        sc[sub][a] = sc_next[sub][a];
+                        // the next stage's scales travel while this one is converted
+                        if (kb + 1 < kb1 && live_row[a] && sub < p.ksub)
+                            sc_next[sub][a] = __ldg(srow[a] + ((kb + 1) * p.ksub + sub) * 2);
+                    }
                 }
                 alive = mbar_wait(bar_full + slot * 8, phase, status) &&
                         mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
-                const unsigned char *st = smem + 2 * A_BUF + (size_t)slot * p.stage_bytes + act_bytes;
+                const unsigned char *st = smem + 2 * A_BUF + (size_t)slot * p.stage_bytes + p.ksub * act_bytes;
 #pragma unroll
-                for (int a = 0; a < NA; ++a) {
-                    const uint4 w4 = *reinterpret_cast<const uint4 *>(st + (a * PG_BM + r) * 32 + half * 16);
-                    const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
-                    const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[a]);
-                    unsigned char *arow = smem + (size_t)abuf * A_BUF + (size_t)a * A_TILE + (size_t)r * 128;
+                for (int sub = 0; sub < 2; ++sub) {
+                    if (sub < p.ksub) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t w = words[i];
-                        uint32_t x[4];
-                        // 0x4300 | (nibble ^ 8) is the bf16 value 136 + q, exactly
-                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[0]) : "r"(w));
-                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[1]) : "r"(w >> 4));
-                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[2]) : "r"(w >> 8));
-                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[3]) : "r"(w >> 12));
-                        uint4 o;
-                        uint32_t *ov = &o.x;
+                        for (int a = 0; a < NA; ++a) {
+                            const uint4 w4 = *reinterpret_cast<const uint4 *>(st + sub * W_BYTES + (a * PG_BM + r) * 32 + half * 16);
+                            const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+                            const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[sub][a]);
+                            unsigned char *arow = smem + (size_t)abuf * A_BUF + (size_t)(sub * NA + a) * A_TILE + (size_t)r * 128;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&x[j]);
-                            v = __hmul2(__hsub2(v, bias), s2);
-                            ov[j] = *reinterpret_cast<uint32_t *>(&v);
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t w = words[i];
+                                uint32_t x[4];
+                                // 0x4300 | (nibble ^ 8) is the bf16 value 136 + q, exactly
+                                asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[0]) : "r"(w));
+                                asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[1]) : "r"(w >> 4));
+                                asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[2]) : "r"(w >> 8));
+                                asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[3]) : "r"(w >> 12));
+                                uint4 o;
+                                uint32_t *ov = &o.x;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&x[j]);
+                                    v = __hmul2(__hsub2(v, bias), s2);
+                                    ov[j] = *reinterpret_cast<uint32_t *>(&v);
+                                }
+                                // 16-byte chunk c of row r sits at chunk c ^ (r & 7) (128-byte swizzle)
+                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + i) ^ (r & 7)) << 4)) = o;
+                            }
                         }
-                        // 16-byte chunk c of row r sits at chunk c ^ (r & 7) (128-byte swizzle)
-                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + i) ^ (r & 7)) << 4)) = o;
                     }
                 }
                 // make the generic-proxy writes visible to the tensor core's async proxy
@@ -388,11 +409,13 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     p.acc_bufs = NA * acc_cols > 256 ? 1 : 2;
     p.n_tiles = (p.N + NA * PG_BM - 1) / (NA * PG_BM);
     p.t_chunks = (p.M + acc_cols - 1) / acc_cols;
-    p.k_blocks = p.K / PG_BK;
-    p.stage_bytes = ((p.NT * p.BT * 128 + NA * PG_BM * 32 + 1023) / 1024) * 1024;
-    p.stages = (227 * 1024 - 2 * NA * PG_BM * PG_BK * 2 - 1024) / p.stage_bytes;
+    // narrow token tiles: two 64-k sub-blocks per stage and hand-over (see PGParams)
+    p.ksub = (NA == 1 && p.BT <= 128 && p.K % (2 * PG_BK) == 0) ? 2 : 1;
+    p.k_blocks = p.K / (PG_BK * p.ksub);
+    p.stage_bytes = ((p.ksub * (p.NT * p.BT * 128 + NA * PG_BM * 32) + 1023) / 1024) * 1024;
+    p.stages = (227 * 1024 - 2 * p.ksub * NA * PG_BM * PG_BK * 2 - 1024) / p.stage_bytes;
     if (p.stages > 8) p.stages = 8;
-    const int smem = 2 * NA * PG_BM * PG_BK * 2 + p.stages * p.stage_bytes + 256;
+    const int smem = 2 * p.ksub * NA * PG_BM * PG_BK * 2 + p.stages * p.stage_bytes + 256;
     // few tiles (a wide decode batch against a narrow matrix): split K so that most SMs get a piece
     p.ksplit = 1;
     {
@@ -400,7 +423,7 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
         if (base_tiles * 2 <= ctx->sm_count && (m * n) % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
             int s = ctx->sm_count / base_tiles;
             if (s > 8) s = 8;
-            while (s > 1 && p.k_blocks / s < 8) --s;   // at least 8 k blocks per piece
+            while (s > 1 && p.k_blocks / s < 8 / p.ksub) --s;   // at least 512 k per piece
             p.ksplit = s;
         }
     }
