@@ -125,14 +125,16 @@ __global__ void act_to_bf16_kernel(const float *__restrict__ act, __nv_bfloat16 
 // fetched once for 256 weight rows: the kernel is bound by what the SMs pull through the crossbar
 // from L2 (with the dequantisation switched off and three quarters of the MMAs left out it still
 // takes 0.8 of its time), and the activation tile is nine tenths of that.
-template <int NA>
+// KSUB = 64-k sub-blocks per ring stage and hand-over (1 or 2; PGParams::ksub); SPLITK: the tiles'
+// K loops may be cut into slices (PGParams::ksplit > 1), else every tile walks all of K
+template <int NA, int KSUB, bool SPLITK>
 __global__ void __launch_bounds__(PG_THREADS, 1)
 int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                          const float *__restrict__ scales, float *__restrict__ out, PGParams p,
                          int *__restrict__ status) {
     constexpr int W_BYTES = NA * PG_BM * 32;       // packed nibbles of one k block: 4 KB per 128 rows
     constexpr int A_TILE = PG_BM * PG_BK * 2;      // dequantised bf16 tile of 128 rows: 16 KB
-    const int A_BUF = p.ksub * NA * A_TILE;        // one buffer of dequantised tiles: [sub-block][weight tile]
+    constexpr int A_BUF = KSUB * NA * A_TILE;      // one buffer of dequantised tiles: [sub-block][weight tile]
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = smem_u32(smem);
@@ -145,7 +147,7 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     const uint32_t bar_full = bars, bar_empty = bars + 64, bar_afull = bars + 128, bar_aempty = bars + 144;
     const uint32_t bar_tfull = bars + 160, bar_tempty = bars + 176;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 2 * A_BUF + (size_t)p.stages * p.stage_bytes + 192);
-    const int tiles = p.n_tiles * p.t_chunks * p.ksplit;
+    const int tiles = p.n_tiles * p.t_chunks * (SPLITK ? p.ksplit : 1);
     const int acc_cols = p.NT * p.BT;              // tokens per pass; NA * acc_cols TMEM columns per accumulator buffer (<= 256)
 
     if (tid == 0) {
@@ -178,19 +180,21 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
             uint32_t phase = 0;
             bool alive = true;
             for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
-                const int nt_i = t % p.n_tiles, ks = (t / p.n_tiles) % p.ksplit, tc = t / (p.n_tiles * p.ksplit);
-                const int kb0 = ks * p.kb_per, kb1 = min(p.k_blocks, kb0 + p.kb_per);
+                const int ksplit = SPLITK ? p.ksplit : 1;
+                const int nt_i = t % p.n_tiles, ks = SPLITK ? (t / p.n_tiles) % ksplit : 0, tc = t / (p.n_tiles * ksplit);
+                const int kb0 = SPLITK ? ks * p.kb_per : 0, kb1 = SPLITK ? min(p.k_blocks, kb0 + p.kb_per) : p.k_blocks;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
                     if (!alive) break;
                     const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
                     const uint32_t full = bar_full + slot * 8;
-                    mbar_expect_tx(full, (uint32_t)(p.ksub * (act_bytes + W_BYTES)));
-                    for (int sub = 0; sub < p.ksub; ++sub) {
-                        const int kx = kb * p.ksub + sub;   // 64-k block
+                    mbar_expect_tx(full, (uint32_t)(KSUB * (act_bytes + W_BYTES)));
+                    #pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub) {
+                        const int kx = kb * KSUB + sub;   // 64-k block
                         for (int j = 0; j < p.NT; ++j)
                             tma_load_2d(st + sub * act_bytes + j * (p.BT * 128), &tm_a, kx * PG_BK, tc * acc_cols + j * p.BT, full);
-                        tma_load_2d(st + p.ksub * act_bytes + sub * W_BYTES, &tm_w, kx * 32, nt_i * (NA * PG_BM), full);
+                        tma_load_2d(st + KSUB * act_bytes + sub * W_BYTES, &tm_w, kx * 32, nt_i * (NA * PG_BM), full);
                     }
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
@@ -210,14 +214,16 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                 if (!alive) break;
                 pg_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)tbuf * 256;
-                const int kb0 = ((t / p.n_tiles) % p.ksplit) * p.kb_per, kb1 = min(p.k_blocks, kb0 + p.kb_per);
+                const int kb0 = SPLITK ? ((t / p.n_tiles) % p.ksplit) * p.kb_per : 0;
+                const int kb1 = SPLITK ? min(p.k_blocks, kb0 + p.kb_per) : p.k_blocks;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     alive = mbar_wait(bar_full + slot * 8, phase, status) &&
                             mbar_wait(bar_afull + abuf * 8, aphase, status);
                     if (!alive) break;
                     pg_fence_after();
                     const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
-                    for (int sub = 0; sub < p.ksub; ++sub) {
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub) {
 #pragma unroll
                         for (int a = 0; a < NA; ++a) {
                             const uint64_t da = pg_desc_sw128(a_tiles + abuf * A_BUF + (sub * NA + a) * A_TILE);
@@ -250,39 +256,40 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
         for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
             const int nt_i = t % p.n_tiles;
-            const int kb0 = ((t / p.n_tiles) % p.ksplit) * p.kb_per, kb1 = min(p.k_blocks, kb0 + p.kb_per);
+            const int kb0 = SPLITK ? ((t / p.n_tiles) % p.ksplit) * p.kb_per : 0;
+            const int kb1 = SPLITK ? min(p.k_blocks, kb0 + p.kb_per) : p.k_blocks;
             // this thread's weight row in each of the NA tiles, its scale pointer, the scale of the first block
             const float *srow[NA];
             bool live_row[NA];
-            float sc_next[2][NA];   // [sub-block][weight tile]
+            float sc_next[KSUB][NA];   // [sub-block][weight tile]
 #pragma unroll
             for (int a = 0; a < NA; ++a) {
                 const int row = nt_i * (NA * PG_BM) + a * PG_BM + r;
                 live_row[a] = row < p.N;
                 srow[a] = scales + (size_t)(live_row[a] ? row : 0) * groups + half;
 #pragma unroll
-                for (int sub = 0; sub < 2; ++sub)
-                    sc_next[sub][a] = (live_row[a] && sub < p.ksub) ? __ldg(srow[a] + (kb0 * p.ksub + sub) * 2) : 0.0f;
+                for (int sub = 0; sub < KSUB; ++sub)
+                    sc_next[sub][a] = live_row[a] ? __ldg(srow[a] + (kb0 * KSUB + sub) * 2) : 0.0f;
             }
             for (int kb = kb0; kb < kb1; ++kb) {
-                float sc[2][NA];
+                float sc[KSUB][NA];
 #pragma unroll
-                for (int sub = 0; sub < 2; ++sub) {
+                for (int sub = 0; sub < KSUB; ++sub) {
 #pragma unroll
                     for (int a = 0; a < NA; ++a) {
                         sc[sub][a] = sc_next[sub][a];
                         // the next stage's scales travel while this one is converted
-                        if (kb + 1 < kb1 && live_row[a] && sub < p.ksub)
-                            sc_next[sub][a] = __ldg(srow[a] + ((kb + 1) * p.ksub + sub) * 2);
+                        if (kb + 1 < kb1 && live_row[a])
+                            sc_next[sub][a] = __ldg(srow[a] + ((kb + 1) * KSUB + sub) * 2);
                     }
                 }
                 alive = mbar_wait(bar_full + slot * 8, phase, status) &&
                         mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
-                const unsigned char *st = smem + 2 * A_BUF + (size_t)slot * p.stage_bytes + p.ksub * act_bytes;
+                const unsigned char *st = smem + 2 * A_BUF + (size_t)slot * p.stage_bytes + KSUB * act_bytes;
 #pragma unroll
-                for (int sub = 0; sub < 2; ++sub) {
-                    if (sub < p.ksub) {
+                for (int sub = 0; sub < KSUB; ++sub) {
+                    {
 #pragma unroll
                         for (int a = 0; a < NA; ++a) {
                             const uint4 w4 = *reinterpret_cast<const uint4 *>(st + sub * W_BYTES + (a * PG_BM + r) * 32 + half * 16);
@@ -327,8 +334,9 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         uint32_t tphase = 0;
         bool alive = true;
         for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
-            const int nt_i = t % p.n_tiles, ks = (t / p.n_tiles) % p.ksplit, tc = t / (p.n_tiles * p.ksplit);
-            float *const o_base = out + (size_t)ks * p.M * p.N;   // (ksplit > 1: `out` is the workspace)
+            const int ksplit = SPLITK ? p.ksplit : 1;
+            const int nt_i = t % p.n_tiles, ks = SPLITK ? (t / p.n_tiles) % ksplit : 0, tc = t / (p.n_tiles * ksplit);
+            float *const o_base = SPLITK ? out + (size_t)ks * p.M * p.N : out;   // (ksplit > 1: `out` is the workspace)
             alive = mbar_wait(bar_tfull + tbuf * 8, tphase, status);
             if (!alive) break;
             pg_fence_after();
@@ -420,7 +428,7 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     p.ksplit = 1;
     {
         const int base_tiles = p.n_tiles * p.t_chunks;
-        if (base_tiles * 2 <= ctx->sm_count && (m * n) % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        if (NA == 1 && base_tiles * 2 <= ctx->sm_count && (m * n) % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
             int s = ctx->sm_count / base_tiles;
             if (s > 8) s = 8;
             while (s > 1 && p.k_blocks / s < 8 / p.ksub) --s;   // at least 512 k per piece
@@ -449,7 +457,9 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, m, k, k * 2, (uint32_t)p.BT, PG_BK,
                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    auto kern = NA == 2 ? int4_prefill_gemm_kernel<2> : int4_prefill_gemm_kernel<1>;
+    auto kern = NA == 2 ? int4_prefill_gemm_kernel<2, 1, false>
+                        : p.ksub == 2 ? (p.ksplit > 1 ? int4_prefill_gemm_kernel<1, 2, true> : int4_prefill_gemm_kernel<1, 2, false>)
+                                      : (p.ksplit > 1 ? int4_prefill_gemm_kernel<1, 1, true> : int4_prefill_gemm_kernel<1, 1, false>);
     {
         const int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
         if (arc) return arc;
