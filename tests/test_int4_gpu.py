@@ -92,7 +92,8 @@ def test_odd_shapes(ctx, oracle, m, n, k, g):
 # ---- prefill shapes: tcgen05 bf16 GEMM, relative Frobenius error <= 2e-2 ----------
 
 @pytest.mark.parametrize("m,n,k", [(17, 128, 64), (128, 2560, 2048), (200, 1000, 1024), (333, 130, 4096),
-                                   (512, 4096, 512), (1024, 300, 256), (2048, 1024, 2048)])
+                                   (512, 4096, 512), (1024, 300, 256), (2048, 1024, 2048), (1100, 8000, 512),
+                                   (64, 1024, 4096)])
 def test_prefill_gemm(ctx, oracle, m, n, k):
     g = 32
     packed, scales = make_weights(oracle, 21, n, k, g)
@@ -100,6 +101,11 @@ def test_prefill_gemm(ctx, oracle, m, n, k):
     want = oracle.exec_matmul_int4(packed, scales, act, m, n, k, g, threads=8)
     got = ctx.packed_int4_gemm(packed, scales, act, m, n, k, g)
     assert "prefill" in ctx.last_kernel()
+    report = ctx.dispatch_report()
+    if (m, n, k) == (1100, 8000, 512):     # enough tiles for 256 weight rows x 256 tokens per CTA, ragged in both
+        assert "CTA tile 256 rows x 256 tokens" in report, report
+    if (m, n, k) == (64, 1024, 4096):      # a wide decode batch on a narrow matrix: two sub-blocks, K slices
+        assert "128 k per stage" in report and "8 K slice(s)" in report, report
     e = fro_err(got, want)
     assert e <= FRO_TOL, e
     assert e > 1e-6          # it really is the bf16 path

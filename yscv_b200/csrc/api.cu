@@ -82,9 +82,6 @@ static int int4_matmul_dev(yscv_cuda_ctx *ctx, const uint8_t *d_packed, const fl
         rc = ctx->scratch.reserve(int4_prefill_scratch_bytes(m, k));
         if (rc) return rc;
         op_counters().int4_gemm_calls++;
-        snprintf(ctx->report_int4, sizeof(ctx->report_int4),
-                 "int4_prefill_gemm m=%zu n=%zu k=%zu: tcgen05 bf16, 128-row weight tiles, dequant in shared memory",
-                 m, n, k);
         return int4_prefill_gemm(ctx, d_packed, d_scales, d_act, d_out, m, n, k, ctx->scratch.ptr);
     }
     for (size_t m0 = 0; m0 < m; m0 += 16) {

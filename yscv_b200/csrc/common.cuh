@@ -121,7 +121,7 @@ struct yscv_cuda_ctx {
     int gemm_epoch = 0;
     bool int8_tail_split = true;
     // variant / tile report of the last int4 and int8 dispatch (yscv_cuda_dispatch_report)
-    char report_int4[160] = "none";
+    char report_int4[224] = "none";
     char report_int8[224] = "none";
 };
 

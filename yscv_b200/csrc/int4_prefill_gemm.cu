@@ -478,6 +478,9 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
                                  reinterpret_cast<const float4 *>(kernel_out), reinterpret_cast<float4 *>(out), n4, p.ksplit));
         ctx->launches++;
     }
+    snprintf(ctx->report_int4, sizeof(ctx->report_int4),
+             "int4_prefill_gemm m=%zu n=%zu k=%zu: tcgen05 bf16, CTA tile %d rows x %d tokens, %d k per stage, %d stages, "
+             "%d K slice(s), %d tiles on %d CTAs", m, n, k, NA * PG_BM, p.BT, p.ksub * PG_BK, p.stages, p.ksplit, tiles, grid);
     ctx->last_kernel = "int4_prefill_gemm(tcgen05,bf16)";
     return YSCV_CUDA_OK;
 }
