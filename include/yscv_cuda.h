@@ -127,6 +127,12 @@ int yscv_cuda_ctx_set_int8_cta_pairs(yscv_cuda_ctx *ctx, int enable);
  * status 2). Integer sums do not depend on the order, so the results are identical with the
  * switch off; 0 keeps whole tiles per CTA. */
 int yscv_cuda_ctx_set_int8_tail_split(yscv_cuda_ctx *ctx, int enable);
+/* Decode attention over int8 caches (yscv_cuda_gqa_attention_i8_dev with one query position and a
+ * cache longer than 128, head size 64 or 128): on by default, both contractions run as fp16
+ * tensor-core MMAs with fp32 accumulators (an int8 cache entry is exact in fp16, the query and the
+ * softmax weights are split into two fp16 terms), which differs from the fp32 loop (0) only in
+ * summation order. */
+int yscv_cuda_ctx_set_attention_tensor_cores(yscv_cuda_ctx *ctx, int enable);
 /* Per-kernel timing, the counterpart of YSCV_RUNNER_PROFILE
  * (crates/yscv-onnx/src/runner/profile.rs:1-120): while enabled, the dominant
  * kernel of every call is bracketed by CUDA events on the context's stream

@@ -534,6 +534,41 @@ def test_int8_kv_cache_fused_step_appends_the_same_rows_as_the_chain(tctx):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,pos", [(8, 2, 64, 300), (32, 4, 128, 129), (16, 1, 128, 1000), (8, 8, 64, 0)])
+def test_int8_decode_attention_tensor_core_kernel(tctx, n_q, n_kv, d, pos):
+    """Decode attention over an int8 cache: the fp16 tensor-core kernel (int8 entries exact in
+    fp16, query and softmax weights as two fp16 terms, fp32 accumulation) against the fp32 loop
+    on the same cache: groups of 4, 8, 16 and 1 query heads per KV head, both head sizes, a last
+    chunk that is not full, a single cached position, three sequences at once."""
+    import torch
+    ctx, s = tctx
+    B, max_seq = 3, 1100
+    rng = np.random.default_rng(31)
+    kc = dev(rng.integers(-127, 128, size=(B, max_seq, n_kv * d), dtype=np.int8))
+    vc = dev(rng.integers(-127, 128, size=(B, max_seq, n_kv * d), dtype=np.int8))
+    ks = dev((rng.random((B, max_seq), dtype=np.float32) * 0.02 + 0.001))
+    vs = dev((rng.random((B, max_seq), dtype=np.float32) * 0.02 + 0.001))
+    qkv_w = (n_q + 2 * n_kv) * d
+    qkv = dev(rng.normal(0, 1.5, (B, qkv_w)).astype(np.float32))
+    d_pos = dev(np.array([pos], np.int32))
+    outs = {}
+    try:
+        for tc in (False, True):
+            ctx.set_attention_tensor_cores(tc)
+            out = torch.zeros(B, n_q * d, device="cuda")
+            torch.cuda.synchronize()
+            ctx.gqa_attention_i8_dev(qkv.data_ptr(), qkv_w, B, 1, n_q, n_kv, d, kc.data_ptr(), ks.data_ptr(),
+                                     vc.data_ptr(), vs.data_ptr(), max_seq, d_pos.data_ptr(), True, out.data_ptr())
+            ctx.synchronize()
+            assert ("mma" in ctx.last_kernel()) == tc
+            outs[tc] = out.cpu().numpy()
+    finally:
+        ctx.set_attention_tensor_cores(True)
+    err = np.abs(outs[True] - outs[False]).max() / np.abs(outs[False]).max()
+    assert err < 1e-4, err   # (summation order and two-term fp16 operands; the scores here reach +-30)
+    assert ctx.device_status() == 0
+
+
 def test_int8_kv_cache_bytes(tctx, oracle):
     """The cache rows themselves: int8 values and scales bit-identical to the reference's append."""
     import torch

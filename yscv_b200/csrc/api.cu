@@ -266,6 +266,12 @@ int yscv_cuda_ctx_set_int8_tail_split(yscv_cuda_ctx *ctx, int enable) {
     return YSCV_CUDA_OK;
 }
 
+int yscv_cuda_ctx_set_attention_tensor_cores(yscv_cuda_ctx *ctx, int enable) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    ctx->attn_tensor_cores = enable != 0;
+    return YSCV_CUDA_OK;
+}
+
 const char *yscv_cuda_last_kernel(const yscv_cuda_ctx *ctx) { return ctx ? ctx->last_kernel : "none"; }
 
 uint64_t yscv_cuda_ctx_launch_count(const yscv_cuda_ctx *ctx) { return ctx ? ctx->launches : 0; }

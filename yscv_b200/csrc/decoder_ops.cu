@@ -17,6 +17,8 @@
 // whole decode step stays on the device and can be replayed as one CUDA graph: the
 // sequence position and the token ids are read from device memory, never passed as
 // kernel arguments.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -394,6 +396,226 @@ gqa_decode_split_kernel(const float *__restrict__ q, int q_stride, int n_q, int 
     }
 }
 
+// ---- decode attention over an int8 cache on the tensor cores ------------------------------
+//
+// Same work split and the same `part` records as gqa_decode_split_kernel (one block per key chunk
+// of 128, KV head and sequence, eight query heads of the group per pass), but both contractions
+// run as mma.sync.m16n8k16 on fp16 operands with fp32 accumulators: an int8 cache entry is exact
+// in fp16 (0x6400 | (q ^ 0x80) is 1024 + q + 128, minus 1152), the rotated query and the softmax
+// weights are split into two fp16 terms (hi + lo, error below 2^-21 relative), so the result
+// differs from the fp32 loop only in summation order.
+//   scores^T [16 keys x 8 heads] = K tile [16 keys x d] (A, straight from the staged rows) x
+//                                  Q^T [d x 8 heads] (B, two terms)
+//   out [8 heads x d]            = P [8 (of 16 rows) x 128 keys] (A, two terms) x V [128 keys x d]
+//                                  (B, read from a transposed copy of the chunk's value rows)
+// The k order inside an MMA is free as long as both operands agree: a thread takes 4 consecutive
+// d (or keys) for the four k slots it owns, so its K bytes are one 16-byte read per 64 d and its V
+// bytes one 32-bit read per 16 keys. d is 64 or 128.
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// four int8 -> two fp16 pairs {x0, x1}, {x2, x3}, exact
+__device__ __forceinline__ void s8x4_to_h2x2(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    const uint32_t x = w ^ 0x80808080u;
+    const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+    uint32_t p0 = __byte_perm(x, 0x64646464u, 0x4140), p1 = __byte_perm(x, 0x64646464u, 0x4342);
+    __half2 h0 = __hsub2(*reinterpret_cast<__half2 *>(&p0), bias), h1 = __hsub2(*reinterpret_cast<__half2 *>(&p1), bias);
+    lo = *reinterpret_cast<uint32_t *>(&h0);
+    hi = *reinterpret_cast<uint32_t *>(&h1);
+}
+// two floats -> fp16 pair of their leading terms and fp16 pair of the remainders
+__device__ __forceinline__ void split_h2(float a, float b, uint32_t &hi, uint32_t &lo) {
+    const __half ha = __float2half_rn(a), hb = __float2half_rn(b);
+    const __half la = __float2half_rn(a - __half2float(ha)), lb = __float2half_rn(b - __half2float(hb));
+    const __half2 h = __halves2half2(ha, hb), l = __halves2half2(la, lb);
+    hi = *reinterpret_cast<const uint32_t *>(&h);
+    lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+
+__global__ void __launch_bounds__(128)
+gqa_decode_split_tc_kernel(const float *__restrict__ q, int q_stride, int n_q, int n_kv, int d,
+                           const int8_t *__restrict__ kc, const int8_t *__restrict__ vc,
+                           const float *__restrict__ kscale, const float *__restrict__ vscale, int max_seq,
+                           const int32_t *__restrict__ pos, float *__restrict__ part) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int CH = 128, HB = 8;
+    constexpr int SP = CH + 4;            // scores row pitch (floats)
+    constexpr int PP = CH + 8;            // weight row pitch (halves)
+    extern __shared__ __align__(16) unsigned char tsm[];
+    const int kp = d;                     // key row pitch (bytes); for d = 128 the 16-byte piece c of row r sits
+    const int ksw = d == 128 ? 4 : 0;     // at piece c ^ ((r & 1) * 4): the eight lanes of a read phase (two
+                                          // rows x four pieces) then touch eight different bank groups
+    const int vp = CH + 16;               // transposed value row pitch (bytes): conflict-free 32-bit reads
+    unsigned char *Ks = tsm;                                         // [CH][d]
+    unsigned char *Vt = Ks + CH * kp;                                // [d][CH + 16]
+    float *Ssm = reinterpret_cast<float *>(Vt + d * vp);             // [HB][SP]
+    __half *Ph = reinterpret_cast<__half *>(Ssm + HB * SP);          // [HB][PP] leading terms
+    __half *Pl = Ph + HB * PP;                                       // [HB][PP] remainders
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, kv_h = blockIdx.y, b = blockIdx.z, n_splits = gridDim.x;
+    const int grp = n_q / n_kv;
+    int limit = *pos + 1;
+    limit = limit > max_seq ? max_seq : (limit < 0 ? 0 : limit);
+    const int k0 = split * CH, k1 = min(limit, k0 + CH);
+    const int nk = k1 - k0;
+    if (nk <= 0) {  // nothing for this split yet: the neutral element of the merge
+        for (int i = tid; i < grp * (d + 2); i += blockDim.x) {
+            const int hh = i / (d + 2), j = i - hh * (d + 2);
+            part[(((size_t)b * n_q + kv_h * grp + hh) * n_splits + split) * (d + 2) + j] = j == d ? -INFINITY : 0.0f;
+        }
+        return;
+    }
+    const float scale = 1.0f / sqrtf((float)d);
+    const int8_t *kb = kc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const int8_t *vb = vc + (size_t)b * max_seq * n_kv * d + (size_t)kv_h * d;
+    const float *ksc = kscale + (size_t)b * max_seq, *vsc = vscale + (size_t)b * max_seq;
+
+    // ---- stage the chunk: key rows as they are, value rows transposed; rows past nk are zeros ----
+    {
+        const int pieces = d / 16;        // 16-byte pieces per row
+        uint4 kw[8], vw[8];               // every load in flight before the first store
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = tid + u * 128, row = i / pieces, pc = i - row * pieces;
+            kw[u] = vw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (u < pieces && row < nk) {
+                kw[u] = __ldg(reinterpret_cast<const uint4 *>(kb + (size_t)(k0 + row) * n_kv * d) + pc);
+                vw[u] = __ldg(reinterpret_cast<const uint4 *>(vb + (size_t)(k0 + row) * n_kv * d) + pc);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = tid + u * 128, row = i / pieces, pc = i - row * pieces;
+            if (u < pieces) {
+                *reinterpret_cast<uint4 *>(Ks + row * kp + ((pc ^ ((row & 1) * ksw)) << 4)) = kw[u];
+                const uint32_t w[4] = {vw[u].x, vw[u].y, vw[u].z, vw[u].w};
+#pragma unroll
+                // (value row d keeps key k at byte k ^ ((d >> 4) << 2): the eight lanes that hold the
+                // eight pieces of one key row then store into eight different banks)
+                for (int e = 0; e < 16; ++e)
+                    Vt[(pc * 16 + e) * vp + (row ^ (pc << 2))] = (unsigned char)(w[e >> 2] >> (8 * (e & 3)));
+            }
+        }
+    }
+    __syncthreads();
+
+    for (int h0 = 0; h0 < grp; h0 += HB) {
+        const int nh = min(HB, grp - h0);
+        const int qh0 = kv_h * grp + h0;
+        // ---- this thread's query operands: head g, for the k step (64-block B, quarter s4) the
+        // four d = 64 B + 16 t + 4 s4 .. + 3, as leading terms and remainders ----
+        uint32_t qh[8][2], ql[8][2];      // [k step][b0, b1]
+        {
+            const float *qr = q + (size_t)b * q_stride + (size_t)(qh0 + (g < nh ? g : 0)) * d;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (ks * 16 < d && g < nh) v = __ldg(reinterpret_cast<const float4 *>(qr + (ks >> 2) * 64 + 16 * t + 4 * (ks & 3)));
+                split_h2(v.x, v.y, qh[ks][0], ql[ks][0]);
+                split_h2(v.z, v.w, qh[ks][1], ql[ks][1]);
+            }
+        }
+        // ---- scores^T: warp w takes keys 32 w .. 32 w + 31 as two tiles of 16 ----
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            const int keyA = warp * 32 + mt * 16 + g, keyB = keyA + 8;
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                if (blk * 64 < d) {
+                    // (keyA and keyB = keyA + 8 have the same parity, hence the same swizzle)
+                    const int pc = (blk * 4 + t) ^ ((keyA & 1) * ksw);
+                    const uint4 wa = *reinterpret_cast<const uint4 *>(Ks + keyA * kp + (pc << 4));
+                    const uint4 wb = *reinterpret_cast<const uint4 *>(Ks + keyB * kp + (pc << 4));
+                    const uint32_t xa[4] = {wa.x, wa.y, wa.z, wa.w}, xb[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                    for (int s4 = 0; s4 < 4; ++s4) {
+                        uint32_t a0, a2, a1, a3;
+                        s8x4_to_h2x2(xa[s4], a0, a2);
+                        s8x4_to_h2x2(xb[s4], a1, a3);
+                        const int ks = blk * 4 + s4;
+                        mma_f16(c, a0, a1, a2, a3, ql[ks][0], ql[ks][1]);
+                        mma_f16(c, a0, a1, a2, a3, qh[ks][0], qh[ks][1]);
+                    }
+                }
+            }
+            // c0, c1 = (keyA, heads 2t, 2t+1); c2, c3 = (keyB, same heads)
+            const float sa = keyA < nk ? __ldg(ksc + k0 + keyA) * scale : 0.0f;
+            const float sb = keyB < nk ? __ldg(ksc + k0 + keyB) * scale : 0.0f;
+            Ssm[(2 * t) * SP + keyA] = keyA < nk ? c[0] * sa : -INFINITY;
+            Ssm[(2 * t + 1) * SP + keyA] = keyA < nk ? c[1] * sa : -INFINITY;
+            Ssm[(2 * t) * SP + keyB] = keyB < nk ? c[2] * sb : -INFINITY;
+            Ssm[(2 * t + 1) * SP + keyB] = keyB < nk ? c[3] * sb : -INFINITY;
+        }
+        __syncthreads();
+        // ---- softmax over the chunk: warp w takes heads 2 w and 2 w + 1, a lane four keys ----
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int h = 2 * warp + hh;
+            const float4 sv = *reinterpret_cast<const float4 *>(Ssm + h * SP + 4 * lane);
+            float mx = fmaxf(fmaxf(sv.x, sv.y), fmaxf(sv.z, sv.w));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const int key = 4 * lane;
+            float e[4] = {sv.x, sv.y, sv.z, sv.w};
+            float se = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                e[i] = (key + i < nk && h < nh) ? expf(e[i] - mx) : 0.0f;
+                se += e[i];
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+            if (lane == 0 && h < nh) {
+                float *po = part + (((size_t)b * n_q + qh0 + h) * n_splits + split) * (d + 2);
+                po[d] = mx;
+                po[d + 1] = se;
+            }
+            // the value row's scale is folded into its weight; two fp16 terms per weight
+            uint32_t hi01, lo01, hi23, lo23;
+            const float4 vs = key < nk ? make_float4(__ldg(vsc + k0 + min(key, nk - 1)), __ldg(vsc + k0 + min(key + 1, nk - 1)),
+                                                     __ldg(vsc + k0 + min(key + 2, nk - 1)), __ldg(vsc + k0 + min(key + 3, nk - 1)))
+                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            split_h2(e[0] * vs.x, e[1] * vs.y, hi01, lo01);
+            split_h2(e[2] * vs.z, e[3] * vs.w, hi23, lo23);
+            *reinterpret_cast<uint2 *>(Ph + h * PP + key) = make_uint2(hi01, hi23);
+            *reinterpret_cast<uint2 *>(Pl + h * PP + key) = make_uint2(lo01, lo23);
+        }
+        __syncthreads();
+        // ---- out = P x V: warp w takes d / 32 column tiles of 8; rows 8..15 of P are zero ----
+        const int ntw = d / 32;           // column tiles per warp (2 or 4)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (j < ntw) {
+                const int col = (warp * ntw + j) * 8 + g;     // this thread's B column (a d index)
+                float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int ks = 0; ks < CH / 16; ++ks) {
+                    const int key0 = ks * 16 + 4 * t;
+                    const uint2 ah = *reinterpret_cast<const uint2 *>(Ph + g * PP + key0);
+                    const uint2 al = *reinterpret_cast<const uint2 *>(Pl + g * PP + key0);
+                    uint32_t b0, b1;
+                    s8x4_to_h2x2(*reinterpret_cast<const uint32_t *>(Vt + col * vp + (key0 ^ ((col >> 4) << 2))), b0, b1);
+                    mma_f16(o, al.x, 0u, al.y, 0u, b0, b1);
+                    mma_f16(o, ah.x, 0u, ah.y, 0u, b0, b1);
+                }
+                // o0, o1 = (head g, d = tile * 8 + 2t, + 1)
+                if (g < nh) {
+                    float *po = part + (((size_t)b * n_q + qh0 + g) * n_splits + split) * (d + 2) + (warp * ntw + j) * 8 + 2 * t;
+                    po[0] = o[0];
+                    po[1] = o[1];
+                }
+            }
+        }
+        __syncthreads();   // the score and weight arrays are reused by the next pass
+    }
+}
+
 __global__ void attention_combine_kernel(const float *__restrict__ part, int n_splits, int d,
                                          float *__restrict__ out) {
     pdl_wait();
@@ -740,6 +962,22 @@ static int gqa_attention_impl(yscv_cuda_ctx *ctx, const float *d_q, size_t q_str
         dim3 grid((unsigned)n_splits, (unsigned)n_kv, (unsigned)batch);
         const size_t kgroups = 128 / (d_head / 4);
         const size_t split_smem = (8 * d_head + 8 * chunk + kgroups * 8 * d_head) * sizeof(float);
+        if constexpr (sizeof(KV) == 1) {
+            // int8 caches with head sizes of 64 or 128: both contractions on the tensor cores
+            if ((d_head == 64 || d_head == 128) && ctx->attn_tensor_cores) {
+                const size_t tc_smem = 128 * d_head + d_head * (128 + 16) + 8 * (128 + 4) * sizeof(float) +
+                                       2 * 8 * (128 + 8) * sizeof(uint16_t);
+                YSCV_CUDA_TRY(launch_pdl(gqa_decode_split_tc_kernel, dim3(grid), dim3(128), tc_smem, ctx->stream, d_q,
+                                         (int)q_stride, (int)n_q, (int)n_kv, (int)d_head,
+                                         reinterpret_cast<const int8_t *>(d_kcache), reinterpret_cast<const int8_t *>(d_vcache),
+                                         d_kscale, d_vscale, (int)max_seq, d_pos, part));
+                YSCV_CUDA_TRY(cudaGetLastError());
+                ctx->launches++;
+                YSCV_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3(dim3((unsigned)n_q, (unsigned)batch)), dim3(128), 0,
+                                         ctx->stream, part, n_splits, (int)d_head, d_out));
+                DEC_EPILOGUE(ctx, "gqa_attention(split-k,int8 cache,mma)");
+            }
+        }
         YSCV_CUDA_TRY(launch_pdl(gqa_decode_split_kernel<KV>, dim3(grid), dim3(128), split_smem,
                                  ctx->stream, d_q, (int)q_stride, (int)n_q, (int)n_kv, (int)d_head, d_kcache, d_vcache,
                                  d_kscale, d_vscale, (int)max_seq, d_pos, chunk, part));

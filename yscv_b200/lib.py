@@ -43,6 +43,7 @@ SIGNATURES = {
     "yscv_cuda_ctx_set_int4_prefill_exact": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_set_int8_cta_pairs": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_set_int8_tail_split": (C.c_int, [_vp, C.c_int]),
+    "yscv_cuda_ctx_set_attention_tensor_cores": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_enable": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_read": (C.c_int, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "yscv_cuda_int4_matmul": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
@@ -487,6 +488,10 @@ class Context:
     def set_int8_cta_pairs(self, on: bool):
         """int8 GEMM: allow the CTA-pair kernel (cta_group::2) or keep the one-CTA kernel everywhere (default)."""
         _check(self.lib.yscv_cuda_ctx_set_int8_cta_pairs(self.handle, int(on)))
+
+    def set_attention_tensor_cores(self, on: bool):
+        """Decode attention over int8 caches: fp16 tensor-core kernel (default) or the fp32 loop."""
+        _check(self.lib.yscv_cuda_ctx_set_attention_tensor_cores(self.handle, int(on)))
 
     def set_int8_tail_split(self, on: bool):
         """int8 GEMM: cut the K loops of the tiles beyond the last full wave over all CTAs (default) or not."""
