@@ -236,9 +236,44 @@ def bench_int4_gemm(ctx, stream, dev, iters, only):
               f"fro err {err:.1e}  [{ctx.last_kernel()}]")
 
 
+def bench_attention(ctx, stream, dev, iters, only):
+    """Decode attention (one query position per sequence) over int8 KV caches at the Llama-3-70B and
+    TinyLlama head shapes: the fp16 tensor-core kernel and the fp32 loop on the same caches."""
+    print("\n== decode attention over an int8 KV cache (one query position, 2101 cached positions) ==")
+    shapes = [("L3-70B heads 64/8 x 128, 16 sequences", 16, 64, 8, 128),
+              ("L3-70B heads 64/8 x 128, 64 sequences", 64, 64, 8, 128),
+              ("TLlama heads 32/4 x 64, 32 sequences", 32, 32, 4, 64)]
+    S, pos_v = 2178, 2100
+    for label, B, nq, nkv, d in shapes:
+        if only and only not in label:
+            continue
+        with torch.cuda.stream(stream):
+            kc = torch.randint(-127, 128, (B, S, nkv * d), dtype=torch.int8, device=dev)
+            vc = torch.randint(-127, 128, (B, S, nkv * d), dtype=torch.int8, device=dev)
+            ks = torch.rand(B, S, device=dev) * 0.02 + 0.001
+            vs = torch.rand(B, S, device=dev) * 0.02 + 0.001
+            qkv_w = (nq + 2 * nkv) * d
+            qkv = torch.randn(B, qkv_w, device=dev)
+            out = torch.empty(B, nq * d, device=dev)
+            pos = torch.full((1,), pos_v, dtype=torch.int32, device=dev)
+        call = lambda: ctx.gqa_attention_i8_dev(qkv.data_ptr(), qkv_w, B, 1, nq, nkv, d, kc.data_ptr(), ks.data_ptr(),
+                                                vc.data_ptr(), vs.data_ptr(), S, pos.data_ptr(), True, out.data_ptr())
+        res = {}
+        for tc in (True, False):
+            ctx.set_attention_tensor_cores(tc)
+            med, mn = time_us(stream, call, iters)
+            res[tc] = (mn, out.clone(), ctx.last_kernel())
+        ctx.set_attention_tensor_cores(True)
+        err = float((res[True][1] - res[False][1]).abs().max() / res[False][1].abs().max())
+        mb = 2 * B * (pos_v + 1) * nkv * d / 1e6
+        print(f"  {label:42s}: mma {res[True][0]:8.2f} us ({mb / res[True][0] * 1e3:6.0f} GB/s of cache)  "
+              f"fp32 loop {res[False][0]:8.2f} us  max diff {err:.1e}  [{res[True][2]}]")
+        del kc, vc
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--section", choices=["int8", "conv1x1", "int4_gemv", "int4_gemm"], default=None)
+    ap.add_argument("--section", choices=["int8", "conv1x1", "int4_gemv", "int4_gemm", "attention"], default=None)
     ap.add_argument("--only", default=None, help="substring of the shape label")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--copies", type=int, default=16)
@@ -257,6 +292,8 @@ def main():
         bench_int4_gemv(ctx, stream, dev, a.iters, a.only, a.copies)
     if a.section in (None, "int4_gemm"):
         bench_int4_gemm(ctx, stream, dev, a.iters, a.only)
+    if a.section in (None, "attention"):
+        bench_attention(ctx, stream, dev, a.iters, a.only)
     assert ctx.device_status() == 0
 
 
