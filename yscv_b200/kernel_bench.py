@@ -61,6 +61,9 @@ INT4_GEMM_SHAPES = [  # (label, M, N, K)
     ("TLlama prefill M=128 2048x2048", 128, 2048, 2048),
     ("TLlama prefill M=128 5632x2048", 128, 5632, 2048),
     ("TLlama prefill M=128 2048x5632", 128, 2048, 5632),
+    ("L3-70B decode batch M=64 10240x8192", 64, 10240, 8192),
+    ("L3-70B decode batch M=64 57344x8192", 64, 57344, 8192),
+    ("L3-70B decode batch M=64 8192x28672", 64, 8192, 28672),
     ("cfg2 weights M=2048 14336x4096", 2048, 14336, 4096),
     ("L3-70B prefill M=2048 8192x8192", 2048, 8192, 8192),
     ("L3-70B prefill M=2048 8192x28672", 2048, 8192, 28672),
