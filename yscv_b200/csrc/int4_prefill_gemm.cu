@@ -424,15 +424,22 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     p.stages = (227 * 1024 - 2 * p.ksub * NA * PG_BM * PG_BK * 2 - 1024) / p.stage_bytes;
     if (p.stages > 8) p.stages = 8;
     const int smem = 2 * p.ksub * NA * PG_BM * PG_BK * 2 + p.stages * p.stage_bytes + 256;
-    // few tiles (a wide decode batch against a narrow matrix): split K so that most SMs get a piece
+    // A decode batch (one narrow token tile): cut K into slices so that the work items fill whole
+    // rounds of CTAs. Among 1..8 slices take the count with the shortest makespan
+    // (rounds of items / slices), as long as a slice keeps at least 512 k and the fp32 partial sums
+    // (written and read once per slice) stay below the bytes of the weights.
     p.ksplit = 1;
     {
         const int base_tiles = p.n_tiles * p.t_chunks;
-        if (NA == 1 && base_tiles * 2 <= ctx->sm_count && (m * n) % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
-            int s = ctx->sm_count / base_tiles;
-            if (s > 8) s = 8;
-            while (s > 1 && p.k_blocks / s < 8 / p.ksub) --s;   // at least 512 k per piece
-            p.ksplit = s;
+        if (NA == 1 && p.t_chunks == 1 && p.BT <= 128 && (m * n) % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+            const int sms = ctx->sm_count;
+            double best = (double)((base_tiles + sms - 1) / sms);
+            for (int sl = 2; sl <= 8; ++sl) {
+                if (p.k_blocks / sl < 8 / p.ksub) break;
+                if (16.0 * sl * (double)m > (double)k) break;
+                const double cost = (double)((base_tiles * sl + sms - 1) / sms) / sl + 0.02 * sl;
+                if (cost < best - 1e-9) { best = cost; p.ksplit = sl; }
+            }
         }
     }
     p.kb_per = (p.k_blocks + p.ksplit - 1) / p.ksplit;
