@@ -13,11 +13,12 @@
 //   * the staging of every phase works on all rows at once (64 threads per row): RMSNorm,
 //     the merge of the attention splits, SwiGLU products, each straight from registers into the
 //     digit planes;
-//   * attention runs per (sequence, query head, key chunk) work item over the CTAs;
+//   * attention runs per (sequence, query head, key chunk) work item over the CTAs (or, on
+//     request, per (sequence, KV head, key chunk) serving the whole group of query heads);
 //   * the tail does the final norm of every row, the LM head with one pass over the weights
 //     for all rows, and one greedy token per row.
 // Limits (checked when the plan is built): hidden, n_q * head_dim <= 2048 and K chunks of 2048
-// (32 activations per thread in registers), f32 caches, per-head attention form, one GPU.
+// (32 activations per thread in registers), f32 caches, at most four key chunks per head, one GPU.
 
 constexpr int DSB_ROWS = 8;                               // activation rows of the MMA (batch padded)
 constexpr int DSB_TPR = DS_CONSUMERS / DSB_ROWS;          // 64 threads stage one row
