@@ -815,15 +815,8 @@ static int launch_g8_pair(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const
     rc = ensure_dynamic_smem(reinterpret_cast<const void *>(int8_gemm_pair_kernel), ctx->device, 227 * 1024);
     if (rc) return rc;
     const int tiles = p.m_blocks * p.n_blocks;
-    const int max_pairs = ctx->sm_count / 2;
-    const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    snprintf(ctx->report_int8, sizeof(ctx->report_int8),
-             "int8_gemm_pair m=%d n=%d k=%d: tcgen05 kind::i8 cta_group::2, pair tile 256x%d, %d stages of %d KB per CTA, "
-             "%d tiles on %d CTA pairs, %s",
-             p.M, p.N, p.K, G8P_BN, p.stages, G8P_STAGE / 1024, tiles, pairs,
-             p.mode == 0 ? "int32 out" : "requantised bytes out");
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * pairs);
+    cfg.gridDim = dim3(ctx->sm_count / 2 * 2);
     cfg.blockDim = dim3(G8_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
@@ -834,6 +827,22 @@ static int launch_g8_pair(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // The kernel is persistent with a static walk over the tiles, so every pair of the grid must
+    // be resident at once: a GPC with an odd number of usable SMs leaves one SM without a
+    // partner, and a pair that only starts when another has finished would do all its tiles
+    // after everybody else's.
+    if (ctx->max_pairs == 0) {
+        int n = 0;
+        YSCV_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, int8_gemm_pair_kernel, &cfg));
+        ctx->max_pairs = n > 0 ? n : 1;
+    }
+    const int pairs = tiles < ctx->max_pairs ? tiles : ctx->max_pairs;
+    cfg.gridDim = dim3(2 * pairs);
+    snprintf(ctx->report_int8, sizeof(ctx->report_int8),
+             "int8_gemm_pair m=%d n=%d k=%d: tcgen05 kind::i8 cta_group::2, pair tile 256x%d, %d stages of %d KB per CTA, "
+             "%d tiles on %d CTA pairs (%d can be resident), %s",
+             p.M, p.N, p.K, G8P_BN, p.stages, G8P_STAGE / 1024, tiles, pairs, ctx->max_pairs,
+             p.mode == 0 ? "int32 out" : "requantised bytes out");
     ctx->prof_begin();
     YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, int8_gemm_pair_kernel, tm_a, tm_b, (const int32_t *)b->d_colsum, d_out, p,
                                      ctx->d_status));
