@@ -291,11 +291,13 @@ def test_matmul_integer_with_b_zero_point(ctx, oracle, m, k, n, a_unsigned, a_zp
     packed.free()
 
 
-@pytest.mark.parametrize("m,k,n", [(2048, 1024, 2560), (2000, 300, 2304), (4096, 256, 4096)])
+@pytest.mark.parametrize("m,k,n", [(2048, 1024, 2560), (2000, 300, 2304), (4096, 256, 4096),
+                                   (2048, 512, 4136), (1100, 384, 4000), (2048, 640, 4096)])
 def test_cta_pair_kernel_is_bit_identical(ctx, oracle, m, k, n):
-    """The cta_group::2 kernel (two CTAs per 256 x 256 tile, off by default) against the one-CTA
+    """The cta_group::2 kernel (two CTAs per tile of 256 rows x 64..256 columns) against the one-CTA
     kernel and, on a row sample, the oracle: int32 and requantised outputs, ragged M, K not a
-    multiple of the stage, more tiles than CTA pairs."""
+    multiple of the stage, N not a multiple of a 64-column unit, tiles of every width, more tiles
+    than CTA pairs."""
     import torch
     rng = np.random.default_rng(17)
     a = rng.integers(0, 256, size=(m, k), dtype=np.uint8)

@@ -162,22 +162,42 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+// Words per row of an epilogue warp's transposition scratch: 32 columns + 4 of padding, so that
+// 16-byte accesses by row (one thread, eight pieces) and by piece (eight threads, one row) both
+// spread over all banks.
+constexpr int G8_XP_PITCH = 36;
+constexpr int G8_XP_BYTES = 4 * 32 * G8_XP_PITCH * 4;   // four epilogue warps
+
+// fp32 -> integer in [lo, hi], round to nearest even. Clamping first and rounding second gives
+// the same integer as rint-then-clamp for integer bounds; the rounding itself is the fp32 add of
+// 1.5 * 2^23 (exact for |v| < 2^22), whose low mantissa bits are the integer in two's complement:
+// no conversion instruction (a quarter-rate pipe) on the way out.
+__device__ __forceinline__ int round_clamped(float v, float lo, float hi) {
+    v = fminf(fmaxf(v, lo), hi);
+    return __float_as_int(__fadd_rn(v, 12582912.0f)) - 0x4B400000;
+}
+
 // Epilogue of one accumulator row: the thread owns output row `row`, whose BN int32 sums sit in
 // TMEM at `taddr` (this warp's lane group, the tile's first column); columns nb * BN ... of the
 // output. Subtracts the zero-point terms, then stores int32 or requantises and stores bytes.
+// int32 rows go through `xpose` (this warp's 32 x G8_XP_PITCH words of shared memory) so that a
+// store instruction writes four 128-byte row segments instead of 16 bytes of 32 different rows.
 // [c_first, c_last]: CTAs whose partial sums of this tile (slots of p.ws, row `rt` of the tile) are
 // added first; empty range when the tile was not split.
 template <int BN>
 __device__ __forceinline__ void epilogue_row(const G8Params &p, const int32_t *__restrict__ colsum,
                                              void *__restrict__ out, int row, uint32_t taddr, int nb,
-                                             int rt = 0, int c_first = 0, int c_last = -1) {
+                                             uint32_t *xpose, int rt = 0, int c_first = 0, int c_last = -1) {
+    const int lane = threadIdx.x & 31;
     const bool general = p.corr != nullptr || p.comp_pc != nullptr || p.relu != 0 || p.b_zp != 0;
     // 16-byte vector stores need a 16-byte aligned output (rows then stay aligned through
     // the pitch conditions below); anything else takes scalar stores
     const bool out_vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    const bool live = row < p.M;
+    const float lo = (float)p.qmin, hi = (float)p.qmax;
     // what the zero point of B adds to every element of this row
     int row_term = 0;
-    if (p.b_zp != 0 && row < p.M)
+    if (p.b_zp != 0 && live)
         row_term = (int)((uint32_t)p.k_true * (uint32_t)p.a_zp * (uint32_t)p.b_zp -
                          (uint32_t)p.b_zp * (uint32_t)__ldg(p.rowsum + row));
 #pragma unroll 1
@@ -185,7 +205,8 @@ __device__ __forceinline__ void epilogue_row(const G8Params &p, const int32_t *_
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
         const int col0 = nb * BN + c0;
-        if (row < p.M && col0 < p.N) {
+        if (col0 >= p.N) continue;   // the same for the whole warp
+        if (live) {
             // partial sums: 16-byte piece (4 columns) j of row rt sits at piece index j * 128 + rt of
             // the slot, so a warp reads 512 contiguous bytes; two slots are in flight at a time
             for (int c = c_first; c <= c_last; c += 2) {
@@ -203,64 +224,84 @@ __device__ __forceinline__ void epilogue_row(const G8Params &p, const int32_t *_
                     r[4 * j + 2] += (uint32_t)(v0[j].z + v1[j].z); r[4 * j + 3] += (uint32_t)(v0[j].w + v1[j].w);
                 }
             }
-            if (p.mode == 0) {
-                int32_t *o = reinterpret_cast<int32_t *>(out) + (size_t)row * p.ldc + col0;
-                if (col0 + 32 <= p.N && (p.ldc & 3) == 0 && out_vec_ok) {
+        }
+        if (p.mode == 0) {
+            int32_t *o = reinterpret_cast<int32_t *>(out) + (size_t)row * p.ldc + col0;
+            if (col0 + 32 <= p.N && (p.ldc & 3) == 0 && out_vec_ok) {
+                // every lane takes part (rows past M carry sums of zero rows and are not stored)
+                int4 *mine = reinterpret_cast<int4 *>(xpose + lane * G8_XP_PITCH);
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        int4 v;
-                        v.x = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
-                        v.y = (int)r[j + 1] - p.a_zp * __ldg(colsum + col0 + j + 1) + row_term;
-                        v.z = (int)r[j + 2] - p.a_zp * __ldg(colsum + col0 + j + 2) + row_term;
-                        v.w = (int)r[j + 3] - p.a_zp * __ldg(colsum + col0 + j + 3) + row_term;
-                        *reinterpret_cast<int4 *>(o + j) = v;
-                    }
-                } else {
+                for (int j = 0; j < 32; j += 4) {
+                    int4 v;
+                    v.x = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
+                    v.y = (int)r[j + 1] - p.a_zp * __ldg(colsum + col0 + j + 1) + row_term;
+                    v.z = (int)r[j + 2] - p.a_zp * __ldg(colsum + col0 + j + 2) + row_term;
+                    v.w = (int)r[j + 3] - p.a_zp * __ldg(colsum + col0 + j + 3) + row_term;
+                    mine[j >> 2] = v;
+                }
+                __syncwarp();
+                const int row0 = row - lane, piece = lane & 7;
+                int32_t *ob = reinterpret_cast<int32_t *>(out) + col0 + 4 * piece;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) o[j] = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
+                for (int i = 0; i < 8; ++i) {
+                    const int rr = 4 * i + (lane >> 3);
+                    const int4 v = *reinterpret_cast<const int4 *>(xpose + rr * G8_XP_PITCH + 4 * piece);
+                    if (row0 + rr < p.M) *reinterpret_cast<int4 *>(ob + (size_t)(row0 + rr) * p.ldc) = v;
+                }
+                __syncwarp();
+            } else if (live) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.N) o[j] = (int)r[j] - p.a_zp * __ldg(colsum + col0 + j) + row_term;
+            }
+        } else if (live) {
+            uint8_t *o = reinterpret_cast<uint8_t *>(out) + (size_t)row * p.ldc + col0;
+            uint32_t packed[8];
+            if (general) {
+                // per-channel vectors, bias, ReLU or a zero point on B
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int cc = (col0 + j < p.N) ? col0 + j : col0;
+                    int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc) + row_term;
+                    float comp = p.composite;
+                    if (p.corr) acc = (int)((uint32_t)acc + (uint32_t)__ldg(p.corr + cc));
+                    if (p.comp_pc) comp = __ldg(p.comp_pc + cc);
+                    // separate multiply and add: the CPU kernel does not fuse them
+                    const float v = __fadd_rn(__fmul_rn((float)acc, comp), p.y_zp);
+                    int qv = p.round_mode ? (int)fminf(fmaxf(roundf(v), lo), hi) : round_clamped(v, lo, hi);
+                    if (p.relu && qv < 0) qv = 0;
+                    if ((j & 3) == 0) packed[j >> 2] = 0;
+                    packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
+                }
+            } else if (p.round_mode == 0) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int cc = (col0 + j < p.N) ? col0 + j : col0;
+                    const int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc);
+                    // separate multiply and add: the CPU kernel does not fuse them
+                    const float v = __fadd_rn(__fmul_rn((float)acc, p.composite), p.y_zp);
+                    const int qv = round_clamped(v, lo, hi);
+                    if ((j & 3) == 0) packed[j >> 2] = 0;
+                    packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
                 }
             } else {
-                uint8_t *o = reinterpret_cast<uint8_t *>(out) + (size_t)row * p.ldc + col0;
-                uint32_t packed[8];
-                if (general) {
-                    // per-channel vectors, bias, ReLU or a zero point on B
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int cc = (col0 + j < p.N) ? col0 + j : col0;
-                        int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc) + row_term;
-                        float comp = p.composite;
-                        if (p.corr) acc = (int)((uint32_t)acc + (uint32_t)__ldg(p.corr + cc));
-                        if (p.comp_pc) comp = __ldg(p.comp_pc + cc);
-                        // separate multiply and add: the CPU kernel does not fuse them
-                        const float v = __fadd_rn(__fmul_rn((float)acc, comp), p.y_zp);
-                        const float rr = p.round_mode ? roundf(v) : rintf(v);
-                        int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
-                        if (p.relu && qv < 0) qv = 0;
-                        if ((j & 3) == 0) packed[j >> 2] = 0;
-                        packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int cc = (col0 + j < p.N) ? col0 + j : col0;
-                        const int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc);
-                        // separate multiply and add: the CPU kernel does not fuse them
-                        const float v = __fadd_rn(__fmul_rn((float)acc, p.composite), p.y_zp);
-                        const float rr = p.round_mode ? roundf(v) : rintf(v);
-                        const int qv = (int)fminf(fmaxf(rr, (float)p.qmin), (float)p.qmax);
-                        if ((j & 3) == 0) packed[j >> 2] = 0;
-                        packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
-                    }
+                for (int j = 0; j < 32; ++j) {
+                    const int cc = (col0 + j < p.N) ? col0 + j : col0;
+                    const int acc = (int)r[j] - p.a_zp * __ldg(colsum + cc);
+                    const float v = __fadd_rn(__fmul_rn((float)acc, p.composite), p.y_zp);
+                    const int qv = (int)fminf(fmaxf(roundf(v), lo), hi);
+                    if ((j & 3) == 0) packed[j >> 2] = 0;
+                    packed[j >> 2] |= ((uint32_t)qv & 255u) << (8 * (j & 3));
                 }
-                if (col0 + 32 <= p.N && (p.ldc & 15) == 0 && out_vec_ok) {
-                    *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    *reinterpret_cast<uint4 *>(o + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                } else {
+            }
+            if (col0 + 32 <= p.N && (p.ldc & 15) == 0 && out_vec_ok) {
+                *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4 *>(o + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) o[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
-                }
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.N) o[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
             }
         }
     }
@@ -298,6 +339,8 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const uint32_t bar_full = bars, bar_empty = bars + 8 * 8;
     const uint32_t bar_tfull = bars + 16 * 8, bar_tempty = bars + 18 * 8;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)p.stages * STAGE_BYTES + 20 * 8);
+    // transposition scratch of the epilogue warps, behind the 256 bytes of barriers
+    uint32_t *xpose_all = reinterpret_cast<uint32_t *>(smem + (size_t)p.stages * STAGE_BYTES + 256);
 
     if (tid == 0) {
         for (int i = 0; i < p.stages; ++i) {
@@ -383,6 +426,7 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     } else {
         // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp%4).. ----------------
         const int q = warp & 3;
+        uint32_t *xpose = xpose_all + q * 32 * G8_XP_PITCH;
         int abuf = 0;
         uint32_t aphase = 0;
         bool alive = true;
@@ -418,9 +462,9 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
                 }
                 alive = __all_sync(0xffffffffu, alive);
-                if (alive) epilogue_row<BN>(p, colsum, out, row, taddr, nb, rt, c_first, c_last);
+                if (alive) epilogue_row<BN>(p, colsum, out, row, taddr, nb, xpose, rt, c_first, c_last);
             } else {
-                epilogue_row<BN>(p, colsum, out, row, taddr, nb);
+                epilogue_row<BN>(p, colsum, out, row, taddr, nb, xpose);
             }
             // all columns of this buffer have been read: hand it back to the MMA warp
             tc_fence_before();
@@ -452,15 +496,16 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 // from L2 for the same flops: shared-memory bandwidth (TMA fill + MMA operand reads on one
 // 128 B/clk port) is what holds the one-CTA kernel at ~60 % of the tensor rate.
 //
-// Signalling (every barrier is a local mbarrier of the CTA that waits on it; remote arrivals
-// go through mapa + mbarrier.arrive.release.cluster; no multicast form is used anywhere):
-//   full[s]       own TMA loads of stage s landed                     (each CTA)
-//   peer_full[s]  leader only: the peer's relay thread saw the peer's full[s]
-//   empty[s]      leader: tcgen05.commit after the MMAs of stage s; peer: the leader's producer
-//                 forwards it once it has seen its own
-//   tfull[b]      leader: tcgen05.commit after the last K step; peer: forwarded by the leader's
-//                 first epilogue warp
-//   tempty[b]     leader only, 8 arrivals: the four epilogue warps of both CTAs drained buffer b
+// Signalling (no multicast form is used anywhere; every cross-CTA signal is raised by the
+// hardware unit that finishes the work, never relayed by a polling thread):
+//   full[s]    leader only, one arrival (the leader's expect_tx of BOTH CTAs' bytes): the peer's
+//              TMA loads are issued with .cta_group::2 and complete their bytes on the leader's
+//              barrier (address through mapa), so the MMA issuer waits on one barrier
+//   empty[s]   each CTA its own: the leader commits the MMAs of stage s twice, once to its own
+//              barrier and once to the peer's (a plain tcgen05.commit to a shared::cluster address)
+//   tfull[b]   each CTA its own, committed twice the same way after the last K step
+//   tempty[b]  leader only, 8 arrivals: the four epilogue warps of both CTAs drained buffer b
+//              (remote mbarrier.arrive from the peer's warps, once per tile)
 // All waits are bounded; a wait that runs out sets the status word, the roles fall through to the
 // cluster-wide barrier at the end, and TMEM is released.
 constexpr int G8P_BN = 256;           // columns of the pair tile
@@ -499,6 +544,16 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     if (status) atomicExch(status, 1 /* YSCV_DEV_MBARRIER_TIMEOUT */);
     return false;
 }
+// 2-D tiled load into this CTA's shared memory whose bytes complete on a barrier of either CTA
+// of the pair (`bar`: a shared::cluster address). No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                                 uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+        "{%2, %3}], [%4];\n" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
@@ -528,20 +583,19 @@ int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_rank();       // 0: leader (issues the MMAs), 1: peer
-    const uint32_t other = rank ^ 1u;
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bars = smem_base + (uint32_t)p.stages * G8P_STAGE;
-    const uint32_t bar_full = bars, bar_empty = bars + 8 * 8, bar_pfull = bars + 16 * 8;
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * 8;
     const uint32_t bar_tfull = bars + 24 * 8, bar_tempty = bars + 26 * 8;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)p.stages * G8P_STAGE + 28 * 8);
+    uint32_t *xpose_all = reinterpret_cast<uint32_t *>(smem + (size_t)p.stages * G8P_STAGE + 256);
     const int tiles = p.m_blocks * p.n_blocks;   // pair tiles of 256 x 256
 
     if (tid == 0) {
         for (int i = 0; i < p.stages; ++i) {
             mbar_init(bar_full + i * 8, 1);
             mbar_init(bar_empty + i * 8, 1);
-            mbar_init(bar_pfull + i * 8, 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + i * 8, 1);
@@ -566,25 +620,21 @@ int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_a));
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_b));
-            int slot = 0, turn = 0;   // turn: how many times the ring has wrapped
+            int slot = 0;
             uint32_t phase = 0;
             bool alive = true;
+            const uint32_t leader_full = map_to_cta(bar_full, 0);
             for (int t = pair; t < tiles && alive; t += n_pairs) {
                 const int mb = t % p.m_blocks, nb = t / p.m_blocks;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    // the leader's slot is freed by the MMA commit, the peer's by the leader's
-                    // forward of that same event (issued right below; never for a slot's first
-                    // use, which needs no freeing)
-                    alive = rank == 0 ? mbar_wait(bar_empty + slot * 8, phase ^ 1u, status)
-                                      : mbar_wait_cluster(bar_empty + slot * 8, phase ^ 1u, status);
+                    alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
                     if (!alive) break;
-                    if (rank == 0 && turn > 0) mbar_arrive_remote(map_to_cta(bar_empty + slot * 8, other));
                     const uint32_t st = smem_base + (uint32_t)slot * G8P_STAGE;
-                    const uint32_t full = bar_full + slot * 8;
-                    mbar_expect_tx(full, G8P_STAGE);
-                    tma_load_2d(st, &tm_a, kb * G8_BK, mb * 256 + (int)rank * G8_BM, full);
-                    tma_load_2d(st + HALF_BYTES, &tm_b, kb * G8_BK, nb * BN + (int)rank * G8_BM, full);
-                    if (++slot == p.stages) { slot = 0; phase ^= 1u; ++turn; }
+                    const uint32_t full = leader_full + slot * 8;
+                    if (rank == 0) mbar_expect_tx(bar_full + slot * 8, 2 * G8P_STAGE);
+                    tma_load_2d_pair(st, &tm_a, kb * G8_BK, mb * 256 + (int)rank * G8_BM, full);
+                    tma_load_2d_pair(st + HALF_BYTES, &tm_b, kb * G8_BK, nb * BN + (int)rank * G8_BM, full);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
             }
         }
@@ -596,14 +646,14 @@ int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             int slot = 0, abuf = 0;
             uint32_t phase = 0, aphase = 0;
             bool alive = true;
+            const uint32_t peer_empty = map_to_cta(bar_empty, 1), peer_tfull = map_to_cta(bar_tfull, 1);
             for (int t = pair; t < tiles && alive; t += n_pairs) {
                 alive = mbar_wait_cluster(bar_tempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)abuf * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    alive = mbar_wait(bar_full + slot * 8, phase, status) &&
-                            mbar_wait_cluster(bar_pfull + slot * 8, phase, status);
+                    alive = mbar_wait_cluster(bar_full + slot * 8, phase, status);
                     if (!alive) break;
                     tc_fence_after();
                     const uint32_t st = smem_base + (uint32_t)slot * G8P_STAGE;
@@ -613,43 +663,31 @@ int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                         umma_i8_pair(tacc, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc,
                                      (kb > 0 || j > 0) ? 1u : 0u);
                     umma_commit_pair(bar_empty + slot * 8);
+                    umma_commit_pair(peer_empty + slot * 8);
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
                 if (!alive) break;
                 umma_commit_pair(bar_tfull + abuf * 8);
+                umma_commit_pair(peer_tfull + abuf * 8);
                 if (++abuf == 2) { abuf = 0; aphase ^= 1u; }
-            }
-        } else if (lane == 0 && rank == 1) {
-            // ---------------- peer: tell the leader when this CTA's stage has landed ----------------
-            int slot = 0;
-            uint32_t phase = 0;
-            bool alive = true;
-            for (int t = pair; t < tiles && alive; t += n_pairs) {
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    alive = mbar_wait(bar_full + slot * 8, phase, status);
-                    if (!alive) break;
-                    mbar_arrive_remote(map_to_cta(bar_pfull + slot * 8, 0));
-                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
-                }
             }
         }
     } else {
         // ---------------- epilogue (both CTAs): warps 2..5 own TMEM lanes 32*(warp%4).. ----------------
         const int q = warp & 3;
+        uint32_t *xpose = xpose_all + q * 32 * G8_XP_PITCH;
         int abuf = 0;
         uint32_t aphase = 0;
         bool alive = true;
         const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
         for (int t = pair; t < tiles && alive; t += n_pairs) {
             const int mb = t % p.m_blocks, nb = t / p.m_blocks;
-            alive = rank == 0 ? mbar_wait(bar_tfull + abuf * 8, aphase, status)
-                              : mbar_wait_cluster(bar_tfull + abuf * 8, aphase, status);
+            alive = mbar_wait(bar_tfull + abuf * 8, aphase, status);
             if (!alive) break;
-            if (rank == 0 && q == 0 && lane == 0) mbar_arrive_remote(map_to_cta(bar_tfull + abuf * 8, other));
             tc_fence_after();
             const int row = mb * 256 + (int)rank * G8_BM + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)abuf * BN;
-            epilogue_row<BN>(p, colsum, out, row, taddr, nb);
+            epilogue_row<BN>(p, colsum, out, row, taddr, nb, xpose);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(leader_tempty + abuf * 8);
@@ -737,9 +775,9 @@ static int launch_g8(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const yscv
     p.n_blocks = (p.N + BN - 1) / BN;
     p.k_blocks = (p.K + G8_BK - 1) / G8_BK;
     const int stage_bytes = G8_BM * G8_BK + BN * G8_BK;
-    p.stages = (227 * 1024 - 1024) / stage_bytes;
+    p.stages = (227 * 1024 - 1024 - G8_XP_BYTES) / stage_bytes;
     if (p.stages > 8) p.stages = 8;
-    const int smem = p.stages * stage_bytes + 256;
+    const int smem = p.stages * stage_bytes + 256 + G8_XP_BYTES;
     CUtensorMap tm_a, tm_b;
     int rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d_a, m, b->kp, lda, G8_BM, G8_BK,
                        CU_TENSOR_MAP_SWIZZLE_128B);
@@ -802,9 +840,9 @@ static int launch_g8_pair(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const
     p.m_blocks = (p.M + 255) / 256;
     p.n_blocks = (p.N + G8P_BN - 1) / G8P_BN;
     p.k_blocks = (p.K + G8_BK - 1) / G8_BK;
-    p.stages = (227 * 1024 - 1024) / G8P_STAGE;
+    p.stages = (227 * 1024 - 1024 - G8_XP_BYTES) / G8P_STAGE;
     if (p.stages > 8) p.stages = 8;
-    const int smem = p.stages * G8P_STAGE + 256;
+    const int smem = p.stages * G8P_STAGE + 256 + G8_XP_BYTES;
     CUtensorMap tm_a, tm_b;
     int rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d_a, m, b->kp, lda, G8_BM, G8_BK,
                        CU_TENSOR_MAP_SWIZZLE_128B);
