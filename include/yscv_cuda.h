@@ -114,12 +114,15 @@ void yscv_cuda_quant_stats_reset(void);
  * (crates/yscv-kernels/src/ops/int4_matmul.rs:548-605). */
 int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact);
 /* Kernel-selection switch of the int8 GEMM, like the reference's environment gates on its
- * int8 paths (crates/yscv-onnx/src/runner/quant_stats.rs:68-71): enable != 0 lets shapes with
- * enough 256 x 256 tiles run on CTA pairs (tcgen05 cta_group::2, two SMs per tile, each staging
- * half of both operands); 0 (the default) keeps the one-CTA kernel everywhere, which measured
- * faster on every shape tried: the tensor pipe, not shared memory, bounds this GEMM. The
- * results are identical (integer arithmetic), only the speed differs. */
-int yscv_cuda_ctx_set_int8_cta_pairs(yscv_cuda_ctx *ctx, int enable);
+ * int8 paths (crates/yscv-onnx/src/runner/quant_stats.rs:68-71). The GEMM has a one-CTA kernel
+ * and a CTA-pair kernel (tcgen05 cta_group::2: two SMs per 256 x 256 tile, each staging half of
+ * both operands, so half the operand traffic from L2 per flop). mode < 0 (the default): the pair
+ * kernel where it measured faster: int32 output with at least three rounds of pair tiles, and
+ * any output when the one-CTA kernel would run a single round on more than half of the SMs;
+ * mode == 0: the one-CTA kernel everywhere; mode > 0: the pair kernel on every shape it supports
+ * (m, n >= 256 and pair tiles for at least 0.8 of the pairs). The results are identical
+ * (integer arithmetic), only the speed differs. */
+int yscv_cuda_ctx_set_int8_cta_pairs(yscv_cuda_ctx *ctx, int mode);
 /* Second switch of the int8 GEMM, on by default: when the output tiles occupy at most half of
  * the SMs and K >= 8192, the K loops are cut into equal runs over all CTAs and the int32 partial
  * sums are added by the CTA that owns the tile (workspace of 128 KB per SM in the context,

@@ -312,7 +312,7 @@ def test_cta_pair_kernel_is_bit_identical(ctx, oracle, m, k, n):
             assert ("cta_group::2" in ctx.last_kernel()) == pairs
             outs[pairs] = (q, ctx.matmul_integer(a, pk, m, a_zp=128))
     finally:
-        ctx.set_int8_cta_pairs(False)
+        ctx.set_int8_cta_pairs(None)
     assert np.array_equal(outs[False][0], outs[True][0]) and np.array_equal(outs[False][1], outs[True][1])
     rows = rng.choice(m, size=16, replace=False)
     acc = oracle.int8_matmul((a[rows] ^ 0x80).view(np.int8), b, len(rows), k, n)

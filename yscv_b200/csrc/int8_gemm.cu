@@ -939,7 +939,19 @@ int int8_gemm(yscv_cuda_ctx *ctx, const void *d_a, const yscv_cuda_i8b *b, size_
     const size_t tiles256 = ((m + G8_BM - 1) / G8_BM) * ((b->n + 255) / 256);
     // CTA pairs (256 x 256 per pair) once there are enough pair tiles to occupy most pairs
     const size_t pair_tiles = ((m + 255) / 256) * ((b->n + 255) / 256);
-    if (ctx->int8_pairs && b->n >= 256 && m >= 256 && pair_tiles * 10 >= (size_t)(ctx->sm_count / 2) * 8) {
+    const size_t pairs = (size_t)(ctx->sm_count / 2);
+    const bool pair_ok = b->n >= 256 && m >= 256 && pair_tiles * 10 >= pairs * 8;
+    // Where the pair kernel measured faster: int32 output (the rows written are four times the
+    // bytes, and halving the operand traffic leaves them room) from three rounds of pair tiles
+    // on, and a single round of the one-CTA kernel on more than half of the SMs, which the
+    // L2 -> SM traffic bounds (1024 x 4096 x 4096: 27.2 -> 22.7 us).
+    // Neither holds for K < 2048 (the pair's longer fill shows) or when the 256-row blocks leave
+    // the pairs more rounds than the one-CTA kernel has (300 rows: two blocks, the second nearly empty).
+    const bool pair_wins = b->kp >= 2048 &&
+                           ((mode == 0 && pair_tiles >= 3 * pairs) ||
+                            (tiles256 <= (size_t)ctx->sm_count && tiles256 * 2 > (size_t)ctx->sm_count &&
+                             pair_tiles <= pairs));
+    if (pair_ok && (ctx->int8_pairs > 0 || (ctx->int8_pairs < 0 && pair_wins))) {
         ctx->last_kernel = "int8_gemm_pair(tcgen05,cta_group::2,256x256)";
         return launch_g8_pair(ctx, a, lda, b, m, d_out, p);
     }

@@ -485,9 +485,10 @@ class Context:
         """m > 16 int4 matmuls: fp32-exact kernel (True) or bf16 tensor-core GEMM (False, default)."""
         _check(self.lib.yscv_cuda_ctx_set_int4_prefill_exact(self.handle, int(exact)))
 
-    def set_int8_cta_pairs(self, on: bool):
-        """int8 GEMM: allow the CTA-pair kernel (cta_group::2) or keep the one-CTA kernel everywhere (default)."""
-        _check(self.lib.yscv_cuda_ctx_set_int8_cta_pairs(self.handle, int(on)))
+    def set_int8_cta_pairs(self, on):
+        """int8 GEMM: None = the CTA-pair kernel (cta_group::2) where it measured faster (default),
+        False = the one-CTA kernel everywhere, True = the pair kernel on every shape it supports."""
+        _check(self.lib.yscv_cuda_ctx_set_int8_cta_pairs(self.handle, -1 if on is None else int(bool(on))))
 
     def set_attention_tensor_cores(self, on: bool):
         """Decode attention over int8 caches: fp16 tensor-core kernel (default) or the fp32 loop."""
