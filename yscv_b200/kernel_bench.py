@@ -85,6 +85,24 @@ def time_us(stream, fn, iters, warmup=5):
     return statistics.median(ts), min(ts)
 
 
+def time_b2b_us(stream, fn, iters, warmup=5, rounds=3):
+    """Device time per call of `iters` calls enqueued back to back between two CUDA events (best of
+    `rounds`): no event record between the launches, so no bubble around each kernel."""
+    best = float("inf")
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            fn()
+        for _ in range(rounds):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(iters):
+                fn()
+            b.record(stream)
+            stream.synchronize()
+            best = min(best, a.elapsed_time(b) * 1e3 / iters)
+    return best
+
+
 def sample_idx(rows, cols, count, dev):
     g = torch.Generator(device=dev)
     g.manual_seed(1234)
@@ -116,8 +134,12 @@ def bench_int8(ctx, stream, dev, iters, only, calibrate=False):
         med, mn = time_us(stream, lambda: ctx.matmul_integer_dev(a.data_ptr(), True, 128, pk, m, o32.data_ptr()), iters)
         medq, mnq = time_us(stream, lambda: ctx.qlinear_matmul_dev(a.data_ptr(), pk, m, rq, o8.data_ptr()), iters)
         ops = 2.0 * m * k * n
+        bb = time_b2b_us(stream, lambda: ctx.matmul_integer_dev(a.data_ptr(), True, 128, pk, m, o32.data_ptr()), iters)
+        bbq = time_b2b_us(stream, lambda: ctx.qlinear_matmul_dev(a.data_ptr(), pk, m, rq, o8.data_ptr()), iters)
         print(f"  {label:46s} i32: med {med:9.2f} us min {mn:9.2f} us {ops / mn / 1e6:8.1f} TOPS | "
               f"requant-u8: min {mnq:9.2f} us {ops / mnq / 1e6:8.1f} TOPS  [{ctx.last_kernel()}]  parity: bit-exact")
+        print(f"  {'':46s} back to back (no event between launches): i32 {bb:9.2f} us {ops / bb / 1e6:8.1f} TOPS | "
+              f"requant-u8 {bbq:9.2f} us {ops / bbq / 1e6:8.1f} TOPS")
         if calibrate and m % 8 == 0 and k % 8 == 0 and n % 8 == 0 and m > 16:
             # CALIBRATION ONLY: what the vendor's own int8 GEMM (cuBLASLt through torch._int_mm)
             # reaches on this shape and this GPU, the practical ceiling of the int8 tensor pipe.
@@ -127,8 +149,10 @@ def bench_int8(ctx, stream, dev, iters, only, calibrate=False):
                 lib = torch._int_mm(a8, b)
                 same = bool(torch.equal(lib, o32))
             lmed, lmn = time_us(stream, lambda: torch._int_mm(a8, b), iters)
+            lbb = time_b2b_us(stream, lambda: torch._int_mm(a8, b), iters)
             print(f"  {'':46s} calibration, library int8 GEMM (cuBLASLt, i32 out): min {lmn:9.2f} us "
-                  f"{ops / lmn / 1e6:8.1f} TOPS  same result: {same}")
+                  f"{ops / lmn / 1e6:8.1f} TOPS, back to back {lbb:9.2f} us {ops / lbb / 1e6:8.1f} TOPS  "
+                  f"same result: {same}")
         pk.free()
 
 
