@@ -113,6 +113,11 @@ void yscv_cuda_quant_stats_reset(void);
  * counterpart of choosing packed_int4_gemm_scalar over a SIMD variant
  * (crates/yscv-kernels/src/ops/int4_matmul.rs:548-605). */
 int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact);
+/* Kernel-selection switch of the bf16 prefill GEMM: enable != 0 (the default) lets prefills
+ * with at least one 512-row x 256-token tile per CTA pair run on CTA pairs (tcgen05
+ * cta_group::2: each CTA dequantises 256 weight rows and stages half of the activation tile);
+ * 0 keeps the one-CTA kernel. Same products, same summation order over k. */
+int yscv_cuda_ctx_set_int4_prefill_cta_pairs(yscv_cuda_ctx *ctx, int enable);
 /* Kernel-selection switch of the int8 GEMM, like the reference's environment gates on its
  * int8 paths (crates/yscv-onnx/src/runner/quant_stats.rs:68-71). The GEMM has a one-CTA kernel
  * and a CTA-pair kernel (tcgen05 cta_group::2: two SMs per 256 x 256 tile, each staging half of

@@ -254,6 +254,12 @@ int yscv_cuda_ctx_set_int4_prefill_exact(yscv_cuda_ctx *ctx, int exact) {
     return YSCV_CUDA_OK;
 }
 
+int yscv_cuda_ctx_set_int4_prefill_cta_pairs(yscv_cuda_ctx *ctx, int enable) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    ctx->prefill_pairs = enable != 0;
+    return YSCV_CUDA_OK;
+}
+
 int yscv_cuda_ctx_set_int8_cta_pairs(yscv_cuda_ctx *ctx, int mode) {
     if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
     ctx->int8_pairs = mode < 0 ? -1 : (mode > 0 ? 1 : 0);

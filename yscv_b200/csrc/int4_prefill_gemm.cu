@@ -371,6 +371,273 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     }
 }
 
+// ---------------------------------------------------------------------------
+// CTA-pair form for large prefills: tcgen05.mma.cta_group::2
+// ---------------------------------------------------------------------------
+//
+// Two CTAs on the two SMs of a TPC (a cluster of 2) share a tile of 512 weight rows x 256 tokens.
+// Each CTA dequantises its own 256 weight rows (two 128-row tiles, as the NA = 2 form above) and
+// stages HALF of the activation tile of a k block (128 tokens); the leader (cluster rank 0) issues
+// MMAs of M = 256, N = 256 that read both CTAs' shared memory and leave rows 0..127 in its own
+// TMEM and rows 128..255 in the peer's. Per k block an SM then pulls 8 KB of nibbles + 16 KB of
+// activations from L2 instead of 8 + 32 KB, and its tensor core reads half the activation bytes
+// from shared memory per flop: the two limits of the one-CTA form.
+//
+// Signals (no multicast form; every signal is raised by the unit that finishes the work):
+//   full_w[s]    each CTA: its own nibble tile of stage s landed (its dequantising warps wait)
+//   full_act[s]  leader: BOTH CTAs' activation halves landed (the peer's load is the
+//                .cta_group::2 form of the TMA load, completing its bytes on the leader's barrier)
+//   afull[b]     leader, 16 arrivals: the eight dequantising warps of both CTAs filled A buffer b
+//                (the peer's warps arrive remotely, after fence.proxy.async)
+//   empty[s], aempty[b], tfull   each CTA its own: the leader commits its MMAs to both CTAs' barriers
+//   tempty       leader, 8 arrivals: the epilogue warps of both CTAs drained the accumulators
+// All waits are bounded; a wait that runs out sets the status word and the roles fall through to the
+// cluster barrier at the end.
+constexpr int PP_ACT = 128 * 128;              // 128 tokens x 64 k bf16: this CTA's half of the activation tile
+constexpr int PP_W = 2 * PG_BM * 32;           // nibbles of this CTA's 256 rows for one k block
+constexpr int PP_STAGE = PP_ACT + PP_W;        // 24 KB
+constexpr int PP_A_TILE = PG_BM * PG_BK * 2;   // 16 KB
+constexpr int PP_A_BUF = 2 * PP_A_TILE;
+constexpr int PP_ABUFS = 3;                    // buffers of dequantised tiles: the hand-over crosses the pair twice
+
+__device__ __forceinline__ void pp_mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// commit to a barrier of either CTA of the pair (shared::cluster address)
+__device__ __forceinline__ void pp_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(PG_THREADS, 1)
+int4_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
+                         const float *__restrict__ scales, float *__restrict__ out, PGParams p,
+                         int *__restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const uint32_t smem_base = smem_u32(smem);
+    // [A buffers][stages x {activation half | packed nibbles}][barriers][tmem slot]
+    const uint32_t a_tiles = smem_base;
+    const uint32_t ring = smem_base + PP_ABUFS * PP_A_BUF;
+    const uint32_t bars = ring + (uint32_t)p.stages * PP_STAGE;
+    const uint32_t bar_full_w = bars, bar_full_act = bars + 64, bar_empty = bars + 128;
+    const uint32_t bar_afull = bars + 192, bar_aempty = bars + 224, bar_tfull = bars + 256, bar_tempty = bars + 264;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + PP_ABUFS * PP_A_BUF + (size_t)p.stages * PP_STAGE + 272);
+    const int tiles = p.n_tiles * p.t_chunks;   // pair tiles: 512 weight rows x 256 tokens
+
+    if (tid == 0) {
+        for (int i = 0; i < p.stages; ++i) {
+            mbar_init(bar_full_w + i * 8, 1);
+            mbar_init(bar_full_act + i * 8, 1);
+            mbar_init(bar_empty + i * 8, 1);
+        }
+        for (int i = 0; i < PP_ABUFS; ++i) {
+            mbar_init(bar_afull + i * 8, 2 * PG_DEQ_WARPS);
+            mbar_init(bar_aempty + i * 8, 1);
+        }
+        mbar_init(bar_tfull, 1);
+        mbar_init(bar_tempty, 8);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
+    }
+    pg_fence_before();
+    cluster_sync_all();   // both CTAs' barriers exist before anyone arrives on a remote one
+    pg_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_w));
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tm_a));
+            int slot = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            const uint32_t leader_full_act = map_to_cta(bar_full_act, 0);
+            for (int t = pair; t < tiles && alive; t += n_pairs) {
+                const int nt_i = t % p.n_tiles, tc = t / p.n_tiles;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
+                    if (!alive) break;
+                    const uint32_t st = ring + (uint32_t)slot * PP_STAGE;
+                    if (rank == 0) mbar_expect_tx(bar_full_act + slot * 8, 2 * PP_ACT);
+                    mbar_expect_tx(bar_full_w + slot * 8, PP_W);
+                    tma_load_2d_pair(st, &tm_a, kb * PG_BK, tc * 256 + (int)rank * 128, leader_full_act + slot * 8);
+                    tma_load_2d(st + PP_ACT, &tm_w, kb * 32, nt_i * 512 + (int)rank * 256, bar_full_w + slot * 8);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader only) ----------------
+        if (lane == 0 && rank == 0) {
+            // D fp32, A and B bf16, both K-major, N = 256, M = 256 over the pair
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) |
+                                   ((uint32_t)(256 >> 4) << 24);
+            int slot = 0, abuf = 0;
+            uint32_t phase = 0, aphase = 0, tphase = 0;
+            bool alive = true;
+            const uint32_t peer_empty = map_to_cta(bar_empty, 1), peer_aempty = map_to_cta(bar_aempty, 1);
+            const uint32_t peer_tfull = map_to_cta(bar_tfull, 1);
+            for (int t = pair; t < tiles && alive; t += n_pairs) {
+                alive = mbar_spin_cluster(bar_tempty, tphase ^ 1u, status);
+                if (!alive) break;
+                pg_fence_after();
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    alive = mbar_wait_cluster(bar_full_act + slot * 8, phase, status) &&
+                            mbar_spin_cluster(bar_afull + abuf * 8, aphase, status);
+                    if (!alive) break;
+                    pg_fence_after();
+                    const uint64_t db = pg_desc_sw128(ring + (uint32_t)slot * PP_STAGE);
+#pragma unroll
+                    for (int a = 0; a < 2; ++a) {
+                        const uint64_t da = pg_desc_sw128(a_tiles + abuf * PP_A_BUF + a * PP_A_TILE);
+#pragma unroll
+                        for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
+                            pp_mma_bf16(tmem_base + a * 256, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
+                                        (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    pp_commit(bar_empty + slot * 8);
+                    pp_commit(peer_empty + slot * 8);
+                    pp_commit(bar_aempty + abuf * 8);
+                    pp_commit(peer_aempty + abuf * 8);
+                    if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                    if (++abuf == PP_ABUFS) { abuf = 0; aphase ^= 1u; }
+                }
+                if (!alive) break;
+                pp_commit(bar_tfull);
+                pp_commit(peer_tfull);
+                tphase ^= 1u;
+            }
+        }
+    } else if (warp < 2 + PG_DEQ_WARPS) {
+        // ------- dequantise (both CTAs): lanes 2i, 2i+1 share weight row (warp - 2) * 16 + i of each 128-row tile -------
+        const int r = (warp - 2) * 16 + (lane >> 1), half = lane & 1;
+        const int groups = p.K / 32;
+        int slot = 0, abuf = 0;
+        uint32_t phase = 0, aphase = 0;
+        bool alive = true;
+        const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
+        const uint32_t leader_afull = map_to_cta(bar_afull, 0);
+        for (int t = pair; t < tiles && alive; t += n_pairs) {
+            const int nt_i = t % p.n_tiles;
+            const float *srow[2];
+            bool live_row[2];
+            float sc_next[2];
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+                const int row = nt_i * 512 + (int)rank * 256 + a * PG_BM + r;
+                live_row[a] = row < p.N;
+                srow[a] = scales + (size_t)(live_row[a] ? row : 0) * groups + half;
+                sc_next[a] = live_row[a] ? __ldg(srow[a]) : 0.0f;
+            }
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                float sc[2];
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    sc[a] = sc_next[a];
+                    // the next block's scales travel while this one is converted
+                    if (kb + 1 < p.k_blocks && live_row[a]) sc_next[a] = __ldg(srow[a] + (kb + 1) * 2);
+                }
+                alive = mbar_wait(bar_full_w + slot * 8, phase, status) &&
+                        mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
+                if (!alive) break;
+                const unsigned char *st = smem + PP_ABUFS * PP_A_BUF + (size_t)slot * PP_STAGE + PP_ACT;
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    const uint4 w4 = *reinterpret_cast<const uint4 *>(st + (a * PG_BM + r) * 32 + half * 16);
+                    const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+                    const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[a]);
+                    unsigned char *arow = smem + (size_t)abuf * PP_A_BUF + (size_t)a * PP_A_TILE + (size_t)r * 128;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t w = words[i];
+                        uint32_t x[4];
+                        // 0x4300 | (nibble ^ 8) is the bf16 value 136 + q, exactly
+                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[0]) : "r"(w));
+                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[1]) : "r"(w >> 4));
+                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[2]) : "r"(w >> 8));
+                        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6a;\n" : "=r"(x[3]) : "r"(w >> 12));
+                        uint4 o;
+                        uint32_t *ov = &o.x;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&x[j]);
+                            v = __hmul2(__hsub2(v, bias), s2);
+                            ov[j] = *reinterpret_cast<uint32_t *>(&v);
+                        }
+                        // 16-byte chunk c of row r sits at chunk c ^ (r & 7) (128-byte swizzle)
+                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + i) ^ (r & 7)) << 4)) = o;
+                    }
+                }
+                // make the generic-proxy writes visible to the async proxy: each CTA's tensor core reads
+                // the A tile of its own shared memory
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(leader_afull + abuf * 8);
+                if (++slot == p.stages) { slot = 0; phase ^= 1u; }
+                if (++abuf == PP_ABUFS) { abuf = 0; aphase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs): warps 10..13 own TMEM lanes 32*(warp%4).. ----------------
+        const int q = warp & 3;
+        uint32_t tphase = 0;
+        bool alive = true;
+        const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
+        for (int t = pair; t < tiles && alive; t += n_pairs) {
+            const int nt_i = t % p.n_tiles, tc = t / p.n_tiles;
+            alive = mbar_wait(bar_tfull, tphase, status);
+            if (!alive) break;
+            pg_fence_after();
+#pragma unroll 1
+            for (int a = 0; a < 2; ++a) {
+                const int n = nt_i * 512 + (int)rank * 256 + a * PG_BM + q * 32 + lane;   // output channel of this lane
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 256);
+#pragma unroll 1
+                for (int c0 = 0; c0 < 256; c0 += 32) {
+                    uint32_t rr[32];
+                    pg_tmem_ld32(taddr + c0, rr);
+                    const int tok0 = tc * 256 + c0;
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (tok0 + j < p.M) out[(size_t)(tok0 + j) * p.N + n] = __uint_as_float(rr[j]);
+                    }
+                }
+            }
+            pg_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_tempty);
+            tphase ^= 1u;
+        }
+    }
+
+    // neither CTA may leave (or give its TMEM back) while the other can still read its shared
+    // memory or arrive on its barriers
+    pg_fence_before();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 1) {
+        pg_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
+    }
+}
+
 // out = slice 0 + slice 1 + ... of the K-split workspace, in that order
 __global__ void __launch_bounds__(256) add_kslices_kernel(const float4 *__restrict__ ws, float4 *__restrict__ out,
                                                           size_t n4, int slices) {
@@ -391,6 +658,53 @@ size_t int4_prefill_scratch_bytes(size_t m, size_t k) { return m * k * 2 + 256; 
 bool int4_prefill_supported(size_t m, size_t n, size_t k, size_t gs) {
     return tensor_map_encoder() != nullptr && gs == 32 && k % 64 == 0 && m > 16 && n >= 1 &&
            m < (1u << 30) && n < (1u << 30) && k < (1u << 30);
+}
+
+static int launch_prefill_pairs(yscv_cuda_ctx *ctx, const CUtensorMap &tm_w, const CUtensorMap &tm_a,
+                                const float *scales, float *out, PGParams p) {
+    p.n_tiles = (p.N + 511) / 512;
+    p.t_chunks = (p.M + 255) / 256;
+    p.k_blocks = p.K / PG_BK;
+    p.ksub = 1;
+    p.ksplit = 1;
+    p.acc_bufs = 1;
+    p.stage_bytes = PP_STAGE;
+    p.stages = (227 * 1024 - PP_ABUFS * PP_A_BUF - 1024) / PP_STAGE;
+    if (p.stages > 8) p.stages = 8;
+    const int smem = PP_ABUFS * PP_A_BUF + p.stages * PP_STAGE + 512;
+    int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(int4_prefill_pair_kernel), ctx->device, 227 * 1024);
+    if (rc) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctx->sm_count / 2 * 2);
+    cfg.blockDim = dim3(PG_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // persistent kernel with a static walk over the tiles: every pair of the grid must be resident
+    if (ctx->max_prefill_pairs == 0) {
+        int nres = 0;
+        YSCV_CUDA_TRY(cudaOccupancyMaxActiveClusters(&nres, int4_prefill_pair_kernel, &cfg));
+        ctx->max_prefill_pairs = nres > 0 ? nres : 1;
+    }
+    const int tiles = p.n_tiles * p.t_chunks;
+    const int pairs = tiles < ctx->max_prefill_pairs ? tiles : ctx->max_prefill_pairs;
+    cfg.gridDim = dim3(2 * pairs);
+    ctx->prof_begin();
+    YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, int4_prefill_pair_kernel, tm_w, tm_a, scales, out, p, ctx->d_status));
+    ctx->prof_end();
+    YSCV_CUDA_TRY(cudaGetLastError());
+    ctx->launches++;
+    snprintf(ctx->report_int4, sizeof(ctx->report_int4),
+             "int4_prefill_gemm m=%d n=%d k=%d: tcgen05 bf16 cta_group::2, pair tile 512 rows x 256 tokens, 64 k per stage, "
+             "%d stages of %d KB per CTA, %d tiles on %d CTA pairs", p.M, p.N, p.K, p.stages, PP_STAGE / 1024, tiles, pairs);
+    ctx->last_kernel = "int4_prefill_gemm(tcgen05,bf16,cta_group::2)";
+    return YSCV_CUDA_OK;
 }
 
 int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, const float *act,
@@ -450,6 +764,10 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
         kernel_out = reinterpret_cast<float *>(ctx->gemm_ws.ptr);
     }
 
+    // CTA pairs (512 weight rows x 256 tokens per pair) when every pair still gets a tile
+    const size_t pair_tiles = ((n + 511) / 512) * ((m + 255) / 256);
+    const bool use_pairs = ctx->prefill_pairs && NA == 2 && pair_tiles >= (size_t)(ctx->sm_count / 2);
+
     __nv_bfloat16 *abf = reinterpret_cast<__nv_bfloat16 *>(scratch);
     const size_t groups8 = m * k / 8;
     const unsigned cb = (unsigned)((groups8 + 255) / 256 < 8192 ? (groups8 + 255) / 256 : 8192);
@@ -461,9 +779,10 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     int rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, n, k / 2, k / 2, (uint32_t)(NA * PG_BM), 32,
                        CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, m, k, k * 2, (uint32_t)p.BT, PG_BK,
+    rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, m, k, k * 2, use_pairs ? 128u : (uint32_t)p.BT, PG_BK,
                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    if (use_pairs) return launch_prefill_pairs(ctx, tm_w, tm_a, scales, out, p);
     auto kern = NA == 2 ? int4_prefill_gemm_kernel<2, 1, false>
                         : p.ksub == 2 ? (p.ksplit > 1 ? int4_prefill_gemm_kernel<1, 2, true> : int4_prefill_gemm_kernel<1, 2, false>)
                                       : (p.ksplit > 1 ? int4_prefill_gemm_kernel<1, 1, true> : int4_prefill_gemm_kernel<1, 1, false>);

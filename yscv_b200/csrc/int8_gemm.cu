@@ -511,53 +511,6 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 constexpr int G8P_BN = 256;           // columns of the pair tile
 constexpr int G8P_STAGE = 2 * G8_BM * G8_BK;  // per CTA: 128 rows of A + 128 rows of B^T
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
-    uint32_t a;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local_addr), "r"(rank));
-    return a;
-}
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// bounded wait on a barrier that a thread of the other CTA arrives on
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int *status) {
-    for (uint32_t i = 0; i < (1u << 22); ++i)
-        if (mbar_try_wait_cluster(bar, parity)) return true;
-    if (status) atomicExch(status, 1 /* YSCV_DEV_MBARRIER_TIMEOUT */);
-    return false;
-}
-// 2-D tiled load into this CTA's shared memory whose bytes complete on a barrier of either CTA
-// of the pair (`bar`: a shared::cluster address). No multicast.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y,
-                                                 uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
-        "{%2, %3}], [%4];\n" ::"r"(dst),
-        "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
 __device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
                                              uint32_t accumulate) {
     asm volatile(
@@ -648,7 +601,7 @@ int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             bool alive = true;
             const uint32_t peer_empty = map_to_cta(bar_empty, 1), peer_tfull = map_to_cta(bar_tfull, 1);
             for (int t = pair; t < tiles && alive; t += n_pairs) {
-                alive = mbar_wait_cluster(bar_tempty + abuf * 8, aphase ^ 1u, status);
+                alive = mbar_spin_cluster(bar_tempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)abuf * BN;

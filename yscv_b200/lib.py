@@ -42,6 +42,7 @@ SIGNATURES = {
     "yscv_cuda_ctx_launch_count": (C.c_uint64, [_vp]),
     "yscv_cuda_ctx_set_int4_prefill_exact": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_set_int8_cta_pairs": (C.c_int, [_vp, C.c_int]),
+    "yscv_cuda_ctx_set_int4_prefill_cta_pairs": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_set_int8_tail_split": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_set_attention_tensor_cores": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_enable": (C.c_int, [_vp, C.c_int]),
@@ -484,6 +485,10 @@ class Context:
     def set_int4_prefill_exact(self, exact: bool):
         """m > 16 int4 matmuls: fp32-exact kernel (True) or bf16 tensor-core GEMM (False, default)."""
         _check(self.lib.yscv_cuda_ctx_set_int4_prefill_exact(self.handle, int(exact)))
+
+    def set_int4_prefill_cta_pairs(self, on: bool):
+        """bf16 prefill GEMM: allow the CTA-pair kernel (cta_group::2) for large prefills (default) or not."""
+        _check(self.lib.yscv_cuda_ctx_set_int4_prefill_cta_pairs(self.handle, int(bool(on))))
 
     def set_int8_cta_pairs(self, on):
         """int8 GEMM: None = the CTA-pair kernel (cta_group::2) where it measured faster (default),
