@@ -395,10 +395,14 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
 // cluster barrier at the end.
 constexpr int PP_ACT = 128 * 128;              // 128 tokens x 64 k bf16: this CTA's half of the activation tile
 constexpr int PP_W = 2 * PG_BM * 32;           // nibbles of this CTA's 256 rows for one k block
-constexpr int PP_STAGE = PP_ACT + PP_W;        // 24 KB
 constexpr int PP_A_TILE = PG_BM * PG_BK * 2;   // 16 KB
-constexpr int PP_A_BUF = 2 * PP_A_TILE;
-constexpr int PP_ABUFS = 3;                    // buffers of dequantised tiles: the hand-over crosses the pair twice
+// KSUB 64-k sub-blocks per ring stage and hand-over, as in the one-CTA kernel: a stage holds
+// [KSUB activation halves][KSUB nibble tiles], an A buffer [sub-block][weight tile]
+template <int KSUB> struct PPGeom {
+    static constexpr int STAGE = KSUB * (PP_ACT + PP_W);     // 24 KB per sub-block
+    static constexpr int A_BUF = KSUB * 2 * PP_A_TILE;
+    static constexpr int ABUFS = KSUB == 1 ? 3 : 2;           // buffers of dequantised tiles
+};
 
 __device__ __forceinline__ void pp_mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
                                             uint32_t accumulate) {
@@ -417,10 +421,12 @@ __device__ __forceinline__ void pp_commit(uint32_t bar) {
                  : "memory");
 }
 
+template <int KSUB>
 __global__ void __launch_bounds__(PG_THREADS, 1)
 int4_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                          const float *__restrict__ scales, float *__restrict__ out, PGParams p,
                          int *__restrict__ status) {
+    constexpr int PP_STAGE = PPGeom<KSUB>::STAGE, PP_A_BUF = PPGeom<KSUB>::A_BUF, PP_ABUFS = PPGeom<KSUB>::ABUFS;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_rank();
@@ -474,10 +480,14 @@ int4_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                     alive = mbar_wait(bar_empty + slot * 8, phase ^ 1u, status);
                     if (!alive) break;
                     const uint32_t st = ring + (uint32_t)slot * PP_STAGE;
-                    if (rank == 0) mbar_expect_tx(bar_full_act + slot * 8, 2 * PP_ACT);
-                    mbar_expect_tx(bar_full_w + slot * 8, PP_W);
-                    tma_load_2d_pair(st, &tm_a, kb * PG_BK, tc * 256 + (int)rank * 128, leader_full_act + slot * 8);
-                    tma_load_2d(st + PP_ACT, &tm_w, kb * 32, nt_i * 512 + (int)rank * 256, bar_full_w + slot * 8);
+                    if (rank == 0) mbar_expect_tx(bar_full_act + slot * 8, 2 * KSUB * PP_ACT);
+                    mbar_expect_tx(bar_full_w + slot * 8, KSUB * PP_W);
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub) {
+                        const int kx = kb * KSUB + sub;   // 64-k block
+                        tma_load_2d_pair(st + sub * PP_ACT, &tm_a, kx * PG_BK, tc * 256 + (int)rank * 128, leader_full_act + slot * 8);
+                        tma_load_2d(st + KSUB * PP_ACT + sub * PP_W, &tm_w, kx * 32, nt_i * 512 + (int)rank * 256, bar_full_w + slot * 8);
+                    }
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
             }
@@ -502,14 +512,17 @@ int4_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                             mbar_spin_cluster(bar_afull + abuf * 8, aphase, status);
                     if (!alive) break;
                     pg_fence_after();
-                    const uint64_t db = pg_desc_sw128(ring + (uint32_t)slot * PP_STAGE);
 #pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        const uint64_t da = pg_desc_sw128(a_tiles + abuf * PP_A_BUF + a * PP_A_TILE);
+                    for (int sub = 0; sub < KSUB; ++sub) {
+                        const uint64_t db = pg_desc_sw128(ring + (uint32_t)slot * PP_STAGE + sub * PP_ACT);
 #pragma unroll
-                        for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
-                            pp_mma_bf16(tmem_base + a * 256, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
-                                        (kb > 0 || kk > 0) ? 1u : 0u);
+                        for (int a = 0; a < 2; ++a) {
+                            const uint64_t da = pg_desc_sw128(a_tiles + abuf * PP_A_BUF + (sub * 2 + a) * PP_A_TILE);
+#pragma unroll
+                            for (int kk = 0; kk < PG_BK / 16; ++kk)  // K = 16 per instruction: +32 bytes
+                                pp_mma_bf16(tmem_base + a * 256, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
+                                            (kb > 0 || sub > 0 || kk > 0) ? 1u : 0u);
+                        }
                     }
                     pp_commit(bar_empty + slot * 8);
                     pp_commit(peer_empty + slot * 8);
@@ -537,32 +550,37 @@ int4_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
             const int nt_i = t % p.n_tiles;
             const float *srow[2];
             bool live_row[2];
-            float sc_next[2];
+            float sc_next[KSUB][2];
 #pragma unroll
             for (int a = 0; a < 2; ++a) {
                 const int row = nt_i * 512 + (int)rank * 256 + a * PG_BM + r;
                 live_row[a] = row < p.N;
                 srow[a] = scales + (size_t)(live_row[a] ? row : 0) * groups + half;
-                sc_next[a] = live_row[a] ? __ldg(srow[a]) : 0.0f;
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub) sc_next[sub][a] = live_row[a] ? __ldg(srow[a] + sub * 2) : 0.0f;
             }
             for (int kb = 0; kb < p.k_blocks; ++kb) {
-                float sc[2];
+                float sc[KSUB][2];
 #pragma unroll
-                for (int a = 0; a < 2; ++a) {
-                    sc[a] = sc_next[a];
-                    // the next block's scales travel while this one is converted
-                    if (kb + 1 < p.k_blocks && live_row[a]) sc_next[a] = __ldg(srow[a] + (kb + 1) * 2);
+                for (int sub = 0; sub < KSUB; ++sub) {
+#pragma unroll
+                    for (int a = 0; a < 2; ++a) {
+                        sc[sub][a] = sc_next[sub][a];
+                        // the next stage's scales travel while this one is converted
+                        if (kb + 1 < p.k_blocks && live_row[a]) sc_next[sub][a] = __ldg(srow[a] + ((kb + 1) * KSUB + sub) * 2);
+                    }
                 }
                 alive = mbar_wait(bar_full_w + slot * 8, phase, status) &&
                         mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
-                const unsigned char *st = smem + PP_ABUFS * PP_A_BUF + (size_t)slot * PP_STAGE + PP_ACT;
+                const unsigned char *st = smem + PP_ABUFS * PP_A_BUF + (size_t)slot * PP_STAGE + KSUB * PP_ACT;
 #pragma unroll
-                for (int a = 0; a < 2; ++a) {
-                    const uint4 w4 = *reinterpret_cast<const uint4 *>(st + (a * PG_BM + r) * 32 + half * 16);
+                for (int sa = 0; sa < KSUB * 2; ++sa) {
+                    const int sub = sa >> 1, a = sa & 1;
+                    const uint4 w4 = *reinterpret_cast<const uint4 *>(st + sub * PP_W + (a * PG_BM + r) * 32 + half * 16);
                     const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
-                    const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[a]);
-                    unsigned char *arow = smem + (size_t)abuf * PP_A_BUF + (size_t)a * PP_A_TILE + (size_t)r * 128;
+                    const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[sub][a]);
+                    unsigned char *arow = smem + (size_t)abuf * PP_A_BUF + (size_t)sa * PP_A_TILE + (size_t)r * 128;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const uint32_t w = words[i];
@@ -660,19 +678,22 @@ bool int4_prefill_supported(size_t m, size_t n, size_t k, size_t gs) {
            m < (1u << 30) && n < (1u << 30) && k < (1u << 30);
 }
 
+template <int KSUB>
 static int launch_prefill_pairs(yscv_cuda_ctx *ctx, const CUtensorMap &tm_w, const CUtensorMap &tm_a,
                                 const float *scales, float *out, PGParams p) {
+    using G = PPGeom<KSUB>;
     p.n_tiles = (p.N + 511) / 512;
     p.t_chunks = (p.M + 255) / 256;
-    p.k_blocks = p.K / PG_BK;
-    p.ksub = 1;
+    p.ksub = KSUB;
+    p.k_blocks = p.K / (PG_BK * KSUB);
     p.ksplit = 1;
     p.acc_bufs = 1;
-    p.stage_bytes = PP_STAGE;
-    p.stages = (227 * 1024 - PP_ABUFS * PP_A_BUF - 1024) / PP_STAGE;
+    p.stage_bytes = G::STAGE;
+    p.stages = (227 * 1024 - G::ABUFS * G::A_BUF - 1024) / G::STAGE;
     if (p.stages > 8) p.stages = 8;
-    const int smem = PP_ABUFS * PP_A_BUF + p.stages * PP_STAGE + 512;
-    int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(int4_prefill_pair_kernel), ctx->device, 227 * 1024);
+    const int smem = G::ABUFS * G::A_BUF + p.stages * G::STAGE + 512;
+    auto kern = int4_prefill_pair_kernel<KSUB>;
+    int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
     if (rc) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctx->sm_count / 2 * 2);
@@ -689,20 +710,20 @@ static int launch_prefill_pairs(yscv_cuda_ctx *ctx, const CUtensorMap &tm_w, con
     // persistent kernel with a static walk over the tiles: every pair of the grid must be resident
     if (ctx->max_prefill_pairs == 0) {
         int nres = 0;
-        YSCV_CUDA_TRY(cudaOccupancyMaxActiveClusters(&nres, int4_prefill_pair_kernel, &cfg));
+        YSCV_CUDA_TRY(cudaOccupancyMaxActiveClusters(&nres, kern, &cfg));
         ctx->max_prefill_pairs = nres > 0 ? nres : 1;
     }
     const int tiles = p.n_tiles * p.t_chunks;
     const int pairs = tiles < ctx->max_prefill_pairs ? tiles : ctx->max_prefill_pairs;
     cfg.gridDim = dim3(2 * pairs);
     ctx->prof_begin();
-    YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, int4_prefill_pair_kernel, tm_w, tm_a, scales, out, p, ctx->d_status));
+    YSCV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tm_w, tm_a, scales, out, p, ctx->d_status));
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
     snprintf(ctx->report_int4, sizeof(ctx->report_int4),
-             "int4_prefill_gemm m=%d n=%d k=%d: tcgen05 bf16 cta_group::2, pair tile 512 rows x 256 tokens, 64 k per stage, "
-             "%d stages of %d KB per CTA, %d tiles on %d CTA pairs", p.M, p.N, p.K, p.stages, PP_STAGE / 1024, tiles, pairs);
+             "int4_prefill_gemm m=%d n=%d k=%d: tcgen05 bf16 cta_group::2, pair tile 512 rows x 256 tokens, %d k per stage, "
+             "%d stages of %d KB per CTA, %d tiles on %d CTA pairs", p.M, p.N, p.K, KSUB * PG_BK, p.stages, G::STAGE / 1024, tiles, pairs);
     ctx->last_kernel = "int4_prefill_gemm(tcgen05,bf16,cta_group::2)";
     return YSCV_CUDA_OK;
 }
@@ -782,7 +803,10 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, m, k, k * 2, use_pairs ? 128u : (uint32_t)p.BT, PG_BK,
                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    if (use_pairs) return launch_prefill_pairs(ctx, tm_w, tm_a, scales, out, p);
+    if (use_pairs) {
+        const bool two = p.K % (2 * PG_BK) == 0 && !getenv("YSCV_PP_KSUB1");
+        return two ? launch_prefill_pairs<2>(ctx, tm_w, tm_a, scales, out, p) : launch_prefill_pairs<1>(ctx, tm_w, tm_a, scales, out, p);
+    }
     auto kern = NA == 2 ? int4_prefill_gemm_kernel<2, 1, false>
                         : p.ksub == 2 ? (p.ksplit > 1 ? int4_prefill_gemm_kernel<1, 2, true> : int4_prefill_gemm_kernel<1, 2, false>)
                                       : (p.ksplit > 1 ? int4_prefill_gemm_kernel<1, 1, true> : int4_prefill_gemm_kernel<1, 1, false>);
