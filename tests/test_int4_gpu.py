@@ -93,7 +93,7 @@ def test_odd_shapes(ctx, oracle, m, n, k, g):
 
 @pytest.mark.parametrize("m,n,k", [(17, 128, 64), (128, 2560, 2048), (200, 1000, 1024), (333, 130, 4096),
                                    (512, 4096, 512), (1024, 300, 256), (2048, 1024, 2048), (1100, 8000, 512),
-                                   (64, 1024, 4096), (2048, 4608, 1024)])
+                                   (64, 1024, 4096), (2048, 4608, 1024), (1100, 8000, 448)])
 def test_prefill_gemm(ctx, oracle, m, n, k):
     g = 32
     packed, scales = make_weights(oracle, 21, n, k, g)
@@ -103,7 +103,7 @@ def test_prefill_gemm(ctx, oracle, m, n, k):
     assert "prefill" in ctx.last_kernel()
     report = ctx.dispatch_report()
     if (m, n, k) == (1100, 8000, 512):     # enough tiles for CTA pairs (512 weight rows x 256 tokens), ragged in both
-        assert "pair tile 512 rows x 256 tokens" in report, report
+        assert "pair tile 512 rows x 256 tokens, 128 k per stage" in report, report
         ctx.set_int4_prefill_cta_pairs(False)
         try:
             one = ctx.packed_int4_gemm(packed, scales, act, m, n, k, g)
@@ -112,6 +112,8 @@ def test_prefill_gemm(ctx, oracle, m, n, k):
             ctx.set_int4_prefill_cta_pairs(True)
         # same bf16 products, same order over k
         assert np.array_equal(one, got)
+    if (m, n, k) == (1100, 8000, 448):     # K not a multiple of 128: CTA pairs with one 64-k sub-block per stage
+        assert "pair tile 512 rows x 256 tokens, 64 k per stage" in report, report
     if (m, n, k) == (64, 1024, 4096):      # a wide decode batch on a narrow matrix: two sub-blocks, K slices
         assert "128 k per stage" in report and "K slice(s)" in report and "1 K slice(s)" not in report, report
     e = fro_err(got, want)

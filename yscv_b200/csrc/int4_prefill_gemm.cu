@@ -804,7 +804,8 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     if (use_pairs) {
-        const bool two = p.K % (2 * PG_BK) == 0 && !getenv("YSCV_PP_KSUB1");
+        // two 64-k sub-blocks per stage and hand-over whenever K allows: 243 -> 232 us on 2048 x 8192 x 8192
+        const bool two = p.K % (2 * PG_BK) == 0;
         return two ? launch_prefill_pairs<2>(ctx, tm_w, tm_a, scales, out, p) : launch_prefill_pairs<1>(ctx, tm_w, tm_a, scales, out, p);
     }
     auto kern = NA == 2 ? int4_prefill_gemm_kernel<2, 1, false>
