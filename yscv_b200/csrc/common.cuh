@@ -124,6 +124,14 @@ struct yscv_cuda_ctx {
     yscv::DeviceBuffer gemm_ws, gemm_flags;
     int gemm_epoch = 0;
     bool int8_tail_split = true;
+    // encoded TMA descriptors of the last few decode GEMV weight matrices (int4_gemv.cu)
+    struct TmCacheEntry {
+        const void *a = nullptr, *b = nullptr;
+        int n = 0, k = 0, rows = 0, gs = 0;
+        alignas(64) unsigned char w[128], s[128];
+    };
+    TmCacheEntry tm_cache[16];
+    int tm_next = 0;
     // variant / tile report of the last int4 and int8 dispatch (yscv_cuda_dispatch_report)
     char report_int4[224] = "none";
     char report_int8[224] = "none";

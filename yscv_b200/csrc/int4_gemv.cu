@@ -496,14 +496,27 @@ static int launch_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scale
     const int smem = g.stages * g.stage_bytes + red_bytes + bar_bytes + digit_bytes + g.act_bytes;
     // tensor maps: weights as bytes [N][K/2], box [rb_rows][128] with the 128-byte swizzle;
     // scales as f32 [N][K/32], box [rb_rows][GS] with the swizzle that matches its width
-    CUtensorMap tm_w, tm_s;
-    int rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, (uint64_t)N, (uint64_t)K / 2,
-                       (uint64_t)K / 2, (uint32_t)rb_rows, 128, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc) return rc;
-    rc = encode_2d(&tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, scales, (uint64_t)N, (uint64_t)K / 32,
-                   (uint64_t)K / 8, (uint32_t)rb_rows, GS,
-                   GS == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
-    if (rc) return rc;
+    // (a decode loop calls with the same few weight matrices over and over: the encoded maps of the
+    // last calls are kept in the context; a map depends only on the addresses and the shape)
+    static_assert(sizeof(CUtensorMap) == sizeof(ctx->tm_cache[0].w), "tensor map size");
+    int rc;
+    yscv_cuda_ctx::TmCacheEntry *ce = nullptr;
+    for (auto &e : ctx->tm_cache)
+        if (e.a == wq && e.b == scales && e.n == N && e.k == K && e.rows == rb_rows && e.gs == GS) ce = &e;
+    if (!ce) {
+        ce = &ctx->tm_cache[ctx->tm_next];
+        ctx->tm_next = (ctx->tm_next + 1) % (int)(sizeof(ctx->tm_cache) / sizeof(ctx->tm_cache[0]));
+        ce->a = nullptr;
+        rc = encode_2d(reinterpret_cast<CUtensorMap *>(ce->w), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, (uint64_t)N,
+                       (uint64_t)K / 2, (uint64_t)K / 2, (uint32_t)rb_rows, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        rc = encode_2d(reinterpret_cast<CUtensorMap *>(ce->s), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, scales, (uint64_t)N,
+                       (uint64_t)K / 32, (uint64_t)K / 8, (uint32_t)rb_rows, GS,
+                       GS == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+        if (rc) return rc;
+        ce->a = wq; ce->b = scales; ce->n = N; ce->k = K; ce->rows = rb_rows; ce->gs = GS;
+    }
+    const CUtensorMap &tm_w = *reinterpret_cast<const CUtensorMap *>(ce->w), &tm_s = *reinterpret_cast<const CUtensorMap *>(ce->s);
     auto kern = int4_gemv_fast_kernel<MP, GS, TP2, FUSEQ>;
     rc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
     if (rc) return rc;
