@@ -141,6 +141,12 @@ int yscv_cuda_ctx_set_int8_tail_split(yscv_cuda_ctx *ctx, int enable);
  * softmax weights are split into two fp16 terms), which differs from the fp32 loop (0) only in
  * summation order. */
 int yscv_cuda_ctx_set_attention_tensor_cores(yscv_cuda_ctx *ctx, int enable);
+/* fp32 matmul of the decoder (yscv_cuda_f32_matmul_dev: the fp32 LM head) with more than 8
+ * activation rows and k a multiple of 32: on by default, every fp32 product runs as three TF32
+ * tensor-core products with fp32 accumulators (operands split into a TF32 part and a remainder;
+ * relative error of a product ~2^-21), the weights cross HBM once; 0 keeps the tiled fp32 FMA
+ * kernel. */
+int yscv_cuda_ctx_set_f32_tensor_cores(yscv_cuda_ctx *ctx, int enable);
 /* Per-kernel timing, the counterpart of YSCV_RUNNER_PROFILE
  * (crates/yscv-onnx/src/runner/profile.rs:1-120): while enabled, the dominant
  * kernel of every call is bracketed by CUDA events on the context's stream

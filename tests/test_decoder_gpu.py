@@ -605,22 +605,31 @@ def test_int8_kv_cache_bytes(tctx, oracle):
 
 
 def test_f32_matmul_wide_batch(tctx):
-    """The LM-head product for more than 8 rows (tiled kernel) against float64, ragged edges."""
+    """The LM-head product for more than 8 rows against float64: the 3xTF32 tensor-core kernel (k a
+    multiple of 32; ragged rows and columns, more than one pass of 256 rows, more tiles than CTAs) and
+    the tiled FMA kernel (any k, or on request). Both keep fp32 accuracy."""
     import torch
     ctx, s = tctx
     rng = np.random.default_rng(31)
-    for m, n, k in [(9, 1000, 512), (32, 3207, 2048), (70, 130, 36)]:
+    for m, n, k, tc in [(9, 1000, 512, True), (32, 3207, 2048, True), (70, 130, 36, False), (64, 20000, 256, True),
+                        (300, 515, 96, True), (33, 129, 32, True)]:
         w = rng.normal(0, 0.02, (n, k)).astype(np.float32)
         x = rng.normal(0, 1.0, (m, k)).astype(np.float32)
         d_w, d_x = dev(w), dev(x)
-        out = torch.full((m, n), float("nan"), device="cuda")
-        with torch.cuda.stream(s):
-            ctx.f32_matmul_dev(d_w.data_ptr(), d_x.data_ptr(), m, n, k, out.data_ptr())
-        s.synchronize()
-        assert "tiled" in ctx.last_kernel()
         want = x.astype(np.float64) @ w.astype(np.float64).T
-        got = out.cpu().numpy()
-        assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 1e-5, (m, n, k)
+        for allow in (True, False):
+            out = torch.full((m, n), float("nan"), device="cuda")
+            ctx.set_f32_tensor_cores(allow)
+            try:
+                with torch.cuda.stream(s):
+                    ctx.f32_matmul_dev(d_w.data_ptr(), d_x.data_ptr(), m, n, k, out.data_ptr())
+                s.synchronize()
+            finally:
+                ctx.set_f32_tensor_cores(True)
+            assert ("3xtf32" in ctx.last_kernel()) == (allow and tc), ctx.last_kernel()
+            assert ("tiled" in ctx.last_kernel()) == (not (allow and tc))
+            got = out.cpu().numpy()
+            assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 1e-5, (m, n, k, allow)
     assert ctx.device_status() == 0
 
 

@@ -272,6 +272,12 @@ int yscv_cuda_ctx_set_int8_tail_split(yscv_cuda_ctx *ctx, int enable) {
     return YSCV_CUDA_OK;
 }
 
+int yscv_cuda_ctx_set_f32_tensor_cores(yscv_cuda_ctx *ctx, int enable) {
+    if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
+    ctx->f32_tensor_cores = enable != 0;
+    return YSCV_CUDA_OK;
+}
+
 int yscv_cuda_ctx_set_attention_tensor_cores(yscv_cuda_ctx *ctx, int enable) {
     if (!ctx) return fail(YSCV_CUDA_ERR_BAD_ARG, "ctx is null");
     ctx->attn_tensor_cores = enable != 0;

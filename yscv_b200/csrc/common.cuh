@@ -103,6 +103,7 @@ struct yscv_cuda_ctx {
     bool prefill_exact = false;  // int4 matmul with m > 16: fp32-exact kernel instead of bf16 MMA
     bool prefill_pairs = true;   // int4 prefill GEMM: CTA-pair kernel (cta_group::2) for large prefills
     int max_prefill_pairs = 0;   // CTA pairs of that kernel that can be resident at once (0: not asked yet)
+    bool f32_tensor_cores = true;   // fp32 matmul with more than 8 rows: 3xTF32 tensor-core kernel (else the SIMT tiled kernel)
     bool attn_tensor_cores = true;  // decode attention over int8 caches: mma.sync kernel (else the fp32 loop)
     int int8_pairs = -1;         // int8 GEMM, CTA-pair kernel (cta_group::2): -1 where it measured faster, 0 never, 1 wherever the shape allows
     int max_pairs = 0;           // CTA pairs of that kernel that can be resident at once (0: not asked yet)

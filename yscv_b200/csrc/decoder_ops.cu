@@ -1039,8 +1039,18 @@ int yscv_cuda_f32_matmul_dev(yscv_cuda_ctx *ctx, const float *d_w, const float *
         return fail(YSCV_CUDA_ERR_UNSUPPORTED, "weights and activations must be 16-byte aligned");
     if (m * n == 0) return YSCV_CUDA_OK;
     const unsigned blocks = (unsigned)((n + 7) / 8 < (size_t)(16 * ctx->sm_count) ? (n + 7) / 8 : 16 * ctx->sm_count);
+    if (m > 8 && ctx->f32_tensor_cores && f32_gemm_tc_supported(d_w, d_x, m, n, k)) {
+        // wide batch: three TF32 products per fp32 product on the tensor cores, weights read once
+        int rc = ctx->scratch.reserve(f32_gemm_tc_scratch_bytes(m, k));
+        if (rc) return rc;
+        rc = f32_gemm_tc(ctx, d_w, d_x, m, n, k, d_out, ctx->scratch.ptr);
+        if (rc) return rc;
+        ctx->last_kernel = "f32_matmul(tcgen05,3xtf32)";
+        return YSCV_CUDA_OK;
+    }
     if (m > 8) {
-        // wide batch: tiled SGEMM, the weights cross HBM once per 64 activation rows
+        // wide batch without the tensor-core form (k not a multiple of 32): tiled SGEMM, the weights
+        // cross HBM once per 64 activation rows
         dim3 grid((unsigned)((n + FM_BN - 1) / FM_BN), (unsigned)((m + FM_BM - 1) / FM_BM));
         YSCV_CUDA_TRY(launch_pdl(f32_matmul_tiled_kernel, grid, dim3(256), 0, ctx->stream, d_w, d_x, d_out, (int)m, (int)n, (int)k));
         YSCV_CUDA_TRY(cudaGetLastError());

@@ -11,6 +11,12 @@ namespace yscv {
 // int4_gemv.cu
 bool int4_gemv_fast_supported(size_t m, size_t n, size_t k, size_t gs);
 size_t int4_gemv_scratch_bytes(size_t m, size_t k);
+// fp32 matmul out[m][n] = sum_k x[m][k] w[n][k] for m > 8 as three TF32 products per fp32 product
+// on the tensor cores (f32_gemm_tf32x3.cu)
+bool f32_gemm_tc_supported(const float *d_w, const float *d_x, size_t m, size_t n, size_t k);
+size_t f32_gemm_tc_scratch_bytes(size_t m, size_t k);
+int f32_gemm_tc(yscv_cuda_ctx *ctx, const float *d_w, const float *d_x, size_t m, size_t n, size_t k,
+                float *d_out, void *scratch);
 int int4_gemv_fast(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, const float *act,
                    float *out, size_t m, size_t n, size_t k, void *scratch);
 int int4_gemv_generic(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales,

@@ -45,6 +45,7 @@ SIGNATURES = {
     "yscv_cuda_ctx_set_int4_prefill_cta_pairs": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_set_int8_tail_split": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_set_attention_tensor_cores": (C.c_int, [_vp, C.c_int]),
+    "yscv_cuda_ctx_set_f32_tensor_cores": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_enable": (C.c_int, [_vp, C.c_int]),
     "yscv_cuda_ctx_profile_read": (C.c_int, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "yscv_cuda_int4_matmul": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
@@ -494,6 +495,10 @@ class Context:
         """int8 GEMM: None = the CTA-pair kernel (cta_group::2) where it measured faster (default),
         False = the one-CTA kernel everywhere, True = the pair kernel on every shape it supports."""
         _check(self.lib.yscv_cuda_ctx_set_int8_cta_pairs(self.handle, -1 if on is None else int(bool(on))))
+
+    def set_f32_tensor_cores(self, on: bool):
+        """fp32 matmul with more than 8 rows: the 3xTF32 tensor-core kernel (default) or the tiled FMA kernel."""
+        _check(self.lib.yscv_cuda_ctx_set_f32_tensor_cores(self.handle, int(bool(on))))
 
     def set_attention_tensor_cores(self, on: bool):
         """Decode attention over int8 caches: fp16 tensor-core kernel (default) or the fp32 loop."""
