@@ -604,6 +604,53 @@ def test_int8_kv_cache_bytes(tctx, oracle):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("B,seq,p0,nq,nkv,d,causal,i8", [
+    (2, 100, 0, 8, 2, 64, True, False),      # tiles of 4 positions x 4 heads, ragged last tile, two key chunks
+    (1, 70, 37, 8, 1, 128, True, False),     # a prompt appended behind 37 cached positions, 8 heads per KV head
+    (1, 33, 0, 6, 2, 64, False, False),      # not causal, 3 heads per KV head (5 positions per tile)
+    (2, 130, 5, 16, 4, 128, True, True),     # int8 cache, three key chunks
+])
+def test_prompt_attention_in_tiles(tctx, oracle, B, seq, p0, nq, nkv, d, causal, i8):
+    """The prompt-pass attention kernel (query positions in tiles, keys and values staged in shared memory
+    once per tile, chunked softmax) against the oracle's attention over the same cache contents."""
+    import torch
+    ctx, s = tctx
+    rng = np.random.default_rng(77)
+    total = p0 + seq
+    max_seq = total + 3
+    q = rng.normal(0, 1, (B, seq, nq * d)).astype(np.float32)
+    if i8:
+        kq = rng.integers(-127, 128, (B, max_seq, nkv * d), dtype=np.int8)
+        vq = rng.integers(-127, 128, (B, max_seq, nkv * d), dtype=np.int8)
+        ksc = rng.uniform(0.005, 0.02, (B, max_seq)).astype(np.float32)
+        vsc = rng.uniform(0.005, 0.02, (B, max_seq)).astype(np.float32)
+        kf = (kq.astype(np.float32) * ksc[:, :, None]).astype(np.float32)
+        vf = (vq.astype(np.float32) * vsc[:, :, None]).astype(np.float32)
+    else:
+        kf = rng.normal(0, 1, (B, max_seq, nkv * d)).astype(np.float32)
+        vf = rng.normal(0, 1, (B, max_seq, nkv * d)).astype(np.float32)
+    pos = dev(np.array([p0], np.int32))
+    out = torch.full((B * seq, nq * d), float("nan"), device="cuda")
+    d_q = dev(q.reshape(B * seq, -1))
+    with torch.cuda.stream(s):
+        if i8:
+            d_k, d_v, d_ks, d_vs = dev(kq), dev(vq), dev(ksc), dev(vsc)
+            ctx.gqa_attention_i8_dev(d_q.data_ptr(), nq * d, B, seq, nq, nkv, d, d_k.data_ptr(), d_ks.data_ptr(),
+                                     d_v.data_ptr(), d_vs.data_ptr(), max_seq, pos.data_ptr(), causal, out.data_ptr())
+        else:
+            d_k, d_v = dev(kf), dev(vf)
+            ctx.gqa_attention_dev(d_q.data_ptr(), nq * d, B, seq, nq, nkv, d, d_k.data_ptr(), d_v.data_ptr(), max_seq,
+                                  pos.data_ptr(), causal, out.data_ptr())
+    s.synchronize()
+    assert "prompt tiles" in ctx.last_kernel(), ctx.last_kernel()
+    got = out.cpu().numpy().reshape(B, seq, -1)
+    for b in range(B):
+        want = oracle.gqa_attention(q[b].ravel(), kf[b, :total].ravel(), vf[b, :total].ravel(), 1, seq, total, nq, nkv, d,
+                                    causal).reshape(seq, -1)
+        assert np.max(np.abs(got[b] - want)) < 2e-5, (b, float(np.max(np.abs(got[b] - want))))
+    assert ctx.device_status() == 0
+
+
 def test_f32_matmul_wide_batch(tctx):
     """The LM-head product for more than 8 rows against float64: the 3xTF32 tensor-core kernel (k a
     multiple of 32; ragged rows and columns, more than one pass of 256 rows, more tiles than CTAs) and

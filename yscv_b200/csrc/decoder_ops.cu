@@ -244,6 +244,118 @@ gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n
     }
 }
 
+// Prompt-pass attention (many query positions per sequence): the kernel above reads every key and
+// value row of a sequence once per (query position, query head), from L2: 137 GB per layer for a
+// 2048-token prompt at the 70B shape. Here a block takes QB consecutive query positions x all the
+// query heads of ONE KV head (a warp per (position, head), G * QB <= 16 warps) and walks the keys in
+// chunks of 64 rows staged in shared memory (dequantised on the way in for int8 caches), so a row
+// is read once per block; every warp keeps a running maximum, exp-sum and unnormalised output
+// (the usual max-rescaling of a chunked softmax), lanes striding the head dimension.
+// D = head size (64 or 128); dynamic shared memory: keys [64][D], values [64][D], weights [warps][64].
+constexpr int PF_KT = 64;
+template <typename KV, int D>
+__global__ void __launch_bounds__(512)
+gqa_prefill_tiled_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n_q, int n_kv,
+                         const KV *__restrict__ kc, const KV *__restrict__ vc,
+                         const float *__restrict__ kscale, const float *__restrict__ vscale, int max_seq,
+                         const int32_t *__restrict__ pos, int causal, float *__restrict__ out, int QB) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr bool I8 = sizeof(KV) == 1;
+    constexpr int PER = D / 32;
+    extern __shared__ __align__(16) float pf_sm[];
+    float *ks = pf_sm, *vs = pf_sm + PF_KT * D, *sc_all = vs + PF_KT * D;
+    const int G = n_q / n_kv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = warp % G, qi = warp / G;
+    const int sq = blockIdx.x * QB + qi, kv_h = blockIdx.y, b = blockIdx.z;
+    const int qh = kv_h * G + g;
+    const bool live = sq < seq_q;
+    const int p0 = *pos;
+    auto limit_of = [&](int s) {
+        const int l = p0 + (causal ? s + 1 : seq_q);
+        return l > max_seq ? max_seq : (l < 0 ? 0 : l);
+    };
+    const int my_limit = live ? limit_of(sq) : 0;
+    const int last_sq = min(seq_q, ((int)blockIdx.x + 1) * QB) - 1;
+    const int block_limit = limit_of(last_sq);   // limits do not decrease with the position
+    const float scale = 1.0f / sqrtf((float)D);
+    float qr[PER], acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        qr[i] = live ? q[((size_t)b * seq_q + sq) * q_stride + (size_t)qh * D + lane + 32 * i] : 0.0f;
+        acc[i] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    float *sc = sc_all + warp * PF_KT;
+    const size_t row_elems = (size_t)n_kv * D;
+    const KV *kb = kc + (size_t)b * max_seq * row_elems + (size_t)kv_h * D;
+    const KV *vb = vc + (size_t)b * max_seq * row_elems + (size_t)kv_h * D;
+    for (int c0 = 0; c0 < block_limit; c0 += PF_KT) {
+        const int rows = min(PF_KT, block_limit - c0);
+        // stage the chunk: 4 values per thread and step
+        for (int idx = threadIdx.x; idx < rows * (D / 4); idx += blockDim.x) {
+            const int r = idx / (D / 4), c4 = (idx % (D / 4)) * 4;
+            const size_t off = (size_t)(c0 + r) * row_elems + c4;
+            float4 kv4, vv4;
+            if constexpr (I8) {
+                const float rk = kscale[(size_t)b * max_seq + c0 + r], rv = vscale[(size_t)b * max_seq + c0 + r];
+                const char4 k4 = *reinterpret_cast<const char4 *>(kb + off), v4 = *reinterpret_cast<const char4 *>(vb + off);
+                kv4 = make_float4(__fmul_rn((float)k4.x, rk), __fmul_rn((float)k4.y, rk), __fmul_rn((float)k4.z, rk), __fmul_rn((float)k4.w, rk));
+                vv4 = make_float4(__fmul_rn((float)v4.x, rv), __fmul_rn((float)v4.y, rv), __fmul_rn((float)v4.z, rv), __fmul_rn((float)v4.w, rv));
+            } else {
+                kv4 = *reinterpret_cast<const float4 *>(kb + off);
+                vv4 = *reinterpret_cast<const float4 *>(vb + off);
+            }
+            *reinterpret_cast<float4 *>(ks + r * D + c4) = kv4;
+            *reinterpret_cast<float4 *>(vs + r * D + c4) = vv4;
+        }
+        __syncthreads();
+        const int nk = min(rows, my_limit - c0);
+        if (nk > 0) {
+            float cm = -INFINITY;
+            for (int k = 0; k < nk; ++k) {
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < PER; ++i) dot = fmaf(qr[i], ks[k * D + lane + 32 * i], dot);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                const float sv = dot * scale;
+                if (lane == 0) sc[k] = sv;
+                cm = fmaxf(cm, sv);
+            }
+            const float m_new = fmaxf(m, cm);
+            const float alpha = expf(m - m_new);   // 0 for the first chunk
+            __syncwarp();
+            float ps = 0.0f;
+            for (int k = lane; k < nk; k += 32) {
+                const float e = expf(sc[k] - m_new);
+                sc[k] = e;
+                ps += e;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+            l = l * alpha + ps;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) acc[i] *= alpha;
+            __syncwarp();
+            for (int k = 0; k < nk; ++k) {
+                const float pk = sc[k];
+#pragma unroll
+                for (int i = 0; i < PER; ++i) acc[i] = fmaf(pk, vs[k * D + lane + 32 * i], acc[i]);
+            }
+            m = m_new;
+        }
+        __syncthreads();
+    }
+    if (live) {
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        float *orow = out + ((size_t)b * seq_q + sq) * (size_t)n_q * D + (size_t)qh * D;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) orow[lane + 32 * i] = acc[i] * inv;
+    }
+}
+
 // Decode-shaped attention (one query position per sequence) with the keys split across
 // blocks so that a long cache fills the machine: block (split, kv head, b) handles keys
 // [split*chunk, ...) for ALL the query heads of its KV head's group from one pass over the
@@ -986,6 +1098,22 @@ static int gqa_attention_impl(yscv_cuda_ctx *ctx, const float *d_q, size_t q_str
         YSCV_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3(dim3((unsigned)n_q, (unsigned)batch)), dim3(128), 0, ctx->stream, part, n_splits,
                                                                                                (int)d_head, d_out));
         DEC_EPILOGUE(ctx, sizeof(KV) == 1 ? "gqa_attention(split-k,int8 cache)" : "gqa_attention(split-k)");
+    }
+    // a prompt pass: query positions in tiles, keys and values staged once per tile
+    const size_t group = n_q / n_kv;
+    const bool rows_aligned = ((reinterpret_cast<uintptr_t>(d_kcache) | reinterpret_cast<uintptr_t>(d_vcache)) & 15) == 0;
+    if (seq_q >= 16 && (d_head == 64 || d_head == 128) && group <= 16 && rows_aligned) {
+        const int QB = (int)(16 / group);
+        const int warps = (int)group * QB;
+        const size_t pf_smem = (2 * PF_KT * d_head + (size_t)warps * PF_KT) * sizeof(float);
+        auto kern = d_head == 64 ? gqa_prefill_tiled_kernel<KV, 64> : gqa_prefill_tiled_kernel<KV, 128>;
+        int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 100 * 1024);
+        if (arc) return arc;
+        dim3 pgrid((unsigned)((seq_q + QB - 1) / QB), (unsigned)n_kv, (unsigned)batch);
+        YSCV_CUDA_TRY(launch_pdl(kern, dim3(pgrid), dim3(32 * warps), pf_smem, ctx->stream, d_q, (int)q_stride, (int)seq_q,
+                                 (int)n_q, (int)n_kv, d_kcache, d_vcache, d_kscale, d_vscale, (int)max_seq, d_pos, causal,
+                                 d_out, QB));
+        DEC_EPILOGUE(ctx, sizeof(KV) == 1 ? "gqa_attention(prompt tiles,int8 cache)" : "gqa_attention(prompt tiles)");
     }
     const size_t smem = (max_seq + d_head) * sizeof(float);
     if (smem > 200 * 1024) return fail(YSCV_CUDA_ERR_UNSUPPORTED, "max_seq %zu too long for the attention kernel", max_seq);
