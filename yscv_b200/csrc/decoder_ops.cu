@@ -247,14 +247,19 @@ gqa_attention_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n
 // Prompt-pass attention (many query positions per sequence): the kernel above reads every key and
 // value row of a sequence once per (query position, query head), from L2: 137 GB per layer for a
 // 2048-token prompt at the 70B shape. Here a block takes QB consecutive query positions x all the
-// query heads of ONE KV head (a warp per (position, head), G * QB <= 16 warps) and walks the keys in
-// chunks of 64 rows staged in shared memory (dequantised on the way in for int8 caches), so a row
-// is read once per block; every warp keeps a running maximum, exp-sum and unnormalised output
-// (the usual max-rescaling of a chunked softmax), lanes striding the head dimension.
-// D = head size (64 or 128); dynamic shared memory: keys [64][D], values [64][D], weights [warps][64].
-constexpr int PF_KT = 64;
+// query heads of ONE KV head, 64 (position, head) pairs, four per warp, and walks the keys in chunks
+// of 64 rows staged in shared memory (dequantised on the way in for int8 caches), so a row is read
+// from L2 once per block. Scores: a lane per key (its row read 16 bytes at a time, the four query
+// rows broadcast from shared memory: every key value read feeds four FMAs). Weighted value sum: a
+// lane owns four consecutive elements of the head (with D = 64 the half warps take alternate keys),
+// every value read again feeds four FMAs. Each pair keeps a running maximum, exp-sum and
+// unnormalised output (the usual max-rescaling of a chunked softmax).
+// D = head size (64 or 128); dynamic shared memory: keys [64][D + 4], values [64][D], weights
+// [pairs][64], query rows [pairs][D].
+constexpr int PF_KT = 64;      // keys per chunk
+constexpr int PF_QH = 4;       // (position, head) pairs per warp
 template <typename KV, int D>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, 1)
 gqa_prefill_tiled_kernel(const float *__restrict__ q, int q_stride, int seq_q, int n_q, int n_kv,
                          const KV *__restrict__ kc, const KV *__restrict__ vc,
                          const float *__restrict__ kscale, const float *__restrict__ vscale, int max_seq,
@@ -262,32 +267,49 @@ gqa_prefill_tiled_kernel(const float *__restrict__ q, int q_stride, int seq_q, i
     pdl_wait();
     pdl_trigger();
     constexpr bool I8 = sizeof(KV) == 1;
-    constexpr int PER = D / 32;
+    constexpr int KP = D + 4;   // key row pitch: a lane per key reads its row 16 bytes at a time without bank conflicts
+    constexpr int KPAR = 32 / (D / 4);
     extern __shared__ __align__(16) float pf_sm[];
-    float *ks = pf_sm, *vs = pf_sm + PF_KT * D, *sc_all = vs + PF_KT * D;
+    const int n_pairs = (blockDim.x >> 5) * PF_QH;
+    float *ks = pf_sm, *vs = pf_sm + PF_KT * KP, *sc_all = vs + PF_KT * D;
+    float *qs_all = sc_all + n_pairs * PF_KT;
     const int G = n_q / n_kv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = warp % G, qi = warp / G;
-    const int sq = blockIdx.x * QB + qi, kv_h = blockIdx.y, b = blockIdx.z;
-    const int qh = kv_h * G + g;
-    const bool live = sq < seq_q;
+    const int kv_h = blockIdx.y, b = blockIdx.z;
     const int p0 = *pos;
     auto limit_of = [&](int s) {
         const int l = p0 + (causal ? s + 1 : seq_q);
         return l > max_seq ? max_seq : (l < 0 ? 0 : l);
     };
-    const int my_limit = live ? limit_of(sq) : 0;
+    // this warp's pairs: index warp * 4 + j -> head idx % G of the group, position idx / G of the tile
+    int sq[PF_QH], qh[PF_QH], lim[PF_QH];
+    bool live[PF_QH];
+    int warp_limit = 0;
+#pragma unroll
+    for (int j = 0; j < PF_QH; ++j) {
+        const int idx = warp * PF_QH + j;
+        sq[j] = blockIdx.x * QB + idx / G;
+        qh[j] = kv_h * G + idx % G;
+        live[j] = idx < G * QB && sq[j] < seq_q;
+        lim[j] = live[j] ? limit_of(sq[j]) : 0;
+        warp_limit = max(warp_limit, lim[j]);
+    }
     const int last_sq = min(seq_q, ((int)blockIdx.x + 1) * QB) - 1;
     const int block_limit = limit_of(last_sq);   // limits do not decrease with the position
     const float scale = 1.0f / sqrtf((float)D);
-    float qr[PER], acc[PER];
+    const int e4 = (lane % (D / 4)) * 4, kpar = lane / (D / 4);
+    float4 acc[PF_QH];
+    float m[PF_QH], l[PF_QH];
+    float *sc = sc_all + warp * PF_QH * PF_KT, *qs = qs_all + warp * PF_QH * D;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        qr[i] = live ? q[((size_t)b * seq_q + sq) * q_stride + (size_t)qh * D + lane + 32 * i] : 0.0f;
-        acc[i] = 0.0f;
+    for (int j = 0; j < PF_QH; ++j) {
+        acc[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        m[j] = -INFINITY;
+        l[j] = 0.0f;
+        for (int i = lane; i < D; i += 32)
+            qs[j * D + i] = live[j] ? q[((size_t)b * seq_q + sq[j]) * q_stride + (size_t)qh[j] * D + i] : 0.0f;
     }
-    float m = -INFINITY, l = 0.0f;
-    float *sc = sc_all + warp * PF_KT;
+    __syncwarp();
     const size_t row_elems = (size_t)n_kv * D;
     const KV *kb = kc + (size_t)b * max_seq * row_elems + (size_t)kv_h * D;
     const KV *vb = vc + (size_t)b * max_seq * row_elems + (size_t)kv_h * D;
@@ -307,52 +329,89 @@ gqa_prefill_tiled_kernel(const float *__restrict__ q, int q_stride, int seq_q, i
                 kv4 = *reinterpret_cast<const float4 *>(kb + off);
                 vv4 = *reinterpret_cast<const float4 *>(vb + off);
             }
-            *reinterpret_cast<float4 *>(ks + r * D + c4) = kv4;
+            *reinterpret_cast<float4 *>(ks + r * KP + c4) = kv4;
             *reinterpret_cast<float4 *>(vs + r * D + c4) = vv4;
         }
         __syncthreads();
-        const int nk = min(rows, my_limit - c0);
-        if (nk > 0) {
-            float cm = -INFINITY;
-            for (int k = 0; k < nk; ++k) {
-                float dot = 0.0f;
+        const int nkw = min(rows, warp_limit - c0);   // keys of this chunk any of the warp's pairs attends to
+        if (nkw > 0) {
+            // scores: a lane per key (keys lane and lane + 32 of the chunk)
+            float sv[2][PF_QH];
 #pragma unroll
-                for (int i = 0; i < PER; ++i) dot = fmaf(qr[i], ks[k * D + lane + 32 * i], dot);
+            for (int h = 0; h < 2; ++h) {
+                const int k = lane + 32 * h;
+                float dot[PF_QH];
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                const float sv = dot * scale;
-                if (lane == 0) sc[k] = sv;
-                cm = fmaxf(cm, sv);
+                for (int j = 0; j < PF_QH; ++j) dot[j] = 0.0f;
+                if (32 * h < nkw) {   // the same for the whole warp
+                    const float4 *kr = reinterpret_cast<const float4 *>(ks + k * KP);
+#pragma unroll 4
+                    for (int i = 0; i < D / 4; ++i) {
+                        const float4 kk = kr[i];
+#pragma unroll
+                        for (int j = 0; j < PF_QH; ++j) {
+                            const float4 a = reinterpret_cast<const float4 *>(qs + j * D)[i];
+                            dot[j] = fmaf(a.x, kk.x, dot[j]);
+                            dot[j] = fmaf(a.y, kk.y, dot[j]);
+                            dot[j] = fmaf(a.z, kk.z, dot[j]);
+                            dot[j] = fmaf(a.w, kk.w, dot[j]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < PF_QH; ++j)
+                    sv[h][j] = k < lim[j] - c0 && k < rows ? dot[j] * scale : -INFINITY;   // rows past the limit hold stale values
             }
-            const float m_new = fmaxf(m, cm);
-            const float alpha = expf(m - m_new);   // 0 for the first chunk
+#pragma unroll
+            for (int j = 0; j < PF_QH; ++j) {
+                float cm = fmaxf(sv[0][j], sv[1][j]);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+                const float m_new = fmaxf(m[j], cm);
+                // a pair whose limit lies before this chunk keeps its state (m_new == m, nothing added)
+                const float alpha = m_new == -INFINITY ? 1.0f : expf(m[j] - m_new);   // 0 for a pair's first chunk
+                float ps = 0.0f;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float e = sv[h][j] == -INFINITY ? 0.0f : expf(sv[h][j] - m_new);
+                    sc[j * PF_KT + lane + 32 * h] = e;
+                    ps += e;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+                l[j] = l[j] * alpha + ps;
+                acc[j].x *= alpha; acc[j].y *= alpha; acc[j].z *= alpha; acc[j].w *= alpha;
+                m[j] = m_new;
+            }
             __syncwarp();
-            float ps = 0.0f;
-            for (int k = lane; k < nk; k += 32) {
-                const float e = expf(sc[k] - m_new);
-                sc[k] = e;
-                ps += e;
+#pragma unroll 2
+            for (int k = kpar; k < nkw; k += KPAR) {
+                const float4 v4 = *reinterpret_cast<const float4 *>(vs + k * D + e4);
+#pragma unroll
+                for (int j = 0; j < PF_QH; ++j) {
+                    const float pk = sc[j * PF_KT + k];   // 0 past the pair's limit
+                    acc[j].x = fmaf(pk, v4.x, acc[j].x);
+                    acc[j].y = fmaf(pk, v4.y, acc[j].y);
+                    acc[j].z = fmaf(pk, v4.z, acc[j].z);
+                    acc[j].w = fmaf(pk, v4.w, acc[j].w);
+                }
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-            l = l * alpha + ps;
-#pragma unroll
-            for (int i = 0; i < PER; ++i) acc[i] *= alpha;
-            __syncwarp();
-            for (int k = 0; k < nk; ++k) {
-                const float pk = sc[k];
-#pragma unroll
-                for (int i = 0; i < PER; ++i) acc[i] = fmaf(pk, vs[k * D + lane + 32 * i], acc[i]);
-            }
-            m = m_new;
         }
         __syncthreads();
     }
-    if (live) {
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        float *orow = out + ((size_t)b * seq_q + sq) * (size_t)n_q * D + (size_t)qh * D;
 #pragma unroll
-        for (int i = 0; i < PER; ++i) orow[lane + 32 * i] = acc[i] * inv;
+    for (int j = 0; j < PF_QH; ++j) {
+        if constexpr (KPAR == 2) {
+            acc[j].x += __shfl_xor_sync(0xffffffffu, acc[j].x, 16);
+            acc[j].y += __shfl_xor_sync(0xffffffffu, acc[j].y, 16);
+            acc[j].z += __shfl_xor_sync(0xffffffffu, acc[j].z, 16);
+            acc[j].w += __shfl_xor_sync(0xffffffffu, acc[j].w, 16);
+        }
+        if (live[j] && kpar == 0) {
+            const float inv = l[j] > 0.0f ? 1.0f / l[j] : 0.0f;
+            float *orow = out + ((size_t)b * seq_q + sq[j]) * (size_t)n_q * D + (size_t)qh[j] * D;
+            *reinterpret_cast<float4 *>(orow + e4) = make_float4(acc[j].x * inv, acc[j].y * inv, acc[j].z * inv, acc[j].w * inv);
+        }
     }
 }
 
@@ -1102,12 +1161,15 @@ static int gqa_attention_impl(yscv_cuda_ctx *ctx, const float *d_q, size_t q_str
     // a prompt pass: query positions in tiles, keys and values staged once per tile
     const size_t group = n_q / n_kv;
     const bool rows_aligned = ((reinterpret_cast<uintptr_t>(d_kcache) | reinterpret_cast<uintptr_t>(d_vcache)) & 15) == 0;
-    if (seq_q >= 16 && (d_head == 64 || d_head == 128) && group <= 16 && rows_aligned) {
-        const int QB = (int)(16 / group);
-        const int warps = (int)group * QB;
-        const size_t pf_smem = (2 * PF_KT * d_head + (size_t)warps * PF_KT) * sizeof(float);
+    if (seq_q >= 16 && (d_head == 64 || d_head == 128) && group <= 64 && rows_aligned &&
+        (reinterpret_cast<uintptr_t>(d_out) & 15) == 0) {
+        // 64 (position, head) pairs per block where the group allows, four per warp
+        const int QB = (int)(64 / group) > 0 ? (int)(64 / group) : 1;
+        const int pairs = (int)group * QB;
+        const int warps = (pairs + PF_QH - 1) / PF_QH;
+        const size_t pf_smem = (PF_KT * (d_head + 4) + PF_KT * d_head + (size_t)warps * PF_QH * (PF_KT + d_head)) * sizeof(float);
         auto kern = d_head == 64 ? gqa_prefill_tiled_kernel<KV, 64> : gqa_prefill_tiled_kernel<KV, 128>;
-        int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 100 * 1024);
+        int arc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 160 * 1024);
         if (arc) return arc;
         dim3 pgrid((unsigned)((seq_q + QB - 1) / QB), (unsigned)n_kv, (unsigned)batch);
         YSCV_CUDA_TRY(launch_pdl(kern, dim3(pgrid), dim3(32 * warps), pf_smem, ctx->stream, d_q, (int)q_stride, (int)seq_q,
