@@ -104,6 +104,8 @@ __device__ __forceinline__ void pg_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) 
 // fp32 activations -> bf16, k order inside every group of 8 permuted to 0,4,1,5,2,6,3,7
 __global__ void act_to_bf16_kernel(const float *__restrict__ act, __nv_bfloat16 *__restrict__ out,
                                    size_t groups8) {
+    pdl_wait();      // the activations come from the predecessor, which may also still read `out`
+    pdl_trigger();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < groups8;
          i += (size_t)gridDim.x * blockDim.x) {
         const float4 a = __ldg(reinterpret_cast<const float4 *>(act) + 2 * i);
@@ -172,6 +174,10 @@ int4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     __syncthreads();
     pg_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // programmatic dependent launch: the set-up above may overlap the tail of the predecessor (the
+    // activation pre-pass); everything below reads what it wrote or writes what it may still read
+    pdl_wait();
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -464,6 +470,8 @@ int4_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     cluster_sync_all();   // both CTAs' barriers exist before anyone arrives on a remote one
     pg_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();      // as in the one-CTA kernel
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
@@ -700,13 +708,15 @@ static int launch_prefill_pairs(yscv_cuda_ctx *ctx, const CUtensorMap &tm_w, con
     cfg.blockDim = dim3(PG_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     // persistent kernel with a static walk over the tiles: every pair of the grid must be resident
     if (ctx->max_prefill_pairs == 0) {
         int nres = 0;
@@ -792,7 +802,7 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     __nv_bfloat16 *abf = reinterpret_cast<__nv_bfloat16 *>(scratch);
     const size_t groups8 = m * k / 8;
     const unsigned cb = (unsigned)((groups8 + 255) / 256 < 8192 ? (groups8 + 255) / 256 : 8192);
-    act_to_bf16_kernel<<<cb, 256, 0, ctx->stream>>>(act, abf, groups8);
+    YSCV_CUDA_TRY(launch_pdl(act_to_bf16_kernel, dim3(cb), dim3(256), 0, ctx->stream, act, abf, groups8));
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
 
@@ -818,7 +828,8 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     const int tiles = p.n_tiles * p.t_chunks * p.ksplit;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     ctx->prof_begin();
-    kern<<<grid, PG_THREADS, smem, ctx->stream>>>(tm_w, tm_a, scales, kernel_out, p, ctx->d_status);
+    YSCV_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(PG_THREADS), (size_t)smem, ctx->stream, tm_w, tm_a, scales, kernel_out, p,
+                             ctx->d_status));
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
