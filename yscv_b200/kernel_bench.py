@@ -4,7 +4,7 @@ same kind plus the BASELINE configurations, a parity gate before every timing, a
 same derived figures (weight bandwidth N*K/2 / t for the GEMV, kernel_bench.rs:317-324;
 2*M*N*K / t for the GEMMs, :389-396), median and min over the timed iterations (:54-69).
 
-    python -m yscv_b200.kernel_bench [--section int8|conv1x1|int4_gemv|int4_gemm] [--only SUBSTR]
+    python -m yscv_b200.kernel_bench [--section int8|conv1x1|int4_gemv|int4_gemm|attention|lm_head] [--only SUBSTR]
                                      [--iters N] [--copies C]
 
 The parity gate recomputes a random sample of outputs on the GPU in float64 from the raw
@@ -298,9 +298,40 @@ def bench_attention(ctx, stream, dev, iters, only):
         del kc, vc
 
 
+def bench_lm_head(ctx, stream, dev, iters, only):
+    """The decoder's fp32 LM head for a wide batch (yscv_cuda_f32_matmul_dev, more than 8 rows): the
+    3xTF32 tensor-core kernel and the tiled fp32 FMA kernel, both against float64 on sampled outputs."""
+    print("\n== fp32 LM head, wide batch (out[m][n] = sum_k x[m][k] w[n][k]) ==")
+    shapes = [("TLlama vocab 32000x2048, 32 rows", 32, 32000, 2048),
+              ("TLlama vocab 32000x2048, 128 rows", 128, 32000, 2048),
+              ("L3-70B vocab 128256x8192, 64 rows", 64, 128256, 8192)]
+    for label, m, n, k in shapes:
+        if only and only not in label:
+            continue
+        with torch.cuda.stream(stream):
+            g = torch.Generator(device=dev)
+            g.manual_seed(0xF3)
+            w = torch.randn(n, k, device=dev, generator=g) * 0.02
+            x = torch.randn(m, k, device=dev, generator=g)
+            out = torch.empty(m, n, device=dev)
+            r, c = sample_idx(m, n, 4096, dev)
+            want = (x[r].double() * w[c].double()).sum(dim=1)
+        call = lambda: ctx.f32_matmul_dev(w.data_ptr(), x.data_ptr(), m, n, k, out.data_ptr())
+        res = {}
+        for tc in (True, False):
+            ctx.set_f32_tensor_cores(tc)
+            med, mn = time_us(stream, call, max(3, iters // 3))
+            err = float((out[r, c].double() - want).abs().max() / want.abs().max())
+            res[tc] = (mn, err, ctx.last_kernel())
+        ctx.set_f32_tensor_cores(True)
+        print(f"  {label:38s}: 3xTF32 {res[True][0]:9.2f} us ({n * k * 4 / res[True][0] / 1e6:5.2f} TB/s of weights, "
+              f"rel err {res[True][1]:.1e})  fp32 FMA {res[False][0]:9.2f} us (rel err {res[False][1]:.1e})  [{res[True][2]}]")
+        del w, x, out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--section", choices=["int8", "conv1x1", "int4_gemv", "int4_gemm", "attention"], default=None)
+    ap.add_argument("--section", choices=["int8", "conv1x1", "int4_gemv", "int4_gemm", "attention", "lm_head"], default=None)
     ap.add_argument("--only", default=None, help="substring of the shape label")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--copies", type=int, default=16)
@@ -321,6 +352,8 @@ def main():
         bench_int4_gemm(ctx, stream, dev, a.iters, a.only)
     if a.section in (None, "attention"):
         bench_attention(ctx, stream, dev, a.iters, a.only)
+    if a.section in (None, "lm_head"):
+        bench_lm_head(ctx, stream, dev, a.iters, a.only)
     assert ctx.device_status() == 0
 
 
