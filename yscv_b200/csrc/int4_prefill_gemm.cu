@@ -788,6 +788,7 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
         }
     }
     p.kb_per = (p.k_blocks + p.ksplit - 1) / p.ksplit;
+    p.ksplit = (p.k_blocks + p.kb_per - 1) / p.kb_per;   // no empty slice (33 blocks in 8 slices of 5: seven slices)
     float *kernel_out = out;
     if (p.ksplit > 1) {
         rc_ws = ctx->gemm_ws.reserve((size_t)p.ksplit * m * n * sizeof(float));
