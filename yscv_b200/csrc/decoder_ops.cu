@@ -335,32 +335,54 @@ gqa_prefill_tiled_kernel(const float *__restrict__ q, int q_stride, int seq_q, i
         __syncthreads();
         const int nkw = min(rows, warp_limit - c0);   // keys of this chunk any of the warp's pairs attends to
         if (nkw > 0) {
-            // scores: a lane per key (keys lane and lane + 32 of the chunk)
+            // scores: a lane per key (keys lane and lane + 32 of the chunk); a query piece read once for both keys
             float sv[2][PF_QH];
+            {
+                float dot[2][PF_QH];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int k = lane + 32 * h;
-                float dot[PF_QH];
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int j = 0; j < PF_QH; ++j) dot[j] = 0.0f;
-                if (32 * h < nkw) {   // the same for the whole warp
-                    const float4 *kr = reinterpret_cast<const float4 *>(ks + k * KP);
-#pragma unroll 4
+                    for (int j = 0; j < PF_QH; ++j) dot[h][j] = 0.0f;
+                const float4 *kr0 = reinterpret_cast<const float4 *>(ks + lane * KP);
+                const float4 *kr1 = reinterpret_cast<const float4 *>(ks + (lane + 32) * KP);
+                if (nkw > 32) {   // the same for the whole warp
+#pragma unroll 2
                     for (int i = 0; i < D / 4; ++i) {
-                        const float4 kk = kr[i];
+                        const float4 k0 = kr0[i], k1 = kr1[i];
 #pragma unroll
                         for (int j = 0; j < PF_QH; ++j) {
                             const float4 a = reinterpret_cast<const float4 *>(qs + j * D)[i];
-                            dot[j] = fmaf(a.x, kk.x, dot[j]);
-                            dot[j] = fmaf(a.y, kk.y, dot[j]);
-                            dot[j] = fmaf(a.z, kk.z, dot[j]);
-                            dot[j] = fmaf(a.w, kk.w, dot[j]);
+                            dot[0][j] = fmaf(a.x, k0.x, dot[0][j]);
+                            dot[0][j] = fmaf(a.y, k0.y, dot[0][j]);
+                            dot[0][j] = fmaf(a.z, k0.z, dot[0][j]);
+                            dot[0][j] = fmaf(a.w, k0.w, dot[0][j]);
+                            dot[1][j] = fmaf(a.x, k1.x, dot[1][j]);
+                            dot[1][j] = fmaf(a.y, k1.y, dot[1][j]);
+                            dot[1][j] = fmaf(a.z, k1.z, dot[1][j]);
+                            dot[1][j] = fmaf(a.w, k1.w, dot[1][j]);
+                        }
+                    }
+                } else {
+#pragma unroll 4
+                    for (int i = 0; i < D / 4; ++i) {
+                        const float4 k0 = kr0[i];
+#pragma unroll
+                        for (int j = 0; j < PF_QH; ++j) {
+                            const float4 a = reinterpret_cast<const float4 *>(qs + j * D)[i];
+                            dot[0][j] = fmaf(a.x, k0.x, dot[0][j]);
+                            dot[0][j] = fmaf(a.y, k0.y, dot[0][j]);
+                            dot[0][j] = fmaf(a.z, k0.z, dot[0][j]);
+                            dot[0][j] = fmaf(a.w, k0.w, dot[0][j]);
                         }
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < PF_QH; ++j)
-                    sv[h][j] = k < lim[j] - c0 && k < rows ? dot[j] * scale : -INFINITY;   // rows past the limit hold stale values
+                for (int h = 0; h < 2; ++h) {
+                    const int k = lane + 32 * h;
+#pragma unroll
+                    for (int j = 0; j < PF_QH; ++j)
+                        sv[h][j] = k < lim[j] - c0 && k < rows ? dot[h][j] * scale : -INFINITY;   // rows past the limit hold stale values
+                }
             }
 #pragma unroll
             for (int j = 0; j < PF_QH; ++j) {
@@ -384,16 +406,26 @@ gqa_prefill_tiled_kernel(const float *__restrict__ q, int q_stride, int seq_q, i
                 m[j] = m_new;
             }
             __syncwarp();
-#pragma unroll 2
-            for (int k = kpar; k < nkw; k += KPAR) {
-                const float4 v4 = *reinterpret_cast<const float4 *>(vs + k * D + e4);
+            // weighted value sum: the weights of four consecutive keys of a pair come with one 16-byte read
+            // (weights past nkw are 0 or belong to rows that are not read)
+            for (int k4 = 0; k4 < nkw; k4 += 4 * KPAR) {
+                const int kq = k4 + 4 * kpar;   // this half warp's four keys
+                float4 pj[PF_QH];
 #pragma unroll
-                for (int j = 0; j < PF_QH; ++j) {
-                    const float pk = sc[j * PF_KT + k];   // 0 past the pair's limit
-                    acc[j].x = fmaf(pk, v4.x, acc[j].x);
-                    acc[j].y = fmaf(pk, v4.y, acc[j].y);
-                    acc[j].z = fmaf(pk, v4.z, acc[j].z);
-                    acc[j].w = fmaf(pk, v4.w, acc[j].w);
+                for (int j = 0; j < PF_QH; ++j) pj[j] = *reinterpret_cast<const float4 *>(sc + j * PF_KT + kq);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (kq + u < nkw) {
+                        const float4 v4 = *reinterpret_cast<const float4 *>(vs + (kq + u) * D + e4);
+#pragma unroll
+                        for (int j = 0; j < PF_QH; ++j) {
+                            const float pk = u == 0 ? pj[j].x : u == 1 ? pj[j].y : u == 2 ? pj[j].z : pj[j].w;
+                            acc[j].x = fmaf(pk, v4.x, acc[j].x);
+                            acc[j].y = fmaf(pk, v4.y, acc[j].y);
+                            acc[j].z = fmaf(pk, v4.z, acc[j].z);
+                            acc[j].w = fmaf(pk, v4.w, acc[j].w);
+                        }
+                    }
                 }
             }
         }
