@@ -322,6 +322,31 @@ def test_cta_pair_kernel_is_bit_identical(ctx, oracle, m, k, n):
     assert ctx.device_status() == 0
 
 
+def test_cta_pair_kernel_is_chosen_where_it_measured_faster(ctx):
+    """The default kernel selection (yscv_cuda_ctx_set_int8_cta_pairs(-1)): CTA pairs for a single round of
+    the one-CTA kernel on more than half of the SMs and for int32 output from three rounds of pair tiles
+    on, the one-CTA kernel for requantised output with full rounds, for K < 2048 and for row counts that
+    would leave the 256-row blocks more rounds than the 128-row tiles."""
+    import torch
+    ctx.set_int8_cta_pairs(None)
+    rng = np.random.default_rng(5)
+    cases = [((1024, 2048, 4096), True, True),     # 128 tiles of 128 x 256: one partial round
+             ((2048, 2048, 4096), False, False),   # config-3-like: 1.73 rounds
+             ((4096, 2048, 4096), True, False),    # 256 pair tiles >= 3 x 74: int32 output only
+             ((1024, 1024, 4096), False, False),   # K < 2048
+             ((300, 2048, 11008), False, False)]   # two 256-row blocks for 300 rows
+    for (m, k, n), pair_i32, pair_u8 in cases:
+        a = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+        b = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+        pk = ctx.pack_i8_b(b, k, n)
+        ctx.matmul_integer(a, pk, m, a_zp=128)
+        assert ("cta_group::2" in ctx.last_kernel()) == pair_i32, ((m, k, n), ctx.last_kernel())
+        ctx.qlinear_matmul(a, pk, m, ctx.requant(3e-4, 128.0, 0, 255, a_unsigned=True, a_zp=128))
+        assert ("cta_group::2" in ctx.last_kernel()) == pair_u8, ((m, k, n), ctx.last_kernel())
+        pk.free()
+    assert ctx.device_status() == 0
+
+
 @pytest.mark.parametrize("m,k,n,splits", [(64, 11008, 4096, True), (300, 8200, 700, True),
                                           (130, 16384, 1100, True), (2048, 4096, 4096, False)])
 def test_tail_split_is_bit_identical(ctx, oracle, m, k, n, splits):
