@@ -364,6 +364,10 @@ int8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // programmatic dependent launch: the set-up above may overlap the tail of the previous kernel of
+    // the stream; everything below reads what it may have written or writes what it may still read
+    pdl_wait();
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -567,6 +571,8 @@ int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     cluster_sync_all();   // both CTAs' barriers exist before anyone arrives on a remote one
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();      // as in the one-CTA kernel
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs): own 128 rows of A, own 128 rows of B^T ----------------
@@ -777,7 +783,8 @@ static int launch_g8(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const yscv
              p.M, p.N, p.K, G8_BM, BN, p.stages, stage_bytes / 1024, tiles, grid,
              p.tail_units ? " (tail split along K)" : "", p.mode == 0 ? "int32 out" : "requantised bytes out");
     ctx->prof_begin();
-    kern<<<grid, G8_THREADS, smem, ctx->stream>>>(tm_a, tm_b, b->d_colsum, d_out, p, ctx->d_status);
+    YSCV_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(G8_THREADS), (size_t)smem, ctx->stream, tm_a, tm_b,
+                             (const int32_t *)b->d_colsum, d_out, p, ctx->d_status));
     ctx->prof_end();
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
@@ -811,13 +818,15 @@ static int launch_g8_pair(yscv_cuda_ctx *ctx, const void *d_a, size_t lda, const
     cfg.blockDim = dim3(G8_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     // The kernel is persistent with a static walk over the tiles, so every pair of the grid must
     // be resident at once: a GPC with an odd number of usable SMs leaves one SM without a
     // partner, and a pair that only starts when another has finished would do all its tiles
