@@ -118,6 +118,10 @@ int4_gemv_generic_kernel(const uint8_t *__restrict__ wq, const float *__restrict
 __global__ void __launch_bounds__(128)
 act_quant_kernel(const float *__restrict__ act, unsigned char *__restrict__ blobs, int M, int K,
                  QuantLayout q) {
+    // programmatic dependent launch: the activations come from the predecessor, and the main kernel of
+    // the previous call may still read the blobs
+    pdl_wait();
+    pdl_trigger();
     const int slots = quant_slots(q);
     const int total = (K / 32) * slots;
     const int t = threadIdx.x & 3;
@@ -561,7 +565,7 @@ static int launch_fast_tp(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *sc
     }
     unsigned char *blobs = reinterpret_cast<unsigned char *>(scratch);
     const int items = (K / 32) * quant_slots(q);
-    act_quant_kernel<<<(items * 4 + 127) / 128, 128, 0, ctx->stream>>>(act, blobs, M, K, q);
+    YSCV_CUDA_TRY(launch_pdl(act_quant_kernel, dim3((items * 4 + 127) / 128), dim3(128), 0, ctx->stream, act, blobs, M, K, q));
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
     ctx->last_kernel = "int4_gemv_fast(imma,tma)";
@@ -610,7 +614,7 @@ static int launch_scratch_variant(yscv_cuda_ctx *ctx, const uint8_t *wq, const f
     const QuantLayout q = quant_layout(MP, GS);
     const int rows_per_cta = (N + ctx->sm_count - 1) / ctx->sm_count;
     const int items = (K / 32) * quant_slots(q);
-    act_quant_kernel<<<(items * 4 + 127) / 128, 128, 0, ctx->stream>>>(act, blobs, M, K, q);
+    YSCV_CUDA_TRY(launch_pdl(act_quant_kernel, dim3((items * 4 + 127) / 128), dim3(128), 0, ctx->stream, act, blobs, M, K, q));
     YSCV_CUDA_TRY(cudaGetLastError());
     ctx->launches++;
     ctx->last_kernel = "int4_gemv_fast(imma,tma,static-scratch)";
