@@ -199,6 +199,17 @@ void yscv_cuda_int4_weight_free(yscv_cuda_int4_weight *w);
 int yscv_cuda_int4_matmul_dev(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
                               const float *d_activation, float *d_output, size_t m);
 
+/* The fusion the reference's plan asks for (docs/int4-quant-pipeline-plan.md:45-51: the
+ * activation conversion folded into the producing operator): yscv_cuda_int4_matmul_dev for
+ * m > 16 whose activations the caller already holds as bf16 in the order the tensor-core GEMM
+ * consumes (k = 0,4,1,5,2,6,3,7 of every group of 8, round to nearest even), as
+ * yscv_cuda_add_rms_norm_act_dev and yscv_cuda_swiglu_act_dev write them: the GEMM's own
+ * conversion pass is skipped, the result is the same bit for bit. Needs what the bf16 path of
+ * yscv_cuda_int4_matmul_dev needs (group_size 32, k % 64 == 0, 16-byte aligned operands, the
+ * fp32-exact prefill mode off); YSCV_CUDA_ERR_UNSUPPORTED otherwise. */
+int yscv_cuda_int4_matmul_act_dev(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
+                                  const void *d_activation_bf16, float *d_output, size_t m);
+
 /* The same operator as a runner calls it: weights resident (uploaded once at load
  * time, like the reference's side-table built by quantize_matmul_weights_int4_packed,
  * crates/yscv-onnx/src/quantize/packed_int4.rs:50-128), activation and output in host
@@ -400,6 +411,11 @@ int yscv_cuda_embedding_dev(yscv_cuda_ctx *ctx, const float *d_weight, size_t vo
 int yscv_cuda_add_rms_norm_dev(yscv_cuda_ctx *ctx, const float *d_x, const float *d_delta,
                                const float *d_gamma, float eps, size_t rows, size_t hidden,
                                float *d_x_out, float *d_normed);
+/* The same with the normalised rows written as the bf16 activations of a following
+ * yscv_cuda_int4_matmul_act_dev (hidden % 8 == 0, d_normed_act 16-byte aligned, rows x hidden bf16) */
+int yscv_cuda_add_rms_norm_act_dev(yscv_cuda_ctx *ctx, const float *d_x, const float *d_delta,
+                                   const float *d_gamma, float eps, size_t rows, size_t hidden,
+                                   float *d_x_out, void *d_normed_act);
 
 /* apply_rotary_embedding (crates/yscv-kernels/src/ops/rope.rs:24-117, rotate-half) on the
  * q and k parts of fused qkv rows [q | k | v] at positions *d_pos + s, fused with the
@@ -440,6 +456,10 @@ int yscv_cuda_gqa_attention_i8_dev(yscv_cuda_ctx *ctx, const float *d_q, size_t 
  * crates/yscv-kernels/src/ops/simd/activation.rs:1000-1005: out = gate/(1+exp(-gate)) * up */
 int yscv_cuda_swiglu_dev(yscv_cuda_ctx *ctx, const float *d_gate_up, size_t rows, size_t inter,
                          float *d_out);
+/* The same with the result written as the bf16 activations of a following
+ * yscv_cuda_int4_matmul_act_dev (inter % 8 == 0, d_out_act 16-byte aligned, rows x inter bf16) */
+int yscv_cuda_swiglu_act_dev(yscv_cuda_ctx *ctx, const float *d_gate_up, size_t rows, size_t inter,
+                             void *d_out_act);
 
 /* fp32 matmul against a row-major [n,k] weight (the unquantized LM head):
  * out[m,n] = x[m,k] . w[n,k] */

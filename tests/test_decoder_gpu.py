@@ -604,6 +604,65 @@ def test_int8_kv_cache_bytes(tctx, oracle):
     assert ctx.device_status() == 0
 
 
+def test_norm_and_swiglu_write_the_gemm_activations(tctx, oracle):
+    """add_rms_norm_act / swiglu_act hand the tensor-core GEMM its bf16 activations: the linear that follows
+    (int4_matmul_act_dev) gives the same output, bit for bit, as the fp32 operators followed by
+    int4_matmul_dev with its own conversion pass; shapes the bf16 path does not take are refused."""
+    import torch
+    import yscv_b200
+    ctx, s = tctx
+    rows, H, inter, n = 40, 512, 320, 300
+    rng = np.random.default_rng(91)
+    x = rng.normal(0, 1, (rows, H)).astype(np.float32)
+    dl = rng.normal(0, 1, (rows, H)).astype(np.float32)
+    gm = rng.normal(1, 0.1, H).astype(np.float32)
+    gu = rng.normal(0, 2, (rows, 2 * inter)).astype(np.float32)
+    w1 = rng.normal(0, 0.02, (n, H)).astype(np.float32)
+    w2 = rng.normal(0, 0.02, (n, inter)).astype(np.float32)
+    p1, s1 = oracle.pack_int4(w1.ravel(), n, H, 32)
+    p2, s2 = oracle.pack_int4(w2.ravel(), n, inter, 32)
+    h1, h2 = ctx.int4_weight_upload(p1, s1, n, H, 32), ctx.int4_weight_upload(p2, s2, n, inter, 32)
+    with torch.cuda.stream(s):
+        dx, dd, dg, dgu = dev(x), dev(dl), dev(gm), dev(gu)
+        xo_a, xo_b = torch.empty_like(dx), torch.empty_like(dx)
+        nm = torch.empty_like(dx)
+        nm16 = torch.empty(rows, H, dtype=torch.bfloat16, device="cuda")
+        act = torch.empty(rows, inter, device="cuda")
+        act16 = torch.empty(rows, inter, dtype=torch.bfloat16, device="cuda")
+        o_a, o_b = torch.empty(rows, n, device="cuda"), torch.empty(rows, n, device="cuda")
+        ctx.add_rms_norm_dev(dx.data_ptr(), dd.data_ptr(), dg.data_ptr(), 1e-5, rows, H, xo_a.data_ptr(), nm.data_ptr())
+        ctx.int4_matmul_dev(h1, nm.data_ptr(), o_a.data_ptr(), rows)
+        ctx.add_rms_norm_act_dev(dx.data_ptr(), dd.data_ptr(), dg.data_ptr(), 1e-5, rows, H, xo_b.data_ptr(), nm16.data_ptr())
+        ctx.int4_matmul_act_dev(h1, nm16.data_ptr(), o_b.data_ptr(), rows)
+        s.synchronize()
+        assert "prefill" in ctx.last_kernel()
+        assert torch.equal(xo_a, xo_b) and torch.equal(o_a, o_b)
+        # in place, as the decoder uses it
+        x_in = dx.clone()
+        ctx.add_rms_norm_act_dev(x_in.data_ptr(), dd.data_ptr(), dg.data_ptr(), 1e-5, rows, H, x_in.data_ptr(), nm16.data_ptr())
+        ctx.int4_matmul_act_dev(h1, nm16.data_ptr(), o_b.data_ptr(), rows)
+        s.synchronize()
+        assert torch.equal(x_in, xo_a) and torch.equal(o_a, o_b)
+        ctx.swiglu_dev(dgu.data_ptr(), rows, inter, act.data_ptr())
+        ctx.int4_matmul_dev(h2, act.data_ptr(), o_a.data_ptr(), rows)
+        ctx.swiglu_act_dev(dgu.data_ptr(), rows, inter, act16.data_ptr())
+        ctx.int4_matmul_act_dev(h2, act16.data_ptr(), o_b.data_ptr(), rows)
+        s.synchronize()
+        assert torch.equal(o_a, o_b)
+        # refused: a decode-shaped call, and the fp32-exact prefill mode
+        with pytest.raises(yscv_b200.YscvCudaError):
+            ctx.int4_matmul_act_dev(h2, act16.data_ptr(), o_b.data_ptr(), 8)
+        ctx.set_int4_prefill_exact(True)
+        try:
+            with pytest.raises(yscv_b200.YscvCudaError):
+                ctx.int4_matmul_act_dev(h2, act16.data_ptr(), o_b.data_ptr(), rows)
+        finally:
+            ctx.set_int4_prefill_exact(False)
+    assert ctx.device_status() == 0
+    h1.free()
+    h2.free()
+
+
 @pytest.mark.parametrize("B,seq,p0,nq,nkv,d,causal,i8", [
     (2, 100, 0, 8, 2, 64, True, False),      # tiles of 4 positions x 4 heads, ragged last tile, two key chunks
     (1, 70, 37, 8, 1, 128, True, False),     # a prompt appended behind 37 cached positions, 8 heads per KV head

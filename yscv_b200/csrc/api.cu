@@ -442,6 +442,25 @@ int yscv_cuda_int4_matmul_dev(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w
                            d_output, m);
 }
 
+int yscv_cuda_int4_matmul_act_dev(yscv_cuda_ctx *ctx, const yscv_cuda_int4_weight *w,
+                                  const void *d_activation_bf16, float *d_output, size_t m) {
+    if (!ctx || !w) return fail(YSCV_CUDA_ERR_BAD_ARG, "null argument");
+    if (!d_activation_bf16 || !d_output) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    YSCV_CUDA_TRY(cudaSetDevice(ctx->device));
+    int rc = check_int4_shape(w->m_w, w->k, w->group_size);
+    if (rc) return rc;
+    if (m == 0) return YSCV_CUDA_OK;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(w->d_packed) | reinterpret_cast<uintptr_t>(w->d_scales) |
+                           reinterpret_cast<uintptr_t>(d_activation_bf16)) & 15) == 0;
+    if (ctx->prefill_exact || !aligned || !int4_prefill_supported(m, w->m_w, w->k, w->group_size))
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED,
+                    "bf16 activations need the tensor-core prefill path: m > 16, group 32, k %% 64 == 0, 16-byte "
+                    "aligned operands, exact-prefill mode off (m=%zu n=%zu k=%zu)", m, w->m_w, w->k);
+    op_counters().int4_gemm_calls++;
+    return int4_prefill_gemm(ctx, w->d_packed, w->d_scales, nullptr, d_output, m, w->m_w, w->k, nullptr,
+                             d_activation_bf16);
+}
+
 // Device alias of a host buffer the kernels may write directly (page-locked and mapped into the
 // device's address space: cudaHostAlloc / cudaHostRegister memory under unified addressing),
 // or null for pageable memory.

@@ -19,6 +19,8 @@
 // kernel arguments.
 #include <cuda_fp16.h>
 
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -89,6 +91,79 @@ add_rms_norm_kernel(const float *x, const float *__restrict__ delta,
             if (delta) v += delta[base + i];
         }
         normed[base + i] = (v * inv) * gamma[i];
+    }
+}
+
+// Eight fp32 values -> bf16 in the order the packed-int4 prefill GEMM consumes its activations:
+// k = 0,4,1,5,2,6,3,7 of every group of 8 (what its nibble unpack produces), round to nearest even;
+// the same bits as its own activation pre-pass writes.
+__device__ __forceinline__ uint4 pack_bf16_gemm_order(const float (&v)[8]) {
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[4]);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(v[1], v[5]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[2], v[6]);
+    __nv_bfloat162 p3 = __floats2bfloat162_rn(v[3], v[7]);
+    uint4 o;
+    o.x = *reinterpret_cast<uint32_t *>(&p0);
+    o.y = *reinterpret_cast<uint32_t *>(&p1);
+    o.z = *reinterpret_cast<uint32_t *>(&p2);
+    o.w = *reinterpret_cast<uint32_t *>(&p3);
+    return o;
+}
+
+// add_rms_norm_kernel with the normalised rows written as bf16 activations of the next prefill-shaped
+// linear (hidden % 8 == 0); the same arithmetic, so the bf16 values equal those the linear's own
+// pre-pass would make of the fp32 rows.
+__global__ void __launch_bounds__(256)
+add_rms_norm_act_kernel(const float *x, const float *__restrict__ delta, const float *__restrict__ gamma, float eps,
+                        int hidden, float *x_out, uint4 *__restrict__ normed_act) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float red[8];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[base + i];
+        if (delta) v += delta[base + i];
+        if (x_out) x_out[base + i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    if (x_out) __syncthreads();   // the second pass reads elements other threads wrote
+    for (int g8 = threadIdx.x; g8 < hidden / 8; g8 += blockDim.x) {
+        float n[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = g8 * 8 + j;
+            float v;
+            if (x_out) {
+                v = x_out[base + i];
+            } else {
+                v = x[base + i];
+                if (delta) v += delta[base + i];
+            }
+            n[j] = (v * inv) * gamma[i];
+        }
+        normed_act[base / 8 + g8] = pack_bf16_gemm_order(n);
+    }
+}
+
+// swiglu_kernel with the result written as bf16 activations of the next prefill-shaped linear (inter % 8 == 0)
+__global__ void swiglu_act_kernel(const float *__restrict__ gu, uint4 *__restrict__ out_act, size_t rows, int inter) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t total8 = rows * (size_t)(inter / 8);
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (inter / 8);
+        const int c = (int)(i % (inter / 8)) * 8;
+        float n[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float g = gu[r * 2 * inter + c + j], u = gu[r * 2 * inter + inter + c + j];
+            const float sg = 1.0f / (1.0f + expf(-g));
+            n[j] = (g * sg) * u;
+        }
+        out_act[i] = pack_bf16_gemm_order(n);
     }
 }
 
@@ -1250,6 +1325,31 @@ int yscv_cuda_swiglu_dev(yscv_cuda_ctx *ctx, const float *d_gate_up, size_t rows
     const unsigned blocks = (unsigned)((total + 255) / 256 < 65535 ? (total + 255) / 256 : 65535);
     YSCV_CUDA_TRY(launch_pdl(swiglu_kernel, dim3(blocks), dim3(256), 0, ctx->stream, d_gate_up, d_out, rows, (int)inter));
     DEC_EPILOGUE(ctx, "swiglu");
+}
+
+int yscv_cuda_add_rms_norm_act_dev(yscv_cuda_ctx *ctx, const float *d_x, const float *d_delta, const float *d_gamma,
+                                   float eps, size_t rows, size_t hidden, float *d_x_out, void *d_normed_act) {
+    DEC_PROLOGUE(ctx);
+    if (!d_x || !d_gamma || !d_normed_act) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (hidden % 8 != 0 || (reinterpret_cast<uintptr_t>(d_normed_act) & 15))
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "hidden must be a multiple of 8 and the activation buffer 16-byte aligned");
+    if (rows == 0) return YSCV_CUDA_OK;
+    YSCV_CUDA_TRY(launch_pdl(add_rms_norm_act_kernel, dim3((unsigned)rows), dim3(256), 0, ctx->stream, d_x, d_delta, d_gamma, eps,
+                             (int)hidden, d_x_out, reinterpret_cast<uint4 *>(d_normed_act)));
+    DEC_EPILOGUE(ctx, "add_rms_norm(bf16 activations out)");
+}
+
+int yscv_cuda_swiglu_act_dev(yscv_cuda_ctx *ctx, const float *d_gate_up, size_t rows, size_t inter, void *d_out_act) {
+    DEC_PROLOGUE(ctx);
+    if (!d_gate_up || !d_out_act) return fail(YSCV_CUDA_ERR_BAD_ARG, "null operand");
+    if (inter % 8 != 0 || (reinterpret_cast<uintptr_t>(d_out_act) & 15))
+        return fail(YSCV_CUDA_ERR_UNSUPPORTED, "inter must be a multiple of 8 and the activation buffer 16-byte aligned");
+    if (rows * inter == 0) return YSCV_CUDA_OK;
+    const size_t total8 = rows * (inter / 8);
+    const unsigned blocks = (unsigned)((total8 + 255) / 256 < 65535 ? (total8 + 255) / 256 : 65535);
+    YSCV_CUDA_TRY(launch_pdl(swiglu_act_kernel, dim3(blocks), dim3(256), 0, ctx->stream, d_gate_up,
+                             reinterpret_cast<uint4 *>(d_out_act), rows, (int)inter));
+    DEC_EPILOGUE(ctx, "swiglu(bf16 activations out)");
 }
 
 int yscv_cuda_f32_matmul_dev(yscv_cuda_ctx *ctx, const float *d_w, const float *d_x, size_t m, size_t n,

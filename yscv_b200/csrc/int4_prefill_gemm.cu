@@ -738,8 +738,10 @@ static int launch_prefill_pairs(yscv_cuda_ctx *ctx, const CUtensorMap &tm_w, con
     return YSCV_CUDA_OK;
 }
 
+// act_bf16 != nullptr: the activations are already bf16 in the GEMM's k order (what the pre-pass
+// below writes; the decoder's norm and SwiGLU kernels can emit it): `act` and `scratch` are not used.
 int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, const float *act,
-                      float *out, size_t m, size_t n, size_t k, void *scratch) {
+                      float *out, size_t m, size_t n, size_t k, void *scratch, const void *act_bf16) {
     PGParams p = {};
     int rc_ws = 0;
     p.M = (int)m;
@@ -800,12 +802,16 @@ int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
     const size_t pair_tiles = ((n + 511) / 512) * ((m + 255) / 256);
     const bool use_pairs = ctx->prefill_pairs && NA == 2 && pair_tiles >= (size_t)(ctx->sm_count / 2);
 
-    __nv_bfloat16 *abf = reinterpret_cast<__nv_bfloat16 *>(scratch);
-    const size_t groups8 = m * k / 8;
-    const unsigned cb = (unsigned)((groups8 + 255) / 256 < 8192 ? (groups8 + 255) / 256 : 8192);
-    YSCV_CUDA_TRY(launch_pdl(act_to_bf16_kernel, dim3(cb), dim3(256), 0, ctx->stream, act, abf, groups8));
-    YSCV_CUDA_TRY(cudaGetLastError());
-    ctx->launches++;
+    const __nv_bfloat16 *abf = reinterpret_cast<const __nv_bfloat16 *>(act_bf16);
+    if (!abf) {
+        __nv_bfloat16 *mine = reinterpret_cast<__nv_bfloat16 *>(scratch);
+        const size_t groups8 = m * k / 8;
+        const unsigned cb = (unsigned)((groups8 + 255) / 256 < 8192 ? (groups8 + 255) / 256 : 8192);
+        YSCV_CUDA_TRY(launch_pdl(act_to_bf16_kernel, dim3(cb), dim3(256), 0, ctx->stream, act, mine, groups8));
+        YSCV_CUDA_TRY(cudaGetLastError());
+        ctx->launches++;
+        abf = mine;
+    }
 
     CUtensorMap tm_w, tm_a;
     int rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, n, k / 2, k / 2, (uint32_t)(NA * PG_BM), 32,

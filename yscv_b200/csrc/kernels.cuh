@@ -26,7 +26,7 @@ int int4_gemv_generic(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales
 bool int4_prefill_supported(size_t m, size_t n, size_t k, size_t gs);
 size_t int4_prefill_scratch_bytes(size_t m, size_t k);
 int int4_prefill_gemm(yscv_cuda_ctx *ctx, const uint8_t *wq, const float *scales, const float *act,
-                      float *out, size_t m, size_t n, size_t k, void *scratch);
+                      float *out, size_t m, size_t n, size_t k, void *scratch, const void *act_bf16 = nullptr);
 
 // int4_pack.cu
 int pack_int4(yscv_cuda_ctx *ctx, const float *d_weights, size_t m_w, size_t k, size_t gs,

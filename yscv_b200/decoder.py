@@ -219,6 +219,12 @@ class Int4Decoder:
         gu = self._buf("gu", rows, 2 * self.mlp_l)
         act = self._buf("act", rows, self.mlp_l)
         down = self._buf("down", rows, H)
+        # more than 16 rows take the tensor-core GEMM, whose bf16 activations the norm and SwiGLU kernels
+        # can write themselves (one launch less in front of the QKV, gate/up and down projections)
+        act16 = rows > 16 and not ctx.prefill_exact and H % 64 == 0 and self.mlp_l % 64 == 0
+        if act16:
+            h16 = self._buf("h16", rows, H, dtype=torch.bfloat16)
+            a16 = self._buf("a16", rows, self.mlp_l, dtype=torch.bfloat16)
         fused = self.plan is not None and seq == 1
         if fused:
             # the whole step in one launch: layers, final norm, LM head, greedy token, position
@@ -234,8 +240,12 @@ class Int4Decoder:
         ctx.embedding_dev(self.embedding.data_ptr(), c.vocab, H, tokens.data_ptr(), rows, x.data_ptr())
         delta = 0
         for l in range(self.n_layers):
-            ctx.add_rms_norm_dev(x.data_ptr(), delta, self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
-            ctx.int4_matmul_dev(self.wqkv[l].handle, h.data_ptr(), qkv.data_ptr(), rows)
+            if act16:
+                ctx.add_rms_norm_act_dev(x.data_ptr(), delta, self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h16.data_ptr())
+                ctx.int4_matmul_act_dev(self.wqkv[l].handle, h16.data_ptr(), qkv.data_ptr(), rows)
+            else:
+                ctx.add_rms_norm_dev(x.data_ptr(), delta, self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
+                ctx.int4_matmul_dev(self.wqkv[l].handle, h.data_ptr(), qkv.data_ptr(), rows)
             if self.kv_int8:
                 ctx.rope_kv_append_i8_dev(qkv.data_ptr(), B, seq, self.nq_l, self.nkv_l, d, c.rope_theta,
                                           self.pos.data_ptr(), self.kcache[l].data_ptr(), self.kscale[l].data_ptr(),
@@ -251,10 +261,16 @@ class Int4Decoder:
                                       self.vcache[l].data_ptr(), self.max_seq, self.pos.data_ptr(), True, attn.data_ptr())
             ctx.int4_matmul_dev(self.wo[l].handle, attn.data_ptr(), o.data_ptr(), rows)
             self._all_reduce(o)
-            ctx.add_rms_norm_dev(x.data_ptr(), o.data_ptr(), self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
-            ctx.int4_matmul_dev(self.wgu[l].handle, h.data_ptr(), gu.data_ptr(), rows)
-            ctx.swiglu_dev(gu.data_ptr(), rows, self.mlp_l, act.data_ptr())
-            ctx.int4_matmul_dev(self.wdown[l].handle, act.data_ptr(), down.data_ptr(), rows)
+            if act16:
+                ctx.add_rms_norm_act_dev(x.data_ptr(), o.data_ptr(), self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h16.data_ptr())
+                ctx.int4_matmul_act_dev(self.wgu[l].handle, h16.data_ptr(), gu.data_ptr(), rows)
+                ctx.swiglu_act_dev(gu.data_ptr(), rows, self.mlp_l, a16.data_ptr())
+                ctx.int4_matmul_act_dev(self.wdown[l].handle, a16.data_ptr(), down.data_ptr(), rows)
+            else:
+                ctx.add_rms_norm_dev(x.data_ptr(), o.data_ptr(), self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())
+                ctx.int4_matmul_dev(self.wgu[l].handle, h.data_ptr(), gu.data_ptr(), rows)
+                ctx.swiglu_dev(gu.data_ptr(), rows, self.mlp_l, act.data_ptr())
+                ctx.int4_matmul_dev(self.wdown[l].handle, act.data_ptr(), down.data_ptr(), rows)
             self._all_reduce(down)
             delta = down.data_ptr()
         ctx.add_rms_norm_dev(x.data_ptr(), delta, self.gamma.data_ptr(), c.eps, rows, H, x.data_ptr(), h.data_ptr())

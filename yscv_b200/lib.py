@@ -56,6 +56,7 @@ SIGNATURES = {
     "yscv_cuda_int4_weight_wrap": (C.c_int, [_vp, _vp, _sz, _sz, _sz, C.POINTER(_vp)]),
     "yscv_cuda_int4_weight_free": (None, [_vp]),
     "yscv_cuda_int4_matmul_dev": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
+    "yscv_cuda_int4_matmul_act_dev": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
     "yscv_cuda_pack_int4_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _vp, _vp]),
     "yscv_cuda_int4_matmul_dev_static": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _vp, _sz]),
     "yscv_cuda_int8_matmul": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp]),
@@ -72,9 +73,11 @@ SIGNATURES = {
     "yscv_cuda_matmul_integer_dev": (C.c_int, [_vp, _vp, C.c_int, C.c_int32, _vp, _sz, _vp]),
     "yscv_cuda_embedding_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _sz, _vp]),
     "yscv_cuda_add_rms_norm_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_float, _sz, _sz, _vp, _vp]),
+    "yscv_cuda_add_rms_norm_act_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_float, _sz, _sz, _vp, _vp]),
     "yscv_cuda_rope_kv_append_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _vp, _vp, _vp, _sz]),
     "yscv_cuda_gqa_attention_dev": (C.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _sz, _vp, C.c_int, _vp]),
     "yscv_cuda_swiglu_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
+    "yscv_cuda_swiglu_act_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
     "yscv_cuda_f32_matmul_dev": (C.c_int, [_vp, _vp, _vp, _sz, _sz, _sz, _vp]),
     "yscv_cuda_argmax_last_dev": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
     "yscv_cuda_advance_pos_dev": (C.c_int, [_vp, _vp, C.c_int]),
@@ -456,6 +459,7 @@ class Context:
             _check(self.lib.yscv_cuda_ctx_create_on_stream(device, _vp(stream), C.byref(h)))
         self.handle = h.value
         self.device = device
+        self.prefill_exact = False   # mirrors yscv_cuda_ctx_set_int4_prefill_exact
 
     def close(self):
         if getattr(self, "handle", None):
@@ -486,6 +490,7 @@ class Context:
     def set_int4_prefill_exact(self, exact: bool):
         """m > 16 int4 matmuls: fp32-exact kernel (True) or bf16 tensor-core GEMM (False, default)."""
         _check(self.lib.yscv_cuda_ctx_set_int4_prefill_exact(self.handle, int(exact)))
+        self.prefill_exact = bool(exact)
 
     def set_int4_prefill_cta_pairs(self, on: bool):
         """bf16 prefill GEMM: allow the CTA-pair kernel (cta_group::2) for large prefills (default) or not."""
@@ -557,6 +562,11 @@ class Context:
     def int4_matmul_dev(self, w: Int4Weight, d_activation: int, d_output: int, m: int):
         _check(self.lib.yscv_cuda_int4_matmul_dev(self.handle, w.handle, _vp(d_activation),
                                                   _vp(d_output), m))
+
+    def int4_matmul_act_dev(self, w: Int4Weight, d_activation_bf16: int, d_output: int, m: int):
+        """int4_matmul_dev for m > 16 on activations already in the tensor-core GEMM's bf16 form."""
+        _check(self.lib.yscv_cuda_int4_matmul_act_dev(self.handle, w.handle, _vp(d_activation_bf16),
+                                                      _vp(d_output), m))
 
     def int4_matmul(self, w: Int4Weight, activation, m: int, out=None):
         """Resident weights, host activation [m,k] -> host output [m,n]."""
@@ -663,6 +673,11 @@ class Context:
         _check(self.lib.yscv_cuda_add_rms_norm_dev(self.handle, _vp(d_x), _vp(d_delta or 0), _vp(d_gamma), eps,
                                                    rows, hidden, _vp(d_x_out or 0), _vp(d_normed)))
 
+    def add_rms_norm_act_dev(self, d_x, d_delta, d_gamma, eps, rows, hidden, d_x_out, d_normed_act):
+        """add_rms_norm_dev with the normalised rows written as bf16 activations for int4_matmul_act_dev."""
+        _check(self.lib.yscv_cuda_add_rms_norm_act_dev(self.handle, _vp(d_x), _vp(d_delta or 0), _vp(d_gamma), eps,
+                                                       rows, hidden, _vp(d_x_out or 0), _vp(d_normed_act)))
+
     def rope_kv_append_dev(self, d_qkv, batch, seq, n_q, n_kv, d_head, theta, d_pos, d_kc, d_vc, max_seq):
         _check(self.lib.yscv_cuda_rope_kv_append_dev(self.handle, _vp(d_qkv), batch, seq, n_q, n_kv, d_head, theta,
                                                      _vp(d_pos), _vp(d_kc), _vp(d_vc), max_seq))
@@ -674,6 +689,10 @@ class Context:
 
     def swiglu_dev(self, d_gate_up, rows, inter, d_out):
         _check(self.lib.yscv_cuda_swiglu_dev(self.handle, _vp(d_gate_up), rows, inter, _vp(d_out)))
+
+    def swiglu_act_dev(self, d_gate_up, rows, inter, d_out_act):
+        """swiglu_dev with the result written as bf16 activations for int4_matmul_act_dev."""
+        _check(self.lib.yscv_cuda_swiglu_act_dev(self.handle, _vp(d_gate_up), rows, inter, _vp(d_out_act)))
 
     def f32_matmul_dev(self, d_w, d_x, m, n, k, d_out):
         _check(self.lib.yscv_cuda_f32_matmul_dev(self.handle, _vp(d_w), _vp(d_x), m, n, k, _vp(d_out)))
