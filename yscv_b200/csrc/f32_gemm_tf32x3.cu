@@ -33,13 +33,14 @@ constexpr int FT_SPLIT_WARPS = 4;
 constexpr int FT_EPI_WARPS = 8;  // two per TMEM lane quadrant: columns 0..63 and 64..127 of the accumulator
 constexpr int FT_THREADS = (2 + FT_SPLIT_WARPS + FT_EPI_WARPS) * 32;
 constexpr int FT_KC = 2;         // k blocks per accumulator chunk
+constexpr int FT_MIN_STAGES2 = 2; // ring stages needed to carry two blocks per stage
 constexpr int FT_BT_MAX = 128;   // batch rows per pass: 64 accumulator columns per epilogue thread
 constexpr int FT_W_BYTES = FT_BM * FT_BK * 4;   // 16 KB
 
 struct FTParams {
     int M, N, K;
     int BT;                 // batch rows per pass (multiple of 16, <= FT_BT_MAX)
-    int n_tiles, t_chunks, k_blocks;
+    int n_tiles, t_chunks, k_blocks;   // k_blocks counts ring stages (KSUB blocks of 32 k each)
     int stages, stage_bytes;
 };
 
@@ -105,6 +106,10 @@ __global__ void __launch_bounds__(256) ft_split_act_kernel(const float4 *__restr
     }
 }
 
+// KSUB = blocks of 32 k per ring stage and hand-over (split tile -> MMA -> buffer back): 2 whenever K
+// allows, a hand-over costs over a thousand cycles whatever it carries. A stage holds
+// [KSUB weight tiles][KSUB x_hi tiles][KSUB x_lo tiles], a remainder buffer KSUB tiles.
+template <int KSUB>
 __global__ void __launch_bounds__(FT_THREADS, 1)
 f32_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_xh,
                        const __grid_constant__ CUtensorMap tm_xl, float *__restrict__ out, FTParams p,
@@ -113,13 +118,15 @@ f32_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = smem_u32(smem);
     // [w_lo buffer 0][w_lo buffer 1][stages x {weight tile | x_hi tile | x_lo tile}][barriers][tmem slot]
+    constexpr int LO_BUF = KSUB * FT_W_BYTES;
+    constexpr int CHUNK_STAGES = FT_KC / KSUB;   // ring stages per accumulator chunk
     const uint32_t lo_tiles = smem_base;
-    const uint32_t ring = smem_base + 2 * FT_W_BYTES;
+    const uint32_t ring = smem_base + 2 * LO_BUF;
     const int x_bytes = p.BT * 128;
     const uint32_t bars = ring + (uint32_t)p.stages * p.stage_bytes;
     const uint32_t bar_full = bars, bar_empty = bars + 64, bar_afull = bars + 128, bar_aempty = bars + 144;
     const uint32_t bar_tfull = bars + 160, bar_tempty = bars + 176;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 2 * FT_W_BYTES + (size_t)p.stages * p.stage_bytes + 192);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 2 * LO_BUF + (size_t)p.stages * p.stage_bytes + 192);
     const int tiles = p.n_tiles * p.t_chunks;
 
     if (tid == 0) {
@@ -160,10 +167,14 @@ f32_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                     if (!alive) break;
                     const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
                     const uint32_t full = bar_full + slot * 8;
-                    mbar_expect_tx(full, (uint32_t)(FT_W_BYTES + 2 * x_bytes));
-                    tma_load_2d(st, &tm_w, kb * FT_BK, nt_i * FT_BM, full);
-                    tma_load_2d(st + FT_W_BYTES, &tm_xh, kb * FT_BK, tc * p.BT, full);
-                    tma_load_2d(st + FT_W_BYTES + x_bytes, &tm_xl, kb * FT_BK, tc * p.BT, full);
+                    mbar_expect_tx(full, (uint32_t)(KSUB * (FT_W_BYTES + 2 * x_bytes)));
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub) {
+                        const int kx = (kb * KSUB + sub) * FT_BK;
+                        tma_load_2d(st + sub * FT_W_BYTES, &tm_w, kx, nt_i * FT_BM, full);
+                        tma_load_2d(st + KSUB * FT_W_BYTES + sub * x_bytes, &tm_xh, kx, tc * p.BT, full);
+                        tma_load_2d(st + KSUB * FT_W_BYTES + (KSUB + sub) * x_bytes, &tm_xl, kx, tc * p.BT, full);
+                    }
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                 }
             }
@@ -179,7 +190,7 @@ f32_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             bool alive = true;
             for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    const bool chunk_start = kb % FT_KC == 0;
+                    const bool chunk_start = kb % CHUNK_STAGES == 0;
                     if (chunk_start) {
                         // the epilogue has drained this accumulator buffer
                         alive = mbar_wait(bar_tempty + tbuf * 8, tphase ^ 1u, status);
@@ -190,20 +201,25 @@ f32_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                     ft_fence_after();
                     const uint32_t tacc = tmem_base + (uint32_t)tbuf * FT_BT_MAX;
                     const uint32_t st = ring + (uint32_t)slot * p.stage_bytes;
-                    const uint64_t d_whi = ft_desc_sw128(st), d_wlo = ft_desc_sw128(lo_tiles + abuf * FT_W_BYTES);
-                    const uint64_t d_xhi = ft_desc_sw128(st + FT_W_BYTES), d_xlo = ft_desc_sw128(st + FT_W_BYTES + x_bytes);
 #pragma unroll
-                    for (int kk = 0; kk < FT_BK / 8; ++kk) {   // K = 8 per instruction: +32 bytes
-                        const uint64_t o = (uint64_t)(kk * 2);
-                        ft_mma_tf32(tacc, d_wlo + o, d_xhi + o, idesc, (!chunk_start || kk > 0) ? 1u : 0u);
-                        ft_mma_tf32(tacc, d_whi + o, d_xlo + o, idesc, 1u);
-                        ft_mma_tf32(tacc, d_whi + o, d_xhi + o, idesc, 1u);
+                    for (int sub = 0; sub < KSUB; ++sub) {
+                        const uint64_t d_whi = ft_desc_sw128(st + sub * FT_W_BYTES);
+                        const uint64_t d_wlo = ft_desc_sw128(lo_tiles + abuf * LO_BUF + sub * FT_W_BYTES);
+                        const uint64_t d_xhi = ft_desc_sw128(st + KSUB * FT_W_BYTES + sub * x_bytes);
+                        const uint64_t d_xlo = ft_desc_sw128(st + KSUB * FT_W_BYTES + (KSUB + sub) * x_bytes);
+#pragma unroll
+                        for (int kk = 0; kk < FT_BK / 8; ++kk) {   // K = 8 per instruction: +32 bytes
+                            const uint64_t o = (uint64_t)(kk * 2);
+                            ft_mma_tf32(tacc, d_wlo + o, d_xhi + o, idesc, (!chunk_start || sub > 0 || kk > 0) ? 1u : 0u);
+                            ft_mma_tf32(tacc, d_whi + o, d_xlo + o, idesc, 1u);
+                            ft_mma_tf32(tacc, d_whi + o, d_xhi + o, idesc, 1u);
+                        }
                     }
                     ft_commit(bar_empty + slot * 8);
                     ft_commit(bar_aempty + abuf * 8);
                     if (++slot == p.stages) { slot = 0; phase ^= 1u; }
                     if (++abuf == 2) { abuf = 0; aphase ^= 1u; }
-                    if (kb % FT_KC == FT_KC - 1 || kb == p.k_blocks - 1) {
+                    if (kb % CHUNK_STAGES == CHUNK_STAGES - 1 || kb == p.k_blocks - 1) {
                         ft_commit(bar_tfull + tbuf * 8);   // chunk complete
                         if (++tbuf == 2) { tbuf = 0; tphase ^= 1u; }
                     }
@@ -221,21 +237,24 @@ f32_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 alive = mbar_wait(bar_full + slot * 8, phase, status) &&
                         mbar_wait(bar_aempty + abuf * 8, aphase ^ 1u, status);
                 if (!alive) break;
-                unsigned char *wrow = smem + 2 * FT_W_BYTES + (size_t)slot * p.stage_bytes + (size_t)r * 128;
-                unsigned char *lrow = smem + (size_t)abuf * FT_W_BYTES + (size_t)r * 128;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    // an element-wise pass: the pieces of a row in an order that spreads a quarter warp over all banks
-                    const int off = ((c + r) & 7) << 4;
-                    const uint4 v = *reinterpret_cast<const uint4 *>(wrow + off);
-                    uint4 h, l;
-                    h.x = v.x & FT_HI_MASK; h.y = v.y & FT_HI_MASK; h.z = v.z & FT_HI_MASK; h.w = v.w & FT_HI_MASK;
-                    l.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(h.x));
-                    l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y));
-                    l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z));
-                    l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w));
-                    *reinterpret_cast<uint4 *>(wrow + off) = h;
-                    *reinterpret_cast<uint4 *>(lrow + off) = l;
+                for (int sub = 0; sub < KSUB; ++sub) {
+                    unsigned char *wrow = smem + 2 * LO_BUF + (size_t)slot * p.stage_bytes + (size_t)sub * FT_W_BYTES + (size_t)r * 128;
+                    unsigned char *lrow = smem + (size_t)abuf * LO_BUF + (size_t)sub * FT_W_BYTES + (size_t)r * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        // an element-wise pass: the pieces of a row in an order that spreads a quarter warp over all banks
+                        const int off = ((c + r) & 7) << 4;
+                        const uint4 v = *reinterpret_cast<const uint4 *>(wrow + off);
+                        uint4 h, l;
+                        h.x = v.x & FT_HI_MASK; h.y = v.y & FT_HI_MASK; h.z = v.z & FT_HI_MASK; h.w = v.w & FT_HI_MASK;
+                        l.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(h.x));
+                        l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y));
+                        l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z));
+                        l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w));
+                        *reinterpret_cast<uint4 *>(wrow + off) = h;
+                        *reinterpret_cast<uint4 *>(lrow + off) = l;
+                    }
                 }
                 // make the generic-proxy writes visible to the tensor core's async proxy
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -249,7 +268,7 @@ f32_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         // ---------------- epilogue: eight warps, TMEM lanes 32*(warp%4).., columns 64*half.. ----------------
         const int q = warp & 3, half = (warp - 2 - FT_SPLIT_WARPS) >> 2;
         const int col_base = half * 64;
-        const int n_chunks = (p.k_blocks + FT_KC - 1) / FT_KC;
+        const int n_chunks = (p.k_blocks + CHUNK_STAGES - 1) / CHUNK_STAGES;
         int tbuf = 0;
         uint32_t tphase = 0;
         bool alive = true;
@@ -321,11 +340,16 @@ int f32_gemm_tc(yscv_cuda_ctx *ctx, const float *d_w, const float *d_x, size_t m
     p.BT = m16 <= FT_BT_MAX ? m16 : FT_BT_MAX;
     p.n_tiles = (p.N + FT_BM - 1) / FT_BM;
     p.t_chunks = (p.M + p.BT - 1) / p.BT;
-    p.k_blocks = p.K / FT_BK;
-    p.stage_bytes = ((FT_W_BYTES + 2 * p.BT * 128 + 1023) / 1024) * 1024;
-    p.stages = (227 * 1024 - 2 * FT_W_BYTES - 1024) / p.stage_bytes;
+    // two blocks per stage and hand-over when K allows and the ring still has at least two such stages
+    int ksub = p.K % (2 * FT_BK) == 0 ? 2 : 1;
+    for (;; ksub = 1) {
+        p.stage_bytes = ((ksub * (FT_W_BYTES + 2 * p.BT * 128) + 1023) / 1024) * 1024;
+        p.stages = (227 * 1024 - 2 * ksub * FT_W_BYTES - 1024) / p.stage_bytes;
+        if (p.stages >= FT_MIN_STAGES2 || ksub == 1) break;
+    }
+    p.k_blocks = p.K / (FT_BK * ksub);
     if (p.stages > 8) p.stages = 8;
-    const int smem = 2 * FT_W_BYTES + p.stages * p.stage_bytes + 256;
+    const int smem = 2 * ksub * FT_W_BYTES + p.stages * p.stage_bytes + 256;
 
     float *x_hi = reinterpret_cast<float *>(scratch), *x_lo = x_hi + m * k;
     const size_t n4 = m * k / 4;
@@ -342,12 +366,13 @@ int f32_gemm_tc(yscv_cuda_ctx *ctx, const float *d_w, const float *d_x, size_t m
     if (rc) return rc;
     rc = encode_2d(&tm_xl, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x_lo, m, k, k * 4, (uint32_t)p.BT, FT_BK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = ensure_dynamic_smem(reinterpret_cast<const void *>(f32_gemm_tf32x3_kernel), ctx->device, 227 * 1024);
+    auto kern = ksub == 2 ? f32_gemm_tf32x3_kernel<2> : f32_gemm_tf32x3_kernel<1>;
+    rc = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), ctx->device, 227 * 1024);
     if (rc) return rc;
     const int tiles = p.n_tiles * p.t_chunks;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    YSCV_CUDA_TRY(launch_pdl(f32_gemm_tf32x3_kernel, dim3(grid), dim3(FT_THREADS), (size_t)smem, ctx->stream, tm_w, tm_xh,
-                             tm_xl, d_out, p, ctx->d_status));
+    YSCV_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(FT_THREADS), (size_t)smem, ctx->stream, tm_w, tm_xh, tm_xl, d_out, p,
+                             ctx->d_status));
     ctx->launches++;
     return YSCV_CUDA_OK;
 }
